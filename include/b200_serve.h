@@ -1,0 +1,204 @@
+/*
+ * b200_serve.h -- C ABI of the sm_100a KernelIR backend (libb200serve.so).
+ *
+ * Every entry point replaces one kernel wrapper (or one PyTorch fallback op) of
+ * StatefulLLM-Compiler's GPU executor; the reference symbol each one stands in
+ * for is cited as  <file>:<lines>  relative to the reference project root
+ * (src/stateful_llm_compiler/...).
+ *
+ * Conventions
+ *  - All pointers are DEVICE pointers unless the name ends in _host.
+ *  - Dimensions and strides are int64; strides are in ELEMENTS.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ *  - The library never allocates, frees or synchronises: the caller owns every
+ *    buffer, workspaces included. Calls are therefore legal inside CUDA graph
+ *    capture (the one exception is documented on the entry point itself).
+ *  - Return value: 0 on success, a negative B200_ERR_* code when the request is
+ *    rejected on the host (nothing was launched).
+ *  - Errors that only the device can see (a KV position past the capacity, a
+ *    token id outside the vocabulary, a length above the mask length) never
+ *    trap: the kernel skips / clamps the access and ORs a B200_STATUS_* bit into
+ *    the caller's int32 status word, which the host reads at a step boundary.
+ */
+#ifndef B200_SERVE_H_
+#define B200_SERVE_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types */
+#define B200_F32 0
+#define B200_BF16 1
+
+/* numerical modes: lowering.py:24-37 (_NUMERICAL_LOWERINGS) */
+#define B200_MODE_FAST 0
+#define B200_MODE_PYTORCH_COMPATIBLE 1
+
+/* host-side rejections */
+#define B200_OK 0
+#define B200_ERR_BAD_ARGUMENT (-1)  /* null pointer, negative size, bad enum          */
+#define B200_ERR_UNSUPPORTED (-2)   /* dtype / head_dim / stride the kernels do not do */
+#define B200_ERR_ALIGNMENT (-3)     /* a pointer or stride breaks the 16-byte rule      */
+#define B200_ERR_WORKSPACE (-4)     /* workspace missing or too small                  */
+#define B200_ERR_LAUNCH (-5)        /* cudaLaunch / cudaGetLastError reported an error */
+#define B200_ERR_TOO_LARGE (-6)     /* beyond a documented fixed maximum               */
+
+/* device-side status bits (OR-ed into *status) */
+#define B200_STATUS_KV_OVERFLOW 1       /* position + tokens > capacity: write skipped    */
+#define B200_STATUS_LENGTH_OVER_MASK 2  /* lengths[b] > mask length: clamped              */
+#define B200_STATUS_BAD_TOKEN_ID 4      /* embedding id outside [0, vocab): row zeroed    */
+#define B200_STATUS_BAD_POSITION 8      /* negative KV position: write skipped            */
+
+/* Version / build probe. Returns 100 * major + minor of this ABI. */
+int b200_abi_version(void);
+/* Human-readable message for a B200_ERR_* code (static storage). */
+const char* b200_error_string(int code);
+
+/* ---- KV store --------------------------------------------------------------
+ * buf[b, positions[b] + t, h, :] = x[b, h, t, :] for K and V in one launch.
+ * Replaces triton_kv_store (backends/triton_kv.py:71-129); oracle native_kv_store
+ * (execution.py:1242-1280). key/value are B x Hkv x T x D with arbitrary element
+ * strides (they arrive as view+transpose); buffers are contiguous B x C x Hkv x D.
+ * Bit-exact copy. */
+int b200_kv_store(void* key_buffer, void* value_buffer, const void* key, const void* value,
+                  const int64_t* positions, int64_t batch, int64_t capacity, int64_t kv_heads,
+                  int64_t tokens, int64_t head_dim, const int64_t key_strides[4],
+                  const int64_t value_strides[4], int dtype, int32_t* status, void* stream);
+
+/* ---- RoPE --------------------------------------------------------------------
+ * Dual-output Qwen2 half rotation, y = r(r(x*cos) + r(rot(x)*sin)).
+ * Replaces triton_rope (backends/triton_rope.py:299-390); oracle
+ * ReferenceExecutor._serve_rope (execution.py:741-767). q: B x Hq x T x D, k: B x Hkv x T x D
+ * (strided, last dim contiguous), cos/sin: B x T x D. Outputs are contiguous
+ * B x H x T x D. Same rounding points in both numerical modes. */
+int b200_rope(const void* query, const void* key, const void* cosine, const void* sine,
+              void* query_out, void* key_out, int64_t batch, int64_t q_heads, int64_t kv_heads,
+              int64_t tokens, int64_t head_dim, const int64_t query_strides[4],
+              const int64_t key_strides[4], const int64_t cos_strides[3],
+              const int64_t sin_strides[3], int dtype, void* stream);
+
+/* Decode fusion of serve.rope + serve.kv.store (T == 1): rotates q into query_out
+ * (B x Hq x D contiguous), rotates k and writes it with v straight into the KV
+ * buffers at positions[b]. Same arithmetic as b200_rope followed by b200_kv_store
+ * (passes/kv_bufferize.py:175-200 orders them rope -> length -> store). */
+int b200_rope_kv_store(const void* query, const void* key, const void* value, const void* cosine,
+                       const void* sine, void* query_out, void* key_buffer, void* value_buffer,
+                       const int64_t* positions, int64_t batch, int64_t q_heads, int64_t kv_heads,
+                       int64_t head_dim, int64_t capacity, int64_t q_batch_stride,
+                       int64_t q_head_stride, int64_t k_batch_stride, int64_t k_head_stride,
+                       int64_t v_batch_stride, int64_t v_head_stride, int64_t cos_batch_stride,
+                       int dtype, int32_t* status, void* stream);
+
+/* cos/sin table from position ids: f = float(pos) * inv_freq, e = cat(f, f),
+ * cos = r(cos(e)), sin = r(sin(e)). Replaces the unlowered aten.to/unsqueeze/mul/cat/
+ * cos/sin chain of Qwen2RotaryEmbedding.forward (qwen2.py:136-149). rows = B*T,
+ * outputs rows x (2*half_dim). */
+int b200_rope_table(const int64_t* position_ids, const float* inv_freq, void* cosine, void* sine,
+                    int64_t rows, int64_t half_dim, int out_dtype, void* stream);
+
+/* ---- RMSNorm -----------------------------------------------------------------
+ * Replaces triton_rms_norm (backends/triton_rmsnorm.py:205-443) and the
+ * kernel.cuda.rms_norm composite (backends/triton_executor.py:149-157); oracle
+ * ReferenceExecutor._serve_rms_norm (execution.py:674-692).
+ * round_before_weight != 0: y = r(w * r(x * rsqrt(mean(x^2) + eps)));
+ * otherwise y = r(x * rsqrt(..) * float(w)).
+ * mode FAST sums x^2 in a tree; mode PYTORCH_COMPATIBLE reproduces the summation
+ * order of the CPU executor's float sum (16 vector lanes x 4 interleaved
+ * accumulators, cascaded) with IEEE sqrt and divide, so the result is bit-identical
+ * to the reference's CPU executor. */
+int b200_rms_norm(const void* input, const void* weight, void* output, int64_t rows,
+                  int64_t hidden, int64_t input_row_stride, double epsilon,
+                  int round_before_weight, int in_dtype, int weight_dtype, int out_dtype,
+                  int mode, void* stream);
+
+/* ---- Decode attention --------------------------------------------------------
+ * One-token GQA attention over the physical B x C x Hkv x D buffers with
+ * per-sequence device lengths; split-KV online softmax.
+ * Replaces triton_decode_attention (backends/triton_attention.py:134-210); oracle
+ * PreallocatedKVCacheState.decode_attention (execution.py:281-327).
+ *  query   B x Hq x 1 x D, strides (q_batch_stride, q_head_stride), last dim contiguous
+ *  mask    B x 1 x 1 x mask_len additive, dtype mask_dtype, or NULL for "all zero"
+ *  output  B x Hq x D contiguous (viewed by the caller as B x Hq x 1 x D)
+ *  split_tokens  tokens per split (0 = library default); max_length_hint: an upper
+ *                bound on lengths[] known to the host (0 = mask_len / capacity).
+ * Workspace: b200_decode_attention_workspace_bytes(...) bytes, 256-byte aligned. */
+int64_t b200_decode_attention_workspace_bytes(int64_t batch, int64_t q_heads, int64_t kv_heads,
+                                              int64_t head_dim, int64_t max_length,
+                                              int64_t split_tokens);
+int b200_decode_attention(const void* query, const void* key_buffer, const void* value_buffer,
+                          const int64_t* lengths, const void* mask, void* output, int64_t batch,
+                          int64_t q_heads, int64_t kv_heads, int64_t head_dim, int64_t capacity,
+                          int64_t mask_len, int64_t q_batch_stride, int64_t q_head_stride,
+                          int64_t mask_batch_stride, int mask_dtype, double scale, int dtype,
+                          int mode, int64_t split_tokens, int64_t max_length_hint,
+                          void* workspace, int64_t workspace_bytes, int32_t* status,
+                          void* stream);
+
+/* ---- Prefill attention -------------------------------------------------------
+ * T-token GQA attention with an arbitrary additive B x 1 x T x T mask, or with
+ * proven causality (causal != 0: mask may be NULL and fully masked tiles are skipped).
+ * Replaces triton_prefill_attention (backends/triton_prefill_attention.py:152-232);
+ * oracle ReferenceExecutor._serve_prefill_attention (execution.py:707-739).
+ * q: B x Hq x T x D, k/v: B x Hkv x T x D strided (last dim contiguous);
+ * output memory is B x T x Hq x D contiguous (the caller views it as B x Hq x T x D). */
+int b200_prefill_attention(const void* query, const void* key, const void* value,
+                           const void* mask, void* output, int64_t batch, int64_t q_heads,
+                           int64_t kv_heads, int64_t tokens, int64_t head_dim,
+                           const int64_t query_strides[4], const int64_t key_strides[4],
+                           const int64_t value_strides[4], const int64_t mask_strides[4],
+                           int mask_dtype, double scale, int causal, int dtype, int mode,
+                           void* stream);
+
+/* ---- Linear ------------------------------------------------------------------
+ * y[M,N] = x[M,K] * W[N,K]^T (+ bias[N]) with fp32 accumulation and an optional
+ * fused epilogue. Replaces triton_linear (backends/triton_linear.py:87-148) and the
+ * kernel.cublas.linear call (backends/triton_executor.py:159-176); oracle F.linear
+ * (execution.py:694-705).
+ * epilogue: 0 none; 1 residual add, y = r(r(acc + bias) + residual) (the unlowered
+ * aten.add.Tensor that follows o_proj / down_proj, qwen2.py:299-304); 2 SwiGLU over
+ * row-interleaved gate/up weights: W holds 2N rows (gate_j, up_j alternating) and
+ * y[M,N] = r(r(silu(r(gate))) * r(up)) (qwen2.py:262-264).
+ * Workspace (split-K partial sums + tile counters): b200_linear_workspace_bytes. */
+#define B200_EPILOGUE_NONE 0
+#define B200_EPILOGUE_RESIDUAL 1
+#define B200_EPILOGUE_SWIGLU 2
+int64_t b200_linear_workspace_bytes(int64_t m, int64_t k, int64_t n, int dtype, int epilogue);
+int b200_linear(const void* input, const void* weight, const void* bias, const void* residual,
+                void* output, int64_t m, int64_t k, int64_t n, int64_t input_row_stride,
+                int dtype, int epilogue, void* workspace, int64_t workspace_bytes,
+                void* stream);
+
+/* ---- Ops the reference leaves to PyTorch eager (execution.py:500-528) ---------- */
+/* aten.embedding.default: out[r,:] = table[ids[r],:]. */
+int b200_embedding(const void* table, const int64_t* ids, void* output, int64_t rows,
+                   int64_t hidden, int64_t vocab, int dtype, int32_t* status, void* stream);
+/* aten.silu.default + aten.mul.Tensor: out = r(r(silu(gate)) * up) (qwen2.py:262-264). */
+int b200_swiglu(const void* gate, const void* up, void* output, int64_t count, int dtype,
+                void* stream);
+/* aten.add.Tensor on same-shape contiguous tensors: out = r(a + b) (qwen2.py:299-304). */
+int b200_add(const void* a, const void* b, void* output, int64_t count, int dtype, void* stream);
+/* aten.contiguous.default / aten.to.dtype on a strided 4-D tensor: dense copy with
+ * optional f32 <-> bf16 conversion. */
+int b200_copy_4d(const void* input, void* output, const int64_t sizes[4],
+                 const int64_t input_strides[4], int in_dtype, int out_dtype, void* stream);
+
+/* ---- Runtime KV helpers --------------------------------------------------------
+ * runtime.kv.advance (execution.py:421-443): lengths[b] += delta, in place so that
+ * replayed CUDA graphs see fixed addresses; a length that would pass `capacity` is
+ * clamped and B200_STATUS_KV_OVERFLOW is raised instead of the reference's device
+ * assert (execution.py:1283-1293). `slots` length vectors of `batch` entries,
+ * contiguous (slots x batch). */
+int b200_advance_lengths(int64_t* lengths, int64_t slots, int64_t batch, int64_t delta,
+                         int64_t capacity, int32_t* status, void* stream);
+/* Greedy sampling: ids[r] = argmax(logits[r, :]) (lowest index wins ties), the step
+ * the reference's callers do with torch.argmax (benchmarks/validate_qwen2_checkpoint.py:365-396). */
+int b200_argmax(const void* logits, int64_t* ids, int64_t rows, int64_t vocab,
+                int64_t row_stride, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_SERVE_H_ */

@@ -1,0 +1,252 @@
+"""Qwen2 serving engine: stateful prefill -> greedy decode on the sm_100a kernels, with the
+decode step captured in a CUDA graph over fixed KV / length / token buffer addresses.
+
+This is the fused form of the per-layer KernelIR sequence the reference interprets op by
+op (backends/triton_executor.py:69-130): per decode layer
+
+    rms_norm -> linear(q|k|v fused, +bias) -> rope + kv.store (one launch)
+             -> decode_attention -> linear(o) + residual (epilogue)
+    rms_norm -> linear(gate|up interleaved) + SwiGLU (epilogue) -> linear(down) + residual
+
+Every rounding point of the reference graph is kept (each linear result is rounded to the
+model dtype before its bias-free residual add, SwiGLU rounds silu(gate) then the product),
+so the fusions change launch counts, not numerics. One replica lives on one GPU; batch
+partitioning across GPUs is in serving.py.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from . import kernels
+from .kv_state import ExecutionError, PreallocatedKVCacheState
+from .qwen2 import Qwen2Config, inverse_frequency
+
+
+class Qwen2Engine:
+    def __init__(self, config: Qwen2Config, weights: Dict[str, torch.Tensor], *, batch: int,
+                 capacity: int, numerical_mode: str = "fast",
+                 device: Optional[torch.device] = None) -> None:
+        if numerical_mode not in ("fast", "pytorch_compatible"):
+            raise ValueError(f"unknown numerical mode {numerical_mode!r}")
+        self.config = config
+        self.batch = batch
+        self.capacity = capacity
+        self.mode = numerical_mode
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.dtype = weights["embed_tokens.weight"].dtype
+        self.scale = config.head_dim ** -0.5
+        self._pack_weights(weights)
+        self.inv_freq = inverse_frequency(config, self.device)
+
+        layers = config.num_layers
+        # length arena rows: [0, L) per-slot lengths, L = positions, L + 1 = attention lengths
+        self.state = PreallocatedKVCacheState.allocate(
+            num_layers=layers, batch=batch, capacity=capacity, kv_heads=config.num_kv_heads,
+            head_dim=config.head_dim, dtype=self.dtype, device=self.device, extra_length_rows=2)
+        arena = self.state._length_arena
+        self.positions = arena[layers]
+        self.attention_lengths = arena[layers + 1]
+        self.input_ids = torch.zeros(batch, dtype=torch.int64, device=self.device)
+        self.next_ids = torch.zeros(batch, dtype=torch.int64, device=self.device)
+        self.logits: Optional[torch.Tensor] = None
+        self._graph: Optional[torch.cuda.CUDAGraph] = None
+        self._host_ids = torch.zeros(batch, dtype=torch.int64).pin_memory()
+        self._host_tokens = torch.zeros(batch, dtype=torch.int64).pin_memory()
+        self.max_length_hint = 0  # host-known upper bound of the context (0 = capacity)
+        self.split_tokens = 0
+        self.kernels_per_step = 0
+
+    # ------------------------------------------------------------------ weights ----
+    def _pack_weights(self, weights: Dict[str, torch.Tensor]) -> None:
+        cfg = self.config
+        for name, tensor in weights.items():
+            if not tensor.is_cuda:
+                raise ValueError(f"weight {name} is not on a CUDA device")
+        self.embed = weights["embed_tokens.weight"]
+        self.lm_head = weights["lm_head.weight"]
+        self.final_norm = weights["decoder.norm.weight"]
+        self.layers = []
+        for index in range(cfg.num_layers):
+            p = f"decoder.layers.{index}."
+            qkv_w = torch.cat([weights[p + "self_attn.q_proj.weight"],
+                               weights[p + "self_attn.k_proj.weight"],
+                               weights[p + "self_attn.v_proj.weight"]], dim=0).contiguous()
+            qkv_b = torch.cat([weights[p + "self_attn.q_proj.bias"],
+                               weights[p + "self_attn.k_proj.bias"],
+                               weights[p + "self_attn.v_proj.bias"]], dim=0).contiguous()
+            gate_up = kernels.interleave_gate_up(weights[p + "mlp.gate_proj.weight"],
+                                                 weights[p + "mlp.up_proj.weight"])
+            self.layers.append({
+                "input_norm": weights[p + "input_layernorm.weight"],
+                "post_norm": weights[p + "post_attention_layernorm.weight"],
+                "qkv_w": qkv_w, "qkv_b": qkv_b,
+                "o_w": weights[p + "self_attn.o_proj.weight"],
+                "gate_up_w": gate_up,
+                "down_w": weights[p + "mlp.down_proj.weight"],
+            })
+
+    # ------------------------------------------------------------------ prefill ----
+    def prefill(self, input_ids: torch.Tensor, *, all_logits: bool = False) -> torch.Tensor:
+        """Stateful prefill of a B x T prompt from an empty state. Returns logits for the last
+        position (B x V) or, with all_logits=True, for every position (B x T x V) as the
+        reference graph does (qwen2.py:418-424). Also primes the greedy next token."""
+
+        cfg = self.config
+        if input_ids.shape[0] != self.batch or input_ids.ndim != 2:
+            raise ValueError("prompt must be batch x tokens")
+        batch, tokens = input_ids.shape
+        if tokens > self.capacity:
+            raise ExecutionError(f"prompt of {tokens} tokens exceeds capacity {self.capacity}")
+        ids = input_ids.to(self.device)
+        self.state._length_arena.zero_()
+        position_ids = torch.arange(tokens, dtype=torch.int64, device=self.device).repeat(batch, 1)
+        x = kernels.b200_embedding(self.embed, ids)
+        cosine, sine = kernels.b200_rope_table(position_ids, self.inv_freq, self.dtype)
+        zeros = self.positions  # all zero right now
+        q_size, kv_size = cfg.q_size, cfg.kv_size
+        for index, layer in enumerate(self.layers):
+            h = kernels.b200_rms_norm(x, layer["input_norm"], epsilon=cfg.rms_norm_eps,
+                                      round_before_weight=True, numerical_mode=self.mode)
+            qkv = kernels.b200_linear(h, layer["qkv_w"], layer["qkv_b"])
+            q = qkv[..., :q_size].view(batch, tokens, cfg.num_heads, cfg.head_dim).transpose(1, 2)
+            k = qkv[..., q_size:q_size + kv_size].view(batch, tokens, cfg.num_kv_heads,
+                                                       cfg.head_dim).transpose(1, 2)
+            v = qkv[..., q_size + kv_size:].view(batch, tokens, cfg.num_kv_heads,
+                                                 cfg.head_dim).transpose(1, 2)
+            q, k = kernels.b200_rope(q, k, cosine, sine)
+            kernels.b200_kv_store(self.state.keys[index], self.state.values[index], k, v, zeros)
+            attn = kernels.b200_prefill_attention(q, k, v, None, scale=self.scale, causal=True,
+                                                  numerical_mode=self.mode)
+            attn = attn.transpose(1, 2).reshape(batch, tokens, q_size)  # a view: memory is B,T,H,D
+            x = kernels.b200_linear(attn, layer["o_w"], residual=x, epilogue="residual")
+            h = kernels.b200_rms_norm(x, layer["post_norm"], epsilon=cfg.rms_norm_eps,
+                                      round_before_weight=True, numerical_mode=self.mode)
+            a = kernels.b200_linear(h, layer["gate_up_w"], epilogue="swiglu")
+            x = kernels.b200_linear(a, layer["down_w"], residual=x, epilogue="residual")
+        if all_logits:
+            h = kernels.b200_rms_norm(x, self.final_norm, epsilon=cfg.rms_norm_eps,
+                                      round_before_weight=True, numerical_mode=self.mode)
+            logits = kernels.b200_linear(h, self.lm_head)
+            last = logits[:, -1]
+        else:
+            h = kernels.b200_rms_norm(x[:, -1], self.final_norm, epsilon=cfg.rms_norm_eps,
+                                      round_before_weight=True, numerical_mode=self.mode)
+            logits = kernels.b200_linear(h, self.lm_head)
+            last = logits
+        kernels.b200_argmax(last, self.next_ids)
+        self.input_ids.copy_(self.next_ids)
+        kernels.b200_advance_lengths(self.state._length_arena, tokens, self.capacity)
+        # attention lengths run one ahead of the positions: they include the token being decoded
+        kernels.b200_advance_lengths(self.attention_lengths, 1, self.capacity + 1)
+        self.logits = last
+        return logits
+
+    def load_context(self, lengths: torch.Tensor, *, next_ids: Optional[torch.Tensor] = None) -> None:
+        """Benchmark entry: declares that the KV buffers already hold `lengths[b]` tokens per
+        sequence (filled by the caller) and sets the next input token ids."""
+
+        lengths = lengths.to(device=self.device, dtype=torch.int64)
+        layers = self.config.num_layers
+        self.state._length_arena[:layers + 1].copy_(lengths.unsqueeze(0).expand(layers + 1, -1))
+        self.attention_lengths.copy_(lengths + 1)
+        if next_ids is not None:
+            self.input_ids.copy_(next_ids.to(self.device))
+
+    # ------------------------------------------------------------------- decode ----
+    def _decode_step(self) -> None:
+        cfg = self.config
+        batch = self.batch
+        before = kernels.launch_count(self.device)
+        x = kernels.b200_embedding(self.embed, self.input_ids)
+        cosine, sine = kernels.b200_rope_table(self.positions.view(batch, 1), self.inv_freq,
+                                               self.dtype)
+        q_size, kv_size = cfg.q_size, cfg.kv_size
+        for index, layer in enumerate(self.layers):
+            h = kernels.b200_rms_norm(x, layer["input_norm"], epsilon=cfg.rms_norm_eps,
+                                      round_before_weight=True, numerical_mode=self.mode)
+            qkv = kernels.b200_linear(h, layer["qkv_w"], layer["qkv_b"])
+            q = qkv[:, :q_size].view(batch, cfg.num_heads, cfg.head_dim)
+            k = qkv[:, q_size:q_size + kv_size].view(batch, cfg.num_kv_heads, cfg.head_dim)
+            v = qkv[:, q_size + kv_size:].view(batch, cfg.num_kv_heads, cfg.head_dim)
+            q = kernels.b200_rope_kv_store(q, k, v, cosine, sine, self.state.keys[index],
+                                           self.state.values[index], self.positions)
+            attn = kernels.b200_decode_attention(
+                q, self.state.keys[index], self.state.values[index], self.attention_lengths,
+                None, scale=self.scale, numerical_mode=self.mode,
+                split_tokens=self.split_tokens, max_length_hint=self.max_length_hint)
+            x = kernels.b200_linear(attn.view(batch, q_size), layer["o_w"], residual=x,
+                                    epilogue="residual")
+            h = kernels.b200_rms_norm(x, layer["post_norm"], epsilon=cfg.rms_norm_eps,
+                                      round_before_weight=True, numerical_mode=self.mode)
+            a = kernels.b200_linear(h, layer["gate_up_w"], epilogue="swiglu")
+            x = kernels.b200_linear(a, layer["down_w"], residual=x, epilogue="residual")
+        h = kernels.b200_rms_norm(x, self.final_norm, epsilon=cfg.rms_norm_eps,
+                                  round_before_weight=True, numerical_mode=self.mode)
+        self.logits = kernels.b200_linear(h, self.lm_head)
+        kernels.b200_argmax(self.logits, self.next_ids)
+        # all slot lengths, the positions row and the attention-length row move together
+        kernels.b200_advance_lengths(self.state._length_arena, 1, self.capacity + 1)
+        self.kernels_per_step = kernels.launch_count(self.device) - before
+
+    def capture(self) -> None:
+        """Captures one decode step in a CUDA graph. A warm-up step runs first so that every
+        workspace exists; lengths, positions and ids are restored afterwards (the KV row the
+        warm-up wrote lies beyond the valid length and is overwritten by the real step)."""
+
+        saved_lengths = self.state._length_arena.clone()
+        saved_ids = self.input_ids.clone()
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            self._decode_step()
+            self.state._length_arena.copy_(saved_lengths)
+            self.input_ids.copy_(saved_ids)
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._decode_step()
+        self._graph = graph
+        kernels.runtime(self.device).status.zero_()
+
+    def decode_step(self, *, feed_back: bool = True) -> torch.Tensor:
+        """One decode step for the whole batch on device-resident inputs. Returns the device
+        tensor of greedy tokens; with feed_back they become the next step's input ids."""
+
+        if self._graph is not None:
+            self._graph.replay()
+        else:
+            self._decode_step()
+        if feed_back:
+            self.input_ids.copy_(self.next_ids, non_blocking=True)
+        return self.next_ids
+
+    def step(self, host_ids: torch.Tensor) -> torch.Tensor:
+        """The call a serving loop makes: host token ids in, host greedy tokens out. Copies
+        the ids from pinned host memory, runs one decode step, copies the tokens back and
+        waits for them."""
+
+        self._host_ids.copy_(host_ids)
+        self.input_ids.copy_(self._host_ids, non_blocking=True)
+        self.decode_step(feed_back=False)
+        self._host_tokens.copy_(self.next_ids, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return self._host_tokens
+
+    def generate(self, prompt_ids: torch.Tensor, steps: int, *, use_graph: bool = True) -> torch.Tensor:
+        """Greedy generation: prefill then `steps` decode steps. Returns B x (steps + 1) token
+        ids (the token sampled from the prompt first)."""
+
+        self.prefill(prompt_ids)
+        history = torch.empty((steps + 1, self.batch), dtype=torch.int64, device=self.device)
+        history[0].copy_(self.next_ids)
+        if use_graph and self._graph is None and steps > 0:
+            self.capture()
+        for index in range(steps):
+            self.decode_step()
+            history[index + 1].copy_(self.next_ids)
+        self.state.check()
+        return history.transpose(0, 1).contiguous()

@@ -1,0 +1,660 @@
+"""Python wrappers over the C ABI, one per kernel wrapper of the reference backend.
+
+Names, argument order and error behaviour follow the reference's Triton wrappers
+(backends/__init__.py:3-19): precondition failures raise ValueError before anything is
+launched; outputs are allocated with torch.empty on the inputs' device; kernels launch on
+torch's current stream and never synchronise, so every call is legal under CUDA graph
+capture. PyTorch is used for memory and streams only: all arithmetic runs in
+libb200serve.so, and a missing library or a CPU tensor is an error, never a fallback.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+_DTYPE_CODES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+_MODES = {"fast": _lib.MODE_FAST, "pytorch_compatible": _lib.MODE_PYTORCH_COMPATIBLE}
+_EPILOGUES = {"none": _lib.EPILOGUE_NONE, "residual": _lib.EPILOGUE_RESIDUAL,
+              "swiglu": _lib.EPILOGUE_SWIGLU}
+
+
+class KernelStatusError(RuntimeError):
+    """A kernel flagged a device-side error (KV overflow, bad token id, ...)."""
+
+
+# --------------------------------------------------------------------------- runtime ----
+class DeviceRuntime:
+    """Per-device scratch owned by Python: the int32 status word and named workspaces.
+
+    Workspaces only grow; they are zero-filled when (re)allocated because the split-K
+    linear kernel keeps tile counters there that must start at zero (it leaves them at
+    zero after every call).
+    """
+
+    def __init__(self, device: torch.device) -> None:
+        self.device = device
+        self.status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._workspaces: dict[str, torch.Tensor] = {}
+        self.launches = 0
+
+    def workspace(self, name: str, nbytes: int) -> Optional[torch.Tensor]:
+        if nbytes <= 0:
+            return None
+        current = self._workspaces.get(name)
+        if current is None or current.numel() < nbytes:
+            current = torch.zeros(int(nbytes), dtype=torch.uint8, device=self.device)
+            self._workspaces[name] = current
+        return current
+
+    def reserve(self, name: str, nbytes: int) -> None:
+        """Pre-sizes a workspace (call before CUDA graph capture)."""
+
+        self.workspace(name, nbytes)
+
+    def check_status(self) -> None:
+        """Host read of the status word (synchronises); raises and clears on error."""
+
+        value = int(self.status.item())
+        if value == 0:
+            return
+        self.status.zero_()
+        reasons = []
+        if value & _lib.STATUS_KV_OVERFLOW:
+            reasons.append("KV position beyond capacity (write skipped / length clamped)")
+        if value & _lib.STATUS_LENGTH_OVER_MASK:
+            reasons.append("KV length above the attention mask length (clamped)")
+        if value & _lib.STATUS_BAD_TOKEN_ID:
+            reasons.append("token id outside the vocabulary (row zeroed)")
+        if value & _lib.STATUS_BAD_POSITION:
+            reasons.append("negative KV position (write skipped)")
+        raise KernelStatusError("; ".join(reasons) or f"status word {value}")
+
+
+_RUNTIMES: dict[int, DeviceRuntime] = {}
+
+
+def runtime(device: torch.device | None = None) -> DeviceRuntime:
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    found = _RUNTIMES.get(index)
+    if found is None:
+        found = DeviceRuntime(torch.device("cuda", index))
+        _RUNTIMES[index] = found
+    return found
+
+
+def launch_count(device: torch.device | None = None) -> int:
+    return runtime(device).launches
+
+
+# ------------------------------------------------------------------------- helpers ----
+def _require_cuda(*tensors: torch.Tensor) -> torch.device:
+    device = None
+    for tensor in tensors:
+        if tensor is None:
+            continue
+        if not isinstance(tensor, torch.Tensor) or not tensor.is_cuda:
+            raise ValueError("the B200 backend only runs CUDA tensors (there is no CPU fallback)")
+        if device is None:
+            device = tensor.device
+        elif tensor.device != device:
+            raise ValueError("all operands must live on the same CUDA device")
+    assert device is not None
+    return device
+
+
+def _code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODES[dtype]
+    except KeyError as error:
+        raise ValueError(f"unsupported dtype {dtype}: the B200 backend runs f32 and bf16") from error
+
+
+def _mode(numerical_mode: str) -> int:
+    try:
+        return _MODES[numerical_mode]
+    except KeyError as error:
+        raise ValueError(f"unknown numerical mode {numerical_mode!r}") from error
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    message = f"{what}: {_lib.error_string(code)}"
+    if code in (_lib.ERR_LAUNCH,):
+        raise RuntimeError(message)
+    raise ValueError(message)
+
+
+def _ptr(tensor: Optional[torch.Tensor]) -> Optional[int]:
+    return None if tensor is None else tensor.data_ptr()
+
+
+def _count(rt: DeviceRuntime, launches: int = 1) -> None:
+    rt.launches += launches
+
+
+def _dense(tensor: torch.Tensor) -> torch.Tensor:
+    """Contiguous version of a floating-point tensor, copied by this library's own kernel."""
+
+    if tensor.is_contiguous():
+        return tensor
+    return b200_contiguous(tensor)
+
+
+def _dense_index(tensor: torch.Tensor, what: str) -> torch.Tensor:
+    if not tensor.is_contiguous():
+        raise ValueError(f"{what} must be contiguous")
+    return tensor
+
+
+# ------------------------------------------------------------------------ KV store ----
+def b200_kv_store(key_buffer: torch.Tensor, value_buffer: torch.Tensor, key: torch.Tensor,
+                  value: torch.Tensor, positions: torch.Tensor) -> None:
+    """buf[b, positions[b]+t, h, :] = x[b, h, t, :] for K and V, in place, one launch.
+
+    Mirrors triton_kv_store (backends/triton_kv.py:71-129).
+    """
+
+    device = _require_cuda(key_buffer, value_buffer, key, value, positions)
+    if key_buffer.ndim != 4 or key_buffer.shape != value_buffer.shape:
+        raise ValueError("KV buffers must be B x C x H x D tensors of one shape")
+    if key.ndim != 4 or key.shape != value.shape:
+        raise ValueError("key/value must be B x H x T x D tensors of one shape")
+    batch, capacity, heads, dim = key_buffer.shape
+    if key.shape[0] != batch or key.shape[1] != heads or key.shape[3] != dim:
+        raise ValueError("key/value batch, heads or head_dim do not match the KV buffers")
+    if not key_buffer.is_contiguous() or not value_buffer.is_contiguous():
+        raise ValueError("KV buffers must be contiguous")
+    if len({key_buffer.dtype, value_buffer.dtype, key.dtype, value.dtype}) != 1:
+        raise ValueError("KV buffers and key/value must share one dtype")
+    if positions.shape != (batch,) or positions.dtype != torch.int64:
+        raise ValueError("positions must be a one-dimensional int64 batch tensor")
+    positions = _dense_index(positions, "positions")
+    rt = runtime(device)
+    tokens = key.shape[2]
+    code = _lib.load().b200_kv_store(
+        key_buffer.data_ptr(), value_buffer.data_ptr(), key.data_ptr(), value.data_ptr(),
+        positions.data_ptr(), batch, capacity, heads, tokens, dim,
+        _lib.i64_array(key.stride()), _lib.i64_array(value.stride()), _code(key.dtype),
+        rt.status.data_ptr(), _stream())
+    _check(code, "b200_kv_store")
+    _count(rt)
+
+
+# ---------------------------------------------------------------------------- RoPE ----
+def b200_rope(query: torch.Tensor, key: torch.Tensor, cosine: torch.Tensor,
+              sine: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Qwen2 half-rotation RoPE on Q and K in one launch; returns new contiguous tensors.
+
+    Mirrors triton_rope (backends/triton_rope.py:299-390).
+    """
+
+    device = _require_cuda(query, key, cosine, sine)
+    if query.ndim != 4 or key.ndim != 4:
+        raise ValueError("query/key must be B x H x T x D")
+    batch, q_heads, tokens, dim = query.shape
+    if key.shape[0] != batch or key.shape[2] != tokens or key.shape[3] != dim:
+        raise ValueError("query and key disagree on batch, tokens or head_dim")
+    if dim % 2:
+        raise ValueError("head_dim must be even")
+    if cosine.shape != (batch, tokens, dim) or sine.shape != (batch, tokens, dim):
+        raise ValueError("cosine/sine must be B x T x D")
+    if len({query.dtype, key.dtype, cosine.dtype, sine.dtype}) != 1:
+        raise ValueError("query, key, cosine and sine must share one dtype")
+    kv_heads = key.shape[1]
+    query_out = torch.empty((batch, q_heads, tokens, dim), dtype=query.dtype, device=device)
+    key_out = torch.empty((batch, kv_heads, tokens, dim), dtype=key.dtype, device=device)
+    rt = runtime(device)
+    code = _lib.load().b200_rope(
+        query.data_ptr(), key.data_ptr(), cosine.data_ptr(), sine.data_ptr(),
+        query_out.data_ptr(), key_out.data_ptr(), batch, q_heads, kv_heads, tokens, dim,
+        _lib.i64_array(query.stride()), _lib.i64_array(key.stride()),
+        _lib.i64_array(cosine.stride()), _lib.i64_array(sine.stride()), _code(query.dtype),
+        _stream())
+    _check(code, "b200_rope")
+    _count(rt)
+    return query_out, key_out
+
+
+def b200_rope_kv_store(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                       cosine: torch.Tensor, sine: torch.Tensor, key_buffer: torch.Tensor,
+                       value_buffer: torch.Tensor, positions: torch.Tensor,
+                       query_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode fusion (T == 1): rope(q) -> query_out, rope(k) and v -> KV buffers at positions.
+
+    query/key/value are B x H x 1 x D (or B x H x D) views with a contiguous last dim;
+    cosine/sine are B x 1 x D. Returns the rotated query, B x Hq x 1 x D contiguous.
+    """
+
+    device = _require_cuda(query, key, value, cosine, sine, key_buffer, value_buffer, positions)
+
+    def squeeze(tensor: torch.Tensor) -> torch.Tensor:
+        if tensor.ndim == 4:
+            if tensor.shape[2] != 1:
+                raise ValueError("the fused rope + store kernel handles one token per sequence")
+            return tensor[:, :, 0, :]
+        return tensor
+
+    q3, k3, v3 = squeeze(query), squeeze(key), squeeze(value)
+    batch, q_heads, dim = q3.shape
+    kv_heads = k3.shape[1]
+    if k3.shape != (batch, kv_heads, dim) or v3.shape != (batch, kv_heads, dim):
+        raise ValueError("key/value must be B x Hkv x D")
+    if key_buffer.shape != value_buffer.shape or key_buffer.shape[0] != batch or \
+            key_buffer.shape[2] != kv_heads or key_buffer.shape[3] != dim:
+        raise ValueError("KV buffers do not match key/value")
+    cos2 = cosine.reshape(batch, dim) if cosine.ndim == 3 else cosine
+    sin2 = sine.reshape(batch, dim) if sine.ndim == 3 else sine
+    if cos2.stride() != sin2.stride():
+        sin2 = _dense(sin2)
+        cos2 = _dense(cos2)
+    for tensor in (q3, k3, v3, cos2, sin2):
+        if tensor.stride(-1) != 1:
+            raise ValueError("last dimension must be contiguous")
+    if positions.shape != (batch,) or positions.dtype != torch.int64:
+        raise ValueError("positions must be a one-dimensional int64 batch tensor")
+    if query_out is None:
+        query_out = torch.empty((batch, q_heads, 1, dim), dtype=query.dtype, device=device)
+    rt = runtime(device)
+    code = _lib.load().b200_rope_kv_store(
+        q3.data_ptr(), k3.data_ptr(), v3.data_ptr(), cos2.data_ptr(), sin2.data_ptr(),
+        query_out.data_ptr(), key_buffer.data_ptr(), value_buffer.data_ptr(),
+        positions.data_ptr(), batch, q_heads, kv_heads, dim, key_buffer.shape[1],
+        q3.stride(0), q3.stride(1), k3.stride(0), k3.stride(1), v3.stride(0), v3.stride(1),
+        cos2.stride(0), _code(query.dtype), rt.status.data_ptr(), _stream())
+    _check(code, "b200_rope_kv_store")
+    _count(rt)
+    return query_out
+
+
+def b200_rope_table(position_ids: torch.Tensor, inv_freq: torch.Tensor,
+                    dtype: torch.dtype) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos/sin tables B x T x D from int64 position ids and fp32 inverse frequencies.
+
+    Replaces the eager to/unsqueeze/mul/cat/cos/sin chain of Qwen2RotaryEmbedding.forward
+    (qwen2.py:136-149).
+    """
+
+    device = _require_cuda(position_ids, inv_freq)
+    if position_ids.dtype != torch.int64 or position_ids.ndim != 2:
+        raise ValueError("position_ids must be a B x T int64 tensor")
+    if inv_freq.dtype != torch.float32 or inv_freq.ndim != 1:
+        raise ValueError("inv_freq must be a one-dimensional fp32 tensor")
+    position_ids = _dense_index(position_ids, "position_ids")
+    inv_freq = _dense(inv_freq)
+    batch, tokens = position_ids.shape
+    half = inv_freq.shape[0]
+    cosine = torch.empty((batch, tokens, 2 * half), dtype=dtype, device=device)
+    sine = torch.empty_like(cosine)
+    rt = runtime(device)
+    code = _lib.load().b200_rope_table(position_ids.data_ptr(), inv_freq.data_ptr(),
+                                       cosine.data_ptr(), sine.data_ptr(), batch * tokens, half,
+                                       _code(dtype), _stream())
+    _check(code, "b200_rope_table")
+    _count(rt)
+    return cosine, sine
+
+
+# ------------------------------------------------------------------------- RMSNorm ----
+def b200_rms_norm(tensor: torch.Tensor, weight: torch.Tensor, *, epsilon: float,
+                  output_dtype=None, round_before_weight: bool = False,
+                  numerical_mode: str = "fast") -> torch.Tensor:
+    """RMSNorm over the last dimension. Mirrors triton_rms_norm
+    (backends/triton_rmsnorm.py:205-443); `pytorch_compatible` reproduces the CPU
+    executor's result bit for bit (execution.py:686-692)."""
+
+    device = _require_cuda(tensor, weight)
+    hidden = tensor.shape[-1]
+    if weight.shape != (hidden,):
+        raise ValueError("weight must be a vector of the hidden size")
+    out_dtype = _resolve_dtype(output_dtype, tensor.dtype)
+    if not (tensor.dtype == weight.dtype == out_dtype):
+        raise ValueError("input, weight and output dtype must agree")
+    if tensor.is_contiguous():
+        source, row_stride = tensor, hidden
+    elif tensor.ndim == 2 and tensor.stride(1) == 1 and tensor.stride(0) >= hidden:
+        source, row_stride = tensor, tensor.stride(0)
+    else:
+        source, row_stride = _dense(tensor), hidden
+    rows = source.numel() // hidden if hidden else 0
+    weight = _dense(weight)
+    output = torch.empty(tensor.shape, dtype=out_dtype, device=device)
+    rt = runtime(device)
+    code = _lib.load().b200_rms_norm(
+        source.data_ptr(), weight.data_ptr(), output.data_ptr(), rows, hidden, row_stride,
+        float(epsilon), int(bool(round_before_weight)), _code(tensor.dtype), _code(weight.dtype),
+        _code(out_dtype), _mode(numerical_mode), _stream())
+    _check(code, "b200_rms_norm")
+    _count(rt)
+    return output
+
+
+def _resolve_dtype(value, default: torch.dtype) -> torch.dtype:
+    if value is None:
+        return default
+    if isinstance(value, torch.dtype):
+        return value
+    names = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}
+    if value not in names:
+        raise ValueError(f"unsupported output dtype {value!r}")
+    return names[value]
+
+
+# ---------------------------------------------------------------- decode attention ----
+def decode_attention_workspace_bytes(batch: int, q_heads: int, kv_heads: int, head_dim: int,
+                                     max_length: int, split_tokens: int = 0) -> int:
+    return int(_lib.load().b200_decode_attention_workspace_bytes(
+        batch, q_heads, kv_heads, head_dim, max_length, split_tokens))
+
+
+def b200_decode_attention(query: torch.Tensor, key_buffer: torch.Tensor,
+                          value_buffer: torch.Tensor, lengths: torch.Tensor,
+                          attention_mask: Optional[torch.Tensor], *, scale: float,
+                          numerical_mode: str = "fast", split_tokens: int = 0,
+                          max_length_hint: int = 0,
+                          output: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One-token GQA attention over the physical KV buffers. Mirrors
+    triton_decode_attention (backends/triton_attention.py:134-210).
+
+    attention_mask is B x 1 x 1 x S additive (S <= capacity) or None for an all-zero mask
+    of length `capacity`. Returns B x Hq x 1 x D (memory order B, Hq, D).
+    """
+
+    device = _require_cuda(query, key_buffer, value_buffer, lengths, attention_mask)
+    if query.ndim != 4 or query.shape[2] != 1:
+        raise ValueError("query must be B x H x 1 x D")
+    if key_buffer.ndim != 4 or key_buffer.shape != value_buffer.shape:
+        raise ValueError("KV buffers must be B x C x H x D tensors of one shape")
+    batch, q_heads, _, dim = query.shape
+    _, capacity, kv_heads, buffer_dim = key_buffer.shape
+    if key_buffer.shape[0] != batch or buffer_dim != dim:
+        raise ValueError("query batch or head_dim does not match the KV buffers")
+    if kv_heads <= 0 or q_heads % kv_heads:
+        raise ValueError("query heads must be a multiple of KV heads")
+    if not key_buffer.is_contiguous() or not value_buffer.is_contiguous():
+        raise ValueError("KV buffers must be contiguous")
+    if lengths.shape != (batch,) or lengths.dtype != torch.int64:
+        raise ValueError("lengths must be a one-dimensional int64 batch tensor")
+    if not (query.dtype == key_buffer.dtype == value_buffer.dtype):
+        raise ValueError("query and KV buffers must share one dtype")
+    if query.stride(3) != 1:
+        query = _dense(query)
+    mask_len, mask_stride, mask_code = capacity, 0, _lib.F32
+    if attention_mask is not None:
+        if attention_mask.ndim != 4 or attention_mask.shape[1] != 1 or \
+                attention_mask.shape[2] != 1 or attention_mask.shape[0] != batch:
+            raise ValueError("attention_mask must be B x 1 x 1 x S")
+        mask_len = attention_mask.shape[3]
+        if mask_len > capacity or mask_len <= 0:
+            raise ValueError("mask length must be in [1, capacity]")
+        if attention_mask.stride(3) != 1:
+            attention_mask = _dense(attention_mask)
+        mask_stride = attention_mask.stride(0)
+        mask_code = _code(attention_mask.dtype)
+    lengths = _dense_index(lengths, "lengths")
+    if output is None:
+        output = torch.empty((batch, q_heads, 1, dim), dtype=query.dtype, device=device)
+    rt = runtime(device)
+    library = _lib.load()
+    max_length = min(max_length_hint, mask_len) if max_length_hint > 0 else mask_len
+    need = 0
+    if query.dtype == torch.bfloat16:
+        need = int(library.b200_decode_attention_workspace_bytes(
+            batch, q_heads, kv_heads, dim, max_length, split_tokens))
+    workspace = rt.workspace("decode_attention", need)
+    code = library.b200_decode_attention(
+        query.data_ptr(), key_buffer.data_ptr(), value_buffer.data_ptr(), lengths.data_ptr(),
+        _ptr(attention_mask), output.data_ptr(), batch, q_heads, kv_heads, dim, capacity,
+        mask_len, query.stride(0), query.stride(1), mask_stride, mask_code, float(scale),
+        _code(query.dtype), _mode(numerical_mode), int(split_tokens), int(max_length_hint),
+        _ptr(workspace), need, rt.status.data_ptr(), _stream())
+    _check(code, "b200_decode_attention")
+    _count(rt, 2 if need else 1)
+    return output
+
+
+# --------------------------------------------------------------- prefill attention ----
+def b200_prefill_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                           attention_mask: Optional[torch.Tensor], *, scale: float,
+                           causal: bool = False, numerical_mode: str = "fast") -> torch.Tensor:
+    """T-token GQA attention with an additive B x 1 x T x T mask (or proven causality).
+    Mirrors triton_prefill_attention (backends/triton_prefill_attention.py:152-232).
+
+    Returns a B x Hq x T x D tensor whose memory order is B, T, Hq, D, so that the
+    transpose(1, 2) + reshape that follows in Qwen2 graphs is a view.
+    """
+
+    device = _require_cuda(query, key, value, attention_mask)
+    if query.ndim != 4 or key.ndim != 4 or key.shape != value.shape:
+        raise ValueError("query must be B x Hq x T x D and key/value B x Hkv x T x D")
+    batch, q_heads, tokens, dim = query.shape
+    kv_heads = key.shape[1]
+    if key.shape[0] != batch or key.shape[2] != tokens or key.shape[3] != dim:
+        raise ValueError("query and key/value disagree on batch, tokens or head_dim")
+    if kv_heads <= 0 or q_heads % kv_heads:
+        raise ValueError("query heads must be a multiple of KV heads")
+    if not (query.dtype == key.dtype == value.dtype):
+        raise ValueError("query, key and value must share one dtype")
+    if attention_mask is None and not causal:
+        raise ValueError("a mask is required unless causality is proven")
+    mask_strides = None
+    mask_code = _lib.F32
+    if attention_mask is not None:
+        if attention_mask.ndim != 4 or attention_mask.shape[1] != 1 or \
+                attention_mask.shape[2] != tokens or attention_mask.shape[3] != tokens or \
+                attention_mask.shape[0] not in (1, batch):
+            raise ValueError("attention_mask must be B x 1 x T x T")
+        strides = list(attention_mask.stride())
+        if attention_mask.shape[0] == 1:
+            strides[0] = 0
+        mask_strides = _lib.i64_array(strides)
+        mask_code = _code(attention_mask.dtype)
+    query = query if query.stride(3) == 1 else _dense(query)
+    key = key if key.stride(3) == 1 else _dense(key)
+    value = value if value.stride(3) == 1 else _dense(value)
+    storage = torch.empty((batch, tokens, q_heads, dim), dtype=query.dtype, device=device)
+    rt = runtime(device)
+    code = _lib.load().b200_prefill_attention(
+        query.data_ptr(), key.data_ptr(), value.data_ptr(), _ptr(attention_mask),
+        storage.data_ptr(), batch, q_heads, kv_heads, tokens, dim,
+        _lib.i64_array(query.stride()), _lib.i64_array(key.stride()),
+        _lib.i64_array(value.stride()), mask_strides, mask_code, float(scale), int(bool(causal)),
+        _code(query.dtype), _mode(numerical_mode), _stream())
+    _check(code, "b200_prefill_attention")
+    _count(rt)
+    return storage.transpose(1, 2)
+
+
+# -------------------------------------------------------------------------- linear ----
+def linear_workspace_bytes(m: int, k: int, n: int, dtype: torch.dtype,
+                           epilogue: str = "none") -> int:
+    return int(_lib.load().b200_linear_workspace_bytes(m, k, n, _code(dtype),
+                                                       _EPILOGUES[epilogue]))
+
+
+def b200_linear(tensor: torch.Tensor, weight: torch.Tensor,
+                bias: Optional[torch.Tensor] = None, *, residual: Optional[torch.Tensor] = None,
+                epilogue: str = "none") -> torch.Tensor:
+    """y = x W^T (+ bias) with fp32 accumulation. Mirrors triton_linear
+    (backends/triton_linear.py:87-148).
+
+    epilogue "residual": y = r(r(x W^T + b) + residual) (same shape as y).
+    epilogue "swiglu": weight holds 2N rows, gate_j and up_j alternating, and the result has
+    N columns: r(r(silu(r(gate))) * r(up)).
+    """
+
+    device = _require_cuda(tensor, weight, bias, residual)
+    if weight.ndim != 2:
+        raise ValueError("weight must be N x K")
+    n, k = weight.shape
+    if tensor.ndim < 1 or tensor.shape[-1] != k:
+        raise ValueError("the last input dimension must equal the weight's K")
+    if tensor.dtype != weight.dtype:
+        raise ValueError("input and weight must share one dtype")
+    if bias is not None and (bias.shape != (n,) or bias.dtype != tensor.dtype):
+        raise ValueError("bias must be a vector of N elements in the input dtype")
+    if epilogue not in _EPILOGUES:
+        raise ValueError(f"unknown epilogue {epilogue!r}")
+    weight = _dense(weight)
+    source = _dense(tensor) if tensor.ndim <= 4 else tensor
+    if not source.is_contiguous():
+        raise ValueError("inputs of rank > 4 must be contiguous")
+    m = source.numel() // k
+    out_features = n // 2 if epilogue == "swiglu" else n
+    output = torch.empty((*tensor.shape[:-1], out_features), dtype=tensor.dtype, device=device)
+    if epilogue == "residual":
+        if residual is None or residual.shape != output.shape or residual.dtype != tensor.dtype:
+            raise ValueError("residual must match the output shape and dtype")
+        residual = _dense(residual)
+    elif residual is not None:
+        raise ValueError("residual given without the residual epilogue")
+    if bias is not None:
+        bias = _dense(bias)
+    rt = runtime(device)
+    library = _lib.load()
+    code_dtype = _code(tensor.dtype)
+    need = int(library.b200_linear_workspace_bytes(m, k, n, code_dtype, _EPILOGUES[epilogue]))
+    workspace = rt.workspace("linear", need)
+    code = library.b200_linear(source.data_ptr(), weight.data_ptr(), _ptr(bias), _ptr(residual),
+                               output.data_ptr(), m, k, n, k, code_dtype, _EPILOGUES[epilogue],
+                               _ptr(workspace), need, _stream())
+    _check(code, "b200_linear")
+    _count(rt)
+    return output
+
+
+def interleave_gate_up(gate_weight: torch.Tensor, up_weight: torch.Tensor) -> torch.Tensor:
+    """Row-interleaves gate and up projection weights (gate_0, up_0, gate_1, ...) for the
+    SwiGLU epilogue. A one-time weight repack done at load time with a device copy."""
+
+    if gate_weight.shape != up_weight.shape:
+        raise ValueError("gate and up weights must have one shape")
+    n, k = gate_weight.shape
+    packed = torch.empty((2 * n, k), dtype=gate_weight.dtype, device=gate_weight.device)
+    packed[0::2].copy_(gate_weight)
+    packed[1::2].copy_(up_weight)
+    return packed
+
+
+# ------------------------------------------------- ops the reference leaves to eager ----
+def b200_embedding(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """aten.embedding.default: rows of `table` gathered by int64 ids."""
+
+    device = _require_cuda(table, ids)
+    if table.ndim != 2 or ids.dtype != torch.int64:
+        raise ValueError("embedding needs a V x H table and int64 ids")
+    table = _dense(table)
+    ids = _dense_index(ids, "ids")
+    vocab, hidden = table.shape
+    output = torch.empty((*ids.shape, hidden), dtype=table.dtype, device=device)
+    rt = runtime(device)
+    code = _lib.load().b200_embedding(table.data_ptr(), ids.data_ptr(), output.data_ptr(),
+                                      ids.numel(), hidden, vocab, _code(table.dtype),
+                                      rt.status.data_ptr(), _stream())
+    _check(code, "b200_embedding")
+    _count(rt)
+    return output
+
+
+def b200_swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """aten.silu.default + aten.mul.Tensor: r(r(silu(gate)) * up)."""
+
+    device = _require_cuda(gate, up)
+    if gate.shape != up.shape or gate.dtype != up.dtype:
+        raise ValueError("gate and up must share shape and dtype")
+    gate = _dense(gate)
+    up = _dense(up)
+    output = torch.empty_like(gate)
+    rt = runtime(device)
+    code = _lib.load().b200_swiglu(gate.data_ptr(), up.data_ptr(), output.data_ptr(),
+                                   gate.numel(), _code(gate.dtype), _stream())
+    _check(code, "b200_swiglu")
+    _count(rt)
+    return output
+
+
+def b200_add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """aten.add.Tensor on same-shape tensors: r(a + b)."""
+
+    device = _require_cuda(a, b)
+    if a.shape != b.shape or a.dtype != b.dtype:
+        raise ValueError("add operands must share shape and dtype")
+    a = _dense(a)
+    b = _dense(b)
+    output = torch.empty_like(a)
+    rt = runtime(device)
+    code = _lib.load().b200_add(a.data_ptr(), b.data_ptr(), output.data_ptr(), a.numel(),
+                                _code(a.dtype), _stream())
+    _check(code, "b200_add")
+    _count(rt)
+    return output
+
+
+def b200_contiguous(tensor: torch.Tensor, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """aten.contiguous.default / a real aten.to.dtype: dense copy of a (<= 4-D) strided view,
+    optionally converting between f32 and bf16."""
+
+    device = _require_cuda(tensor)
+    dtype = dtype or tensor.dtype
+    if tensor.ndim > 4:
+        raise ValueError("strided copies handle at most 4 dimensions")
+    sizes = [1] * (4 - tensor.ndim) + list(tensor.shape)
+    strides = [0] * (4 - tensor.ndim) + list(tensor.stride())
+    output = torch.empty(tensor.shape, dtype=dtype, device=device)
+    rt = runtime(device)
+    code = _lib.load().b200_copy_4d(tensor.data_ptr(), output.data_ptr(), _lib.i64_array(sizes),
+                                    _lib.i64_array(strides), _code(tensor.dtype), _code(dtype),
+                                    _stream())
+    _check(code, "b200_copy_4d")
+    _count(rt)
+    return output
+
+
+def b200_advance_lengths(lengths: torch.Tensor, delta: int, capacity: int) -> None:
+    """runtime.kv.advance in place: lengths += delta, clamped at capacity with a status bit.
+    `lengths` is int64 of shape [batch] or [slots, batch], contiguous."""
+
+    device = _require_cuda(lengths)
+    if lengths.dtype != torch.int64 or not lengths.is_contiguous() or lengths.ndim not in (1, 2):
+        raise ValueError("lengths must be a contiguous int64 tensor of rank 1 or 2")
+    if delta <= 0:
+        raise ValueError("advance delta must be positive")
+    slots = lengths.shape[0] if lengths.ndim == 2 else 1
+    batch = lengths.shape[-1]
+    rt = runtime(device)
+    code = _lib.load().b200_advance_lengths(lengths.data_ptr(), slots, batch, int(delta),
+                                            int(capacity), rt.status.data_ptr(), _stream())
+    _check(code, "b200_advance_lengths")
+    _count(rt)
+
+
+def b200_argmax(logits: torch.Tensor, output: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Greedy token per row of a [..., V] logits tensor (lowest index wins ties)."""
+
+    device = _require_cuda(logits)
+    vocab = logits.shape[-1]
+    source = _dense(logits)
+    rows = source.numel() // vocab
+    if output is None:
+        output = torch.empty(logits.shape[:-1], dtype=torch.int64, device=device)
+    rt = runtime(device)
+    code = _lib.load().b200_argmax(source.data_ptr(), output.data_ptr(), rows, vocab, vocab,
+                                   _code(logits.dtype), _stream())
+    _check(code, "b200_argmax")
+    _count(rt)
+    return output
+
+
+def default_scale(head_dim: int) -> float:
+    return 1.0 / math.sqrt(head_dim)
