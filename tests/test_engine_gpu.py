@@ -1,0 +1,125 @@
+"""Whole-model parity of the serving engine (CUDA-graph decode) against the reference.
+
+qwen2_tiny_{fp32,bf16}.pt hold what the reference's own ReferenceExecutor produced for the
+2-layer stateful decode (batch 3, prompt 5, capacity 64, 4 greedy steps). Tolerances: fp32
+graphs 1e-4 on logits; bf16 graphs 2e-2 with greedy tokens equal (a token may differ only
+where the reference's own top-2 logits are closer than the tolerance).
+"""
+
+import pytest
+import torch
+
+from oracle import qwen2_model
+import llm_compiler_b200 as b200
+from llm_compiler_b200 import qwen2 as q2
+from llm_compiler_b200.engine import Qwen2Engine
+
+pytestmark = pytest.mark.gpu
+
+
+def cuda_weights(config, dtype, seed=0):
+    return {k: v.cuda() for k, v in q2.make_weights(config, seed=seed, dtype=dtype).items()}
+
+
+def assert_logits(actual, expected, tol):
+    actual, expected = actual.float().cpu(), expected.float()
+    scale = max(1e-3, float(expected.abs().max()))
+    diff = float((actual - expected).abs().max())
+    assert diff <= tol * max(1.0, scale) or diff <= tol * scale * 4, f"logit diff {diff} (scale {scale})"
+
+
+def assert_tokens(actual, expected, expected_logits, tol):
+    actual = actual.cpu()
+    for row in range(expected.shape[0]):
+        if actual[row] == expected[row]:
+            continue
+        top2 = expected_logits[row].float().topk(2).values
+        assert float(top2[0] - top2[1]) <= tol, "greedy token differs beyond a near-tie"
+
+
+@pytest.mark.parametrize("tag,mode", [("fp32", "fast"), ("fp32", "pytorch_compatible"),
+                                      ("bf16", "fast"), ("bf16", "pytorch_compatible")])
+def test_tiny_stateful_decode_matches_reference(tag, mode, golden_tiny):
+    gold = golden_tiny[tag]
+    dtype = torch.float32 if tag == "fp32" else torch.bfloat16
+    tol = 1e-4 if tag == "fp32" else 2e-2
+    config = q2.Qwen2Config(**gold["config"])
+    engine = Qwen2Engine(config, cuda_weights(config, dtype), batch=gold["batch"],
+                         capacity=gold["capacity"], numerical_mode=mode)
+    pointers = [k.data_ptr() for k in engine.state.keys]
+    logits = engine.prefill(gold["input_ids"], all_logits=True)
+    assert_logits(logits, gold["prefill_logits"], tol)
+    assert_tokens(engine.next_ids, gold["tokens"][:, 0], gold["prefill_logits"][:, -1], tol)
+    engine.capture()
+    for step in range(gold["steps"]):
+        engine.input_ids.copy_(gold["tokens"][:, step].cuda())  # teacher forcing
+        engine.decode_step(feed_back=False)
+        assert_logits(engine.logits, gold["decode_logits"][step], tol)
+        assert_tokens(engine.next_ids, gold["tokens"][:, step + 1], gold["decode_logits"][step], tol)
+    engine.state.check()
+    used = gold["prompt"] + gold["steps"]
+    lengths = torch.stack([l for l in engine.state.lengths], 0).cpu()
+    assert torch.equal(lengths, gold["lengths"])
+    keys = torch.stack([k[:, :used] for k in engine.state.keys], 0)
+    values = torch.stack([v[:, :used] for v in engine.state.values], 0)
+    assert_logits(keys, gold["keys"], tol)
+    assert_logits(values, gold["values"], tol)
+    assert pointers == [k.data_ptr() for k in engine.state.keys]  # fixed KV addresses
+
+
+def test_greedy_generation_with_graph_equals_eager(golden_tiny):
+    gold = golden_tiny["fp32"]
+    config = q2.Qwen2Config(**gold["config"])
+    weights = cuda_weights(config, torch.float32)
+    graph = Qwen2Engine(config, weights, batch=3, capacity=64)
+    eager = Qwen2Engine(config, weights, batch=3, capacity=64)
+    a = graph.generate(gold["input_ids"], 6, use_graph=True)
+    b = eager.generate(gold["input_ids"], 6, use_graph=False)
+    assert torch.equal(a, b)
+    assert torch.equal(a[:, :5].cpu(), gold["tokens"])
+
+
+def test_host_step_api_round_trip(golden_tiny):
+    gold = golden_tiny["fp32"]
+    config = q2.Qwen2Config(**gold["config"])
+    engine = Qwen2Engine(config, cuda_weights(config, torch.float32), batch=3, capacity=64)
+    engine.prefill(gold["input_ids"])
+    engine.capture()
+    tokens = gold["tokens"][:, 0].clone()
+    for step in range(gold["steps"]):
+        tokens = engine.step(tokens).clone()
+        assert torch.equal(tokens, gold["tokens"][:, step + 1])
+
+
+def test_capacity_overflow_is_reported_not_trapped(golden_tiny):
+    gold = golden_tiny["fp32"]
+    config = q2.Qwen2Config(**gold["config"])
+    engine = Qwen2Engine(config, cuda_weights(config, torch.float32), batch=3, capacity=8)
+    engine.prefill(gold["input_ids"])  # 5 tokens
+    for _ in range(3):
+        engine.decode_step()
+    engine.state.check()  # 8 tokens: full, still fine
+    engine.decode_step()
+    with pytest.raises(b200.ExecutionError):
+        engine.state.check()
+
+
+def test_qwen2_0_5b_shaped_layers_match_oracle():
+    """Qwen2-0.5B shapes (hidden 896, 14/2 heads x 64, SwiGLU 4864, biases, theta 1e6) with 2
+    layers and a reduced vocabulary so that the CPU oracle finishes in seconds; bf16."""
+    config = q2.Qwen2Config(hidden_size=896, intermediate_size=4864, num_layers=2, num_heads=14,
+                            num_kv_heads=2, rms_norm_eps=1e-6, rope_theta=1e6, vocab_size=4096,
+                            tie_word_embeddings=True)
+    weights = q2.make_weights(config, seed=3, dtype=torch.bfloat16)
+    prompt = q2.make_prompt_ids(config, 4, 37, seed=1)
+    ref_tokens, ref_logits, _ = qwen2_model.greedy_generate(config, weights, prompt, 3, capacity=64)
+    engine = Qwen2Engine(config, {k: v.cuda() for k, v in weights.items()}, batch=4, capacity=64)
+    engine.prefill(prompt)
+    assert_logits(engine.logits, ref_logits[0], 2e-2)
+    engine.capture()
+    for step in range(3):
+        engine.input_ids.copy_(ref_tokens[:, step].cuda())
+        engine.decode_step(feed_back=False)
+        assert_logits(engine.logits, ref_logits[step + 1], 2e-2)
+        assert_tokens(engine.next_ids, ref_tokens[:, step + 1], ref_logits[step + 1], 2e-2)
+    engine.state.check()

@@ -1,0 +1,465 @@
+"""Parity of every CUDA kernel, called through the C ABI, against the reference.
+
+Three layers of evidence per operator:
+  1. the committed golden outputs of the reference's own CPU executor (tests/golden/ops.pt)
+     on the seeded inputs of tests/golden/cases.py;
+  2. the CPU oracle (oracle/serve_ops.py, itself pinned to those goldens) on further seeded
+     inputs: ragged lengths, length 0 and length == capacity, odd sizes, strided operands;
+  3. size-independent properties at the benchmark's full shapes (store -> read-back round
+     trip, invariance of decode attention to the number of KV splits).
+
+Tolerances: KV store, RoPE and pytorch_compatible RMSNorm are bit-exact; fp32 kernels
+3e-5; bf16 attention / GEMM 2e-2 (max abs and relative to the output scale).
+"""
+
+import pytest
+import torch
+
+import cases
+from oracle import serve_ops
+import llm_compiler_b200 as b200
+from llm_compiler_b200 import kernels
+
+pytestmark = pytest.mark.gpu
+
+BF16_TOL = 2e-2
+F32_TOL = 3e-5
+
+
+def dev(x):
+    return x.cuda() if isinstance(x, torch.Tensor) else x
+
+
+def exact(actual, expected):
+    torch.testing.assert_close(actual.cpu(), expected, rtol=0, atol=0, equal_nan=True)
+
+
+def close(actual, expected, tol):
+    actual = actual.float().cpu()
+    expected = expected.float()
+    assert actual.shape == expected.shape
+    assert torch.equal(torch.isnan(actual), torch.isnan(expected))
+    scale = max(1.0, float(expected.nan_to_num().abs().max()))
+    diff = (actual - expected).nan_to_num().abs().max().item()
+    assert diff <= tol * scale, f"max abs diff {diff} > {tol} * {scale}"
+
+
+def tol_for(dtype):
+    return F32_TOL if dtype == torch.float32 else BF16_TOL
+
+
+# ------------------------------------------------------------------------ KV store ----
+@pytest.mark.parametrize("name", list(cases.KV_STORE))
+def test_kv_store_golden(name, golden_ops):
+    x = cases.kv_store_inputs(name)
+    kbuf, vbuf = dev(x["key_buffer"]), dev(x["value_buffer"])
+    b200.b200_kv_store(kbuf, vbuf, dev(x["key"]), dev(x["value"]), dev(x["positions"]))
+    exact(kbuf, golden_ops[name]["key_out"])
+    exact(vbuf, golden_ops[name]["value_out"])
+    kernels.runtime().check_status()
+
+
+def test_kv_store_ragged_edges():
+    g = torch.Generator().manual_seed(3)
+    b, c, h, d, t = 5, 33, 2, 64, 4
+    kbuf = torch.randn(b, c, h, d, generator=g).bfloat16()
+    vbuf = torch.randn(b, c, h, d, generator=g).bfloat16()
+    key = torch.randn(b, t, h, d, generator=g).bfloat16().transpose(1, 2)
+    value = torch.randn(b, h, t, d, generator=g).bfloat16()  # contiguous B,H,T,D
+    positions = torch.tensor([0, c - t, 7, 1, 20])  # first row, last legal row, ragged
+    k_ref, v_ref = kbuf.clone(), vbuf.clone()
+    serve_ops.kv_store(k_ref, v_ref, key, value, positions)
+    k_dev, v_dev = kbuf.cuda(), vbuf.cuda()
+    b200.b200_kv_store(k_dev, v_dev, key.cuda(), value.cuda(), positions.cuda())
+    exact(k_dev, k_ref)
+    exact(v_dev, v_ref)
+    kernels.runtime().check_status()
+
+
+def test_kv_store_overflow_sets_status_and_skips():
+    kbuf = torch.zeros(2, 8, 2, 64, dtype=torch.bfloat16, device="cuda")
+    vbuf = torch.zeros_like(kbuf)
+    key = torch.ones(2, 2, 3, 64, dtype=torch.bfloat16, device="cuda")
+    positions = torch.tensor([6, 1], device="cuda")  # row 0: tokens 6, 7 fit, 8 does not
+    b200.b200_kv_store(kbuf, vbuf, key, key, positions)
+    with pytest.raises(b200.KernelStatusError):
+        kernels.runtime().check_status()
+    assert kbuf[0, 6:8].eq(1).all() and kbuf[1, 1:4].eq(1).all()
+    assert kbuf[0, :6].eq(0).all() and kbuf[1, 4:].eq(0).all()
+    kernels.runtime().check_status()  # cleared
+
+
+def test_kv_store_round_trip_full_size():
+    """Benchmark shape (batch 16 x 4096 tokens into capacity 8192): store then read back."""
+    b, c, h, d, t = 16, 8192, 2, 64, 4096
+    g = torch.Generator(device="cuda").manual_seed(1)
+    kbuf = torch.zeros(b, c, h, d, dtype=torch.bfloat16, device="cuda")
+    vbuf = torch.zeros_like(kbuf)
+    key = torch.randn(b, t, h, d, generator=g, device="cuda").bfloat16().transpose(1, 2)
+    value = torch.randn(b, t, h, d, generator=g, device="cuda").bfloat16().transpose(1, 2)
+    positions = torch.zeros(b, dtype=torch.int64, device="cuda")
+    b200.b200_kv_store(kbuf, vbuf, key, value, positions)
+    assert torch.equal(kbuf[:, :t].transpose(1, 2), key)
+    assert torch.equal(vbuf[:, :t].transpose(1, 2), value)
+    assert kbuf[:, t:].eq(0).all()
+    # one decode append at position T (config 3 of the benchmark plan)
+    positions.fill_(t)
+    step = torch.randn(b, 1, h, d, generator=g, device="cuda").bfloat16().transpose(1, 2)
+    b200.b200_kv_store(kbuf, vbuf, step, step, positions)
+    assert torch.equal(kbuf[:, t], step[:, :, 0]) and torch.equal(kbuf[:, :t].transpose(1, 2), key)
+    kernels.runtime().check_status()
+
+
+# ---------------------------------------------------------------------------- RoPE ----
+@pytest.mark.parametrize("name", list(cases.ROPE))
+def test_rope_golden_bit_exact(name, golden_ops):
+    x = cases.rope_inputs(name)
+    gold = golden_ops[name]
+    q, k = b200.b200_rope(dev(x["query"]), dev(x["key"]), dev(gold["cosine"]), dev(gold["sine"]))
+    assert q.is_contiguous() and k.is_contiguous()
+    exact(q, gold["query_out"])
+    exact(k, gold["key_out"])
+
+
+def test_rope_unaligned_head_dim_uses_scalar_path():
+    g = torch.Generator().manual_seed(4)
+    q = torch.randn(2, 3, 5, 12, generator=g).bfloat16()
+    k = torch.randn(2, 1, 5, 12, generator=g).bfloat16()
+    cos = torch.randn(2, 5, 12, generator=g).bfloat16()
+    sin = torch.randn(2, 5, 12, generator=g).bfloat16()
+    q_ref, k_ref = serve_ops.rope(q, k, cos, sin)
+    q_out, k_out = b200.b200_rope(q.cuda(), k.cuda(), cos.cuda(), sin.cuda())
+    exact(q_out, q_ref)
+    exact(k_out, k_ref)
+
+
+@pytest.mark.parametrize("name", ["rope_bf16_decode", "rope_f32"])
+def test_rope_kv_store_fusion_matches_separate_ops(name, golden_ops):
+    x = cases.rope_inputs(name)
+    gold = golden_ops[name]
+    b, hkv, d = x["key"].shape[0], x["kv_heads"], x["head_dim"]
+    dtype = x["query"].dtype
+    capacity = 16
+    g = torch.Generator().manual_seed(8)
+    value = torch.randn(b, hkv, 1, d, generator=g).to(dtype)
+    positions = torch.arange(b, dtype=torch.int64) % capacity
+    kbuf = torch.zeros(b, capacity, hkv, d, dtype=dtype)
+    vbuf = torch.zeros_like(kbuf)
+    serve_ops.kv_store(kbuf, vbuf, gold["key_out"], value, positions)
+    k_dev, v_dev = torch.zeros_like(kbuf).cuda(), torch.zeros_like(vbuf).cuda()
+    q_out = b200.b200_rope_kv_store(dev(x["query"]), dev(x["key"]), value.cuda(),
+                                    dev(gold["cosine"]), dev(gold["sine"]), k_dev, v_dev,
+                                    positions.cuda())
+    exact(q_out, gold["query_out"])
+    exact(k_dev, kbuf)
+    exact(v_dev, vbuf)
+
+
+@pytest.mark.parametrize("name", list(cases.ROPE_TABLE))
+def test_rope_table(name, golden_ops):
+    x = cases.rope_table_inputs(name)
+    inv_freq = serve_ops.rope_inverse_frequency(x["head_dim"], x["theta"])
+    cos, sin = b200.b200_rope_table(dev(x["position_ids"]), inv_freq.cuda(), x["dtype"])
+    for actual, expected in ((cos, golden_ops[name]["cosine"]), (sin, golden_ops[name]["sine"])):
+        actual = actual.cpu()
+        if x["dtype"] == torch.float32:
+            torch.testing.assert_close(actual, expected, rtol=0, atol=2e-7)
+        else:
+            # cos/sin come from different libms (device vs host): after bf16 rounding a value
+            # may land on the neighbouring bf16 in rare ties; never further
+            differing = (actual != expected).float().mean().item()
+            assert differing <= 0.01, f"{differing:.4f} of the table differs"
+            torch.testing.assert_close(actual.float(), expected.float(), rtol=0, atol=2 ** -8)
+
+
+# ------------------------------------------------------------------------- RMSNorm ----
+@pytest.mark.parametrize("name", list(cases.RMS_NORM))
+def test_rms_norm_pytorch_compatible_bit_exact(name, golden_ops):
+    x = cases.rms_norm_inputs(name)
+    out = b200.b200_rms_norm(dev(x["input"]), dev(x["weight"]), epsilon=x["epsilon"],
+                             round_before_weight=x["round_before_weight"],
+                             numerical_mode="pytorch_compatible")
+    exact(out, golden_ops[name]["output"])
+
+
+@pytest.mark.parametrize("name", list(cases.RMS_NORM))
+def test_rms_norm_fast(name, golden_ops):
+    x = cases.rms_norm_inputs(name)
+    out = b200.b200_rms_norm(dev(x["input"]), dev(x["weight"]), epsilon=x["epsilon"],
+                             round_before_weight=x["round_before_weight"], numerical_mode="fast")
+    close(out, golden_ops[name]["output"], tol_for(x["input"].dtype))
+
+
+def test_rms_norm_3d_and_strided_rows():
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(4, 3, 896, generator=g).bfloat16()
+    w = torch.randn(896, generator=g).bfloat16()
+    ref = serve_ops.rms_norm(x, w, 1e-6, round_before_weight=True)
+    exact(b200.b200_rms_norm(x.cuda(), w.cuda(), epsilon=1e-6, round_before_weight=True,
+                             numerical_mode="pytorch_compatible"), ref)
+    wide = torch.randn(6, 2048, generator=g).bfloat16()
+    view = wide[:, :896]
+    ref = serve_ops.rms_norm(view, w, 1e-6, round_before_weight=True)
+    for mode in ("pytorch_compatible", "fast"):
+        out = b200.b200_rms_norm(wide.cuda()[:, :896], w.cuda(), epsilon=1e-6,
+                                 round_before_weight=True, numerical_mode=mode)
+        (exact if mode == "pytorch_compatible" else lambda a, e: close(a, e, BF16_TOL))(out, ref)
+
+
+# ---------------------------------------------------------------- decode attention ----
+@pytest.mark.parametrize("mode", ["fast", "pytorch_compatible"])
+@pytest.mark.parametrize("name", list(cases.DECODE_ATTENTION))
+def test_decode_attention_golden(name, mode, golden_ops):
+    x = cases.decode_attention_inputs(name)
+    out = b200.b200_decode_attention(dev(x["query"]), dev(x["key_buffer"]), dev(x["value_buffer"]),
+                                     dev(x["lengths"]), dev(x["mask"]), scale=x["scale"],
+                                     numerical_mode=mode)
+    assert out.shape == golden_ops[name]["output"].shape
+    close(out, golden_ops[name]["output"], tol_for(x["query"].dtype))
+    kernels.runtime().check_status()
+
+
+@pytest.mark.parametrize("split_tokens", [0, 16, 64, 256, 4096])
+def test_decode_attention_splits_ragged_and_masked(split_tokens):
+    """Ragged lengths incl. 0 (NaN row, as the oracle), 1 and == capacity; a mask with -inf
+    holes; every split size must agree with the oracle."""
+    g = torch.Generator().manual_seed(21)
+    b, c, hq, hkv, d = 6, 777, 14, 2, 64
+    q = torch.randn(b, 1, hq, d, generator=g).bfloat16().transpose(1, 2)
+    kbuf = torch.randn(b, c, hkv, d, generator=g).bfloat16()
+    vbuf = torch.randn(b, c, hkv, d, generator=g).bfloat16()
+    lengths = torch.tensor([0, 1, 16, 17, 500, c])
+    mask = torch.zeros(b, 1, 1, c)
+    mask[:, :, :, 3::7] = float("-inf")
+    mask[4, :, :, :64] = float("-inf")  # a fully masked first tile
+    mask[1, :, :, 0] = 0.0
+    ref = serve_ops.decode_attention(q, kbuf, vbuf, lengths, mask, groups=hq // hkv, scale=0.125)
+    out = b200.b200_decode_attention(q.cuda(), kbuf.cuda(), vbuf.cuda(), lengths.cuda(),
+                                     mask.cuda(), scale=0.125, split_tokens=split_tokens)
+    assert torch.isnan(out[0]).all()
+    close(out, ref, BF16_TOL)
+    kernels.runtime().check_status()
+
+
+def test_decode_attention_no_mask_and_bf16_mask():
+    x = cases.decode_attention_inputs("decode_attention_bf16_long")
+    ref = serve_ops.decode_attention(x["query"], x["key_buffer"], x["value_buffer"], x["lengths"],
+                                     x["mask"], groups=x["groups"], scale=x["scale"])
+    args = [dev(x[k]) for k in ("query", "key_buffer", "value_buffer", "lengths")]
+    close(b200.b200_decode_attention(*args, None, scale=x["scale"]), ref, BF16_TOL)
+    close(b200.b200_decode_attention(*args, dev(x["mask"].bfloat16()), scale=x["scale"]), ref,
+          BF16_TOL)
+    short = x["mask"][..., :1200].contiguous()
+    close(b200.b200_decode_attention(*args, dev(short), scale=x["scale"], max_length_hint=1200),
+          ref, BF16_TOL)
+
+
+def test_decode_attention_length_over_mask_sets_status():
+    x = cases.decode_attention_inputs("decode_attention_bf16")
+    mask = x["mask"][..., :200].contiguous()  # lengths are [1, 130, 300]
+    b200.b200_decode_attention(dev(x["query"]), dev(x["key_buffer"]), dev(x["value_buffer"]),
+                               dev(x["lengths"]), dev(mask), scale=x["scale"])
+    with pytest.raises(b200.KernelStatusError):
+        kernels.runtime().check_status()
+
+
+def test_decode_attention_qwen2_7b_shape():
+    g = torch.Generator().manual_seed(31)
+    b, c, hq, hkv, d = 3, 1500, 28, 4, 128
+    q = torch.randn(b, 1, hq, d, generator=g).bfloat16().transpose(1, 2)
+    kbuf = torch.randn(b, c, hkv, d, generator=g).bfloat16()
+    vbuf = torch.randn(b, c, hkv, d, generator=g).bfloat16()
+    lengths = torch.tensor([1500, 1024, 333])
+    mask = torch.zeros(b, 1, 1, c)
+    ref = serve_ops.decode_attention(q, kbuf, vbuf, lengths, mask, groups=7, scale=d ** -0.5)
+    for split in (0, 128):
+        out = b200.b200_decode_attention(q.cuda(), kbuf.cuda(), vbuf.cuda(), lengths.cuda(),
+                                         mask.cuda(), scale=d ** -0.5, split_tokens=split)
+        close(out, ref, BF16_TOL)
+
+
+@pytest.mark.parametrize("hq,hkv", [(24, 2), (40, 2), (16, 1), (9, 1)])
+def test_decode_attention_wide_groups(hq, hkv):
+    """More than 8 (and more than 16) query heads per KV head: both row halves of the
+    tensor-core tile and several 16-row blocks per KV head."""
+    g = torch.Generator().manual_seed(hq)
+    b, c, d = 2, 210, 64
+    q = torch.randn(b, 1, hq, d, generator=g).bfloat16().transpose(1, 2)
+    kbuf = torch.randn(b, c, hkv, d, generator=g).bfloat16()
+    vbuf = torch.randn(b, c, hkv, d, generator=g).bfloat16()
+    lengths = torch.tensor([210, 45])
+    mask = torch.zeros(b, 1, 1, c)
+    ref = serve_ops.decode_attention(q, kbuf, vbuf, lengths, mask, groups=hq // hkv, scale=0.125)
+    for split in (0, 64):
+        out = b200.b200_decode_attention(q.cuda(), kbuf.cuda(), vbuf.cuda(), lengths.cuda(),
+                                         mask.cuda(), scale=0.125, split_tokens=split)
+        close(out, ref, BF16_TOL)
+
+
+def test_decode_attention_split_invariance_full_size():
+    """Benchmark shape (batch 64, capacity 4608, lengths ~4096, 14/2 heads x 64): the result
+    must not depend on how the KV range is split; one sequence is checked against the oracle."""
+    b, c, hq, hkv, d = 64, 4608, 14, 2, 64
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q = torch.randn(b, hq, 1, d, generator=g, device="cuda").bfloat16()
+    kbuf = torch.randn(b, c, hkv, d, generator=g, device="cuda").bfloat16()
+    vbuf = torch.randn(b, c, hkv, d, generator=g, device="cuda").bfloat16()
+    lengths = torch.randint(64, 4097, (b,), generator=g, device="cuda")
+    lengths[0] = 4096
+    outs = [b200.b200_decode_attention(q, kbuf, vbuf, lengths, None, scale=0.125,
+                                       split_tokens=s, max_length_hint=4096)
+            for s in (0, 256, 1024, 8192)]
+    for other in outs[1:]:
+        close(other, outs[0].float().cpu(), 4e-3)
+    ref = serve_ops.decode_attention(q[:1].cpu(), kbuf[:1].cpu(), vbuf[:1].cpu(),
+                                     lengths[:1].cpu(), torch.zeros(1, 1, 1, c), groups=7,
+                                     scale=0.125)
+    close(outs[0][:1], ref, BF16_TOL)
+    kernels.runtime().check_status()
+
+
+# --------------------------------------------------------------- prefill attention ----
+@pytest.mark.parametrize("mode", ["fast", "pytorch_compatible"])
+@pytest.mark.parametrize("name", list(cases.PREFILL_ATTENTION))
+def test_prefill_attention_golden(name, mode, golden_ops):
+    x = cases.prefill_attention_inputs(name)
+    gold = golden_ops[name]["output"]
+    tol = tol_for(x["query"].dtype)
+    out = b200.b200_prefill_attention(dev(x["query"]), dev(x["key"]), dev(x["value"]),
+                                      dev(x["mask"]), scale=x["scale"], numerical_mode=mode)
+    assert out.shape == gold.shape
+    assert out.transpose(1, 2).is_contiguous()  # token-major memory
+    close(out, gold, tol)
+    if not x["zero_mask"]:
+        causal = b200.b200_prefill_attention(dev(x["query"]), dev(x["key"]), dev(x["value"]),
+                                             None, scale=x["scale"], causal=True,
+                                             numerical_mode=mode)
+        close(causal, gold, tol)
+
+
+def test_prefill_attention_arbitrary_mask_and_broadcast_batch():
+    g = torch.Generator().manual_seed(44)
+    b, t, hq, hkv, d = 2, 150, 14, 2, 64
+    q = torch.randn(b, t, hq, d, generator=g).bfloat16().transpose(1, 2)
+    k = torch.randn(b, t, hkv, d, generator=g).bfloat16().transpose(1, 2)
+    v = torch.randn(b, t, hkv, d, generator=g).bfloat16().transpose(1, 2)
+    mask = torch.randn(1, 1, t, t, generator=g)  # soft additive mask, broadcast over batch
+    mask[:, :, :, 5::9] = float("-inf")
+    ref = serve_ops.prefill_attention(q, k, v, mask, groups=7, scale=0.125)
+    out = b200.b200_prefill_attention(q.cuda(), k.cuda(), v.cuda(), mask.cuda(), scale=0.125)
+    close(out, ref, BF16_TOL)
+
+
+@pytest.mark.parametrize("tokens", [16, 128, 512])
+def test_prefill_attention_config3_shapes(tokens):
+    g = torch.Generator().manual_seed(tokens)
+    b, hq, hkv, d = 4, 14, 2, 64
+    q = torch.randn(b, tokens, hq, d, generator=g).bfloat16().transpose(1, 2)
+    k = torch.randn(b, tokens, hkv, d, generator=g).bfloat16().transpose(1, 2)
+    v = torch.randn(b, tokens, hkv, d, generator=g).bfloat16().transpose(1, 2)
+    ref = serve_ops.prefill_attention(q, k, v, None, groups=7, scale=0.125, causal=True)
+    out = b200.b200_prefill_attention(q.cuda(), k.cuda(), v.cuda(), None, scale=0.125, causal=True)
+    close(out, ref, BF16_TOL)
+    masked = b200.b200_prefill_attention(q.cuda(), k.cuda(), v.cuda(),
+                                         serve_ops.causal_mask(b, tokens).cuda(), scale=0.125)
+    close(masked, ref, BF16_TOL)
+
+
+# -------------------------------------------------------------------------- linear ----
+@pytest.mark.parametrize("name", list(cases.LINEAR))
+def test_linear_golden(name, golden_ops):
+    x = cases.linear_inputs(name)
+    out = b200.b200_linear(dev(x["input"]), dev(x["weight"]), dev(x["bias"]))
+    close(out, golden_ops[name]["output"], tol_for(x["input"].dtype))
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 896, 896), (16, 896, 1152), (64, 896, 9728), (64, 4864, 896),
+                                   (33, 896, 130), (256, 896, 896), (500, 512, 330)])
+def test_linear_shapes_and_epilogues(m, k, n):
+    g = torch.Generator().manual_seed(m * 31 + n)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+    bias = torch.randn(n, generator=g).bfloat16()
+    res = torch.randn(m, n, generator=g).bfloat16()
+    ref = serve_ops.linear(x, w, bias)
+    close(b200.b200_linear(x.cuda(), w.cuda(), bias.cuda()), ref, BF16_TOL)
+    close(b200.b200_linear(x.cuda(), w.cuda()), serve_ops.linear(x, w), BF16_TOL)
+    ref_res = serve_ops.residual_add(res, serve_ops.linear(x, w))
+    close(b200.b200_linear(x.cuda(), w.cuda(), residual=res.cuda(), epilogue="residual"), ref_res,
+          BF16_TOL)
+    if n % 2 == 0:
+        gate_w, up_w = w[: n // 2], w[n // 2:]
+        ref_mlp = serve_ops.swiglu(serve_ops.linear(x, gate_w), serve_ops.linear(x, up_w))
+        packed = kernels.interleave_gate_up(gate_w.cuda(), up_w.cuda())
+        close(b200.b200_linear(x.cuda(), packed, epilogue="swiglu"), ref_mlp, BF16_TOL)
+
+
+def test_linear_f32_epilogues():
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(7, 256, generator=g)
+    w = torch.randn(512, 256, generator=g) * 0.05
+    res = torch.randn(7, 512, generator=g)
+    close(b200.b200_linear(x.cuda(), w.cuda(), residual=res.cuda(), epilogue="residual"),
+          res + serve_ops.linear(x, w), F32_TOL)
+    packed = kernels.interleave_gate_up(w[:256].cuda(), w[256:].cuda())
+    close(b200.b200_linear(x.cuda(), packed, epilogue="swiglu"),
+          serve_ops.swiglu(serve_ops.linear(x, w[:256]), serve_ops.linear(x, w[256:])), F32_TOL)
+
+
+def test_linear_repeated_split_k_calls_leave_counters_clean():
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(64, 4864, generator=g).bfloat16().cuda()
+    w = (torch.randn(896, 4864, generator=g) * 0.02).bfloat16().cuda()
+    first = b200.b200_linear(x, w)
+    for _ in range(3):
+        assert torch.equal(b200.b200_linear(x, w), first)  # deterministic split-K reduction
+
+
+# ------------------------------------------------------- ops left to eager upstream ----
+def test_embedding_swiglu_add_argmax_advance():
+    g = torch.Generator().manual_seed(9)
+    table = torch.randn(1000, 896, generator=g).bfloat16()
+    ids = torch.randint(0, 1000, (3, 5), generator=g)
+    exact(b200.b200_embedding(table.cuda(), ids.cuda()), serve_ops.embedding(table, ids))
+    gate = torch.randn(5, 4864, generator=g).bfloat16()
+    up = torch.randn(5, 4864, generator=g).bfloat16()
+    close(b200.b200_swiglu(gate.cuda(), up.cuda()), serve_ops.swiglu(gate, up), 1e-2)
+    a = torch.randn(3, 7, 896, generator=g).bfloat16()
+    b = torch.randn(3, 7, 896, generator=g).bfloat16()
+    exact(b200.b200_add(a.cuda(), b.cuda()), a + b)
+    af, bf = torch.randn(33, generator=g), torch.randn(33, generator=g)
+    exact(b200.b200_add(af.cuda(), bf.cuda()), af + bf)
+    logits = torch.randn(6, 151936, generator=g).bfloat16()
+    logits[2, 77] = 100.0
+    logits[2, 5000] = 100.0  # tie: lowest index wins
+    out = b200.b200_argmax(logits.cuda()).cpu()
+    assert out[2] == 77
+    assert torch.equal(logits.float().max(-1).values, logits.float().gather(1, out.view(-1, 1))[:, 0])
+    lengths = torch.tensor([[1, 5], [7, 63]], device="cuda")
+    b200.b200_advance_lengths(lengths, 1, 64)
+    assert lengths.tolist() == [[2, 6], [8, 64]]
+    kernels.runtime().check_status()
+    b200.b200_advance_lengths(lengths, 1, 64)
+    with pytest.raises(b200.KernelStatusError):
+        kernels.runtime().check_status()
+    strided = torch.randn(4, 6, 10, generator=g).bfloat16().cuda().transpose(0, 2)
+    exact(b200.b200_contiguous(strided), strided.cpu().contiguous())
+
+
+def test_embedding_bad_id_sets_status():
+    table = torch.ones(10, 64, dtype=torch.bfloat16, device="cuda")
+    out = b200.b200_embedding(table, torch.tensor([1, 10, -1], device="cuda"))
+    assert out[0].eq(1).all() and out[1:].eq(0).all()
+    with pytest.raises(b200.KernelStatusError):
+        kernels.runtime().check_status()
+
+
+def test_wrappers_reject_cpu_tensors_and_bad_shapes():
+    x = torch.zeros(2, 4, 1, 64)
+    with pytest.raises(ValueError):
+        b200.b200_rms_norm(x, torch.zeros(64), epsilon=1e-6)
+    q = torch.zeros(2, 4, 1, 64, device="cuda", dtype=torch.bfloat16)
+    kv = torch.zeros(2, 8, 3, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(ValueError):  # 4 query heads over 3 KV heads
+        b200.b200_decode_attention(q, kv, kv, torch.zeros(2, dtype=torch.int64, device="cuda"),
+                                   None, scale=1.0)
