@@ -309,9 +309,15 @@ TilePlan plan_bf16(int64_t m, int64_t k, int64_t n) {
   return t;
 }
 
+// The tile counters sit in a fixed-size region at the start of the workspace, so that calls
+// with different tile grids can share one workspace: the region is only ever touched as
+// counters (and left at zero), never as partial sums. Split-K is used for < 2 * 148 tiles.
+constexpr int64_t kCounterBytes = 4096;
 int64_t counters_bytes(const TilePlan& t) {
-  return (static_cast<int64_t>(t.tiles_m) * t.tiles_n * 4 + 255) / 256 * 256;
+  (void)t;
+  return kCounterBytes;
 }
+static_assert(2 * kNumSMs * 4 <= kCounterBytes, "counter region too small");
 
 template <int BM, int BN, int WM, int WN, int STAGES>
 int launch_tile(const LinearParams& p, const TilePlan& t, cudaStream_t stream) {

@@ -1,0 +1,233 @@
+"""Per-kernel micro-benchmarks of the serve.* operator surface (one JSON line per case).
+
+    python llm-compiler_b200/microbench.py decode_attention --batch 64 --length 4096
+    python llm-compiler_b200/microbench.py decode_attention --sweep
+    python llm-compiler_b200/microbench.py prefill_attention --batch 4 --tokens 4096
+    python llm-compiler_b200/microbench.py linear --m 64 --k 896 --n 9728 --epilogue swiglu
+    python llm-compiler_b200/microbench.py kv_store --batch 16 --tokens 4096
+
+Timing: CUDA events on the launching stream around `--iters` launches after `--warmup`
+launches, rotating over enough independent buffer sets that one round exceeds the 126 MB L2
+(so every launch reads from HBM). Reported bytes / flops are the algorithmic ones:
+  decode attention  512 * sum(len) + 3592 * B bytes at 14/2 heads x 64 (K and V read once, Q,
+                    O, lengths); 4 * Hq * D * sum(len) flops
+  prefill attention 2 * B * Hq * T^2 * D flops (causal half of 4 * B * Hq * T^2 * D)
+  KV store          2 * (read + write) * B * Hkv * T * D * 2 bytes
+  linear            2 * M * K * N flops; (M*K + N*K + M*N) * 2 bytes
+Also the small-case target for `ncu -k regex:<kernel>` captures.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+
+import llm_compiler_b200 as b200  # noqa: E402
+from llm_compiler_b200 import kernels  # noqa: E402
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def time_launches(launch, sets, warmup, iters):
+    for index in range(warmup):
+        launch(index % sets)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for index in range(iters):
+        launch(index % sets)
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) * 1e-3 / iters
+
+
+def graph_time(launch, sets, warmup, iters):
+    """Same, but the `sets` launches of one round are replayed from a CUDA graph so that host
+    launch overhead does not pollute kernels that last a few microseconds."""
+
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for index in range(sets):
+            launch(index)
+    torch.cuda.current_stream().wait_stream(stream)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for index in range(sets):
+            launch(index)
+    rounds = max(1, iters // sets)
+    for _ in range(max(1, warmup // sets)):
+        graph.replay()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    for _ in range(rounds):
+        graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) * 1e-3 / (rounds * sets)
+
+
+def sets_for(bytes_per_set, limit=16):
+    return int(min(limit, max(1, -(-2 * L2_BYTES // max(1, bytes_per_set)))))
+
+
+def decode_attention_case(args, batch, length):
+    hq, hkv, d = args.q_heads, args.kv_heads, args.head_dim
+    capacity = args.capacity or max(length, 64)
+    generator = torch.Generator(device="cuda").manual_seed(batch * 10000 + length)
+    lengths = torch.randint(min(64, length), length + 1, (batch,), generator=generator,
+                            device="cuda") if not args.full_length else \
+        torch.full((batch,), length, device="cuda", dtype=torch.int64)
+    total = int(lengths.sum())
+    kv_bytes = 2 * total * hkv * d * 2
+    sets = sets_for(kv_bytes)
+    # only the first max(len) rows of each buffer are touched: allocate what is read
+    rows = int(lengths.max())
+    keys = [torch.randn(batch, rows, hkv, d, generator=generator, device="cuda",
+                        dtype=torch.float32).bfloat16() for _ in range(sets)]
+    values = [torch.randn_like(k) for k in keys]
+    query = torch.randn(batch, hq, 1, d, device="cuda", dtype=torch.bfloat16)
+    output = torch.empty_like(query)
+
+    def launch(index):
+        kernels.b200_decode_attention(query, keys[index], values[index], lengths, None,
+                                      scale=d ** -0.5, split_tokens=args.split_tokens,
+                                      max_length_hint=length, output=output,
+                                      numerical_mode=args.mode)
+
+    timer = time_launches if args.no_graph else graph_time
+    seconds = timer(launch, sets, args.warmup, args.iters)
+    algorithmic = kv_bytes + 2 * batch * hq * d * 2 + 8 * batch
+    flops = 4 * hq * d * total
+    return {"op": "decode_attention", "batch": batch, "max_length": length, "buffer_rows": rows,
+            "sum_lengths": total, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
+            "split_tokens": args.split_tokens, "buffer_sets": sets, "us": seconds * 1e6,
+            "gbs": algorithmic / seconds / 1e9, "tflops": flops / seconds / 1e12,
+            "algorithmic_bytes": algorithmic}
+
+
+def prefill_attention_case(args):
+    b, t, hq, hkv, d = args.batch, args.tokens, args.q_heads, args.kv_heads, args.head_dim
+    generator = torch.Generator(device="cuda").manual_seed(b * 10000 + t)
+    q = torch.randn(b, t, hq, d, generator=generator, device="cuda").bfloat16().transpose(1, 2)
+    k = torch.randn(b, t, hkv, d, generator=generator, device="cuda").bfloat16().transpose(1, 2)
+    v = torch.randn(b, t, hkv, d, generator=generator, device="cuda").bfloat16().transpose(1, 2)
+    mask = None
+    if args.general_mask:
+        future = torch.triu(torch.ones(t, t, dtype=torch.bool, device="cuda"), diagonal=1)
+        mask = torch.zeros(b, 1, t, t, device="cuda").masked_fill(future, float("-inf"))
+
+    def launch(_):
+        kernels.b200_prefill_attention(q, k, v, mask, scale=d ** -0.5, causal=mask is None,
+                                       numerical_mode=args.mode)
+
+    seconds = time_launches(launch, 1, args.warmup, args.iters)
+    flops = 2 * b * hq * t * t * d
+    return {"op": "prefill_attention", "batch": b, "tokens": t, "general_mask": bool(args.general_mask),
+            "us": seconds * 1e6, "tflops_causal": flops / seconds / 1e12}
+
+
+def kv_store_case(args):
+    b, t, hkv, d = args.batch, args.tokens, args.kv_heads, args.head_dim
+    capacity = args.capacity or 2 * t
+    nbytes = 2 * 2 * b * hkv * t * d * 2
+    sets = sets_for(nbytes)
+    keys = [torch.randn(b, t, hkv, d, device="cuda").bfloat16().transpose(1, 2) for _ in range(sets)]
+    buffers = [torch.zeros(b, capacity, hkv, d, device="cuda", dtype=torch.bfloat16)
+               for _ in range(sets)]
+    positions = torch.zeros(b, dtype=torch.int64, device="cuda")
+
+    def launch(index):
+        kernels.b200_kv_store(buffers[index], buffers[index], keys[index], keys[index], positions)
+
+    seconds = graph_time(launch, sets, args.warmup, args.iters)
+    return {"op": "kv_store", "batch": b, "tokens": t, "us": seconds * 1e6,
+            "gbs": nbytes / seconds / 1e9, "algorithmic_bytes": nbytes}
+
+
+def linear_case(args):
+    m, k, n = args.m, args.k, args.n
+    sets = sets_for(n * k * 2)
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    weights = [(torch.randn(n, k, device="cuda") * 0.02).bfloat16() for _ in range(sets)]
+    residual = torch.randn(m, n, device="cuda").bfloat16() if args.epilogue == "residual" else None
+
+    def launch(index):
+        kernels.b200_linear(x, weights[index], residual=residual, epilogue=args.epilogue)
+
+    timer = time_launches if m > 1024 else graph_time
+    seconds = timer(launch, sets, args.warmup, args.iters)
+    nbytes = (m * k + n * k + m * n) * 2
+    return {"op": "linear", "m": m, "k": k, "n": n, "epilogue": args.epilogue, "us": seconds * 1e6,
+            "gbs": nbytes / seconds / 1e9, "tflops": 2 * m * k * n / seconds / 1e12}
+
+
+def rms_norm_case(args):
+    rows, hidden = args.m, args.k
+    sets = sets_for(rows * hidden * 4)
+    xs = [torch.randn(rows, hidden, device="cuda").bfloat16() for _ in range(sets)]
+    w = torch.randn(hidden, device="cuda").bfloat16()
+
+    def launch(index):
+        kernels.b200_rms_norm(xs[index], w, epsilon=1e-6, round_before_weight=True,
+                              numerical_mode=args.mode)
+
+    seconds = graph_time(launch, sets, args.warmup, args.iters)
+    return {"op": "rms_norm", "rows": rows, "hidden": hidden, "mode": args.mode,
+            "us": seconds * 1e6, "gbs": rows * hidden * 4 / seconds / 1e9}
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("op", choices=["decode_attention", "prefill_attention", "kv_store", "linear",
+                                       "rms_norm"])
+    parser.add_argument("--batch", type=int, default=64)
+    parser.add_argument("--length", type=int, default=4096)
+    parser.add_argument("--tokens", type=int, default=512)
+    parser.add_argument("--capacity", type=int, default=0)
+    parser.add_argument("--q-heads", type=int, default=14)
+    parser.add_argument("--kv-heads", type=int, default=2)
+    parser.add_argument("--head-dim", type=int, default=64)
+    parser.add_argument("--split-tokens", type=int, default=0)
+    parser.add_argument("--m", type=int, default=64)
+    parser.add_argument("--k", type=int, default=896)
+    parser.add_argument("--n", type=int, default=896)
+    parser.add_argument("--epilogue", default="none")
+    parser.add_argument("--mode", default="fast")
+    parser.add_argument("--general-mask", action="store_true")
+    parser.add_argument("--full-length", action="store_true",
+                        help="every sequence at --length instead of uniform [64, length]")
+    parser.add_argument("--sweep", action="store_true",
+                        help="decode attention over batch {1,8,64,256} x length {64,1024,4096,32768}")
+    parser.add_argument("--no-graph", action="store_true")
+    parser.add_argument("--warmup", type=int, default=20)
+    parser.add_argument("--iters", type=int, default=100)
+    args = parser.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("microbench.py needs a CUDA device")
+    if args.op == "decode_attention":
+        shapes = [(b, l) for b in (1, 8, 64, 256) for l in (64, 1024, 4096, 32768)] \
+            if args.sweep else [(args.batch, args.length)]
+        for batch, length in shapes:
+            print(json.dumps(decode_attention_case(args, batch, length)), flush=True)
+    elif args.op == "prefill_attention":
+        print(json.dumps(prefill_attention_case(args)))
+    elif args.op == "kv_store":
+        print(json.dumps(kv_store_case(args)))
+    elif args.op == "linear":
+        print(json.dumps(linear_case(args)))
+    else:
+        print(json.dumps(rms_norm_case(args)))
+    kernels.runtime().check_status()
+
+
+if __name__ == "__main__":
+    main()
