@@ -51,6 +51,7 @@ extern "C" {
 #define B200_STATUS_LENGTH_OVER_MASK 2  /* lengths[b] > mask length: clamped              */
 #define B200_STATUS_BAD_TOKEN_ID 4      /* embedding id outside [0, vocab): row zeroed    */
 #define B200_STATUS_BAD_POSITION 8      /* negative KV position: write skipped            */
+#define B200_STATUS_WAIT_TIMEOUT 16     /* a bounded in-kernel wait gave up: result invalid */
 
 /* Version / build probe. Returns 100 * major + minor of this ABI. */
 int b200_abi_version(void);
@@ -106,7 +107,7 @@ int b200_rope_table(const int64_t* position_ids, const float* inv_freq, void* co
  * round_before_weight != 0: y = r(w * r(x * rsqrt(mean(x^2) + eps)));
  * otherwise y = r(x * rsqrt(..) * float(w)).
  * mode FAST sums x^2 in a tree; mode PYTORCH_COMPATIBLE reproduces the summation
- * order of the CPU executor's float sum (16 vector lanes x 4 interleaved
+ * order of the CPU executor's float sum (8 vector lanes x 4 interleaved
  * accumulators, cascaded) with IEEE sqrt and divide, so the result is bit-identical
  * to the reference's CPU executor. */
 int b200_rms_norm(const void* input, const void* weight, void* output, int64_t rows,
@@ -159,8 +160,8 @@ int b200_prefill_attention(const void* query, const void* key, const void* value
  * (execution.py:694-705).
  * epilogue: 0 none; 1 residual add, y = r(r(acc + bias) + residual) (the unlowered
  * aten.add.Tensor that follows o_proj / down_proj, qwen2.py:299-304); 2 SwiGLU over
- * row-interleaved gate/up weights: W holds 2N rows (gate_j, up_j alternating) and
- * y[M,N] = r(r(silu(r(gate))) * r(up)) (qwen2.py:262-264).
+ * row-interleaved gate/up weights: W holds n rows (gate_j, up_j alternating), the output is
+ * [M, n/2] and y[m,j] = r(r(silu(r(gate_j))) * r(up_j)) (qwen2.py:262-264).
  * Workspace (split-K partial sums + tile counters): b200_linear_workspace_bytes. */
 #define B200_EPILOGUE_NONE 0
 #define B200_EPILOGUE_RESIDUAL 1

@@ -21,6 +21,7 @@ STATUS_KV_OVERFLOW = 1
 STATUS_LENGTH_OVER_MASK = 2
 STATUS_BAD_TOKEN_ID = 4
 STATUS_BAD_POSITION = 8
+STATUS_WAIT_TIMEOUT = 16
 
 ERR_BAD_ARGUMENT, ERR_UNSUPPORTED, ERR_ALIGNMENT = -1, -2, -3
 ERR_WORKSPACE, ERR_LAUNCH, ERR_TOO_LARGE = -4, -5, -6

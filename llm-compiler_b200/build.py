@@ -74,7 +74,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
                 future.result()
     if force or jobs or _stale(LIBRARY, objects):
         command = [nvcc, "-shared", "-o", str(LIBRARY), *map(str, objects),
-                   "-gencode", "arch=compute_100a,code=sm_100a", "-lcuda"]
+                   "-gencode", "arch=compute_100a,code=sm_100a"]
         result = subprocess.run(command, capture_output=True, text=True)
         if result.returncode != 0:
             raise RuntimeError(f"link failed:\n{result.stdout}\n{result.stderr}")

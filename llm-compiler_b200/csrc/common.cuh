@@ -140,6 +140,55 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// ---- TMA (tensor-map bulk copies) and mbarriers ----------------------------------
+__device__ __forceinline__ void mbarrier_init(uint32_t bar, uint32_t arrive_count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%1], %0;\n" ::"r"(arrive_count), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_mbarrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+}
+__device__ __forceinline__ void mbarrier_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%1], %0;\n" ::"r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ bool mbarrier_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred P1;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P1;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait: gives up after `limit` polls (each poll may itself block for a
+// hardware-defined slice) instead of spinning forever; the caller records the failure.
+__device__ __forceinline__ bool mbarrier_wait_bounded(uint32_t bar, uint32_t parity,
+                                                      uint32_t limit = 4000000u) {
+  for (uint32_t i = 0; i < limit; ++i)
+    if (mbarrier_try_wait(bar, parity)) return true;
+  return false;
+}
+// One 3-D box of a tiled tensor map into shared memory; completion is signalled on `bar`.
+// No cluster multicast anywhere: every CTA fetches its own tiles.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tensor_map, uint32_t bar,
+                                            int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tensor_map, uint32_t bar,
+                                            int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(tensor_map)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+
 // Shared-memory tiles whose rows are 128 bytes (64 bf16) are stored with the 16-byte
 // chunk index XOR-ed by (row & 7): ldmatrix reads of 8 consecutive rows at one logical
 // chunk then touch 8 different bank groups.

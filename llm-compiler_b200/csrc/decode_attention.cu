@@ -5,16 +5,24 @@
 // split of `split_tokens` tokens) and serves ALL grouped query heads of that KV head
 // from one read of K and V: the G query heads are the M rows (padded to 16) of
 // warp-level tensor-core tiles, S = Q K^T and O += P V. The CTA's 4 warps take
-// interleaved 16-token sub-tiles; each warp streams its own sub-tiles through a
-// private multi-stage cp.async ring (16-byte copies, XOR-swizzled rows), so the main
-// loop has no CTA-wide barrier. Loop bounds come from lengths[b] on the device, never
-// from the capacity. Warps merge their (max, sum, O) partials through shared memory;
-// with more than one split the CTA writes an fp32 partial and a small merge kernel
-// combines the splits.
+// interleaved sub-tiles of 32 tokens (16 at head_dim 128); each warp streams its own
+// sub-tiles through a private 3-stage ring in shared memory, so the main loop has no
+// CTA-wide barrier. The ring is filled by TMA: one elected lane issues one tensor-map box
+// copy for K and one for V per stage (128-byte swizzled rows, completion on a per-stage
+// mbarrier, every wait bounded); a 16-byte cp.async path with the same layout is kept as
+// the variant for buffers a tensor map cannot describe. Loop bounds come from lengths[b]
+// on the device, never from the capacity. The softmax keeps the running maximum in the
+// raw-score domain (one FFMA + ex2 per probability) and rescales O only when a maximum
+// actually moved. Warps merge their (max, sum, O) partials through shared memory; with
+// more than one split the CTA parks an fp32 partial in the workspace and the CTA that
+// arrives last at the (sequence, head block) counter combines the splits in order.
 //
 // Algorithmic traffic per call: every valid K and V byte once (2 * len * Hkv * D * 2 B
 // per sequence) + Q + O; the split partials add 4*(D+2) bytes per (q head, split).
+#include <cuda.h>
 #include <math.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include "common.cuh"
 
@@ -23,8 +31,10 @@ namespace {
 
 constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
-constexpr int kSubTokens = 16;  // tokens per warp step (two n=8 MMA tiles)
+constexpr int kStages = 3;
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int64_t kCounterBytes = 65536;  // fixed region: calls of any shape share a workspace
+constexpr int64_t kMaxCounters = kCounterBytes / 4;
 
 struct DecodeParams {
   const __nv_bfloat16* q;
@@ -33,8 +43,9 @@ struct DecodeParams {
   const int64_t* lengths;
   const void* mask;
   __nv_bfloat16* out;
-  float* ws_o;   // [B, Hq, splits, D]
-  float* ws_ml;  // [B, Hq, splits, 2]  (max in log2 domain, sum)
+  float* ws_o;    // [B, Hq, splits, D]
+  float* ws_ml;   // [B, Hq, splits, 2]  (max in log2 domain, sum)
+  int* counters;  // [B * head blocks], zero between calls; nullptr = separate merge kernel
   int32_t* status;
   int64_t q_batch_stride, q_head_stride, mask_batch_stride;
   int batch, q_heads, kv_heads, groups, capacity, mask_len, split_tokens, num_splits;
@@ -54,24 +65,33 @@ __device__ __forceinline__ float load_mask(const void* mask, int dtype, int64_t 
   return __bfloat162float(static_cast<const __nv_bfloat16*>(mask)[index]);
 }
 
-template <int D>
+// A tile of TOK rows x D bf16 is stored as D/64 panels of [TOK][64] (128-byte rows), the
+// 16-byte chunk index XOR-ed with (row & 7): the layout a 128B-swizzled TMA box produces.
+template <int TOK>
 __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
-  // rows of D bf16; 16-byte chunks XOR-swizzled inside each 128-byte segment
-  return static_cast<uint32_t>(row * (D * 2) + (((chunk & ~7) | ((chunk ^ row) & 7)) << 4));
+  return static_cast<uint32_t>((chunk >> 3) * (TOK * 128) + row * 128 +
+                               (((chunk ^ row) & 7) << 4));
 }
 
-template <int D, int STAGES, bool WIDE>  // WIDE: groups > 8, rows 8..15 of the tile are live
+// FAST: no mask and fast numerics (the serving engine's case); otherwise mask and the
+// compatible rounding are runtime flags.
+template <int D, int TOK, bool WIDE, bool FAST, bool TMA>
 __global__ void __launch_bounds__(kThreads)
-decode_attention_kernel(const DecodeParams p) {
+decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
+                        const __grid_constant__ CUtensorMap vmap) {
   constexpr int kChunksPerRow = D / 8;
-  constexpr int kTileBytes = kSubTokens * D * 2;    // one of K or V, one stage
+  constexpr int kTileBytes = TOK * D * 2;  // one of K or V, one stage
   constexpr int kStageBytes = 2 * kTileBytes;
-  constexpr int kWarpBytes = STAGES * kStageBytes;
-  constexpr int kCopiesPerLane = kSubTokens * kChunksPerRow / 32;
+  constexpr int kWarpBytes = kStages * kStageBytes;
+  constexpr int kCopiesPerLane = TOK * kChunksPerRow / 32;
   constexpr int kKSteps = D / 16;
   constexpr int kNTiles = D / 8;
+  constexpr int kSTiles = TOK / 8;  // score n-tiles per step
+  constexpr int kRows = WIDE ? 2 : 1;
 
   extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full_bar[kWarps][kStages];
+  __shared__ int merge_flag;
 
   const int split = blockIdx.x;
   const int head_block = blockIdx.y;  // kv head * blocks-per-kv-head + 16-row block
@@ -118,158 +138,260 @@ decode_attention_kernel(const DecodeParams p) {
   }
 
   const uint32_t warp_smem = smem_u32(smem) + warp * kWarpBytes;
+  const uint32_t bar0 = smem_u32(&full_bar[warp][0]);
+  const int64_t token_stride = static_cast<int64_t>(p.kv_heads) * D;
   const __nv_bfloat16* kglob = p.kbuf + (static_cast<int64_t>(b) * p.capacity * p.kv_heads + kvh) * D;
   const __nv_bfloat16* vglob = p.vbuf + (static_cast<int64_t>(b) * p.capacity * p.kv_heads + kvh) * D;
-  const int64_t token_stride = static_cast<int64_t>(p.kv_heads) * D;
 
-  // sub-tile j of this split covers tokens start + j*16 ...; warp w owns j = w, w+4, ...
-  const int n_sub = (end - start + kSubTokens - 1) / kSubTokens;
+  // sub-tile j of this split covers tokens start + j*TOK ...; warp w owns j = w, w+4, ...
+  const int n_sub = (end - start + TOK - 1) / TOK;
   const int my_count = n_sub > warp ? (n_sub - warp + kWarps - 1) / kWarps : 0;
 
-  auto issue_load = [&](int it) {
-    const int t0 = start + (it * kWarps + warp) * kSubTokens;
-    const uint32_t kdst = warp_smem + (it % STAGES) * kStageBytes;
-    const uint32_t vdst = kdst + kTileBytes;
+  if (TMA) {
+    if (lane == 0) {
+#pragma unroll
+      for (int s = 0; s < kStages; ++s) mbarrier_init(bar0 + s * 8, 1);
+      fence_mbarrier_init();
+    }
+    __syncwarp();
+  }
+
+  // per-lane constants of the cp.async variant: this lane's rows / chunks inside a sub-tile
+  uint32_t lane_soff[TMA ? 1 : kCopiesPerLane];
+  int64_t lane_goff[TMA ? 1 : kCopiesPerLane];
+  int lane_row[TMA ? 1 : kCopiesPerLane];
+  if (!TMA) {
 #pragma unroll
     for (int i = 0; i < kCopiesPerLane; ++i) {
       const int id = i * 32 + lane;
-      const int r = id / kChunksPerRow;
-      const int c = id % kChunksPerRow;
-      const int token = t0 + r;
-      const bool valid = token < end;
-      const int64_t goff = valid ? token * token_stride + c * 8 : 0;
-      const uint32_t soff = tile_offset<D>(r, c);
-      cp_async16_zfill(kdst + soff, kglob + goff, valid ? 16 : 0);
-      cp_async16_zfill(vdst + soff, vglob + goff, valid ? 16 : 0);
+      const int r = id / kChunksPerRow, c = id % kChunksPerRow;
+      lane_row[i] = r;
+      lane_soff[i] = tile_offset<TOK>(r, c);
+      lane_goff[i] = r * token_stride + c * 8;
+    }
+  }
+
+  auto issue_load = [&](int it) {
+    const int t0 = start + (it * kWarps + warp) * TOK;
+    const uint32_t kdst = warp_smem + (it % kStages) * kStageBytes;
+    const uint32_t vdst = kdst + kTileBytes;
+    if (TMA) {
+      if (lane == 0) {
+        const uint32_t bar = bar0 + (it % kStages) * 8;
+        mbarrier_arrive_expect_tx(bar, kStageBytes);
+        const int row = b * p.capacity + t0;  // rows past the tensor end are zero-filled
+#pragma unroll
+        for (int panel = 0; panel < D / 64; ++panel) {
+          tma_load_3d(kdst + panel * (TOK * 128), &kmap, bar, panel * 64, kvh, row);
+          tma_load_3d(vdst + panel * (TOK * 128), &vmap, bar, panel * 64, kvh, row);
+        }
+      }
+    } else {
+      const __nv_bfloat16* ksrc = kglob + t0 * token_stride;
+      const __nv_bfloat16* vsrc = vglob + t0 * token_stride;
+      if (t0 + TOK <= end) {
+#pragma unroll
+        for (int i = 0; i < kCopiesPerLane; ++i) {
+          cp_async16(kdst + lane_soff[i], ksrc + lane_goff[i]);
+          cp_async16(vdst + lane_soff[i], vsrc + lane_goff[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < kCopiesPerLane; ++i) {
+          const bool valid = t0 + lane_row[i] < end;
+          cp_async16_zfill(kdst + lane_soff[i], valid ? ksrc + lane_goff[i] : kglob, valid ? 16 : 0);
+          cp_async16_zfill(vdst + lane_soff[i], valid ? vsrc + lane_goff[i] : vglob, valid ? 16 : 0);
+        }
+      }
     }
   };
 
-  float m_run[2] = {-INFINITY, -INFINITY};  // running max, log2 domain (rows r0, r0+8)
-  float l_run[2] = {0.0f, 0.0f};            // this thread's share of the running sum
+  // running max: raw-score domain when FAST, log2 domain otherwise (rows r0, r0 + 8)
+  float m_run[2] = {-INFINITY, -INFINITY};
+  float l_run[2] = {0.0f, 0.0f};  // this thread's share of the running sum
   float oacc[kNTiles][4];
 #pragma unroll
   for (int i = 0; i < kNTiles; ++i)
     oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.0f;
 
   const float scale_log2 = p.scale * kLog2e;
+  const float softmax_scale = FAST ? scale_log2 : 1.0f;
+  bool timed_out = false;
 
 #pragma unroll
-  for (int s = 0; s < STAGES - 1; ++s) {
+  for (int s = 0; s < kStages - 1; ++s) {
     if (s < my_count) issue_load(s);
-    cp_async_commit();
+    if (!TMA) cp_async_commit();
   }
 
   for (int it = 0; it < my_count; ++it) {
-    cp_async_wait<STAGES - 2>();
-    __syncwarp();
-    if (it + STAGES - 1 < my_count) issue_load(it + STAGES - 1);
-    cp_async_commit();
+    if (TMA) {
+      if (!mbarrier_wait_bounded(bar0 + (it % kStages) * 8, (it / kStages) & 1)) {
+        timed_out = true;
+        break;
+      }
+    } else {
+      cp_async_wait<kStages - 2>();
+    }
+    __syncwarp();  // every lane is done reading the stage that is refilled next
+    if (it + kStages - 1 < my_count) issue_load(it + kStages - 1);
+    if (!TMA) cp_async_commit();
 
-    const int t0 = start + (it * kWarps + warp) * kSubTokens;
-    const uint32_t ksm = warp_smem + (it % STAGES) * kStageBytes;
+    const int t0 = start + (it * kWarps + warp) * TOK;
+    const uint32_t ksm = warp_smem + (it % kStages) * kStageBytes;
     const uint32_t vsm = ksm + kTileBytes;
+    const bool partial = t0 + TOK > end;
 
-    // ---- S = Q K^T : 16 x 16 ----
-    float sacc[2][4];
+    if (TMA && partial) {
+      // a box copy brings whole rows: rows past `end` hold whatever the buffer holds, and a
+      // non-finite V there would poison 0 * V. Zero them (K is masked by score instead).
+      for (int id = lane; id < TOK * kChunksPerRow; id += 32) {
+        const int r = id / kChunksPerRow, c = id % kChunksPerRow;
+        if (t0 + r >= end)
+          *reinterpret_cast<uint4*>(smem + (vsm - smem_u32(smem)) + tile_offset<TOK>(r, c)) =
+              make_uint4(0, 0, 0, 0);
+      }
+      __syncwarp();
+    }
+
+    // ---- S = Q K^T : 16 x TOK ----
+    float sacc[kSTiles][4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.0f;
+    for (int i = 0; i < kSTiles; ++i) sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.0f;
     {
       const int mat = lane >> 3;
       const int krow = ((mat >> 1) << 3) + (lane & 7);
 #pragma unroll
       for (int ks = 0; ks < kKSteps; ++ks) {
-        uint32_t kb[4];
-        ldmatrix_x4(kb, ksm + tile_offset<D>(krow, ks * 2 + (mat & 1)));
-        mma_bf16_16816(sacc[0], qa[ks], kb[0], kb[1]);
-        mma_bf16_16816(sacc[1], qa[ks], kb[2], kb[3]);
+#pragma unroll
+        for (int np = 0; np < kSTiles / 2; ++np) {
+          uint32_t kb[4];
+          ldmatrix_x4(kb, ksm + tile_offset<TOK>(np * 16 + krow, ks * 2 + (mat & 1)));
+          mma_bf16_16816(sacc[np * 2], qa[ks], kb[0], kb[1]);
+          mma_bf16_16816(sacc[np * 2 + 1], qa[ks], kb[2], kb[3]);
+        }
       }
     }
 
-    // ---- scale, mask, online softmax (log2 domain) ----
-    float row_max[2] = {-INFINITY, -INFINITY};
+    // ---- scores -> softmax domain, tail masking ----
+    if (!FAST) {
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
+      for (int nt = 0; nt < kSTiles; ++nt) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        if (!WIDE && e >= 2) continue;
-        const int token = t0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-        float s;
-        if (p.compat) {
-          // reference order: r(q k^T) -> r(. * scale) -> fp32 (+ mask)
-          s = round_bf16(round_bf16(sacc[nt][e]) * p.scale) * kLog2e;
-        } else {
-          s = sacc[nt][e] * scale_log2;
+        for (int e = 0; e < 2 * kRows; ++e) {
+          const int token = t0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+          float s;
+          if (p.compat)  // reference order: r(q k^T) -> r(. * scale) -> fp32 (+ mask)
+            s = round_bf16(round_bf16(sacc[nt][e]) * p.scale) * kLog2e;
+          else
+            s = sacc[nt][e] * scale_log2;
+          if (token < end) {
+            if (p.mask != nullptr)
+              s += load_mask(p.mask, p.mask_dtype, b * p.mask_batch_stride + token) * kLog2e;
+          } else {
+            s = -INFINITY;
+          }
+          sacc[nt][e] = s;
         }
-        if (token < end) {
-          if (p.mask != nullptr)
-            s += load_mask(p.mask, p.mask_dtype, b * p.mask_batch_stride + token) * kLog2e;
-        } else {
-          s = -INFINITY;
+      }
+    } else if (partial) {
+#pragma unroll
+      for (int nt = 0; nt < kSTiles; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 2 * kRows; ++e) {
+          const int token = t0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+          if (token >= end) sacc[nt][e] = -INFINITY;
         }
-        sacc[nt][e] = s;
-        row_max[e >> 1] = fmaxf(row_max[e >> 1], s);
       }
     }
-    uint32_t pa[4];
-    float alpha[2];
+
+    // ---- online softmax ----
+    float m_new[2], m_safe[2];
+    bool moved = false;
 #pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      if (!WIDE && r == 1) {
-        alpha[1] = 1.0f;
-        continue;
-      }
-      float mx = row_max[r];
+    for (int r = 0; r < kRows; ++r) {
+      float mx = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < kSTiles; ++nt)
+        mx = fmaxf(mx, fmaxf(sacc[nt][2 * r], sacc[nt][2 * r + 1]));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-      const float m_new = fmaxf(m_run[r], mx);
-      const float m_safe = m_new == -INFINITY ? 0.0f : m_new;
-      alpha[r] = fast_exp2(m_run[r] - m_safe);  // exp2(-inf) = 0 on the first tile
-      m_run[r] = m_new;
+      m_new[r] = fmaxf(m_run[r], mx);
+      m_safe[r] = m_new[r] == -INFINITY ? 0.0f : m_new[r];
+      moved = moved || m_new[r] != m_run[r];
+    }
+    if (__any_sync(0xffffffffu, moved)) {
+      float alpha[2] = {1.0f, 1.0f};
+#pragma unroll
+      for (int r = 0; r < kRows; ++r) {
+        alpha[r] = fast_exp2((m_run[r] - m_safe[r]) * softmax_scale);  // exp2(-inf) = 0 at first
+        m_run[r] = m_new[r];
+        l_run[r] *= alpha[r];
+      }
+#pragma unroll
+      for (int i = 0; i < kNTiles; ++i) {
+        oacc[i][0] *= alpha[0];
+        oacc[i][1] *= alpha[0];
+        if (WIDE) {
+          oacc[i][2] *= alpha[1];
+          oacc[i][3] *= alpha[1];
+        }
+      }
+    }
+    uint32_t pa[kSTiles][2];  // [n-tile][row half] packed bf16 probabilities
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) {
+      const float bias = -m_safe[r] * softmax_scale;
       float sum = 0.0f;
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt) {
-        const float p0 = fast_exp2(sacc[nt][2 * r] - m_safe);
-        const float p1 = fast_exp2(sacc[nt][2 * r + 1] - m_safe);
+      for (int nt = 0; nt < kSTiles; ++nt) {
+        const float p0 = fast_exp2(fmaf(sacc[nt][2 * r], softmax_scale, bias));
+        const float p1 = fast_exp2(fmaf(sacc[nt][2 * r + 1], softmax_scale, bias));
         sum += p0 + p1;
-        pa[nt * 2 + r] = pack_bf16x2(p0, p1);
+        pa[nt][r] = pack_bf16x2(p0, p1);
       }
-      l_run[r] = l_run[r] * alpha[r] + sum;
-    }
-    if (!WIDE) {
-      pa[1] = 0u;
-      pa[3] = 0u;
-    }
-#pragma unroll
-    for (int i = 0; i < kNTiles; ++i) {
-      oacc[i][0] *= alpha[0];
-      oacc[i][1] *= alpha[0];
-      if (WIDE) {
-        oacc[i][2] *= alpha[1];
-        oacc[i][3] *= alpha[1];
-      }
+      l_run[r] += sum;
     }
 
-    // ---- O += P V : (16 x 16) x (16 x D) ----
+    // ---- O += P V : (16 x TOK) x (TOK x D) ----
     {
       const int mat = lane >> 3;
       const int vrow = ((mat & 1) << 3) + (lane & 7);
 #pragma unroll
-      for (int np = 0; np < kNTiles / 2; ++np) {
-        uint32_t vb[4];
-        ldmatrix_x4_trans(vb, vsm + tile_offset<D>(vrow, np * 2 + (mat >> 1)));
-        mma_bf16_16816(oacc[np * 2], pa, vb[0], vb[1]);
-        mma_bf16_16816(oacc[np * 2 + 1], pa, vb[2], vb[3]);
+      for (int kk = 0; kk < TOK / 16; ++kk) {
+        uint32_t a[4];
+        a[0] = pa[kk * 2][0];
+        a[1] = WIDE ? pa[kk * 2][1] : 0u;
+        a[2] = pa[kk * 2 + 1][0];
+        a[3] = WIDE ? pa[kk * 2 + 1][1] : 0u;
+#pragma unroll
+        for (int np = 0; np < kNTiles / 2; ++np) {
+          uint32_t vb[4];
+          ldmatrix_x4_trans(vb, vsm + tile_offset<TOK>(kk * 16 + vrow, np * 2 + (mat >> 1)));
+          mma_bf16_16816(oacc[np * 2], a, vb[0], vb[1]);
+          mma_bf16_16816(oacc[np * 2 + 1], a, vb[2], vb[3]);
+        }
       }
     }
   }
-  cp_async_wait<0>();
+  if (TMA) {
+    if (timed_out) {
+      if (lane == 0 && p.status != nullptr) atomicOr(p.status, B200_STATUS_WAIT_TIMEOUT);
+      // give the copies still in flight a bounded chance to land before the CTA retires
+      for (int it = 0; it < my_count && it < kStages; ++it)
+        mbarrier_wait_bounded(bar0 + (it % kStages) * 8, 0, 100000u);
+    }
+  } else {
+    cp_async_wait<0>();
+  }
   __syncwarp();
 
-  // quad-reduce the row sums
+  // quad-reduce the row sums; bring the maxima to the log2 domain
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
     l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    if (FAST) m_run[r] *= scale_log2;  // -inf stays -inf (scale > 0)
   }
 
   // ---- merge the 4 warps through shared memory (each warp reuses its own ring) ----
@@ -280,12 +402,10 @@ decode_attention_kernel(const DecodeParams p) {
     const int col = (lane & 3) * 2;
 #pragma unroll
     for (int nt = 0; nt < kNTiles; ++nt) {
-      my_o[r0 * D + nt * 8 + col] = oacc[nt][0];
-      my_o[r0 * D + nt * 8 + col + 1] = oacc[nt][1];
-      if (WIDE) {
-        my_o[(r0 + 8) * D + nt * 8 + col] = oacc[nt][2];
-        my_o[(r0 + 8) * D + nt * 8 + col + 1] = oacc[nt][3];
-      }
+      *reinterpret_cast<float2*>(my_o + r0 * D + nt * 8 + col) = make_float2(oacc[nt][0], oacc[nt][1]);
+      if (WIDE)
+        *reinterpret_cast<float2*>(my_o + (r0 + 8) * D + nt * 8 + col) =
+            make_float2(oacc[nt][2], oacc[nt][3]);
     }
     if ((lane & 3) == 0) {
       my_ml[r0 * 2] = m_run[0];
@@ -328,9 +448,58 @@ decode_attention_kernel(const DecodeParams p) {
       }
     }
   }
+  if (p.num_splits == 1 || p.counters == nullptr) return;
+
+  // ---- the CTA that arrives last for this (sequence, head block) combines the splits ----
+  int used = (n_tokens + p.split_tokens - 1) / p.split_tokens;
+  if (used < 1) used = 1;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* counter = p.counters + b * gridDim.y + head_block;
+    const int arrived = atomicAdd(counter, 1);
+    merge_flag = arrived == used - 1;
+    if (merge_flag) *counter = 0;  // ready for the next call on this workspace
+  }
+  __syncthreads();
+  if (!merge_flag) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < rows * D; idx += kThreads) {
+    const int row = idx / D;
+    const int col = idx % D;
+    const int hq = kvh * p.groups + g0 + row;
+    const int64_t base = (static_cast<int64_t>(b) * p.q_heads + hq) * p.num_splits;
+    float m_all = -INFINITY;
+    for (int s = 0; s < used; ++s) m_all = fmaxf(m_all, __ldcg(p.ws_ml + (base + s) * 2));
+    float l_all = 0.0f, o_all = 0.0f;
+    int s = 0;
+    for (; s + 4 <= used; s += 4) {  // four independent loads in flight per round
+      float m4[4], l4[4], o4[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        m4[j] = __ldcg(p.ws_ml + (base + s + j) * 2);
+        l4[j] = __ldcg(p.ws_ml + (base + s + j) * 2 + 1);
+        o4[j] = __ldcg(p.ws_o + (base + s + j) * D + col);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float wgt = m4[j] == -INFINITY ? 0.0f : fast_exp2(m4[j] - m_all);
+        l_all += l4[j] * wgt;
+        o_all += o4[j] * wgt;
+      }
+    }
+    for (; s < used; ++s) {
+      const float m = __ldcg(p.ws_ml + (base + s) * 2);
+      const float wgt = m == -INFINITY ? 0.0f : fast_exp2(m - m_all);
+      l_all += __ldcg(p.ws_ml + (base + s) * 2 + 1) * wgt;
+      o_all += __ldcg(p.ws_o + (base + s) * D + col) * wgt;
+    }
+    p.out[(static_cast<int64_t>(b) * p.q_heads + hq) * D + col] = __float2bfloat16_rn(o_all / l_all);
+  }
 }
 
-// Combines the per-split partials of one (sequence, q head). blockDim.x == D.
+// Combines the per-split partials of one (sequence, q head) when the in-kernel merge is
+// not available (more head blocks than counters). blockDim.x == D.
 __global__ void decode_merge_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml,
                                     const int64_t* __restrict__ lengths,
                                     __nv_bfloat16* __restrict__ out, int q_heads, int head_dim,
@@ -426,35 +595,88 @@ __global__ void decode_attention_f32_kernel(const float* __restrict__ q,
 }
 
 template <int D>
-constexpr int stages_for() {
-  return D <= 64 ? 4 : 3;
+constexpr int tokens_per_step() {
+  return D <= 64 ? 32 : 16;
 }
 
-template <int D>
-int smem_bytes_for() {
-  return kWarps * stages_for<D>() * 2 * kSubTokens * D * 2;
+// 128B-swizzled box of TOK tokens x 64 elements of one KV head out of the B x C x Hkv x D buffer,
+// seen as a 3-D tensor (D, Hkv, B*C).
+bool make_kv_tensor_map(CUtensorMap* map, const void* buffer, int64_t batch, int64_t capacity,
+                        int64_t kv_heads, int64_t head_dim, int tokens_per_box) {
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(kv_heads),
+                              static_cast<cuuint64_t>(batch * capacity)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(head_dim * 2),
+                                 static_cast<cuuint64_t>(kv_heads * head_dim * 2)};
+  const cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(tokens_per_box)};
+  const cuuint32_t element_strides[3] = {1, 1, 1};
+  if (batch * capacity >= (int64_t(1) << 31)) return false;
+  // The driver entry point is resolved through the runtime, so the library links against
+  // nothing but cudart and still loads on a machine without a GPU driver.
+  using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeTiled encode = nullptr;
+  static bool resolved = false;
+  if (!resolved) {
+    void* entry = nullptr;
+    cudaDriverEntryPointQueryResult query;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &query) ==
+            cudaSuccess &&
+        query == cudaDriverEntryPointSuccess)
+      encode = reinterpret_cast<EncodeTiled>(entry);
+    resolved = true;
+  }
+  if (encode == nullptr) return false;
+  const CUresult result = encode(
+      map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(buffer), dims, strides, box,
+      element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return result == CUDA_SUCCESS;
+}
+
+bool use_tma_loads() {
+  const char* value = getenv("B200_DECODE_ATTENTION_LOADS");
+  return value == nullptr || strcmp(value, "cp.async") != 0;
+}
+
+template <int D, bool WIDE, bool FAST, bool TMA>
+int launch_variant(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap,
+                   cudaStream_t stream) {
+  constexpr int TOK = tokens_per_step<D>();
+  constexpr int smem = kWarps * kStages * 2 * TOK * D * 2;
+  const int row_blocks = (p.groups + 15) / 16;
+  dim3 grid(p.num_splits, p.kv_heads * row_blocks, p.batch);
+  auto kernel = decode_attention_kernel<D, TOK, WIDE, FAST, TMA>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    return B200_ERR_LAUNCH;
+  kernel<<<grid, kThreads, smem, stream>>>(p, kmap, vmap);
+  return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
 
 template <int D>
 int launch_bf16(const DecodeParams& p, cudaStream_t stream) {
-  constexpr int STAGES = stages_for<D>();
-  const int smem = smem_bytes_for<D>();
-  const int row_blocks = (p.groups + 15) / 16;
-  dim3 grid(p.num_splits, p.kv_heads * row_blocks, p.batch);
-  cudaError_t err;
-  if (p.groups > 8) {
-    auto kernel = decode_attention_kernel<D, STAGES, true>;
-    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (err != cudaSuccess) return B200_ERR_LAUNCH;
-    kernel<<<grid, kThreads, smem, stream>>>(p);
+  const bool fast = p.mask == nullptr && !p.compat && p.scale > 0.0f;
+  const bool wide = p.groups > 8;
+  CUtensorMap kmap, vmap;
+  memset(&kmap, 0, sizeof(kmap));
+  memset(&vmap, 0, sizeof(vmap));
+  bool tma = use_tma_loads();
+  if (tma)
+    tma = make_kv_tensor_map(&kmap, p.kbuf, p.batch, p.capacity, p.kv_heads, D, tokens_per_step<D>()) &&
+          make_kv_tensor_map(&vmap, p.vbuf, p.batch, p.capacity, p.kv_heads, D, tokens_per_step<D>());
+  int code;
+#define B200_DISPATCH(W, F, T) code = launch_variant<D, W, F, T>(p, kmap, vmap, stream)
+  if (tma) {
+    if (wide) { if (fast) B200_DISPATCH(true, true, true); else B200_DISPATCH(true, false, true); }
+    else { if (fast) B200_DISPATCH(false, true, true); else B200_DISPATCH(false, false, true); }
   } else {
-    auto kernel = decode_attention_kernel<D, STAGES, false>;
-    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (err != cudaSuccess) return B200_ERR_LAUNCH;
-    kernel<<<grid, kThreads, smem, stream>>>(p);
+    if (wide) { if (fast) B200_DISPATCH(true, true, false); else B200_DISPATCH(true, false, false); }
+    else { if (fast) B200_DISPATCH(false, true, false); else B200_DISPATCH(false, false, false); }
   }
-  if (cudaGetLastError() != cudaSuccess) return B200_ERR_LAUNCH;
-  if (p.num_splits > 1) {
+#undef B200_DISPATCH
+  if (code != B200_OK) return code;
+  if (p.num_splits > 1 && p.counters == nullptr) {
     decode_merge_kernel<<<p.batch * p.q_heads, D, 0, stream>>>(
         p.ws_o, p.ws_ml, p.lengths, p.out, p.q_heads, D, p.num_splits, p.split_tokens,
         p.mask_len);
@@ -464,17 +686,35 @@ int launch_bf16(const DecodeParams& p, cudaStream_t stream) {
 
 int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
-// Tokens per split when the caller does not choose: enough CTAs for ~4 waves of
-// 148 SMs x 3 resident CTAs, never below 256 tokens (a warp then still pipelines
-// 4 sub-tiles), rounded to the 64 tokens the 4 warps cover per step.
+// Tokens per split when the caller does not choose. The grid is (splits x head blocks x
+// batch) CTAs over 148 SMs x 2 resident CTAs; the score of a candidate split count is the
+// fill of its last wave times the share of a CTA's life spent streaming rather than ramping
+// its pipeline up (about 96 tokens' worth). Splits are multiples of the 128 tokens the four
+// warps cover per step and never shorter than 256 tokens.
 int64_t default_split_tokens(int64_t batch, int64_t head_blocks, int64_t max_length) {
-  const int64_t target_ctas = static_cast<int64_t>(kNumSMs) * 3 * 4;
+  const int64_t slots = static_cast<int64_t>(kNumSMs) * 2;
   const int64_t units = batch * head_blocks;
-  int64_t splits = units > 0 ? target_ctas / units : 1;
-  if (splits < 1) splits = 1;
-  int64_t tokens = round_up(ceil_div(max_length, splits), 64);
-  if (tokens < 256) tokens = 256;
-  return tokens;
+  int64_t best_tokens = round_up(max_length, 128);
+  double best_score = -1.0;
+  for (int64_t splits = 1; splits <= 64; ++splits) {
+    const int64_t tokens = round_up(ceil_div(max_length, splits), 128);
+    if (tokens < 256 && splits > 1) break;
+    const int64_t real_splits = ceil_div(max_length, tokens);
+    const int64_t ctas = units * real_splits;
+    const int64_t waves = ceil_div(ctas, slots);
+    const double fill = static_cast<double>(ctas) / static_cast<double>(waves * slots);
+    const double streaming = static_cast<double>(tokens) / static_cast<double>(tokens + 96);
+    const double score = fill * streaming;
+    if (score > best_score + 1e-9) {
+      best_score = score;
+      best_tokens = tokens;
+    }
+  }
+  return best_tokens;
+}
+
+int64_t workspace_bytes_for(int64_t batch, int64_t q_heads, int64_t head_dim, int64_t splits) {
+  return kCounterBytes + round_up(batch * q_heads * splits * (head_dim + 2) * 4, 256);
 }
 
 }  // namespace
@@ -490,9 +730,10 @@ extern "C" int64_t b200_decode_attention_workspace_bytes(int64_t batch, int64_t 
   const int64_t groups = q_heads / kv_heads;
   const int64_t head_blocks = kv_heads * ceil_div(groups, 16);
   if (split_tokens <= 0) split_tokens = default_split_tokens(batch, head_blocks, max_length);
+  split_tokens = round_up(split_tokens, 32);
   const int64_t splits = ceil_div(max_length, split_tokens);
   if (splits <= 1) return 0;
-  return round_up(batch * q_heads * splits * (head_dim + 2) * 4, 256);
+  return workspace_bytes_for(batch, q_heads, head_dim, splits);
 }
 
 extern "C" int b200_decode_attention(const void* query, const void* key_buffer,
@@ -539,12 +780,12 @@ extern "C" int b200_decode_attention(const void* query, const void* key_buffer,
       (reinterpret_cast<uintptr_t>(query) & 3u) != 0 || q_head_stride % 2 != 0 ||
       q_batch_stride % 2 != 0)
     return B200_ERR_ALIGNMENT;
+  if (capacity > INT32_MAX / 2 || batch * capacity > INT32_MAX) return B200_ERR_TOO_LARGE;
 
   int64_t max_length = max_length_hint > 0 && max_length_hint < mask_len ? max_length_hint : mask_len;
   const int64_t head_blocks = kv_heads * ceil_div(groups, 16);
   if (split_tokens <= 0) split_tokens = default_split_tokens(batch, head_blocks, max_length);
-  split_tokens = round_up(split_tokens, 16);
-  // lengths above the hint are still honoured: the grid covers mask_len when no hint is given
+  split_tokens = round_up(split_tokens, 32);
   const int64_t splits = ceil_div(max_length, split_tokens);
   if (splits > 65535 || split_tokens > INT32_MAX) return B200_ERR_TOO_LARGE;
 
@@ -564,7 +805,7 @@ extern "C" int b200_decode_attention(const void* query, const void* key_buffer,
   p.kv_heads = static_cast<int>(kv_heads);
   p.groups = groups;
   p.capacity = static_cast<int>(capacity);
-  p.mask_len = static_cast<int>(max_length < mask_len ? max_length : mask_len);
+  p.mask_len = static_cast<int>(max_length);
   p.split_tokens = static_cast<int>(split_tokens);
   p.num_splits = static_cast<int>(splits);
   p.mask_dtype = mask_dtype;
@@ -572,10 +813,12 @@ extern "C" int b200_decode_attention(const void* query, const void* key_buffer,
   p.scale = static_cast<float>(scale);
   p.ws_o = nullptr;
   p.ws_ml = nullptr;
+  p.counters = nullptr;
   if (splits > 1) {
-    const int64_t need = round_up(batch * q_heads * splits * (head_dim + 2) * 4, 256);
+    const int64_t need = workspace_bytes_for(batch, q_heads, head_dim, splits);
     if (!workspace || workspace_bytes < need) return B200_ERR_WORKSPACE;
-    p.ws_o = static_cast<float*>(workspace);
+    if (batch * head_blocks <= kMaxCounters) p.counters = static_cast<int*>(workspace);
+    p.ws_o = reinterpret_cast<float*>(static_cast<char*>(workspace) + kCounterBytes);
     p.ws_ml = p.ws_o + batch * q_heads * splits * head_dim;
   }
   return head_dim == 64 ? launch_bf16<64>(p, s) : launch_bf16<128>(p, s);

@@ -177,18 +177,17 @@ __global__ void __launch_bounds__(WM* WN * 32) linear_bf16_kernel(const LinearPa
     if (!is_last) return;
     __threadfence();
     const float* all = p.partials + static_cast<int64_t>(tile) * p.splits * (kAcc * kThreads);
+    // split-major, with all kAcc loads of a split in flight together: the sum order is fixed
+    // (split 0, 1, ...), the latency of a round is paid once per split, not once per element
+    float* flat = &acc[0][0][0];
+    for (int s = 0; s < p.splits; ++s) {
+      float part[kAcc];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+      for (int i = 0; i < kAcc; ++i)
+        part[i] = __ldcg(all + (static_cast<int64_t>(s) * kAcc + i) * kThreads + threadIdx.x);
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float sum = 0.0f;
-          for (int s = 0; s < p.splits; ++s)
-            sum += __ldcg(all + (static_cast<int64_t>(s) * kAcc + (mt * NT + nt) * 4 + e) * kThreads +
-                          threadIdx.x);
-          acc[mt][nt][e] = sum;
-        }
+      for (int i = 0; i < kAcc; ++i) flat[i] = s == 0 ? part[i] : flat[i] + part[i];
+    }
   }
 
 #pragma unroll
@@ -298,7 +297,7 @@ TilePlan plan_bf16(int64_t m, int64_t k, int64_t n) {
   const int64_t target = 2 * kNumSMs;
   if (tiles < target) {
     splits = ceil_div(target, tiles);
-    if (splits > 16) splits = 16;
+    if (splits > 8) splits = 8;
     if (splits > kb) splits = kb;
     // no empty splits: every split gets at least one k block
     const int64_t per = ceil_div(kb, splits);

@@ -72,6 +72,8 @@ class DeviceRuntime:
             reasons.append("token id outside the vocabulary (row zeroed)")
         if value & _lib.STATUS_BAD_POSITION:
             reasons.append("negative KV position (write skipped)")
+        if value & _lib.STATUS_WAIT_TIMEOUT:
+            reasons.append("a bounded in-kernel wait gave up (result invalid)")
         raise KernelStatusError("; ".join(reasons) or f"status word {value}")
 
 
@@ -420,7 +422,7 @@ def b200_decode_attention(query: torch.Tensor, key_buffer: torch.Tensor,
         _code(query.dtype), _mode(numerical_mode), int(split_tokens), int(max_length_hint),
         _ptr(workspace), need, rt.status.data_ptr(), _stream())
     _check(code, "b200_decode_attention")
-    _count(rt, 2 if need else 1)
+    _count(rt)
     return output
 
 

@@ -207,9 +207,16 @@ def test_rms_norm_3d_and_strided_rows():
 
 
 # ---------------------------------------------------------------- decode attention ----
+@pytest.fixture(params=["tma", "cp.async"])
+def decode_loads(request, monkeypatch):
+    """Both ways of filling the shared-memory ring: tensor-map box copies and 16-byte cp.async."""
+    monkeypatch.setenv("B200_DECODE_ATTENTION_LOADS", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("mode", ["fast", "pytorch_compatible"])
 @pytest.mark.parametrize("name", list(cases.DECODE_ATTENTION))
-def test_decode_attention_golden(name, mode, golden_ops):
+def test_decode_attention_golden(name, mode, golden_ops, decode_loads):
     x = cases.decode_attention_inputs(name)
     out = b200.b200_decode_attention(dev(x["query"]), dev(x["key_buffer"]), dev(x["value_buffer"]),
                                      dev(x["lengths"]), dev(x["mask"]), scale=x["scale"],
@@ -220,7 +227,7 @@ def test_decode_attention_golden(name, mode, golden_ops):
 
 
 @pytest.mark.parametrize("split_tokens", [0, 16, 64, 256, 4096])
-def test_decode_attention_splits_ragged_and_masked(split_tokens):
+def test_decode_attention_splits_ragged_and_masked(split_tokens, decode_loads):
     """Ragged lengths incl. 0 (NaN row, as the oracle), 1 and == capacity; a mask with -inf
     holes; every split size must agree with the oracle."""
     g = torch.Generator().manual_seed(21)
@@ -241,7 +248,7 @@ def test_decode_attention_splits_ragged_and_masked(split_tokens):
     kernels.runtime().check_status()
 
 
-def test_decode_attention_no_mask_and_bf16_mask():
+def test_decode_attention_no_mask_and_bf16_mask(decode_loads):
     x = cases.decode_attention_inputs("decode_attention_bf16_long")
     ref = serve_ops.decode_attention(x["query"], x["key_buffer"], x["value_buffer"], x["lengths"],
                                      x["mask"], groups=x["groups"], scale=x["scale"])
@@ -254,6 +261,26 @@ def test_decode_attention_no_mask_and_bf16_mask():
           ref, BF16_TOL)
 
 
+def test_decode_attention_ignores_rows_beyond_the_length(decode_loads):
+    """Rows past lengths[b] may hold anything, NaN included: they must not reach the output."""
+    g = torch.Generator().manual_seed(17)
+    b, c, hq, hkv, d = 4, 400, 14, 2, 64
+    q = torch.randn(b, 1, hq, d, generator=g).bfloat16().transpose(1, 2)
+    kbuf = torch.randn(b, c, hkv, d, generator=g).bfloat16()
+    vbuf = torch.randn(b, c, hkv, d, generator=g).bfloat16()
+    lengths = torch.tensor([399, 33, 250, 64])
+    ref = serve_ops.decode_attention(q, kbuf, vbuf, lengths, torch.zeros(b, 1, 1, c), groups=7,
+                                     scale=0.125)
+    for row, n in enumerate(lengths.tolist()):
+        kbuf[row, n:] = float("nan")
+        vbuf[row, n:] = float("inf")
+    for split in (0, 64, 128):
+        out = b200.b200_decode_attention(q.cuda(), kbuf.cuda(), vbuf.cuda(), lengths.cuda(), None,
+                                         scale=0.125, split_tokens=split)
+        close(out, ref, BF16_TOL)
+    kernels.runtime().check_status()
+
+
 def test_decode_attention_length_over_mask_sets_status():
     x = cases.decode_attention_inputs("decode_attention_bf16")
     mask = x["mask"][..., :200].contiguous()  # lengths are [1, 130, 300]
@@ -263,7 +290,7 @@ def test_decode_attention_length_over_mask_sets_status():
         kernels.runtime().check_status()
 
 
-def test_decode_attention_qwen2_7b_shape():
+def test_decode_attention_qwen2_7b_shape(decode_loads):
     g = torch.Generator().manual_seed(31)
     b, c, hq, hkv, d = 3, 1500, 28, 4, 128
     q = torch.randn(b, 1, hq, d, generator=g).bfloat16().transpose(1, 2)
@@ -279,7 +306,7 @@ def test_decode_attention_qwen2_7b_shape():
 
 
 @pytest.mark.parametrize("hq,hkv", [(24, 2), (40, 2), (16, 1), (9, 1)])
-def test_decode_attention_wide_groups(hq, hkv):
+def test_decode_attention_wide_groups(hq, hkv, decode_loads):
     """More than 8 (and more than 16) query heads per KV head: both row halves of the
     tensor-core tile and several 16-row blocks per KV head."""
     g = torch.Generator().manual_seed(hq)
@@ -296,7 +323,7 @@ def test_decode_attention_wide_groups(hq, hkv):
         close(out, ref, BF16_TOL)
 
 
-def test_decode_attention_split_invariance_full_size():
+def test_decode_attention_split_invariance_full_size(decode_loads):
     """Benchmark shape (batch 64, capacity 4608, lengths ~4096, 14/2 heads x 64): the result
     must not depend on how the KV range is split; one sequence is checked against the oracle."""
     b, c, hq, hkv, d = 64, 4608, 14, 2, 64
