@@ -45,9 +45,10 @@ CONTEXT = 4096
 METRIC = "qwen2_0.5b_bf16_decode_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the decode-attention kernel at the
-# bench shape, from the ncu capture summarised in profiles/ (None until one exists)
-DECODE_ATTENTION_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch over 64 x 4096 =
+# 262144 tokens, from the ncu capture summarised in profiles/decode_attention_b64_l4096_ncu_full.md;
+# scaled to the bench launch by the tokens it processes (traffic is proportional to the tokens read)
+NCU_TRAFFIC_BYTES, NCU_TRAFFIC_TOKENS = 137_794_816, 262_144
 
 
 def parse_args():
@@ -358,7 +359,8 @@ def b200_arm(args, config):
             roofline = {"bound": "hbm", "kernel": "decode_attention_kernel", "achieved": achieved,
                         "peak": peak, "peak_source": f"{peak_kind} copy bandwidth", "unit": "GB/s",
                         "frac": achieved / peak, "frac_of_nominal_8000": achieved / 8000.0,
-                        "traffic": DECODE_ATTENTION_TRAFFIC_BYTES,
+                        "traffic": NCU_TRAFFIC_BYTES * lengths_sum / NCU_TRAFFIC_TOKENS
+                        if args.batch == BATCH_PER_GPU else None,
                         "algorithmic_bytes_per_launch": bytes_per_launch,
                         "us_per_launch": launch_s * 1e6}
     engine.state.check()
