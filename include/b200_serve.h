@@ -138,6 +138,32 @@ int b200_decode_attention(const void* query, const void* key_buffer, const void*
                           void* workspace, int64_t workspace_bytes, int32_t* status,
                           void* stream);
 
+/* Decode attention for callers that must not allocate device memory (no counterpart in
+ * the reference, whose wrappers allocate with torch.empty on every call). Some hosts of
+ * this library cannot call cudaMalloc at all: code running inside a CUDA-graph capture or a
+ * real-time serving loop with a frozen memory budget, plugins handed a fixed arena by their
+ * framework, and runtimes whose allocator is owned by another component. For them the
+ * split-KV scratch (tile counters and fp32 partials) is a fixed 8 MiB array that lives in
+ * the library itself, on every GPU that loads it, until the process exits
+ * (b200_decode_attention_static_scratch_bytes() returns that size). The caller still passes
+ * the inputs and the output; arguments are those of b200_decode_attention without the
+ * workspace pair. bf16 only (the fp32 kernel needs no scratch).
+ *  - A request whose partials do not fit the array (roughly batch * q_heads * splits *
+ *    (head_dim + 2) * 4 bytes + 64 KiB > 8 MiB) is refused with B200_ERR_TOO_LARGE; nothing
+ *    is launched and nothing is allocated. A larger split_tokens lowers the need.
+ *  - The first call on each device looks the array's device address up; make that first
+ *    call outside any stream capture.
+ *  - All calls on one GPU share the array, which keeps the previous call's contents (the
+ *    counter region is cleared at the start of every call): two calls that overlap on the
+ *    GPU, on different streams, race. Issue them on one stream or order them with events. */
+int64_t b200_decode_attention_static_scratch_bytes(void);
+int b200_decode_attention_static_scratch(
+    const void* query, const void* key_buffer, const void* value_buffer, const int64_t* lengths,
+    const void* mask, void* output, int64_t batch, int64_t q_heads, int64_t kv_heads,
+    int64_t head_dim, int64_t capacity, int64_t mask_len, int64_t q_batch_stride,
+    int64_t q_head_stride, int64_t mask_batch_stride, int mask_dtype, double scale, int dtype,
+    int mode, int64_t split_tokens, int64_t max_length_hint, int32_t* status, void* stream);
+
 /* ---- Prefill attention -------------------------------------------------------
  * T-token GQA attention with an arbitrary additive B x 1 x T x T mask, or with
  * proven causality (causal != 0: mask may be NULL and fully masked tiles are skipped).

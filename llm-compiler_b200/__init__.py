@@ -14,6 +14,7 @@ from .kernels import (
     b200_argmax,
     b200_contiguous,
     b200_decode_attention,
+    b200_decode_attention_no_alloc,
     b200_embedding,
     b200_kv_store,
     b200_linear,
@@ -31,7 +32,7 @@ __all__ = [
     "ExecutionError", "KernelStatusError", "PreallocatedKVCacheState", "Qwen2Config",
     "QWEN2_0_5B", "QWEN2_7B", "TINY_FP32", "make_prompt_ids", "make_weights",
     "b200_add", "b200_advance_lengths", "b200_argmax", "b200_contiguous",
-    "b200_decode_attention", "b200_embedding", "b200_kv_store", "b200_linear",
+    "b200_decode_attention", "b200_decode_attention_no_alloc", "b200_embedding", "b200_kv_store", "b200_linear",
     "b200_prefill_attention", "b200_rms_norm", "b200_rope", "b200_rope_kv_store",
     "b200_rope_table", "b200_swiglu",
 ]

@@ -823,3 +823,107 @@ extern "C" int b200_decode_attention(const void* query, const void* key_buffer,
   }
   return head_dim == 64 ? launch_bf16<64>(p, s) : launch_bf16<128>(p, s);
 }
+
+// ---- Entry point that allocates nothing ------------------------------------------------
+// Same computation as b200_decode_attention, for callers that are not allowed to allocate
+// device memory at all: the split-KV scratch (tile counters + fp32 partials) lives in a
+// file-scope device array that every GPU loading this library holds until the process exits.
+namespace b200 {
+namespace {
+
+constexpr int64_t kStaticScratchBytes = 8ll << 20;  // 8 MiB per GPU, the stated maximum
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+// Device addresses of g_static_scratch, one per device. In host code the array's name is
+// only a host-side stand-in; the address a kernel may use comes from cudaGetSymbolAddress.
+void* g_static_scratch_address[kMaxDevices] = {};
+
+// Set-up, once per device, with that device current. Returns nullptr on failure.
+void* static_scratch_for_current_device() {
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) return nullptr;
+  if (g_static_scratch_address[device] == nullptr) {
+    void* address = nullptr;
+    if (cudaGetSymbolAddress(&address, g_static_scratch) != cudaSuccess) return nullptr;
+    g_static_scratch_address[device] = address;
+  }
+  return g_static_scratch_address[device];
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" int64_t b200_decode_attention_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int b200_decode_attention_static_scratch(
+    const void* query, const void* key_buffer, const void* value_buffer, const int64_t* lengths,
+    const void* mask, void* output, int64_t batch, int64_t q_heads, int64_t kv_heads,
+    int64_t head_dim, int64_t capacity, int64_t mask_len, int64_t q_batch_stride,
+    int64_t q_head_stride, int64_t mask_batch_stride, int mask_dtype, double scale, int dtype,
+    int mode, int64_t split_tokens, int64_t max_length_hint, int32_t* status, void* stream) {
+  if (!query || !key_buffer || !value_buffer || !lengths || !output || batch < 0 ||
+      q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || capacity <= 0 || mask_len <= 0 ||
+      mask_len > capacity || q_heads % kv_heads != 0)
+    return B200_ERR_BAD_ARGUMENT;
+  if (mask != nullptr && mask_dtype != B200_F32 && mask_dtype != B200_BF16)
+    return B200_ERR_UNSUPPORTED;
+  if (dtype != B200_BF16) return B200_ERR_UNSUPPORTED;  // the fp32 kernel needs no scratch
+  if (head_dim != 64 && head_dim != 128) return B200_ERR_UNSUPPORTED;
+  if (batch == 0) return B200_OK;
+  if (batch > 65535) return B200_ERR_TOO_LARGE;
+  if (!aligned16(key_buffer) || !aligned16(value_buffer) ||
+      (reinterpret_cast<uintptr_t>(query) & 3u) != 0 || q_head_stride % 2 != 0 ||
+      q_batch_stride % 2 != 0)
+    return B200_ERR_ALIGNMENT;
+  if (capacity > INT32_MAX / 2 || batch * capacity > INT32_MAX) return B200_ERR_TOO_LARGE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int groups = static_cast<int>(q_heads / kv_heads);
+
+  int64_t max_length = max_length_hint > 0 && max_length_hint < mask_len ? max_length_hint : mask_len;
+  const int64_t head_blocks = kv_heads * ceil_div(groups, 16);
+  if (split_tokens <= 0) split_tokens = default_split_tokens(batch, head_blocks, max_length);
+  split_tokens = round_up(split_tokens, 32);
+  const int64_t splits = ceil_div(max_length, split_tokens);
+  if (splits > 65535 || split_tokens > INT32_MAX) return B200_ERR_TOO_LARGE;
+  // the request must fit the fixed array: counters + partials, or it is refused outright
+  if (splits > 1 && (workspace_bytes_for(batch, q_heads, head_dim, splits) > kStaticScratchBytes ||
+                     batch * head_blocks > kMaxCounters))
+    return B200_ERR_TOO_LARGE;
+
+  DecodeParams p;
+  p.q = static_cast<const __nv_bfloat16*>(query);
+  p.kbuf = static_cast<const __nv_bfloat16*>(key_buffer);
+  p.vbuf = static_cast<const __nv_bfloat16*>(value_buffer);
+  p.lengths = lengths;
+  p.mask = mask;
+  p.out = static_cast<__nv_bfloat16*>(output);
+  p.status = status;
+  p.q_batch_stride = q_batch_stride;
+  p.q_head_stride = q_head_stride;
+  p.mask_batch_stride = mask_batch_stride;
+  p.batch = static_cast<int>(batch);
+  p.q_heads = static_cast<int>(q_heads);
+  p.kv_heads = static_cast<int>(kv_heads);
+  p.groups = groups;
+  p.capacity = static_cast<int>(capacity);
+  p.mask_len = static_cast<int>(max_length);
+  p.split_tokens = static_cast<int>(split_tokens);
+  p.num_splits = static_cast<int>(splits);
+  p.mask_dtype = mask_dtype;
+  p.compat = mode == B200_MODE_PYTORCH_COMPATIBLE ? 1 : 0;
+  p.scale = static_cast<float>(scale);
+  p.ws_o = nullptr;
+  p.ws_ml = nullptr;
+  p.counters = nullptr;
+  if (splits > 1) {
+    void* scratch = static_scratch_for_current_device();
+    if (scratch == nullptr) return B200_ERR_LAUNCH;
+    // the array keeps whatever the last call left: the counters must start from zero
+    if (cudaMemsetAsync(scratch, 0, kCounterBytes, s) != cudaSuccess) return B200_ERR_LAUNCH;
+    p.counters = static_cast<int*>(scratch);
+    p.ws_o = reinterpret_cast<float*>(static_cast<char*>(scratch) + kCounterBytes);
+    p.ws_ml = p.ws_o + batch * q_heads * splits * head_dim;
+  }
+  return head_dim == 64 ? launch_bf16<64>(p, s) : launch_bf16<128>(p, s);
+}

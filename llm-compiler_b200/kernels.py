@@ -426,6 +426,68 @@ def b200_decode_attention(query: torch.Tensor, key_buffer: torch.Tensor,
     return output
 
 
+def b200_decode_attention_no_alloc(query: torch.Tensor, key_buffer: torch.Tensor,
+                                   value_buffer: torch.Tensor, lengths: torch.Tensor,
+                                   attention_mask: Optional[torch.Tensor], output: torch.Tensor, *,
+                                   scale: float, numerical_mode: str = "fast",
+                                   split_tokens: int = 0, max_length_hint: int = 0) -> torch.Tensor:
+    """Decode attention for callers that must not allocate on the device.
+
+    Some users of this backend cannot let a call reach cudaMalloc or torch's caching
+    allocator: a step being captured into a CUDA graph, a serving loop whose memory budget is
+    frozen after start-up, a host framework that hands its plugins a fixed arena. This
+    variant takes the output tensor from the caller and keeps the split-KV scratch in an
+    8 MiB array inside the library (one per GPU, alive until the process exits) instead of a
+    workspace tensor. Nothing is allocated here or in the library; tensors that would need a
+    contiguous copy are rejected. Requests whose partial sums do not fit the array raise
+    ValueError (raise split_tokens to shrink the need). Calls on one GPU share the array, so
+    calls that overlap on different streams race; the first call on a device should happen
+    outside graph capture because it looks the array's address up. bf16 only.
+    """
+
+    device = _require_cuda(query, key_buffer, value_buffer, lengths, attention_mask, output)
+    if query.ndim != 4 or query.shape[2] != 1 or query.stride(3) != 1:
+        raise ValueError("query must be B x H x 1 x D with a contiguous last dimension")
+    if key_buffer.ndim != 4 or key_buffer.shape != value_buffer.shape or \
+            not key_buffer.is_contiguous() or not value_buffer.is_contiguous():
+        raise ValueError("KV buffers must be contiguous B x C x H x D tensors of one shape")
+    batch, q_heads, _, dim = query.shape
+    _, capacity, kv_heads, buffer_dim = key_buffer.shape
+    if key_buffer.shape[0] != batch or buffer_dim != dim or kv_heads <= 0 or q_heads % kv_heads:
+        raise ValueError("query does not match the KV buffers")
+    if lengths.shape != (batch,) or lengths.dtype != torch.int64 or not lengths.is_contiguous():
+        raise ValueError("lengths must be a contiguous one-dimensional int64 batch tensor")
+    if not (query.dtype == key_buffer.dtype == value_buffer.dtype == output.dtype):
+        raise ValueError("query, KV buffers and output must share one dtype")
+    if output.shape != (batch, q_heads, 1, dim) or not output.is_contiguous():
+        raise ValueError("output must be a contiguous B x H x 1 x D tensor")
+    mask_len, mask_stride, mask_code = capacity, 0, _lib.F32
+    if attention_mask is not None:
+        if attention_mask.ndim != 4 or attention_mask.shape[:3] != (batch, 1, 1) or \
+                attention_mask.stride(3) != 1:
+            raise ValueError("attention_mask must be B x 1 x 1 x S with a contiguous last dimension")
+        mask_len = attention_mask.shape[3]
+        if mask_len > capacity or mask_len <= 0:
+            raise ValueError("mask length must be in [1, capacity]")
+        mask_stride = attention_mask.stride(0)
+        mask_code = _code(attention_mask.dtype)
+    rt = runtime(device)
+    code = _lib.load().b200_decode_attention_static_scratch(
+        query.data_ptr(), key_buffer.data_ptr(), value_buffer.data_ptr(), lengths.data_ptr(),
+        _ptr(attention_mask), output.data_ptr(), batch, q_heads, kv_heads, dim, capacity,
+        mask_len, query.stride(0), query.stride(1), mask_stride, mask_code, float(scale),
+        _code(query.dtype), _mode(numerical_mode), int(split_tokens), int(max_length_hint),
+        rt.status.data_ptr(), _stream())
+    if code == _lib.ERR_TOO_LARGE:
+        raise ValueError(
+            "b200_decode_attention_static_scratch: the split partials do not fit the library's "
+            f"{_lib.load().b200_decode_attention_static_scratch_bytes()} byte scratch array; "
+            "use a larger split_tokens or the workspace entry point")
+    _check(code, "b200_decode_attention_static_scratch")
+    _count(rt)
+    return output
+
+
 # --------------------------------------------------------------- prefill attention ----
 def b200_prefill_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                            attention_mask: Optional[torch.Tensor], *, scale: float,
