@@ -1,0 +1,298 @@
+"""KernelIR executor for the B200 target: same contract as the reference's GPU executor
+(`TritonExecutor.run(module, arguments, function_name=None) -> ExecutionResult`,
+backends/triton_executor.py:42-130 on top of execution.py:530-579), every op executed by a
+kernel of libb200serve.so or by host metadata — there is nothing to fall back to.
+
+`strict=True` (the default here; the reference defaults to False) checks the whole graph
+before the first op runs, exactly like `require_full_lowering` upstream, and raises
+LoweringCoverageError for anything `kernel_ir.lower_to_b200` did not lower. The run is free
+of host synchronisation and of allocations other than torch.empty outputs, so a caller may
+capture it in a CUDA graph once shapes are fixed.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from . import kernels
+from .kernel_ir import decode_attribute, require_full_lowering, value_dtype, value_rank
+from .kv_state import ExecutionError, PreallocatedKVCacheState
+
+_DTYPES = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16,
+           "i64": torch.int64, "i32": torch.int32, "i1": torch.bool}
+
+
+@dataclass
+class ExecutionResult:
+    outputs: Tuple[Any, ...]
+    executed_operations: Tuple[str, ...]
+    symbolic_dimensions: Dict[str, int]
+
+
+def _select_function(module, function_name: Optional[str]):
+    if function_name is None:
+        if len(module.functions) != 1:
+            raise ExecutionError("the module holds several functions: pass function_name")
+        return module.functions[0]
+    for function in module.functions:
+        if function.name == function_name:
+            return function
+    raise ExecutionError(f"no function @{function_name}")
+
+
+def _as_state(value: Any) -> PreallocatedKVCacheState:
+    """Accepts this package's state or any object with the reference's fields
+    (keys, values, lengths, capacity, generation): wrapped without copying."""
+
+    if isinstance(value, PreallocatedKVCacheState):
+        return value
+    if all(hasattr(value, name) for name in ("keys", "values", "lengths", "capacity")):
+        return PreallocatedKVCacheState(tuple(value.keys), tuple(value.values),
+                                        tuple(value.lengths), int(value.capacity),
+                                        int(getattr(value, "generation", 0)))
+    raise ExecutionError("expected a PreallocatedKVCacheState")
+
+
+def bind_arguments(function, weights: Dict[str, torch.Tensor], inputs: Dict[str, Any]) -> List[Any]:
+    """Positional argument list for `function` from named values: the counterpart, for modules
+    that travel as JSON, of bind_exported_program_arguments / bind_stateful_decode_arguments
+    (execution.py:908-1004), which need the ExportedProgram. `inputs` maps user input names
+    (input_ids, attention_mask, position_ids, kv_state, inv_freq) to values; parameters are
+    matched by their state_dict name with '.' flattened to '_' (the exporter's
+    `p_model_<flattened name>` convention); a buffer ending in `inv_freq` takes inputs["inv_freq"]."""
+
+    flattened = sorted(((name.replace(".", "_"), tensor) for name, tensor in weights.items()),
+                       key=lambda item: -len(item[0]))
+    arguments = []
+    for declared in function.block.arguments:
+        name = declared.name.lstrip("%")
+        if name in inputs:
+            arguments.append(inputs[name])
+        elif name.endswith("inv_freq") and "inv_freq" in inputs:
+            arguments.append(inputs["inv_freq"])
+        else:
+            for flat, tensor in flattened:
+                if name.endswith(flat):
+                    arguments.append(tensor)
+                    break
+            else:
+                raise ExecutionError(f"no value for graph argument {declared.name}")
+    return arguments
+
+
+class B200Executor:
+    def __init__(self, *, strict: bool = True) -> None:
+        self.strict = strict
+        self.lowering_trace: List[Dict[str, Any]] = []
+        self._handlers = {
+            "kernel.b200.rms_norm": self._rms_norm,
+            "kernel.b200.linear": self._linear,
+            "kernel.b200.rope": self._rope,
+            "kernel.b200.rope_table": self._rope_table,
+            "kernel.b200.prefill_attention": self._prefill_attention,
+            "kernel.b200.decode_attention": self._decode_attention,
+            "kernel.b200.kv_store": self._kv_store,
+            "kernel.b200.kv_prefill_store": self._kv_prefill_store,
+            "kernel.b200.embedding": self._embedding,
+            "kernel.b200.swiglu": lambda o, a, e: kernels.b200_swiglu(o[0], o[1]),
+            "kernel.b200.add": lambda o, a, e: kernels.b200_add(o[0], o[1]),
+            "kernel.b200.contiguous": self._contiguous,
+            "kernel.b200.cast": self._cast,
+            "runtime.kv.init": self._kv_init,
+            "runtime.kv.length": lambda o, a, e: _as_state(o[0]).positions(int(a.get("slot", 0))),
+            "runtime.kv.advance": lambda o, a, e: _as_state(o[0]).advance(
+                int(a.get("slot", 0)), delta=int(a.get("delta", 1))),
+            "runtime.view.view": self._view,
+            "runtime.view.reshape": self._view,
+            "runtime.view.transpose": self._transpose,
+            "runtime.view.unsqueeze": self._unsqueeze,
+            "runtime.view.sym_size": self._sym_size,
+        }
+
+    # ------------------------------------------------------------------ run ----
+    def run(self, module, arguments: Sequence[Any], *,
+            function_name: Optional[str] = None) -> ExecutionResult:
+        if self.strict:
+            require_full_lowering(module)  # before any op runs (triton_executor.py:60-62)
+        function = _select_function(module, function_name)
+        if len(arguments) != len(function.block.arguments):
+            raise ExecutionError(
+                f"@{function.name} takes {len(function.block.arguments)} arguments, "
+                f"got {len(arguments)}")
+        environment: Dict[str, Any] = {}
+        for declared, runtime_value in zip(function.block.arguments, arguments):
+            self._validate_argument(declared, runtime_value)
+            environment[declared.name] = runtime_value
+        trace = []
+        for operation in function.block.operations:
+            handler = self._handlers.get(operation.name)
+            if handler is None:
+                raise ExecutionError(
+                    f"the B200 executor has no kernel for {operation.name}: run "
+                    "kernel_ir.lower_to_b200 on the module first (there is no eager fallback)")
+            operands = [environment[value.name] for value in operation.operands]
+            results = handler(operands, operation.attributes, environment)
+            expected = len(operation.results)
+            if expected == 1:
+                results = (results,)
+            elif expected == 0:
+                results = ()
+            elif not isinstance(results, (tuple, list)) or len(results) != expected:
+                raise ExecutionError(f"{operation.name} must produce {expected} results")
+            for declared, runtime_value in zip(operation.results, results):
+                environment[declared.name] = runtime_value
+            trace.append(operation.name)
+        outputs = tuple(environment[value.name] for value in function.returns)
+        return ExecutionResult(outputs, tuple(trace), {})
+
+    @staticmethod
+    def _validate_argument(declared, runtime_value) -> None:
+        dtype = value_dtype(declared)
+        if dtype is None:
+            return
+        if not isinstance(runtime_value, torch.Tensor):
+            raise ExecutionError(f"argument {declared.name} must be a tensor")
+        if not runtime_value.is_cuda:
+            raise ExecutionError(f"argument {declared.name} must live on a CUDA device")
+        expected = _DTYPES.get(dtype)
+        if expected is not None and runtime_value.dtype != expected:
+            raise ExecutionError(f"argument {declared.name}: dtype {runtime_value.dtype}, "
+                                 f"expected {expected}")
+        rank = value_rank(declared)
+        if rank is not None and runtime_value.ndim != rank:
+            raise ExecutionError(f"argument {declared.name}: rank {runtime_value.ndim}, "
+                                 f"expected {rank}")
+
+    # ------------------------------------------------------------- kernel ops ----
+    def _rms_norm(self, operands, attributes, environment):
+        if len(operands) != 2:
+            raise ExecutionError("rms_norm takes input and weight")
+        mode = attributes.get("numerical_mode", "fast")
+        rows = operands[0].numel() // operands[0].shape[-1]
+        self.lowering_trace.append({"backend": "b200", "source": "kernel_ir", "rows": rows,
+                                    "numerical_mode": mode})
+        return kernels.b200_rms_norm(
+            operands[0], operands[1], epsilon=float(attributes["epsilon"]),
+            output_dtype=attributes.get("output_dtype"),
+            round_before_weight=bool(attributes.get("round_before_weight", False)),
+            numerical_mode=mode)
+
+    @staticmethod
+    def _linear(operands, attributes, environment):
+        has_bias = bool(attributes.get("has_bias"))
+        epilogue = attributes.get("epilogue") or "none"
+        expected = 2 + int(has_bias) + int(epilogue == "residual")
+        if len(operands) != expected:
+            raise ExecutionError("linear: has_bias / epilogue disagree with the operand count")
+        tensor, weight = operands[0], operands[1]
+        bias = operands[2] if has_bias else None
+        residual = operands[-1] if epilogue == "residual" else None
+        return kernels.b200_linear(tensor, weight, bias, residual=residual, epilogue=epilogue)
+
+    @staticmethod
+    def _rope(operands, attributes, environment):
+        if len(operands) != 4:
+            raise ExecutionError("rope takes query, key, cosine and sine")
+        if operands[0].shape[-1] != int(attributes["head_dim"]):
+            raise ExecutionError("rope: head_dim does not match the attribute")
+        return kernels.b200_rope(*operands)
+
+    @staticmethod
+    def _rope_table(operands, attributes, environment):
+        positions, inv_freq = operands
+        dtype = _DTYPES[attributes["dtype"]]
+        return kernels.b200_rope_table(positions, inv_freq.reshape(-1), dtype)
+
+    @staticmethod
+    def _prefill_attention(operands, attributes, environment):
+        if len(operands) != 4:
+            raise ExecutionError("prefill_attention takes q, k, v and mask")
+        query, key, value, mask = operands
+        if query.shape[1] != key.shape[1] * int(attributes["groups"]):
+            raise ExecutionError("prefill_attention: GQA groups mismatch")
+        return kernels.b200_prefill_attention(
+            query, key, value, mask, scale=float(attributes["scale"]),
+            causal=attributes.get("causal") is True,
+            numerical_mode=attributes.get("numerical_mode", "fast"))
+
+    @staticmethod
+    def _decode_attention(operands, attributes, environment):
+        if len(operands) != 3:
+            raise ExecutionError("decode_attention takes state, query and mask")
+        state = _as_state(operands[0])
+        return state.decode_attention(
+            int(attributes.get("slot", 0)), operands[1], operands[2],
+            groups=int(attributes["groups"]), scale=float(attributes["scale"]),
+            numerical_mode=attributes.get("numerical_mode", "fast"))
+
+    @staticmethod
+    def _kv_store(operands, attributes, environment):
+        if len(operands) != 4:
+            raise ExecutionError("kv_store takes state, key, value and positions")
+        state = _as_state(operands[0])
+        return state.store(int(attributes.get("slot", 0)), operands[1], operands[2], operands[3])
+
+    @staticmethod
+    def _kv_prefill_store(operands, attributes, environment):
+        if len(operands) != 3:
+            raise ExecutionError("kv_prefill_store takes state, key and value")
+        state = _as_state(operands[0])
+        return state.prefill_store(int(attributes.get("slot", 0)), operands[1], operands[2])
+
+    @staticmethod
+    def _kv_init(operands, attributes, environment):
+        if len(operands) != 1 or not isinstance(operands[0], torch.Tensor):
+            raise ExecutionError("kv.init takes one key tensor as its template")
+        return PreallocatedKVCacheState.empty_from_key_template(
+            operands[0], num_layers=int(attributes["num_layers"]),
+            capacity=int(attributes["capacity"]))
+
+    @staticmethod
+    def _embedding(operands, attributes, environment):
+        table, ids = operands
+        return kernels.b200_embedding(table, ids)
+
+    @staticmethod
+    def _contiguous(operands, attributes, environment):
+        tensor = operands[0]
+        return tensor if tensor.is_contiguous() else kernels.b200_contiguous(tensor)
+
+    @staticmethod
+    def _cast(operands, attributes, environment):
+        args = decode_attribute(attributes["args"], environment)
+        tensor, dtype = args[0], _DTYPES[args[1]]
+        if tensor.dtype == dtype:
+            return tensor
+        if tensor.dtype not in (torch.float32, torch.bfloat16) or \
+                dtype not in (torch.float32, torch.bfloat16):
+            raise ExecutionError(f"no B200 kernel casts {tensor.dtype} to {dtype}")
+        return kernels.b200_contiguous(tensor, dtype)
+
+    # ------------------------------------------------------------ metadata ops ----
+    @staticmethod
+    def _view(operands, attributes, environment):
+        tensor, shape = decode_attribute(attributes["args"], environment)
+        shape = [int(extent) for extent in shape]
+        try:
+            return tensor.view(shape)
+        except RuntimeError:
+            # strides do not allow a view: densify with the library's own copy kernel
+            return kernels.b200_contiguous(tensor).view(shape)
+
+    @staticmethod
+    def _transpose(operands, attributes, environment):
+        tensor, first, second = decode_attribute(attributes["args"], environment)
+        return tensor.transpose(int(first), int(second))
+
+    @staticmethod
+    def _unsqueeze(operands, attributes, environment):
+        tensor, axis = decode_attribute(attributes["args"], environment)
+        return tensor.unsqueeze(int(axis))
+
+    @staticmethod
+    def _sym_size(operands, attributes, environment):
+        tensor, axis = decode_attribute(attributes["args"], environment)
+        return int(tensor.shape[int(axis)])

@@ -1,0 +1,134 @@
+"""The KernelIR executor on the reference's own graphs: the reference-compiled KernelIR of
+the 2-layer stateful Qwen2 (golden JSON), finished by lower_to_b200, run op by op on the
+B200 kernels, against the logits / tokens / KV state the reference's CPU executor produced
+for the same seeded weights and ids (qwen2_tiny_fp32.pt)."""
+
+import json
+from pathlib import Path
+
+import pytest
+import torch
+
+from llm_compiler_b200 import kernel_ir as ir
+from llm_compiler_b200 import qwen2 as q2
+from llm_compiler_b200.executor import B200Executor, bind_arguments
+from llm_compiler_b200.kv_state import ExecutionError, PreallocatedKVCacheState
+
+pytestmark = pytest.mark.gpu
+GOLDEN = Path(__file__).resolve().parent / "golden"
+
+
+def lowered(kind, mode, **options):
+    module = ir.module_from_json(json.loads((GOLDEN / f"kernel_ir_tiny_{kind}_{mode}.json").read_text()))
+    ir.lower_to_b200(module, **options)
+    return module
+
+
+def causal_mask(batch, tokens):
+    future = torch.triu(torch.ones(tokens, tokens, dtype=torch.bool), diagonal=1)
+    return torch.zeros(batch, 1, tokens, tokens).masked_fill(future, float("-inf")).cuda()
+
+
+@pytest.mark.parametrize("mode", ["fast", "pytorch_compatible"])
+@pytest.mark.parametrize("fuse", [True, False])
+def test_prefill_then_decode_graphs_match_the_reference_executor(mode, fuse, golden_tiny):
+    gold = golden_tiny["fp32"]
+    config = q2.Qwen2Config(**gold["config"])
+    weights = {k: v.cuda() for k, v in q2.make_weights(config, seed=0).items()}
+    inv_freq = q2.inverse_frequency(config, "cuda")
+    batch, prompt = gold["batch"], gold["prompt"]
+    executor = B200Executor(strict=True)
+
+    prefill = lowered("prefill", mode, fuse_epilogues=fuse)
+    ids = gold["input_ids"].cuda()
+    positions = torch.arange(prompt).repeat(batch, 1).cuda()
+    result = executor.run(prefill, bind_arguments(prefill.functions[0], weights, {
+        "input_ids": ids, "attention_mask": causal_mask(batch, prompt), "position_ids": positions,
+        "inv_freq": inv_freq}))
+    logits, state = result.outputs
+    assert isinstance(state, PreallocatedKVCacheState) and state.capacity == gold["capacity"]
+    torch.testing.assert_close(logits.cpu(), gold["prefill_logits"], rtol=1e-4, atol=1e-4)
+    assert all(name.startswith(("kernel.b200.", "runtime.")) for name in result.executed_operations)
+    assert state.generation == config.num_layers  # one advance per layer slot
+    pointers = [k.data_ptr() for k in state.keys]
+
+    decode = lowered("decode", mode, fuse_epilogues=fuse)
+    token = logits[:, -1].argmax(-1)
+    assert torch.equal(token.cpu(), gold["tokens"][:, 0])
+    for step in range(gold["steps"]):
+        length = prompt + step
+        arguments = bind_arguments(decode.functions[0], weights, {
+            "input_ids": gold["tokens"][:, step].view(batch, 1).cuda(),
+            "attention_mask": torch.zeros(batch, 1, 1, length + 1, device="cuda"),
+            "position_ids": torch.full((batch, 1), length, device="cuda"),
+            "kv_state": state, "inv_freq": inv_freq})
+        logits, state = executor.run(decode, arguments).outputs
+        torch.testing.assert_close(logits[:, 0].cpu(), gold["decode_logits"][step], rtol=1e-4,
+                                   atol=1e-4)
+        assert torch.equal(logits[:, 0].argmax(-1).cpu(), gold["tokens"][:, step + 1])
+    state.check()
+    used = prompt + gold["steps"]
+    assert torch.equal(torch.stack(list(state.lengths), 0).cpu(), gold["lengths"])
+    torch.testing.assert_close(torch.stack([k[:, :used] for k in state.keys], 0).cpu(), gold["keys"],
+                               rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(torch.stack([v[:, :used] for v in state.values], 0).cpu(),
+                               gold["values"], rtol=1e-4, atol=1e-5)
+    assert pointers == [k.data_ptr() for k in state.keys]  # prefill -> decode on the same buffers
+    assert state.generation == config.num_layers * (1 + gold["steps"])
+    assert len(executor.lowering_trace) == 5 * (1 + gold["steps"])
+
+
+def test_decode_graph_runs_under_cuda_graph_capture(golden_tiny):
+    """The interpreter itself is capture-safe: one decode step captured and replayed."""
+    gold = golden_tiny["fp32"]
+    config = q2.Qwen2Config(**gold["config"])
+    weights = {k: v.cuda() for k, v in q2.make_weights(config, seed=0).items()}
+    inv_freq = q2.inverse_frequency(config, "cuda")
+    batch, prompt = gold["batch"], gold["prompt"]
+    executor = B200Executor()
+    prefill = lowered("prefill", "fast")
+    logits, state = executor.run(prefill, bind_arguments(prefill.functions[0], weights, {
+        "input_ids": gold["input_ids"].cuda(), "attention_mask": causal_mask(batch, prompt),
+        "position_ids": torch.arange(prompt).repeat(batch, 1).cuda(), "inv_freq": inv_freq})).outputs
+    decode = lowered("decode", "fast")
+    ids = torch.zeros(batch, 1, dtype=torch.int64, device="cuda")
+    positions = torch.full((batch, 1), prompt, device="cuda")
+    mask = torch.zeros(batch, 1, 1, gold["capacity"], device="cuda")  # fixed-capacity zero mask
+    arguments = bind_arguments(decode.functions[0], weights, {
+        "input_ids": ids, "attention_mask": mask, "position_ids": positions, "kv_state": state,
+        "inv_freq": inv_freq})
+    saved = [l.clone() for l in state.lengths]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        executor.run(decode, arguments)  # warm-up: sizes every workspace
+    torch.cuda.current_stream().wait_stream(side)
+    for length, value in zip(state.lengths, saved):
+        length.copy_(value)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out_logits, _ = executor.run(decode, arguments).outputs
+    for length, value in zip(state.lengths, saved):
+        length.copy_(value)
+    for step in range(gold["steps"]):
+        ids.copy_(gold["tokens"][:, step].view(batch, 1))
+        positions.fill_(prompt + step)
+        graph.replay()
+        torch.testing.assert_close(out_logits[:, 0].cpu(), gold["decode_logits"][step], rtol=1e-4,
+                                   atol=1e-4)
+    state.check()
+
+
+def test_executor_errors_mirror_the_reference(golden_tiny):
+    gold = golden_tiny["fp32"]
+    config = q2.Qwen2Config(**gold["config"])
+    weights = {k: v.cuda() for k, v in q2.make_weights(config, seed=0).items()}
+    decode = lowered("decode", "fast")
+    executor = B200Executor()
+    with pytest.raises(ExecutionError, match="arguments"):
+        executor.run(decode, [])
+    cpu_inputs = {"input_ids": torch.zeros(3, 1, dtype=torch.int64), "attention_mask": torch.zeros(3, 1, 1, 6),
+                  "position_ids": torch.zeros(3, 1, dtype=torch.int64), "kv_state": None,
+                  "inv_freq": q2.inverse_frequency(config, "cuda")}
+    with pytest.raises(ExecutionError, match="CUDA"):
+        executor.run(decode, bind_arguments(decode.functions[0], weights, cpu_inputs))

@@ -1,0 +1,150 @@
+"""The B200 lowering pass and coverage check on the reference's own KernelIR (golden JSON
+written by tests/golden/make_golden.py) — host logic only, no GPU."""
+
+import copy
+import json
+import sys
+from collections import Counter
+from pathlib import Path
+
+import pytest
+
+from llm_compiler_b200 import kernel_ir as ir
+
+GOLDEN = Path(__file__).resolve().parent / "golden"
+KINDS = ["prefill", "decode"]
+MODES = ["fast", "pytorch_compatible"]
+
+
+def load(kind, mode):
+    return ir.module_from_json(json.loads((GOLDEN / f"kernel_ir_tiny_{kind}_{mode}.json").read_text()))
+
+
+@pytest.mark.parametrize("kind", KINDS)
+@pytest.mark.parametrize("mode", MODES)
+def test_reference_kernel_ir_is_not_fully_lowered_but_b200_is(kind, mode):
+    module = load(kind, mode)
+    ir.verify_module(module)
+    before = ir.analyze_lowering_coverage(module)
+    # only the runtime.kv.* bookkeeping names are shared with the reference's dialect
+    assert set(before.lowered_by_name) <= {"runtime.kv.init", "runtime.kv.length", "runtime.kv.advance"}
+    assert before.unlowered_operations >= before.total_operations - 4
+    with pytest.raises(ir.LoweringCoverageError):
+        ir.require_full_lowering(module)
+    report = ir.lower_to_b200(module)
+    ir.verify_module(module)
+    coverage = ir.require_full_lowering(module)
+    assert coverage.is_complete and coverage.coverage == 1.0
+    assert report.coverage == coverage
+    names = Counter(op.name for op in module.functions[0].block.operations)
+    assert not any(name.startswith(("aten.", "serve.", "kernel.triton.", "kernel.cuda.",
+                                    "kernel.cublas.")) for name in names)
+    # 2 layers: 5 RMSNorm, 15 linears, 2 RoPE, 1 RoPE table, 2 SwiGLU, 1 embedding
+    assert names["kernel.b200.rms_norm"] == 5
+    assert names["kernel.b200.linear"] == 15
+    assert names["kernel.b200.rope"] == 2
+    assert names["kernel.b200.rope_table"] == 1
+    assert names["kernel.b200.swiglu"] == 2
+    assert names["kernel.b200.embedding"] == 1
+    assert names["kernel.b200.add"] == 0  # all four residual adds became GEMM epilogues
+    assert names.get("kernel.b200.cast", 0) == 0  # fp32 graph: every cast was an identity
+    if kind == "decode":
+        assert names["kernel.b200.decode_attention"] == 2 and names["kernel.b200.kv_store"] == 2
+        assert names["runtime.kv.length"] == 2 and names["runtime.kv.advance"] == 2
+    else:
+        assert names["kernel.b200.prefill_attention"] == 2
+        assert names["kernel.b200.kv_prefill_store"] == 2 and names["runtime.kv.init"] == 1
+    assert report.removed_casts + report.removed_dead >= 10
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_numerical_mode_is_carried_onto_every_kernel(mode):
+    module = load("decode", mode)
+    ir.lower_to_b200(module)
+    for op in module.functions[0].block.operations:
+        if op.name in ("kernel.b200.rms_norm", "kernel.b200.rope", "kernel.b200.decode_attention",
+                       "kernel.b200.linear"):
+            assert op.attributes["numerical_mode"] == mode, op.name
+    forced = load("decode", mode)
+    ir.lower_to_b200(forced, numerical_mode="pytorch_compatible")
+    assert all(op.attributes["numerical_mode"] == "pytorch_compatible"
+               for op in forced.functions[0].block.operations if op.name == "kernel.b200.rms_norm")
+    with pytest.raises(ValueError):
+        ir.lower_to_b200(load("decode", mode), numerical_mode="exact")
+
+
+def test_lowering_is_idempotent_and_keeps_unknown_ops_unlowered():
+    module = load("decode", "fast")
+    ir.lower_to_b200(module)
+    snapshot = json.dumps(ir.module_to_json(module), sort_keys=True)
+    ir.lower_to_b200(module)
+    assert json.dumps(ir.module_to_json(module), sort_keys=True) == snapshot
+    # an op of an unknown dialect is never claimed (tests/test_lowering.py:97-114 upstream)
+    function = module.functions[0]
+    odd = ir.Operation("kernel.vendor.magic", [function.block.arguments[0]],
+                       [ir.Value("%odd", "tensor<1xf32, cpu>")])
+    function.block.operations.insert(0, odd)
+    function.returns.append(odd.results[0])
+    ir.lower_to_b200(module)
+    coverage = ir.analyze_lowering_coverage(module)
+    assert coverage.unlowered_by_name == {"kernel.vendor.magic": 1}
+    with pytest.raises(ir.LoweringCoverageError, match="kernel.vendor.magic"):
+        ir.require_full_lowering(module)
+
+
+def test_without_epilogue_fusion_the_adds_stay_separate_kernels():
+    module = load("prefill", "fast")
+    ir.lower_to_b200(module, fuse_epilogues=False)
+    names = Counter(op.name for op in module.functions[0].block.operations)
+    assert names["kernel.b200.add"] == 4
+    ir.require_full_lowering(module)
+
+
+def test_json_round_trip_preserves_the_graph():
+    module = load("prefill", "fast")
+    again = ir.module_from_json(json.dumps(ir.module_to_json(module)))
+    assert ir.module_to_json(again) == ir.module_to_json(module)
+
+
+def test_strict_executor_refuses_before_running_anything():
+    from llm_compiler_b200.executor import B200Executor
+
+    module = load("decode", "fast")  # still the reference's partial lowering
+    with pytest.raises(ir.LoweringCoverageError):
+        B200Executor(strict=True).run(module, [])
+
+
+REFERENCE_SRC = Path("/root/reference/src")
+
+
+@pytest.mark.skipif(not REFERENCE_SRC.exists(), reason="reference package not mounted")
+def test_pass_accepts_the_reference_module_objects():
+    """Where the reference is installed its own Module objects go straight into the pass."""
+
+    sys.path.insert(0, str(REFERENCE_SRC))
+    try:
+        import torch
+        from stateful_llm_compiler.compiler import CompileOptions, compile_exported_program
+        from stateful_llm_compiler.frontend import export_qwen2_causal_lm_prefill
+        from stateful_llm_compiler.lowering import LoweringCoverageError as UpstreamError
+        from stateful_llm_compiler.qwen2 import (Qwen2CompatConfig, StatefulQwen2ForCausalLM,
+                                                 make_qwen2_prefill_inputs)
+
+        cfg = Qwen2CompatConfig(hidden_size=128, intermediate_size=256, num_layers=1, num_heads=2,
+                                num_kv_heads=1, vocab_size=64, tie_word_embeddings=True)
+        model = StatefulQwen2ForCausalLM(cfg).bfloat16().eval()
+        inputs = make_qwen2_prefill_inputs(cfg, 2, 4, seed=0)
+        program = export_qwen2_causal_lm_prefill(model, inputs, max_batch=4, max_prompt_length=16)
+        with pytest.raises(UpstreamError):  # upstream cannot satisfy --require-full-lowering
+            compile_exported_program(program, options=CompileOptions(
+                prefill_kv_state=True, kv_capacity=32, require_full_lowering=True))
+        artifact = compile_exported_program(program, options=CompileOptions(
+            prefill_kv_state=True, kv_capacity=32, numerical_mode="pytorch_compatible"))
+        report = ir.lower_to_b200(artifact.module)
+        ir.require_full_lowering(artifact.module)
+        names = Counter(op.name for op in artifact.module.functions[0].block.operations)
+        assert names["kernel.b200.rope_table"] == 1 and names["kernel.b200.swiglu"] == 1
+        assert names.get("kernel.b200.cast", 0) == 0  # bf16: the only real casts are in the table
+        assert report.coverage.is_complete
+    finally:
+        sys.path.remove(str(REFERENCE_SRC))
