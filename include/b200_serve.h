@@ -188,7 +188,11 @@ int b200_prefill_attention(const void* query, const void* key, const void* value
  * aten.add.Tensor that follows o_proj / down_proj, qwen2.py:299-304); 2 SwiGLU over
  * row-interleaved gate/up weights: W holds n rows (gate_j, up_j alternating), the output is
  * [M, n/2] and y[m,j] = r(r(silu(r(gate_j))) * r(up_j)) (qwen2.py:262-264).
- * Workspace (split-K partial sums + tile counters): b200_linear_workspace_bytes. */
+ * bf16 problems with more than 64 rows run on tcgen05 tensor cores (TMEM accumulator, TMA-fed
+ * 128 x 256 tiles); up to 64 rows on warp-level tiles that stream every weight byte once,
+ * with deterministic split-K. Workspace (split-K partial sums + tile counters):
+ * b200_linear_workspace_bytes. `status` receives B200_STATUS_WAIT_TIMEOUT if a bounded
+ * in-kernel wait gives up. */
 #define B200_EPILOGUE_NONE 0
 #define B200_EPILOGUE_RESIDUAL 1
 #define B200_EPILOGUE_SWIGLU 2
@@ -196,7 +200,7 @@ int64_t b200_linear_workspace_bytes(int64_t m, int64_t k, int64_t n, int dtype, 
 int b200_linear(const void* input, const void* weight, const void* bias, const void* residual,
                 void* output, int64_t m, int64_t k, int64_t n, int64_t input_row_stride,
                 int dtype, int epilogue, void* workspace, int64_t workspace_bytes,
-                void* stream);
+                int32_t* status, void* stream);
 
 /* ---- Ops the reference leaves to PyTorch eager (execution.py:500-528) ---------- */
 /* aten.embedding.default: out[r,:] = table[ids[r],:]. */

@@ -60,7 +60,7 @@ SIGNATURES = {
                                [c_int, c_double, c_int, c_int, c_int, c_void_p]),
     "b200_linear_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int, c_int]),
     "b200_linear": (c_int, [c_void_p] * 5 + [c_int64] * 4 + [c_int, c_int, c_void_p, c_int64,
-                                                              c_void_p]),
+                                                              c_void_p, c_void_p]),
     "b200_embedding": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
                                c_void_p, c_void_p]),
     "b200_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),

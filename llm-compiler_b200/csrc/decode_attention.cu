@@ -25,6 +25,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "tensor_map.cuh"
 
 namespace b200 {
 namespace {
@@ -610,23 +611,7 @@ bool make_kv_tensor_map(CUtensorMap* map, const void* buffer, int64_t batch, int
   const cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(tokens_per_box)};
   const cuuint32_t element_strides[3] = {1, 1, 1};
   if (batch * capacity >= (int64_t(1) << 31)) return false;
-  // The driver entry point is resolved through the runtime, so the library links against
-  // nothing but cudart and still loads on a machine without a GPU driver.
-  using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-  static EncodeTiled encode = nullptr;
-  static bool resolved = false;
-  if (!resolved) {
-    void* entry = nullptr;
-    cudaDriverEntryPointQueryResult query;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &query) ==
-            cudaSuccess &&
-        query == cudaDriverEntryPointSuccess)
-      encode = reinterpret_cast<EncodeTiled>(entry);
-    resolved = true;
-  }
+  EncodeTiledFn encode = tensor_map_encoder();
   if (encode == nullptr) return false;
   const CUresult result = encode(
       map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(buffer), dims, strides, box,

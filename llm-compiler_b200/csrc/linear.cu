@@ -10,6 +10,9 @@
 // (deterministic) and runs the epilogue. Counters are left at zero for the next call.
 //
 // fp32: CUDA-core tiled GEMM with IEEE fp32 FMAs (small full-precision graphs).
+#include <stdlib.h>
+#include <string.h>
+
 #include "common.cuh"
 
 namespace b200 {
@@ -332,7 +335,20 @@ int launch_tile(const LinearParams& p, const TilePlan& t, cudaStream_t stream) {
 }  // namespace
 }  // namespace b200
 
+namespace b200 {
+int linear_tcgen05(const void* input, const void* weight, const void* bias, const void* residual,
+                   void* output, int64_t m, int64_t k, int64_t n, int64_t input_row_stride,
+                   int epilogue, int32_t* status, cudaStream_t stream);
+}
+
 using namespace b200;
+
+// tcgen05 tiles are 128 rows tall: worth it once a 64-row warp-level tile no longer covers M.
+static bool use_tcgen05(int64_t m) {
+  if (m <= 64) return false;
+  const char* value = getenv("B200_LINEAR_PATH");
+  return value == nullptr || strcmp(value, "mma.sync") != 0;
+}
 
 extern "C" int64_t b200_linear_workspace_bytes(int64_t m, int64_t k, int64_t n, int dtype,
                                                int epilogue) {
@@ -347,7 +363,7 @@ extern "C" int64_t b200_linear_workspace_bytes(int64_t m, int64_t k, int64_t n, 
 extern "C" int b200_linear(const void* input, const void* weight, const void* bias,
                            const void* residual, void* output, int64_t m, int64_t k, int64_t n,
                            int64_t input_row_stride, int dtype, int epilogue, void* workspace,
-                           int64_t workspace_bytes, void* stream) {
+                           int64_t workspace_bytes, int32_t* status, void* stream) {
   if (!input || !weight || !output || m < 0 || k <= 0 || n <= 0 || input_row_stride < k)
     return B200_ERR_BAD_ARGUMENT;
   if (epilogue != B200_EPILOGUE_NONE && epilogue != B200_EPILOGUE_RESIDUAL &&
@@ -380,6 +396,11 @@ extern "C" int b200_linear(const void* input, const void* weight, const void* bi
   if (k % 8 != 0 || input_row_stride % 8 != 0) return B200_ERR_UNSUPPORTED;
   if (!aligned16(input) || !aligned16(weight)) return B200_ERR_ALIGNMENT;
 
+  if (use_tcgen05(m)) {
+    const int code = linear_tcgen05(input, weight, bias, residual, output, m, k, n,
+                                    input_row_stride, epilogue, status, s);
+    if (code != B200_ERR_UNSUPPORTED) return code;
+  }
   const TilePlan t = plan_bf16(m, k, n);
   if (t.tiles_m > 65535) return B200_ERR_TOO_LARGE;
   LinearParams p;

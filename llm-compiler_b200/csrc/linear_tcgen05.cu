@@ -1,0 +1,278 @@
+// serve.linear for prefill-size M on the 5th-generation tensor cores: tcgen05.mma with the
+// accumulator in tensor memory (TMEM), operands staged in shared memory by TMA.
+//
+// y[M,N] = x[M,K] W[N,K]^T, both operands K-major bf16. One CTA computes a 128 x BN tile
+// (BN = 256 or 128 accumulator columns of TMEM, fp32). Roles inside the CTA of 4 warps:
+//   warp 0, one elected lane  TMA producer: per k-block one 128 x 64 box of x and one BN x 64
+//                             box of W (128-byte swizzled rows) into a ring of stages,
+//                             completion on the stage's `full` mbarrier;
+//   warp 1, one elected lane  MMA issuer: per stage four tcgen05.mma (M 128, N BN, K 16) whose
+//                             shared-memory descriptors walk the 64-wide swizzled tile in 32-byte
+//                             steps; tcgen05.commit arrives on the stage's `empty` mbarrier when
+//                             the tensor core is done reading it, and on `accum` after the last
+//                             k-block;
+//   all 4 warps               epilogue: tcgen05.ld of the warp's 32 TMEM lanes (= 32 output
+//                             rows) x 32 columns at a time, bias / residual / SwiGLU with the
+//                             reference's bf16 rounding points, 64-byte row segments to HBM.
+// Every mbarrier wait is bounded; a wait that gives up sets B200_STATUS_WAIT_TIMEOUT, the CTA
+// still frees its TMEM columns and returns. No cluster launch, no multicast: each CTA fetches
+// its own tiles; the second CTA resident on an SM overlaps its main loop with this one's
+// epilogue (BN 128: 2 x 96 KB of stages, 2 x 128 TMEM columns).
+#include <stdlib.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "tensor_map.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kThreads = 128;
+
+struct Tcgen05Params {
+  const __nv_bfloat16* bias;
+  const __nv_bfloat16* residual;
+  __nv_bfloat16* out;
+  int32_t* status;
+  int m, k, n, epilogue;
+};
+
+__device__ __forceinline__ float silu_f32(float x) {
+  return __fdiv_rn(x, __fadd_rn(1.0f, expf(-x)));
+}
+
+// Shared-memory matrix descriptor of a K-major tile of 128-byte swizzled rows: start address,
+// leading byte offset 16 B (unused by swizzled K-major layouts), stride byte offset 1024 B
+// (8 rows of 128 B per swizzle atom), descriptor version 1 (Blackwell), layout SWIZZLE_128B.
+__device__ __forceinline__ uint64_t smem_descriptor(uint32_t smem_addr) {
+  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) |
+         (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+
+// Instruction descriptor of kind::f16: fp32 accumulator, bf16 A and B, both K-major.
+__host__ __device__ constexpr uint32_t instruction_descriptor(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_32x32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads)
+linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap a_map,
+                      const __grid_constant__ CUtensorMap b_map) {
+  constexpr int kABytes = kBM * 128;
+  constexpr int kBBytes = BN * 128;
+  constexpr int kStageBytes = kABytes + kBBytes;
+  constexpr uint32_t kIdesc = instruction_descriptor(kBM, BN);
+
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int failed;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile_n = blockIdx.x, tile_m = blockIdx.y;
+  const int nkb = (p.k + kBK - 1) / kBK;
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (threadIdx.x == 0) {
+    failed = 0;
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbarrier_init(smem_u32(&full_bar[s]), 1);
+      mbarrier_init(smem_u32(&empty_bar[s]), 1);
+    }
+    mbarrier_init(smem_u32(&accum_bar), 1);
+    fence_mbarrier_init();
+  }
+  if (warp == 1) {  // one warp allocates the accumulator columns and later frees them
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_slot)), "r"(static_cast<uint32_t>(BN)) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 0 && lane == 0) {
+    // ---- TMA producer ----
+    for (int kb = 0; kb < nkb; ++kb) {
+      const int s = kb % STAGES;
+      if (kb >= STAGES &&
+          !mbarrier_wait_bounded(smem_u32(&empty_bar[s]), ((kb / STAGES) - 1) & 1)) {
+        failed = 1;
+        break;
+      }
+      const uint32_t bar = smem_u32(&full_bar[s]);
+      const uint32_t a_dst = smem_base + s * kStageBytes;
+      mbarrier_arrive_expect_tx(bar, kStageBytes);
+      tma_load_2d(a_dst, &a_map, bar, kb * kBK, tile_m * kBM);
+      tma_load_2d(a_dst + kABytes, &b_map, bar, kb * kBK, tile_n * BN);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer ----
+    for (int kb = 0; kb < nkb; ++kb) {
+      const int s = kb % STAGES;
+      if (!mbarrier_wait_bounded(smem_u32(&full_bar[s]), (kb / STAGES) & 1)) {
+        failed = 1;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t a_addr = smem_base + s * kStageBytes;
+      const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+      for (int j = 0; j < kBK / 16; ++j)
+        umma_bf16(tmem_base, smem_descriptor(a_addr + j * 32), smem_descriptor(b_addr + j * 32),
+                  kIdesc, (kb > 0 || j > 0) ? 1u : 0u);
+      umma_commit(smem_u32(&empty_bar[s]));  // the stage is free once these MMAs have read it
+    }
+    umma_commit(smem_u32(&accum_bar));  // the accumulator is complete once all MMAs retired
+  }
+  __syncwarp();
+
+  // ---- epilogue: all four warps, warp w reads TMEM lanes 32w .. 32w+31 = output rows ----
+  bool ok = mbarrier_wait_bounded(smem_u32(&accum_bar), 0);
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  ok = ok && failed == 0;
+  if (ok) {
+    const int row = tile_m * kBM + warp * 32 + lane;
+    const int out_cols = p.epilogue == B200_EPILOGUE_SWIGLU ? p.n / 2 : p.n;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+      const int col0 = tile_n * BN + c0;
+      if (col0 >= p.n) break;  // warp-uniform: tcgen05.ld is a warp-wide instruction
+      float v[32];
+      tmem_load_32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c0, v);
+      if (row >= p.m) continue;
+      if (p.bias != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (col0 + i < p.n) v[i] += __bfloat162float(p.bias[col0 + i]);
+      }
+      if (p.epilogue == B200_EPILOGUE_SWIGLU) {
+        // columns 2j / 2j+1 are gate_j / up_j
+        __nv_bfloat16* dst = p.out + static_cast<int64_t>(row) * out_cols + col0 / 2;
+        float y[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j)
+          y[j] = round_bf16(silu_f32(round_bf16(v[2 * j]))) * round_bf16(v[2 * j + 1]);
+        if (col0 + 32 <= p.n && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+            reinterpret_cast<uint4*>(dst)[i] =
+                make_uint4(pack_bf16x2(y[8 * i], y[8 * i + 1]), pack_bf16x2(y[8 * i + 2], y[8 * i + 3]),
+                           pack_bf16x2(y[8 * i + 4], y[8 * i + 5]), pack_bf16x2(y[8 * i + 6], y[8 * i + 7]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (col0 / 2 + j < out_cols) dst[j] = __float2bfloat16_rn(y[j]);
+        }
+        continue;
+      }
+      const int64_t o = static_cast<int64_t>(row) * p.n + col0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = round_bf16(v[i]);
+      if (p.epilogue == B200_EPILOGUE_RESIDUAL) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (col0 + i < p.n) v[i] = __fadd_rn(v[i], __bfloat162float(p.residual[o + i]));
+      }
+      __nv_bfloat16* dst = p.out + o;
+      if (col0 + 32 <= p.n && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          reinterpret_cast<uint4*>(dst)[i] =
+              make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
+                         pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (col0 + i < p.n) dst[i] = __float2bfloat16_rn(v[i]);
+      }
+    }
+  } else if (threadIdx.x == 0 && p.status != nullptr) {
+    atomicOr(p.status, B200_STATUS_WAIT_TIMEOUT);
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                 ::"r"(tmem_base), "r"(static_cast<uint32_t>(BN)) : "memory");
+}
+
+template <int BN, int STAGES>
+int launch(const Tcgen05Params& p, const CUtensorMap& a_map, const CUtensorMap& b_map,
+           cudaStream_t stream) {
+  constexpr int smem = STAGES * (kBM + BN) * 128 + 1024;
+  auto kernel = linear_tcgen05_kernel<BN, STAGES>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    return B200_ERR_LAUNCH;
+  dim3 grid(static_cast<unsigned>(ceil_div(p.n, BN)), static_cast<unsigned>(ceil_div(p.m, kBM)));
+  kernel<<<grid, kThreads, smem, stream>>>(p, a_map, b_map);
+  return launch_status();
+}
+
+}  // namespace
+
+// Called by b200_linear for bf16 problems with more rows than the decode tiles serve.
+// Returns B200_ERR_UNSUPPORTED when a tensor map cannot describe the operands, in which case
+// the caller uses the warp-level kernel.
+int linear_tcgen05(const void* input, const void* weight, const void* bias, const void* residual,
+                   void* output, int64_t m, int64_t k, int64_t n, int64_t input_row_stride,
+                   int epilogue, int32_t* status, cudaStream_t stream) {
+  if (ceil_div(m, kBM) > 65535) return B200_ERR_UNSUPPORTED;
+  const int bn = n % 256 == 0 || n > 1024 ? 256 : 128;
+  CUtensorMap a_map, b_map;
+  if (!make_bf16_matrix_map(&a_map, input, m, k, input_row_stride, kBM) ||
+      !make_bf16_matrix_map(&b_map, weight, n, k, k, bn))
+    return B200_ERR_UNSUPPORTED;
+  Tcgen05Params p;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.out = static_cast<__nv_bfloat16*>(output);
+  p.status = status;
+  p.m = static_cast<int>(m);
+  p.k = static_cast<int>(k);
+  p.n = static_cast<int>(n);
+  p.epilogue = epilogue;
+  return bn == 256 ? launch<256, 4>(p, a_map, b_map, stream) : launch<128, 3>(p, a_map, b_map, stream);
+}
+
+}  // namespace b200

@@ -592,7 +592,7 @@ def b200_linear(tensor: torch.Tensor, weight: torch.Tensor,
     workspace = rt.workspace("linear", need)
     code = library.b200_linear(source.data_ptr(), weight.data_ptr(), _ptr(bias), _ptr(residual),
                                output.data_ptr(), m, k, n, k, code_dtype, _EPILOGUES[epilogue],
-                               _ptr(workspace), need, _stream())
+                               _ptr(workspace), need, rt.status.data_ptr(), _stream())
     _check(code, "b200_linear")
     _count(rt)
     return output

@@ -52,9 +52,9 @@ def test_host_side_rejections_happen_before_any_launch():
     assert library.b200_linear_workspace_bytes(64, 896, 151936, _lib.BF16, 0) == 0
     fake = ctypes.c_void_p(256)  # never dereferenced: rejected on the host
     assert library.b200_linear(fake, fake, None, None, fake, 4, 7, 8, 7, _lib.BF16, 0, None, 0,
-                               None) == _lib.ERR_UNSUPPORTED  # K not a multiple of 8
+                               None, None) == _lib.ERR_UNSUPPORTED  # K not a multiple of 8
     assert library.b200_linear(fake, fake, None, None, fake, 4, 8, 8, 8, _lib.BF16, 1, None, 0,
-                               None) == _lib.ERR_BAD_ARGUMENT  # residual epilogue without residual
+                               None, None) == _lib.ERR_BAD_ARGUMENT  # residual epilogue without residual
     assert library.b200_decode_attention(fake, fake, fake, fake, None, fake, 2, 5, 2, 64, 16, 16,
                                          320, 64, 0, 0, 0.125, _lib.BF16, 0, 0, 0, None, 0, None,
                                          None) == _lib.ERR_BAD_ARGUMENT  # 5 heads over 2 KV heads

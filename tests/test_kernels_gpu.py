@@ -421,6 +421,36 @@ def test_linear_shapes_and_epilogues(m, k, n):
         close(b200.b200_linear(x.cuda(), packed, epilogue="swiglu"), ref_mlp, BF16_TOL)
 
 
+@pytest.mark.parametrize("m,k,n", [(128, 64, 128), (256, 896, 896), (1000, 4864, 896),
+                                   (2048, 896, 9728), (300, 896, 1152), (129, 200, 72)])
+def test_linear_tcgen05_path_matches_the_oracle_and_the_warp_level_path(m, k, n, monkeypatch):
+    """More than 64 rows run on tcgen05 / TMEM / TMA; the same call with
+    B200_LINEAR_PATH=mma.sync runs the warp-level kernel. Both against the CPU oracle, all
+    epilogues, full and ragged tiles in M, N and K."""
+    g = torch.Generator().manual_seed(m + n)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+    bias = torch.randn(n, generator=g).bfloat16()
+    res = torch.randn(m, n, generator=g).bfloat16()
+    ref = serve_ops.linear(x, w, bias)
+    ref_res = serve_ops.residual_add(res, serve_ops.linear(x, w))
+    ref_mlp = serve_ops.swiglu(serve_ops.linear(x, w[: n // 2]), serve_ops.linear(x, w[n // 2:]))
+    xd, wd, bd, rd = x.cuda(), w.cuda(), bias.cuda(), res.cuda()
+    packed = kernels.interleave_gate_up(wd[: n // 2], wd[n // 2:])
+    outputs = {}
+    for path in ("tcgen05", "mma.sync"):
+        if path == "mma.sync":
+            monkeypatch.setenv("B200_LINEAR_PATH", "mma.sync")
+        outputs[path] = (b200.b200_linear(xd, wd, bd), b200.b200_linear(xd, wd, residual=rd, epilogue="residual"),
+                         b200.b200_linear(xd, packed, epilogue="swiglu"))
+        close(outputs[path][0], ref, BF16_TOL)
+        close(outputs[path][1], ref_res, BF16_TOL)
+        close(outputs[path][2], ref_mlp, BF16_TOL)
+    kernels.runtime().check_status()
+    # the two kernels round at the same points: they agree to an ulp of the output scale
+    close(outputs["tcgen05"][0], outputs["mma.sync"][0].float().cpu(), 1e-2)
+
+
 def test_linear_f32_epilogues():
     g = torch.Generator().manual_seed(77)
     x = torch.randn(7, 256, generator=g)
