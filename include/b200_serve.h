@@ -202,6 +202,35 @@ int b200_linear(const void* input, const void* weight, const void* bias, const v
                 int dtype, int epilogue, void* workspace, int64_t workspace_bytes,
                 int32_t* status, void* stream);
 
+/* ---- Decode-step chain: split-K partial sums reduced by the operator that follows ----------
+ * At decode sizes (M <= 128 rows) the projections are weight streaming: the GEMM is cut into
+ * N tiles x K slices so that every SM pulls weights, each CTA writes its fp32 partial tile,
+ * and the reduction over the K slices happens while the NEXT operator of the layer loads its
+ * input (fixed slice order: deterministic). These entry points stand for the op sequences of
+ * one decoder layer of the reference graph (qwen2.py:152-304 after the passes):
+ *   b200_linear_partial            serve.linear without its epilogue: partials[s, m, n] (fp32),
+ *                                  s < b200_linear_partial_splits(m, k, n)
+ *   b200_reduce_residual_rms_norm  (o_proj | down_proj result) -> aten.add (residual) ->
+ *                                  serve.rms_norm of the next block: x_out = r(r(sum) + residual),
+ *                                  h_out = r(w * r(x_out * rsqrt(mean(x_out^2) + eps)));
+ *                                  residual and h_out / norm_weight may be NULL
+ *   b200_reduce_rope_kv_store      (q|k|v projection result + bias) -> serve.rope -> serve.kv.length
+ *                                  -> serve.kv.store: rotated q to query_out (B x Hq x D), rotated
+ *                                  k and v into the KV buffers at positions[b]
+ * bf16 only; partial buffers are caller-owned, 16-byte aligned, n a multiple of 4. */
+int64_t b200_linear_partial_splits(int64_t m, int64_t k, int64_t n);
+int b200_linear_partial(const void* input, const void* weight, void* partials, int64_t m,
+                        int64_t k, int64_t n, int64_t input_row_stride, int64_t splits,
+                        int32_t* status, void* stream);
+int b200_reduce_residual_rms_norm(const void* partials, int64_t splits, const void* residual,
+                                  const void* norm_weight, void* x_out, void* h_out, int64_t rows,
+                                  int64_t hidden, double epsilon, int mode, void* stream);
+int b200_reduce_rope_kv_store(const void* partials, int64_t splits, const void* bias,
+                              const void* cosine, const void* sine, void* query_out,
+                              void* key_buffer, void* value_buffer, const int64_t* positions,
+                              int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                              int64_t capacity, int32_t* status, void* stream);
+
 /* ---- Ops the reference leaves to PyTorch eager (execution.py:500-528) ---------- */
 /* aten.embedding.default: out[r,:] = table[ids[r],:]. */
 int b200_embedding(const void* table, const int64_t* ids, void* output, int64_t rows,

@@ -343,9 +343,10 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
 
 using namespace b200;
 
-// tcgen05 tiles are 128 rows tall: worth it once a 64-row warp-level tile no longer covers M.
+// The tcgen05 path takes every problem it can fill the GPU with (it declines decode-size M
+// with few N tiles, which need split-K); B200_LINEAR_PATH=mma.sync forces the warp-level kernel.
 static bool use_tcgen05(int64_t m) {
-  if (m <= 64) return false;
+  (void)m;
   const char* value = getenv("B200_LINEAR_PATH");
   return value == nullptr || strcmp(value, "mma.sync") != 0;
 }

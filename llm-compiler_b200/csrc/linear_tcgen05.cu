@@ -31,12 +31,15 @@ constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kThreads = 128;
 
+constexpr int kEpiloguePartial = 100;  // internal: fp32 split-K partials, no rounding
+
 struct Tcgen05Params {
   const __nv_bfloat16* bias;
   const __nv_bfloat16* residual;
   __nv_bfloat16* out;
+  float* partials;  // [splits, m, n] fp32 when epilogue == kEpiloguePartial
   int32_t* status;
-  int m, k, n, epilogue;
+  int m, k, n, epilogue, splits;
 };
 
 __device__ __forceinline__ float silu_f32(float x) {
@@ -106,8 +109,11 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   __shared__ int failed;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_n = blockIdx.x, tile_m = blockIdx.y;
-  const int nkb = (p.k + kBK - 1) / kBK;
+  const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z;
+  const int kb_total = (p.k + kBK - 1) / kBK;
+  const int kb_per = (kb_total + p.splits - 1) / p.splits;
+  const int kb_first = split * kb_per;
+  const int nkb = max(0, min(kb_first + kb_per, kb_total) - kb_first);
   const uint32_t smem_base = smem_u32(smem);
 
   if (threadIdx.x == 0) {
@@ -142,8 +148,8 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
       const uint32_t bar = smem_u32(&full_bar[s]);
       const uint32_t a_dst = smem_base + s * kStageBytes;
       mbarrier_arrive_expect_tx(bar, kStageBytes);
-      tma_load_2d(a_dst, &a_map, bar, kb * kBK, tile_m * kBM);
-      tma_load_2d(a_dst + kABytes, &b_map, bar, kb * kBK, tile_n * BN);
+      tma_load_2d(a_dst, &a_map, bar, (kb_first + kb) * kBK, tile_m * kBM);
+      tma_load_2d(a_dst + kABytes, &b_map, bar, (kb_first + kb) * kBK, tile_n * BN);
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer ----
@@ -180,6 +186,24 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
       float v[32];
       tmem_load_32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c0, v);
       if (row >= p.m) continue;
+      if (nkb == 0) {  // a K slice without k blocks contributes zeros, not stale TMEM
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+      }
+      if (p.epilogue == kEpiloguePartial) {
+        float* dst = p.partials + (static_cast<int64_t>(split) * p.m + row) * p.n + col0;
+        if (col0 + 32 <= p.n && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            reinterpret_cast<float4*>(dst)[i] =
+                make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (col0 + i < p.n) dst[i] = v[i];
+        }
+        continue;
+      }
       if (p.bias != nullptr) {
 #pragma unroll
         for (int i = 0; i < 32; ++i)
@@ -244,21 +268,31 @@ int launch(const Tcgen05Params& p, const CUtensorMap& a_map, const CUtensorMap& 
   auto kernel = linear_tcgen05_kernel<BN, STAGES>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return B200_ERR_LAUNCH;
-  dim3 grid(static_cast<unsigned>(ceil_div(p.n, BN)), static_cast<unsigned>(ceil_div(p.m, kBM)));
+  dim3 grid(static_cast<unsigned>(ceil_div(p.n, BN)), static_cast<unsigned>(ceil_div(p.m, kBM)),
+            static_cast<unsigned>(p.splits));
   kernel<<<grid, kThreads, smem, stream>>>(p, a_map, b_map);
   return launch_status();
 }
 
 }  // namespace
 
-// Called by b200_linear for bf16 problems with more rows than the decode tiles serve.
-// Returns B200_ERR_UNSUPPORTED when a tensor map cannot describe the operands, in which case
-// the caller uses the warp-level kernel.
+// Called by b200_linear. Returns B200_ERR_UNSUPPORTED when this path does not apply (a
+// tensor map cannot describe the operands, or a decode-size M with too few N tiles to fill
+// the GPU without split-K), in which case the caller uses the warp-level kernel.
 int linear_tcgen05(const void* input, const void* weight, const void* bias, const void* residual,
                    void* output, int64_t m, int64_t k, int64_t n, int64_t input_row_stride,
                    int epilogue, int32_t* status, cudaStream_t stream) {
   if (ceil_div(m, kBM) > 65535) return B200_ERR_UNSUPPORTED;
-  const int bn = n % 256 == 0 || n > 1024 ? 256 : 128;
+  int bn;
+  if (m > 64) {
+    bn = n % 256 == 0 || n > 1024 ? 256 : 128;
+  } else {
+    // weight streaming: one wave of >= 148 CTAs, as wide an N tile as that allows
+    if (ceil_div(n, 256) >= 2 * kNumSMs) bn = 256;
+    else if (ceil_div(n, 128) >= kNumSMs) bn = 128;
+    else if (ceil_div(n, 64) >= kNumSMs) bn = 64;
+    else return B200_ERR_UNSUPPORTED;
+  }
   CUtensorMap a_map, b_map;
   if (!make_bf16_matrix_map(&a_map, input, m, k, input_row_stride, kBM) ||
       !make_bf16_matrix_map(&b_map, weight, n, k, k, bn))
@@ -267,12 +301,70 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
   p.bias = static_cast<const __nv_bfloat16*>(bias);
   p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.out = static_cast<__nv_bfloat16*>(output);
+  p.partials = nullptr;
   p.status = status;
   p.m = static_cast<int>(m);
   p.k = static_cast<int>(k);
   p.n = static_cast<int>(n);
   p.epilogue = epilogue;
-  return bn == 256 ? launch<256, 4>(p, a_map, b_map, stream) : launch<128, 3>(p, a_map, b_map, stream);
+  p.splits = 1;
+  if (bn == 256) return launch<256, 4>(p, a_map, b_map, stream);
+  if (bn == 128) return launch<128, 3>(p, a_map, b_map, stream);
+  return launch<64, 4>(p, a_map, b_map, stream);
+}
+
+// Split-K plan of the partial-sum producer: 128-column tiles, as many K slices as it takes
+// to put about one CTA on each of the 148 SMs, every slice at least one 64-wide k block.
+int linear_partial_splits(int64_t k, int64_t n) {
+  const int64_t tiles = ceil_div(n, 128);
+  const int64_t kb = ceil_div(k, kBK);
+  int64_t splits = (kNumSMs + tiles / 2) / tiles;
+  if (splits < 1) splits = 1;
+  if (splits > kb) splits = kb;
+  const int64_t per = ceil_div(kb, splits);
+  return static_cast<int>(ceil_div(kb, per));
+}
+
+int linear_partial_tcgen05(const void* input, const void* weight, float* partials, int64_t m,
+                           int64_t k, int64_t n, int64_t input_row_stride, int splits,
+                           int32_t* status, cudaStream_t stream) {
+  CUtensorMap a_map, b_map;
+  if (!make_bf16_matrix_map(&a_map, input, m, k, input_row_stride, kBM) ||
+      !make_bf16_matrix_map(&b_map, weight, n, k, k, 128))
+    return B200_ERR_UNSUPPORTED;
+  Tcgen05Params p;
+  p.bias = nullptr;
+  p.residual = nullptr;
+  p.out = nullptr;
+  p.partials = partials;
+  p.status = status;
+  p.m = static_cast<int>(m);
+  p.k = static_cast<int>(k);
+  p.n = static_cast<int>(n);
+  p.epilogue = kEpiloguePartial;
+  p.splits = splits;
+  return launch<128, 3>(p, a_map, b_map, stream);
 }
 
 }  // namespace b200
+
+using namespace b200;
+
+extern "C" int64_t b200_linear_partial_splits(int64_t m, int64_t k, int64_t n) {
+  if (m <= 0 || k <= 0 || n <= 0) return 0;
+  return linear_partial_splits(k, n);
+}
+
+extern "C" int b200_linear_partial(const void* input, const void* weight, void* partials,
+                                   int64_t m, int64_t k, int64_t n, int64_t input_row_stride,
+                                   int64_t splits, int32_t* status, void* stream) {
+  if (!input || !weight || !partials || m <= 0 || k <= 0 || n <= 0 || input_row_stride < k ||
+      splits <= 0)
+    return B200_ERR_BAD_ARGUMENT;
+  if (m > 128 || splits > ceil_div(k, kBK) || splits > 65535) return B200_ERR_TOO_LARGE;
+  if (k % 8 != 0 || input_row_stride % 8 != 0 || n % 4 != 0) return B200_ERR_UNSUPPORTED;
+  if (!aligned16(input) || !aligned16(weight) || !aligned16(partials)) return B200_ERR_ALIGNMENT;
+  return linear_partial_tcgen05(input, weight, static_cast<float*>(partials), m, k, n,
+                                input_row_stride, static_cast<int>(splits), status,
+                                static_cast<cudaStream_t>(stream));
+}

@@ -157,6 +157,48 @@ class Qwen2Engine:
 
     # ------------------------------------------------------------------- decode ----
     def _decode_step(self) -> None:
+        if self.dtype == torch.bfloat16 and self.mode == "fast" and self.batch <= 128:
+            self._decode_step_chain()
+        else:
+            self._decode_step_separate()
+
+    def _decode_step_chain(self) -> None:
+        """Fast bf16 decode step: every small projection is a split-K partial-sum producer on
+        the tcgen05 kernel and the reduction rides in the next operator (bias + RoPE + KV store
+        after q|k|v; residual + RMSNorm after o and down). 8 launches per layer."""
+
+        cfg = self.config
+        batch = self.batch
+        before = kernels.launch_count(self.device)
+        x = kernels.b200_embedding(self.embed, self.input_ids)
+        cosine, sine = kernels.b200_rope_table(self.positions.view(batch, 1), self.inv_freq,
+                                               self.dtype)
+        h = kernels.b200_rms_norm(x, self.layers[0]["input_norm"], epsilon=cfg.rms_norm_eps,
+                                  round_before_weight=True, numerical_mode=self.mode)
+        for index, layer in enumerate(self.layers):
+            partials = kernels.b200_linear_partial(h, layer["qkv_w"])
+            q = kernels.b200_reduce_rope_kv_store(
+                partials, layer["qkv_b"], cosine, sine, self.state.keys[index],
+                self.state.values[index], self.positions, q_heads=cfg.num_heads)
+            attn = kernels.b200_decode_attention(
+                q, self.state.keys[index], self.state.values[index], self.attention_lengths,
+                None, scale=self.scale, numerical_mode=self.mode,
+                split_tokens=self.split_tokens, max_length_hint=self.max_length_hint)
+            partials = kernels.b200_linear_partial(attn.view(batch, cfg.q_size), layer["o_w"])
+            x, h = kernels.b200_reduce_residual_rms_norm(partials, x, layer["post_norm"],
+                                                         epsilon=cfg.rms_norm_eps)
+            a = kernels.b200_linear(h, layer["gate_up_w"], epilogue="swiglu")
+            partials = kernels.b200_linear_partial(a, layer["down_w"])
+            next_norm = self.layers[index + 1]["input_norm"] if index + 1 < len(self.layers) \
+                else self.final_norm
+            x, h = kernels.b200_reduce_residual_rms_norm(partials, x, next_norm,
+                                                         epsilon=cfg.rms_norm_eps)
+        self.logits = kernels.b200_linear(h, self.lm_head)
+        kernels.b200_argmax(self.logits, self.next_ids)
+        kernels.b200_advance_lengths(self.state._length_arena, 1, self.capacity + 1)
+        self.kernels_per_step = kernels.launch_count(self.device) - before
+
+    def _decode_step_separate(self) -> None:
         cfg = self.config
         batch = self.batch
         before = kernels.launch_count(self.device)

@@ -598,6 +598,90 @@ def b200_linear(tensor: torch.Tensor, weight: torch.Tensor,
     return output
 
 
+def linear_partial_splits(m: int, k: int, n: int) -> int:
+    return int(_lib.load().b200_linear_partial_splits(m, k, n))
+
+
+def b200_linear_partial(tensor: torch.Tensor, weight: torch.Tensor,
+                        partials: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Decode-size projection without its epilogue: fp32 partial sums [splits, M, N] over K
+    slices, to be reduced by the operator that follows (b200_reduce_*). M <= 128, bf16."""
+
+    device = _require_cuda(tensor, weight, partials)
+    if weight.ndim != 2 or tensor.ndim != 2 or tensor.shape[1] != weight.shape[1]:
+        raise ValueError("input must be M x K and weight N x K")
+    if tensor.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        raise ValueError("the partial-sum producer runs bf16")
+    if tensor.stride(1) != 1 or not weight.is_contiguous():
+        raise ValueError("input rows and the weight must be contiguous")
+    m, k = tensor.shape
+    n = weight.shape[0]
+    library = _lib.load()
+    splits = int(library.b200_linear_partial_splits(m, k, n))
+    if partials is None:
+        partials = torch.empty((splits, m, n), dtype=torch.float32, device=device)
+    elif partials.shape != (splits, m, n) or partials.dtype != torch.float32 or \
+            not partials.is_contiguous():
+        raise ValueError(f"partials must be a contiguous fp32 tensor of shape {(splits, m, n)}")
+    rt = runtime(device)
+    code = library.b200_linear_partial(tensor.data_ptr(), weight.data_ptr(), partials.data_ptr(),
+                                       m, k, n, tensor.stride(0), splits, rt.status.data_ptr(),
+                                       _stream())
+    _check(code, "b200_linear_partial")
+    _count(rt)
+    return partials
+
+
+def b200_reduce_residual_rms_norm(partials: torch.Tensor, residual: Optional[torch.Tensor],
+                                  norm_weight: Optional[torch.Tensor], *, epsilon: float,
+                                  numerical_mode: str = "fast"):
+    """x = r(r(sum of partials) + residual); h = RMSNorm(x) * w (Qwen2 rounding order).
+    Returns (x, h); h is None when norm_weight is None."""
+
+    device = _require_cuda(partials, residual, norm_weight)
+    if partials.ndim != 3 or partials.dtype != torch.float32 or not partials.is_contiguous():
+        raise ValueError("partials must be a contiguous fp32 [splits, rows, hidden] tensor")
+    splits, rows, hidden = partials.shape
+    if residual is not None and (residual.shape != (rows, hidden) or not residual.is_contiguous()
+                                 or residual.dtype != torch.bfloat16):
+        raise ValueError("residual must be a contiguous bf16 rows x hidden tensor")
+    x_out = torch.empty((rows, hidden), dtype=torch.bfloat16, device=device)
+    h_out = torch.empty_like(x_out) if norm_weight is not None else None
+    rt = runtime(device)
+    code = _lib.load().b200_reduce_residual_rms_norm(
+        partials.data_ptr(), splits, _ptr(residual), _ptr(norm_weight), x_out.data_ptr(),
+        _ptr(h_out), rows, hidden, float(epsilon), _mode(numerical_mode), _stream())
+    _check(code, "b200_reduce_residual_rms_norm")
+    _count(rt)
+    return x_out, h_out
+
+
+def b200_reduce_rope_kv_store(partials: torch.Tensor, bias: Optional[torch.Tensor],
+                              cosine: torch.Tensor, sine: torch.Tensor, key_buffer: torch.Tensor,
+                              value_buffer: torch.Tensor, positions: torch.Tensor, *,
+                              q_heads: int) -> torch.Tensor:
+    """q|k|v = r(sum of partials + bias); RoPE on q and k; k, v into the KV buffers at
+    positions[b]. Returns the rotated query, B x Hq x 1 x D."""
+
+    device = _require_cuda(partials, bias, cosine, sine, key_buffer, value_buffer, positions)
+    splits, batch, width = partials.shape
+    _, capacity, kv_heads, dim = key_buffer.shape
+    if width != (q_heads + 2 * kv_heads) * dim or key_buffer.shape[0] != batch:
+        raise ValueError("partials do not match the head layout of the KV buffers")
+    cos2, sin2 = cosine.reshape(batch, dim), sine.reshape(batch, dim)
+    if not (cos2.is_contiguous() and sin2.is_contiguous()):
+        raise ValueError("cosine / sine must be contiguous")
+    query_out = torch.empty((batch, q_heads, 1, dim), dtype=torch.bfloat16, device=device)
+    rt = runtime(device)
+    code = _lib.load().b200_reduce_rope_kv_store(
+        partials.data_ptr(), splits, _ptr(bias), cos2.data_ptr(), sin2.data_ptr(),
+        query_out.data_ptr(), key_buffer.data_ptr(), value_buffer.data_ptr(), positions.data_ptr(),
+        batch, q_heads, kv_heads, dim, capacity, rt.status.data_ptr(), _stream())
+    _check(code, "b200_reduce_rope_kv_store")
+    _count(rt)
+    return query_out
+
+
 def interleave_gate_up(gate_weight: torch.Tensor, up_weight: torch.Tensor) -> torch.Tensor:
     """Row-interleaves gate and up projection weights (gate_0, up_0, gate_1, ...) for the
     SwiGLU epilogue. A one-time weight repack done at load time with a device copy."""

@@ -451,6 +451,61 @@ def test_linear_tcgen05_path_matches_the_oracle_and_the_warp_level_path(m, k, n,
     close(outputs["tcgen05"][0], outputs["mma.sync"][0].float().cpu(), 1e-2)
 
 
+@pytest.mark.parametrize("m,k,n", [(64, 896, 1152), (64, 896, 896), (64, 4864, 896), (3, 256, 512),
+                                   (128, 896, 896), (17, 512, 260)])
+def test_split_k_partial_producer_and_its_consumers(m, k, n):
+    """b200_linear_partial + reduce_residual_rms_norm == linear -> add -> rms_norm of the oracle;
+    the partial sums themselves add up to the fp32 product."""
+    g = torch.Generator().manual_seed(m * 7 + n)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
+    res = torch.randn(m, n, generator=g).bfloat16()
+    nw = (1 + 0.1 * torch.randn(n, generator=g)).bfloat16()
+    partials = b200.kernels.b200_linear_partial(x.cuda(), w.cuda())
+    assert partials.shape[0] == kernels.linear_partial_splits(m, k, n)
+    exact_product = x.float() @ w.float().t()
+    torch.testing.assert_close(partials.sum(0).cpu(), exact_product, rtol=1e-3, atol=1e-3)
+    y = serve_ops.residual_add(res, serve_ops.linear(x, w))
+    h = serve_ops.rms_norm(y, nw, 1e-6, round_before_weight=True)
+    x_out, h_out = b200.kernels.b200_reduce_residual_rms_norm(partials, res.cuda(), nw.cuda(),
+                                                              epsilon=1e-6)
+    close(x_out, y, BF16_TOL)
+    close(h_out, h, BF16_TOL)
+    plain, none = b200.kernels.b200_reduce_residual_rms_norm(partials, None, None, epsilon=1e-6)
+    assert none is None
+    close(plain, serve_ops.linear(x, w), BF16_TOL)
+    kernels.runtime().check_status()
+
+
+def test_split_k_partials_feed_rope_and_kv_store():
+    g = torch.Generator().manual_seed(99)
+    b, hq, hkv, d, hidden, capacity = 5, 14, 2, 64, 896, 32
+    width = (hq + 2 * hkv) * d
+    x = torch.randn(b, hidden, generator=g).bfloat16()
+    w = (torch.randn(width, hidden, generator=g) * 0.05).bfloat16()
+    bias = torch.randn(width, generator=g).bfloat16()
+    positions = torch.tensor([0, 31, 7, 7, 20])
+    inv_freq = serve_ops.rope_inverse_frequency(d, 1e6)
+    cos, sin = serve_ops.rope_table(positions.view(b, 1), inv_freq, torch.bfloat16)
+    qkv = serve_ops.linear(x, w, bias)
+    q = qkv[:, : hq * d].view(b, 1, hq, d).transpose(1, 2)
+    k = qkv[:, hq * d: (hq + hkv) * d].view(b, 1, hkv, d).transpose(1, 2)
+    v = qkv[:, (hq + hkv) * d:].view(b, 1, hkv, d).transpose(1, 2)
+    q_ref, k_ref = serve_ops.rope(q, k, cos, sin)
+    kbuf = torch.zeros(b, capacity, hkv, d, dtype=torch.bfloat16)
+    vbuf = torch.zeros_like(kbuf)
+    serve_ops.kv_store(kbuf, vbuf, k_ref, v, positions)
+    k_dev, v_dev = torch.zeros_like(kbuf).cuda(), torch.zeros_like(vbuf).cuda()
+    partials = b200.kernels.b200_linear_partial(x.cuda(), w.cuda())
+    q_out = b200.kernels.b200_reduce_rope_kv_store(partials, bias.cuda(), cos.cuda(), sin.cuda(),
+                                                   k_dev, v_dev, positions.cuda(), q_heads=hq)
+    close(q_out, q_ref, BF16_TOL)
+    close(k_dev, kbuf, BF16_TOL)
+    close(v_dev, vbuf, BF16_TOL)
+    assert k_dev[0, 1:].eq(0).all()  # only the addressed rows were written
+    kernels.runtime().check_status()
+
+
 def test_linear_f32_epilogues():
     g = torch.Generator().manual_seed(77)
     x = torch.randn(7, 256, generator=g)
