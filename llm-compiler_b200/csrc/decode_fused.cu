@@ -15,8 +15,32 @@
 namespace b200 {
 namespace {
 
-constexpr int kNormThreads = 256;
-constexpr int kMaxPerThread = 16;  // hidden <= 256 * 16 = 4096 kept in registers
+constexpr int kNormThreads = 1024;  // one element per thread at hidden <= 1024
+constexpr int kMaxPerThread = 4;    // hidden <= 4096 kept in registers
+
+// Sum over the K slices of one element, slice order fixed; eight loads in flight per round
+// so that the latency of a round is paid once per eight slices.
+__device__ __forceinline__ float sum_slices(const float* first, int64_t slice, int splits) {
+  float acc = 0.0f;
+  int s = 0;
+  for (; s + 8 <= splits; s += 8) {
+    float t[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t[j] = __ldcg(first + (s + j) * slice);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += t[j];
+  }
+  if (s + 4 <= splits) {
+    float t[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) t[j] = __ldcg(first + (s + j) * slice);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc += t[j];
+    s += 4;
+  }
+  for (; s < splits; ++s) acc += __ldcg(first + s * slice);
+  return acc;
+}
 
 __global__ void __launch_bounds__(kNormThreads)
 reduce_residual_rms_norm_kernel(const float* __restrict__ partials, int splits,
@@ -31,12 +55,10 @@ reduce_residual_rms_norm_kernel(const float* __restrict__ partials, int splits,
   float sum = 0.0f;
 #pragma unroll
   for (int i = 0; i < kMaxPerThread; ++i) {
-    const int c = threadIdx.x + i * kNormThreads;
+    const int c = threadIdx.x + i * blockDim.x;
     x[i] = 0.0f;
     if (c < hidden) {
-      float acc = 0.0f;
-      for (int s = 0; s < splits; ++s) acc += __ldcg(prow + s * slice + c);
-      float v = round_bf16(acc);
+      float v = round_bf16(sum_slices(prow + c, slice, splits));
       if (residual != nullptr)
         v = round_bf16(__fadd_rn(v, __bfloat162float(residual[static_cast<int64_t>(row) * hidden + c])));
       x[i] = v;
@@ -51,7 +73,7 @@ reduce_residual_rms_norm_kernel(const float* __restrict__ partials, int splits,
   if ((threadIdx.x & 31) == 0) partial_sum[threadIdx.x >> 5] = sum;
   __syncthreads();
   if (threadIdx.x < 32) {
-    float v = threadIdx.x < kNormThreads / 32 ? partial_sum[threadIdx.x] : 0.0f;
+    float v = threadIdx.x < (blockDim.x >> 5) ? partial_sum[threadIdx.x] : 0.0f;
     v = warp_sum(v);
     if (threadIdx.x == 0) total = v;
   }
@@ -60,7 +82,7 @@ reduce_residual_rms_norm_kernel(const float* __restrict__ partials, int splits,
                                : rsqrtf(total / static_cast<float>(hidden) + epsilon);
 #pragma unroll
   for (int i = 0; i < kMaxPerThread; ++i) {
-    const int c = threadIdx.x + i * kNormThreads;
+    const int c = threadIdx.x + i * blockDim.x;
     if (c < hidden) {
       const float n = round_bf16(__fmul_rn(x[i], inv_rms));
       h_out[static_cast<int64_t>(row) * hidden + c] =
@@ -91,11 +113,8 @@ __global__ void reduce_rope_kv_store_kernel(const float* __restrict__ partials, 
     const int b = idx / (half * heads);
     const int col_lo = hh * dim + d, col_hi = col_lo + half;
     const float* prow = partials + static_cast<int64_t>(b) * width;
-    float lo = 0.0f, hi = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-      lo += __ldcg(prow + s * slice + col_lo);
-      hi += __ldcg(prow + s * slice + col_hi);
-    }
+    float lo = sum_slices(prow + col_lo, slice, splits);
+    float hi = sum_slices(prow + col_hi, slice, splits);
     if (bias != nullptr) {
       lo += __bfloat162float(bias[col_lo]);
       hi += __bfloat162float(bias[col_hi]);
@@ -144,7 +163,9 @@ extern "C" int b200_reduce_residual_rms_norm(const void* partials, int64_t split
     return B200_ERR_BAD_ARGUMENT;
   if (hidden > kNormThreads * kMaxPerThread) return B200_ERR_TOO_LARGE;
   if (rows == 0) return B200_OK;
-  reduce_residual_rms_norm_kernel<<<static_cast<int>(rows), kNormThreads, 0,
+  int threads = static_cast<int>((hidden + 31) / 32 * 32);
+  if (threads > kNormThreads) threads = kNormThreads;
+  reduce_residual_rms_norm_kernel<<<static_cast<int>(rows), threads, 0,
                                     static_cast<cudaStream_t>(stream)>>>(
       static_cast<const float*>(partials), static_cast<int>(splits),
       static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(norm_weight),

@@ -40,6 +40,7 @@ struct Tcgen05Params {
   float* partials;  // [splits, m, n] fp32 when epilogue == kEpiloguePartial
   int32_t* status;
   int m, k, n, epilogue, splits;
+  int bn;  // columns per tile: a multiple of 16, at most the kernel's BN
 };
 
 __device__ __forceinline__ float silu_f32(float x) {
@@ -92,14 +93,19 @@ __device__ __forceinline__ void tmem_load_32x32(uint32_t taddr, float (&v)[32]) 
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-template <int BN, int STAGES>
+// A_ROWS: rows of the x box a stage holds. With at most 64 activation rows (decode) the box
+// is 64 rows and the MMA, which always spans 128 rows, reads on into the W tile behind it:
+// accumulator lanes 64..127 then hold junk that the epilogue never touches (rows >= M).
+template <int BN, int STAGES, int A_ROWS>
 __global__ void __launch_bounds__(kThreads)
 linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap a_map,
                       const __grid_constant__ CUtensorMap b_map) {
-  constexpr int kABytes = kBM * 128;
+  constexpr int kABytes = A_ROWS * 128;
   constexpr int kBBytes = BN * 128;
   constexpr int kStageBytes = kABytes + kBBytes;
-  constexpr uint32_t kIdesc = instruction_descriptor(kBM, BN);
+  const int bn = p.bn;
+  const uint32_t idesc = instruction_descriptor(kBM, bn);
+  const uint32_t stage_tx_bytes = static_cast<uint32_t>(kABytes + bn * 128);
 
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t full_bar[STAGES];
@@ -128,7 +134,8 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   }
   if (warp == 1) {  // one warp allocates the accumulator columns and later frees them
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(&tmem_base_slot)), "r"(static_cast<uint32_t>(BN)) : "memory");
+                 ::"r"(smem_u32(&tmem_base_slot)), "r"(static_cast<uint32_t>(BN < 32 ? 32 : BN))
+                 : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -147,9 +154,9 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
       }
       const uint32_t bar = smem_u32(&full_bar[s]);
       const uint32_t a_dst = smem_base + s * kStageBytes;
-      mbarrier_arrive_expect_tx(bar, kStageBytes);
+      mbarrier_arrive_expect_tx(bar, stage_tx_bytes);
       tma_load_2d(a_dst, &a_map, bar, (kb_first + kb) * kBK, tile_m * kBM);
-      tma_load_2d(a_dst + kABytes, &b_map, bar, (kb_first + kb) * kBK, tile_n * BN);
+      tma_load_2d(a_dst + kABytes, &b_map, bar, (kb_first + kb) * kBK, tile_n * bn);
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer ----
@@ -165,7 +172,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
 #pragma unroll
       for (int j = 0; j < kBK / 16; ++j)
         umma_bf16(tmem_base, smem_descriptor(a_addr + j * 32), smem_descriptor(b_addr + j * 32),
-                  kIdesc, (kb > 0 || j > 0) ? 1u : 0u);
+                  idesc, (kb > 0 || j > 0) ? 1u : 0u);
       umma_commit(smem_u32(&empty_bar[s]));  // the stage is free once these MMAs have read it
     }
     umma_commit(smem_u32(&accum_bar));  // the accumulator is complete once all MMAs retired
@@ -180,9 +187,10 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
     const int row = tile_m * kBM + warp * 32 + lane;
     const int out_cols = p.epilogue == B200_EPILOGUE_SWIGLU ? p.n / 2 : p.n;
 #pragma unroll 1
-    for (int c0 = 0; c0 < BN; c0 += 32) {
-      const int col0 = tile_n * BN + c0;
-      if (col0 >= p.n) break;  // warp-uniform: tcgen05.ld is a warp-wide instruction
+    const int n_end = min(p.n, (tile_n + 1) * bn);  // columns of this tile
+    for (int c0 = 0; c0 < bn; c0 += 32) {
+      const int col0 = tile_n * bn + c0;
+      if (col0 >= n_end) break;  // warp-uniform: tcgen05.ld is a warp-wide instruction
       float v[32];
       tmem_load_32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c0, v);
       if (row >= p.m) continue;
@@ -192,7 +200,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
       }
       if (p.epilogue == kEpiloguePartial) {
         float* dst = p.partials + (static_cast<int64_t>(split) * p.m + row) * p.n + col0;
-        if (col0 + 32 <= p.n && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+        if (col0 + 32 <= n_end && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
           for (int i = 0; i < 8; ++i)
             reinterpret_cast<float4*>(dst)[i] =
@@ -200,14 +208,14 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (col0 + i < p.n) dst[i] = v[i];
+            if (col0 + i < n_end) dst[i] = v[i];
         }
         continue;
       }
       if (p.bias != nullptr) {
 #pragma unroll
         for (int i = 0; i < 32; ++i)
-          if (col0 + i < p.n) v[i] += __bfloat162float(p.bias[col0 + i]);
+          if (col0 + i < n_end) v[i] += __bfloat162float(p.bias[col0 + i]);
       }
       if (p.epilogue == B200_EPILOGUE_SWIGLU) {
         // columns 2j / 2j+1 are gate_j / up_j
@@ -216,7 +224,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
 #pragma unroll
         for (int j = 0; j < 16; ++j)
           y[j] = round_bf16(silu_f32(round_bf16(v[2 * j]))) * round_bf16(v[2 * j + 1]);
-        if (col0 + 32 <= p.n && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+        if (col0 + 32 <= n_end && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
           for (int i = 0; i < 2; ++i)
             reinterpret_cast<uint4*>(dst)[i] =
@@ -225,7 +233,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
         } else {
 #pragma unroll
           for (int j = 0; j < 16; ++j)
-            if (col0 / 2 + j < out_cols) dst[j] = __float2bfloat16_rn(y[j]);
+            if (col0 + 2 * j + 1 < n_end) dst[j] = __float2bfloat16_rn(y[j]);
         }
         continue;
       }
@@ -235,10 +243,10 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
       if (p.epilogue == B200_EPILOGUE_RESIDUAL) {
 #pragma unroll
         for (int i = 0; i < 32; ++i)
-          if (col0 + i < p.n) v[i] = __fadd_rn(v[i], __bfloat162float(p.residual[o + i]));
+          if (col0 + i < n_end) v[i] = __fadd_rn(v[i], __bfloat162float(p.residual[o + i]));
       }
       __nv_bfloat16* dst = p.out + o;
-      if (col0 + 32 <= p.n && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+      if (col0 + 32 <= n_end && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
         for (int i = 0; i < 4; ++i)
           reinterpret_cast<uint4*>(dst)[i] =
@@ -247,7 +255,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i)
-          if (col0 + i < p.n) dst[i] = __float2bfloat16_rn(v[i]);
+          if (col0 + i < n_end) dst[i] = __float2bfloat16_rn(v[i]);
       }
     }
   } else if (threadIdx.x == 0 && p.status != nullptr) {
@@ -258,20 +266,53 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   __syncthreads();
   if (warp == 1)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
-                 ::"r"(tmem_base), "r"(static_cast<uint32_t>(BN)) : "memory");
+                 ::"r"(tmem_base), "r"(static_cast<uint32_t>(BN < 32 ? 32 : BN)) : "memory");
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int A_ROWS>
 int launch(const Tcgen05Params& p, const CUtensorMap& a_map, const CUtensorMap& b_map,
            cudaStream_t stream) {
-  constexpr int smem = STAGES * (kBM + BN) * 128 + 1024;
-  auto kernel = linear_tcgen05_kernel<BN, STAGES>;
+  // slack: the last stage's 64-row x box is followed by up to 8 KB that the 128-row MMA reads past
+  constexpr int smem = STAGES * (A_ROWS + BN) * 128 + 9216;
+  static_assert(smem <= 227 * 1024, "stage ring exceeds shared memory");
+  auto kernel = linear_tcgen05_kernel<BN, STAGES, A_ROWS>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return B200_ERR_LAUNCH;
-  dim3 grid(static_cast<unsigned>(ceil_div(p.n, BN)), static_cast<unsigned>(ceil_div(p.m, kBM)),
+  if (p.bn <= 0 || p.bn > BN || p.bn % 16 != 0) return B200_ERR_BAD_ARGUMENT;
+  dim3 grid(static_cast<unsigned>(ceil_div(p.n, p.bn)), static_cast<unsigned>(ceil_div(p.m, kBM)),
             static_cast<unsigned>(p.splits));
   kernel<<<grid, kThreads, smem, stream>>>(p, a_map, b_map);
   return launch_status();
+}
+
+// Split-K plan of the partial-sum producer: N tile width and K slices chosen to put about
+// one CTA on each of the 148 SMs at the least traffic (activation re-reads per N tile +
+// fp32 partials written and read back per K slice).
+struct PartialPlan {
+  int bn, splits;
+};
+
+PartialPlan plan_partial(int64_t m, int64_t k, int64_t n) {
+  const int64_t kb = ceil_div(k, kBK);
+  PartialPlan best{128, 1};
+  double best_cost = 1e300;
+  for (int bn : {32, 64, 128}) {
+    const int64_t tiles = ceil_div(n, bn);
+    int64_t splits = (kNumSMs + tiles / 2) / tiles;
+    if (splits < 1) splits = 1;
+    if (splits > kb) splits = kb;
+    const int64_t per = ceil_div(kb, splits);
+    splits = ceil_div(kb, per);
+    const double ctas = static_cast<double>(tiles * splits);
+    const double bytes = static_cast<double>(tiles) * m * k * 2 + 2.0 * splits * m * n * 4;
+    const double fill = ctas >= kNumSMs ? 1.0 : ctas / kNumSMs;
+    const double cost = bytes / fill;
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = PartialPlan{bn, static_cast<int>(splits)};
+    }
+  }
+  return best;
 }
 
 }  // namespace
@@ -287,14 +328,27 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
   if (m > 64) {
     bn = n % 256 == 0 || n > 1024 ? 256 : 128;
   } else {
-    // weight streaming: one wave of >= 148 CTAs, as wide an N tile as that allows
-    if (ceil_div(n, 256) >= 2 * kNumSMs) bn = 256;
-    else if (ceil_div(n, 128) >= kNumSMs) bn = 128;
-    else if (ceil_div(n, 64) >= kNumSMs) bn = 64;
-    else return B200_ERR_UNSUPPORTED;
+    // Weight streaming with one deep-pipelined CTA per SM: the N tile is the width (a
+    // multiple of 16, at most 256) whose tile count fills whole waves of 148 CTAs best;
+    // fewer than ~120 tiles would leave SMs idle and is left to the split-K kernel.
+    if (ceil_div(n, 16) < kNumSMs - 28) return B200_ERR_UNSUPPORTED;
+    double best = -1.0;
+    bn = 0;
+    for (int candidate = 256; candidate >= 16; candidate -= 16) {
+      const int64_t tiles = ceil_div(n, candidate);
+      const int64_t waves = ceil_div(tiles, kNumSMs);
+      const double fill = static_cast<double>(tiles) / static_cast<double>(waves * kNumSMs);
+      // wider tiles re-read the activations less often: prefer them on (near) ties
+      const double score = fill + 0.0002 * candidate;
+      if (score > best) {
+        best = score;
+        bn = candidate;
+      }
+    }
+    if (best < 0.8) return B200_ERR_UNSUPPORTED;
   }
   CUtensorMap a_map, b_map;
-  if (!make_bf16_matrix_map(&a_map, input, m, k, input_row_stride, kBM) ||
+  if (!make_bf16_matrix_map(&a_map, input, m, k, input_row_stride, m <= 64 ? 64 : kBM) ||
       !make_bf16_matrix_map(&b_map, weight, n, k, k, bn))
     return B200_ERR_UNSUPPORTED;
   Tcgen05Params p;
@@ -308,29 +362,27 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
   p.n = static_cast<int>(n);
   p.epilogue = epilogue;
   p.splits = 1;
-  if (bn == 256) return launch<256, 4>(p, a_map, b_map, stream);
-  if (bn == 128) return launch<128, 3>(p, a_map, b_map, stream);
-  return launch<64, 4>(p, a_map, b_map, stream);
+  p.bn = bn;
+  if (m <= 64) {
+    if (bn > 128) return launch<256, 5, 64>(p, a_map, b_map, stream);
+    if (bn > 64) return launch<128, 8, 64>(p, a_map, b_map, stream);
+    return launch<64, 12, 64>(p, a_map, b_map, stream);
+  }
+  if (bn == 256) return launch<256, 4, 128>(p, a_map, b_map, stream);
+  if (bn == 128) return launch<128, 3, 128>(p, a_map, b_map, stream);
+  return launch<64, 4, 128>(p, a_map, b_map, stream);
 }
 
-// Split-K plan of the partial-sum producer: 128-column tiles, as many K slices as it takes
-// to put about one CTA on each of the 148 SMs, every slice at least one 64-wide k block.
-int linear_partial_splits(int64_t k, int64_t n) {
-  const int64_t tiles = ceil_div(n, 128);
-  const int64_t kb = ceil_div(k, kBK);
-  int64_t splits = (kNumSMs + tiles / 2) / tiles;
-  if (splits < 1) splits = 1;
-  if (splits > kb) splits = kb;
-  const int64_t per = ceil_div(kb, splits);
-  return static_cast<int>(ceil_div(kb, per));
-}
+int linear_partial_splits(int64_t m, int64_t k, int64_t n) { return plan_partial(m, k, n).splits; }
 
 int linear_partial_tcgen05(const void* input, const void* weight, float* partials, int64_t m,
                            int64_t k, int64_t n, int64_t input_row_stride, int splits,
                            int32_t* status, cudaStream_t stream) {
+  const PartialPlan plan = plan_partial(m, k, n);
+  const int a_rows = m <= 64 ? 64 : 128;
   CUtensorMap a_map, b_map;
-  if (!make_bf16_matrix_map(&a_map, input, m, k, input_row_stride, kBM) ||
-      !make_bf16_matrix_map(&b_map, weight, n, k, k, 128))
+  if (!make_bf16_matrix_map(&a_map, input, m, k, input_row_stride, a_rows) ||
+      !make_bf16_matrix_map(&b_map, weight, n, k, k, plan.bn))
     return B200_ERR_UNSUPPORTED;
   Tcgen05Params p;
   p.bias = nullptr;
@@ -343,7 +395,15 @@ int linear_partial_tcgen05(const void* input, const void* weight, float* partial
   p.n = static_cast<int>(n);
   p.epilogue = kEpiloguePartial;
   p.splits = splits;
-  return launch<128, 3>(p, a_map, b_map, stream);
+  p.bn = plan.bn;
+  if (a_rows == 64) {
+    if (plan.bn == 32) return launch<32, 8, 64>(p, a_map, b_map, stream);
+    if (plan.bn == 64) return launch<64, 6, 64>(p, a_map, b_map, stream);
+    return launch<128, 4, 64>(p, a_map, b_map, stream);
+  }
+  if (plan.bn == 32) return launch<32, 6, 128>(p, a_map, b_map, stream);
+  if (plan.bn == 64) return launch<64, 4, 128>(p, a_map, b_map, stream);
+  return launch<128, 3, 128>(p, a_map, b_map, stream);
 }
 
 }  // namespace b200
@@ -352,7 +412,7 @@ using namespace b200;
 
 extern "C" int64_t b200_linear_partial_splits(int64_t m, int64_t k, int64_t n) {
   if (m <= 0 || k <= 0 || n <= 0) return 0;
-  return linear_partial_splits(k, n);
+  return linear_partial_splits(m, k, n);
 }
 
 extern "C" int b200_linear_partial(const void* input, const void* weight, void* partials,
