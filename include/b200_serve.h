@@ -53,6 +53,23 @@ extern "C" {
 #define B200_STATUS_BAD_POSITION 8      /* negative KV position: write skipped            */
 #define B200_STATUS_WAIT_TIMEOUT 16     /* a bounded in-kernel wait gave up: result invalid */
 
+/* launch-mode flags (b200_set_launch_mode) */
+#define B200_LAUNCH_PROGRAMMATIC 1      /* decode-chain kernels use programmatic dependent launch */
+#define B200_LAUNCH_CONSTANT_WEIGHTS 2  /* weight operands are written by no kernel in flight  */
+
+/* Process-wide launch mode of the decode-chain kernels (embedding, rope table, rms_norm fast
+ * path, linear on tcgen05, linear_partial, the two reduce_* consumers, decode attention,
+ * argmax, advance_lengths). No counterpart in the reference, whose Triton launches are always
+ * fully serialised (ReferenceExecutor.run, execution.py:530-575, runs one operation after another).
+ * B200_LAUNCH_PROGRAMMATIC: each of those kernels may become resident before its predecessor
+ * in the stream has finished and waits on the device (griddepcontrol.wait) before touching
+ * any tensor; results are unchanged. B200_LAUNCH_CONSTANT_WEIGHTS additionally lets a linear
+ * kernel fetch its `weight` tiles before that wait: only valid while no kernel that writes a
+ * weight tensor is in flight on the device. Returns the previous flags, or
+ * B200_ERR_BAD_ARGUMENT for unknown bits. Default 0. */
+int b200_set_launch_mode(int flags);
+int b200_get_launch_mode(void);
+
 /* Version / build probe. Returns 100 * major + minor of this ABI. */
 int b200_abi_version(void);
 /* Human-readable message for a B200_ERR_* code (static storage). */

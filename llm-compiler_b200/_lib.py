@@ -23,6 +23,9 @@ STATUS_BAD_TOKEN_ID = 4
 STATUS_BAD_POSITION = 8
 STATUS_WAIT_TIMEOUT = 16
 
+LAUNCH_PROGRAMMATIC = 1
+LAUNCH_CONSTANT_WEIGHTS = 2
+
 ERR_BAD_ARGUMENT, ERR_UNSUPPORTED, ERR_ALIGNMENT = -1, -2, -3
 ERR_WORKSPACE, ERR_LAUNCH, ERR_TOO_LARGE = -4, -5, -6
 
@@ -37,6 +40,8 @@ _I64P = POINTER(c_int64)
 SIGNATURES = {
     "b200_abi_version": (c_int, []),
     "b200_error_string": (c_char_p, [c_int]),
+    "b200_set_launch_mode": (c_int, [c_int]),
+    "b200_get_launch_mode": (c_int, []),
     "b200_kv_store": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
                               c_int64, c_int64, c_int64, _I64P, _I64P, c_int, c_void_p, c_void_p]),
     "b200_rope": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,

@@ -1,7 +1,24 @@
 // ABI probe and error strings of libb200serve.so.
+#include <atomic>
+
 #include "b200_serve.h"
 
+namespace b200 {
+namespace {
+std::atomic<int> g_launch_mode{0};
+}
+int launch_mode() { return g_launch_mode.load(std::memory_order_relaxed); }
+}  // namespace b200
+
 extern "C" int b200_abi_version(void) { return 100; }
+
+extern "C" int b200_set_launch_mode(int flags) {
+  if ((flags & ~(B200_LAUNCH_PROGRAMMATIC | B200_LAUNCH_CONSTANT_WEIGHTS)) != 0)
+    return B200_ERR_BAD_ARGUMENT;
+  return b200::g_launch_mode.exchange(flags, std::memory_order_relaxed);
+}
+
+extern "C" int b200_get_launch_mode(void) { return b200::launch_mode(); }
 
 extern "C" const char* b200_error_string(int code) {
   switch (code) {

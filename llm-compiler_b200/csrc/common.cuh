@@ -15,6 +15,44 @@ inline int launch_status() {
   return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
 
+// ---- Programmatic dependent launch -------------------------------------------------------
+// With B200_LAUNCH_PROGRAMMATIC set (b200_set_launch_mode) the kernels of the decode chain are
+// launched with programmatic stream serialisation: a kernel may become resident while its
+// predecessor in the stream still runs. Every such kernel signals its own dependents at its
+// top and executes grid_dependency_wait() before its first access to memory that another
+// kernel writes, and before its first write; only set-up (mbarriers, tensor memory) and, with
+// B200_LAUNCH_CONSTANT_WEIGHTS, loads of weight operands come before the wait. Completion is
+// transitive: the wait returns once the predecessor has finished, and the predecessor could
+// not finish before its own wait did.
+int launch_mode();  // defined in api.cu
+
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Launches `kernel`; under B200_LAUNCH_PROGRAMMATIC with the programmatic attribute. Only for
+// kernels that execute grid_dependency_wait().
+template <typename... Params, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  if ((launch_mode() & B200_LAUNCH_PROGRAMMATIC) != 0) {
+    config.attrs = attribute;
+    config.numAttrs = 1;
+  }
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
@@ -149,6 +187,11 @@ __device__ __forceinline__ void fence_mbarrier_init() {
 }
 __device__ __forceinline__ void mbarrier_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%1], %0;\n" ::"r"(bytes), "r"(bar)
+               : "memory");
+}
+// Adds `bytes` to the transaction count of the current phase without arriving.
+__device__ __forceinline__ void mbarrier_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%1], %0;\n" ::"r"(bytes), "r"(bar)
                : "memory");
 }
 __device__ __forceinline__ bool mbarrier_try_wait(uint32_t bar, uint32_t parity) {

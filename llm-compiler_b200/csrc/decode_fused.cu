@@ -48,6 +48,8 @@ reduce_residual_rms_norm_kernel(const float* __restrict__ partials, int splits,
                                 const __nv_bfloat16* __restrict__ weight,
                                 __nv_bfloat16* __restrict__ x_out, __nv_bfloat16* __restrict__ h_out,
                                 int rows, int hidden, float epsilon, int compat) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int row = blockIdx.x;
   const int64_t slice = static_cast<int64_t>(rows) * hidden;
   const float* prow = partials + static_cast<int64_t>(row) * hidden;
@@ -102,6 +104,8 @@ __global__ void reduce_rope_kv_store_kernel(const float* __restrict__ partials, 
                                             const int64_t* __restrict__ positions, int batch,
                                             int q_heads, int kv_heads, int dim, int capacity,
                                             int32_t* status) {
+  grid_launch_dependents();
+  grid_dependency_wait();
   const int half = dim / 2;
   const int heads = q_heads + 2 * kv_heads;
   const int width = heads * dim;  // columns of the fused q|k|v projection
@@ -165,14 +169,14 @@ extern "C" int b200_reduce_residual_rms_norm(const void* partials, int64_t split
   if (rows == 0) return B200_OK;
   int threads = static_cast<int>((hidden + 31) / 32 * 32);
   if (threads > kNormThreads) threads = kNormThreads;
-  reduce_residual_rms_norm_kernel<<<static_cast<int>(rows), threads, 0,
-                                    static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const float*>(partials), static_cast<int>(splits),
+  const cudaError_t launched = launch_chained(
+      reduce_residual_rms_norm_kernel, dim3(static_cast<unsigned>(rows)), dim3(threads), 0,
+      static_cast<cudaStream_t>(stream), static_cast<const float*>(partials), static_cast<int>(splits),
       static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(norm_weight),
       static_cast<__nv_bfloat16*>(x_out), static_cast<__nv_bfloat16*>(h_out),
       static_cast<int>(rows), static_cast<int>(hidden), static_cast<float>(epsilon),
       mode == B200_MODE_PYTORCH_COMPATIBLE ? 1 : 0);
-  return launch_status();
+  return launched == cudaSuccess ? launch_status() : B200_ERR_LAUNCH;
 }
 
 extern "C" int b200_reduce_rope_kv_store(const void* partials, int64_t splits, const void* bias,
@@ -191,13 +195,13 @@ extern "C" int b200_reduce_rope_kv_store(const void* partials, int64_t splits, c
   const int threads = 256;
   int64_t blocks = ceil_div(total, threads);
   if (blocks > kNumSMs * 8) blocks = kNumSMs * 8;
-  reduce_rope_kv_store_kernel<<<static_cast<int>(blocks), threads, 0,
-                                static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const float*>(partials), static_cast<int>(splits),
+  const cudaError_t launched = launch_chained(
+      reduce_rope_kv_store_kernel, dim3(static_cast<unsigned>(blocks)), dim3(threads), 0,
+      static_cast<cudaStream_t>(stream), static_cast<const float*>(partials), static_cast<int>(splits),
       static_cast<const __nv_bfloat16*>(bias), static_cast<const __nv_bfloat16*>(cosine),
       static_cast<const __nv_bfloat16*>(sine), static_cast<__nv_bfloat16*>(query_out),
       static_cast<__nv_bfloat16*>(key_buffer), static_cast<__nv_bfloat16*>(value_buffer),
       positions, static_cast<int>(batch), static_cast<int>(q_heads), static_cast<int>(kv_heads),
       static_cast<int>(head_dim), static_cast<int>(capacity), status);
-  return launch_status();
+  return launched == cudaSuccess ? launch_status() : B200_ERR_LAUNCH;
 }

@@ -41,6 +41,7 @@ struct Tcgen05Params {
   int32_t* status;
   int m, k, n, epilogue, splits;
   int bn;  // columns per tile: a multiple of 16, at most the kernel's BN
+  int prefetch_weights;  // W tiles may be fetched before the predecessor kernel has finished
 };
 
 __device__ __forceinline__ float silu_f32(float x) {
@@ -114,6 +115,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   __shared__ uint32_t tmem_base_slot;
   __shared__ int failed;
 
+  grid_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z;
   const int kb_total = (p.k + kBK - 1) / kBK;
@@ -145,6 +147,17 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
 
   if (warp == 0 && lane == 0) {
     // ---- TMA producer ----
+    // The first ring of W tiles does not depend on the kernel before this one: fetch it
+    // before waiting for that kernel (the transaction bytes are announced without arriving,
+    // so a stage cannot complete before its x box has been requested as well).
+    const int early = p.prefetch_weights ? min(nkb, STAGES) : 0;
+    for (int kb = 0; kb < early; ++kb) {
+      const uint32_t bar = smem_u32(&full_bar[kb]);
+      mbarrier_expect_tx(bar, static_cast<uint32_t>(bn * 128));
+      tma_load_2d(smem_base + kb * kStageBytes + kABytes, &b_map, bar, (kb_first + kb) * kBK,
+                  tile_n * bn);
+    }
+    grid_dependency_wait();
     for (int kb = 0; kb < nkb; ++kb) {
       const int s = kb % STAGES;
       if (kb >= STAGES &&
@@ -154,11 +167,19 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
       }
       const uint32_t bar = smem_u32(&full_bar[s]);
       const uint32_t a_dst = smem_base + s * kStageBytes;
-      mbarrier_arrive_expect_tx(bar, stage_tx_bytes);
-      tma_load_2d(a_dst, &a_map, bar, (kb_first + kb) * kBK, tile_m * kBM);
-      tma_load_2d(a_dst + kABytes, &b_map, bar, (kb_first + kb) * kBK, tile_n * bn);
+      if (kb < early) {
+        mbarrier_arrive_expect_tx(bar, static_cast<uint32_t>(kABytes));
+        tma_load_2d(a_dst, &a_map, bar, (kb_first + kb) * kBK, tile_m * kBM);
+      } else {
+        mbarrier_arrive_expect_tx(bar, stage_tx_bytes);
+        tma_load_2d(a_dst, &a_map, bar, (kb_first + kb) * kBK, tile_m * kBM);
+        tma_load_2d(a_dst + kABytes, &b_map, bar, (kb_first + kb) * kBK, tile_n * bn);
+      }
     }
-  } else if (warp == 1 && lane == 0) {
+  } else {
+    grid_dependency_wait();
+  }
+  if (warp == 1 && lane == 0) {
     // ---- MMA issuer ----
     for (int kb = 0; kb < nkb; ++kb) {
       const int s = kb % STAGES;
@@ -281,7 +302,8 @@ int launch(const Tcgen05Params& p, const CUtensorMap& a_map, const CUtensorMap& 
   if (p.bn <= 0 || p.bn > BN || p.bn % 16 != 0) return B200_ERR_BAD_ARGUMENT;
   dim3 grid(static_cast<unsigned>(ceil_div(p.n, p.bn)), static_cast<unsigned>(ceil_div(p.m, kBM)),
             static_cast<unsigned>(p.splits));
-  kernel<<<grid, kThreads, smem, stream>>>(p, a_map, b_map);
+  if (launch_chained(kernel, grid, dim3(kThreads), smem, stream, p, a_map, b_map) != cudaSuccess)
+    return B200_ERR_LAUNCH;
   return launch_status();
 }
 
@@ -363,6 +385,7 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
   p.epilogue = epilogue;
   p.splits = 1;
   p.bn = bn;
+  p.prefetch_weights = (launch_mode() & B200_LAUNCH_CONSTANT_WEIGHTS) != 0 ? 1 : 0;
   if (m <= 64) {
     if (bn > 128) return launch<256, 5, 64>(p, a_map, b_map, stream);
     if (bn > 64) return launch<128, 8, 64>(p, a_map, b_map, stream);
@@ -396,6 +419,7 @@ int linear_partial_tcgen05(const void* input, const void* weight, float* partial
   p.epilogue = kEpiloguePartial;
   p.splits = splits;
   p.bn = plan.bn;
+  p.prefetch_weights = (launch_mode() & B200_LAUNCH_CONSTANT_WEIGHTS) != 0 ? 1 : 0;
   if (a_rows == 64) {
     if (plan.bn == 32) return launch<32, 8, 64>(p, a_map, b_map, stream);
     if (plan.bn == 64) return launch<64, 6, 64>(p, a_map, b_map, stream);

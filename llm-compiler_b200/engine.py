@@ -16,6 +16,7 @@ partitioning across GPUs is in serving.py.
 
 from __future__ import annotations
 
+import os
 from typing import Dict, Optional
 
 import torch
@@ -56,6 +57,8 @@ class Qwen2Engine:
         self._host_ids = torch.zeros(batch, dtype=torch.int64).pin_memory()
         self._host_tokens = torch.zeros(batch, dtype=torch.int64).pin_memory()
         self.max_length_hint = 0  # host-known upper bound of the context (0 = capacity)
+        # programmatic dependent launch of the chain (B200_PROGRAMMATIC_LAUNCH=0 turns it off)
+        self.programmatic_launch = os.environ.get("B200_PROGRAMMATIC_LAUNCH", "1") != "0"
         self.split_tokens = 0
         self.kernels_per_step = 0
 
@@ -167,6 +170,12 @@ class Qwen2Engine:
         the tcgen05 kernel and the reduction rides in the next operator (bias + RoPE + KV store
         after q|k|v; residual + RMSNorm after o and down). 8 launches per layer."""
 
+        # the weights are written once, when the engine is built: constant for every step
+        with kernels.launch_mode(programmatic=self.programmatic_launch,
+                                 constant_weights=self.programmatic_launch):
+            self._chain_launches()
+
+    def _chain_launches(self) -> None:
         cfg = self.config
         batch = self.batch
         before = kernels.launch_count(self.device)

@@ -10,6 +10,7 @@ libb200serve.so, and a missing library or a CPU tensor is an error, never a fall
 
 from __future__ import annotations
 
+import contextlib
 import math
 from typing import Optional, Tuple
 
@@ -96,6 +97,27 @@ def launch_count(device: torch.device | None = None) -> int:
 
 
 # ------------------------------------------------------------------------- helpers ----
+@contextlib.contextmanager
+def launch_mode(*, programmatic: bool, constant_weights: bool = False):
+    """Scope in which the decode-chain kernels are launched with programmatic dependent launch
+    (each may become resident while its predecessor still runs and waits on the device before
+    touching a tensor). constant_weights promises that no kernel in flight writes a weight
+    tensor, which lets the tcgen05 linear fetch weight tiles before that wait. The mode is
+    process-wide in the library; launches captured into a CUDA graph keep the mode they were
+    captured with."""
+
+    flags = (_lib.LAUNCH_PROGRAMMATIC if programmatic else 0) | \
+        (_lib.LAUNCH_CONSTANT_WEIGHTS if constant_weights else 0)
+    library = _lib.load()
+    previous = library.b200_set_launch_mode(flags)
+    if previous < 0:
+        raise ValueError(f"b200_set_launch_mode: {_lib.error_string(previous)}")
+    try:
+        yield
+    finally:
+        library.b200_set_launch_mode(previous)
+
+
 def _require_cuda(*tensors: torch.Tensor) -> torch.device:
     device = None
     for tensor in tensors:

@@ -345,6 +345,40 @@ def test_decode_attention_split_invariance_full_size(decode_loads):
     kernels.runtime().check_status()
 
 
+@pytest.mark.parametrize("schedule", ["flat", "grid"])
+@pytest.mark.parametrize("shape", ["one_long", "many_short", "large_batch"])
+def test_decode_attention_schedules_on_skewed_lengths(shape, schedule, monkeypatch, decode_loads):
+    """With split_tokens == 0 the kernel runs on a fixed (split, head, batch) grid, or, with
+    B200_DECODE_ATTENTION_SCHEDULE=flat, cuts the work by chunks counted from lengths[] on the
+    device. Skewed batches make one pair span many CTAs and one CTA span many pairs; a second
+    call on the same workspace checks that the arrival counters were left at zero."""
+    monkeypatch.setenv("B200_DECODE_ATTENTION_SCHEDULE", schedule)
+    g = torch.Generator().manual_seed(len(shape))
+    hq, hkv, d = 14, 2, 64
+    if shape == "one_long":
+        b, c = 5, 6000
+        lengths = torch.tensor([6000, 0, 3, 129, 0])
+    elif shape == "many_short":
+        b, c = 40, 300
+        lengths = torch.randint(0, 301, (b,), generator=g)
+        lengths[7] = 300
+    else:
+        b, c = 300, 140  # more sequences than threads in a CTA
+        lengths = torch.randint(1, 141, (b,), generator=g)
+    q = torch.randn(b, 1, hq, d, generator=g).bfloat16().transpose(1, 2)
+    kbuf = torch.randn(b, c, hkv, d, generator=g).bfloat16()
+    vbuf = torch.randn(b, c, hkv, d, generator=g).bfloat16()
+    ref = serve_ops.decode_attention(q, kbuf, vbuf, lengths, torch.zeros(b, 1, 1, c),
+                                     groups=hq // hkv, scale=0.125)
+    args = (q.cuda(), kbuf.cuda(), vbuf.cuda(), lengths.cuda(), None)
+    for _ in range(2):
+        out = b200.b200_decode_attention(*args, scale=0.125)
+        empty = lengths == 0
+        assert torch.isnan(out[empty.cuda()]).all()
+        close(out[~empty.cuda()], ref[~empty], BF16_TOL)
+    kernels.runtime().check_status()
+
+
 # --------------------------------------------------------------- prefill attention ----
 @pytest.mark.parametrize("mode", ["fast", "pytorch_compatible"])
 @pytest.mark.parametrize("name", list(cases.PREFILL_ATTENTION))
