@@ -49,7 +49,9 @@ def _stale(target: Path, inputs: list[Path]) -> bool:
 
 
 def _compile(nvcc: str, source: Path, obj: Path) -> None:
-    command = [nvcc, *NVCC_FLAGS, "-c", str(source), "-o", str(obj)]
+    # B200_NVCC_EXTRA: extra compiler flags, e.g. -DB200_TRACE for the timeline-trace build
+    extra = os.environ.get("B200_NVCC_EXTRA", "").split()
+    command = [nvcc, *NVCC_FLAGS, *extra, "-c", str(source), "-o", str(obj)]
     result = subprocess.run(command, capture_output=True, text=True)
     if result.returncode != 0:
         raise RuntimeError(f"nvcc failed on {source.name}:\n{result.stdout}\n{result.stderr}")

@@ -32,3 +32,24 @@ extern "C" const char* b200_error_string(int code) {
     default: return "unknown error code";
   }
 }
+
+#ifdef B200_TRACE
+#include <cuda_runtime.h>
+namespace b200 {
+namespace {
+constexpr int kMaxSetters = 16;
+void (*g_setters[kMaxSetters])(unsigned long long*);
+int g_setter_count = 0;
+}  // namespace
+void register_trace_setter(void (*setter)(unsigned long long*)) {
+  if (g_setter_count < kMaxSetters) g_setters[g_setter_count++] = setter;
+}
+}  // namespace b200
+
+// buffer: device memory of (1 + 8 * 65536) + (1 + 64 * 512) 64-bit words, zeroed by the caller; NULL detaches.
+extern "C" int b200_trace_attach(void* buffer) {
+  for (int i = 0; i < b200::g_setter_count; ++i)
+    b200::g_setters[i](static_cast<unsigned long long*>(buffer));
+  return cudaDeviceSynchronize() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+}
+#endif

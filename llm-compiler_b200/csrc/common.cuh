@@ -53,6 +53,82 @@ inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 blo
   return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 
+// ---- Timeline trace (only in builds with -DB200_TRACE) -----------------------------------
+// Thread 0 of every block of a traced kernel records {kernel id, block, SM, globaltimer and
+// SM clock at the top, after the dependency wait, at the end} into a caller-provided device
+// buffer (b200_trace_attach): word 0 is the next free record, records of 8 words follow.
+#ifdef B200_TRACE
+static __constant__ unsigned long long* c_trace_buffer;
+void register_trace_setter(void (*setter)(unsigned long long*));  // api.cu
+static void set_trace_buffer_of_this_file(unsigned long long* buffer) {
+  cudaMemcpyToSymbol(c_trace_buffer, &buffer, sizeof(buffer));
+}
+namespace {
+struct TraceRegistrar {
+  TraceRegistrar() { register_trace_setter(&set_trace_buffer_of_this_file); }
+} g_trace_registrar;
+}  // namespace
+constexpr unsigned kTraceRecords = 65536;
+__device__ __forceinline__ unsigned long long trace_globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)::"memory");
+  return t;
+}
+struct TraceScope {
+  unsigned long long* record;
+  __device__ __forceinline__ TraceScope(int kernel_id) : record(nullptr) {
+    const unsigned block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    if (threadIdx.x != 0 || c_trace_buffer == nullptr) return;
+    const unsigned long long slot = atomicAdd(c_trace_buffer, 1ull) % kTraceRecords;
+    record = c_trace_buffer + 1 + slot * 8;
+    unsigned smid;
+    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+    record[0] = static_cast<unsigned long long>(kernel_id) | (static_cast<unsigned long long>(block) << 16) |
+                (static_cast<unsigned long long>(smid) << 48);
+    record[1] = trace_globaltimer();
+    record[2] = clock64();
+    record[3] = record[5] = record[7] = 0;
+  }
+  __device__ __forceinline__ void mark(int which) {  // 0: after the wait, 1: end
+    if (record == nullptr) return;
+    record[3 + 2 * which] = trace_globaltimer();
+    record[4 + 2 * which] = clock64();
+  }
+  __device__ __forceinline__ void mark_middle() {  // one more globaltimer sample
+    if (record != nullptr) record[7] = trace_globaltimer();
+  }
+};
+// Fine-grained samples from block 0 of a kernel: up to 62 SM-clock values per row of 64
+// words (word 0: kernel id, word 1: top of the kernel), rows behind the records, the row
+// counter in the word before them. Any one thread of block 0 may own a row.
+constexpr unsigned kTraceSampleRows = 512;
+struct TraceSamples {
+  unsigned long long* row;
+  __device__ __forceinline__ TraceSamples(int kernel_id, bool owner) : row(nullptr) {
+    if (!owner || c_trace_buffer == nullptr || blockIdx.x + blockIdx.y + blockIdx.z != 0) return;
+    unsigned long long* area = c_trace_buffer + 1 + 8ull * kTraceRecords;
+    const unsigned long long r = atomicAdd(area, 1ull) % kTraceSampleRows;
+    row = area + 1 + r * 64;
+    row[0] = static_cast<unsigned long long>(kernel_id) | (static_cast<unsigned long long>(gridDim.x) << 16);
+    row[1] = trace_globaltimer();
+    for (int i = 2; i < 64; ++i) row[i] = 0;
+  }
+  __device__ __forceinline__ void sample(int i) {
+    if (row != nullptr && i >= 0 && i < 62) row[2 + i] = clock64();  // cheap: SM cycles
+  }
+};
+#else
+struct TraceScope {
+  __device__ __forceinline__ TraceScope(int) {}
+  __device__ __forceinline__ void mark(int) {}
+  __device__ __forceinline__ void mark_middle() {}
+};
+struct TraceSamples {
+  __device__ __forceinline__ TraceSamples(int, bool) {}
+  __device__ __forceinline__ void sample(int) {}
+};
+#endif
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
@@ -211,6 +287,23 @@ __device__ __forceinline__ bool mbarrier_wait_bounded(uint32_t bar, uint32_t par
                                                       uint32_t limit = 4000000u) {
   for (uint32_t i = 0; i < limit; ++i)
     if (mbarrier_try_wait(bar, parity)) return true;
+  return false;
+}
+// Same bound, polling with the non-suspending test: for a wait whose latency matters more
+// than the issue slots one spinning thread takes.
+__device__ __forceinline__ bool mbarrier_spin_bounded(uint32_t bar, uint32_t parity,
+                                                      uint32_t limit = 40000000u) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred P1;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, P1;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+  }
   return false;
 }
 // One 3-D box of a tiled tensor map into shared memory; completion is signalled on `bar`.

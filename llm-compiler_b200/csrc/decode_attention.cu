@@ -416,8 +416,10 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  TraceScope trace(4);
   grid_launch_dependents();
   grid_dependency_wait();  // lengths, q and the newest KV row come from kernels before this one
+  trace.mark(0);
   int64_t len = p.lengths[b];
   if (len > p.mask_len) {
     if (threadIdx.x == 0 && split == 0 && head_block == 0 && p.status != nullptr)
@@ -442,6 +444,7 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
   int it_base = 0;
   stream_segment<D, TOK, WIDE, FAST, TMA>(p, kmap, vmap, smem, bar0, b, kvh, g0, rows, start, end,
                                           it_base);
+  trace.mark_middle();
 
   for (int idx = threadIdx.x; idx < rows * D; idx += kThreads) {
     const int row = idx / D;
@@ -473,6 +476,7 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
       }
     }
   }
+  trace.mark(1);
   if (p.num_splits == 1 || p.counters == nullptr) return;
 
   // ---- the CTA that arrives last for this (sequence, head block) combines the splits ----

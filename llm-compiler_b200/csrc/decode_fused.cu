@@ -48,8 +48,10 @@ reduce_residual_rms_norm_kernel(const float* __restrict__ partials, int splits,
                                 const __nv_bfloat16* __restrict__ weight,
                                 __nv_bfloat16* __restrict__ x_out, __nv_bfloat16* __restrict__ h_out,
                                 int rows, int hidden, float epsilon, int compat) {
+  TraceScope trace(2);
   grid_launch_dependents();
   grid_dependency_wait();
+  trace.mark(0);
   const int row = blockIdx.x;
   const int64_t slice = static_cast<int64_t>(rows) * hidden;
   const float* prow = partials + static_cast<int64_t>(row) * hidden;
@@ -68,7 +70,10 @@ reduce_residual_rms_norm_kernel(const float* __restrict__ partials, int splits,
       sum = fmaf(v, v, sum);
     }
   }
-  if (h_out == nullptr) return;
+  if (h_out == nullptr) {
+    trace.mark(1);
+    return;
+  }
   __shared__ float partial_sum[kNormThreads / 32];
   __shared__ float total;
   sum = warp_sum(sum);
@@ -91,6 +96,7 @@ reduce_residual_rms_norm_kernel(const float* __restrict__ partials, int splits,
           __float2bfloat16_rn(__fmul_rn(__bfloat162float(weight[c]), n));
     }
   }
+  trace.mark(1);
 }
 
 // One thread handles one (sequence, head, rotation pair d / d + D/2).
@@ -104,8 +110,10 @@ __global__ void reduce_rope_kv_store_kernel(const float* __restrict__ partials, 
                                             const int64_t* __restrict__ positions, int batch,
                                             int q_heads, int kv_heads, int dim, int capacity,
                                             int32_t* status) {
+  TraceScope trace(3);
   grid_launch_dependents();
   grid_dependency_wait();
+  trace.mark(0);
   const int half = dim / 2;
   const int heads = q_heads + 2 * kv_heads;
   const int width = heads * dim;  // columns of the fused q|k|v projection
@@ -151,6 +159,7 @@ __global__ void reduce_rope_kv_store_kernel(const float* __restrict__ partials, 
     dst[d] = __float2bfloat16_rn(ylo);
     dst[d + half] = __float2bfloat16_rn(yhi);
   }
+  trace.mark(1);
 }
 
 }  // namespace

@@ -44,8 +44,12 @@ struct Tcgen05Params {
   int prefetch_weights;  // W tiles may be fetched before the predecessor kernel has finished
 };
 
+// silu for the fused SwiGLU epilogue: x / (1 + 2^(-x log2 e)) on the special-function unit
+// (ex2.approx, rcp.approx: a few ulp of fp32, far below the bf16 rounding that follows). An
+// IEEE expf + division costs ~160 cycles per element on the epilogue's lone warps, which made
+// the epilogue of the gate|up projection longer than its main loop.
 __device__ __forceinline__ float silu_f32(float x) {
-  return __fdiv_rn(x, __fadd_rn(1.0f, expf(-x)));
+  return __fdividef(x, 1.0f + exp2f(-1.4426950408889634f * x));
 }
 
 // Shared-memory matrix descriptor of a K-major tile of 128-byte swizzled rows: start address,
@@ -115,6 +119,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   __shared__ uint32_t tmem_base_slot;
   __shared__ int failed;
 
+  TraceScope trace(1);
   grid_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z;
@@ -158,6 +163,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
                   tile_n * bn);
     }
     grid_dependency_wait();
+    trace.mark(0);
     for (int kb = 0; kb < nkb; ++kb) {
       const int s = kb % STAGES;
       if (kb >= STAGES &&
@@ -187,6 +193,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
         failed = 1;
         break;
       }
+
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t a_addr = smem_base + s * kStageBytes;
       const uint32_t b_addr = a_addr + kABytes;
@@ -202,6 +209,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
 
   // ---- epilogue: all four warps, warp w reads TMEM lanes 32w .. 32w+31 = output rows ----
   bool ok = mbarrier_wait_bounded(smem_u32(&accum_bar), 0);
+  trace.mark_middle();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   ok = ok && failed == 0;
   if (ok) {
@@ -288,6 +296,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   if (warp == 1)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
                  ::"r"(tmem_base), "r"(static_cast<uint32_t>(BN < 32 ? 32 : BN)) : "memory");
+  trace.mark(1);
 }
 
 template <int BN, int STAGES, int A_ROWS>
