@@ -33,24 +33,55 @@ __device__ __forceinline__ void grid_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// Thread-block cluster helpers: a barrier over all threads of the cluster (release / acquire,
+// so shared-memory writes before it are visible to the other CTAs after it) and a load from
+// the shared memory of the cluster's CTA `rank` at the offset of a local address.
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n"
+               "barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ float load_cluster_f32(uint32_t local_smem_addr, int rank) {
+  uint32_t remote;
+  float value;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(value) : "r"(remote) : "memory");
+  return value;
+}
+
 // Launches `kernel`; under B200_LAUNCH_PROGRAMMATIC with the programmatic attribute. Only for
-// kernels that execute grid_dependency_wait().
+// kernels that execute grid_dependency_wait(). cluster_x > 1 makes every cluster_x consecutive
+// CTAs along x a thread-block cluster.
 template <typename... Params, typename... Args>
-inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
-                                  cudaStream_t stream, Args&&... args) {
+inline cudaError_t launch_chained_cluster(void (*kernel)(Params...), dim3 grid, dim3 block,
+                                          size_t smem, cudaStream_t stream, unsigned cluster_x,
+                                          Args&&... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
   config.dynamicSmemBytes = smem;
   config.stream = stream;
-  cudaLaunchAttribute attribute[1];
-  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attribute[2];
+  unsigned count = 0;
   if ((launch_mode() & B200_LAUNCH_PROGRAMMATIC) != 0) {
-    config.attrs = attribute;
-    config.numAttrs = 1;
+    attribute[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
   }
+  if (cluster_x > 1) {
+    attribute[count].id = cudaLaunchAttributeClusterDimension;
+    attribute[count].val.clusterDim.x = cluster_x;
+    attribute[count].val.clusterDim.y = 1;
+    attribute[count].val.clusterDim.z = 1;
+    ++count;
+  }
+  config.attrs = count > 0 ? attribute : nullptr;
+  config.numAttrs = count;
   return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+template <typename... Params, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                  cudaStream_t stream, Args&&... args) {
+  return launch_chained_cluster(kernel, grid, block, smem, stream, 1u, static_cast<Args&&>(args)...);
 }
 
 // ---- Timeline trace (only in builds with -DB200_TRACE) -----------------------------------

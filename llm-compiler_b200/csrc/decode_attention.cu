@@ -396,11 +396,17 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
   return __syncthreads_and(!timed_out) != 0;  // the same answer in every thread of the CTA
 }
 
-template <int D, int TOK, bool WIDE, bool FAST, bool TMA>
+// CLUSTER: the splits of one (sequence, head block) form a thread-block cluster (gridDim.x ==
+// cluster size <= 8) and are combined through distributed shared memory by the cluster's
+// first CTA; otherwise through the fp32 scratch in global memory by whichever CTA arrives last.
+template <int D, int TOK, bool WIDE, bool FAST, bool TMA, bool CLUSTER>
 __global__ void __launch_bounds__(kThreads)
 decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                         const __grid_constant__ CUtensorMap vmap) {
   constexpr int kWarpBytes = kStages * 2 * TOK * D * 2;
+  constexpr int kStagingBytes = kWarpBytes / 2;  // merged partial of this CTA, in warp 0's ring
+  static_assert(kStagingBytes >= 16 * D * 4 + 128 && kWarpBytes - kStagingBytes >= 16 * D * 4 + 128,
+                "ring region too small to hold the partials");
 
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t full_bar[kWarps][kStages];
@@ -429,8 +435,8 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
   if (len < 0) len = 0;
   const int n_tokens = static_cast<int>(len);
   const int start = split * p.split_tokens;
-  if (start >= n_tokens && split > 0) return;
-  const int end = min(start + p.split_tokens, n_tokens);
+  if (!CLUSTER && start >= n_tokens && split > 0) return;  // (a cluster member must stay for the barriers)
+  const int end = max(start, min(start + p.split_tokens, n_tokens));
 
   const uint32_t bar0 = smem_u32(&full_bar[warp][0]);
   if (TMA) {
@@ -467,6 +473,13 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
     if (p.num_splits == 1) {
       p.out[(static_cast<int64_t>(b) * p.q_heads + hq) * D + col] =
           __float2bfloat16_rn(o_all / l_all);  // 0/0 = NaN for an empty sequence, as the oracle
+    } else if (CLUSTER) {
+      float* staging = reinterpret_cast<float*>(smem + kStagingBytes);
+      staging[idx] = o_all;
+      if (col == 0) {
+        staging[16 * D + row * 2] = m_all;
+        staging[16 * D + row * 2 + 1] = l_all;
+      }
     } else {
       const int64_t slot = (static_cast<int64_t>(b) * p.q_heads + hq) * p.num_splits + split;
       p.ws_o[slot * D + col] = o_all;
@@ -477,7 +490,35 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
     }
   }
   trace.mark(1);
-  if (p.num_splits == 1 || p.counters == nullptr) return;
+  if (p.num_splits == 1) return;
+  if (CLUSTER) {
+    // every CTA of the cluster has published its partial; the first one combines them in split
+    // order, the others stay until it has read them
+    cluster_sync();
+    if (split == 0) {
+      const uint32_t staging = smem_u32(smem + kStagingBytes);
+      for (int idx = threadIdx.x; idx < rows * D; idx += kThreads) {
+        const int row = idx / D;
+        const int col = idx % D;
+        float m_all = -INFINITY;
+        for (int s = 0; s < p.num_splits; ++s)
+          m_all = fmaxf(m_all, load_cluster_f32(staging + (16 * D + row * 2) * 4, s));
+        float l_all = 0.0f, o_all = 0.0f;
+        for (int s = 0; s < p.num_splits; ++s) {
+          const float m = load_cluster_f32(staging + (16 * D + row * 2) * 4, s);
+          const float wgt = m == -INFINITY ? 0.0f : fast_exp2(m - m_all);
+          l_all += load_cluster_f32(staging + (16 * D + row * 2 + 1) * 4, s) * wgt;
+          o_all += load_cluster_f32(staging + idx * 4, s) * wgt;
+        }
+        const int hq = kvh * p.groups + g0 + row;
+        p.out[(static_cast<int64_t>(b) * p.q_heads + hq) * D + col] =
+            __float2bfloat16_rn(o_all / l_all);
+      }
+    }
+    cluster_sync();
+    return;
+  }
+  if (p.counters == nullptr) return;
 
   // ---- the CTA that arrives last for this (sequence, head block) combines the splits ----
   int used = (n_tokens + p.split_tokens - 1) / p.split_tokens;
@@ -861,6 +902,13 @@ bool use_tma_loads() {
   return value == nullptr || strcmp(value, "cp.async") != 0;
 }
 
+// The splits of a pair merge through distributed shared memory when they fit one portable
+// cluster (B200_DECODE_ATTENTION_MERGE=global keeps the scratch in global memory).
+bool cluster_merge_enabled() {
+  const char* value = getenv("B200_DECODE_ATTENTION_MERGE");
+  return value == nullptr || strcmp(value, "global") != 0;
+}
+
 template <int D, bool WIDE, bool FAST, bool TMA>
 int launch_variant(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap,
                    cudaStream_t stream) {
@@ -868,10 +916,14 @@ int launch_variant(const DecodeParams& p, const CUtensorMap& kmap, const CUtenso
   constexpr int smem = kWarps * kStages * 2 * TOK * D * 2;
   const int row_blocks = (p.groups + 15) / 16;
   dim3 grid(p.num_splits, p.kv_heads * row_blocks, p.batch);
-  auto kernel = decode_attention_kernel<D, TOK, WIDE, FAST, TMA>;
+  const bool cluster = p.num_splits >= 2 && p.num_splits <= 8 && cluster_merge_enabled();
+  auto kernel = cluster ? decode_attention_kernel<D, TOK, WIDE, FAST, TMA, true>
+                        : decode_attention_kernel<D, TOK, WIDE, FAST, TMA, false>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return B200_ERR_LAUNCH;
-  if (launch_chained(kernel, dim3(grid), dim3(kThreads), smem, stream, p, kmap, vmap) != cudaSuccess)
+  if (launch_chained_cluster(kernel, grid, dim3(kThreads), smem, stream,
+                             cluster ? static_cast<unsigned>(p.num_splits) : 1u, p, kmap,
+                             vmap) != cudaSuccess)
     return B200_ERR_LAUNCH;
   return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
@@ -914,7 +966,8 @@ int launch_bf16(const DecodeParams& p, cudaStream_t stream, int flat_grid = 0) {
   }
 #undef B200_DISPATCH
   if (code != B200_OK) return code;
-  if (flat_grid == 0 && p.num_splits > 1 && p.counters == nullptr) {
+  const bool clustered = p.num_splits >= 2 && p.num_splits <= 8 && cluster_merge_enabled();
+  if (flat_grid == 0 && p.num_splits > 1 && p.counters == nullptr && !clustered) {
     decode_merge_kernel<<<p.batch * p.q_heads, D, 0, stream>>>(
         p.ws_o, p.ws_ml, p.lengths, p.out, p.q_heads, D, p.num_splits, p.split_tokens,
         p.mask_len);
@@ -1110,7 +1163,8 @@ extern "C" int b200_decode_attention(const void* query, const void* key_buffer,
     }
     return head_dim == 64 ? launch_bf16<64>(p, s, flat.grid) : launch_bf16<128>(p, s, flat.grid);
   }
-  if (splits > 1) {
+  const bool clustered = splits >= 2 && splits <= 8 && cluster_merge_enabled();
+  if (splits > 1 && !clustered) {  // (a cluster combines its splits in shared memory)
     const int64_t need = workspace_bytes_for(batch, q_heads, head_dim, splits);
     if (!workspace || workspace_bytes < need) return B200_ERR_WORKSPACE;
     if (batch * head_blocks <= kMaxCounters) p.counters = static_cast<int*>(workspace);
