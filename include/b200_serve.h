@@ -56,6 +56,7 @@ extern "C" {
 /* launch-mode flags (b200_set_launch_mode) */
 #define B200_LAUNCH_PROGRAMMATIC 1      /* decode-chain kernels use programmatic dependent launch */
 #define B200_LAUNCH_CONSTANT_WEIGHTS 2  /* weight operands are written by no kernel in flight  */
+#define B200_LAUNCH_STABLE_KV_PREFIX 4  /* lengths[] and KV rows < lengths[b] - 1 likewise       */
 
 /* Process-wide launch mode of the decode-chain kernels (embedding, rope table, rms_norm fast
  * path, linear on tcgen05, linear_partial, the two reduce_* consumers, decode attention,
@@ -65,7 +66,11 @@ extern "C" {
  * in the stream has finished and waits on the device (griddepcontrol.wait) before touching
  * any tensor; results are unchanged. B200_LAUNCH_CONSTANT_WEIGHTS additionally lets a linear
  * kernel fetch its `weight` tiles before that wait: only valid while no kernel that writes a
- * weight tensor is in flight on the device. Returns the previous flags, or
+ * weight tensor is in flight on the device. B200_LAUNCH_STABLE_KV_PREFIX lets decode attention
+ * read lengths[] and request the KV rows below lengths[b] - 1 before the wait: valid when the
+ * only KV row written since the previous synchronisation point is the newest one (row
+ * lengths[b] - 1, stored by the kernel just before attention), as in a decode step whose
+ * lengths were advanced at the end of the step before. Returns the previous flags, or
  * B200_ERR_BAD_ARGUMENT for unknown bits. Default 0. */
 int b200_set_launch_mode(int flags);
 int b200_get_launch_mode(void);

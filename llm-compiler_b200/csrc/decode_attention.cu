@@ -54,6 +54,7 @@ struct DecodeParams {
   int batch, q_heads, kv_heads, groups, capacity, mask_len, split_tokens, num_splits;
   int mask_dtype;  // B200_F32 / B200_BF16
   int compat;      // keep the reference's bf16 rounding of the scores
+  int early_kv;    // lengths[] and the KV rows below lengths[b] - 1 are stable: fetch before the wait
   float scale;
 };
 
@@ -87,7 +88,8 @@ template <int D, int TOK, bool WIDE, bool FAST, bool TMA>
 __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUtensorMap& kmap,
                                                const CUtensorMap& vmap, unsigned char* smem,
                                                uint32_t bar0, int b, int kvh, int g0, int rows,
-                                               int start, int end, int& it_base) {
+                                               int start, int end, int& it_base,
+                                               int stable_end = -1, TraceScope* trace = nullptr) {
   constexpr int kChunksPerRow = D / 8;
   constexpr int kTileBytes = TOK * D * 2;  // one of K or V, one stage
   constexpr int kStageBytes = 2 * kTileBytes;
@@ -100,28 +102,6 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int it0 = it_base;
-
-  // ---- Q fragments straight from global memory (A operand, 16 x D, rows = q heads) ----
-  uint32_t qa[kKSteps][4];
-  {
-    const int r0 = lane >> 2;
-    const int col = (lane & 3) * 2;
-    const __nv_bfloat16* qbase =
-        p.q + b * p.q_batch_stride + static_cast<int64_t>(kvh * p.groups + g0) * p.q_head_stride;
-#pragma unroll
-    for (int ks = 0; ks < kKSteps; ++ks) {
-      const int c0 = ks * 16 + col;
-      qa[ks][0] = r0 < rows ? *reinterpret_cast<const uint32_t*>(qbase + r0 * p.q_head_stride + c0) : 0u;
-      qa[ks][2] = r0 < rows ? *reinterpret_cast<const uint32_t*>(qbase + r0 * p.q_head_stride + c0 + 8) : 0u;
-      if (WIDE) {
-        qa[ks][1] = r0 + 8 < rows ? *reinterpret_cast<const uint32_t*>(qbase + (r0 + 8) * p.q_head_stride + c0) : 0u;
-        qa[ks][3] = r0 + 8 < rows ? *reinterpret_cast<const uint32_t*>(qbase + (r0 + 8) * p.q_head_stride + c0 + 8) : 0u;
-      } else {
-        qa[ks][1] = 0u;
-        qa[ks][3] = 0u;
-      }
-    }
-  }
 
   const uint32_t warp_smem = smem_u32(smem) + warp * kWarpBytes;
   const int64_t token_stride = static_cast<int64_t>(p.kv_heads) * D;
@@ -194,9 +174,50 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
   const float softmax_scale = FAST ? scale_log2 : 1.0f;
   bool timed_out = false;
 
+  // Pipeline prologue. With stable_end >= 0 (the caller vouches that lengths[] and the KV rows
+  // below stable_end are written by no kernel still running) the sub-tiles that end at or
+  // below it are requested BEFORE the dependency wait, so the ring is full when the kernel
+  // before this one finishes; the query, and any sub-tile that may hold the newest row, come
+  // after the wait.
+  uint32_t requested = 0;
+  if (TMA && stable_end > 0) {
+#pragma unroll
+    for (int s = 0; s < kStages - 1; ++s)
+      if (s < my_count && start + (s * kWarps + warp + 1) * TOK <= stable_end) {
+        issue_load(s);
+        requested |= 1u << s;
+      }
+  }
+  if (stable_end >= 0) {
+    grid_dependency_wait();
+    if (trace != nullptr) trace->mark(0);
+  }
+
+  // ---- Q fragments straight from global memory (A operand, 16 x D, rows = q heads) ----
+  uint32_t qa[kKSteps][4];
+  {
+    const int r0 = lane >> 2;
+    const int col = (lane & 3) * 2;
+    const __nv_bfloat16* qbase =
+        p.q + b * p.q_batch_stride + static_cast<int64_t>(kvh * p.groups + g0) * p.q_head_stride;
+#pragma unroll
+    for (int ks = 0; ks < kKSteps; ++ks) {
+      const int c0 = ks * 16 + col;
+      qa[ks][0] = r0 < rows ? *reinterpret_cast<const uint32_t*>(qbase + r0 * p.q_head_stride + c0) : 0u;
+      qa[ks][2] = r0 < rows ? *reinterpret_cast<const uint32_t*>(qbase + r0 * p.q_head_stride + c0 + 8) : 0u;
+      if (WIDE) {
+        qa[ks][1] = r0 + 8 < rows ? *reinterpret_cast<const uint32_t*>(qbase + (r0 + 8) * p.q_head_stride + c0) : 0u;
+        qa[ks][3] = r0 + 8 < rows ? *reinterpret_cast<const uint32_t*>(qbase + (r0 + 8) * p.q_head_stride + c0 + 8) : 0u;
+      } else {
+        qa[ks][1] = 0u;
+        qa[ks][3] = 0u;
+      }
+    }
+  }
+
 #pragma unroll
   for (int s = 0; s < kStages - 1; ++s) {
-    if (s < my_count) issue_load(s);
+    if (s < my_count && !(requested & (1u << s))) issue_load(s);
     if (!TMA) cp_async_commit();
   }
 
@@ -424,8 +445,10 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
 
   TraceScope trace(4);
   grid_launch_dependents();
-  grid_dependency_wait();  // lengths, q and the newest KV row come from kernels before this one
-  trace.mark(0);
+  if (!p.early_kv) {
+    grid_dependency_wait();  // lengths, q and the newest KV row come from kernels before this one
+    trace.mark(0);
+  }
   int64_t len = p.lengths[b];
   if (len > p.mask_len) {
     if (threadIdx.x == 0 && split == 0 && head_block == 0 && p.status != nullptr)
@@ -449,7 +472,7 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
   }
   int it_base = 0;
   stream_segment<D, TOK, WIDE, FAST, TMA>(p, kmap, vmap, smem, bar0, b, kvh, g0, rows, start, end,
-                                          it_base);
+                                          it_base, p.early_kv ? max(n_tokens - 1, 0) : -1, &trace);
   trace.mark_middle();
 
   for (int idx = threadIdx.x; idx < rows * D; idx += kThreads) {
@@ -1149,6 +1172,7 @@ extern "C" int b200_decode_attention(const void* query, const void* key_buffer,
   p.num_splits = static_cast<int>(splits);
   p.mask_dtype = mask_dtype;
   p.compat = mode == B200_MODE_PYTORCH_COMPATIBLE ? 1 : 0;
+  p.early_kv = (launch_mode() & B200_LAUNCH_STABLE_KV_PREFIX) != 0 ? 1 : 0;
   p.scale = static_cast<float>(scale);
   p.ws_o = nullptr;
   p.ws_ml = nullptr;
@@ -1262,6 +1286,7 @@ extern "C" int b200_decode_attention_static_scratch(
   p.num_splits = static_cast<int>(splits);
   p.mask_dtype = mask_dtype;
   p.compat = mode == B200_MODE_PYTORCH_COMPATIBLE ? 1 : 0;
+  p.early_kv = (launch_mode() & B200_LAUNCH_STABLE_KV_PREFIX) != 0 ? 1 : 0;
   p.scale = static_cast<float>(scale);
   p.ws_o = nullptr;
   p.ws_ml = nullptr;

@@ -170,9 +170,12 @@ class Qwen2Engine:
         the tcgen05 kernel and the reduction rides in the next operator (bias + RoPE + KV store
         after q|k|v; residual + RMSNorm after o and down). 8 launches per layer."""
 
-        # the weights are written once, when the engine is built: constant for every step
+        # The weights are written once, when the engine is built. Lengths move at the end of a
+        # step (advance_lengths, a fully serialised launch) and the only KV row a step writes
+        # before its attention is the newest one, so both promises of the launch mode hold.
         with kernels.launch_mode(programmatic=self.programmatic_launch,
-                                 constant_weights=self.programmatic_launch):
+                                 constant_weights=self.programmatic_launch,
+                                 stable_kv_prefix=self.programmatic_launch):
             self._chain_launches()
 
     def _chain_launches(self) -> None:

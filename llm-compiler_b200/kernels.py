@@ -98,16 +98,20 @@ def launch_count(device: torch.device | None = None) -> int:
 
 # ------------------------------------------------------------------------- helpers ----
 @contextlib.contextmanager
-def launch_mode(*, programmatic: bool, constant_weights: bool = False):
+def launch_mode(*, programmatic: bool, constant_weights: bool = False,
+                stable_kv_prefix: bool = False):
     """Scope in which the decode-chain kernels are launched with programmatic dependent launch
     (each may become resident while its predecessor still runs and waits on the device before
     touching a tensor). constant_weights promises that no kernel in flight writes a weight
-    tensor, which lets the tcgen05 linear fetch weight tiles before that wait. The mode is
+    tensor, which lets the tcgen05 linear fetch weight tiles before that wait; stable_kv_prefix
+    promises the same for lengths[] and every KV row below lengths[b] - 1, which lets decode
+    attention fill its pipeline before the wait. The mode is
     process-wide in the library; launches captured into a CUDA graph keep the mode they were
     captured with."""
 
     flags = (_lib.LAUNCH_PROGRAMMATIC if programmatic else 0) | \
-        (_lib.LAUNCH_CONSTANT_WEIGHTS if constant_weights else 0)
+        (_lib.LAUNCH_CONSTANT_WEIGHTS if constant_weights else 0) | \
+        (_lib.LAUNCH_STABLE_KV_PREFIX if stable_kv_prefix else 0)
     library = _lib.load()
     previous = library.b200_set_launch_mode(flags)
     if previous < 0:
