@@ -47,24 +47,48 @@ reduce_residual_rms_norm_kernel(const float* __restrict__ partials, int splits,
                                 const __nv_bfloat16* __restrict__ residual,
                                 const __nv_bfloat16* __restrict__ weight,
                                 __nv_bfloat16* __restrict__ x_out, __nv_bfloat16* __restrict__ h_out,
-                                int rows, int hidden, float epsilon, int compat) {
+                                int rows, int hidden, float epsilon, int compat,
+                                int early_weight) {
   TraceScope trace(2);
   grid_launch_dependents();
+  // the norm weight is a model parameter: when the caller says parameters are constants it is
+  // read before the dependency wait, off the critical path
+  float w[kMaxPerThread];
+  if (early_weight && h_out != nullptr) {
+#pragma unroll
+    for (int i = 0; i < kMaxPerThread; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      w[i] = c < hidden ? __bfloat162float(weight[c]) : 0.0f;
+    }
+  }
   grid_dependency_wait();
   trace.mark(0);
   const int row = blockIdx.x;
   const int64_t slice = static_cast<int64_t>(rows) * hidden;
   const float* prow = partials + static_cast<int64_t>(row) * hidden;
   float x[kMaxPerThread];
+  float r[kMaxPerThread];
   float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kMaxPerThread; ++i) {  // the residual loads fly with the partial loads
+    const int c = threadIdx.x + i * blockDim.x;
+    r[i] = residual != nullptr && c < hidden
+               ? __bfloat162float(residual[static_cast<int64_t>(row) * hidden + c]) : 0.0f;
+  }
+  if (!(early_weight && h_out != nullptr) && h_out != nullptr) {
+#pragma unroll
+    for (int i = 0; i < kMaxPerThread; ++i) {
+      const int c = threadIdx.x + i * blockDim.x;
+      w[i] = c < hidden ? __bfloat162float(weight[c]) : 0.0f;
+    }
+  }
 #pragma unroll
   for (int i = 0; i < kMaxPerThread; ++i) {
     const int c = threadIdx.x + i * blockDim.x;
     x[i] = 0.0f;
     if (c < hidden) {
       float v = round_bf16(sum_slices(prow + c, slice, splits));
-      if (residual != nullptr)
-        v = round_bf16(__fadd_rn(v, __bfloat162float(residual[static_cast<int64_t>(row) * hidden + c])));
+      if (residual != nullptr) v = round_bf16(__fadd_rn(v, r[i]));
       x[i] = v;
       x_out[static_cast<int64_t>(row) * hidden + c] = __float2bfloat16_rn(v);
       sum = fmaf(v, v, sum);
@@ -92,8 +116,7 @@ reduce_residual_rms_norm_kernel(const float* __restrict__ partials, int splits,
     const int c = threadIdx.x + i * blockDim.x;
     if (c < hidden) {
       const float n = round_bf16(__fmul_rn(x[i], inv_rms));
-      h_out[static_cast<int64_t>(row) * hidden + c] =
-          __float2bfloat16_rn(__fmul_rn(__bfloat162float(weight[c]), n));
+      h_out[static_cast<int64_t>(row) * hidden + c] = __float2bfloat16_rn(__fmul_rn(w[i], n));
     }
   }
   trace.mark(1);
@@ -125,15 +148,22 @@ __global__ void reduce_rope_kv_store_kernel(const float* __restrict__ partials, 
     const int b = idx / (half * heads);
     const int col_lo = hh * dim + d, col_hi = col_lo + half;
     const float* prow = partials + static_cast<int64_t>(b) * width;
+    // every operand is requested before the first one is used: one memory latency, not four
+    const int64_t pos = positions[b];
+    const float bias_lo = bias != nullptr ? __bfloat162float(bias[col_lo]) : 0.0f;
+    const float bias_hi = bias != nullptr ? __bfloat162float(bias[col_hi]) : 0.0f;
+    const float clo = __bfloat162float(cosine[static_cast<int64_t>(b) * dim + d]);
+    const float chi = __bfloat162float(cosine[static_cast<int64_t>(b) * dim + d + half]);
+    const float slo = __bfloat162float(sine[static_cast<int64_t>(b) * dim + d]);
+    const float shi = __bfloat162float(sine[static_cast<int64_t>(b) * dim + d + half]);
     float lo = sum_slices(prow + col_lo, slice, splits);
     float hi = sum_slices(prow + col_hi, slice, splits);
     if (bias != nullptr) {
-      lo += __bfloat162float(bias[col_lo]);
-      hi += __bfloat162float(bias[col_hi]);
+      lo += bias_lo;
+      hi += bias_hi;
     }
     lo = round_bf16(lo);  // the linear's bf16 output
     hi = round_bf16(hi);
-    const int64_t pos = positions[b];
     const bool in_range = pos >= 0 && pos < capacity;
     if (hh >= q_heads && !in_range) {
       if (status != nullptr && d == 0 && hh == q_heads)
@@ -147,10 +177,6 @@ __global__ void reduce_rope_kv_store_kernel(const float* __restrict__ partials, 
       dst[d + half] = __float2bfloat16_rn(hi);
       continue;
     }
-    const float clo = __bfloat162float(cosine[static_cast<int64_t>(b) * dim + d]);
-    const float chi = __bfloat162float(cosine[static_cast<int64_t>(b) * dim + d + half]);
-    const float slo = __bfloat162float(sine[static_cast<int64_t>(b) * dim + d]);
-    const float shi = __bfloat162float(sine[static_cast<int64_t>(b) * dim + d + half]);
     const float ylo = round_bf16(__fadd_rn(round_bf16(__fmul_rn(lo, clo)), round_bf16(__fmul_rn(-hi, slo))));
     const float yhi = round_bf16(__fadd_rn(round_bf16(__fmul_rn(hi, chi)), round_bf16(__fmul_rn(lo, shi))));
     __nv_bfloat16* dst = hh < q_heads
@@ -184,7 +210,8 @@ extern "C" int b200_reduce_residual_rms_norm(const void* partials, int64_t split
       static_cast<const __nv_bfloat16*>(residual), static_cast<const __nv_bfloat16*>(norm_weight),
       static_cast<__nv_bfloat16*>(x_out), static_cast<__nv_bfloat16*>(h_out),
       static_cast<int>(rows), static_cast<int>(hidden), static_cast<float>(epsilon),
-      mode == B200_MODE_PYTORCH_COMPATIBLE ? 1 : 0);
+      mode == B200_MODE_PYTORCH_COMPATIBLE ? 1 : 0,
+      (launch_mode() & B200_LAUNCH_CONSTANT_WEIGHTS) != 0 ? 1 : 0);
   return launched == cudaSuccess ? launch_status() : B200_ERR_LAUNCH;
 }
 
