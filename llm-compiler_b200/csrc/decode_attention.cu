@@ -926,10 +926,15 @@ bool use_tma_loads() {
 }
 
 // The splits of a pair merge through distributed shared memory when they fit one portable
-// cluster (B200_DECODE_ATTENTION_MERGE=global keeps the scratch in global memory).
-bool cluster_merge_enabled() {
+// cluster and the whole grid is resident at once (at most 2 CTAs on each of the 148 SMs):
+// that is the latency-bound regime the cluster merge is for. Larger grids measured slower as
+// clusters (batch 256 x 4096: 86 vs 60 us), because a cluster member whose split is empty
+// has to stay for the barriers instead of leaving its slot to the next CTA.
+// B200_DECODE_ATTENTION_MERGE=global always keeps the scratch in global memory.
+bool cluster_merge(int64_t splits, int64_t batch, int64_t head_blocks) {
   const char* value = getenv("B200_DECODE_ATTENTION_MERGE");
-  return value == nullptr || strcmp(value, "global") != 0;
+  if (value != nullptr && strcmp(value, "global") == 0) return false;
+  return splits >= 2 && splits <= 8 && splits * batch * head_blocks <= 2 * kNumSMs;
 }
 
 template <int D, bool WIDE, bool FAST, bool TMA>
@@ -939,7 +944,7 @@ int launch_variant(const DecodeParams& p, const CUtensorMap& kmap, const CUtenso
   constexpr int smem = kWarps * kStages * 2 * TOK * D * 2;
   const int row_blocks = (p.groups + 15) / 16;
   dim3 grid(p.num_splits, p.kv_heads * row_blocks, p.batch);
-  const bool cluster = p.num_splits >= 2 && p.num_splits <= 8 && cluster_merge_enabled();
+  const bool cluster = cluster_merge(p.num_splits, p.batch, p.kv_heads * row_blocks);
   auto kernel = cluster ? decode_attention_kernel<D, TOK, WIDE, FAST, TMA, true>
                         : decode_attention_kernel<D, TOK, WIDE, FAST, TMA, false>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
@@ -989,7 +994,7 @@ int launch_bf16(const DecodeParams& p, cudaStream_t stream, int flat_grid = 0) {
   }
 #undef B200_DISPATCH
   if (code != B200_OK) return code;
-  const bool clustered = p.num_splits >= 2 && p.num_splits <= 8 && cluster_merge_enabled();
+  const bool clustered = cluster_merge(p.num_splits, p.batch, p.kv_heads * ((p.groups + 15) / 16));
   if (flat_grid == 0 && p.num_splits > 1 && p.counters == nullptr && !clustered) {
     decode_merge_kernel<<<p.batch * p.q_heads, D, 0, stream>>>(
         p.ws_o, p.ws_ml, p.lengths, p.out, p.q_heads, D, p.num_splits, p.split_tokens,
@@ -1187,7 +1192,7 @@ extern "C" int b200_decode_attention(const void* query, const void* key_buffer,
     }
     return head_dim == 64 ? launch_bf16<64>(p, s, flat.grid) : launch_bf16<128>(p, s, flat.grid);
   }
-  const bool clustered = splits >= 2 && splits <= 8 && cluster_merge_enabled();
+  const bool clustered = cluster_merge(splits, batch, head_blocks);
   if (splits > 1 && !clustered) {  // (a cluster combines its splits in shared memory)
     const int64_t need = workspace_bytes_for(batch, q_heads, head_dim, splits);
     if (!workspace || workspace_bytes < need) return B200_ERR_WORKSPACE;

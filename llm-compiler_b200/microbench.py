@@ -5,6 +5,7 @@
     python llm-compiler_b200/microbench.py prefill_attention --batch 4 --tokens 4096
     python llm-compiler_b200/microbench.py linear --m 64 --k 896 --n 9728 --epilogue swiglu
     python llm-compiler_b200/microbench.py kv_store --batch 16 --tokens 4096
+    python llm-compiler_b200/microbench.py timeline --batch 64 --length 4096   (trace build only)
 
 Timing: CUDA events on the launching stream around `--iters` launches after `--warmup`
 launches, rotating over enough independent buffer sets that one round exceeds the 126 MB L2
@@ -185,10 +186,88 @@ def rms_norm_case(args):
             "us": seconds * 1e6, "gbs": rows * hidden * 4 / seconds / 1e9}
 
 
+def timeline_case(args):
+    """Per-launch device timeline of one replayed decode step (Qwen2-0.5B architecture, random
+    weights, synthetic KV of --length tokens). Needs the library built with
+    B200_NVCC_EXTRA=-DB200_TRACE: thread 0 of every CTA of the chain kernels then records
+    %globaltimer at its top, after its dependency wait, once in the middle and at its end.
+    Printed per launch, in microseconds from the first record: when its CTAs became resident
+    (top), when the dependency wait returned (wait), the middle mark (GEMM: accumulator
+    complete; attention: streaming done) and the end marks."""
+
+    import ctypes
+    import statistics
+
+    from llm_compiler_b200 import _lib
+    from llm_compiler_b200 import qwen2 as q2
+    from llm_compiler_b200.engine import Qwen2Engine
+
+    library = _lib.load()
+    if not hasattr(library, "b200_trace_attach"):
+        raise SystemExit("this libb200serve.so was built without -DB200_TRACE "
+                         "(B200_NVCC_EXTRA=-DB200_TRACE python llm-compiler_b200/build.py --force)")
+    library.b200_trace_attach.argtypes = [ctypes.c_void_p]
+    device = torch.device("cuda", torch.cuda.current_device())
+    config = q2.QWEN2_0_5B
+    weights = q2.make_weights(config, seed=0, dtype=torch.bfloat16, device=device,
+                              reproducible=False)
+    engine = Qwen2Engine(config, weights, batch=args.batch, capacity=args.length + 128)
+    engine.max_length_hint = args.length + 128
+    generator = torch.Generator(device=device).manual_seed(0)
+    for layer in range(config.num_layers):
+        engine.state.keys[layer].normal_(generator=generator)
+        engine.state.values[layer].normal_(generator=generator)
+    engine.load_context(torch.full((args.batch,), args.length),
+                        next_ids=torch.randint(0, config.vocab_size, (args.batch,)))
+    engine.capture()
+    for _ in range(5):
+        engine.decode_step()
+    torch.cuda.synchronize()
+    records = 65536
+    buffer = torch.zeros(1 + 8 * records + 1 + 64 * 512, dtype=torch.int64, device=device)
+    library.b200_trace_attach(buffer.data_ptr())
+    engine.decode_step()
+    torch.cuda.synchronize()
+    library.b200_trace_attach(None)
+    host = buffer.cpu()
+    count = min(int(host[0]), records)
+    names = {1: "linear_tcgen05", 2: "reduce_residual_rms_norm", 3: "reduce_rope_kv_store",
+             4: "decode_attention"}
+    rows = []
+    for r in host[1:1 + 8 * count].view(count, 8).tolist():
+        rows.append({"kernel": names.get(r[0] & 0xffff, str(r[0] & 0xffff)), "top": r[1],
+                     "wait": r[3], "end": r[5], "middle": r[7]})
+    rows.sort(key=lambda r: r["wait"] or r["top"])
+    origin = min(r["top"] for r in rows)
+    launches = []
+    for r in rows:
+        if launches and launches[-1][0]["kernel"] == r["kernel"] and \
+                r["wait"] - launches[-1][0]["wait"] < 1500:
+            launches[-1].append(r)
+        else:
+            launches.append([r])
+
+    def us(values):
+        values = [(v - origin) / 1000.0 for v in values if v]
+        return (min(values), statistics.median(values), max(values)) if values else (0, 0, 0)
+
+    print(f"{len(rows)} CTA records, {len(launches)} launches; microseconds from the first record")
+    print(f"{'kernel':26s} {'ctas':>4s} {'top max':>8s} {'wait':>8s} {'mid min':>8s} {'mid max':>8s} "
+          f"{'end min':>8s} {'end med':>8s} {'end max':>8s} {'wait->end':>9s}")
+    for launch in launches[:args.launches]:
+        top, wait = us([r["top"] for r in launch]), us([r["wait"] for r in launch])
+        middle, end = us([r["middle"] for r in launch]), us([r["end"] for r in launch])
+        print(f"{launch[0]['kernel']:26s} {len(launch):4d} {top[2]:8.2f} {wait[2]:8.2f} {middle[0]:8.2f} "
+              f"{middle[2]:8.2f} {end[0]:8.2f} {end[1]:8.2f} {end[2]:8.2f} {end[2] - wait[2]:9.2f}")
+    return {"op": "timeline", "batch": args.batch, "context": args.length, "launches": len(launches),
+            "records": len(rows)}
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("op", choices=["decode_attention", "prefill_attention", "kv_store", "linear",
-                                       "rms_norm"])
+                                       "rms_norm", "timeline"])
+    parser.add_argument("--launches", type=int, default=40, help="timeline: launches to print")
     parser.add_argument("--batch", type=int, default=64)
     parser.add_argument("--length", type=int, default=4096)
     parser.add_argument("--tokens", type=int, default=512)
@@ -224,6 +303,8 @@ def main():
         print(json.dumps(kv_store_case(args)))
     elif args.op == "linear":
         print(json.dumps(linear_case(args)))
+    elif args.op == "timeline":
+        print(json.dumps(timeline_case(args)))
     else:
         print(json.dumps(rms_norm_case(args)))
     kernels.runtime().check_status()
