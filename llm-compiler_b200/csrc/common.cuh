@@ -338,7 +338,7 @@ __device__ __forceinline__ bool mbarrier_spin_bounded(uint32_t bar, uint32_t par
   return false;
 }
 // One 3-D box of a tiled tensor map into shared memory; completion is signalled on `bar`.
-// No cluster multicast anywhere: every CTA fetches its own tiles.
+// Every CTA fetches its own tiles: no load is shared between the CTAs of a cluster.
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tensor_map, uint32_t bar,
                                             int c0, int c1, int c2) {
   asm volatile(

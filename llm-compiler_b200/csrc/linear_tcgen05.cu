@@ -1,23 +1,30 @@
-// serve.linear for prefill-size M on the 5th-generation tensor cores: tcgen05.mma with the
-// accumulator in tensor memory (TMEM), operands staged in shared memory by TMA.
+// serve.linear on the 5th-generation tensor cores: tcgen05.mma with the accumulator in tensor
+// memory (TMEM), operands staged in shared memory by TMA.
 //
-// y[M,N] = x[M,K] W[N,K]^T, both operands K-major bf16. One CTA computes a 128 x BN tile
-// (BN = 256 or 128 accumulator columns of TMEM, fp32). Roles inside the CTA of 4 warps:
-//   warp 0, one elected lane  TMA producer: per k-block one 128 x 64 box of x and one BN x 64
+// y[M,N] = x[M,K] W[N,K]^T, both operands K-major bf16. One CTA computes a 128 x bn tile over
+// one K slice (bn: a runtime multiple of 16 up to the template's BN accumulator columns of
+// TMEM, fp32). Roles inside the CTA of 4 warps:
+//   warp 0, one elected lane  TMA producer: per k-block one A_ROWS x 64 box of x and one bn x 64
 //                             box of W (128-byte swizzled rows) into a ring of stages,
-//                             completion on the stage's `full` mbarrier;
-//   warp 1, one elected lane  MMA issuer: per stage four tcgen05.mma (M 128, N BN, K 16) whose
+//                             completion on the stage's `full` mbarrier. W does not depend on
+//                             the kernel before this one: when the caller says weights are
+//                             constants, the first ring of W boxes is requested BEFORE the
+//                             dependency wait (their bytes are announced on the barrier without
+//                             arriving), the x boxes after it;
+//   warp 1, one elected lane  MMA issuer: per stage four tcgen05.mma (M 128, N bn, K 16) whose
 //                             shared-memory descriptors walk the 64-wide swizzled tile in 32-byte
 //                             steps; tcgen05.commit arrives on the stage's `empty` mbarrier when
 //                             the tensor core is done reading it, and on `accum` after the last
 //                             k-block;
 //   all 4 warps               epilogue: tcgen05.ld of the warp's 32 TMEM lanes (= 32 output
-//                             rows) x 32 columns at a time, bias / residual / SwiGLU with the
-//                             reference's bf16 rounding points, 64-byte row segments to HBM.
+//                             rows) x 32 columns at a time; bias / residual / SwiGLU with the
+//                             reference's bf16 rounding points, or fp32 split-K partials.
+// Decode-size M (A_ROWS 64): the x box has 64 rows and the MMA, which always spans 128, reads on
+// into the W tile behind it; accumulator lanes 64..127 then hold junk that nobody reads.
 // Every mbarrier wait is bounded; a wait that gives up sets B200_STATUS_WAIT_TIMEOUT, the CTA
-// still frees its TMEM columns and returns. No cluster launch, no multicast: each CTA fetches
-// its own tiles; the second CTA resident on an SM overlaps its main loop with this one's
-// epilogue (BN 128: 2 x 96 KB of stages, 2 x 128 TMEM columns).
+// still frees its TMEM columns and returns. No cluster launch, no load shared between CTAs:
+// each CTA fetches its own tiles; with BN 128 at prefill sizes a second CTA resident on the SM
+// overlaps its main loop with this one's epilogue (2 x 96 KB of stages, 2 x 128 TMEM columns).
 #include <stdlib.h>
 #include <string.h>
 

@@ -8,6 +8,12 @@ op (backends/triton_executor.py:69-130): per decode layer
              -> decode_attention -> linear(o) + residual (epilogue)
     rms_norm -> linear(gate|up interleaved) + SwiGLU (epilogue) -> linear(down) + residual
 
+and, for bf16 in the fast numerical mode at decode batch sizes, the chain form of the same
+sequence: the small projections leave fp32 split-K partials and the next operator reduces
+them on load (bias + rope + kv.store after q|k|v; residual + rms_norm after o and down),
+8 launches per layer, launched with programmatic dependent launch so that each kernel's
+set-up and weight loads overlap its predecessor.
+
 Every rounding point of the reference graph is kept (each linear result is rounded to the
 model dtype before its bias-free residual add, SwiGLU rounds silu(gate) then the product),
 so the fusions change launch counts, not numerics. One replica lives on one GPU; batch
