@@ -45,6 +45,7 @@ CONTEXT = 4096
 METRIC = "qwen2_0.5b_bf16_decode_tokens_per_s"
 UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
+RESULT_STREAM = sys.stdout  # main() replaces it with a private copy of the process's stdout
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch over 64 x 4096 =
 # 262144 tokens, from the ncu capture summarised in profiles/decode_attention_b64_l4096_ncu_full.md;
 # scaled to the bench launch by the tokens it processes (traffic is proportional to the tokens read)
@@ -191,7 +192,7 @@ def reference_arm(args, config):
                          "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-    }))
+    }), file=RESULT_STREAM, flush=True)
 
 
 # ------------------------------------------------------------------------ B200 arm ----
@@ -397,13 +398,19 @@ def b200_arm(args, config):
             "sample": f"{args.cpu_sample_batch} of the {args.batch} sequences, all "
                       f"{config.num_layers} layers, context {args.context}, median of 3 steps "
                       f"after 1 warm-up ({step_s:.2f} s/step)"}
-    print(json.dumps(result))
+    print(json.dumps(result), file=RESULT_STREAM, flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
 def main():
     args = parse_args()
+    # The JSON line must be the only thing on stdout, but libraries write there too (NCCL prints
+    # its version banner): keep the real stdout for the result and point fd 1 at stderr.
+    global RESULT_STREAM
+    sys.stdout.flush()
+    RESULT_STREAM = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     from llm_compiler_b200 import qwen2 as q2
 
     config = q2.QWEN2_0_5B
