@@ -253,6 +253,24 @@ int b200_reduce_rope_kv_store(const void* partials, int64_t splits, const void* 
                               int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
                               int64_t capacity, int32_t* status, void* stream);
 
+/* b200_reduce_rope_kv_store followed by b200_decode_attention in ONE launch, for the decode
+ * step: the op sequence (q|k|v projection result + bias) -> serve.rope -> serve.kv.length ->
+ * serve.kv.store -> serve.decode_attention of one decoder layer (passes/kv_bufferize.py:175-200
+ * orders them so; oracle execution.py:741-767, 1242-1280, 286-333). The new token sits at row
+ * lengths[b] - 1: lengths[] are the attention lengths, already counting it. Every CTA reduces
+ * the query rows it needs from the partials; the CTA whose KV range holds row lengths[b] - 1
+ * also reduces that token's K and V, stores them into the buffers and lets them join the
+ * softmax from registers, so no CTA reads a row another one is writing. No mask (causal
+ * decode), fast numerical mode, bf16, head_dim 64 or 128. cosine / sine: B x D. Workspace as
+ * for b200_decode_attention. lengths[b] < 1 sets B200_STATUS_BAD_POSITION (nothing stored). */
+int b200_qkv_decode_attention(const void* qkv_partials, int64_t qkv_splits, const void* qkv_bias,
+                              const void* cosine, const void* sine, void* key_buffer,
+                              void* value_buffer, const int64_t* lengths, void* output,
+                              int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                              int64_t capacity, int64_t mask_len, double scale,
+                              int64_t split_tokens, int64_t max_length_hint, void* workspace,
+                              int64_t workspace_bytes, int32_t* status, void* stream);
+
 /* ---- Ops the reference leaves to PyTorch eager (execution.py:500-528) ---------- */
 /* aten.embedding.default: out[r,:] = table[ids[r],:]. */
 int b200_embedding(const void* table, const int64_t* ids, void* output, int64_t rows,

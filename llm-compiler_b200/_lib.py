@@ -7,11 +7,13 @@ shared object is missing and nothing falls back to PyTorch, Triton or the CPU.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, c_char_p, c_double, c_int, c_int32, c_int64, c_void_p
 from pathlib import Path
 
 PACKAGE_DIR = Path(__file__).resolve().parent
-LIBRARY_PATH = PACKAGE_DIR / "libb200serve.so"
+# B200_LIBRARY_PATH: another build of the same library (for instance the -DB200_TRACE one)
+LIBRARY_PATH = Path(os.environ.get("B200_LIBRARY_PATH", PACKAGE_DIR / "libb200serve.so"))
 
 F32, BF16 = 0, 1
 MODE_FAST, MODE_PYTORCH_COMPATIBLE = 0, 1
@@ -73,6 +75,9 @@ SIGNATURES = {
                                               c_void_p, c_int64, c_int64, c_double, c_int, c_void_p]),
     "b200_reduce_rope_kv_store": (c_int, [c_void_p, c_int64] + [c_void_p] * 7 + [c_int64] * 5 +
                                   [c_void_p, c_void_p]),
+    "b200_qkv_decode_attention": (c_int, [c_void_p, c_int64] + [c_void_p] * 7 +
+                                  [c_int64] * 6 + [c_double, c_int64, c_int64, c_void_p, c_int64,
+                                                   c_void_p, c_void_p]),
     "b200_embedding": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
                                c_void_p, c_void_p]),
     "b200_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),

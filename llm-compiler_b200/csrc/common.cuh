@@ -15,6 +15,30 @@ inline int launch_status() {
   return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
 
+// Sum over the K slices of one element, slice order fixed; eight loads in flight per round
+// so that the latency of a round is paid once per eight slices.
+__device__ __forceinline__ float sum_slices(const float* first, int64_t slice, int splits) {
+  float acc = 0.0f;
+  int s = 0;
+  for (; s + 8 <= splits; s += 8) {
+    float t[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t[j] = __ldcg(first + (s + j) * slice);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += t[j];
+  }
+  if (s + 4 <= splits) {
+    float t[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) t[j] = __ldcg(first + (s + j) * slice);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc += t[j];
+    s += 4;
+  }
+  for (; s < splits; ++s) acc += __ldcg(first + s * slice);
+  return acc;
+}
+
 // ---- Programmatic dependent launch -------------------------------------------------------
 // With B200_LAUNCH_PROGRAMMATIC set (b200_set_launch_mode) the kernels of the decode chain are
 // launched with programmatic stream serialisation: a kernel may become resident while its

@@ -56,6 +56,22 @@ struct DecodeParams {
   int compat;      // keep the reference's bf16 rounding of the scores
   int early_kv;    // lengths[] and the KV rows below lengths[b] - 1 are stable: fetch before the wait
   float scale;
+  // Fused form (qkv_partials != nullptr): q, and the K/V row of the newest token, are not read
+  // from memory but reduced here from the fp32 split-K partials [qkv_splits, B, (Hq + 2 Hkv) D]
+  // of the fused q|k|v projection (+ bias, RoPE); the newest row (index lengths[b] - 1) is
+  // stored into the KV buffers by the CTA that owns it and joins the softmax from registers.
+  const float* qkv_partials = nullptr;
+  const __nv_bfloat16* qkv_bias = nullptr;
+  const __nv_bfloat16* cosine = nullptr;  // [B, D]
+  const __nv_bfloat16* sine = nullptr;
+  __nv_bfloat16* kstore = nullptr;  // the KV buffers again, writable
+  __nv_bfloat16* vstore = nullptr;
+  int qkv_splits = 0;
+};
+
+// No-op hook of stream_segment.
+struct NoPrepare {
+  __device__ __forceinline__ void operator()() const {}
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -84,12 +100,17 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
 // continue from `it_base`, which is per warp and advanced here), and leave their partial
 // (max in the log2 domain, sum, O) in their ring regions; ends with a CTA barrier. Returns
 // false when a bounded wait gave up.
-template <int D, int TOK, bool WIDE, bool FAST, bool TMA>
+// `prepare` runs (all threads, may synchronise the CTA) after the dependency wait and before the
+// query fragments are read from `qbase` (row stride `q_row_stride` elements; global or shared).
+template <int D, int TOK, bool WIDE, bool FAST, bool TMA, typename Prepare = NoPrepare>
 __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUtensorMap& kmap,
                                                const CUtensorMap& vmap, unsigned char* smem,
                                                uint32_t bar0, int b, int kvh, int g0, int rows,
                                                int start, int end, int& it_base,
-                                               int stable_end = -1, TraceScope* trace = nullptr) {
+                                               int stable_end = -1, TraceScope* trace = nullptr,
+                                               const __nv_bfloat16* qbase = nullptr,
+                                               int64_t q_row_stride = 0,
+                                               Prepare prepare = Prepare()) {
   constexpr int kChunksPerRow = D / 8;
   constexpr int kTileBytes = TOK * D * 2;  // one of K or V, one stage
   constexpr int kStageBytes = 2 * kTileBytes;
@@ -198,16 +219,19 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
   {
     const int r0 = lane >> 2;
     const int col = (lane & 3) * 2;
-    const __nv_bfloat16* qbase =
-        p.q + b * p.q_batch_stride + static_cast<int64_t>(kvh * p.groups + g0) * p.q_head_stride;
+    prepare();
+    if (qbase == nullptr) {
+      qbase = p.q + b * p.q_batch_stride + static_cast<int64_t>(kvh * p.groups + g0) * p.q_head_stride;
+      q_row_stride = p.q_head_stride;
+    }
 #pragma unroll
     for (int ks = 0; ks < kKSteps; ++ks) {
       const int c0 = ks * 16 + col;
-      qa[ks][0] = r0 < rows ? *reinterpret_cast<const uint32_t*>(qbase + r0 * p.q_head_stride + c0) : 0u;
-      qa[ks][2] = r0 < rows ? *reinterpret_cast<const uint32_t*>(qbase + r0 * p.q_head_stride + c0 + 8) : 0u;
+      qa[ks][0] = r0 < rows ? *reinterpret_cast<const uint32_t*>(qbase + r0 * q_row_stride + c0) : 0u;
+      qa[ks][2] = r0 < rows ? *reinterpret_cast<const uint32_t*>(qbase + r0 * q_row_stride + c0 + 8) : 0u;
       if (WIDE) {
-        qa[ks][1] = r0 + 8 < rows ? *reinterpret_cast<const uint32_t*>(qbase + (r0 + 8) * p.q_head_stride + c0) : 0u;
-        qa[ks][3] = r0 + 8 < rows ? *reinterpret_cast<const uint32_t*>(qbase + (r0 + 8) * p.q_head_stride + c0 + 8) : 0u;
+        qa[ks][1] = r0 + 8 < rows ? *reinterpret_cast<const uint32_t*>(qbase + (r0 + 8) * q_row_stride + c0) : 0u;
+        qa[ks][3] = r0 + 8 < rows ? *reinterpret_cast<const uint32_t*>(qbase + (r0 + 8) * q_row_stride + c0 + 8) : 0u;
       } else {
         qa[ks][1] = 0u;
         qa[ks][3] = 0u;
@@ -432,6 +456,10 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t full_bar[kWarps][kStages];
   __shared__ int merge_flag;
+  // fused form only: the rotated query rows of this head block, the newest token's K and V row
+  // (bf16 values held as floats) and its scores against the query rows (log2 domain)
+  __shared__ __align__(16) __nv_bfloat16 q_stage[16 * D];
+  __shared__ float new_k[D], new_v[D], new_score[16];
 
   const int split = blockIdx.x;
   const int head_block = blockIdx.y;  // kv head * blocks-per-kv-head + 16-row block
@@ -459,7 +487,75 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
   const int n_tokens = static_cast<int>(len);
   const int start = split * p.split_tokens;
   if (!CLUSTER && start >= n_tokens && split > 0) return;  // (a cluster member must stay for the barriers)
-  const int end = max(start, min(start + p.split_tokens, n_tokens));
+  const bool fused = p.qkv_partials != nullptr;
+  // fused: the newest row is not streamed from the buffer (its owner is writing it right now)
+  const int streamed = fused ? max(n_tokens - 1, 0) : n_tokens;
+  const int end = max(start, min(start + p.split_tokens, streamed));
+  const bool owner = fused && n_tokens >= 1 && p.lengths[b] <= p.mask_len &&
+                     n_tokens - 1 >= start && n_tokens - 1 < start + p.split_tokens;
+  if (fused && n_tokens < 1 && threadIdx.x == 0 && split == 0 && head_block == 0 && p.status != nullptr)
+    atomicOr(p.status, B200_STATUS_BAD_POSITION);  // no row for the new token
+
+  // Reduces the q|k|v partials of this CTA's rows (sum over K slices in order, + bias, rounded to
+  // bf16 like the projection's own output), rotates q and k, leaves q in q_stage; the owner of
+  // the newest token also stores its K / V row (first head block only) and keeps it in new_k/v.
+  auto prepare_fused = [&]() {
+    const int half = D / 2;
+    const int width = (p.q_heads + 2 * p.kv_heads) * D;
+    const int64_t slice = static_cast<int64_t>(p.batch) * width;
+    const float* prow = p.qkv_partials + static_cast<int64_t>(b) * width;
+    const __nv_bfloat16* cos_row = p.cosine + static_cast<int64_t>(b) * D;
+    const __nv_bfloat16* sin_row = p.sine + static_cast<int64_t>(b) * D;
+    const int q_items = rows * half;
+    const int items = q_items + (owner ? 2 * half : 0);
+    for (int item = threadIdx.x; item < items; item += kThreads) {
+      int column, d;
+      bool rotate = true;
+      if (item < q_items) {
+        d = item % half;
+        column = (kvh * p.groups + g0 + item / half) * D;
+      } else if (item < q_items + half) {
+        d = item - q_items;
+        column = (p.q_heads + kvh) * D;
+      } else {
+        d = item - q_items - half;
+        column = (p.q_heads + p.kv_heads + kvh) * D;
+        rotate = false;
+      }
+      const float clo = __bfloat162float(cos_row[d]), chi = __bfloat162float(cos_row[d + half]);
+      const float slo = __bfloat162float(sin_row[d]), shi = __bfloat162float(sin_row[d + half]);
+      const float bias_lo = p.qkv_bias != nullptr ? __bfloat162float(p.qkv_bias[column + d]) : 0.0f;
+      const float bias_hi = p.qkv_bias != nullptr ? __bfloat162float(p.qkv_bias[column + d + half]) : 0.0f;
+      float lo = sum_slices(prow + column + d, slice, p.qkv_splits);
+      float hi = sum_slices(prow + column + d + half, slice, p.qkv_splits);
+      if (p.qkv_bias != nullptr) {
+        lo += bias_lo;
+        hi += bias_hi;
+      }
+      lo = round_bf16(lo);
+      hi = round_bf16(hi);
+      float ylo = lo, yhi = hi;
+      if (rotate) {
+        ylo = round_bf16(__fadd_rn(round_bf16(__fmul_rn(lo, clo)), round_bf16(__fmul_rn(-hi, slo))));
+        yhi = round_bf16(__fadd_rn(round_bf16(__fmul_rn(hi, chi)), round_bf16(__fmul_rn(lo, shi))));
+      }
+      if (item < q_items) {
+        q_stage[(item / half) * D + d] = __float2bfloat16_rn(ylo);
+        q_stage[(item / half) * D + d + half] = __float2bfloat16_rn(yhi);
+      } else {
+        float* keep = rotate ? new_k : new_v;
+        keep[d] = ylo;
+        keep[d + half] = yhi;
+        if (g0 == 0) {
+          __nv_bfloat16* dst = (rotate ? p.kstore : p.vstore) +
+              ((static_cast<int64_t>(b) * p.capacity + (n_tokens - 1)) * p.kv_heads + kvh) * D;
+          dst[d] = __float2bfloat16_rn(ylo);
+          dst[d + half] = __float2bfloat16_rn(yhi);
+        }
+      }
+    }
+    __syncthreads();
+  };
 
   const uint32_t bar0 = smem_u32(&full_bar[warp][0]);
   if (TMA) {
@@ -471,9 +567,26 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
     __syncwarp();
   }
   int it_base = 0;
-  stream_segment<D, TOK, WIDE, FAST, TMA>(p, kmap, vmap, smem, bar0, b, kvh, g0, rows, start, end,
-                                          it_base, p.early_kv ? max(n_tokens - 1, 0) : -1, &trace);
+  const int stable_end = p.early_kv ? max(n_tokens - 1, 0) : -1;
+  if (fused)
+    stream_segment<D, TOK, WIDE, FAST, TMA>(p, kmap, vmap, smem, bar0, b, kvh, g0, rows, start, end,
+                                            it_base, stable_end, &trace, q_stage,
+                                            static_cast<int64_t>(D), prepare_fused);
+  else
+    stream_segment<D, TOK, WIDE, FAST, TMA>(p, kmap, vmap, smem, bar0, b, kvh, g0, rows, start, end,
+                                            it_base, stable_end, &trace);
   trace.mark_middle();
+  if (owner) {
+    // the newest token as one more partial: max = its score (log2 domain), sum = 1, O = its V row
+    for (int row = warp; row < rows; row += kWarps) {
+      float dot = 0.0f;
+      for (int c = lane; c < D; c += 32) dot = fmaf(__bfloat162float(q_stage[row * D + c]), new_k[c], dot);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      if (lane == 0) new_score[row] = dot * p.scale * kLog2e;
+    }
+    __syncthreads();
+  }
 
   for (int idx = threadIdx.x; idx < rows * D; idx += kThreads) {
     const int row = idx / D;
@@ -484,6 +597,7 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
       mw[w] = reinterpret_cast<const float*>(smem + w * kWarpBytes)[16 * D + row * 2];
       m_all = fmaxf(m_all, mw[w]);
     }
+    if (owner) m_all = fmaxf(m_all, new_score[row]);
     float l_all = 0.0f, o_all = 0.0f;
 #pragma unroll
     for (int w = 0; w < kWarps; ++w) {
@@ -491,6 +605,11 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
       const float wgt = mw[w] == -INFINITY ? 0.0f : fast_exp2(mw[w] - m_all);
       l_all += wo[16 * D + row * 2 + 1] * wgt;
       o_all += wo[row * D + col] * wgt;
+    }
+    if (owner) {
+      const float wgt = fast_exp2(new_score[row] - m_all);
+      l_all += wgt;
+      o_all += new_v[col] * wgt;
     }
     const int hq = kvh * p.groups + g0 + row;
     if (p.num_splits == 1) {
@@ -1303,6 +1422,75 @@ extern "C" int b200_decode_attention_static_scratch(
     if (cudaMemsetAsync(scratch, 0, kCounterBytes, s) != cudaSuccess) return B200_ERR_LAUNCH;
     p.counters = static_cast<int*>(scratch);
     p.ws_o = reinterpret_cast<float*>(static_cast<char*>(scratch) + kCounterBytes);
+    p.ws_ml = p.ws_o + batch * q_heads * splits * head_dim;
+  }
+  return head_dim == 64 ? launch_bf16<64>(p, s) : launch_bf16<128>(p, s);
+}
+
+// ---- Fused q|k|v reduction + RoPE + KV store + decode attention ---------------------------
+extern "C" int b200_qkv_decode_attention(
+    const void* qkv_partials, int64_t qkv_splits, const void* qkv_bias, const void* cosine,
+    const void* sine, void* key_buffer, void* value_buffer, const int64_t* lengths, void* output,
+    int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim, int64_t capacity,
+    int64_t mask_len, double scale, int64_t split_tokens, int64_t max_length_hint, void* workspace,
+    int64_t workspace_bytes, int32_t* status, void* stream) {
+  if (!qkv_partials || !cosine || !sine || !key_buffer || !value_buffer || !lengths || !output ||
+      qkv_splits <= 0 || batch < 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 ||
+      capacity <= 0 || mask_len <= 0 || mask_len > capacity || q_heads % kv_heads != 0 ||
+      !(scale > 0.0))
+    return B200_ERR_BAD_ARGUMENT;
+  if (head_dim != 64 && head_dim != 128) return B200_ERR_UNSUPPORTED;
+  if (batch == 0) return B200_OK;
+  if (batch > 65535) return B200_ERR_TOO_LARGE;
+  if (!aligned16(key_buffer) || !aligned16(value_buffer) || !aligned16(qkv_partials))
+    return B200_ERR_ALIGNMENT;
+  if (capacity > INT32_MAX / 2 || batch * capacity > INT32_MAX) return B200_ERR_TOO_LARGE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int groups = static_cast<int>(q_heads / kv_heads);
+  int64_t max_length = max_length_hint > 0 && max_length_hint < mask_len ? max_length_hint : mask_len;
+  const int64_t head_blocks = kv_heads * ceil_div(groups, 16);
+  if (split_tokens <= 0) split_tokens = default_split_tokens(batch, head_blocks, max_length);
+  split_tokens = round_up(split_tokens, 32);
+  const int64_t splits = ceil_div(max_length, split_tokens);
+  if (splits > 65535 || split_tokens > INT32_MAX) return B200_ERR_TOO_LARGE;
+
+  DecodeParams p;
+  p.q = nullptr;
+  p.kbuf = static_cast<const __nv_bfloat16*>(key_buffer);
+  p.vbuf = static_cast<const __nv_bfloat16*>(value_buffer);
+  p.lengths = lengths;
+  p.mask = nullptr;
+  p.out = static_cast<__nv_bfloat16*>(output);
+  p.status = status;
+  p.q_batch_stride = p.q_head_stride = p.mask_batch_stride = 0;
+  p.batch = static_cast<int>(batch);
+  p.q_heads = static_cast<int>(q_heads);
+  p.kv_heads = static_cast<int>(kv_heads);
+  p.groups = groups;
+  p.capacity = static_cast<int>(capacity);
+  p.mask_len = static_cast<int>(max_length);
+  p.split_tokens = static_cast<int>(split_tokens);
+  p.num_splits = static_cast<int>(splits);
+  p.mask_dtype = B200_F32;
+  p.compat = 0;
+  p.early_kv = (launch_mode() & B200_LAUNCH_STABLE_KV_PREFIX) != 0 ? 1 : 0;
+  p.scale = static_cast<float>(scale);
+  p.ws_o = nullptr;
+  p.ws_ml = nullptr;
+  p.counters = nullptr;
+  p.qkv_partials = static_cast<const float*>(qkv_partials);
+  p.qkv_bias = static_cast<const __nv_bfloat16*>(qkv_bias);
+  p.cosine = static_cast<const __nv_bfloat16*>(cosine);
+  p.sine = static_cast<const __nv_bfloat16*>(sine);
+  p.kstore = static_cast<__nv_bfloat16*>(key_buffer);
+  p.vstore = static_cast<__nv_bfloat16*>(value_buffer);
+  p.qkv_splits = static_cast<int>(qkv_splits);
+  const bool clustered = cluster_merge(splits, batch, head_blocks);
+  if (splits > 1 && !clustered) {
+    const int64_t need = workspace_bytes_for(batch, q_heads, head_dim, splits);
+    if (!workspace || workspace_bytes < need) return B200_ERR_WORKSPACE;
+    if (batch * head_blocks <= kMaxCounters) p.counters = static_cast<int*>(workspace);
+    p.ws_o = reinterpret_cast<float*>(static_cast<char*>(workspace) + kCounterBytes);
     p.ws_ml = p.ws_o + batch * q_heads * splits * head_dim;
   }
   return head_dim == 64 ? launch_bf16<64>(p, s) : launch_bf16<128>(p, s);

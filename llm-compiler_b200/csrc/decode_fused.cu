@@ -18,30 +18,6 @@ namespace {
 constexpr int kNormThreads = 1024;  // one element per thread at hidden <= 1024
 constexpr int kMaxPerThread = 4;    // hidden <= 4096 kept in registers
 
-// Sum over the K slices of one element, slice order fixed; eight loads in flight per round
-// so that the latency of a round is paid once per eight slices.
-__device__ __forceinline__ float sum_slices(const float* first, int64_t slice, int splits) {
-  float acc = 0.0f;
-  int s = 0;
-  for (; s + 8 <= splits; s += 8) {
-    float t[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) t[j] = __ldcg(first + (s + j) * slice);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc += t[j];
-  }
-  if (s + 4 <= splits) {
-    float t[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) t[j] = __ldcg(first + (s + j) * slice);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) acc += t[j];
-    s += 4;
-  }
-  for (; s < splits; ++s) acc += __ldcg(first + s * slice);
-  return acc;
-}
-
 __global__ void __launch_bounds__(kNormThreads)
 reduce_residual_rms_norm_kernel(const float* __restrict__ partials, int splits,
                                 const __nv_bfloat16* __restrict__ residual,

@@ -65,6 +65,9 @@ class Qwen2Engine:
         self.max_length_hint = 0  # host-known upper bound of the context (0 = capacity)
         # programmatic dependent launch of the chain (B200_PROGRAMMATIC_LAUNCH=0 turns it off)
         self.programmatic_launch = os.environ.get("B200_PROGRAMMATIC_LAUNCH", "1") != "0"
+        # q|k|v reduction + RoPE + KV store inside the attention kernel (B200_FUSED_QKV_ATTENTION=0
+        # keeps them a launch of their own)
+        self.fused_qkv_attention = os.environ.get("B200_FUSED_QKV_ATTENTION", "1") != "0"
         self.split_tokens = 0
         self.kernels_per_step = 0
 
@@ -195,13 +198,20 @@ class Qwen2Engine:
                                   round_before_weight=True, numerical_mode=self.mode)
         for index, layer in enumerate(self.layers):
             partials = kernels.b200_linear_partial(h, layer["qkv_w"])
-            q = kernels.b200_reduce_rope_kv_store(
-                partials, layer["qkv_b"], cosine, sine, self.state.keys[index],
-                self.state.values[index], self.positions, q_heads=cfg.num_heads)
-            attn = kernels.b200_decode_attention(
-                q, self.state.keys[index], self.state.values[index], self.attention_lengths,
-                None, scale=self.scale, numerical_mode=self.mode,
-                split_tokens=self.split_tokens, max_length_hint=self.max_length_hint)
+            if self.fused_qkv_attention:
+                attn = kernels.b200_qkv_decode_attention(
+                    partials, layer["qkv_b"], cosine, sine, self.state.keys[index],
+                    self.state.values[index], self.attention_lengths, q_heads=cfg.num_heads,
+                    scale=self.scale, split_tokens=self.split_tokens,
+                    max_length_hint=self.max_length_hint)
+            else:
+                q = kernels.b200_reduce_rope_kv_store(
+                    partials, layer["qkv_b"], cosine, sine, self.state.keys[index],
+                    self.state.values[index], self.positions, q_heads=cfg.num_heads)
+                attn = kernels.b200_decode_attention(
+                    q, self.state.keys[index], self.state.values[index], self.attention_lengths,
+                    None, scale=self.scale, numerical_mode=self.mode,
+                    split_tokens=self.split_tokens, max_length_hint=self.max_length_hint)
             partials = kernels.b200_linear_partial(attn.view(batch, cfg.q_size), layer["o_w"])
             x, h = kernels.b200_reduce_residual_rms_norm(partials, x, layer["post_norm"],
                                                          epsilon=cfg.rms_norm_eps)

@@ -708,6 +708,46 @@ def b200_reduce_rope_kv_store(partials: torch.Tensor, bias: Optional[torch.Tenso
     return query_out
 
 
+def b200_qkv_decode_attention(partials: torch.Tensor, bias: Optional[torch.Tensor],
+                              cosine: torch.Tensor, sine: torch.Tensor, key_buffer: torch.Tensor,
+                              value_buffer: torch.Tensor, lengths: torch.Tensor, *, q_heads: int,
+                              scale: float, split_tokens: int = 0,
+                              max_length_hint: int = 0) -> torch.Tensor:
+    """b200_reduce_rope_kv_store + b200_decode_attention of a decode step in one launch: the
+    q|k|v partials are reduced (+ bias, RoPE) inside the attention kernel, the new token's K / V
+    row is stored at row lengths[b] - 1 and attends from registers. lengths are the attention
+    lengths (the new token counted). Returns B x Hq x 1 x D."""
+
+    device = _require_cuda(partials, bias, cosine, sine, key_buffer, value_buffer, lengths)
+    splits, batch, width = partials.shape
+    _, capacity, kv_heads, dim = key_buffer.shape
+    if partials.dtype != torch.float32 or key_buffer.dtype != torch.bfloat16:
+        raise ValueError("fp32 partials and bf16 KV buffers expected")
+    if width != (q_heads + 2 * kv_heads) * dim or key_buffer.shape[0] != batch:
+        raise ValueError("partials do not match the head layout of the KV buffers")
+    if not (key_buffer.is_contiguous() and value_buffer.is_contiguous() and partials.is_contiguous()):
+        raise ValueError("partials and KV buffers must be contiguous")
+    cos2, sin2 = cosine.reshape(batch, dim), sine.reshape(batch, dim)
+    if not (cos2.is_contiguous() and sin2.is_contiguous()):
+        raise ValueError("cosine / sine must be contiguous")
+    lengths = _dense_index(lengths, "lengths")
+    output = torch.empty((batch, q_heads, 1, dim), dtype=torch.bfloat16, device=device)
+    rt = runtime(device)
+    library = _lib.load()
+    max_length = min(max_length_hint, capacity) if max_length_hint > 0 else capacity
+    need = int(library.b200_decode_attention_workspace_bytes(batch, q_heads, kv_heads, dim,
+                                                            max_length, split_tokens))
+    workspace = rt.workspace("decode_attention", need)
+    code = library.b200_qkv_decode_attention(
+        partials.data_ptr(), splits, _ptr(bias), cos2.data_ptr(), sin2.data_ptr(),
+        key_buffer.data_ptr(), value_buffer.data_ptr(), lengths.data_ptr(), output.data_ptr(),
+        batch, q_heads, kv_heads, dim, capacity, capacity, float(scale), int(split_tokens),
+        int(max_length_hint), _ptr(workspace), need, rt.status.data_ptr(), _stream())
+    _check(code, "b200_qkv_decode_attention")
+    _count(rt)
+    return output
+
+
 def interleave_gate_up(gate_weight: torch.Tensor, up_weight: torch.Tensor) -> torch.Tensor:
     """Row-interleaves gate and up projection weights (gate_0, up_0, gate_1, ...) for the
     SwiGLU epilogue. A one-time weight repack done at load time with a device copy."""

@@ -540,6 +540,59 @@ def test_split_k_partials_feed_rope_and_kv_store():
     kernels.runtime().check_status()
 
 
+@pytest.mark.parametrize("split_tokens", [0, 64, 4096])
+@pytest.mark.parametrize("hq,hkv,d", [(14, 2, 64), (28, 4, 128), (24, 2, 64)])
+def test_fused_qkv_rope_store_attention_equals_separate_launches(hq, hkv, d, split_tokens,
+                                                                 decode_loads):
+    """One launch (q|k|v partial reduction + bias + RoPE + KV store inside decode attention, the
+    new token attending from registers) against the two launches it replaces and against the
+    oracle. Lengths put the new token first in the buffer, on split boundaries (63/64/65) and
+    at the end of the capacity; the KV rows it writes must be bit-equal, all others untouched."""
+    g = torch.Generator().manual_seed(hq + d + split_tokens)
+    hidden, capacity = 256, 300
+    lengths = torch.tensor([1, 2, 64, 65, 129, 300, 257])
+    b = lengths.numel()
+    width = (hq + 2 * hkv) * d
+    x = torch.randn(b, hidden, generator=g).bfloat16()
+    w = (torch.randn(width, hidden, generator=g) * 0.08).bfloat16()
+    bias = torch.randn(width, generator=g).bfloat16()
+    positions = lengths - 1
+    inv_freq = serve_ops.rope_inverse_frequency(d, 1e6)
+    cos, sin = serve_ops.rope_table(positions.view(b, 1), inv_freq, torch.bfloat16)
+    kbuf = torch.randn(b, capacity, hkv, d, generator=g).bfloat16()
+    vbuf = torch.randn(b, capacity, hkv, d, generator=g).bfloat16()
+    # oracle: projection -> rope -> store -> attention
+    qkv = serve_ops.linear(x, w, bias)
+    q = qkv[:, : hq * d].view(b, 1, hq, d).transpose(1, 2)
+    k = qkv[:, hq * d: (hq + hkv) * d].view(b, 1, hkv, d).transpose(1, 2)
+    v = qkv[:, (hq + hkv) * d:].view(b, 1, hkv, d).transpose(1, 2)
+    q_ref, k_ref = serve_ops.rope(q, k, cos, sin)
+    k_gold, v_gold = kbuf.clone(), vbuf.clone()
+    serve_ops.kv_store(k_gold, v_gold, k_ref, v, positions)
+    ref = serve_ops.decode_attention(q_ref, k_gold, v_gold, lengths, torch.zeros(b, 1, 1, capacity),
+                                     groups=hq // hkv, scale=d ** -0.5)
+    for row, n in enumerate(lengths.tolist()):  # on the device, rows at and past the new token hold poison
+        kbuf[row, n - 1:] = float("nan")
+        vbuf[row, n - 1:] = float("inf")
+    partials = kernels.b200_linear_partial(x.cuda(), w.cuda())
+    # the two launches
+    k_two, v_two = kbuf.cuda(), vbuf.cuda()
+    q_two = kernels.b200_reduce_rope_kv_store(partials, bias.cuda(), cos.cuda(), sin.cuda(), k_two,
+                                              v_two, positions.cuda(), q_heads=hq)
+    out_two = b200.b200_decode_attention(q_two, k_two, v_two, lengths.cuda(), None, scale=d ** -0.5,
+                                         split_tokens=split_tokens)
+    # the one launch
+    k_one, v_one = kbuf.cuda(), vbuf.cuda()
+    out_one = kernels.b200_qkv_decode_attention(partials, bias.cuda(), cos.cuda(), sin.cuda(), k_one,
+                                                v_one, lengths.cuda(), q_heads=hq, scale=d ** -0.5,
+                                                split_tokens=split_tokens)
+    assert torch.equal(k_one.view(torch.int16), k_two.view(torch.int16))
+    assert torch.equal(v_one.view(torch.int16), v_two.view(torch.int16))
+    close(out_one, ref, BF16_TOL)
+    close(out_one, out_two.float().cpu(), 1e-2)
+    kernels.runtime().check_status()
+
+
 def test_linear_f32_epilogues():
     g = torch.Generator().manual_seed(77)
     x = torch.randn(7, 256, generator=g)
