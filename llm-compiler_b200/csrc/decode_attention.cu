@@ -102,7 +102,8 @@ __device__ __forceinline__ uint32_t tile_offset(int row, int chunk) {
 // false when a bounded wait gave up.
 // `prepare` runs (all threads, may synchronise the CTA) after the dependency wait and before the
 // query fragments are read from `qbase` (row stride `q_row_stride` elements; global or shared).
-template <int D, int TOK, bool WIDE, bool FAST, bool TMA, typename Prepare = NoPrepare>
+template <int D, int TOK, bool WIDE, bool FAST, bool TMA, typename Prepare = NoPrepare,
+          int WARPS = kWarps>
 __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUtensorMap& kmap,
                                                const CUtensorMap& vmap, unsigned char* smem,
                                                uint32_t bar0, int b, int kvh, int g0, int rows,
@@ -131,7 +132,7 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
 
   // sub-tile j of this split covers tokens start + j*TOK ...; warp w owns j = w, w+4, ...
   const int n_sub = (end - start + TOK - 1) / TOK;
-  const int my_count = n_sub > warp ? (n_sub - warp + kWarps - 1) / kWarps : 0;
+  const int my_count = n_sub > warp ? (n_sub - warp + WARPS - 1) / WARPS : 0;
 
   // per-lane constants of the cp.async variant: this lane's rows / chunks inside a sub-tile
   uint32_t lane_soff[TMA ? 1 : kCopiesPerLane];
@@ -149,7 +150,7 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
   }
 
   auto issue_load = [&](int it) {
-    const int t0 = start + (it * kWarps + warp) * TOK;
+    const int t0 = start + (it * WARPS + warp) * TOK;
     const uint32_t kdst = warp_smem + ((it0 + it) % kStages) * kStageBytes;
     const uint32_t vdst = kdst + kTileBytes;
     if (TMA) {
@@ -204,7 +205,7 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
   if (TMA && stable_end > 0) {
 #pragma unroll
     for (int s = 0; s < kStages - 1; ++s)
-      if (s < my_count && start + (s * kWarps + warp + 1) * TOK <= stable_end) {
+      if (s < my_count && start + (s * WARPS + warp + 1) * TOK <= stable_end) {
         issue_load(s);
         requested |= 1u << s;
       }
@@ -258,7 +259,7 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
     if (it + kStages - 1 < my_count) issue_load(it + kStages - 1);
     if (!TMA) cp_async_commit();
 
-    const int t0 = start + (it * kWarps + warp) * TOK;
+    const int t0 = start + (it * WARPS + warp) * TOK;
     const uint32_t ksm = warp_smem + ((it0 + it) % kStages) * kStageBytes;
     const uint32_t vsm = ksm + kTileBytes;
     const bool partial = t0 + TOK > end;
@@ -444,8 +445,8 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
 // CLUSTER: the splits of one (sequence, head block) form a thread-block cluster (gridDim.x ==
 // cluster size <= 8) and are combined through distributed shared memory by the cluster's
 // first CTA; otherwise through the fp32 scratch in global memory by whichever CTA arrives last.
-template <int D, int TOK, bool WIDE, bool FAST, bool TMA, bool CLUSTER>
-__global__ void __launch_bounds__(kThreads)
+template <int D, int TOK, bool WIDE, bool FAST, bool TMA, bool CLUSTER, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                         const __grid_constant__ CUtensorMap vmap) {
   constexpr int kWarpBytes = kStages * 2 * TOK * D * 2;
@@ -454,7 +455,7 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
                 "ring region too small to hold the partials");
 
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t full_bar[kWarps][kStages];
+  __shared__ __align__(8) uint64_t full_bar[WARPS][kStages];
   __shared__ int merge_flag;
   // fused form only: the rotated query rows of this head block, the newest token's K and V row
   // (bf16 values held as floats) and its scores against the query rows (log2 domain)
@@ -508,7 +509,7 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
     const __nv_bfloat16* sin_row = p.sine + static_cast<int64_t>(b) * D;
     const int q_items = rows * half;
     const int items = q_items + (owner ? 2 * half : 0);
-    for (int item = threadIdx.x; item < items; item += kThreads) {
+    for (int item = threadIdx.x; item < items; item += (WARPS * 32)) {
       int column, d;
       bool rotate = true;
       if (item < q_items) {
@@ -569,16 +570,16 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
   int it_base = 0;
   const int stable_end = p.early_kv ? max(n_tokens - 1, 0) : -1;
   if (fused)
-    stream_segment<D, TOK, WIDE, FAST, TMA>(p, kmap, vmap, smem, bar0, b, kvh, g0, rows, start, end,
-                                            it_base, stable_end, &trace, q_stage,
-                                            static_cast<int64_t>(D), prepare_fused);
+    stream_segment<D, TOK, WIDE, FAST, TMA, decltype(prepare_fused), WARPS>(
+        p, kmap, vmap, smem, bar0, b, kvh, g0, rows, start, end, it_base, stable_end, &trace, q_stage,
+        static_cast<int64_t>(D), prepare_fused);
   else
-    stream_segment<D, TOK, WIDE, FAST, TMA>(p, kmap, vmap, smem, bar0, b, kvh, g0, rows, start, end,
-                                            it_base, stable_end, &trace);
+    stream_segment<D, TOK, WIDE, FAST, TMA, NoPrepare, WARPS>(
+        p, kmap, vmap, smem, bar0, b, kvh, g0, rows, start, end, it_base, stable_end, &trace);
   trace.mark_middle();
   if (owner) {
     // the newest token as one more partial: max = its score (log2 domain), sum = 1, O = its V row
-    for (int row = warp; row < rows; row += kWarps) {
+    for (int row = warp; row < rows; row += WARPS) {
       float dot = 0.0f;
       for (int c = lane; c < D; c += 32) dot = fmaf(__bfloat162float(q_stage[row * D + c]), new_k[c], dot);
 #pragma unroll
@@ -588,19 +589,19 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
     __syncthreads();
   }
 
-  for (int idx = threadIdx.x; idx < rows * D; idx += kThreads) {
+  for (int idx = threadIdx.x; idx < rows * D; idx += (WARPS * 32)) {
     const int row = idx / D;
     const int col = idx % D;
-    float mw[kWarps], m_all = -INFINITY;
+    float mw[WARPS], m_all = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
+    for (int w = 0; w < WARPS; ++w) {
       mw[w] = reinterpret_cast<const float*>(smem + w * kWarpBytes)[16 * D + row * 2];
       m_all = fmaxf(m_all, mw[w]);
     }
     if (owner) m_all = fmaxf(m_all, new_score[row]);
     float l_all = 0.0f, o_all = 0.0f;
 #pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
+    for (int w = 0; w < WARPS; ++w) {
       const float* wo = reinterpret_cast<const float*>(smem + w * kWarpBytes);
       const float wgt = mw[w] == -INFINITY ? 0.0f : fast_exp2(mw[w] - m_all);
       l_all += wo[16 * D + row * 2 + 1] * wgt;
@@ -639,7 +640,7 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
     cluster_sync();
     if (split == 0) {
       const uint32_t staging = smem_u32(smem + kStagingBytes);
-      for (int idx = threadIdx.x; idx < rows * D; idx += kThreads) {
+      for (int idx = threadIdx.x; idx < rows * D; idx += (WARPS * 32)) {
         const int row = idx / D;
         const int col = idx % D;
         float m_all = -INFINITY;
@@ -676,7 +677,7 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
   __syncthreads();
   if (!merge_flag) return;
   __threadfence();
-  for (int idx = threadIdx.x; idx < rows * D; idx += kThreads) {
+  for (int idx = threadIdx.x; idx < rows * D; idx += (WARPS * 32)) {
     const int row = idx / D;
     const int col = idx % D;
     const int hq = kvh * p.groups + g0 + row;
@@ -1044,35 +1045,74 @@ bool use_tma_loads() {
   return value == nullptr || strcmp(value, "cp.async") != 0;
 }
 
+// Two splits of a pair on two 4-warp CTAs that share an SM, or the same tokens on one 8-warp
+// CTA that merges in its own shared memory: the second form halves the cross-CTA merging (a
+// two-split plan needs none at all) and measured 24.0 against 27.8 us at batch 64 x 4096. It is
+// used whenever the plan has an even number of splits (B200_DECODE_ATTENTION_WARPS=4 keeps
+// 4-warp CTAs).
+bool wide_cta_enabled() {
+  const char* value = getenv("B200_DECODE_ATTENTION_WARPS");
+  return value == nullptr || strcmp(value, "4") != 0;
+}
+
 // The splits of a pair merge through distributed shared memory when they fit one portable
-// cluster and the whole grid is resident at once (at most 2 CTAs on each of the 148 SMs):
-// that is the latency-bound regime the cluster merge is for. Larger grids measured slower as
-// clusters (batch 256 x 4096: 86 vs 60 us), because a cluster member whose split is empty
-// has to stay for the barriers instead of leaving its slot to the next CTA.
-// B200_DECODE_ATTENTION_MERGE=global always keeps the scratch in global memory.
-bool cluster_merge(int64_t splits, int64_t batch, int64_t head_blocks) {
-  const char* value = getenv("B200_DECODE_ATTENTION_MERGE");
-  if (value != nullptr && strcmp(value, "global") == 0) return false;
-  return splits >= 2 && splits <= 8 && splits * batch * head_blocks <= 2 * kNumSMs;
+// cluster and the whole grid is resident at once: that is the latency-bound regime the cluster
+// merge is for. Larger grids measured slower as clusters (batch 256 x 4096: 86 vs 60 us),
+// because a cluster member whose split is empty has to stay for the barriers instead of leaving
+// its slot to the next CTA. B200_DECODE_ATTENTION_MERGE=global always keeps the scratch in
+// global memory.
+struct GridPlan {
+  int warps;         // 4 or 8 per CTA
+  int splits;        // CTAs per (sequence, head block)
+  int split_tokens;  // tokens per CTA
+  bool cluster;      // the splits of a pair form a thread-block cluster
+};
+
+GridPlan plan_grid(int64_t splits, int64_t split_tokens, int64_t batch, int64_t head_blocks) {
+  GridPlan plan = {kWarps, static_cast<int>(splits), static_cast<int>(split_tokens), false};
+  if (splits % 2 == 0 && wide_cta_enabled()) {
+    plan.warps = 2 * kWarps;
+    plan.splits = static_cast<int>(splits / 2);
+    plan.split_tokens = static_cast<int>(2 * split_tokens);
+  }
+  const char* merge = getenv("B200_DECODE_ATTENTION_MERGE");
+  const bool global_only = merge != nullptr && strcmp(merge, "global") == 0;
+  const int64_t resident = plan.warps == kWarps ? 2 * kNumSMs : kNumSMs;  // CTAs at once
+  plan.cluster = !global_only && plan.splits >= 2 && plan.splits <= 8 &&
+                 plan.splits * batch * head_blocks <= resident;
+  return plan;
+}
+
+template <int D, bool WIDE, bool FAST, bool TMA, int WARPS>
+int launch_grid(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap,
+                bool cluster, cudaStream_t stream) {
+  constexpr int TOK = tokens_per_step<D>();
+  constexpr int smem = WARPS * kStages * 2 * TOK * D * 2;
+  const int row_blocks = (p.groups + 15) / 16;
+  dim3 grid(p.num_splits, p.kv_heads * row_blocks, p.batch);
+  auto kernel = cluster ? decode_attention_kernel<D, TOK, WIDE, FAST, TMA, true, WARPS>
+                        : decode_attention_kernel<D, TOK, WIDE, FAST, TMA, false, WARPS>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    return B200_ERR_LAUNCH;
+  if (launch_chained_cluster(kernel, grid, dim3(WARPS * 32), smem, stream,
+                             cluster ? static_cast<unsigned>(p.num_splits) : 1u, p, kmap,
+                             vmap) != cudaSuccess)
+    return B200_ERR_LAUNCH;
+  return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
 
 template <int D, bool WIDE, bool FAST, bool TMA>
 int launch_variant(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap,
                    cudaStream_t stream) {
-  constexpr int TOK = tokens_per_step<D>();
-  constexpr int smem = kWarps * kStages * 2 * TOK * D * 2;
   const int row_blocks = (p.groups + 15) / 16;
-  dim3 grid(p.num_splits, p.kv_heads * row_blocks, p.batch);
-  const bool cluster = cluster_merge(p.num_splits, p.batch, p.kv_heads * row_blocks);
-  auto kernel = cluster ? decode_attention_kernel<D, TOK, WIDE, FAST, TMA, true>
-                        : decode_attention_kernel<D, TOK, WIDE, FAST, TMA, false>;
-  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-    return B200_ERR_LAUNCH;
-  if (launch_chained_cluster(kernel, grid, dim3(kThreads), smem, stream,
-                             cluster ? static_cast<unsigned>(p.num_splits) : 1u, p, kmap,
-                             vmap) != cudaSuccess)
-    return B200_ERR_LAUNCH;
-  return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
+  const GridPlan plan = plan_grid(p.num_splits, p.split_tokens, p.batch, p.kv_heads * row_blocks);
+  DecodeParams q = p;
+  q.num_splits = plan.splits;
+  q.split_tokens = plan.split_tokens;
+  if (q.ws_o != nullptr)  // the scratch was sized for at least this many splits
+    q.ws_ml = q.ws_o + static_cast<int64_t>(p.batch) * p.q_heads * plan.splits * D;
+  if (plan.warps == kWarps) return launch_grid<D, WIDE, FAST, TMA, kWarps>(q, kmap, vmap, plan.cluster, stream);
+  return launch_grid<D, WIDE, FAST, TMA, 2 * kWarps>(q, kmap, vmap, plan.cluster, stream);
 }
 
 template <int D, bool WIDE, bool FAST, bool TMA>
@@ -1113,11 +1153,12 @@ int launch_bf16(const DecodeParams& p, cudaStream_t stream, int flat_grid = 0) {
   }
 #undef B200_DISPATCH
   if (code != B200_OK) return code;
-  const bool clustered = cluster_merge(p.num_splits, p.batch, p.kv_heads * ((p.groups + 15) / 16));
-  if (flat_grid == 0 && p.num_splits > 1 && p.counters == nullptr && !clustered) {
+  const GridPlan plan = plan_grid(p.num_splits, p.split_tokens, p.batch,
+                                  p.kv_heads * ((p.groups + 15) / 16));
+  if (flat_grid == 0 && plan.splits > 1 && p.counters == nullptr && !plan.cluster) {
     decode_merge_kernel<<<p.batch * p.q_heads, D, 0, stream>>>(
-        p.ws_o, p.ws_ml, p.lengths, p.out, p.q_heads, D, p.num_splits, p.split_tokens,
-        p.mask_len);
+        p.ws_o, p.ws_o + static_cast<int64_t>(p.batch) * p.q_heads * plan.splits * D, p.lengths,
+        p.out, p.q_heads, D, plan.splits, plan.split_tokens, p.mask_len);
   }
   return launch_status();
 }
@@ -1311,8 +1352,8 @@ extern "C" int b200_decode_attention(const void* query, const void* key_buffer,
     }
     return head_dim == 64 ? launch_bf16<64>(p, s, flat.grid) : launch_bf16<128>(p, s, flat.grid);
   }
-  const bool clustered = cluster_merge(splits, batch, head_blocks);
-  if (splits > 1 && !clustered) {  // (a cluster combines its splits in shared memory)
+  const GridPlan grid_plan = plan_grid(splits, split_tokens, batch, head_blocks);
+  if (grid_plan.splits > 1 && !grid_plan.cluster) {  // (a cluster combines its splits in shared memory)
     const int64_t need = workspace_bytes_for(batch, q_heads, head_dim, splits);
     if (!workspace || workspace_bytes < need) return B200_ERR_WORKSPACE;
     if (batch * head_blocks <= kMaxCounters) p.counters = static_cast<int*>(workspace);
@@ -1485,8 +1526,8 @@ extern "C" int b200_qkv_decode_attention(
   p.kstore = static_cast<__nv_bfloat16*>(key_buffer);
   p.vstore = static_cast<__nv_bfloat16*>(value_buffer);
   p.qkv_splits = static_cast<int>(qkv_splits);
-  const bool clustered = cluster_merge(splits, batch, head_blocks);
-  if (splits > 1 && !clustered) {
+  const GridPlan grid_plan = plan_grid(splits, split_tokens, batch, head_blocks);
+  if (grid_plan.splits > 1 && !grid_plan.cluster) {
     const int64_t need = workspace_bytes_for(batch, q_heads, head_dim, splits);
     if (!workspace || workspace_bytes < need) return B200_ERR_WORKSPACE;
     if (batch * head_blocks <= kMaxCounters) p.counters = static_cast<int*>(workspace);
