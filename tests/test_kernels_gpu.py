@@ -645,6 +645,24 @@ def test_embedding_swiglu_add_argmax_advance():
     exact(b200.b200_contiguous(strided), strided.cpu().contiguous())
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rows,vocab", [(64, 151936), (3, 40001), (5, 1000), (400, 33000)])
+def test_argmax_matches_torch_with_ties_across_parts(rows, vocab, dtype):
+    """Maxima anywhere in the row, ties far apart (lowest index wins), a maximum in the ragged
+    tail; odd vocabulary sizes take the scalar path."""
+    g = torch.Generator().manual_seed(rows + vocab)
+    logits = torch.randn(rows, vocab, generator=g).to(dtype)
+    span = -(-vocab // 8)
+    for row in range(min(rows, 9)):
+        position = min(vocab - 1, row * span + 17) if row < 8 else vocab - 1
+        logits[row, position] = 50.0
+    logits[0, vocab - 3] = 50.0  # tie with an earlier part: the lower index must win
+    if rows > 1:
+        logits[1, 3] = 50.0      # tie with a later part
+    out = b200.b200_argmax(logits.cuda()).cpu()
+    assert torch.equal(out, logits.float().argmax(-1))
+
+
 def test_embedding_bad_id_sets_status():
     table = torch.ones(10, 64, dtype=torch.bfloat16, device="cuda")
     out = b200.b200_embedding(table, torch.tensor([1, 10, -1], device="cuda"))
