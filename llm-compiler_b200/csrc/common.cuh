@@ -45,6 +45,13 @@ int launch_mode();  // defined in api.cu
 __device__ __forceinline__ void grid_dependency_wait() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
+// The same for a whole CTA: one thread waits for the prerequisite grids (whose writes are then
+// visible to this grid), the others sleep in the CTA barrier and take no issue slots from the
+// kernels still running on the SM. Every thread of the CTA must call it.
+__device__ __forceinline__ void grid_dependency_wait_cta() {
+  if (threadIdx.x == 0) grid_dependency_wait();
+  __syncthreads();
+}
 __device__ __forceinline__ void grid_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }

@@ -211,7 +211,7 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
       }
   }
   if (stable_end >= 0) {
-    grid_dependency_wait();
+    grid_dependency_wait_cta();
     if (trace != nullptr) trace->mark(0);
   }
 

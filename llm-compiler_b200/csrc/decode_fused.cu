@@ -37,7 +37,7 @@ reduce_residual_rms_norm_kernel(const float* __restrict__ partials, int splits,
       w[i] = c < hidden ? __bfloat162float(weight[c]) : 0.0f;
     }
   }
-  grid_dependency_wait();
+  grid_dependency_wait_cta();
   trace.mark(0);
   const int row = blockIdx.x;
   const int64_t slice = static_cast<int64_t>(rows) * hidden;
@@ -111,7 +111,7 @@ __global__ void reduce_rope_kv_store_kernel(const float* __restrict__ partials, 
                                             int32_t* status) {
   TraceScope trace(3);
   grid_launch_dependents();
-  grid_dependency_wait();
+  grid_dependency_wait_cta();
   trace.mark(0);
   const int half = dim / 2;
   const int heads = q_heads + 2 * kv_heads;

@@ -189,7 +189,10 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
         tma_load_2d(a_dst + kABytes, &b_map, bar, (kb_first + kb) * kBK, tile_n * bn);
       }
     }
-  } else {
+  } else if (warp == 1 && lane == 0) {
+    // The MMA issuer waits too (a K slice without k-blocks has no TMA copy to order it after
+    // the producer's wait). The other threads only ever act on what these three hand them
+    // through mbarriers, and stay out of the way of the kernels still running on the SM.
     grid_dependency_wait();
   }
   if (warp == 1 && lane == 0) {
