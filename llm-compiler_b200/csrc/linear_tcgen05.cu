@@ -113,6 +113,8 @@ __global__ void __launch_bounds__(kThreads)
 linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap a_map,
                       const __grid_constant__ CUtensorMap b_map) {
   constexpr int kABytes = A_ROWS * 128;
+  // TMEM is allocated in powers of two of at least 32 columns
+  constexpr int kTmemColumns = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : BN <= 256 ? 256 : 512;
   constexpr int kBBytes = BN * 128;
   constexpr int kStageBytes = kABytes + kBBytes;
   const int bn = p.bn;
@@ -148,7 +150,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   }
   if (warp == 1) {  // one warp allocates the accumulator columns and later frees them
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(&tmem_base_slot)), "r"(static_cast<uint32_t>(BN < 32 ? 32 : BN))
+                 ::"r"(smem_u32(&tmem_base_slot)), "r"(static_cast<uint32_t>(kTmemColumns))
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -305,7 +307,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   __syncthreads();
   if (warp == 1)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
-                 ::"r"(tmem_base), "r"(static_cast<uint32_t>(BN < 32 ? 32 : BN)) : "memory");
+                 ::"r"(tmem_base), "r"(static_cast<uint32_t>(kTmemColumns)) : "memory");
   trace.mark(1);
 }
 
@@ -387,6 +389,10 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
       }
     }
     if (best < 0.8) return B200_ERR_UNSUPPORTED;
+    // Many waves of tiles (an LM head): 192-column tiles with a 3-stage ring leave room for two
+    // CTAs per SM, so one CTA's ramp and epilogue hide under the other's streaming; measured
+    // 60.2 us against 71.2 - 78.3 us for one 208 ... 256-column CTA per SM at N = 151936.
+    if (ceil_div(n, 192) >= 4 * kNumSMs) bn = 192;
   }
   CUtensorMap a_map, b_map;
   if (!make_bf16_matrix_map(&a_map, input, m, k, input_row_stride, m <= 64 ? 64 : kBM) ||
@@ -406,6 +412,7 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
   p.bn = bn;
   p.prefetch_weights = (launch_mode() & B200_LAUNCH_CONSTANT_WEIGHTS) != 0 ? 1 : 0;
   if (m <= 64) {
+    if (bn == 192 && ceil_div(n, 192) >= 4 * kNumSMs) return launch<192, 3, 64>(p, a_map, b_map, stream);
     if (bn > 128) return launch<256, 5, 64>(p, a_map, b_map, stream);
     if (bn > 64) return launch<128, 8, 64>(p, a_map, b_map, stream);
     return launch<64, 12, 64>(p, a_map, b_map, stream);
