@@ -150,3 +150,25 @@ def test_programmatic_launch_changes_nothing(batch):
         logits[programmatic] = steps
     for serial, chained in zip(logits[False], logits[True]):
         assert torch.equal(serial, chained)
+
+
+def test_qwen2_7b_shaped_layers_match_oracle():
+    """Qwen2-7B shapes (hidden 3584, 28/4 heads x 128, SwiGLU 18944, untied LM head) with 2 layers
+    and a reduced vocabulary: the decode chain (split-K partial producers, reduce consumers,
+    fused q|k|v attention at head_dim 128, 80..256-column GEMM tiles) against the CPU oracle."""
+    config = q2.Qwen2Config(hidden_size=3584, intermediate_size=18944, num_layers=2, num_heads=28,
+                            num_kv_heads=4, rms_norm_eps=1e-6, rope_theta=1e6, vocab_size=4096,
+                            tie_word_embeddings=False)
+    weights = q2.make_weights(config, seed=11, dtype=torch.bfloat16)
+    prompt = q2.make_prompt_ids(config, 3, 21, seed=4)
+    ref_tokens, ref_logits, _ = qwen2_model.greedy_generate(config, weights, prompt, 2, capacity=32)
+    engine = Qwen2Engine(config, {k: v.cuda() for k, v in weights.items()}, batch=3, capacity=32)
+    engine.prefill(prompt)
+    assert_logits(engine.logits, ref_logits[0], 2e-2)
+    engine.capture()
+    for step in range(2):
+        engine.input_ids.copy_(ref_tokens[:, step].cuda())
+        engine.decode_step(feed_back=False)
+        assert_logits(engine.logits, ref_logits[step + 1], 2e-2)
+        assert_tokens(engine.next_ids, ref_tokens[:, step + 1], ref_logits[step + 1], 2e-2)
+    engine.state.check()
