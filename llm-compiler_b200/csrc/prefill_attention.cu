@@ -325,6 +325,15 @@ int launch_bf16(const PrefillParams& p, cudaStream_t stream) {
 }  // namespace
 }  // namespace b200
 
+namespace b200 {
+// prefill_attention_tcgen05.cu
+int prefill_attention_tcgen05(const void* query, const void* key, const void* value, void* output,
+                              int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t tokens,
+                              int64_t head_dim, const int64_t query_strides[4],
+                              const int64_t key_strides[4], const int64_t value_strides[4],
+                              double scale, int32_t* status, cudaStream_t stream);
+}  // namespace b200
+
 using namespace b200;
 
 extern "C" int b200_prefill_attention(const void* query, const void* key, const void* value,
@@ -334,7 +343,8 @@ extern "C" int b200_prefill_attention(const void* query, const void* key, const 
                                       const int64_t key_strides[4],
                                       const int64_t value_strides[4],
                                       const int64_t mask_strides[4], int mask_dtype, double scale,
-                                      int causal, int dtype, int mode, void* stream) {
+                                      int causal, int dtype, int mode, int32_t* status,
+                                      void* stream) {
   if (!query || !key || !value || !output || !query_strides || !key_strides || !value_strides ||
       batch < 0 || q_heads <= 0 || kv_heads <= 0 || tokens < 0 || head_dim <= 0 ||
       q_heads % kv_heads != 0)
@@ -379,6 +389,13 @@ extern "C" int b200_prefill_attention(const void* query, const void* key, const 
   for (int i = 0; i < 3; ++i)
     if (query_strides[i] % 8 != 0 || key_strides[i] % 8 != 0 || value_strides[i] % 8 != 0)
       return B200_ERR_ALIGNMENT;
+
+  if (mask == nullptr && causal && mode == B200_MODE_FAST) {
+    const int code = prefill_attention_tcgen05(query, key, value, output, batch, q_heads, kv_heads,
+                                               tokens, head_dim, query_strides, key_strides,
+                                               value_strides, scale, status, s);
+    if (code != B200_ERR_UNSUPPORTED) return code;
+  }
 
   PrefillParams p;
   p.q = static_cast<const __nv_bfloat16*>(query);

@@ -1,0 +1,68 @@
+// tcgen05 (5th-generation tensor core) helpers shared by the GEMM and the prefill attention:
+// shared-memory matrix descriptors, the instruction descriptor of kind::f16, MMA issue and
+// commit, tensor-memory loads.
+#pragma once
+
+#include "common.cuh"
+
+namespace b200 {
+
+// Shared-memory matrix descriptor of a K-major tile of 128-byte swizzled rows: start address,
+// leading byte offset 16 B (unused by swizzled K-major layouts), stride byte offset 1024 B
+// (8 rows of 128 B per swizzle atom), descriptor version 1 (Blackwell), layout SWIZZLE_128B.
+__device__ __forceinline__ uint64_t smem_descriptor(uint32_t smem_addr) {
+  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) |
+         (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+
+// The same for an MN-major operand (rows of the tile are the K index, the 64 elements of a
+// 128-byte swizzled row run along M or N): stride byte offset 1024 B between groups of 8 K
+// rows, leading byte offset = distance between the 64-wide panels along M / N. One K step of
+// 16 advances the start address by 16 rows = 2048 B. (Checked against a reference product.)
+__device__ __forceinline__ uint64_t smem_descriptor_mn_major(uint32_t smem_addr,
+                                                             uint32_t panel_stride_bytes) {
+  return static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4) |
+         (static_cast<uint64_t>(panel_stride_bytes >> 4) << 16) | (uint64_t(1024 >> 4) << 32) |
+         (uint64_t(1) << 46) | (uint64_t(2) << 61);
+}
+
+// Instruction descriptor of kind::f16: fp32 accumulator, bf16 A and B; A K-major, B K-major
+// or (b_mn_major) MN-major.
+__host__ __device__ constexpr uint32_t instruction_descriptor(int m, int n, bool b_mn_major = false) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_32x32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+}  // namespace b200

@@ -560,7 +560,7 @@ def b200_prefill_attention(query: torch.Tensor, key: torch.Tensor, value: torch.
         storage.data_ptr(), batch, q_heads, kv_heads, tokens, dim,
         _lib.i64_array(query.stride()), _lib.i64_array(key.stride()),
         _lib.i64_array(value.stride()), mask_strides, mask_code, float(scale), int(bool(causal)),
-        _code(query.dtype), _mode(numerical_mode), _stream())
+        _code(query.dtype), _mode(numerical_mode), rt.status.data_ptr(), _stream())
     _check(code, "b200_prefill_attention")
     _count(rt)
     return storage.transpose(1, 2)
