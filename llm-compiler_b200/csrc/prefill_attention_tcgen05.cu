@@ -10,7 +10,7 @@
 //   O_j = P V     tcgen05.mma, M 128 x N D, K = 128 keys; V is used as it lies in memory (keys x
 //                 D, an MN-major B operand: no transpose pass); O_j in D TMEM columns
 //   O = O a + O_j in registers (a = exp2(old max - new max)): tensor memory is never rescaled
-// Roles: warps 0-3 softmax + epilogue, warp 4 (one lane) TMA producer with a 2-stage K/V ring,
+// Roles: warps 0-3 softmax + epilogue, warp 4 (one lane) TMA producer (two K buffers, one V),
 // warp 5 (one lane) MMA issuer and owner of the TMEM allocation. The MMA thread issues S of tile
 // j + 1 right behind P V of tile j, so the tensor core works while the softmax warps fold O_j.
 // Every mbarrier wait is bounded: a wait that gives up sets B200_STATUS_WAIT_TIMEOUT, TMEM is
@@ -27,7 +27,7 @@ namespace {
 
 constexpr int kTile = 128;     // query rows per CTA = keys per step
 constexpr int kThreads = 192;  // 4 softmax warps + TMA warp + MMA warp
-constexpr int kKvStages = 2;
+constexpr int kKStages = 2;  // K tiles are double-buffered, V has one buffer (see the kernel)
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct PrefillTcParams {
@@ -50,24 +50,27 @@ __device__ __forceinline__ void load_box(uint32_t dst, const CUtensorMap* map, u
   else tma_load_4d(dst, map, bar, d0, head, t0, batch);
 }
 
+// Launch bounds: at D = 64 two CTAs share an SM, which needs at most 128 registers per thread
+// (the register file is split over four sub-partitions of 16 K registers; two of a CTA's six
+// warps land on the same one). Declaring 256 threads x 2 CTAs makes the compiler keep to that.
 template <int D>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(D == 64 ? 256 : kThreads, D == 64 ? 2 : 1)
 prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant__ CUtensorMap q_map,
                                  const __grid_constant__ CUtensorMap k_map,
                                  const __grid_constant__ CUtensorMap v_map) {
   constexpr int kPanels = D / 64;                   // 64-wide (128-byte) panels along D
   constexpr uint32_t kPanelBytes = kTile * 128;     // 128 rows x 128 B
   constexpr uint32_t kTileBytes = kPanels * kPanelBytes;  // one of Q, K, V
-  constexpr uint32_t kStageBytes = 2 * kTileBytes;  // K then V
   constexpr uint32_t kTmemColumns = 256;            // S: 128, O_j: D
   constexpr uint32_t kSColumn = 0, kOColumn = 128;
 
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t q_full, s_full, p_full, o_full;
-  __shared__ __align__(8) uint64_t kv_full[kKvStages], kv_empty[kKvStages];
+  __shared__ __align__(8) uint64_t k_full[kKStages], k_empty[kKStages], v_full, v_empty;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int failed;
 
+  TraceScope trace(7);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int q_tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // heavy first
   const int hq = blockIdx.y, b = blockIdx.z;
@@ -76,8 +79,12 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
   const int n_tiles = q_tile + 1;  // causal: key tiles 0 .. the diagonal one
 
   const uint32_t q_smem = smem_u32(smem);
-  const uint32_t kv_smem = q_smem + kTileBytes;
-  const uint32_t p_smem = kv_smem + kKvStages * kStageBytes;  // [2 panels][128 rows][128 B]
+  // K_{j+1} is wanted the moment P V_j has been issued, V_{j+1} only a softmax later: two K
+  // buffers and one V buffer keep the CTA below half of the shared memory at D = 64, so that
+  // two CTAs share an SM and fill each other's softmax gaps on the tensor core.
+  const uint32_t k_smem = q_smem + kTileBytes;
+  const uint32_t v_smem = k_smem + kKStages * kTileBytes;
+  const uint32_t p_smem = v_smem + kTileBytes;  // [2 panels][128 rows][128 B]
 
   if (threadIdx.x == 0) {
     failed = 0;
@@ -85,10 +92,12 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
     mbarrier_init(smem_u32(&s_full), 1);
     mbarrier_init(smem_u32(&p_full), 4);  // one arrival per softmax warp
     mbarrier_init(smem_u32(&o_full), 1);
-    for (int s = 0; s < kKvStages; ++s) {
-      mbarrier_init(smem_u32(&kv_full[s]), 1);
-      mbarrier_init(smem_u32(&kv_empty[s]), 1);
+    for (int s = 0; s < kKStages; ++s) {
+      mbarrier_init(smem_u32(&k_full[s]), 1);
+      mbarrier_init(smem_u32(&k_empty[s]), 1);
     }
+    mbarrier_init(smem_u32(&v_full), 1);
+    mbarrier_init(smem_u32(&v_empty), 1);
     fence_mbarrier_init();
   }
   if (warp == 5) {
@@ -110,25 +119,31 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
                p.q_token_dim1);
     for (int j = 0; j < n_tiles; ++j) {
       const int s = j & 1;
-      if (j >= kKvStages && !mbarrier_wait_bounded(smem_u32(&kv_empty[s]), ((j >> 1) - 1) & 1)) {
+      if (j >= kKStages && !mbarrier_wait_bounded(smem_u32(&k_empty[s]), ((j >> 1) - 1) & 1)) {
         failed = 1;
         break;
       }
-      const uint32_t bar = smem_u32(&kv_full[s]);
-      const uint32_t k_dst = kv_smem + s * kStageBytes, v_dst = k_dst + kTileBytes;
-      mbarrier_arrive_expect_tx(bar, kStageBytes);
+      mbarrier_arrive_expect_tx(smem_u32(&k_full[s]), kTileBytes);
 #pragma unroll
-      for (int panel = 0; panel < kPanels; ++panel) {
-        load_box(k_dst + panel * kPanelBytes, &k_map, bar, panel * 64, j * kTile, kvh, b, p.k_token_dim1);
-        load_box(v_dst + panel * kPanelBytes, &v_map, bar, panel * 64, j * kTile, kvh, b, p.v_token_dim1);
+      for (int panel = 0; panel < kPanels; ++panel)
+        load_box(k_smem + s * kTileBytes + panel * kPanelBytes, &k_map, smem_u32(&k_full[s]),
+                 panel * 64, j * kTile, kvh, b, p.k_token_dim1);
+      if (j >= 1 && !mbarrier_wait_bounded(smem_u32(&v_empty), (j - 1) & 1)) {
+        failed = 1;
+        break;
       }
+      mbarrier_arrive_expect_tx(smem_u32(&v_full), kTileBytes);
+#pragma unroll
+      for (int panel = 0; panel < kPanels; ++panel)
+        load_box(v_smem + panel * kPanelBytes, &v_map, smem_u32(&v_full), panel * 64, j * kTile, kvh,
+                 b, p.v_token_dim1);
     }
   } else if (warp == 5 && lane == 0) {
     // ---- MMA issuer ----
     constexpr uint32_t idesc_s = instruction_descriptor(kTile, kTile);
     constexpr uint32_t idesc_o = instruction_descriptor(kTile, D, true);  // V: MN-major B operand
     auto issue_s = [&](int j) {  // S = Q K_j^T, K = D
-      const uint32_t k_tile = kv_smem + (j & 1) * kStageBytes;
+      const uint32_t k_tile = k_smem + (j & 1) * kTileBytes;
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
         const uint32_t offset = (ks / 4) * kPanelBytes + (ks % 4) * 32;
@@ -136,21 +151,23 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
                   smem_descriptor(k_tile + offset), idesc_s, ks > 0 ? 1u : 0u);
       }
       umma_commit(smem_u32(&s_full));
+      umma_commit(smem_u32(&k_empty[j & 1]));  // K_j is free once S_j has been computed
     };
     bool ok = mbarrier_wait_bounded(smem_u32(&q_full), 0) &&
-              mbarrier_wait_bounded(smem_u32(&kv_full[0]), 0);
+              mbarrier_wait_bounded(smem_u32(&k_full[0]), 0);
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       issue_s(0);
     }
     for (int j = 0; ok && j < n_tiles; ++j) {
       // O_j = P V_j once the softmax warps have written P (which also says S and O_{j-1} are read)
-      if (!mbarrier_wait_bounded(smem_u32(&p_full), j & 1)) {
+      if (!mbarrier_wait_bounded(smem_u32(&p_full), j & 1) ||
+          !mbarrier_wait_bounded(smem_u32(&v_full), j & 1)) {
         ok = false;
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t v_tile = kv_smem + (j & 1) * kStageBytes + kTileBytes;
+      const uint32_t v_tile = v_smem;
 #pragma unroll
       for (int ks = 0; ks < kTile / 16; ++ks) {
         const uint32_t p_offset = (ks / 4) * kPanelBytes + (ks % 4) * 32;
@@ -159,9 +176,9 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
                   ks > 0 ? 1u : 0u);
       }
       umma_commit(smem_u32(&o_full));
-      umma_commit(smem_u32(&kv_empty[j & 1]));  // K_j and V_j are free once these MMAs retire
+      umma_commit(smem_u32(&v_empty));  // V_j is free once these MMAs retire
       if (j + 1 < n_tiles) {
-        if (!mbarrier_wait_bounded(smem_u32(&kv_full[(j + 1) & 1]), ((j + 1) >> 1) & 1)) {
+        if (!mbarrier_wait_bounded(smem_u32(&k_full[(j + 1) & 1]), ((j + 1) >> 1) & 1)) {
           ok = false;
           break;
         }
@@ -191,9 +208,14 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
       for (int c0 = 0; c0 < kTile; c0 += 32) {
         float s[32];
         tmem_load_32x32(lane_base + kSColumn + c0, s);
+        if (diagonal) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (!diagonal || c0 + i <= row) row_max = fmaxf(row_max, s[i]);
+          for (int i = 0; i < 32; ++i)
+            if (c0 + i <= row) row_max = fmaxf(row_max, s[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) row_max = fmaxf(row_max, s[i]);
+        }
       }
       const float m_new = fmaxf(m_run, row_max * p.scale_log2);  // key 0 is never masked
       const float alpha = exp2_fast(m_run - m_new);              // exp2(-inf) = 0 at the first tile
@@ -203,14 +225,24 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
         float s[32];
         tmem_load_32x32(lane_base + kSColumn + c0, s);
         uint32_t packed[16];
+        if (diagonal) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = exp2_fast(fmaf(s[i], p.scale_log2, -m_new));
-          float p1 = exp2_fast(fmaf(s[i + 1], p.scale_log2, -m_new));
-          if (diagonal && c0 + i > row) p0 = 0.0f;
-          if (diagonal && c0 + i + 1 > row) p1 = 0.0f;
-          sum += p0 + p1;
-          packed[i / 2] = pack_bf16x2(p0, p1);
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = exp2_fast(fmaf(s[i], p.scale_log2, -m_new));
+            float p1 = exp2_fast(fmaf(s[i + 1], p.scale_log2, -m_new));
+            if (c0 + i > row) p0 = 0.0f;
+            if (c0 + i + 1 > row) p1 = 0.0f;
+            sum += p0 + p1;
+            packed[i / 2] = pack_bf16x2(p0, p1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = exp2_fast(fmaf(s[i], p.scale_log2, -m_new));
+            const float p1 = exp2_fast(fmaf(s[i + 1], p.scale_log2, -m_new));
+            sum += p0 + p1;
+            packed[i / 2] = pack_bf16x2(p0, p1);
+          }
         }
         // K-major A operand: panel = 64 keys, row = query, 16-byte chunks XOR-swizzled by row % 8
         const uint32_t panel = p_smem + (c0 / 64) * kPanelBytes + row * 128;
@@ -263,6 +295,7 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
   if (warp == 5)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns)
                  : "memory");
+  trace.mark(1);
 }
 
 }  // namespace
@@ -302,12 +335,15 @@ int prefill_attention_tcgen05(const void* query, const void* key, const void* va
   p.scale_log2 = static_cast<float>(scale) * kLog2e;
   dim3 grid(static_cast<unsigned>(q_tiles), static_cast<unsigned>(q_heads),
             static_cast<unsigned>(batch));
-  // Q + 2 stages of K|V + P
-  const int smem = static_cast<int>(head_dim) * kTile * 2 * (1 + 2 * kKvStages) + kTile * kTile * 2;
+  // Q + two K tiles + one V tile + P
+  const int smem = static_cast<int>(head_dim) * kTile * 2 * (2 + kKStages) + kTile * kTile * 2;
   if (head_dim == 64) {
     auto kernel = prefill_attention_tcgen05_kernel<64>;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return B200_ERR_LAUNCH;
+    // two CTAs per SM need the largest shared-memory carve-out
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
     kernel<<<grid, kThreads, smem, stream>>>(p, q_map, k_map, v_map);
   } else {
     auto kernel = prefill_attention_tcgen05_kernel<128>;

@@ -426,6 +426,36 @@ def test_prefill_attention_config3_shapes(tokens):
     close(masked, ref, BF16_TOL)
 
 
+@pytest.mark.parametrize("layout", ["token_major", "head_major"])
+@pytest.mark.parametrize("batch,tokens,hq,hkv,d", [(2, 1, 14, 2, 64), (2, 127, 14, 2, 64),
+                                                    (3, 129, 14, 2, 64), (1, 700, 4, 4, 64),
+                                                    (2, 333, 28, 4, 128), (1, 1024, 8, 1, 128)])
+def test_prefill_attention_tensor_memory_path(batch, tokens, hq, hkv, d, layout, monkeypatch):
+    """Causal-proved bf16 calls in the fast mode run on tcgen05 (S and O tiles in tensor memory,
+    TMA boxes of 128 tokens): token counts around and off the 128-row tile, one token, several
+    key tiles, both head dims, inputs as views of [B, T, H, D] (what the graphs produce) and as
+    plain [B, H, T, D]. The oracle and the warp-level kernel must both agree."""
+    g = torch.Generator().manual_seed(tokens + d)
+    if layout == "token_major":
+        q = torch.randn(batch, tokens, hq, d, generator=g).bfloat16().transpose(1, 2)
+        k = torch.randn(batch, tokens, hkv, d, generator=g).bfloat16().transpose(1, 2)
+        v = torch.randn(batch, tokens, hkv, d, generator=g).bfloat16().transpose(1, 2)
+    else:
+        q = torch.randn(batch, hq, tokens, d, generator=g).bfloat16()
+        k = torch.randn(batch, hkv, tokens, d, generator=g).bfloat16()
+        v = torch.randn(batch, hkv, tokens, d, generator=g).bfloat16()
+    scale = d ** -0.5
+    ref = serve_ops.prefill_attention(q, k, v, None, groups=hq // hkv, scale=scale, causal=True)
+    out = b200.b200_prefill_attention(q.cuda(), k.cuda(), v.cuda(), None, scale=scale, causal=True)
+    assert out.transpose(1, 2).is_contiguous()
+    close(out, ref, BF16_TOL)
+    monkeypatch.setenv("B200_PREFILL_ATTENTION_PATH", "mma.sync")
+    warp_level = b200.b200_prefill_attention(q.cuda(), k.cuda(), v.cuda(), None, scale=scale,
+                                             causal=True)
+    close(out, warp_level.float().cpu(), 1e-2)
+    kernels.runtime().check_status()
+
+
 # -------------------------------------------------------------------------- linear ----
 @pytest.mark.parametrize("name", list(cases.LINEAR))
 def test_linear_golden(name, golden_ops):
