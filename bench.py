@@ -302,6 +302,13 @@ def b200_arm(args, config):
         engine.load_context(torch.full((args.batch,), args.context),
                             next_ids=torch.randint(0, config.vocab_size, (args.batch,)))
     torch.cuda.synchronize()
+    # the split plan of decode attention comes from the measured profile that ships with the
+    # package (profile-guided dispatch), resolved with this engine's batch and context bound
+    from llm_compiler_b200.dispatch_plan import DispatchCostModel
+    if args.split_tokens == 0:
+        decision = engine.use_dispatch_profile(DispatchCostModel.packaged(), capacity)
+    else:
+        decision = None
     engine.capture()
     gather = TokenGather(args.batch * world, device=device) if world > 1 else None
 
@@ -382,6 +389,9 @@ def b200_arm(args, config):
                 "ms_per_step": e2e_s / steps * 1e3},
         "gpu_launches": engine.kernels_per_step * steps,
         "kernels_per_step": engine.kernels_per_step,
+        "dispatch": None if decision is None else {
+            "op": "decode_attention", "variant": decision.variant, "source": decision.source,
+            "profile_value": decision.profile_value},
         "clocks": clocks.summary(),
         "roofline": roofline,
         "step_bandwidth": {"algorithmic_gb_per_step": step_bytes / 1e9,

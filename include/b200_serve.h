@@ -57,6 +57,8 @@ extern "C" {
 #define B200_LAUNCH_PROGRAMMATIC 1      /* decode-chain kernels use programmatic dependent launch */
 #define B200_LAUNCH_CONSTANT_WEIGHTS 2  /* weight operands are written by no kernel in flight  */
 #define B200_LAUNCH_STABLE_KV_PREFIX 4  /* lengths[] and KV rows < lengths[b] - 1 likewise       */
+#define B200_LAUNCH_LINEAR_WARP_LEVEL 8    /* b200_linear: warp-level kernel, not tcgen05       */
+#define B200_LAUNCH_PREFILL_WARP_LEVEL 16  /* b200_prefill_attention: warp-level kernel         */
 
 /* Process-wide launch mode of the decode-chain kernels (embedding, rope table, rms_norm fast
  * path, linear on tcgen05, linear_partial, the two reduce_* consumers, decode attention,
@@ -70,7 +72,9 @@ extern "C" {
  * read lengths[] and request the KV rows below lengths[b] - 1 before the wait: valid when the
  * only KV row written since the previous synchronisation point is the newest one (row
  * lengths[b] - 1, stored by the kernel just before attention), as in a decode step whose
- * lengths were advanced at the end of the step before. Returns the previous flags, or
+ * lengths were advanced at the end of the step before. The two *_WARP_LEVEL flags pick the
+ * kernel variant a profile-guided dispatch plan chose (the reference resolves its plan to a
+ * backend per call, cost_model.py:220-245). Returns the previous flags, or
  * B200_ERR_BAD_ARGUMENT for unknown bits. Default 0. */
 int b200_set_launch_mode(int flags);
 int b200_get_launch_mode(void);

@@ -28,6 +28,8 @@ STATUS_WAIT_TIMEOUT = 16
 LAUNCH_PROGRAMMATIC = 1
 LAUNCH_CONSTANT_WEIGHTS = 2
 LAUNCH_STABLE_KV_PREFIX = 4
+LAUNCH_LINEAR_WARP_LEVEL = 8
+LAUNCH_PREFILL_WARP_LEVEL = 16
 
 ERR_BAD_ARGUMENT, ERR_UNSUPPORTED, ERR_ALIGNMENT = -1, -2, -3
 ERR_WORKSPACE, ERR_LAUNCH, ERR_TOO_LARGE = -4, -5, -6

@@ -14,7 +14,8 @@ extern "C" int b200_abi_version(void) { return 100; }
 
 extern "C" int b200_set_launch_mode(int flags) {
   if ((flags & ~(B200_LAUNCH_PROGRAMMATIC | B200_LAUNCH_CONSTANT_WEIGHTS |
-                 B200_LAUNCH_STABLE_KV_PREFIX)) != 0)
+                 B200_LAUNCH_STABLE_KV_PREFIX | B200_LAUNCH_LINEAR_WARP_LEVEL |
+                 B200_LAUNCH_PREFILL_WARP_LEVEL)) != 0)
     return B200_ERR_BAD_ARGUMENT;
   return b200::g_launch_mode.exchange(flags, std::memory_order_relaxed);
 }

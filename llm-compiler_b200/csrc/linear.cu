@@ -344,9 +344,11 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
 using namespace b200;
 
 // The tcgen05 path takes every problem it can fill the GPU with (it declines decode-size M
-// with few N tiles, which need split-K); B200_LINEAR_PATH=mma.sync forces the warp-level kernel.
+// with few N tiles, which need split-K); B200_LINEAR_PATH=mma.sync or the launch-mode flag
+// B200_LAUNCH_LINEAR_WARP_LEVEL (what a dispatch plan sets) force the warp-level kernel.
 static bool use_tcgen05(int64_t m) {
   (void)m;
+  if ((launch_mode() & B200_LAUNCH_LINEAR_WARP_LEVEL) != 0) return false;
   const char* value = getenv("B200_LINEAR_PATH");
   return value == nullptr || strcmp(value, "mma.sync") != 0;
 }

@@ -308,6 +308,7 @@ int prefill_attention_tcgen05(const void* query, const void* key, const void* va
                               int64_t head_dim, const int64_t query_strides[4],
                               const int64_t key_strides[4], const int64_t value_strides[4],
                               double scale, int32_t* status, cudaStream_t stream) {
+  if ((launch_mode() & B200_LAUNCH_PREFILL_WARP_LEVEL) != 0) return B200_ERR_UNSUPPORTED;
   const char* path = getenv("B200_PREFILL_ATTENTION_PATH");
   if (path != nullptr && strcmp(path, "mma.sync") == 0) return B200_ERR_UNSUPPORTED;
   if (head_dim != 64 && head_dim != 128) return B200_ERR_UNSUPPORTED;

@@ -22,6 +22,7 @@ partitioning across GPUs is in serving.py.
 
 from __future__ import annotations
 
+import math
 import os
 from typing import Dict, Optional
 
@@ -260,6 +261,26 @@ class Qwen2Engine:
         # all slot lengths, the positions row and the attention-length row move together
         kernels.b200_advance_lengths(self.state._length_arena, 1, self.capacity + 1)
         self.kernels_per_step = kernels.launch_count(self.device) - before
+
+    def use_dispatch_profile(self, cost_model, context_bound: int):
+        """Takes the decode-attention split size for this engine's batch and a context of up to
+        `context_bound` tokens from a measured profile (dispatch_plan.DispatchCostModel). Call
+        before capture(): the split is baked into the captured launches. Returns the decision."""
+
+        from .dispatch_plan import resolve_dispatch_plan, split_tokens_of
+
+        cfg = self.config
+        batches = sorted({dict(e.key)["batch"] for e in cost_model.entries
+                          if e.op == "decode_attention"})
+        if not batches:
+            return resolve_dispatch_plan(None, context_bound)
+        nearest = min(batches, key=lambda b: abs(math.log(b / self.batch)))
+        plan = cost_model.plan_attribute("decode_attention", batch=nearest, q_heads=cfg.num_heads,
+                                         kv_heads=cfg.num_kv_heads, head_dim=cfg.head_dim,
+                                         dtype=str(self.dtype))
+        decision = resolve_dispatch_plan(plan, context_bound)
+        self.split_tokens = split_tokens_of(decision.variant)
+        return decision
 
     def capture(self) -> None:
         """Captures one decode step in a CUDA graph. A warm-up step runs first so that every

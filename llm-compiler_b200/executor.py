@@ -12,12 +12,14 @@ capture it in a CUDA graph once shapes are fixed.
 
 from __future__ import annotations
 
+import math
 from dataclasses import dataclass
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from . import kernels
+from .dispatch_plan import resolve_dispatch_plan, split_tokens_of
 from .kernel_ir import decode_attribute, require_full_lowering, value_dtype, value_rank
 from .kv_state import ExecutionError, PreallocatedKVCacheState
 
@@ -180,8 +182,25 @@ class B200Executor:
             round_before_weight=bool(attributes.get("round_before_weight", False)),
             numerical_mode=mode)
 
-    @staticmethod
-    def _linear(operands, attributes, environment):
+    def _decide(self, op: str, attributes, value: int, plan_key: str = "lowering_plan",
+                family_key: Optional[int] = None):
+        """Resolves the operation's profile-guided plan with the run-time value of its bucketed
+        dimension and records the decision in lowering_trace (the reference records
+        backend / source / rows for serve.rms_norm, backends/triton_executor.py:299-308)."""
+
+        plan = attributes.get(plan_key)
+        if plan_key == "lowering_plans" and isinstance(plan, dict):
+            # one plan per profiled batch size: the nearest one on a log scale
+            sizes = [int(k) for k in plan if k.isdigit()]
+            plan = plan[str(min(sizes, key=lambda b: abs(math.log(b / max(family_key, 1)))))] \
+                if sizes and family_key else None
+        decision = resolve_dispatch_plan(plan, max(int(value), 1))
+        self.lowering_trace.append({"backend": "b200", "op": op, "source": decision.source,
+                                    "variant": decision.variant, "value": int(value),
+                                    "profile_value": decision.profile_value})
+        return decision.variant
+
+    def _linear(self, operands, attributes, environment):
         has_bias = bool(attributes.get("has_bias"))
         epilogue = attributes.get("epilogue") or "none"
         expected = 2 + int(has_bias) + int(epilogue == "residual")
@@ -190,7 +209,10 @@ class B200Executor:
         tensor, weight = operands[0], operands[1]
         bias = operands[2] if has_bias else None
         residual = operands[-1] if epilogue == "residual" else None
-        return kernels.b200_linear(tensor, weight, bias, residual=residual, epilogue=epilogue)
+        variant = self._decide("linear", attributes, tensor.numel() // tensor.shape[-1]) \
+            if "lowering_plan" in attributes else None
+        with kernels.kernel_variants(linear=variant):
+            return kernels.b200_linear(tensor, weight, bias, residual=residual, epilogue=epilogue)
 
     @staticmethod
     def _rope(operands, attributes, environment):
@@ -206,27 +228,35 @@ class B200Executor:
         dtype = _DTYPES[attributes["dtype"]]
         return kernels.b200_rope_table(positions, inv_freq.reshape(-1), dtype)
 
-    @staticmethod
-    def _prefill_attention(operands, attributes, environment):
+    def _prefill_attention(self, operands, attributes, environment):
         if len(operands) != 4:
             raise ExecutionError("prefill_attention takes q, k, v and mask")
         query, key, value, mask = operands
         if query.shape[1] != key.shape[1] * int(attributes["groups"]):
             raise ExecutionError("prefill_attention: GQA groups mismatch")
-        return kernels.b200_prefill_attention(
-            query, key, value, mask, scale=float(attributes["scale"]),
-            causal=attributes.get("causal") is True,
-            numerical_mode=attributes.get("numerical_mode", "fast"))
+        variant = self._decide("prefill_attention", attributes, query.shape[2]) \
+            if "lowering_plan" in attributes else None
+        with kernels.kernel_variants(prefill_attention=variant):
+            return kernels.b200_prefill_attention(
+                query, key, value, mask, scale=float(attributes["scale"]),
+                causal=attributes.get("causal") is True,
+                numerical_mode=attributes.get("numerical_mode", "fast"))
 
-    @staticmethod
-    def _decode_attention(operands, attributes, environment):
+    def _decode_attention(self, operands, attributes, environment):
         if len(operands) != 3:
             raise ExecutionError("decode_attention takes state, query and mask")
         state = _as_state(operands[0])
+        options = {}
+        if "lowering_plans" in attributes:
+            # bucketed by the context bound the host knows: the mask length (or the capacity)
+            bound = operands[2].shape[-1] if operands[2] is not None else state.capacity
+            variant = self._decide("decode_attention", attributes, bound, "lowering_plans",
+                                   operands[1].shape[0])
+            options["split_tokens"] = split_tokens_of(variant)
         return state.decode_attention(
             int(attributes.get("slot", 0)), operands[1], operands[2],
             groups=int(attributes["groups"]), scale=float(attributes["scale"]),
-            numerical_mode=attributes.get("numerical_mode", "fast"))
+            numerical_mode=attributes.get("numerical_mode", "fast"), **options)
 
     @staticmethod
     def _kv_store(operands, attributes, environment):

@@ -475,6 +475,95 @@ def lower_to_b200(module, *, numerical_mode: Optional[str] = None,
                           removed_casts, removed_dead, analyze_lowering_coverage(module))
 
 
+def static_dims(value) -> Optional[List[Optional[int]]]:
+    """Dimensions of a tensor-typed value: ints where static, None where symbolic."""
+
+    shape = getattr(value.type, "shape", None)
+    if shape is not None:
+        return [getattr(dim, "value", None) if not isinstance(dim, int) else dim for dim in shape]
+    match = _TENSOR_TYPE.match(str(value.type))
+    if not match:
+        return None
+    parts, depth, current = [], 0, ""
+    for char in match.group(1):
+        if char == "<":
+            depth += 1
+        elif char == ">":
+            depth -= 1
+        if char == "x" and depth == 0:
+            parts.append(current)
+            current = ""
+        else:
+            current += char
+    parts.append(current)
+    return [int(part) if part.strip().isdigit() else None for part in parts]
+
+
+_PLAN_DTYPES = {"bf16": "bf16", "f32": "fp32", "f16": "fp16"}
+
+
+def select_dispatch_plans(module, cost_model) -> Dict[str, Any]:
+    """Writes profile-guided `lowering_plan` attributes onto the lowered operations that have
+    kernel variants, the way the reference's SelectRMSNormLoweringPass does for serve.rms_norm
+    (passes/lowering_selection.py:24-71): linear by (k, n, dtype), bucketed by rows at run time;
+    prefill attention by the head layout, bucketed by tokens; decode attention by the head
+    layout, one plan per profiled batch size (`lowering_plans`), bucketed by context length.
+    Returns the pass statistics. `cost_model` is a dispatch_plan.DispatchCostModel."""
+
+    from .dispatch_plan import OPERATORS
+
+    planned = missing = 0
+    chosen: Counter = Counter()
+    changed = False
+
+    def attach(operation, name: str, plan) -> None:
+        nonlocal planned, missing, changed
+        variants = plan["variants"] if "variants" in plan else \
+            [v for family in plan.values() for v in family["variants"]]
+        if not variants:
+            missing += 1
+            return
+        planned += 1
+        chosen.update(variant["variant"] for variant in variants)
+        if operation.attributes.get(name) != plan:
+            operation.attributes[name] = plan
+            changed = True
+
+    for function in module.functions:
+        for operation in function.block.operations:
+            if operation.name == "kernel.b200.linear":
+                dtype = _PLAN_DTYPES.get(value_dtype(operation.results[0]) or "")
+                k, n = operation.attributes.get("input_features"), operation.attributes.get("output_features")
+                if dtype is None or not isinstance(k, int) or not isinstance(n, int):
+                    missing += 1
+                    continue
+                attach(operation, "lowering_plan", cost_model.plan_attribute("linear", k=k, n=n, dtype=dtype))
+            elif operation.name in ("kernel.b200.prefill_attention", "kernel.b200.decode_attention"):
+                decode = operation.name.endswith("decode_attention")
+                query = operation.operands[1] if decode else operation.operands[0]
+                dims, dtype = static_dims(query), _PLAN_DTYPES.get(value_dtype(query) or "")
+                groups = operation.attributes.get("groups")
+                if dims is None or len(dims) != 4 or dims[1] is None or dims[3] is None or \
+                        dtype is None or not isinstance(groups, int) or groups <= 0:
+                    missing += 1
+                    continue
+                layout = {"q_heads": dims[1], "kv_heads": dims[1] // groups, "head_dim": dims[3],
+                          "dtype": dtype}
+                if not decode:
+                    attach(operation, "lowering_plan",
+                           cost_model.plan_attribute("prefill_attention", **layout))
+                    continue
+                batches = sorted({dict(entry.key)["batch"] for entry in cost_model.entries
+                                  if entry.op == "decode_attention" and
+                                  all(dict(entry.key)[name] == layout[name] for name in layout)})
+                attach(operation, "lowering_plans",
+                       {str(batch): cost_model.plan_attribute("decode_attention", batch=batch, **layout)
+                        for batch in batches} or {"none": {"variants": []}})
+    assert set(OPERATORS) >= {"linear", "prefill_attention", "decode_attention"}
+    return {"changed": changed, "planned_operations": planned, "missing_profile": missing,
+            "variants": dict(sorted(chosen.items()))}
+
+
 def verify_module(module) -> None:
     """SSA sanity: unique definitions, operands defined before use (ir.py:220-260)."""
 

@@ -122,6 +122,29 @@ def launch_mode(*, programmatic: bool, constant_weights: bool = False,
         library.b200_set_launch_mode(previous)
 
 
+@contextlib.contextmanager
+def kernel_variants(*, linear: Optional[str] = None, prefill_attention: Optional[str] = None):
+    """Scope in which b200_linear / b200_prefill_attention use the named variant ("tcgen05" or
+    "mma.sync"; None leaves the library's own choice): how a resolved dispatch plan reaches the
+    library. Other launch-mode flags are kept."""
+
+    for name, value in (("linear", linear), ("prefill_attention", prefill_attention)):
+        if value not in (None, "tcgen05", "mma.sync"):
+            raise ValueError(f"unknown {name} variant {value!r}")
+    library = _lib.load()
+    previous = library.b200_get_launch_mode()
+    flags = previous & ~(_lib.LAUNCH_LINEAR_WARP_LEVEL | _lib.LAUNCH_PREFILL_WARP_LEVEL)
+    if linear == "mma.sync":
+        flags |= _lib.LAUNCH_LINEAR_WARP_LEVEL
+    if prefill_attention == "mma.sync":
+        flags |= _lib.LAUNCH_PREFILL_WARP_LEVEL
+    library.b200_set_launch_mode(flags)
+    try:
+        yield
+    finally:
+        library.b200_set_launch_mode(previous)
+
+
 def _require_cuda(*tensors: torch.Tensor) -> torch.device:
     device = None
     for tensor in tensors:

@@ -6,6 +6,7 @@
     python llm-compiler_b200/microbench.py linear --m 64 --k 896 --n 9728 --epilogue swiglu
     python llm-compiler_b200/microbench.py kv_store --batch 16 --tokens 4096
     python llm-compiler_b200/microbench.py timeline --batch 64 --length 4096   (trace build only)
+    python llm-compiler_b200/microbench.py profile --output dispatch_profile.json
 
 Timing: CUDA events on the launching stream around `--iters` launches after `--warmup`
 launches, rotating over enough independent buffer sets that one round exceeds the 126 MB L2
@@ -263,10 +264,66 @@ def timeline_case(args):
             "records": len(rows)}
 
 
+def profile_case(args):
+    """Measures the variants the dispatch plan chooses between and writes a schema-version-1
+    profile (dispatch_plan.py): decode attention split sizes by (batch, context length), prefill
+    attention and linear kernel paths by tokens / rows. All sequences at full length."""
+
+    import copy
+
+    rows = []
+    probe = copy.copy(args)
+    probe.full_length, probe.no_graph, probe.general_mask = True, False, False
+    probe.warmup, probe.iters = max(3, args.warmup // 2), max(10, args.iters // 4)
+    layout = {"q_heads": args.q_heads, "kv_heads": args.kv_heads, "head_dim": args.head_dim,
+              "dtype": "bf16"}
+    for batch in (1, 8, 64, 256):
+        for length in (256, 1024, 4096, 16384):
+            if batch * length > 64 * 16384:
+                continue
+            costs = {}
+            for split in (0, 512, 1024, 2048, 4096):
+                if split > length:
+                    continue
+                probe.split_tokens = split
+                costs[f"split:{split}"] = decode_attention_case(probe, batch, length)["us"]
+            rows.append({"op": "decode_attention", "batch": batch, **layout, "length": length,
+                         "variants_us": costs})
+            print(json.dumps(rows[-1]), flush=True)
+    for tokens in (128, 512, 2048, 4096):
+        probe.batch, probe.tokens = 4, tokens
+        costs = {}
+        for variant in ("tcgen05", "mma.sync"):
+            with kernels.kernel_variants(prefill_attention=variant):
+                costs[variant] = prefill_attention_case(probe)["us"]
+        rows.append({"op": "prefill_attention", **layout, "tokens": tokens, "variants_us": costs})
+        print(json.dumps(rows[-1]), flush=True)
+    probe.epilogue = "none"
+    for k, n in ((896, 1152), (896, 9728), (4864, 896)):
+        for m in (16, 64, 512, 4096):
+            probe.m, probe.k, probe.n = m, k, n
+            costs = {}
+            for variant in ("tcgen05", "mma.sync"):
+                with kernels.kernel_variants(linear=variant):
+                    costs[variant] = linear_case(probe)["us"]
+            rows.append({"op": "linear", "k": k, "n": n, "dtype": "bf16", "m": m, "variants_us": costs})
+            print(json.dumps(rows[-1]), flush=True)
+    properties = torch.cuda.get_device_properties(0)
+    payload = {"schema_version": 1,
+               "target": {"device_name": properties.name,
+                          "compute_capability": f"{properties.major}.{properties.minor}",
+                          "torch_version": torch.__version__,
+                          "library_version": str(b200._lib.load().b200_abi_version())},
+               "results": rows}
+    Path(args.output).write_text(json.dumps(payload, indent=1) + "\n", encoding="utf-8")
+    return {"op": "profile", "rows": len(rows), "output": args.output}
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("op", choices=["decode_attention", "prefill_attention", "kv_store", "linear",
-                                       "rms_norm", "timeline"])
+                                       "rms_norm", "timeline", "profile"])
+    parser.add_argument("--output", default="dispatch_profile.json", help="profile: file to write")
     parser.add_argument("--launches", type=int, default=40, help="timeline: launches to print")
     parser.add_argument("--batch", type=int, default=64)
     parser.add_argument("--length", type=int, default=4096)
@@ -305,6 +362,8 @@ def main():
         print(json.dumps(linear_case(args)))
     elif args.op == "timeline":
         print(json.dumps(timeline_case(args)))
+    elif args.op == "profile":
+        print(json.dumps(profile_case(args)))
     else:
         print(json.dumps(rms_norm_case(args)))
     kernels.runtime().check_status()

@@ -132,3 +132,56 @@ def test_executor_errors_mirror_the_reference(golden_tiny):
                   "inv_freq": q2.inverse_frequency(config, "cuda")}
     with pytest.raises(ExecutionError, match="CUDA"):
         executor.run(decode, bind_arguments(decode.functions[0], weights, cpu_inputs))
+
+
+def test_dispatch_plans_are_resolved_per_call_and_recorded(golden_tiny):
+    """The graphs with profile-guided plans attached (select_dispatch_plans): every planned op
+    resolves its plan with the run-time rows / tokens / context bound, the decision lands in
+    lowering_trace, and the results are those of the reference executor whatever variant the
+    synthetic profile makes it pick."""
+    from llm_compiler_b200.dispatch_plan import DispatchCostModel
+
+    gold = golden_tiny["fp32"]
+    config = q2.Qwen2Config(**gold["config"])
+    weights = {k: v.cuda() for k, v in q2.make_weights(config, seed=0).items()}
+    inv_freq = q2.inverse_frequency(config, "cuda")
+    batch, prompt = gold["batch"], gold["prompt"]
+    layout = {"q_heads": config.num_heads, "kv_heads": config.num_kv_heads,
+              "head_dim": config.head_dim, "dtype": "fp32"}
+    rows = [{"op": "decode_attention", "batch": 2, **layout, "length": 8,
+             "variants_us": {"split:0": 5.0, "split:32": 4.0}},
+            {"op": "decode_attention", "batch": 64, **layout, "length": 8,
+             "variants_us": {"split:0": 5.0, "split:64": 9.0}},
+            {"op": "prefill_attention", **layout, "tokens": 4, "variants_us": {"tcgen05": 9.0, "mma.sync": 7.0}}]
+    for n in (config.hidden_size, config.intermediate_size, config.vocab_size,
+              config.num_kv_heads * config.head_dim):
+        for k in (config.hidden_size, config.intermediate_size):
+            rows.append({"op": "linear", "k": k, "n": n, "dtype": "fp32", "m": 8,
+                         "variants_us": {"tcgen05": 3.0, "mma.sync": 2.0}})
+    model = DispatchCostModel.from_dict(rows)
+    executor = B200Executor(strict=True)
+    prefill = lowered("prefill", "fast")
+    assert ir.select_dispatch_plans(prefill, model)["planned_operations"] > 0
+    result = executor.run(prefill, bind_arguments(prefill.functions[0], weights, {
+        "input_ids": gold["input_ids"].cuda(), "attention_mask": causal_mask(batch, prompt),
+        "position_ids": torch.arange(prompt).repeat(batch, 1).cuda(), "inv_freq": inv_freq}))
+    logits, state = result.outputs
+    torch.testing.assert_close(logits.cpu(), gold["prefill_logits"], rtol=1e-4, atol=1e-4)
+    decode = lowered("decode", "fast")
+    assert ir.select_dispatch_plans(decode, model)["planned_operations"] > 0
+    logits, state = executor.run(decode, bind_arguments(decode.functions[0], weights, {
+        "input_ids": gold["tokens"][:, 0].view(batch, 1).cuda(),
+        "attention_mask": torch.zeros(batch, 1, 1, prompt + 1, device="cuda"),
+        "position_ids": torch.full((batch, 1), prompt, device="cuda"),
+        "kv_state": state, "inv_freq": inv_freq})).outputs
+    torch.testing.assert_close(logits[:, 0].cpu(), gold["decode_logits"][0], rtol=1e-4, atol=1e-4)
+    planned = [entry for entry in executor.lowering_trace if "variant" in entry]
+    by_op = {}
+    for entry in planned:
+        by_op.setdefault(entry["op"], []).append(entry)
+    assert set(by_op) == {"linear", "prefill_attention", "decode_attention"}
+    assert all(e["source"] == "profile" and e["variant"] == "mma.sync" for e in by_op["linear"])
+    assert all(e["variant"] == "mma.sync" and e["value"] == prompt for e in by_op["prefill_attention"])
+    # batch 3 is nearer to the batch-2 plan than to the batch-64 one on a log scale
+    assert all(e["variant"] == "split:32" and e["value"] == prompt + 1 for e in by_op["decode_attention"])
+    state.check()
