@@ -52,6 +52,10 @@ RESULT_STREAM = sys.stdout  # main() replaces it with a private copy of the proc
 NCU_TRAFFIC_BYTES, NCU_TRAFFIC_TOKENS = 139_171_584, 262_144
 
 
+def metric_name(args):
+    return METRIC if args.model == "qwen2-0.5b" else METRIC.replace("qwen2_0.5b", "qwen2_7b")
+
+
 def parse_args():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -65,18 +69,27 @@ def parse_args():
     parser.add_argument("--context-source", default="prefill", choices=["prefill", "synthetic"])
     parser.add_argument("--cpu-sample-batch", type=int, default=8)
     parser.add_argument("--skip-cpu-baseline", action="store_true")
+    parser.add_argument("--model", default="qwen2-0.5b", choices=["qwen2-0.5b", "qwen2-7b"],
+                        help="architecture (the headline metric is quoted on qwen2-0.5b)")
+    parser.add_argument("--context-min", type=int, default=0,
+                        help="with --context-source synthetic: per-sequence contexts uniform in "
+                             "[context-min, context] instead of all at --context")
     return parser.parse_args()
 
 
 def workload_config(args, n_gpus):
     return {
-        "workload": f"qwen2-0.5b-architecture greedy decode, batch {args.batch}/GPU, context "
-                    f"{args.context}, bf16, CUDA-graph step, KV from a {args.context_source} prompt",
+        "workload": f"{args.model}-architecture greedy decode, batch {args.batch}/GPU, context "
+                    + (f"uniform in [{args.context_min}, {args.context}]" if args.context_min > 0
+                       else f"{args.context}")
+                    + f", bf16, CUDA-graph step, KV from a {args.context_source} prompt",
         "global_batch": args.batch * n_gpus,
         "context": args.context,
-        "layers": args.layers or 24,
+        "layers": args.layers or (24 if args.model == "qwen2-0.5b" else 28),
         "parallelism": f"replicas x{n_gpus} (batch-partitioned, NCCL all-gather of token ids)",
-        "l2": "inputs larger than L2 (0.99 GB weights + 3.2 GB KV read per step)",
+        "l2": "inputs larger than L2 (0.99 GB weights + 3.2 GB KV read per step)"
+              if args.model == "qwen2-0.5b" and args.context == CONTEXT and args.batch == BATCH_PER_GPU
+              else "inputs larger than L2 (all weights and every valid KV row are read once per step)",
     }
 
 
@@ -184,7 +197,7 @@ def reference_arm(args, config):
     sample = (f"{args.cpu_sample_batch} of the {args.batch} sequences, all {config.num_layers} "
               f"layers, context {args.context}, median of {steps} steps after {warmup} warm-up")
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "impl": "reference", "metric": metric_name(args), "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": workload_config(args, args.gpus),
@@ -245,7 +258,9 @@ def attention_roofline(engine, lengths_sum, rounds):
     stop.record()
     torch.cuda.synchronize()
     per_launch_s = start.elapsed_time(stop) * 1e-3 / (rounds * config.num_layers)
-    bytes_per_launch = 512 * lengths_sum + 3592 * batch
+    # K and V of every valid token once, q in and o out once, the lengths
+    bytes_per_launch = 4 * config.num_kv_heads * config.head_dim * lengths_sum + \
+        (4 * config.num_heads * config.head_dim + 8) * batch
     return bytes_per_launch, per_launch_s
 
 
@@ -299,8 +314,11 @@ def b200_arm(args, config):
         for layer in range(config.num_layers):
             engine.state.keys[layer].normal_(generator=generator)
             engine.state.values[layer].normal_(generator=generator)
-        engine.load_context(torch.full((args.batch,), args.context),
-                            next_ids=torch.randint(0, config.vocab_size, (args.batch,)))
+        contexts = torch.full((args.batch,), args.context)
+        if args.context_min > 0:
+            contexts = torch.randint(args.context_min, args.context + 1, (args.batch,),
+                                     generator=torch.Generator().manual_seed(rank))
+        engine.load_context(contexts, next_ids=torch.randint(0, config.vocab_size, (args.batch,)))
     torch.cuda.synchronize()
     # the split plan of decode attention comes from the measured profile that ships with the
     # package (profile-guided dispatch), resolved with this engine's batch and context bound
@@ -310,6 +328,7 @@ def b200_arm(args, config):
     else:
         decision = None
     engine.capture()
+    step_tokens_read = int(engine.attention_lengths.sum().item())  # KV rows one step reads, at the start
     gather = TokenGather(args.batch * world, device=device) if world > 1 else None
 
     def run_steps(count):
@@ -368,7 +387,7 @@ def b200_arm(args, config):
                         "peak": peak, "peak_source": f"{peak_kind} copy bandwidth", "unit": "GB/s",
                         "frac": achieved / peak, "frac_of_nominal_8000": achieved / 8000.0,
                         "traffic": NCU_TRAFFIC_BYTES * lengths_sum / NCU_TRAFFIC_TOKENS
-                        if args.batch == BATCH_PER_GPU else None,
+                        if args.batch == BATCH_PER_GPU and args.model == "qwen2-0.5b" else None,
                         "algorithmic_bytes_per_launch": bytes_per_launch,
                         "us_per_launch": launch_s * 1e6}
     engine.state.check()
@@ -378,9 +397,10 @@ def b200_arm(args, config):
             dist.destroy_process_group()
         return
     total_tokens = args.batch * world * steps
-    step_bytes = 2 * q2.parameter_count(config) + 12288 * (args.context + 1) * args.batch
+    kv_bytes_per_token = config.num_layers * 4 * config.num_kv_heads * config.head_dim
+    step_bytes = 2 * q2.parameter_count(config) + kv_bytes_per_token * step_tokens_read
     result = {
-        "metric": METRIC, "value": total_tokens / device_s, "unit": UNIT, "n_gpus": n_gpus,
+        "metric": metric_name(args), "value": total_tokens / device_s, "unit": UNIT, "n_gpus": n_gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": device_s / steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": workload_config(args, n_gpus),
@@ -423,7 +443,7 @@ def main():
     os.dup2(2, 1)
     from llm_compiler_b200 import qwen2 as q2
 
-    config = q2.QWEN2_0_5B
+    config = q2.QWEN2_0_5B if args.model == "qwen2-0.5b" else q2.QWEN2_7B
     if args.layers:
         config = q2.Qwen2Config(**{**config.__dict__, "num_layers": args.layers})
     if args.impl == "reference":
