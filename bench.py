@@ -49,7 +49,7 @@ RESULT_STREAM = sys.stdout  # main() replaces it with a private copy of the proc
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch over 64 x 4096 =
 # 262144 tokens, from the ncu capture summarised in profiles/decode_attention_b64_l4096_ncu_full.md;
 # scaled to the bench launch by the tokens it processes (traffic is proportional to the tokens read)
-NCU_TRAFFIC_BYTES, NCU_TRAFFIC_TOKENS = 139_171_584, 262_144
+NCU_TRAFFIC_BYTES, NCU_TRAFFIC_TOKENS = 138_843_776, 262_144
 
 
 def metric_name(args):
