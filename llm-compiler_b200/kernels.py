@@ -403,6 +403,44 @@ def _resolve_dtype(value, default: torch.dtype) -> torch.dtype:
 
 
 # ---------------------------------------------------------------- decode attention ----
+_packaged_plans: dict = {}
+
+
+def _profiled_split_tokens(batch: int, q_heads: int, kv_heads: int, dim: int, dtype: torch.dtype,
+                           context_bound: int) -> int:
+    """Split size of decode attention from the packaged dispatch profile: the plan of the
+    nearest profiled batch size (log scale) for this head layout, resolved with the context
+    bound; 0 (built-in plan) without matching rows. Plans are built once per layout."""
+
+    from .dispatch_plan import DispatchCostModel, ProfileError, resolve_dispatch_plan, split_tokens_of
+
+    layout = (q_heads, kv_heads, dim, str(dtype))
+    if layout not in _packaged_plans:
+        plans = {}
+        try:
+            model = _packaged_plans.get("model") or DispatchCostModel.packaged()
+            _packaged_plans["model"] = model
+            for entry in model.entries:
+                key = dict(entry.key)
+                if entry.op == "decode_attention" and key["batch"] not in plans:
+                    try:
+                        plan = model.plan_attribute("decode_attention", batch=key["batch"],
+                                                    q_heads=q_heads, kv_heads=kv_heads,
+                                                    head_dim=dim, dtype=str(dtype))
+                    except ProfileError:
+                        continue
+                    if plan["variants"]:
+                        plans[key["batch"]] = plan
+        except (OSError, ValueError):
+            plans = {}
+        _packaged_plans[layout] = plans
+    plans = _packaged_plans[layout]
+    if not plans:
+        return 0
+    nearest = min(plans, key=lambda size: abs(math.log(size / max(batch, 1))))
+    return split_tokens_of(resolve_dispatch_plan(plans[nearest], max(context_bound, 1)).variant)
+
+
 def decode_attention_workspace_bytes(batch: int, q_heads: int, kv_heads: int, head_dim: int,
                                      max_length: int, split_tokens: int = 0) -> int:
     return int(_lib.load().b200_decode_attention_workspace_bytes(
@@ -412,7 +450,7 @@ def decode_attention_workspace_bytes(batch: int, q_heads: int, kv_heads: int, he
 def b200_decode_attention(query: torch.Tensor, key_buffer: torch.Tensor,
                           value_buffer: torch.Tensor, lengths: torch.Tensor,
                           attention_mask: Optional[torch.Tensor], *, scale: float,
-                          numerical_mode: str = "fast", split_tokens: int = 0,
+                          numerical_mode: str = "fast", split_tokens: Optional[int] = None,
                           max_length_hint: int = 0,
                           output: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One-token GQA attention over the physical KV buffers. Mirrors
@@ -420,6 +458,9 @@ def b200_decode_attention(query: torch.Tensor, key_buffer: torch.Tensor,
 
     attention_mask is B x 1 x 1 x S additive (S <= capacity) or None for an all-zero mask
     of length `capacity`. Returns B x Hq x 1 x D (memory order B, Hq, D).
+    split_tokens: tokens per KV split; 0 = the library's built-in plan; None (default) = the
+    profile-guided plan (the measured profile that ships with the package, resolved with the
+    batch and the context bound of this call; the built-in plan where it has no matching rows).
     """
 
     device = _require_cuda(query, key_buffer, value_buffer, lengths, attention_mask)
@@ -459,6 +500,8 @@ def b200_decode_attention(query: torch.Tensor, key_buffer: torch.Tensor,
     rt = runtime(device)
     library = _lib.load()
     max_length = min(max_length_hint, mask_len) if max_length_hint > 0 else mask_len
+    if split_tokens is None:
+        split_tokens = _profiled_split_tokens(batch, q_heads, kv_heads, dim, query.dtype, max_length)
     need = 0
     if query.dtype == torch.bfloat16:
         need = int(library.b200_decode_attention_workspace_bytes(

@@ -278,11 +278,9 @@ def profile_case(args):
     layout = {"q_heads": args.q_heads, "kv_heads": args.kv_heads, "head_dim": args.head_dim,
               "dtype": "bf16"}
     for batch in (1, 8, 64, 256):
-        for length in (256, 1024, 4096, 16384):
-            if batch * length > 64 * 16384:
-                continue
+        for length in (256, 1024, 4096, 16384, 32768):
             costs = {}
-            for split in (0, 512, 1024, 2048, 4096):
+            for split in (0, 512, 1024, 2048, 4096, 8192):
                 if split > length:
                     continue
                 probe.split_tokens = split
@@ -332,7 +330,9 @@ def main():
     parser.add_argument("--q-heads", type=int, default=14)
     parser.add_argument("--kv-heads", type=int, default=2)
     parser.add_argument("--head-dim", type=int, default=64)
-    parser.add_argument("--split-tokens", type=int, default=0)
+    parser.add_argument("--split-tokens", type=int, default=None,
+                        help="decode attention: tokens per KV split; 0 = the library's built-in "
+                             "plan; default: the profile-guided plan")
     parser.add_argument("--m", type=int, default=64)
     parser.add_argument("--k", type=int, default=896)
     parser.add_argument("--n", type=int, default=896)
