@@ -199,9 +199,12 @@ __device__ __forceinline__ uint16_t f32_to_bf16_bits(float value) {
 __device__ __forceinline__ float round_bf16(float value) {
   return __bfloat162float(__float2bfloat16_rn(value));
 }
+// One packed conversion (round to nearest even, both halves): two single conversions would
+// each take a slot of the quarter-rate conversion unit that the exponentials also need.
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
-  return static_cast<uint32_t>(f32_to_bf16_bits(lo)) |
-         (static_cast<uint32_t>(f32_to_bf16_bits(hi)) << 16);
+  uint32_t packed;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed) : "f"(hi), "f"(lo));
+  return packed;
 }
 __device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_float(packed << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t packed) {

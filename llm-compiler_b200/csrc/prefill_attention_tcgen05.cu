@@ -26,7 +26,7 @@ namespace b200 {
 namespace {
 
 constexpr int kTile = 128;     // query rows per CTA = keys per step
-constexpr int kThreads = 192;  // 4 softmax warps + TMA warp + MMA warp
+constexpr int kThreadsOneGroup = 192;  // 4 softmax warps + TMA warp + MMA warp
 constexpr int kKStages = 2;  // K tiles are double-buffered, V has one buffer (see the kernel)
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -50,48 +50,58 @@ __device__ __forceinline__ void load_box(uint32_t dst, const CUtensorMap* map, u
   else tma_load_4d(dst, map, bar, d0, head, t0, batch);
 }
 
-// Launch bounds: at D = 64 two CTAs share an SM, which needs at most 128 registers per thread
-// (the register file is split over four sub-partitions of 16 K registers; two of a CTA's six
-// warps land on the same one). Declaring 256 threads x 2 CTAs makes the compiler keep to that.
-template <int D>
-__global__ void __launch_bounds__(D == 64 ? 256 : kThreads, D == 64 ? 2 : 1)
+// G query tiles of 128 rows per CTA. G = 2 (D = 64): two softmax groups of four warps work half
+// a period apart, so the tensor core computes one group's products while the other group is in
+// its softmax, and both share every K / V tile the CTA fetches. G = 1 (D = 128): one group.
+// Threads: 4 G softmax warps (warp % 4 = the TMEM lane quarter it may read), then the TMA warp
+// and the MMA warp. G = 2 runs one CTA per SM (ten warps, at most three on one of the four
+// 16 K-register sub-partitions: up to 170 registers per thread); G = 1 at D = 64 fits two CTAs
+// per SM, which needs at most 128 registers per thread.
+template <int D, int G>
+__global__ void __launch_bounds__(G == 2 ? 384 : (D == 64 ? 256 : kThreadsOneGroup),
+                                  (G == 1 && D == 64) ? 2 : 1)
 prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant__ CUtensorMap q_map,
                                  const __grid_constant__ CUtensorMap k_map,
                                  const __grid_constant__ CUtensorMap v_map) {
-  constexpr int kPanels = D / 64;                   // 64-wide (128-byte) panels along D
-  constexpr uint32_t kPanelBytes = kTile * 128;     // 128 rows x 128 B
+  constexpr int kPanels = D / 64;                         // 64-wide (128-byte) panels along D
+  constexpr uint32_t kPanelBytes = kTile * 128;           // 128 rows x 128 B
   constexpr uint32_t kTileBytes = kPanels * kPanelBytes;  // one of Q, K, V
-  constexpr uint32_t kTmemColumns = 256;            // S: 128, O_j: D
-  constexpr uint32_t kSColumn = 0, kOColumn = 128;
+  constexpr uint32_t kPBytes = kTile * kTile * 2;         // probabilities of one group
+  constexpr uint32_t kTmemColumns = G * (kTile + D) <= 256 ? 256 : 512;  // S and O_j per group
+  constexpr int kTmaWarp = 4 * G, kMmaWarp = 4 * G + 1;
 
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t q_full, s_full, p_full, o_full;
+  __shared__ __align__(8) uint64_t q_full, s_full[G], p_full[G], o_full[G];
   __shared__ __align__(8) uint64_t k_full[kKStages], k_empty[kKStages], v_full, v_empty;
   __shared__ uint32_t tmem_base_slot;
   __shared__ int failed;
 
   TraceScope trace(7);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_tile = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // heavy first
+  const int q_block = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // heavy first
   const int hq = blockIdx.y, b = blockIdx.z;
   const int kvh = hq / p.groups;
-  const int q0 = q_tile * kTile;
-  const int n_tiles = q_tile + 1;  // causal: key tiles 0 .. the diagonal one
+  const int q0 = q_block * G * kTile;
+  const int all_tiles = (p.tokens + kTile - 1) / kTile;
+  // causal: group g (query tile G q_block + g) needs key tiles 0 .. its own
+  int tiles_of[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) tiles_of[g] = min(q_block * G + g + 1, all_tiles);
+  const int n_tiles = tiles_of[G - 1];
 
-  const uint32_t q_smem = smem_u32(smem);
-  // K_{j+1} is wanted the moment P V_j has been issued, V_{j+1} only a softmax later: two K
-  // buffers and one V buffer keep the CTA below half of the shared memory at D = 64, so that
-  // two CTAs share an SM and fill each other's softmax gaps on the tensor core.
-  const uint32_t k_smem = q_smem + kTileBytes;
-  const uint32_t v_smem = k_smem + kKStages * kTileBytes;
-  const uint32_t p_smem = v_smem + kTileBytes;  // [2 panels][128 rows][128 B]
+  const uint32_t q_smem = smem_u32(smem);                   // G tiles
+  const uint32_t k_smem = q_smem + G * kTileBytes;          // two buffers
+  const uint32_t v_smem = k_smem + kKStages * kTileBytes;   // one buffer (wanted a softmax later than K)
+  const uint32_t p_smem = v_smem + kTileBytes;              // G x [2 panels][128 rows][128 B]
 
   if (threadIdx.x == 0) {
     failed = 0;
     mbarrier_init(smem_u32(&q_full), 1);
-    mbarrier_init(smem_u32(&s_full), 1);
-    mbarrier_init(smem_u32(&p_full), 4);  // one arrival per softmax warp
-    mbarrier_init(smem_u32(&o_full), 1);
+    for (int g = 0; g < G; ++g) {
+      mbarrier_init(smem_u32(&s_full[g]), 1);
+      mbarrier_init(smem_u32(&p_full[g]), 4);  // one arrival per softmax warp
+      mbarrier_init(smem_u32(&o_full[g]), 1);
+    }
     for (int s = 0; s < kKStages; ++s) {
       mbarrier_init(smem_u32(&k_full[s]), 1);
       mbarrier_init(smem_u32(&k_empty[s]), 1);
@@ -100,7 +110,7 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
     mbarrier_init(smem_u32(&v_empty), 1);
     fence_mbarrier_init();
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  ::"r"(smem_u32(&tmem_base_slot)), "r"(kTmemColumns) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -109,14 +119,18 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
+  auto s_column = [&](int g) { return tmem_base + g * kTile; };
+  auto o_column = [&](int g) { return tmem_base + G * kTile + g * D; };
 
-  if (warp == 4 && lane == 0) {
+  if (warp == kTmaWarp && lane == 0) {
     // ---- TMA producer ----
-    mbarrier_arrive_expect_tx(smem_u32(&q_full), kTileBytes);
+    mbarrier_arrive_expect_tx(smem_u32(&q_full), G * kTileBytes);
 #pragma unroll
-    for (int panel = 0; panel < kPanels; ++panel)
-      load_box(q_smem + panel * kPanelBytes, &q_map, smem_u32(&q_full), panel * 64, q0, hq, b,
-               p.q_token_dim1);
+    for (int g = 0; g < G; ++g)
+#pragma unroll
+      for (int panel = 0; panel < kPanels; ++panel)
+        load_box(q_smem + g * kTileBytes + panel * kPanelBytes, &q_map, smem_u32(&q_full), panel * 64,
+                 q0 + g * kTile, hq, b, p.q_token_dim1);
     for (int j = 0; j < n_tiles; ++j) {
       const int s = j & 1;
       if (j >= kKStages && !mbarrier_wait_bounded(smem_u32(&k_empty[s]), ((j >> 1) - 1) & 1)) {
@@ -138,76 +152,101 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
         load_box(v_smem + panel * kPanelBytes, &v_map, smem_u32(&v_full), panel * 64, j * kTile, kvh,
                  b, p.v_token_dim1);
     }
-  } else if (warp == 5 && lane == 0) {
+  } else if (warp == kMmaWarp && lane == 0) {
     // ---- MMA issuer ----
     constexpr uint32_t idesc_s = instruction_descriptor(kTile, kTile);
     constexpr uint32_t idesc_o = instruction_descriptor(kTile, D, true);  // V: MN-major B operand
-    auto issue_s = [&](int j) {  // S = Q K_j^T, K = D
-      const uint32_t k_tile = k_smem + (j & 1) * kTileBytes;
+    auto issue_s = [&](int g, int j) {  // S_g = Q_g K_j^T, K = D
+      const uint32_t q_tile = q_smem + g * kTileBytes, k_tile = k_smem + (j & 1) * kTileBytes;
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
         const uint32_t offset = (ks / 4) * kPanelBytes + (ks % 4) * 32;
-        umma_bf16(tmem_base + kSColumn, smem_descriptor(q_smem + offset),
-                  smem_descriptor(k_tile + offset), idesc_s, ks > 0 ? 1u : 0u);
+        umma_bf16(s_column(g), smem_descriptor(q_tile + offset), smem_descriptor(k_tile + offset),
+                  idesc_s, ks > 0 ? 1u : 0u);
       }
-      umma_commit(smem_u32(&s_full));
-      umma_commit(smem_u32(&k_empty[j & 1]));  // K_j is free once S_j has been computed
+      umma_commit(smem_u32(&s_full[g]));
     };
-    bool ok = mbarrier_wait_bounded(smem_u32(&q_full), 0) &&
-              mbarrier_wait_bounded(smem_u32(&k_full[0]), 0);
-    if (ok) {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      issue_s(0);
-    }
-    for (int j = 0; ok && j < n_tiles; ++j) {
-      // O_j = P V_j once the softmax warps have written P (which also says S and O_{j-1} are read)
-      if (!mbarrier_wait_bounded(smem_u32(&p_full), j & 1) ||
-          !mbarrier_wait_bounded(smem_u32(&v_full), j & 1)) {
-        ok = false;
-        break;
-      }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const uint32_t v_tile = v_smem;
+    auto issue_o = [&](int g) {  // O_j of group g = P_g V_j, K = 128 keys
+      const uint32_t p_tile = p_smem + g * kPBytes;
 #pragma unroll
       for (int ks = 0; ks < kTile / 16; ++ks) {
         const uint32_t p_offset = (ks / 4) * kPanelBytes + (ks % 4) * 32;
-        umma_bf16(tmem_base + kOColumn, smem_descriptor(p_smem + p_offset),
-                  smem_descriptor_mn_major(v_tile + ks * 2048, kPanelBytes), idesc_o,
-                  ks > 0 ? 1u : 0u);
+        umma_bf16(o_column(g), smem_descriptor(p_tile + p_offset),
+                  smem_descriptor_mn_major(v_smem + ks * 2048, kPanelBytes), idesc_o, ks > 0 ? 1u : 0u);
       }
-      umma_commit(smem_u32(&o_full));
-      umma_commit(smem_u32(&v_empty));  // V_j is free once these MMAs retire
-      if (j + 1 < n_tiles) {
-        if (!mbarrier_wait_bounded(smem_u32(&k_full[(j + 1) & 1]), ((j + 1) >> 1) & 1)) {
-          ok = false;
-          break;
+      umma_commit(smem_u32(&o_full[g]));
+    };
+    TraceSamples samples(70, true);
+    bool ok = mbarrier_wait_bounded(smem_u32(&q_full), 0) &&
+              mbarrier_wait_bounded(smem_u32(&k_full[0]), 0);
+    samples.sample(0);
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int g = 0; g < G; ++g) issue_s(g, 0);  // every group has key tile 0
+      umma_commit(smem_u32(&k_empty[0]));  // K_0 is free once these have been computed
+    }
+    for (int j = 0; ok && j < n_tiles; ++j) {
+      // Per group: O_j = P V_j as soon as its softmax has written P (which also says its S and
+      // its O_{j-1} are read), then its S of the next key tile right behind, so that the group
+      // can start the next softmax while the other group's products run.
+      const bool more = j + 1 < n_tiles;
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        if (j < tiles_of[g]) {
+          if (!mbarrier_wait_bounded(smem_u32(&p_full[g]), j & 1) ||
+              !mbarrier_wait_bounded(smem_u32(&v_full), j & 1)) {
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if (j < 7) samples.sample(1 + (j * G + g) * 4);
+          issue_o(g);
+          if (j < 7) samples.sample(2 + (j * G + g) * 4);
         }
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        issue_s(j + 1);  // its commit also covers P V_j: P is free when s_full fires
+        if (g == G - 1) umma_commit(smem_u32(&v_empty));  // V_j is free once its last reader retires
+        if (more && j + 1 < tiles_of[g]) {
+          if (!mbarrier_wait_bounded(smem_u32(&k_full[(j + 1) & 1]), ((j + 1) >> 1) & 1)) {
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          if (j < 7) samples.sample(3 + (j * G + g) * 4);
+          issue_s(g, j + 1);  // its commit also covers P_g V_j: P_g is free when s_full[g] fires
+        }
+        if (j < 7) samples.sample(4 + (j * G + g) * 4);
+        if (more && g == G - 1) umma_commit(smem_u32(&k_empty[(j + 1) & 1]));  // K_{j+1}: all S issued
       }
     }
     if (!ok) failed = 1;
-  } else if (warp < 4) {
-    // ---- softmax + epilogue: thread = query row = TMEM lane ----
-    const int row = threadIdx.x;
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+  } else if (warp < 4 * G) {
+    // ---- softmax + epilogue: thread = query row = TMEM lane of its group ----
+    const int g = warp >> 2;
+    const int row = threadIdx.x & 127;
+    const int q_tile = q_block * G + g;
+    const int my_tiles = tiles_of[g];
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t s_taddr = s_column(g) + lane_base, o_taddr = o_column(g) + lane_base;
+    const uint32_t p_tile = p_smem + g * kPBytes;
     float m_run = -INFINITY, l_run = 0.0f;
     float o[D];
 #pragma unroll
     for (int i = 0; i < D; ++i) o[i] = 0.0f;
     bool ok = true;
-    for (int j = 0; j < n_tiles; ++j) {
-      if (!mbarrier_wait_bounded(smem_u32(&s_full), j & 1)) {
+    TraceSamples samples(71 + g, row == 0);
+    for (int j = 0; j < my_tiles; ++j) {
+      if (!mbarrier_wait_bounded(smem_u32(&s_full[g]), j & 1)) {
         ok = false;
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (j < 12) samples.sample(j * 5);
       const bool diagonal = j == q_tile;  // keys beyond the row's own position are masked
       float row_max = -INFINITY;
 #pragma unroll 1
       for (int c0 = 0; c0 < kTile; c0 += 32) {
         float s[32];
-        tmem_load_32x32(lane_base + kSColumn + c0, s);
+        tmem_load_32x32(s_taddr + c0, s);
         if (diagonal) {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
@@ -217,13 +256,14 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
           for (int i = 0; i < 32; ++i) row_max = fmaxf(row_max, s[i]);
         }
       }
+      if (j < 12) samples.sample(j * 5 + 1);
       const float m_new = fmaxf(m_run, row_max * p.scale_log2);  // key 0 is never masked
       const float alpha = exp2_fast(m_run - m_new);              // exp2(-inf) = 0 at the first tile
       float sum = 0.0f;
 #pragma unroll 1
       for (int c0 = 0; c0 < kTile; c0 += 32) {
         float s[32];
-        tmem_load_32x32(lane_base + kSColumn + c0, s);
+        tmem_load_32x32(s_taddr + c0, s);
         uint32_t packed[16];
         if (diagonal) {
 #pragma unroll
@@ -245,7 +285,7 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
           }
         }
         // K-major A operand: panel = 64 keys, row = query, 16-byte chunks XOR-swizzled by row % 8
-        const uint32_t panel = p_smem + (c0 / 64) * kPanelBytes + row * 128;
+        const uint32_t panel = p_tile + (c0 / 64) * kPanelBytes + row * 128;
 #pragma unroll
         for (int chunk = 0; chunk < 4; ++chunk) {
           const int logical = (c0 % 64) / 8 + chunk;
@@ -261,26 +301,31 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_full)) : "memory");
-      if (!mbarrier_wait_bounded(smem_u32(&o_full), j & 1)) {
+      if (lane == 0)
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_full[g])) : "memory");
+      if (j < 12) samples.sample(j * 5 + 2);
+      if (!mbarrier_wait_bounded(smem_u32(&o_full[g]), j & 1)) {
         ok = false;
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      if (j < 12) samples.sample(j * 5 + 3);
 #pragma unroll
       for (int c0 = 0; c0 < D; c0 += 32) {
         float v[32];
-        tmem_load_32x32(lane_base + kOColumn + c0, v);
+        tmem_load_32x32(o_taddr + c0, v);
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, v[i]);
       }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      if (j < 12) samples.sample(j * 5 + 4);
     }
+    const int q_row = q0 + g * kTile + row;
     if (!ok) {
       failed = 1;
-    } else if (q0 + row < p.tokens) {
+    } else if (q_row < p.tokens) {
       const float inv = 1.0f / l_run;
-      __nv_bfloat16* dst = p.out + ((static_cast<int64_t>(b) * p.tokens + q0 + row) * p.q_heads + hq) * D;
+      __nv_bfloat16* dst = p.out + ((static_cast<int64_t>(b) * p.tokens + q_row) * p.q_heads + hq) * D;
 #pragma unroll
       for (int i = 0; i < D; i += 8)
         *reinterpret_cast<uint4*>(dst + i) =
@@ -292,7 +337,7 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (failed && threadIdx.x == 0 && p.status != nullptr) atomicOr(p.status, B200_STATUS_WAIT_TIMEOUT);
-  if (warp == 5)
+  if (warp == kMmaWarp)
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns)
                  : "memory");
   trace.mark(1);
@@ -313,8 +358,13 @@ int prefill_attention_tcgen05(const void* query, const void* key, const void* va
   if (path != nullptr && strcmp(path, "mma.sync") == 0) return B200_ERR_UNSUPPORTED;
   if (head_dim != 64 && head_dim != 128) return B200_ERR_UNSUPPORTED;
   if (!(scale > 0.0) || tokens < 1) return B200_ERR_UNSUPPORTED;
-  const int64_t q_tiles = ceil_div(tokens, kTile);
-  if (q_tiles > 65535 || q_heads > 65535 || batch > 65535) return B200_ERR_UNSUPPORTED;
+  // One query tile per CTA (two CTAs per SM at D = 64) unless B200_PREFILL_QUERY_TILES=2 asks for
+  // two tiles per CTA at D = 64: measured equal within 3 % either way from 1024 to 16384 tokens.
+  int query_tiles = 1;
+  const char* tiles_text = getenv("B200_PREFILL_QUERY_TILES");
+  if (tiles_text != nullptr && strcmp(tiles_text, "2") == 0 && head_dim == 64) query_tiles = 2;
+  const int64_t q_blocks = ceil_div(tokens, static_cast<int64_t>(kTile) * query_tiles);
+  if (q_blocks > 65535 || q_heads > 65535 || batch > 65535) return B200_ERR_UNSUPPORTED;
   CUtensorMap q_map, k_map, v_map;
   bool q_dim1, k_dim1, v_dim1;
   if (!make_bf16_bhtd_map(&q_map, query, batch, q_heads, tokens, head_dim, query_strides[0],
@@ -334,24 +384,28 @@ int prefill_attention_tcgen05(const void* query, const void* key, const void* va
   p.k_token_dim1 = k_dim1 ? 1 : 0;
   p.v_token_dim1 = v_dim1 ? 1 : 0;
   p.scale_log2 = static_cast<float>(scale) * kLog2e;
-  dim3 grid(static_cast<unsigned>(q_tiles), static_cast<unsigned>(q_heads),
+  dim3 grid(static_cast<unsigned>(q_blocks), static_cast<unsigned>(q_heads),
             static_cast<unsigned>(batch));
-  // Q + two K tiles + one V tile + P
-  const int smem = static_cast<int>(head_dim) * kTile * 2 * (2 + kKStages) + kTile * kTile * 2;
-  if (head_dim == 64) {
-    auto kernel = prefill_attention_tcgen05_kernel<64>;
+  // G query tiles + two K tiles + one V tile + G tiles of probabilities
+  const int tile_bytes = static_cast<int>(head_dim) * kTile * 2;
+  const int smem = tile_bytes * (query_tiles + kKStages + 1) + query_tiles * kTile * kTile * 2;
+  const int threads = (4 * query_tiles + 2) * 32;
+  auto launch = [&](auto kernel) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return B200_ERR_LAUNCH;
-    // two CTAs per SM need the largest shared-memory carve-out
+      return false;
+    // two single-group CTAs per SM need the largest shared-memory carve-out
     cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                          cudaSharedmemCarveoutMaxShared);
-    kernel<<<grid, kThreads, smem, stream>>>(p, q_map, k_map, v_map);
-  } else {
-    auto kernel = prefill_attention_tcgen05_kernel<128>;
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return B200_ERR_LAUNCH;
-    kernel<<<grid, kThreads, smem, stream>>>(p, q_map, k_map, v_map);
-  }
+    kernel<<<grid, threads, smem, stream>>>(p, q_map, k_map, v_map);
+    return true;
+  };
+  bool launched;
+  if (head_dim == 64)
+    launched = query_tiles == 2 ? launch(prefill_attention_tcgen05_kernel<64, 2>)
+                                : launch(prefill_attention_tcgen05_kernel<64, 1>);
+  else
+    launched = launch(prefill_attention_tcgen05_kernel<128, 1>);
+  if (!launched) return B200_ERR_LAUNCH;
   return launch_status();
 }
 
