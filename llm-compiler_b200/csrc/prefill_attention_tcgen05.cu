@@ -11,8 +11,9 @@
 //                 D, an MN-major B operand: no transpose pass); O_j in D TMEM columns
 //   O = O a + O_j in registers (a = exp2(old max - new max)): tensor memory is never rescaled
 // Roles: warps 0-3 softmax + epilogue, warp 4 (one lane) TMA producer (two K buffers, one V),
-// warp 5 (one lane) MMA issuer and owner of the TMEM allocation. The MMA thread issues S of tile
-// j + 1 right behind P V of tile j, so the tensor core works while the softmax warps fold O_j.
+// warp 5 (one lane) MMA issuer and owner of the TMEM allocation. Once P_j is written the MMA
+// thread issues S of tile j + 1 and then P_j V_j: the softmax warps take the row maxima of tile
+// j + 1 while O_j is computed, fold O_j, and only then overwrite P.
 // Every mbarrier wait is bounded: a wait that gives up sets B200_STATUS_WAIT_TIMEOUT, TMEM is
 // freed and the CTA returns. Heavier CTAs (later query tiles) are scheduled first.
 #include <stdlib.h>
@@ -176,10 +177,8 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
       }
       umma_commit(smem_u32(&o_full[g]));
     };
-    TraceSamples samples(70, true);
-    bool ok = mbarrier_wait_bounded(smem_u32(&q_full), 0) &&
-              mbarrier_wait_bounded(smem_u32(&k_full[0]), 0);
-    samples.sample(0);
+    bool ok = mbarrier_spin_bounded(smem_u32(&q_full), 0) &&
+              mbarrier_spin_bounded(smem_u32(&k_full[0]), 0);
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -187,35 +186,35 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
       umma_commit(smem_u32(&k_empty[0]));  // K_0 is free once these have been computed
     }
     for (int j = 0; ok && j < n_tiles; ++j) {
-      // Per group: O_j = P V_j as soon as its softmax has written P (which also says its S and
-      // its O_{j-1} are read), then its S of the next key tile right behind, so that the group
-      // can start the next softmax while the other group's products run.
+      // Per group, once its softmax has written P_j (which also says that its S_j and its
+      // O_{j-1} have been read): first S of the next key tile, so that the group can take the
+      // row maxima of that tile while the tensor core computes O_j = P_j V_j behind it.
       const bool more = j + 1 < n_tiles;
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        if (j < tiles_of[g]) {
-          if (!mbarrier_wait_bounded(smem_u32(&p_full[g]), j & 1) ||
-              !mbarrier_wait_bounded(smem_u32(&v_full), j & 1)) {
+        const bool has_tile = j < tiles_of[g];
+        if (has_tile && !mbarrier_spin_bounded(smem_u32(&p_full[g]), j & 1)) {
+          ok = false;
+          break;
+        }
+        if (more && j + 1 < tiles_of[g]) {
+          if (!mbarrier_spin_bounded(smem_u32(&k_full[(j + 1) & 1]), ((j + 1) >> 1) & 1)) {
             ok = false;
             break;
           }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          if (j < 7) samples.sample(1 + (j * G + g) * 4);
-          issue_o(g);
-          if (j < 7) samples.sample(2 + (j * G + g) * 4);
+          issue_s(g, j + 1);
+        }
+        if (more && g == G - 1) umma_commit(smem_u32(&k_empty[(j + 1) & 1]));  // K_{j+1}: all S issued
+        if (has_tile) {
+          if (!mbarrier_spin_bounded(smem_u32(&v_full), j & 1)) {
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_o(g);  // P_g is free again when o_full[g] fires
         }
         if (g == G - 1) umma_commit(smem_u32(&v_empty));  // V_j is free once its last reader retires
-        if (more && j + 1 < tiles_of[g]) {
-          if (!mbarrier_wait_bounded(smem_u32(&k_full[(j + 1) & 1]), ((j + 1) >> 1) & 1)) {
-            ok = false;
-            break;
-          }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          if (j < 7) samples.sample(3 + (j * G + g) * 4);
-          issue_s(g, j + 1);  // its commit also covers P_g V_j: P_g is free when s_full[g] fires
-        }
-        if (j < 7) samples.sample(4 + (j * G + g) * 4);
-        if (more && g == G - 1) umma_commit(smem_u32(&k_empty[(j + 1) & 1]));  // K_{j+1}: all S issued
       }
     }
     if (!ok) failed = 1;
@@ -233,14 +232,25 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
 #pragma unroll
     for (int i = 0; i < D; ++i) o[i] = 0.0f;
     bool ok = true;
-    TraceSamples samples(71 + g, row == 0);
+    float alpha_pending = 0.0f;  // factor of the O_j that is still in tensor memory
+    auto fold = [&](int j) {     // o = o * alpha_j + O_j
+      if (!mbarrier_wait_ready_first(smem_u32(&o_full[g]), j & 1)) return false;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        float v[32];
+        tmem_load_32x32(o_taddr + c0, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha_pending, v[i]);
+      }
+      return true;
+    };
     for (int j = 0; j < my_tiles; ++j) {
-      if (!mbarrier_wait_bounded(smem_u32(&s_full[g]), j & 1)) {
+      if (!mbarrier_wait_ready_first(smem_u32(&s_full[g]), j & 1)) {
         ok = false;
         break;
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (j < 12) samples.sample(j * 5);
       const bool diagonal = j == q_tile;  // keys beyond the row's own position are masked
       float row_max = -INFINITY;
 #pragma unroll 1
@@ -256,9 +266,14 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
           for (int i = 0; i < 32; ++i) row_max = fmaxf(row_max, s[i]);
         }
       }
-      if (j < 12) samples.sample(j * 5 + 1);
       const float m_new = fmaxf(m_run, row_max * p.scale_log2);  // key 0 is never masked
       const float alpha = exp2_fast(m_run - m_new);              // exp2(-inf) = 0 at the first tile
+      // O_{j-1} ran on the tensor core during the pass above; P is free once it is complete
+      if (j > 0 && !fold(j - 1)) {
+        ok = false;
+        break;
+      }
+      alpha_pending = alpha;
       float sum = 0.0f;
 #pragma unroll 1
       for (int c0 = 0; c0 < kTile; c0 += 32) {
@@ -303,23 +318,9 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
       __syncwarp();
       if (lane == 0)
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_full[g])) : "memory");
-      if (j < 12) samples.sample(j * 5 + 2);
-      if (!mbarrier_wait_bounded(smem_u32(&o_full[g]), j & 1)) {
-        ok = false;
-        break;
-      }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      if (j < 12) samples.sample(j * 5 + 3);
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        float v[32];
-        tmem_load_32x32(o_taddr + c0, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha, v[i]);
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      if (j < 12) samples.sample(j * 5 + 4);
     }
+    if (ok && my_tiles > 0) ok = fold(my_tiles - 1);
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     const int q_row = q0 + g * kTile + row;
     if (!ok) {
       failed = 1;

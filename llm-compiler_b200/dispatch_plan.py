@@ -41,6 +41,12 @@ OPERATORS: Dict[str, Tuple[str, Tuple[str, ...]]] = {
     "rms_norm": ("rows", ("hidden_size", "dtype")),
 }
 
+# The variant a kernel picks by itself, and how much cheaper (as a fraction) a measured
+# alternative must be to replace it: differences inside the measurement noise of a profile
+# must not move a call off the plan that was tuned inside the whole decode step.
+BUILT_IN_VARIANT: Dict[str, str] = {"decode_attention": "split:0"}
+NOISE_MARGIN = 0.05
+
 _DTYPE_ALIASES = {"f16": "fp16", "float16": "fp16", "half": "fp16", "bfloat16": "bf16",
                   "float32": "fp32", "f32": "fp32", "float": "fp32"}
 
@@ -178,8 +184,9 @@ class DispatchCostModel:
 
     def variants(self, op: str, *, allowed: Optional[Iterable[str]] = None,
                  **key_fields: Any) -> List[DispatchVariant]:
-        """One variant per profiled value of the bucketed dimension: the cheapest allowed one,
-        owning the values up to floor(sqrt(this * next)) (cost_model.py:150-153)."""
+        """One variant per profiled value of the bucketed dimension: the cheapest allowed one
+        (the kernel's built-in choice unless another is more than NOISE_MARGIN cheaper), owning
+        the values up to floor(sqrt(this * next)) (cost_model.py:150-153)."""
 
         key = _key(op, key_fields)
         allowed_set = None if allowed is None else set(allowed)
@@ -198,6 +205,9 @@ class DispatchCostModel:
             if not costs:
                 raise ProfileError(f"{op} at {OPERATORS[op][0]}={value}: no allowed variant")
             best = min(sorted(costs), key=costs.get)
+            built_in = BUILT_IN_VARIANT.get(op)
+            if built_in in costs and costs[built_in] <= costs[best] * (1.0 + NOISE_MARGIN):
+                best = built_in
             out.append(DispatchVariant(minimum, maximum, value, best, costs[best]))
             minimum = maximum + 1 if maximum is not None else minimum
         return out

@@ -52,6 +52,14 @@ def test_buckets_are_bounded_by_the_geometric_mean_of_neighbouring_profiled_valu
     assert model.variants("linear", k=999, n=256, dtype="fp32") == []
 
 
+def test_the_built_in_plan_keeps_its_place_inside_the_noise_margin():
+    rows = [{"op": "decode_attention", "batch": 64, **LAYOUT, "length": length, "variants_us": costs}
+            for length, costs in ((4096, {"split:0": 24.82, "split:2048": 24.65}),       # 0.7 % cheaper: noise
+                                  (16384, {"split:0": 97.0, "split:8192": 80.2}))]        # 17 % cheaper: taken
+    variants = DispatchCostModel.from_dict(rows).variants("decode_attention", batch=64, **LAYOUT)
+    assert [(v.variant, v.estimated_us) for v in variants] == [("split:0", 24.82), ("split:8192", 80.2)]
+
+
 def test_allowed_variants_and_dtype_aliases():
     model = DispatchCostModel.from_dict(profile())
     only = model.variants("prefill_attention", allowed=["tcgen05"], q_heads=14, kv_heads=2,
