@@ -1,21 +1,29 @@
-// serve.prefill_attention (causal-proved, bf16, fast mode) on the 5th-generation tensor cores.
+// serve.prefill_attention (causal-proved, bf16, fast mode) on the 5th-generation tensor cores:
+// a pair of 128-row query tiles per CTA, one CTA per SM, the output accumulated in tensor memory.
 //
-// One CTA owns 128 query rows of one (batch, query head) and walks the key tiles 0 .. its own
-// (causal: nothing beyond the diagonal tile is touched). Per 128-key tile:
-//   S = Q K^T     tcgen05.mma, M 128 x N 128, K = D in steps of 16; Q and K tiles K-major in
-//                 128-byte swizzled shared memory (TMA boxes), S in 128 TMEM columns (fp32)
-//   softmax       four warps, one query row per thread = one TMEM lane: two passes of
-//                 tcgen05.ld over the row (max, then exp2 and sum), probabilities rounded to bf16
-//                 and written as the K-major A operand of the next product
-//   O_j = P V     tcgen05.mma, M 128 x N D, K = 128 keys; V is used as it lies in memory (keys x
-//                 D, an MN-major B operand: no transpose pass); O_j in D TMEM columns
-//   O = O a + O_j in registers (a = exp2(old max - new max)): tensor memory is never rescaled
-// Roles: warps 0-3 softmax + epilogue, warp 4 (one lane) TMA producer (two K buffers, one V),
-// warp 5 (one lane) MMA issuer and owner of the TMEM allocation. Once P_j is written the MMA
-// thread issues S of tile j + 1 and then P_j V_j: the softmax warps take the row maxima of tile
-// j + 1 while O_j is computed, fold O_j, and only then overwrite P.
-// Every mbarrier wait is bounded: a wait that gives up sets B200_STATUS_WAIT_TIMEOUT, TMEM is
-// freed and the CTA returns. Heavier CTAs (later query tiles) are scheduled first.
+// Two softmax groups of eight warps each own one query tile of the pair and share every K / V
+// tile the CTA fetches (causal: nothing beyond a tile's diagonal is touched). Per group and
+// 128-key tile:
+//   S = Q K^T     tcgen05.mma M 128 x N 128 into the group's 128 TMEM columns; Q and K tiles
+//                 K-major in 128-byte swizzled shared memory (TMA boxes)
+//   softmax       two threads per query row (a warp may only read its own quarter of the TMEM
+//                 lanes, so warps w and w + 4 share 32 rows and split the keys in halves): the
+//                 half row of S is read into registers once, which frees S for the next product
+//                 at once; the halves exchange their maxima through shared memory; exp2; bf16
+//                 probabilities written as the K-major A operand P
+//   O += P V      tcgen05.mma M 128 x N D accumulating in the group's D TMEM columns; V is used
+//                 as it lies in memory (an MN-major B operand: no transpose pass)
+// The running maximum is lazy: probabilities are taken against a reference maximum that is moved
+// (and O and the row sums rescaled, O in tensor memory by the row's own threads) only when a
+// tile raises a row's maximum by more than 8 in the log2 domain, so probabilities stay below 2^8
+// and most tiles touch O only through the tensor core. The result is O / row sum.
+// With the row in registers a group's next S is computed during its current softmax, and the
+// tensor core works for one group while the other group's warps are in their exponentials.
+// Roles: warps 0-7 and 8-15 softmax groups, warp 16 (one lane) TMA producer (two K buffers, two
+// V buffers at D = 64, one at D = 128; K one tile ahead of V), warp 17 (one lane) MMA issuer and
+// owner of the 512 TMEM columns (S at 0 and 128, O behind them). Every mbarrier wait is bounded:
+// a wait that gives up sets B200_STATUS_WAIT_TIMEOUT, tensor memory is freed and the CTA
+// returns. Query blocks are handed out heaviest first across all heads and sequences.
 #include <stdlib.h>
 #include <string.h>
 
@@ -26,9 +34,8 @@
 namespace b200 {
 namespace {
 
-constexpr int kTile = 128;     // query rows per CTA = keys per step
-constexpr int kThreadsOneGroup = 192;  // 4 softmax warps + TMA warp + MMA warp
-constexpr int kKStages = 2;  // K tiles are double-buffered, V has one buffer (see the kernel)
+constexpr int kTile = 128;    // query rows per group = keys per step
+constexpr int kKStages = 2;  // K tiles are double-buffered
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct PrefillTcParams {
@@ -51,64 +58,74 @@ __device__ __forceinline__ void load_box(uint32_t dst, const CUtensorMap* map, u
   else tma_load_4d(dst, map, bar, d0, head, t0, batch);
 }
 
-// G query tiles of 128 rows per CTA. G = 2 (D = 64): two softmax groups of four warps work half
-// a period apart, so the tensor core computes one group's products while the other group is in
-// its softmax, and both share every K / V tile the CTA fetches. G = 1 (D = 128): one group.
-// Threads: 4 G softmax warps (warp % 4 = the TMEM lane quarter it may read), then the TMA warp
-// and the MMA warp. G = 2 runs one CTA per SM (ten warps, at most three on one of the four
-// 16 K-register sub-partitions: up to 170 registers per thread); G = 1 at D = 64 fits two CTAs
-// per SM, which needs at most 128 registers per thread.
-template <int D, int G>
-__global__ void __launch_bounds__(G == 2 ? 384 : (D == 64 ? 256 : kThreadsOneGroup),
-                                  (G == 1 && D == 64) ? 2 : 1)
+constexpr int kGroups = 2;
+constexpr int kSoftmaxWarps = 8 * kGroups;  // two warps per 32 query rows
+constexpr int kThreads = (kSoftmaxWarps + 2) * 32;  // + TMA warp + MMA warp
+constexpr float kRescaleThreshold = 8.0f;  // log2 domain
+constexpr uint32_t kSpinLimit = 2000000u;   // polls of an MMA thread before it gives up (about 0.1 s)
+
+// 18 warps: five on one of the four 16 K-register sub-partitions, so at most 96 registers each.
+template <int D>
+__global__ void __launch_bounds__(640, 1)
 prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant__ CUtensorMap q_map,
                                  const __grid_constant__ CUtensorMap k_map,
                                  const __grid_constant__ CUtensorMap v_map) {
+  constexpr int G = kGroups;
+  constexpr int kVStages = D == 64 ? 2 : 1;               // 227 KB hold one V tile at D = 128
+  // With two V buffers V_j has long landed when P_j is written and a softmax warp vouches for it;
+  // a single buffer is refilled late, and only the MMA thread should wait for that.
+  constexpr bool kSoftmaxChecksV = kVStages > 1;
   constexpr int kPanels = D / 64;                         // 64-wide (128-byte) panels along D
   constexpr uint32_t kPanelBytes = kTile * 128;           // 128 rows x 128 B
   constexpr uint32_t kTileBytes = kPanels * kPanelBytes;  // one of Q, K, V
   constexpr uint32_t kPBytes = kTile * kTile * 2;         // probabilities of one group
-  constexpr uint32_t kTmemColumns = G * (kTile + D) <= 256 ? 256 : 512;  // S and O_j per group
-  constexpr int kTmaWarp = 4 * G, kMmaWarp = 4 * G + 1;
+  constexpr uint32_t kTmemColumns = 512;
+  constexpr int kTmaWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1;
 
   extern __shared__ __align__(1024) unsigned char smem[];
-  __shared__ __align__(8) uint64_t q_full, s_full[G], p_full[G], o_full[G];
-  __shared__ __align__(8) uint64_t k_full[kKStages], k_empty[kKStages], v_full, v_empty;
+  __shared__ __align__(8) uint64_t q_full, s_full[G], s_free[G], p_full[G], o_done[G];
+  __shared__ __align__(8) uint64_t k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages];
+  // Static shared memory must stay below 3 KB: at D = 128 the tiles take 224 of the 227 KB.
+  __shared__ __nv_bfloat16 row_max_slot[2][G][2][kTile];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int failed;
 
-  TraceScope trace(7);
+  TraceScope trace(8);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q_block = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // heavy first
-  const int hq = blockIdx.y, b = blockIdx.z;
+  // Blocks are handed out with z slowest: every (batch, head) gets its heaviest query block (the
+  // last: most key tiles) before any gets a lighter one, so the lightest blocks fill the tail.
+  const int q_block = static_cast<int>(gridDim.z) - 1 - static_cast<int>(blockIdx.z);
+  const int hq = blockIdx.x, b = blockIdx.y;
   const int kvh = hq / p.groups;
   const int q0 = q_block * G * kTile;
   const int all_tiles = (p.tokens + kTile - 1) / kTile;
   // causal: group g (query tile G q_block + g) needs key tiles 0 .. its own
-  int tiles_of[G];
-#pragma unroll
-  for (int g = 0; g < G; ++g) tiles_of[g] = min(q_block * G + g + 1, all_tiles);
-  const int n_tiles = tiles_of[G - 1];
+  const int tiles_0 = min(q_block * G + 1, all_tiles), tiles_1 = min(q_block * G + 2, all_tiles);
+  auto tiles_of = [&](int g) { return g == 0 ? tiles_0 : tiles_1; };
+  const int n_tiles = tiles_1;
 
   const uint32_t q_smem = smem_u32(smem);                   // G tiles
   const uint32_t k_smem = q_smem + G * kTileBytes;          // two buffers
-  const uint32_t v_smem = k_smem + kKStages * kTileBytes;   // one buffer (wanted a softmax later than K)
-  const uint32_t p_smem = v_smem + kTileBytes;              // G x [2 panels][128 rows][128 B]
+  const uint32_t v_smem = k_smem + kKStages * kTileBytes;   // one or two buffers
+  const uint32_t p_smem = v_smem + kVStages * kTileBytes;   // G x [2 panels][128 rows][128 B]
 
   if (threadIdx.x == 0) {
     failed = 0;
     mbarrier_init(smem_u32(&q_full), 1);
     for (int g = 0; g < G; ++g) {
       mbarrier_init(smem_u32(&s_full[g]), 1);
-      mbarrier_init(smem_u32(&p_full[g]), 4);  // one arrival per softmax warp
-      mbarrier_init(smem_u32(&o_full[g]), 1);
+      mbarrier_init(smem_u32(&s_free[g]), 8);  // one arrival per softmax warp of the group
+      mbarrier_init(smem_u32(&p_full[g]), 8);
+      mbarrier_init(smem_u32(&o_done[g]), 1);
     }
     for (int s = 0; s < kKStages; ++s) {
       mbarrier_init(smem_u32(&k_full[s]), 1);
       mbarrier_init(smem_u32(&k_empty[s]), 1);
     }
-    mbarrier_init(smem_u32(&v_full), 1);
-    mbarrier_init(smem_u32(&v_empty), 1);
+    for (int s = 0; s < kVStages; ++s) {
+      mbarrier_init(smem_u32(&v_full[s]), 1);
+      mbarrier_init(smem_u32(&v_empty[s]), 1);
+    }
     fence_mbarrier_init();
   }
   if (warp == kMmaWarp) {
@@ -132,206 +149,262 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
       for (int panel = 0; panel < kPanels; ++panel)
         load_box(q_smem + g * kTileBytes + panel * kPanelBytes, &q_map, smem_u32(&q_full), panel * 64,
                  q0 + g * kTile, hq, b, p.q_token_dim1);
-    for (int j = 0; j < n_tiles; ++j) {
-      const int s = j & 1;
-      if (j >= kKStages && !mbarrier_wait_bounded(smem_u32(&k_empty[s]), ((j >> 1) - 1) & 1)) {
-        failed = 1;
-        break;
-      }
+    // K runs one tile ahead of V: K_{j+1} is wanted early in the softmax of tile j (for the next
+    // S), V_j only at its end, and a single V buffer is not free before the previous P V is done.
+    auto load_k = [&](int j) {
+      const int s = j % kKStages, use = j / kKStages;
+      if (use > 0 && !mbarrier_wait_bounded(smem_u32(&k_empty[s]), (use - 1) & 1)) return false;
       mbarrier_arrive_expect_tx(smem_u32(&k_full[s]), kTileBytes);
 #pragma unroll
       for (int panel = 0; panel < kPanels; ++panel)
         load_box(k_smem + s * kTileBytes + panel * kPanelBytes, &k_map, smem_u32(&k_full[s]),
                  panel * 64, j * kTile, kvh, b, p.k_token_dim1);
-      if (j >= 1 && !mbarrier_wait_bounded(smem_u32(&v_empty), (j - 1) & 1)) {
-        failed = 1;
-        break;
-      }
-      mbarrier_arrive_expect_tx(smem_u32(&v_full), kTileBytes);
+      return true;
+    };
+    bool ok = load_k(0);
+    for (int j = 0; ok && j < n_tiles; ++j) {
+      if (j + 1 < n_tiles) ok = load_k(j + 1);
+      if (!ok) break;
+      const int vs = j % kVStages, v_use = j / kVStages;
+      ok = v_use == 0 || mbarrier_wait_bounded(smem_u32(&v_empty[vs]), (v_use - 1) & 1);
+      if (!ok) break;
+      mbarrier_arrive_expect_tx(smem_u32(&v_full[vs]), kTileBytes);
 #pragma unroll
       for (int panel = 0; panel < kPanels; ++panel)
-        load_box(v_smem + panel * kPanelBytes, &v_map, smem_u32(&v_full), panel * 64, j * kTile, kvh,
-                 b, p.v_token_dim1);
+        load_box(v_smem + vs * kTileBytes + panel * kPanelBytes, &v_map, smem_u32(&v_full[vs]),
+                 panel * 64, j * kTile, kvh, b, p.v_token_dim1);
     }
+    if (!ok) failed = 1;
   } else if (warp == kMmaWarp && lane == 0) {
     // ---- MMA issuer ----
+    // A poll that follows a tcgen05.commit of the same thread takes a few hundred cycles, so this
+    // thread polls as little as it can: that a K or V tile has landed is checked by a softmax
+    // warp before it reports S read or P written.
     constexpr uint32_t idesc_s = instruction_descriptor(kTile, kTile);
     constexpr uint32_t idesc_o = instruction_descriptor(kTile, D, true);  // V: MN-major B operand
+    const uint64_t q_desc = smem_descriptor(q_smem), k_desc = smem_descriptor(k_smem);
+    const uint64_t p_desc = smem_descriptor(p_smem);
+    const uint64_t v_desc = smem_descriptor_mn_major(v_smem, kPanelBytes);
     auto issue_s = [&](int g, int j) {  // S_g = Q_g K_j^T, K = D
-      const uint32_t q_tile = q_smem + g * kTileBytes, k_tile = k_smem + (j & 1) * kTileBytes;
+      const uint64_t a = descriptor_advance(q_desc, g * kTileBytes);
+      const uint64_t bd = descriptor_advance(k_desc, (j % kKStages) * kTileBytes);
 #pragma unroll
       for (int ks = 0; ks < D / 16; ++ks) {
         const uint32_t offset = (ks / 4) * kPanelBytes + (ks % 4) * 32;
-        umma_bf16(s_column(g), smem_descriptor(q_tile + offset), smem_descriptor(k_tile + offset),
-                  idesc_s, ks > 0 ? 1u : 0u);
+        umma_bf16(s_column(g), descriptor_advance(a, offset), descriptor_advance(bd, offset), idesc_s,
+                  ks > 0 ? 1u : 0u);
       }
       umma_commit(smem_u32(&s_full[g]));
     };
-    auto issue_o = [&](int g) {  // O_j of group g = P_g V_j, K = 128 keys
-      const uint32_t p_tile = p_smem + g * kPBytes;
+    auto issue_o = [&](int g, int j) {  // O_g (+)= P_g V_j, K = 128 keys
+      const uint64_t a = descriptor_advance(p_desc, g * kPBytes);
+      const uint64_t bd = descriptor_advance(v_desc, (j % kVStages) * kTileBytes);
 #pragma unroll
       for (int ks = 0; ks < kTile / 16; ++ks) {
         const uint32_t p_offset = (ks / 4) * kPanelBytes + (ks % 4) * 32;
-        umma_bf16(o_column(g), smem_descriptor(p_tile + p_offset),
-                  smem_descriptor_mn_major(v_smem + ks * 2048, kPanelBytes), idesc_o, ks > 0 ? 1u : 0u);
+        umma_bf16(o_column(g), descriptor_advance(a, p_offset), descriptor_advance(bd, ks * 2048),
+                  idesc_o, (j > 0 || ks > 0) ? 1u : 0u);
       }
-      umma_commit(smem_u32(&o_full[g]));
+      umma_commit(smem_u32(&o_done[g]));
     };
-    bool ok = mbarrier_spin_bounded(smem_u32(&q_full), 0) &&
-              mbarrier_spin_bounded(smem_u32(&k_full[0]), 0);
+    bool ok = mbarrier_spin_bounded(smem_u32(&q_full), 0, kSpinLimit) &&
+              mbarrier_spin_bounded(smem_u32(&k_full[0]), 0, kSpinLimit);
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
       for (int g = 0; g < G; ++g) issue_s(g, 0);  // every group has key tile 0
-      umma_commit(smem_u32(&k_empty[0]));  // K_0 is free once these have been computed
+      umma_commit(smem_u32(&k_empty[0]));
     }
     for (int j = 0; ok && j < n_tiles; ++j) {
-      // Per group, once its softmax has written P_j (which also says that its S_j and its
-      // O_{j-1} have been read): first S of the next key tile, so that the group can take the
-      // row maxima of that tile while the tensor core computes O_j = P_j V_j behind it.
+      // S of the next key tile as soon as a group holds its current row of S in registers (its
+      // report also says that K_{j+1} has landed) ...
       const bool more = j + 1 < n_tiles;
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        const bool has_tile = j < tiles_of[g];
-        if (has_tile && !mbarrier_spin_bounded(smem_u32(&p_full[g]), j & 1)) {
-          ok = false;
-          break;
-        }
-        if (more && j + 1 < tiles_of[g]) {
-          if (!mbarrier_spin_bounded(smem_u32(&k_full[(j + 1) & 1]), ((j + 1) >> 1) & 1)) {
-            ok = false;
-            break;
+        if (ok && more && j + 1 < tiles_of(g)) {
+          ok = mbarrier_spin_bounded(smem_u32(&s_free[g]), j & 1, kSpinLimit);
+          if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_s(g, j + 1);
           }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_s(g, j + 1);
         }
-        if (more && g == G - 1) umma_commit(smem_u32(&k_empty[(j + 1) & 1]));  // K_{j+1}: all S issued
-        if (has_tile) {
-          if (!mbarrier_spin_bounded(smem_u32(&v_full), j & 1)) {
-            ok = false;
-            break;
-          }
-          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          issue_o(g);  // P_g is free again when o_full[g] fires
-        }
-        if (g == G - 1) umma_commit(smem_u32(&v_empty));  // V_j is free once its last reader retires
       }
+      if (ok && more) umma_commit(smem_u32(&k_empty[(j + 1) % kKStages]));  // K_{j+1}: all S issued
+      // ... and O += P V once the group has written its probabilities (and has seen V_j land)
+      bool v_landed = kSoftmaxChecksV;
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        if (ok && j < tiles_of(g)) {
+          ok = mbarrier_spin_bounded(smem_u32(&p_full[g]), j & 1, kSpinLimit) &&
+               (v_landed ||
+                mbarrier_spin_bounded(smem_u32(&v_full[j % kVStages]), (j / kVStages) & 1, kSpinLimit));
+          v_landed = true;
+          if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            issue_o(g, j);
+          }
+        }
+      }
+      if (ok) umma_commit(smem_u32(&v_empty[j % kVStages]));  // V_j is free once its last reader retires
     }
     if (!ok) failed = 1;
-  } else if (warp < 4 * G) {
-    // ---- softmax + epilogue: thread = query row = TMEM lane of its group ----
-    const int g = warp >> 2;
-    const int row = threadIdx.x & 127;
+  } else if (warp < kSoftmaxWarps) {
+    // ---- softmax + epilogue: two threads per query row, each with one half of the keys ----
+    // Warp w of a group may read the TMEM lanes 32 (w % 4) ..: warps w and w + 4 share 32 query
+    // rows and split the 128 key columns (and, where O is touched, its D columns) in halves.
+    const int g = warp >> 3, half = (warp >> 2) & 1;
+    const int row = ((warp & 3) << 5) | lane;
     const int q_tile = q_block * G + g;
-    const int my_tiles = tiles_of[g];
+    const int my_tiles = tiles_of(g);
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t s_taddr = s_column(g) + lane_base, o_taddr = o_column(g) + lane_base;
-    const uint32_t p_tile = p_smem + g * kPBytes;
-    float m_run = -INFINITY, l_run = 0.0f;
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.0f;
+    const uint32_t s_taddr = s_column(g) + lane_base + half * 64;
+    const uint32_t o_taddr = o_column(g) + lane_base + half * (D / 2);
+    const uint32_t p_row = p_smem + g * kPBytes + half * kPanelBytes + row * 128;  // panel = 64 keys
+    const uint32_t swizzle = row & 7;
+    const int key0 = half * 64;               // first key column of this thread inside a tile
+    const uint32_t group_barrier = 1 + g;     // named barrier of the group's 256 threads
+    float m_ref = -INFINITY, l_run = 0.0f;
     bool ok = true;
-    float alpha_pending = 0.0f;  // factor of the O_j that is still in tensor memory
-    auto fold = [&](int j) {     // o = o * alpha_j + O_j
-      if (!mbarrier_wait_ready_first(smem_u32(&o_full[g]), j & 1)) return false;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        float v[32];
-        tmem_load_32x32(o_taddr + c0, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], alpha_pending, v[i]);
-      }
-      return true;
-    };
     for (int j = 0; j < my_tiles; ++j) {
-      if (!mbarrier_wait_ready_first(smem_u32(&s_full[g]), j & 1)) {
-        ok = false;
-        break;
+      // A wait that gives up ends this warp's work, but the warp keeps meeting the group at the
+      // named barrier once per tile. (Every wait's outcome is made warp-uniform: the
+      // tensor-memory accesses are warp-collective.)
+      ok = ok && __all_sync(0xffffffffu, mbarrier_wait_ready_first(smem_u32(&s_full[g]), j & 1));
+      uint32_t s0[32], s1[32];  // this thread's half of the row of S
+      __nv_bfloat16 half_max = __float2bfloat16_rn(0.0f);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        tmem_load_32x32_issue(s_taddr, s0);
+        tmem_load_32x32_issue(s_taddr + 32, s1);
+        tmem_load_wait(s0);
+        tmem_load_wait(s1);
+        // S is free for the product with the next key tile
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          // the group's first warp vouches for K_{j+1}: the MMA thread then needs one poll, not two
+          bool landed = true;
+          if ((warp & 7) == 0 && j + 1 < my_tiles)
+            landed = mbarrier_wait_ready_first(smem_u32(&k_full[(j + 1) % kKStages]), ((j + 1) / kKStages) & 1);
+          if (landed)
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&s_free[g])) : "memory");
+          else
+            failed = 1;
+        }
+        if (j == q_tile) {  // diagonal tile: keys beyond the row's own position are masked
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (key0 + i > row) s0[i] = 0xff800000u;
+            if (key0 + i + 32 > row) s1[i] = 0xff800000u;
+          }
+        }
+        float max0 = -INFINITY, max1 = -INFINITY, max2 = -INFINITY, max3 = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          max0 = fmaxf(max0, __uint_as_float(s0[i]));
+          max1 = fmaxf(max1, __uint_as_float(s0[i + 1]));
+          max2 = fmaxf(max2, __uint_as_float(s1[i]));
+          max3 = fmaxf(max3, __uint_as_float(s1[i + 1]));
+        }
+        half_max = __float2bfloat16_rn(fmaxf(fmaxf(max0, max1), fmaxf(max2, max3)));
       }
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const bool diagonal = j == q_tile;  // keys beyond the row's own position are masked
-      float row_max = -INFINITY;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kTile; c0 += 32) {
-        float s[32];
-        tmem_load_32x32(s_taddr + c0, s);
-        if (diagonal) {
+      // The two halves of a row exchange their maxima (two slots: a thread may be one tile ahead),
+      // rounded to bf16 on both sides so that both take the same reference: it only has to be
+      // near the maximum, not equal to it.
+      row_max_slot[j & 1][g][half][row] = half_max;
+      asm volatile("bar.sync %0, 256;" ::"r"(group_barrier) : "memory");
+      const float m_tile = fmaxf(__bfloat162float(half_max),
+                                 __bfloat162float(row_max_slot[j & 1][g][half ^ 1][row])) * p.scale_log2;
+      if (ok && j == 0) m_ref = m_tile;  // O is still empty: the first product overwrites it
+      if (ok && j > 0) {
+        const bool raise = __any_sync(0xffffffffu, m_tile > m_ref + kRescaleThreshold);
+        // P and O are in use until the group's previous product has completed
+        ok = __all_sync(0xffffffffu, mbarrier_wait_ready_first(smem_u32(&o_done[g]), (j - 1) & 1));
+        if (ok && raise) {  // warp-uniform: move the reference maximum of the warp's rows
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const float m_new = fmaxf(m_ref, m_tile);
+          const float factor = exp2_fast(m_ref - m_new);
+          l_run *= factor;
+          m_ref = m_new;
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c0 + i <= row) row_max = fmaxf(row_max, s[i]);
-        } else {
+          for (int c0 = 0; c0 < D / 2; c0 += 32) {  // this thread's half of the row of O
+            float v[32];
+            tmem_load_32x32(o_taddr + c0, v);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) row_max = fmaxf(row_max, s[i]);
+            for (int i = 0; i < 32; ++i) v[i] *= factor;
+            tmem_store_32x32(o_taddr + c0, v);
+          }
+          tmem_store_wait();
         }
       }
-      const float m_new = fmaxf(m_run, row_max * p.scale_log2);  // key 0 is never masked
-      const float alpha = exp2_fast(m_run - m_new);              // exp2(-inf) = 0 at the first tile
-      // O_{j-1} ran on the tensor core during the pass above; P is free once it is complete
-      if (j > 0 && !fold(j - 1)) {
-        ok = false;
-        break;
-      }
-      alpha_pending = alpha;
-      float sum = 0.0f;
-#pragma unroll 1
-      for (int c0 = 0; c0 < kTile; c0 += 32) {
-        float s[32];
-        tmem_load_32x32(s_taddr + c0, s);
+      if (!ok) continue;
+      const float neg_ref = -m_ref;
+      float sum0 = 0.0f, sum1 = 0.0f;
+      auto emit = [&](const uint32_t (&s)[32], int c0) {  // 32 probabilities: exp2, sum, bf16, store
         uint32_t packed[16];
-        if (diagonal) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float p0 = exp2_fast(fmaf(s[i], p.scale_log2, -m_new));
-            float p1 = exp2_fast(fmaf(s[i + 1], p.scale_log2, -m_new));
-            if (c0 + i > row) p0 = 0.0f;
-            if (c0 + i + 1 > row) p1 = 0.0f;
-            sum += p0 + p1;
-            packed[i / 2] = pack_bf16x2(p0, p1);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = exp2_fast(fmaf(s[i], p.scale_log2, -m_new));
-            const float p1 = exp2_fast(fmaf(s[i + 1], p.scale_log2, -m_new));
-            sum += p0 + p1;
-            packed[i / 2] = pack_bf16x2(p0, p1);
-          }
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = exp2_fast(fmaf(__uint_as_float(s[i]), p.scale_log2, neg_ref));
+          const float p1 = exp2_fast(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, neg_ref));
+          sum0 += p0;
+          sum1 += p1;
+          packed[i / 2] = pack_bf16x2(p0, p1);
         }
-        // K-major A operand: panel = 64 keys, row = query, 16-byte chunks XOR-swizzled by row % 8
-        const uint32_t panel = p_tile + (c0 / 64) * kPanelBytes + row * 128;
+        // K-major A operand: row = query, 16-byte chunks of the 128-byte row XOR-swizzled by row % 8
 #pragma unroll
         for (int chunk = 0; chunk < 4; ++chunk) {
-          const int logical = (c0 % 64) / 8 + chunk;
-          const uint32_t address = panel + ((logical ^ (row & 7)) << 4);
+          const uint32_t logical = c0 / 8 + chunk;
+          const uint32_t address = p_row + ((logical ^ swizzle) << 4);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(address),
                        "r"(packed[chunk * 4]), "r"(packed[chunk * 4 + 1]),
                        "r"(packed[chunk * 4 + 2]), "r"(packed[chunk * 4 + 3]) : "memory");
         }
-      }
-      l_run = l_run * alpha + sum;
-      m_run = m_new;
+      };
+      emit(s0, 0);
+      emit(s1, 32);
+      l_run += sum0 + sum1;
       // generic-proxy writes of P must be visible to the tensor core (async proxy)
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       __syncwarp();
-      if (lane == 0)
-        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_full[g])) : "memory");
+      if (lane == 0) {
+        bool landed = true;  // likewise for V_j
+        if (kSoftmaxChecksV && (warp & 7) == 0)
+          landed = mbarrier_wait_ready_first(smem_u32(&v_full[j % kVStages]), (j / kVStages) & 1);
+        if (landed)
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_full[g])) : "memory");
+        else
+          failed = 1;
+      }
     }
-    if (ok && my_tiles > 0) ok = fold(my_tiles - 1);
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    if (ok && my_tiles > 0)
+      ok = __all_sync(0xffffffffu, mbarrier_wait_ready_first(smem_u32(&o_done[g]), (my_tiles - 1) & 1));
+    // The row sum is the sum of the two halves (both took the same reference maximum); they meet
+    // in the first K buffer, which nothing reads any more once the last product has completed
+    // (on the failure path the sums are not used).
+    float* row_sum_slot = reinterpret_cast<float*>(smem + G * kTileBytes) + g * 2 * kTile;
+    row_sum_slot[half * kTile + row] = l_run;
+    asm volatile("bar.sync %0, 256;" ::"r"(group_barrier) : "memory");
     const int q_row = q0 + g * kTile + row;
     if (!ok) {
       failed = 1;
-    } else if (q_row < p.tokens) {
-      const float inv = 1.0f / l_run;
-      __nv_bfloat16* dst = p.out + ((static_cast<int64_t>(b) * p.tokens + q_row) * p.q_heads + hq) * D;
+    } else {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float inv = 1.0f / (l_run + row_sum_slot[(half ^ 1) * kTile + row]);
+      __nv_bfloat16* dst = p.out + ((static_cast<int64_t>(b) * p.tokens + q_row) * p.q_heads + hq) * D +
+                           half * (D / 2);
 #pragma unroll
-      for (int i = 0; i < D; i += 8)
-        *reinterpret_cast<uint4*>(dst + i) =
-            make_uint4(pack_bf16x2(o[i] * inv, o[i + 1] * inv), pack_bf16x2(o[i + 2] * inv, o[i + 3] * inv),
-                       pack_bf16x2(o[i + 4] * inv, o[i + 5] * inv), pack_bf16x2(o[i + 6] * inv, o[i + 7] * inv));
+      for (int c0 = 0; c0 < D / 2; c0 += 32) {
+        float v[32];
+        tmem_load_32x32(o_taddr + c0, v);  // warp-collective: rows past the end load too
+        if (q_row < p.tokens) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8)
+            *reinterpret_cast<uint4*>(dst + c0 + i) = make_uint4(
+                pack_bf16x2(v[i] * inv, v[i + 1] * inv), pack_bf16x2(v[i + 2] * inv, v[i + 3] * inv),
+                pack_bf16x2(v[i + 4] * inv, v[i + 5] * inv), pack_bf16x2(v[i + 6] * inv, v[i + 7] * inv));
+        }
+      }
     }
   }
   __syncwarp();
@@ -359,13 +432,8 @@ int prefill_attention_tcgen05(const void* query, const void* key, const void* va
   if (path != nullptr && strcmp(path, "mma.sync") == 0) return B200_ERR_UNSUPPORTED;
   if (head_dim != 64 && head_dim != 128) return B200_ERR_UNSUPPORTED;
   if (!(scale > 0.0) || tokens < 1) return B200_ERR_UNSUPPORTED;
-  // One query tile per CTA (two CTAs per SM at D = 64) unless B200_PREFILL_QUERY_TILES=2 asks for
-  // two tiles per CTA at D = 64: measured equal within 3 % either way from 1024 to 16384 tokens.
-  int query_tiles = 1;
-  const char* tiles_text = getenv("B200_PREFILL_QUERY_TILES");
-  if (tiles_text != nullptr && strcmp(tiles_text, "2") == 0 && head_dim == 64) query_tiles = 2;
-  const int64_t q_blocks = ceil_div(tokens, static_cast<int64_t>(kTile) * query_tiles);
-  if (q_blocks > 65535 || q_heads > 65535 || batch > 65535) return B200_ERR_UNSUPPORTED;
+  const int64_t q_blocks = ceil_div(tokens, static_cast<int64_t>(kTile) * kGroups);
+  if (q_blocks > 65535 || batch > 65535) return B200_ERR_UNSUPPORTED;
   CUtensorMap q_map, k_map, v_map;
   bool q_dim1, k_dim1, v_dim1;
   if (!make_bf16_bhtd_map(&q_map, query, batch, q_heads, tokens, head_dim, query_strides[0],
@@ -385,27 +453,19 @@ int prefill_attention_tcgen05(const void* query, const void* key, const void* va
   p.k_token_dim1 = k_dim1 ? 1 : 0;
   p.v_token_dim1 = v_dim1 ? 1 : 0;
   p.scale_log2 = static_cast<float>(scale) * kLog2e;
-  dim3 grid(static_cast<unsigned>(q_blocks), static_cast<unsigned>(q_heads),
-            static_cast<unsigned>(batch));
-  // G query tiles + two K tiles + one V tile + G tiles of probabilities
+  dim3 grid(static_cast<unsigned>(q_heads), static_cast<unsigned>(batch), static_cast<unsigned>(q_blocks));
   const int tile_bytes = static_cast<int>(head_dim) * kTile * 2;
-  const int smem = tile_bytes * (query_tiles + kKStages + 1) + query_tiles * kTile * kTile * 2;
-  const int threads = (4 * query_tiles + 2) * 32;
+  const int v_stages = head_dim == 64 ? 2 : 1;
+  // the pair of Q tiles, two K tiles, one or two V tiles, the pair of probability tiles
+  const int smem = tile_bytes * (kGroups + kKStages + v_stages) + kGroups * kTile * kTile * 2;
   auto launch = [&](auto kernel) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return false;
-    // two single-group CTAs per SM need the largest shared-memory carve-out
-    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                         cudaSharedmemCarveoutMaxShared);
-    kernel<<<grid, threads, smem, stream>>>(p, q_map, k_map, v_map);
+    kernel<<<grid, kThreads, smem, stream>>>(p, q_map, k_map, v_map);
     return true;
   };
-  bool launched;
-  if (head_dim == 64)
-    launched = query_tiles == 2 ? launch(prefill_attention_tcgen05_kernel<64, 2>)
-                                : launch(prefill_attention_tcgen05_kernel<64, 1>);
-  else
-    launched = launch(prefill_attention_tcgen05_kernel<128, 1>);
+  const bool launched = head_dim == 64 ? launch(prefill_attention_tcgen05_kernel<64>)
+                                       : launch(prefill_attention_tcgen05_kernel<128>);
   if (!launched) return B200_ERR_LAUNCH;
   return launch_status();
 }
