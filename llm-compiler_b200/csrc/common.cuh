@@ -210,6 +210,12 @@ __device__ __forceinline__ float bf16_lo(uint32_t packed) { return __uint_as_flo
 __device__ __forceinline__ float bf16_hi(uint32_t packed) {
   return __uint_as_float(packed & 0xffff0000u);
 }
+// Two values rounded to bf16 with one conversion instruction instead of two.
+__device__ __forceinline__ void round_bf16_pair(float& a, float& b) {
+  const uint32_t packed = pack_bf16x2(a, b);
+  a = bf16_lo(packed);
+  b = bf16_hi(packed);
+}
 
 // Element traits so that one kernel body serves f32 and bf16 tensors.
 template <typename T>

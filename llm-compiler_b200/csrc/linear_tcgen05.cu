@@ -216,10 +216,18 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
       if (p.epilogue == B200_EPILOGUE_SWIGLU) {
         // columns 2j / 2j+1 are gate_j / up_j
         __nv_bfloat16* dst = p.out + static_cast<int64_t>(row) * out_cols + col0 / 2;
+        // y = r(r(silu(r(gate))) * r(up)): the roundings go through the conversion unit, which
+        // the exponentials and reciprocals of silu also queue for, so they are taken in pairs
         float y[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j)
-          y[j] = round_bf16(silu_f32(round_bf16(v[2 * j]))) * round_bf16(v[2 * j + 1]);
+        for (int j = 0; j < 16; j += 2) {
+          round_bf16_pair(v[2 * j], v[2 * j + 1]);
+          round_bf16_pair(v[2 * j + 2], v[2 * j + 3]);
+          float g0 = silu_f32(v[2 * j]), g1 = silu_f32(v[2 * j + 2]);
+          round_bf16_pair(g0, g1);
+          y[j] = g0 * v[2 * j + 1];
+          y[j + 1] = g1 * v[2 * j + 3];
+        }
         if (col0 + 32 <= n_end && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
           for (int i = 0; i < 2; ++i)
@@ -234,13 +242,13 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
         continue;
       }
       const int64_t o = static_cast<int64_t>(row) * p.n + col0;
+      if (p.epilogue == B200_EPILOGUE_RESIDUAL) {  // r(r(x W^T + b) + residual)
 #pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = round_bf16(v[i]);
-      if (p.epilogue == B200_EPILOGUE_RESIDUAL) {
+        for (int i = 0; i < 32; i += 2) round_bf16_pair(v[i], v[i + 1]);
 #pragma unroll
         for (int i = 0; i < 32; ++i)
           if (col0 + i < n_end) v[i] = __fadd_rn(v[i], __bfloat162float(p.residual[o + i]));
-      }
+      }  // (without a residual the store below is the one rounding)
       __nv_bfloat16* dst = p.out + o;
       if (col0 + 32 <= n_end && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll

@@ -187,6 +187,33 @@ def rms_norm_case(args):
             "us": seconds * 1e6, "gbs": rows * hidden * 4 / seconds / 1e9}
 
 
+def prefill_step_case(args):
+    """Stateful prefill of --batch prompts of --tokens tokens through Qwen2Engine.prefill (Qwen2-0.5B
+    or, with --model qwen2-7b, Qwen2-7B architecture; random weights, random token ids): embedding,
+    RoPE table, then per layer RMSNorm, q|k|v GEMM, RoPE, KV store, causal attention, o GEMM with the
+    residual, RMSNorm, gate|up GEMM with SwiGLU, down GEMM with the residual; last-position logits
+    and the greedy token. Prompt tokens per second, device-timed."""
+
+    from llm_compiler_b200 import qwen2 as q2
+    from llm_compiler_b200.engine import Qwen2Engine
+
+    device = torch.device("cuda", torch.cuda.current_device())
+    config = q2.QWEN2_7B if args.model == "qwen2-7b" else q2.QWEN2_0_5B
+    weights = q2.make_weights(config, seed=0, dtype=torch.bfloat16, device=device, reproducible=False)
+    engine = Qwen2Engine(config, weights, batch=args.batch, capacity=args.tokens + 64)
+    ids = torch.randint(0, config.vocab_size, (args.batch, args.tokens), device=device)
+    seconds = time_launches(lambda _: engine.prefill(ids), 1, min(args.warmup, 3), min(args.iters, 10))
+    layer_params = (config.hidden_size * (config.q_size + 2 * config.kv_size) + config.q_size * config.hidden_size +
+                    3 * config.hidden_size * config.intermediate_size)
+    tokens = args.batch * args.tokens
+    gemm_flops = 2 * tokens * layer_params * config.num_layers
+    attention_flops = 2 * args.batch * config.num_heads * args.tokens ** 2 * config.head_dim * config.num_layers
+    return {"op": "prefill_step", "model": args.model, "batch": args.batch, "tokens": args.tokens,
+            "ms": seconds * 1e3, "prompt_tokens_per_s": tokens / seconds,
+            "tflops": (gemm_flops + attention_flops) / seconds / 1e12,
+            "gemm_tflop": gemm_flops / 1e12, "causal_attention_tflop": attention_flops / 1e12}
+
+
 def timeline_case(args):
     """Per-launch device timeline of one replayed decode step (Qwen2-0.5B architecture, random
     weights, synthetic KV of --length tokens). Needs the library built with
@@ -320,7 +347,9 @@ def profile_case(args):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("op", choices=["decode_attention", "prefill_attention", "kv_store", "linear",
-                                       "rms_norm", "timeline", "profile"])
+                                       "rms_norm", "timeline", "profile", "prefill_step"])
+    parser.add_argument("--model", default="qwen2-0.5b", choices=["qwen2-0.5b", "qwen2-7b"],
+                        help="prefill_step: architecture")
     parser.add_argument("--output", default="dispatch_profile.json", help="profile: file to write")
     parser.add_argument("--launches", type=int, default=40, help="timeline: launches to print")
     parser.add_argument("--batch", type=int, default=64)
@@ -364,6 +393,8 @@ def main():
         print(json.dumps(timeline_case(args)))
     elif args.op == "profile":
         print(json.dumps(profile_case(args)))
+    elif args.op == "prefill_step":
+        print(json.dumps(prefill_step_case(args)))
     else:
         print(json.dumps(rms_norm_case(args)))
     kernels.runtime().check_status()
