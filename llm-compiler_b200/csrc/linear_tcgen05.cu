@@ -60,6 +60,66 @@ __device__ __forceinline__ float silu_f32(float x) {
   return __fdividef(x, 1.0f + exp2f(-1.4426950408889634f * x));
 }
 
+// The bf16 epilogue of 32 accumulator columns of one output row: bias, then SwiGLU (columns
+// 2j / 2j+1 are gate_j / up_j) or the residual, with the reference's bf16 rounding points.
+__device__ __forceinline__ void store_chunk(const Tcgen05Params& p, int row, int col0, int n_end,
+                                            float (&v)[32]) {
+  const int out_cols = p.epilogue == B200_EPILOGUE_SWIGLU ? p.n / 2 : p.n;
+  if (p.bias != nullptr) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (col0 + i < n_end) v[i] += __bfloat162float(p.bias[col0 + i]);
+  }
+  if (p.epilogue == B200_EPILOGUE_SWIGLU) {
+    // columns 2j / 2j+1 are gate_j / up_j
+    __nv_bfloat16* dst = p.out + static_cast<int64_t>(row) * out_cols + col0 / 2;
+    // y = r(r(silu(r(gate))) * r(up)): the roundings go through the conversion unit, which
+    // the exponentials and reciprocals of silu also queue for, so they are taken in pairs
+    float y[16];
+#pragma unroll
+    for (int j = 0; j < 16; j += 2) {
+      round_bf16_pair(v[2 * j], v[2 * j + 1]);
+      round_bf16_pair(v[2 * j + 2], v[2 * j + 3]);
+      float g0 = silu_f32(v[2 * j]), g1 = silu_f32(v[2 * j + 2]);
+      round_bf16_pair(g0, g1);
+      y[j] = g0 * v[2 * j + 1];
+      y[j + 1] = g1 * v[2 * j + 3];
+    }
+    if (col0 + 32 <= n_end && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+        reinterpret_cast<uint4*>(dst)[i] =
+            make_uint4(pack_bf16x2(y[8 * i], y[8 * i + 1]), pack_bf16x2(y[8 * i + 2], y[8 * i + 3]),
+                       pack_bf16x2(y[8 * i + 4], y[8 * i + 5]), pack_bf16x2(y[8 * i + 6], y[8 * i + 7]));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (col0 + 2 * j + 1 < n_end) dst[j] = __float2bfloat16_rn(y[j]);
+    }
+    return;
+  }
+  const int64_t o = static_cast<int64_t>(row) * p.n + col0;
+  if (p.epilogue == B200_EPILOGUE_RESIDUAL) {  // r(r(x W^T + b) + residual)
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) round_bf16_pair(v[i], v[i + 1]);
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (col0 + i < n_end) v[i] = __fadd_rn(v[i], __bfloat162float(p.residual[o + i]));
+  }  // (without a residual the store below is the one rounding)
+  __nv_bfloat16* dst = p.out + o;
+  if (col0 + 32 <= n_end && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      reinterpret_cast<uint4*>(dst)[i] =
+          make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
+                     pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (col0 + i < n_end) dst[i] = __float2bfloat16_rn(v[i]);
+  }
+}
+
 // A_ROWS: rows of the x box a stage holds. With at most 64 activation rows (decode) the box
 // is 64 rows and the MMA, which always spans 128 rows, reads on into the W tile behind it:
 // accumulator lanes 64..127 then hold junk that the epilogue never touches (rows >= M).
@@ -181,7 +241,6 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   ok = ok && failed == 0;
   if (ok) {
     const int row = tile_m * kBM + warp * 32 + lane;
-    const int out_cols = p.epilogue == B200_EPILOGUE_SWIGLU ? p.n / 2 : p.n;
 #pragma unroll 1
     const int n_end = min(p.n, (tile_n + 1) * bn);  // columns of this tile
     for (int c0 = 0; c0 < bn; c0 += 32) {
@@ -208,59 +267,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
         }
         continue;
       }
-      if (p.bias != nullptr) {
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (col0 + i < n_end) v[i] += __bfloat162float(p.bias[col0 + i]);
-      }
-      if (p.epilogue == B200_EPILOGUE_SWIGLU) {
-        // columns 2j / 2j+1 are gate_j / up_j
-        __nv_bfloat16* dst = p.out + static_cast<int64_t>(row) * out_cols + col0 / 2;
-        // y = r(r(silu(r(gate))) * r(up)): the roundings go through the conversion unit, which
-        // the exponentials and reciprocals of silu also queue for, so they are taken in pairs
-        float y[16];
-#pragma unroll
-        for (int j = 0; j < 16; j += 2) {
-          round_bf16_pair(v[2 * j], v[2 * j + 1]);
-          round_bf16_pair(v[2 * j + 2], v[2 * j + 3]);
-          float g0 = silu_f32(v[2 * j]), g1 = silu_f32(v[2 * j + 2]);
-          round_bf16_pair(g0, g1);
-          y[j] = g0 * v[2 * j + 1];
-          y[j + 1] = g1 * v[2 * j + 3];
-        }
-        if (col0 + 32 <= n_end && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-#pragma unroll
-          for (int i = 0; i < 2; ++i)
-            reinterpret_cast<uint4*>(dst)[i] =
-                make_uint4(pack_bf16x2(y[8 * i], y[8 * i + 1]), pack_bf16x2(y[8 * i + 2], y[8 * i + 3]),
-                           pack_bf16x2(y[8 * i + 4], y[8 * i + 5]), pack_bf16x2(y[8 * i + 6], y[8 * i + 7]));
-        } else {
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            if (col0 + 2 * j + 1 < n_end) dst[j] = __float2bfloat16_rn(y[j]);
-        }
-        continue;
-      }
-      const int64_t o = static_cast<int64_t>(row) * p.n + col0;
-      if (p.epilogue == B200_EPILOGUE_RESIDUAL) {  // r(r(x W^T + b) + residual)
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) round_bf16_pair(v[i], v[i + 1]);
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (col0 + i < n_end) v[i] = __fadd_rn(v[i], __bfloat162float(p.residual[o + i]));
-      }  // (without a residual the store below is the one rounding)
-      __nv_bfloat16* dst = p.out + o;
-      if (col0 + 32 <= n_end && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          reinterpret_cast<uint4*>(dst)[i] =
-              make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
-                         pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (col0 + i < n_end) dst[i] = __float2bfloat16_rn(v[i]);
-      }
+      store_chunk(p, row, col0, n_end, v);
     }
   } else if (threadIdx.x == 0 && p.status != nullptr) {
     atomicOr(p.status, B200_STATUS_WAIT_TIMEOUT);
@@ -272,6 +279,176 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
                  ::"r"(tmem_base), "r"(static_cast<uint32_t>(kTmemColumns)) : "memory");
   trace.mark(1);
+}
+
+// Prefill-size M: a persistent kernel, one CTA per SM walking 128 x bn output tiles (bn up to
+// 256), with two accumulators in tensor memory so that the epilogue of one tile runs under the
+// main loop of the next. With K = 896 (14 k-blocks) the epilogue of a 128 x 256 tile is about a
+// third of its main loop; unhidden it capped these GEMMs near 0.45 of the tensor peak.
+// Roles: warps 0-3 epilogue (warp w reads TMEM lanes 32 w ..), warp 4 (one lane) TMA producer,
+// warp 5 (one lane) MMA issuer and owner of the 512 TMEM columns. The stage ring runs on across
+// tile boundaries: the producer is already fetching the next tile while the last k-blocks of
+// the current one are multiplied. Tiles are taken round-robin with N fastest, so the CTAs that
+// run at the same time share their rows of x and the (small) W in L2.
+constexpr int kPersistentStages = 4;
+constexpr int kPersistentThreads = 192;
+constexpr int kPersistentBN = 256;
+
+__global__ void __launch_bounds__(kPersistentThreads, 1)
+linear_tcgen05_persistent_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap a_map,
+                                 const __grid_constant__ CUtensorMap b_map) {
+  constexpr int STAGES = kPersistentStages;
+  constexpr int kABytes = kBM * 128;
+  constexpr int kStageBytes = kABytes + kPersistentBN * 128;
+  const int bn = p.bn;
+  const uint32_t idesc = instruction_descriptor(kBM, bn);
+  const uint32_t stage_tx_bytes = static_cast<uint32_t>(kABytes + bn * 128);
+
+  extern __shared__ __align__(1024) unsigned char smem[];
+  __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t acc_full[2], acc_empty[2];
+  __shared__ uint32_t tmem_base_slot;
+  __shared__ int failed;
+
+  TraceScope trace(9);
+  grid_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nkb = (p.k + kBK - 1) / kBK;
+  const int tiles_n = (p.n + bn - 1) / bn;
+  const int tiles = tiles_n * ((p.m + kBM - 1) / kBM);
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (threadIdx.x == 0) {
+    failed = 0;
+#pragma unroll
+    for (int s = 0; s < STAGES; ++s) {
+      mbarrier_init(smem_u32(&full_bar[s]), 1);
+      mbarrier_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbarrier_init(smem_u32(&acc_full[a]), 1);
+      mbarrier_init(smem_u32(&acc_empty[a]), 4);  // one arrival per epilogue warp
+    }
+    fence_mbarrier_init();
+  }
+  if (warp == 5) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(&tmem_base_slot)), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = tmem_base_slot;
+
+  if (warp == 4 && lane == 0) {
+    // ---- TMA producer ----
+    grid_dependency_wait();
+    int round = 0;  // k-blocks issued so far, over all tiles
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x) {
+      const int tile_n = tile % tiles_n, tile_m = tile / tiles_n;
+      for (int kb = 0; kb < nkb; ++kb, ++round) {
+        const int s = round % STAGES;
+        if (round >= STAGES &&
+            !mbarrier_wait_bounded(smem_u32(&empty_bar[s]), ((round / STAGES) - 1) & 1)) {
+          ok = false;
+          break;
+        }
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        const uint32_t a_dst = smem_base + s * kStageBytes;
+        mbarrier_arrive_expect_tx(bar, stage_tx_bytes);
+        tma_load_2d(a_dst, &a_map, bar, kb * kBK, tile_m * kBM);
+        tma_load_2d(a_dst + kABytes, &b_map, bar, kb * kBK, tile_n * bn);
+      }
+    }
+    if (!ok) failed = 1;
+  } else if (warp == 5 && lane == 0) {
+    // ---- MMA issuer ----
+    grid_dependency_wait();
+    int round = 0, local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x, ++local) {
+      const int acc = local & 1;
+      // the epilogue must have read this accumulator's previous tile
+      if (local >= 2 && !mbarrier_wait_bounded(smem_u32(&acc_empty[acc]), ((local >> 1) - 1) & 1)) {
+        ok = false;
+        break;
+      }
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const uint32_t d_tmem = tmem_base + acc * kPersistentBN;
+      for (int kb = 0; kb < nkb; ++kb, ++round) {
+        const int s = round % STAGES;
+        if (!mbarrier_wait_bounded(smem_u32(&full_bar[s]), (round / STAGES) & 1)) {
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_addr = smem_base + s * kStageBytes;
+        const uint32_t b_addr = a_addr + kABytes;
+#pragma unroll
+        for (int j = 0; j < kBK / 16; ++j)
+          umma_bf16(d_tmem, smem_descriptor(a_addr + j * 32), smem_descriptor(b_addr + j * 32), idesc,
+                    (kb > 0 || j > 0) ? 1u : 0u);
+        umma_commit(smem_u32(&empty_bar[s]));  // the stage is free once these MMAs have read it
+      }
+      if (ok) umma_commit(smem_u32(&acc_full[acc]));  // the tile's accumulator is complete
+    }
+    if (!ok) failed = 1;
+  } else if (warp < 4) {
+    // ---- epilogue: warp w owns TMEM lanes 32 w .. 32 w + 31 = 32 output rows of the tile ----
+    grid_dependency_wait();  // the residual was written by an earlier kernel
+    int local = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+      const int acc = local & 1;
+      const int tile_n = tile % tiles_n, tile_m = tile / tiles_n;
+      // (the wait's outcome is made warp-uniform: tcgen05.ld is a warp-wide instruction)
+      ok = ok && __all_sync(0xffffffffu, mbarrier_wait_bounded(smem_u32(&acc_full[acc]), (local >> 1) & 1));
+      if (!ok) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int row = tile_m * kBM + warp * 32 + lane;
+      const int n_end = min(p.n, (tile_n + 1) * bn);
+      const uint32_t t_addr = tmem_base + acc * kPersistentBN + (static_cast<uint32_t>(warp * 32) << 16);
+#pragma unroll 1
+      for (int c0 = 0; c0 < bn; c0 += 32) {
+        const int col0 = tile_n * bn + c0;
+        if (col0 >= n_end) break;  // warp-uniform
+        float v[32];
+        tmem_load_32x32(t_addr + c0, v);
+        if (row < p.m) store_chunk(p, row, col0, n_end, v);
+      }
+      // the accumulator may be overwritten by the tile after next
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0)
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&acc_empty[acc])) : "memory");
+    }
+    if (!ok) failed = 1;
+  }
+  __syncwarp();
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (failed && threadIdx.x == 0 && p.status != nullptr) atomicOr(p.status, B200_STATUS_WAIT_TIMEOUT);
+  if (warp == 5)
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u)
+                 : "memory");
+  trace.mark(1);
+}
+
+int launch_persistent(const Tcgen05Params& p, const CUtensorMap& a_map, const CUtensorMap& b_map,
+                      cudaStream_t stream) {
+  constexpr int smem = kPersistentStages * (kBM + kPersistentBN) * 128 + 1024;
+  static_assert(smem <= 227 * 1024, "stage ring exceeds shared memory");
+  auto kernel = linear_tcgen05_persistent_kernel;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    return B200_ERR_LAUNCH;
+  if (p.bn <= 0 || p.bn > kPersistentBN || p.bn % 16 != 0) return B200_ERR_BAD_ARGUMENT;
+  const int64_t tiles = ceil_div(p.n, p.bn) * ceil_div(p.m, kBM);
+  dim3 grid(static_cast<unsigned>(tiles < kNumSMs ? tiles : kNumSMs));
+  if (launch_chained(kernel, grid, dim3(kPersistentThreads), smem, stream, p, a_map, b_map) != cudaSuccess)
+    return B200_ERR_LAUNCH;
+  return launch_status();
 }
 
 template <int BN, int STAGES, int A_ROWS>
@@ -331,8 +508,28 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
                    int epilogue, int32_t* status, cudaStream_t stream) {
   if (ceil_div(m, kBM) > 65535) return B200_ERR_UNSUPPORTED;
   int bn;
+  bool persistent = false;
   if (m > 64) {
     bn = n % 256 == 0 || n > 1024 ? 256 : 128;
+    // From a few tiles per SM on, the persistent kernel (B200_LINEAR_PERSISTENT=0 keeps one tile
+    // per CTA, for comparison). Its tile width is the multiple of 16 up to 256 that wastes the
+    // fewest columns of the last N tile (896 -> 224, 1152 -> 192); 256 if that pads N by at most 1.5 %.
+    const char* persistent_text = getenv("B200_LINEAR_PERSISTENT");
+    if (m >= 1024 && (persistent_text == nullptr || strcmp(persistent_text, "0") != 0)) {
+      persistent = true;
+      int64_t least = -1;
+      for (int candidate = 256; candidate >= 128; candidate -= 16) {
+        const int64_t waste = ceil_div(n, candidate) * candidate - n;
+        if (waste * 64 <= n) {  // the widest tile that pads N by at most 1.5 %
+          bn = candidate;
+          break;
+        }
+        if (least < 0 || waste < least) {
+          least = waste;
+          bn = candidate;
+        }
+      }
+    }
   } else {
     // Weight streaming with one deep-pipelined CTA per SM: the N tile is the width (a
     // multiple of 16, at most 256) whose tile count fills whole waves of 148 CTAs best;
@@ -380,6 +577,7 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
     if (bn > 64) return launch<128, 8, 64>(p, a_map, b_map, stream);
     return launch<64, 12, 64>(p, a_map, b_map, stream);
   }
+  if (persistent) return launch_persistent(p, a_map, b_map, stream);
   if (bn == 256) return launch<256, 4, 128>(p, a_map, b_map, stream);
   if (bn == 128) return launch<128, 3, 128>(p, a_map, b_map, stream);
   return launch<64, 4, 128>(p, a_map, b_map, stream);
