@@ -226,6 +226,7 @@ struct Elem<float> {
   __device__ static float load(const float* p) { return *p; }
   __device__ static void store(float* p, float v) { *p = v; }
   __device__ static float round(float v) { return v; }
+  __device__ static void round_pair(float&, float&) {}
 };
 template <>
 struct Elem<__nv_bfloat16> {
@@ -233,6 +234,7 @@ struct Elem<__nv_bfloat16> {
   __device__ static float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
   __device__ static void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
   __device__ static float round(float v) { return round_bf16(v); }
+  __device__ static void round_pair(float& a, float& b) { round_bf16_pair(a, b); }  // one conversion
 };
 
 // 16-byte vector of elements, unpacked to floats and back.

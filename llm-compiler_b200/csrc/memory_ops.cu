@@ -117,15 +117,19 @@ int kv_store_typed(void* kbuf, void* vbuf, const void* key, const void* value,
 template <typename T>
 __device__ __forceinline__ void rope_pair(float xlo, float xhi, float clo, float chi, float slo,
                                           float shi, float& ylo, float& yhi) {
-  const float a = Elem<T>::round(__fmul_rn(xlo, clo));
-  const float b = Elem<T>::round(__fmul_rn(-xhi, slo));
-  const float c = Elem<T>::round(__fmul_rn(xhi, chi));
-  const float d = Elem<T>::round(__fmul_rn(xlo, shi));
-  ylo = Elem<T>::round(__fadd_rn(a, b));
-  yhi = Elem<T>::round(__fadd_rn(c, d));
+  // Roundings are taken two per conversion instruction; the sums are rounded by the store
+  // (every caller stores y as T, and rounding twice to the same format changes nothing).
+  float a = __fmul_rn(xlo, clo), b = __fmul_rn(-xhi, slo);
+  float c = __fmul_rn(xhi, chi), d = __fmul_rn(xlo, shi);
+  Elem<T>::round_pair(a, b);
+  Elem<T>::round_pair(c, d);
+  ylo = __fadd_rn(a, b);
+  yhi = __fadd_rn(c, d);
 }
 
-template <typename T, bool kVector>
+// IDX: the type the flat index is taken apart in. 64-bit divisions cost dozens of instructions
+// each and there are four per element group; every case whose element count fits 31 bits uses int.
+template <typename T, bool kVector, typename IDX>
 __global__ void rope_kernel(const T* __restrict__ q, const T* __restrict__ k,
                             const T* __restrict__ cosine, const T* __restrict__ sine,
                             T* __restrict__ q_out, T* __restrict__ k_out, int64_t batch,
@@ -133,17 +137,20 @@ __global__ void rope_kernel(const T* __restrict__ q, const T* __restrict__ k,
                             Strides4 qs, Strides4 ks, Strides3 cs, Strides3 ss) {
   constexpr int per = kVector ? Elem<T>::kPerVec : 1;
   const int64_t half = dim / 2;
-  const int64_t chunks = half / per;
-  const int64_t heads = q_heads + kv_heads;
-  const int64_t total = batch * heads * tokens * chunks;
-  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
-       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+  const IDX chunks = static_cast<IDX>(half / per);
+  const IDX heads = static_cast<IDX>(q_heads + kv_heads);
+  const IDX total = static_cast<IDX>(batch * heads * tokens * chunks);
+  const IDX token_count = static_cast<IDX>(tokens);
+  for (IDX idx = static_cast<IDX>(blockIdx.x) * static_cast<IDX>(blockDim.x) + static_cast<IDX>(threadIdx.x);
+       idx < total; idx += static_cast<IDX>(gridDim.x) * static_cast<IDX>(blockDim.x)) {
+    // chunk fastest, then head, then token: a warp reads neighbouring heads of one token, which
+    // lie side by side in a fused q|k|v projection output, and reuses the token's cos / sin
     const int64_t c = idx % chunks;
-    int64_t r = idx / chunks;
-    const int64_t t = r % tokens;
-    r /= tokens;
+    IDX r = idx / chunks;
     const int64_t hh = r % heads;
-    const int64_t b = r / heads;
+    r /= heads;
+    const int64_t t = r % token_count;
+    const int64_t b = r / token_count;
     const bool is_q = hh < q_heads;
     const int64_t h = is_q ? hh : hh - q_heads;
     const T* src = is_q ? q + b * qs.s[0] + h * qs.s[1] + t * qs.s[2]
@@ -205,16 +212,20 @@ int rope_typed(const void* q, const void* k, const void* cosine, const void* sin
   const int64_t total = batch * (q_heads + kv_heads) * tokens * (vec ? half / per : half);
   if (total == 0) return B200_OK;
   const int grid = grid_for(total);
+  auto launch = [&](auto kernel) {
+    kernel<<<grid, kThreads, 0, stream>>>(
+        static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(cosine),
+        static_cast<const T*>(sine), static_cast<T*>(q_out), static_cast<T*>(k_out), batch,
+        q_heads, kv_heads, tokens, dim, q4, k4, c3, s3);
+  };
+  // the grid-stride loop adds up to grid * threads beyond `total`: keep that inside 31 bits too
+  const bool narrow = total + static_cast<int64_t>(grid) * kThreads < (int64_t(1) << 31);
   if (vec) {
-    rope_kernel<T, true><<<grid, kThreads, 0, stream>>>(
-        static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(cosine),
-        static_cast<const T*>(sine), static_cast<T*>(q_out), static_cast<T*>(k_out), batch,
-        q_heads, kv_heads, tokens, dim, q4, k4, c3, s3);
+    if (narrow) launch(rope_kernel<T, true, int>);
+    else launch(rope_kernel<T, true, int64_t>);
   } else {
-    rope_kernel<T, false><<<grid, kThreads, 0, stream>>>(
-        static_cast<const T*>(q), static_cast<const T*>(k), static_cast<const T*>(cosine),
-        static_cast<const T*>(sine), static_cast<T*>(q_out), static_cast<T*>(k_out), batch,
-        q_heads, kv_heads, tokens, dim, q4, k4, c3, s3);
+    if (narrow) launch(rope_kernel<T, false, int>);
+    else launch(rope_kernel<T, false, int64_t>);
   }
   return launch_status();
 }
