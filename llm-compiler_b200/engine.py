@@ -61,6 +61,7 @@ class Qwen2Engine:
         self.next_ids = torch.zeros(batch, dtype=torch.int64, device=self.device)
         self.logits: Optional[torch.Tensor] = None
         self._graph: Optional[torch.cuda.CUDAGraph] = None
+        self._step_graph: Optional[torch.cuda.CUDAGraph] = None  # the same step between its two host copies
         self._host_ids = torch.zeros(batch, dtype=torch.int64).pin_memory()
         self._host_tokens = torch.zeros(batch, dtype=torch.int64).pin_memory()
         self.max_length_hint = 0  # host-known upper bound of the context (0 = capacity)
@@ -301,6 +302,17 @@ class Qwen2Engine:
         with torch.cuda.graph(graph):
             self._decode_step()
         self._graph = graph
+        self._graph_logits = self.logits  # each graph writes the logits into a buffer of its own
+        # step(): the copy of the ids from pinned host memory, the step and the copy of the tokens
+        # back as one graph launch instead of three submissions
+        step_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(step_graph):
+            self.input_ids.copy_(self._host_ids, non_blocking=True)
+            self._decode_step()
+            self._host_tokens.copy_(self.next_ids, non_blocking=True)
+        self._step_graph = step_graph
+        self._step_logits = self.logits
+        self.logits = self._graph_logits
         kernels.runtime(self.device).status.zero_()
 
     def decode_step(self, *, feed_back: bool = True) -> torch.Tensor:
@@ -309,6 +321,7 @@ class Qwen2Engine:
 
         if self._graph is not None:
             self._graph.replay()
+            self.logits = self._graph_logits
         else:
             self._decode_step()
         if feed_back:
@@ -321,9 +334,13 @@ class Qwen2Engine:
         waits for them."""
 
         self._host_ids.copy_(host_ids)
-        self.input_ids.copy_(self._host_ids, non_blocking=True)
-        self.decode_step(feed_back=False)
-        self._host_tokens.copy_(self.next_ids, non_blocking=True)
+        if self._step_graph is not None:
+            self._step_graph.replay()
+            self.logits = self._step_logits
+        else:
+            self.input_ids.copy_(self._host_ids, non_blocking=True)
+            self.decode_step(feed_back=False)
+            self._host_tokens.copy_(self.next_ids, non_blocking=True)
         torch.cuda.current_stream(self.device).synchronize()
         return self._host_tokens
 

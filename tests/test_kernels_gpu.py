@@ -486,11 +486,13 @@ def test_linear_shapes_and_epilogues(m, k, n):
 
 
 @pytest.mark.parametrize("m,k,n", [(128, 64, 128), (256, 896, 896), (1000, 4864, 896),
-                                   (2048, 896, 9728), (300, 896, 1152), (129, 200, 72)])
+                                   (2048, 896, 9728), (300, 896, 1152), (129, 200, 72),
+                                   (1100, 200, 1000), (1536, 896, 1152), (1024, 896, 896)])
 def test_linear_tcgen05_path_matches_the_oracle_and_the_warp_level_path(m, k, n, monkeypatch):
-    """More than 64 rows run on tcgen05 / TMEM / TMA; the same call with
-    B200_LINEAR_PATH=mma.sync runs the warp-level kernel. Both against the CPU oracle, all
-    epilogues, full and ragged tiles in M, N and K."""
+    """More than 64 rows run on tcgen05 / TMEM / TMA (from 1024 rows on the persistent kernel with
+    two accumulators: 608 tiles on 148 CTAs, 256-, 224- and 192-column tiles, ragged M, N and K);
+    the same call with B200_LINEAR_PATH=mma.sync runs the warp-level kernel. Both against the
+    CPU oracle, all epilogues, full and ragged tiles in M, N and K."""
     g = torch.Generator().manual_seed(m + n)
     x = torch.randn(m, k, generator=g).bfloat16()
     w = (torch.randn(n, k, generator=g) * 0.05).bfloat16()
@@ -513,6 +515,13 @@ def test_linear_tcgen05_path_matches_the_oracle_and_the_warp_level_path(m, k, n,
     kernels.runtime().check_status()
     # the two kernels round at the same points: they agree to an ulp of the output scale
     close(outputs["tcgen05"][0], outputs["mma.sync"][0].float().cpu(), 1e-2)
+    if m >= 1024:  # one tile per CTA and the persistent kernel accumulate in the same order
+        monkeypatch.delenv("B200_LINEAR_PATH")
+        monkeypatch.setenv("B200_LINEAR_PERSISTENT", "0")
+        single = (b200.b200_linear(xd, wd, bd), b200.b200_linear(xd, wd, residual=rd, epilogue="residual"),
+                  b200.b200_linear(xd, packed, epilogue="swiglu"))
+        for ours, theirs in zip(outputs["tcgen05"], single):
+            assert torch.equal(ours, theirs)
 
 
 @pytest.mark.parametrize("m,k,n", [(64, 896, 1152), (64, 896, 896), (64, 4864, 896), (3, 256, 512),
