@@ -429,7 +429,9 @@ def test_prefill_attention_config3_shapes(tokens):
 @pytest.mark.parametrize("layout", ["token_major", "head_major"])
 @pytest.mark.parametrize("batch,tokens,hq,hkv,d", [(2, 1, 14, 2, 64), (2, 127, 14, 2, 64),
                                                     (3, 129, 14, 2, 64), (1, 700, 4, 4, 64),
-                                                    (2, 333, 28, 4, 128), (1, 1024, 8, 1, 128)])
+                                                    (2, 333, 28, 4, 128), (1, 1024, 8, 1, 128),
+                                                    (2, 255, 14, 2, 64), (1, 257, 14, 2, 64),
+                                                    (1, 385, 4, 2, 128), (2, 512, 2, 1, 64)])
 def test_prefill_attention_tensor_memory_path(batch, tokens, hq, hkv, d, layout, monkeypatch):
     """Causal-proved bf16 calls in the fast mode run on tcgen05 (S and O tiles in tensor memory,
     TMA boxes of 128 tokens): token counts around and off the 128-row tile, one token, several
@@ -453,6 +455,32 @@ def test_prefill_attention_tensor_memory_path(batch, tokens, hq, hkv, d, layout,
     warp_level = b200.b200_prefill_attention(q.cuda(), k.cuda(), v.cuda(), None, scale=scale,
                                              causal=True)
     close(out, warp_level.float().cpu(), 1e-2)
+    kernels.runtime().check_status()
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_prefill_attention_moves_its_reference_maximum(d):
+    """The tcgen05 kernel keeps O in tensor memory against a lazy reference maximum and rescales
+    it only when a key tile raises a row's maximum by more than 8 (log2 domain). Scores with a
+    standard deviation of 8 and a drift upwards along the keys make that happen tile after tile."""
+    g = torch.Generator().manual_seed(d)
+    batch, tokens, hq, hkv = 2, 1100, 4, 2
+    q = (torch.randn(batch, tokens, hq, d, generator=g) * 8.0).bfloat16().transpose(1, 2)
+    k = torch.randn(batch, tokens, hkv, d, generator=g)
+    k = (k + torch.linspace(0.0, 1.5, tokens)[None, :, None, None] * q.transpose(1, 2)[:, -1:, :hkv].float().sign()).bfloat16().transpose(1, 2)
+    v = torch.randn(batch, tokens, hkv, d, generator=g).bfloat16().transpose(1, 2)
+    scale = d ** -0.5
+    # With scores this large the oracle's own bf16 rounding of the scores (an absolute error of
+    # up to 0.25 at |s| = 40) moves probabilities by tens of per cent, so the yardstick here is
+    # the exact attention of the same bf16 inputs in float64, which the kernel (fp32 scores,
+    # bf16 probabilities) must match within the bf16 tolerance.
+    q64, k64, v64 = (t.double().repeat_interleave(hq // t.shape[1], dim=1) for t in (q, k, v))
+    scores = q64 @ k64.transpose(-1, -2) * scale
+    scores = scores.masked_fill(torch.triu(torch.ones(tokens, tokens, dtype=torch.bool), diagonal=1), float("-inf"))
+    exact = (torch.softmax(scores, dim=-1) @ v64).float()
+    out = b200.b200_prefill_attention(q.cuda(), k.cuda(), v.cuda(), None, scale=scale, causal=True)
+    assert torch.isfinite(out.float()).all()
+    close(out, exact, BF16_TOL)
     kernels.runtime().check_status()
 
 
