@@ -608,9 +608,13 @@ int linear_partial_tcgen05(const void* input, const void* weight, float* partial
   p.bn = plan.bn;
   p.prefetch_weights = (launch_mode() & B200_LAUNCH_CONSTANT_WEIGHTS) != 0 ? 1 : 0;
   if (a_rows == 64) {
+    // A K slice of many k-blocks is a long weight stream: it wants about 2 us x 44 GB/s of
+    // loads in flight per SM, twice what the 96 KB rings of the short slices hold.
+    const bool long_slice = ceil_div(ceil_div(k, kBK), splits) >= 24;
     if (plan.bn == 32) return launch<32, 8, 64>(p, a_map, b_map, stream);
-    if (plan.bn == 64) return launch<64, 6, 64>(p, a_map, b_map, stream);
-    return launch<128, 4, 64>(p, a_map, b_map, stream);
+    if (plan.bn == 64)
+      return long_slice ? launch<64, 12, 64>(p, a_map, b_map, stream) : launch<64, 6, 64>(p, a_map, b_map, stream);
+    return long_slice ? launch<128, 8, 64>(p, a_map, b_map, stream) : launch<128, 4, 64>(p, a_map, b_map, stream);
   }
   if (plan.bn == 32) return launch<32, 6, 128>(p, a_map, b_map, stream);
   if (plan.bn == 64) return launch<64, 4, 128>(p, a_map, b_map, stream);
