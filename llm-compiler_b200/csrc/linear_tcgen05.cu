@@ -60,31 +60,79 @@ __device__ __forceinline__ float silu_f32(float x) {
   return __fdividef(x, 1.0f + exp2f(-1.4426950408889634f * x));
 }
 
+// Bias onto 32 accumulator columns (16-byte loads where all 32 columns exist and are aligned).
+__device__ __forceinline__ void add_bias(const Tcgen05Params& p, int col0, int n_end, float (&v)[32]) {
+  const bool whole = col0 + 32 <= n_end;
+  if (p.bias != nullptr) {
+    if (whole && (reinterpret_cast<uintptr_t>(p.bias + col0) & 15u) == 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col0) + i);
+        v[8 * i] += bf16_lo(b.x); v[8 * i + 1] += bf16_hi(b.x);
+        v[8 * i + 2] += bf16_lo(b.y); v[8 * i + 3] += bf16_hi(b.y);
+        v[8 * i + 4] += bf16_lo(b.z); v[8 * i + 5] += bf16_hi(b.z);
+        v[8 * i + 6] += bf16_lo(b.w); v[8 * i + 7] += bf16_hi(b.w);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < n_end) v[i] += __bfloat162float(p.bias[col0 + i]);
+    }
+  }
+}
+
+// r(r(x W^T + b) + residual) for 32 columns of one output row.
+__device__ __forceinline__ void add_residual(const Tcgen05Params& p, int row, int col0, int n_end,
+                                             float (&v)[32]) {
+  const bool whole = col0 + 32 <= n_end;
+  const int64_t o = static_cast<int64_t>(row) * p.n + col0;
+  if (p.epilogue == B200_EPILOGUE_RESIDUAL) {  // r(r(x W^T + b) + residual)
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) round_bf16_pair(v[i], v[i + 1]);
+    if (whole && (reinterpret_cast<uintptr_t>(p.residual + o) & 15u) == 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 r = *(reinterpret_cast<const uint4*>(p.residual + o) + i);
+        v[8 * i] = __fadd_rn(v[8 * i], bf16_lo(r.x)); v[8 * i + 1] = __fadd_rn(v[8 * i + 1], bf16_hi(r.x));
+        v[8 * i + 2] = __fadd_rn(v[8 * i + 2], bf16_lo(r.y)); v[8 * i + 3] = __fadd_rn(v[8 * i + 3], bf16_hi(r.y));
+        v[8 * i + 4] = __fadd_rn(v[8 * i + 4], bf16_lo(r.z)); v[8 * i + 5] = __fadd_rn(v[8 * i + 5], bf16_hi(r.z));
+        v[8 * i + 6] = __fadd_rn(v[8 * i + 6], bf16_lo(r.w)); v[8 * i + 7] = __fadd_rn(v[8 * i + 7], bf16_hi(r.w));
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < n_end) v[i] = __fadd_rn(v[i], __bfloat162float(p.residual[o + i]));
+    }
+  }  // (without a residual the store below is the one rounding)
+}
+
+// y_j = r(silu(r(gate_j))) * r(up_j) for the 16 (gate, up) column pairs of a 32-column chunk;
+// the caller's store rounds the product. The roundings go through the conversion unit, which
+// the exponentials and reciprocals of silu also queue for, so they are taken in pairs.
+__device__ __forceinline__ void swiglu_of_chunk(float (&v)[32], float (&y)[16]) {
+#pragma unroll
+  for (int j = 0; j < 16; j += 2) {
+    round_bf16_pair(v[2 * j], v[2 * j + 1]);
+    round_bf16_pair(v[2 * j + 2], v[2 * j + 3]);
+    float g0 = silu_f32(v[2 * j]), g1 = silu_f32(v[2 * j + 2]);
+    round_bf16_pair(g0, g1);
+    y[j] = g0 * v[2 * j + 1];
+    y[j + 1] = g1 * v[2 * j + 3];
+  }
+}
+
 // The bf16 epilogue of 32 accumulator columns of one output row: bias, then SwiGLU (columns
 // 2j / 2j+1 are gate_j / up_j) or the residual, with the reference's bf16 rounding points.
 __device__ __forceinline__ void store_chunk(const Tcgen05Params& p, int row, int col0, int n_end,
                                             float (&v)[32]) {
   const int out_cols = p.epilogue == B200_EPILOGUE_SWIGLU ? p.n / 2 : p.n;
-  if (p.bias != nullptr) {
-#pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (col0 + i < n_end) v[i] += __bfloat162float(p.bias[col0 + i]);
-  }
+  const bool whole = col0 + 32 <= n_end;  // all 32 columns exist: 16-byte accesses where aligned
+  add_bias(p, col0, n_end, v);
   if (p.epilogue == B200_EPILOGUE_SWIGLU) {
     // columns 2j / 2j+1 are gate_j / up_j
     __nv_bfloat16* dst = p.out + static_cast<int64_t>(row) * out_cols + col0 / 2;
-    // y = r(r(silu(r(gate))) * r(up)): the roundings go through the conversion unit, which
-    // the exponentials and reciprocals of silu also queue for, so they are taken in pairs
     float y[16];
-#pragma unroll
-    for (int j = 0; j < 16; j += 2) {
-      round_bf16_pair(v[2 * j], v[2 * j + 1]);
-      round_bf16_pair(v[2 * j + 2], v[2 * j + 3]);
-      float g0 = silu_f32(v[2 * j]), g1 = silu_f32(v[2 * j + 2]);
-      round_bf16_pair(g0, g1);
-      y[j] = g0 * v[2 * j + 1];
-      y[j + 1] = g1 * v[2 * j + 3];
-    }
+    swiglu_of_chunk(v, y);
     if (col0 + 32 <= n_end && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
       for (int i = 0; i < 2; ++i)
@@ -99,15 +147,9 @@ __device__ __forceinline__ void store_chunk(const Tcgen05Params& p, int row, int
     return;
   }
   const int64_t o = static_cast<int64_t>(row) * p.n + col0;
-  if (p.epilogue == B200_EPILOGUE_RESIDUAL) {  // r(r(x W^T + b) + residual)
-#pragma unroll
-    for (int i = 0; i < 32; i += 2) round_bf16_pair(v[i], v[i + 1]);
-#pragma unroll
-    for (int i = 0; i < 32; ++i)
-      if (col0 + i < n_end) v[i] = __fadd_rn(v[i], __bfloat162float(p.residual[o + i]));
-  }  // (without a residual the store below is the one rounding)
+  add_residual(p, row, col0, n_end, v);
   __nv_bfloat16* dst = p.out + o;
-  if (col0 + 32 <= n_end && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+  if (whole && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
     for (int i = 0; i < 4; ++i)
       reinterpret_cast<uint4*>(dst)[i] =
@@ -410,13 +452,75 @@ linear_tcgen05_persistent_kernel(const Tcgen05Params p, const __grid_constant__ 
       const int row = tile_m * kBM + warp * 32 + lane;
       const int n_end = min(p.n, (tile_n + 1) * bn);
       const uint32_t t_addr = tmem_base + acc * kPersistentBN + (static_cast<uint32_t>(warp * 32) << 16);
+      // The outputs go through a 4 KB staging tile per warp, 64 output columns at a time: each lane packs its row's 128 bytes into shared memory (16-byte units
+      // XOR-swizzled by row), then the warp stores four whole 128-byte row segments per
+      // instruction instead of 32 scattered 16-byte pieces.
+      const bool swiglu = p.epilogue == B200_EPILOGUE_SWIGLU;
+      const int out_cols = swiglu ? p.n / 2 : p.n;
+      const bool staged = out_cols % 8 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15u) == 0;
+      const int span = swiglu ? 128 : 64;  // accumulator columns that make 64 output columns
+      const uint32_t stage_tile = smem_base + STAGES * kStageBytes + warp * 4096;
+      const int row0 = tile_m * kBM + warp * 32;
 #pragma unroll 1
-      for (int c0 = 0; c0 < bn; c0 += 32) {
+      for (int c0 = 0; c0 < bn;) {
         const int col0 = tile_n * bn + c0;
         if (col0 >= n_end) break;  // warp-uniform
-        float v[32];
-        tmem_load_32x32(t_addr + c0, v);
-        if (row < p.m) store_chunk(p, row, col0, n_end, v);
+        if (staged && c0 + span <= bn && col0 + span <= n_end) {
+          uint4 packed[8];
+          if (swiglu) {
+#pragma unroll
+            for (int quarter = 0; quarter < 4; ++quarter) {
+              float v[32], y[16];
+              tmem_load_32x32(t_addr + c0 + quarter * 32, v);
+              if (row < p.m) add_bias(p, col0 + quarter * 32, n_end, v);
+              swiglu_of_chunk(v, y);
+#pragma unroll
+              for (int i = 0; i < 2; ++i)
+                packed[quarter * 2 + i] =
+                    make_uint4(pack_bf16x2(y[8 * i], y[8 * i + 1]), pack_bf16x2(y[8 * i + 2], y[8 * i + 3]),
+                               pack_bf16x2(y[8 * i + 4], y[8 * i + 5]), pack_bf16x2(y[8 * i + 6], y[8 * i + 7]));
+            }
+          } else {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              float v[32];
+              tmem_load_32x32(t_addr + c0 + half * 32, v);
+              if (row < p.m) {
+                add_bias(p, col0 + half * 32, n_end, v);
+                add_residual(p, row, col0 + half * 32, n_end, v);
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                packed[half * 4 + i] =
+                    make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
+                               pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
+            }
+          }
+          __syncwarp();  // the previous round's reads of the staging tile are done
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
+                             stage_tile + lane * 128 + ((u ^ (lane & 7)) << 4)),
+                         "r"(packed[u].x), "r"(packed[u].y), "r"(packed[u].z), "r"(packed[u].w) : "memory");
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + (lane >> 3), u = lane & 7;
+            uint4 value;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(value.x), "=r"(value.y), "=r"(value.z), "=r"(value.w)
+                         : "r"(stage_tile + r * 128 + ((u ^ (r & 7)) << 4)));
+            if (row0 + r < p.m)
+              *reinterpret_cast<uint4*>(p.out + static_cast<int64_t>(row0 + r) * out_cols +
+                                        (swiglu ? col0 / 2 : col0) + u * 8) = value;
+          }
+          c0 += span;
+        } else {
+          float v[32];
+          tmem_load_32x32(t_addr + c0, v);
+          if (row < p.m) store_chunk(p, row, col0, n_end, v);
+          c0 += 32;
+        }
       }
       // the accumulator may be overwritten by the tile after next
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -438,7 +542,8 @@ linear_tcgen05_persistent_kernel(const Tcgen05Params p, const __grid_constant__ 
 
 int launch_persistent(const Tcgen05Params& p, const CUtensorMap& a_map, const CUtensorMap& b_map,
                       cudaStream_t stream) {
-  constexpr int smem = kPersistentStages * (kBM + kPersistentBN) * 128 + 1024;
+  // the stage ring, 4 KB of store staging per epilogue warp, alignment slack
+  constexpr int smem = kPersistentStages * (kBM + kPersistentBN) * 128 + 4 * 4096 + 1024;
   static_assert(smem <= 227 * 1024, "stage ring exceeds shared memory");
   auto kernel = linear_tcgen05_persistent_kernel;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
