@@ -116,7 +116,9 @@ def test_strict_executor_refuses_before_running_anything():
 
 
 # the reference's src directory, where a checkout of it is present (see tests/golden/make_golden.py)
-REFERENCE_SRC = Path(os.environ.get("LLM_COMPILER_REFERENCE_SRC", "")) / "stateful_llm_compiler"
+# (LLM_COMPILER_REFERENCE_SRC, or a "reference" checkout beside this repository)
+REFERENCE_SRC = Path(os.environ.get("LLM_COMPILER_REFERENCE_SRC") or
+                     Path(__file__).resolve().parents[2] / "reference" / "src") / "stateful_llm_compiler"
 
 
 @pytest.mark.skipif(not REFERENCE_SRC.is_dir(), reason="reference package not present")
