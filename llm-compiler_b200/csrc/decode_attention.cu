@@ -1418,6 +1418,17 @@ extern "C" int b200_decode_attention_static_scratch(
   if (capacity > INT32_MAX / 2 || batch * capacity > INT32_MAX) return B200_ERR_TOO_LARGE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int groups = static_cast<int>(q_heads / kv_heads);
+  {
+    // The scratch array used is the current device's copy: operands that live on another GPU
+    // would pair this GPU's scratch with that GPU's tensors. Refused before anything is queued.
+    int current = -1;
+    cudaPointerAttributes attributes;
+    if (cudaGetDevice(&current) != cudaSuccess) return B200_ERR_LAUNCH;
+    if (cudaPointerGetAttributes(&attributes, output) == cudaSuccess &&
+        attributes.type == cudaMemoryTypeDevice && attributes.device != current)
+      return B200_ERR_BAD_ARGUMENT;
+    (void)cudaGetLastError();
+  }
 
   int64_t max_length = max_length_hint > 0 && max_length_hint < mask_len ? max_length_hint : mask_len;
   const int64_t head_blocks = kv_heads * ceil_div(groups, 16);

@@ -34,13 +34,17 @@ class DeviceRuntime:
 
     Workspaces only grow; they are zero-filled when (re)allocated because the split-K
     linear kernel keeps tile counters there that must start at zero (it leaves them at
-    zero after every call).
+    zero after every call). A workspace that is outgrown is retired, never freed: a CUDA
+    graph captured earlier has its address baked into its launches, and a replay must keep
+    finding memory that nothing else owns (with its counters still at zero). Growth is
+    geometric, so the retired buffers of a name sum to less than the live one.
     """
 
     def __init__(self, device: torch.device) -> None:
         self.device = device
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self._workspaces: dict[str, torch.Tensor] = {}
+        self._retired: list[torch.Tensor] = []
         self.launches = 0
 
     def workspace(self, name: str, nbytes: int) -> Optional[torch.Tensor]:
@@ -48,6 +52,9 @@ class DeviceRuntime:
             return None
         current = self._workspaces.get(name)
         if current is None or current.numel() < nbytes:
+            if current is not None:
+                self._retired.append(current)
+                nbytes = max(int(nbytes), 2 * current.numel())
             current = torch.zeros(int(nbytes), dtype=torch.uint8, device=self.device)
             self._workspaces[name] = current
         return current
@@ -145,6 +152,18 @@ def kernel_variants(*, linear: Optional[str] = None, prefill_attention: Optional
         library.b200_set_launch_mode(previous)
 
 
+def _guard_current_device(device: torch.device) -> None:
+    """The C ABI launches on the calling thread's current device and on its current stream;
+    operands that live on another GPU would be dereferenced by the wrong GPU (an illegal
+    address without peer access, a silent NVLink detour with it). Refused before any launch."""
+
+    current = torch.cuda.current_device()
+    if device.index is not None and device.index != current:
+        raise ValueError(
+            f"operands live on cuda:{device.index} but the current device is cuda:{current}: "
+            "call under torch.cuda.device(...) of the operands' GPU")
+
+
 def _require_cuda(*tensors: torch.Tensor) -> torch.device:
     device = None
     for tensor in tensors:
@@ -157,6 +176,7 @@ def _require_cuda(*tensors: torch.Tensor) -> torch.device:
         elif tensor.device != device:
             raise ValueError("all operands must live on the same CUDA device")
     assert device is not None
+    _guard_current_device(device)
     return device
 
 
@@ -530,8 +550,10 @@ def b200_decode_attention_no_alloc(query: torch.Tensor, key_buffer: torch.Tensor
     frozen after start-up, a host framework that hands its plugins a fixed arena. This
     variant takes the output tensor from the caller and keeps the split-KV scratch in an
     8 MiB array inside the library (one per GPU, alive until the process exits) instead of a
-    workspace tensor. Nothing is allocated here or in the library; tensors that would need a
-    contiguous copy are rejected. Requests whose partial sums do not fit the array raise
+    workspace tensor. Nothing is allocated by this call or in the library (the one exception:
+    the very first use of this package on a GPU creates that GPU's 4-byte status word, so touch
+    `kernels.runtime(device)` once at start-up); tensors that would need a contiguous copy are
+    rejected. Requests whose partial sums do not fit the array raise
     ValueError (raise split_tokens to shrink the need). Calls on one GPU share the array, so
     calls that overlap on different streams race; the first call on a device should happen
     outside graph capture because it looks the array's address up. bf16 only.

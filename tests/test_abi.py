@@ -65,3 +65,17 @@ def test_missing_library_is_an_error(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIBRARY_PATH", tmp_path / "libb200serve.so")
     with pytest.raises(_lib.B200LibraryError):
         _lib.load()
+
+
+def test_operands_on_another_gpu_are_refused_before_any_launch(monkeypatch):
+    """The C ABI launches on the current device with the current stream; tensors of another
+    GPU must be rejected on the host (nothing is launched, no GPU is needed for the check)."""
+    import torch
+
+    from llm_compiler_b200 import kernels
+
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
+    kernels._guard_current_device(torch.device("cuda", 0))
+    kernels._guard_current_device(torch.device("cuda"))  # no index: the current device
+    with pytest.raises(ValueError, match="current device is cuda:0"):
+        kernels._guard_current_device(torch.device("cuda", 1))

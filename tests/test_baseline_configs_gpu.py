@@ -1,0 +1,293 @@
+"""Parity at the stated shapes of the benchmark configurations (not reduced stand-ins).
+
+Each test builds the inputs of one configuration at its own sizes with its own seeding rule,
+runs the CUDA path through the C ABI and compares with the CPU oracle (oracle/serve_ops.py,
+oracle/qwen2_model.py, both pinned to the reference's outputs by tests/test_oracle.py):
+
+  decode-attention micro-benchmark   14/2 heads x 64, bf16, capacity 32768, batch {1, 8, 64,
+                                     256}, lengths uniform in [64, L], seed B*10000+L (the
+                                     reference's rule, benchmarks/bench_decode_attention.py:54-56)
+  prefill attention + KV store       batch {1, 4, 16} x tokens {16, 128, 512, 4096}, RoPE theta
+                                     1e6, store at 0 into capacity 8192, one decode append at T
+  Qwen2-0.5B architecture            24 layers, vocabulary 151936, tied head, 512-token prompt,
+                                     teacher-forced greedy decode, both numerical modes
+  Qwen2-7B architecture              full-width layers, ragged contexts in [1024, 8192]
+
+Whole tensors are compared where the oracle finishes in seconds; for the largest batches the
+oracle runs on sampled sequences (always the longest and the shortest) and every other
+sequence is covered by a size-independent property (the result does not depend on the split
+plan). Tolerances: KV store and RoPE bit-exact; bf16 attention / logits 2e-2 max-abs, and --
+because random N(0, 0.02) weights give logits far smaller than 2e-2 -- also relative to the
+largest reference logit, so that the check cannot pass vacuously.
+"""
+
+import pytest
+import torch
+
+from oracle import qwen2_model, serve_ops
+import llm_compiler_b200 as b200
+from llm_compiler_b200 import kernels
+from llm_compiler_b200 import qwen2 as q2
+from llm_compiler_b200.engine import Qwen2Engine
+
+pytestmark = pytest.mark.gpu
+
+BF16_TOL = 2e-2
+Q_HEADS, KV_HEADS, HEAD_DIM = 14, 2, 64
+
+
+def close(actual, expected, tol=BF16_TOL):
+    actual, expected = actual.float().cpu(), expected.float().cpu()
+    assert actual.shape == expected.shape
+    assert not torch.isnan(actual).any()
+    scale = max(1.0, float(expected.abs().max()))
+    diff = float((actual - expected).abs().max())
+    assert diff <= tol * scale, f"max abs diff {diff} > {tol} * {scale}"
+    return diff
+
+
+# ---------------------------------------------------------- decode-attention config ----
+def decode_micro_inputs(batch, limit, capacity=32768):
+    """The micro-benchmark's tensors, drawn on the device from a CUDA generator seeded with
+    batch * 10000 + limit as the reference does; rows beyond each sequence's length are NaN so
+    that a kernel that reads past lengths[b] cannot pass."""
+    g = torch.Generator(device="cuda").manual_seed(batch * 10000 + limit)
+    query = torch.randn(batch, Q_HEADS, 1, HEAD_DIM, generator=g, device="cuda").bfloat16()
+    keys = torch.empty(batch, capacity, KV_HEADS, HEAD_DIM, dtype=torch.bfloat16, device="cuda")
+    values = torch.empty_like(keys)
+    for begin in range(0, batch, 32):  # bounded fp32 staging
+        stop = min(batch, begin + 32)
+        keys[begin:stop, :limit] = torch.randn(stop - begin, limit, KV_HEADS, HEAD_DIM, generator=g,
+                                               device="cuda")
+        values[begin:stop, :limit] = torch.randn(stop - begin, limit, KV_HEADS, HEAD_DIM,
+                                                 generator=g, device="cuda")
+    lengths = torch.randint(64, limit + 1, (batch,), generator=g, device="cuda") if limit > 64 \
+        else torch.full((batch,), 64, device="cuda")
+    index = torch.arange(capacity, device="cuda").view(1, capacity, 1, 1)
+    beyond = index >= lengths.view(batch, 1, 1, 1)
+    keys.masked_fill_(beyond, float("nan"))
+    values.masked_fill_(beyond, float("nan"))
+    return query, keys, values, lengths
+
+
+def oracle_decode_rows(query, keys, values, lengths, rows, limit):
+    rows = torch.as_tensor(rows)
+    q, k, v = query[rows.cuda()].cpu(), keys[rows.cuda(), :limit].cpu(), values[rows.cuda(), :limit].cpu()
+    k, v = k.nan_to_num(0.0), v.nan_to_num(0.0)  # beyond the length: masked by the oracle anyway
+    return serve_ops.decode_attention(q, k, v, lengths[rows.cuda()].cpu(),
+                                      torch.zeros(len(rows), 1, 1, limit), groups=Q_HEADS // KV_HEADS,
+                                      scale=0.125)
+
+
+@pytest.mark.parametrize("limit", [64, 1024, 4096, 32768])
+@pytest.mark.parametrize("batch", [1, 8, 64, 256])
+def test_decode_attention_micro_benchmark_shapes(batch, limit):
+    query, keys, values, lengths = decode_micro_inputs(batch, limit)
+    mask = torch.zeros(batch, 1, 1, 32768, device="cuda")  # the reference passes a zero mask
+    out = b200.b200_decode_attention(query, keys, values, lengths, mask, scale=0.125)
+    fast = b200.b200_decode_attention(query, keys, values, lengths, None, scale=0.125,
+                                      max_length_hint=limit)
+    if batch <= 8:
+        rows = list(range(batch))
+    else:  # longest, shortest, first, last and two more
+        rows = sorted({int(lengths.argmax()), int(lengths.argmin()), 0, batch - 1, batch // 3,
+                       2 * batch // 3})
+    expected = oracle_decode_rows(query, keys, values, lengths, rows, limit)
+    close(out[rows], expected)
+    close(fast[rows], expected)
+    # every sequence: the plan (masked / mask-free kernel, profile-guided / fixed split) must not
+    # matter beyond fp32 re-association of the partial sums
+    other = b200.b200_decode_attention(query, keys, values, lengths, None, scale=0.125,
+                                       split_tokens=1024, max_length_hint=limit)
+    close(other, fast, 4e-3)
+    close(out, fast, 8e-3)
+    kernels.runtime().check_status()
+
+
+# --------------------------------------------------------- prefill + KV store config ----
+def prefill_inputs(batch, tokens):
+    """q, k, v as the model produces them (B x T x H x D memory, seen as B x H x T x D),
+    drawn on the device with seed batch * 10000 + tokens, and the theta = 1e6 tables."""
+    g = torch.Generator(device="cuda").manual_seed(batch * 10000 + tokens)
+    q = torch.randn(batch, tokens, Q_HEADS, HEAD_DIM, generator=g, device="cuda").bfloat16().transpose(1, 2)
+    k = torch.randn(batch, tokens, KV_HEADS, HEAD_DIM, generator=g, device="cuda").bfloat16().transpose(1, 2)
+    v = torch.randn(batch, tokens, KV_HEADS, HEAD_DIM, generator=g, device="cuda").bfloat16().transpose(1, 2)
+    positions = torch.arange(tokens, dtype=torch.int64).view(1, -1).expand(batch, -1).contiguous()
+    inv_freq = serve_ops.rope_inverse_frequency(HEAD_DIM, 1e6)
+    cosine, sine = serve_ops.rope_table(positions, inv_freq, torch.bfloat16)  # the oracle's tables
+    return q, k, v, cosine, sine
+
+
+@pytest.mark.parametrize("tokens", [16, 128, 512, 4096])
+@pytest.mark.parametrize("batch", [1, 4, 16])
+def test_prefill_attention_rope_store_then_decode_append(batch, tokens):
+    capacity = 8192
+    q, k, v, cosine, sine = prefill_inputs(batch, tokens)
+    # RoPE (bit-exact) on the whole batch
+    q_rot, k_rot = b200.b200_rope(q, k, cosine.cuda(), sine.cuda())
+    sample = sorted({0, batch - 1})
+    q_ref, k_ref = serve_ops.rope(q[sample].cpu(), k[sample].cpu(), cosine[sample], sine[sample])
+    assert torch.equal(q_rot[sample].cpu(), q_ref) and torch.equal(k_rot[sample].cpu(), k_ref)
+    # store at 0 into capacity 8192 (bit-exact, every sequence)
+    keys = torch.zeros(batch, capacity, KV_HEADS, HEAD_DIM, dtype=torch.bfloat16, device="cuda")
+    values = torch.zeros_like(keys)
+    zeros = torch.zeros(batch, dtype=torch.int64, device="cuda")
+    b200.b200_kv_store(keys, values, k_rot, v, zeros)
+    assert torch.equal(keys[:, :tokens], k_rot.transpose(1, 2))
+    assert torch.equal(values[:, :tokens], v.transpose(1, 2))
+    assert not keys[:, tokens:].any() and not values[:, tokens:].any()
+    # causal attention: the reference's contract (additive mask) where the mask fits, and the
+    # causal-proved kernel; the oracle takes whole sequences up to 512 tokens and, at 4096
+    # tokens, one whole sequence (batch 1) or row blocks of the sampled sequences
+    causal = b200.b200_prefill_attention(q_rot, k_rot, v, None, scale=0.125, causal=True)
+    mask = serve_ops.causal_mask(1, tokens).cuda().expand(batch, 1, tokens, tokens)
+    masked = b200.b200_prefill_attention(q_rot, k_rot, v, mask, scale=0.125)
+    close(masked, causal, 8e-3)
+    if tokens < 4096 or batch == 1:
+        blocks = [(0, tokens)]
+    else:
+        blocks = [(0, 128), (1900, 2100), (tokens - 256, tokens)]
+    for row in sample:
+        for begin, stop in blocks:
+            mask_rows = serve_ops.causal_mask(1, tokens)[:, :, begin:stop]
+            expected = serve_ops.prefill_attention(
+                q_ref[sample.index(row):sample.index(row) + 1, :, begin:stop],
+                k_ref[sample.index(row):sample.index(row) + 1], v[row:row + 1].cpu(), mask_rows,
+                groups=Q_HEADS // KV_HEADS, scale=0.125)
+            close(causal[row:row + 1, :, begin:stop], expected)
+            close(masked[row:row + 1, :, begin:stop], expected)
+    # one decode step appends at position T and attends over T + 1 tokens
+    g = torch.Generator(device="cuda").manual_seed(7)
+    new_q = torch.randn(batch, 1, Q_HEADS, HEAD_DIM, generator=g, device="cuda").bfloat16().transpose(1, 2)
+    new_k = torch.randn(batch, 1, KV_HEADS, HEAD_DIM, generator=g, device="cuda").bfloat16().transpose(1, 2)
+    new_v = torch.randn(batch, 1, KV_HEADS, HEAD_DIM, generator=g, device="cuda").bfloat16().transpose(1, 2)
+    step_positions = torch.full((batch, 1), tokens, dtype=torch.int64)
+    step_cos, step_sin = serve_ops.rope_table(step_positions, serve_ops.rope_inverse_frequency(HEAD_DIM, 1e6),
+                                              torch.bfloat16)
+    lengths = torch.full((batch,), tokens, dtype=torch.int64, device="cuda")
+    rotated_q = b200.b200_rope_kv_store(new_q, new_k, new_v, step_cos.cuda(), step_sin.cuda(), keys,
+                                        values, lengths)
+    b200.b200_advance_lengths(lengths, 1, capacity)
+    assert int(lengths.min()) == tokens + 1 == int(lengths.max())
+    context = b200.b200_decode_attention(rotated_q, keys, values, lengths, None, scale=0.125)
+    ref_q, ref_k = serve_ops.rope(new_q[sample].cpu(), new_k[sample].cpu(), step_cos[sample], step_sin[sample])
+    assert torch.equal(rotated_q[sample].cpu(), ref_q)
+    ref_keys = torch.cat([k_ref.transpose(1, 2), ref_k.transpose(1, 2)], dim=1)
+    ref_values = torch.cat([v[sample].cpu().transpose(1, 2), new_v[sample].cpu().transpose(1, 2)], dim=1)
+    assert torch.equal(keys[sample, :tokens + 1].cpu(), ref_keys)
+    assert torch.equal(values[sample, :tokens + 1].cpu(), ref_values)
+    expected = serve_ops.decode_attention(ref_q, ref_keys, ref_values,
+                                          torch.full((len(sample),), tokens + 1),
+                                          torch.zeros(len(sample), 1, 1, tokens + 1),
+                                          groups=Q_HEADS // KV_HEADS, scale=0.125)
+    close(context[sample], expected)
+    kernels.runtime().check_status()
+
+
+# -------------------------------------------------------------- whole-model configs ----
+def logit_errors(actual, expected):
+    actual, expected = actual.float().cpu(), expected.float().cpu()
+    scale = float(expected.abs().max())
+    return float((actual - expected).abs().max()), scale
+
+
+def check_logits(actual, expected, what, relative=5e-2):
+    """2e-2 max-abs (the stated tolerance) AND `relative` of the largest reference logit: the
+    logits of an N(0, 0.02) model are ~1e-2, so the absolute bound alone proves nothing."""
+    diff, scale = logit_errors(actual.reshape(expected.shape), expected)
+    assert diff <= BF16_TOL, f"{what}: logit diff {diff}"
+    assert diff <= relative * scale, f"{what}: logit diff {diff} vs logit scale {scale}"
+    return diff, scale
+
+
+def check_tokens(actual, expected, expected_logits, actual_logits, what, relative=5e-2):
+    """Greedy tokens equal, or the reference's own top-2 margin is inside the tolerance and the
+    token this backend picked is one the reference scores within that margin of its best."""
+    actual = actual.cpu()
+    reference = expected_logits.float().cpu()
+    scale = float(reference.abs().max())
+    for row in range(expected.shape[0]):
+        if int(actual[row]) == int(expected[row]):
+            continue
+        gap = float(reference[row, expected[row]] - reference[row, actual[row]])
+        assert 0.0 <= gap <= relative * scale, \
+            f"{what}: row {row} picked a token {gap} below the reference's best (scale {scale})"
+
+
+@pytest.mark.parametrize("mode", ["fast", "pytorch_compatible"])
+def test_qwen2_0_5b_full_model_prefill_and_decode(mode):
+    """The whole configuration: 24 layers, hidden 896, 14/2 heads x 64, SwiGLU 4864, vocabulary
+    151936 with the tied head, q/k/v biases, theta 1e6; seed-0 N(0, 0.02) weights; a 512-token
+    prompt at batch 2 into capacity 640; 8 teacher-forced greedy decode steps on the same KV
+    buffers from the captured CUDA graph."""
+    config = q2.QWEN2_0_5B
+    steps = 8
+    weights = q2.make_weights(config, seed=0, dtype=torch.bfloat16)
+    prompt = q2.make_prompt_ids(config, 2, 512, seed=0)
+    with torch.no_grad():
+        ref_tokens, ref_logits, ref_state = qwen2_model.greedy_generate(config, weights, prompt,
+                                                                        steps, capacity=640)
+    engine = Qwen2Engine(config, {k: v.cuda() for k, v in weights.items()}, batch=2, capacity=640,
+                         numerical_mode=mode)
+    pointers = [k.data_ptr() for k in engine.state.keys]
+    engine.prefill(prompt)
+    worst = [check_logits(engine.logits, ref_logits[0], "prefill")]
+    check_tokens(engine.next_ids, ref_tokens[:, 0], ref_logits[0], engine.logits, "prefill")
+    engine.capture()
+    for step in range(steps):
+        engine.input_ids.copy_(ref_tokens[:, step].cuda())  # teacher forcing
+        engine.decode_step(feed_back=False)
+        worst.append(check_logits(engine.logits, ref_logits[step + 1], f"decode step {step}"))
+        check_tokens(engine.next_ids, ref_tokens[:, step + 1], ref_logits[step + 1], engine.logits,
+                     f"decode step {step}")
+    engine.state.check()
+    assert pointers == [k.data_ptr() for k in engine.state.keys]
+    used = 512 + steps
+    assert all(int(l.min()) == used == int(l.max()) for l in engine.state.lengths)
+    for layer in (0, 11, 23):
+        close(engine.state.keys[layer][:, :used], ref_state.keys[layer][:, :used])
+        close(engine.state.values[layer][:, :used], ref_state.values[layer][:, :used])
+    print(f"qwen2-0.5b {mode}: worst logit diff {max(d for d, _ in worst):.3e}, "
+          f"logit scale {worst[0][1]:.3e}")
+
+
+def test_qwen2_7b_full_width_layers_ragged_contexts():
+    """Qwen2-7B layer shapes at full width (hidden 3584, 28/4 heads x 128, SwiGLU 18944, untied
+    head) with 4 layers and a reduced vocabulary; 4 sequences whose KV contexts are uniform in
+    [1024, 8192] and pre-filled with N(0, 1) as the serving configuration prescribes; 2
+    teacher-forced decode steps from the captured graph against the oracle on the same KV."""
+    config = q2.Qwen2Config(hidden_size=3584, intermediate_size=18944, num_layers=4, num_heads=28,
+                            num_kv_heads=4, rms_norm_eps=1e-6, rope_theta=1e6, vocab_size=8192,
+                            tie_word_embeddings=False)
+    batch, capacity, steps = 4, 8256, 2
+    weights = q2.make_weights(config, seed=0, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(512)
+    contexts = torch.randint(1024, 8193, (batch,), generator=g)
+    contexts[0], contexts[1] = 8192, 1024  # both ends of the range are present
+    state = qwen2_model.OracleKVState([], [], [], capacity)
+    engine = Qwen2Engine(config, {k: v.cuda() for k, v in weights.items()}, batch=batch,
+                         capacity=capacity)
+    for layer in range(config.num_layers):
+        shape = (batch, capacity, config.num_kv_heads, config.head_dim)
+        state.keys.append(torch.randn(shape, generator=g).bfloat16())
+        state.values.append(torch.randn(shape, generator=g).bfloat16())
+        state.lengths.append(contexts.clone())
+        engine.state.keys[layer].copy_(state.keys[layer])
+        engine.state.values[layer].copy_(state.values[layer])
+    ids = torch.randint(0, config.vocab_size, (batch,), generator=g)
+    engine.load_context(contexts, next_ids=ids)
+    engine.capture()
+    for step in range(steps):
+        with torch.no_grad():
+            expected = qwen2_model.decode(config, weights, ids.view(-1, 1), state)[:, 0]
+        engine.input_ids.copy_(ids.cuda())
+        engine.decode_step(feed_back=False)
+        check_logits(engine.logits, expected, f"decode step {step}")
+        check_tokens(engine.next_ids, expected.argmax(-1), expected, engine.logits, f"decode step {step}")
+        ids = expected.argmax(-1)
+    engine.state.check()
+    for layer in range(config.num_layers):
+        for row in range(batch):
+            used = int(contexts[row]) + steps
+            close(engine.state.keys[layer][row, :used], state.keys[layer][row, :used])
+            close(engine.state.values[layer][row, :used], state.values[layer][row, :used])

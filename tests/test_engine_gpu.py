@@ -174,3 +174,31 @@ def test_qwen2_7b_shaped_layers_match_oracle():
         assert_logits(engine.logits, ref_logits[step + 1], 2e-2)
         assert_tokens(engine.next_ids, ref_tokens[:, step + 1], ref_logits[step + 1], 2e-2)
     engine.state.check()
+
+
+def test_captured_graph_survives_workspace_growth():
+    """A captured step has its workspace addresses baked in. A second, larger engine on the same
+    GPU outgrows the shared workspaces; the runtime must retire the old buffers instead of
+    freeing them, so that replays of the first graph still match an eager step bit for bit."""
+    config = q2.Qwen2Config(hidden_size=896, intermediate_size=4864, num_layers=2, num_heads=14,
+                            num_kv_heads=2, rms_norm_eps=1e-6, rope_theta=1e6, vocab_size=4096,
+                            tie_word_embeddings=True)
+    weights = {k: v.cuda() for k, v in q2.make_weights(config, seed=9, dtype=torch.bfloat16).items()}
+    prompt = q2.make_prompt_ids(config, 4, 300, seed=3)
+    small = Qwen2Engine(config, weights, batch=4, capacity=2048)
+    small.split_tokens = 256  # several KV splits: the attention scratch is in use
+    small.prefill(prompt)
+    small.capture()
+    eager = Qwen2Engine(config, weights, batch=4, capacity=2048)
+    eager.split_tokens = 256
+    eager.prefill(prompt)
+    large = Qwen2Engine(config, weights, batch=64, capacity=4096)
+    large.split_tokens = 256
+    large.prefill(q2.make_prompt_ids(config, 64, 700, seed=4))
+    junk = []
+    for step in range(4):
+        large.decode_step()  # grows the workspaces, then keeps writing into the new ones
+        junk.append(torch.full((1 << 20,), float(step), device="cuda"))  # takes freed blocks, if any
+        assert torch.equal(small.decode_step(), eager.decode_step())
+        assert torch.equal(small.logits, eager.logits)
+    small.state.check()
