@@ -300,6 +300,16 @@ int b200_copy_4d(const void* input, void* output, const int64_t sizes[4],
  * contiguous (slots x batch). */
 int b200_advance_lengths(int64_t* lengths, int64_t slots, int64_t batch, int64_t delta,
                          int64_t capacity, int32_t* status, void* stream);
+/* Run-time proof of causality for serve.prefill_attention. The reference op carries
+ * `causal: "mask"` and an arbitrary additive B x 1 x T x T mask
+ * (passes/prefill_attention.py:173-180) and names a proved `causal=true` as its follow-up
+ * (docs/prefill-attention.md:43-45). flag[0] becomes 1 if every entry is exactly 0 on and
+ * below the diagonal and -inf above it (the mask make_qwen2_prefill_inputs builds,
+ * qwen2.py:552-572), else 0; the host reads it once per mask tensor and then calls
+ * b200_prefill_attention with causal = 1, which reads no mask. strides are element strides
+ * of the 4-D mask (a batch stride of 0 means one mask for all sequences). */
+int b200_classify_causal_mask(const void* mask, int64_t batch, int64_t tokens,
+                              const int64_t strides[4], int dtype, int32_t* flag, void* stream);
 /* Greedy sampling: ids[r] = argmax(logits[r, :]) (lowest index wins ties), the step
  * the reference's callers do with torch.argmax (benchmarks/validate_qwen2_checkpoint.py:365-396). */
 int b200_argmax(const void* logits, int64_t* ids, int64_t rows, int64_t vocab,

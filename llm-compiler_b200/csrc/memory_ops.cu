@@ -419,6 +419,30 @@ __global__ void advance_lengths_kernel(int64_t* lengths, int64_t count, int64_t 
   lengths[idx] = v;
 }
 
+// ------------------------------------------------------------ mask classifier ----
+// flag[0] stays 1 only if every entry of the additive B x 1 x T x T mask is exactly 0 on and
+// below the diagonal and -inf above it (the mask make_qwen2_prefill_inputs builds,
+// qwen2.py:552-572). Grid-stride over B * T * T entries; a CTA that finds a violation clears
+// the flag once. The caller sets flag[0] = 1 before the launch (b200_classify_causal_mask does).
+__global__ void set_flag_kernel(int32_t* flag) { *flag = 1; }
+
+template <typename T>
+__global__ void classify_causal_mask_kernel(const T* __restrict__ mask, int64_t batch,
+                                            int64_t tokens, int64_t stride_b, int64_t stride_q,
+                                            int64_t stride_k, int32_t* flag) {
+  const int64_t total = batch * tokens * tokens;
+  bool ok = true;
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t k = idx % tokens;
+    const int64_t q = (idx / tokens) % tokens;
+    const int64_t b = idx / (tokens * tokens);
+    const float v = Elem<T>::load(mask + b * stride_b + q * stride_q + k * stride_k);
+    ok = ok && (k <= q ? v == 0.0f : (v == -INFINITY));
+  }
+  if (__syncthreads_or(!ok) && threadIdx.x == 0) atomicAnd(flag, 0);
+}
+
 constexpr int kArgmaxThreads = 1024;
 
 template <typename T>
@@ -747,6 +771,26 @@ int b200_advance_lengths(int64_t* lengths, int64_t slots, int64_t batch, int64_t
   advance_lengths_kernel<<<static_cast<int>(ceil_div(count, kThreads)), kThreads, 0,
                            static_cast<cudaStream_t>(stream)>>>(lengths, count, delta, capacity,
                                                                 status);
+  return launch_status();
+}
+
+int b200_classify_causal_mask(const void* mask, int64_t batch, int64_t tokens,
+                              const int64_t strides[4], int dtype, int32_t* flag, void* stream) {
+  if (!mask || !strides || !flag || batch <= 0 || tokens <= 0) return B200_ERR_BAD_ARGUMENT;
+  if (dtype != B200_F32 && dtype != B200_BF16) return B200_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // a batch-broadcast mask (stride 0) is checked once
+  const int64_t distinct = strides[0] == 0 ? 1 : batch;
+  const int64_t total = distinct * tokens * tokens;
+  const int grid = static_cast<int>(std::min<int64_t>(ceil_div(total, kThreads), 16 * kNumSMs));
+  set_flag_kernel<<<1, 1, 0, s>>>(flag);
+  if (dtype == B200_F32)
+    classify_causal_mask_kernel<float><<<grid, kThreads, 0, s>>>(
+        static_cast<const float*>(mask), distinct, tokens, strides[0], strides[2], strides[3], flag);
+  else
+    classify_causal_mask_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(mask), distinct, tokens, strides[0], strides[2],
+        strides[3], flag);
   return launch_status();
 }
 

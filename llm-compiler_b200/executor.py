@@ -86,9 +86,16 @@ def bind_arguments(function, weights: Dict[str, torch.Tensor], inputs: Dict[str,
 
 
 class B200Executor:
-    def __init__(self, *, strict: bool = True) -> None:
+    """`classify_masks`: prefill attention whose graph attribute is still `causal: "mask"` has
+    its mask tensor checked on the device once per tensor (one host read, skipped under graph
+    capture); a mask proved causal takes the mask-free tcgen05 kernel, anything else the
+    general additive-mask kernel."""
+
+    def __init__(self, *, strict: bool = True, classify_masks: bool = True) -> None:
         self.strict = strict
+        self.classify_masks = classify_masks
         self.lowering_trace: List[Dict[str, Any]] = []
+        self._constants: Dict[Any, Any] = {}  # weight-preparation results, by operand storage
         self._handlers = {
             "kernel.b200.rms_norm": self._rms_norm,
             "kernel.b200.linear": self._linear,
@@ -99,6 +106,10 @@ class B200Executor:
             "kernel.b200.kv_store": self._kv_store,
             "kernel.b200.kv_prefill_store": self._kv_prefill_store,
             "kernel.b200.embedding": self._embedding,
+            "kernel.b200.rope_kv_store": self._rope_kv_store,
+            "kernel.b200.pack_rows": lambda o, a, e: kernels.b200_pack_rows(*o),
+            "kernel.b200.interleave_rows": lambda o, a, e: kernels.interleave_gate_up(o[0], o[1]),
+            "runtime.view.slice": self._slice,
             "kernel.b200.swiglu": lambda o, a, e: kernels.b200_swiglu(o[0], o[1]),
             "kernel.b200.add": lambda o, a, e: kernels.b200_add(o[0], o[1]),
             "kernel.b200.contiguous": self._contiguous,
@@ -136,7 +147,10 @@ class B200Executor:
                     f"the B200 executor has no kernel for {operation.name}: run "
                     "kernel_ir.lower_to_b200 on the module first (there is no eager fallback)")
             operands = [environment[value.name] for value in operation.operands]
-            results = handler(operands, operation.attributes, environment)
+            if operation.attributes.get("constant") is True:
+                results = self._constant(operation, handler, operands, environment)
+            else:
+                results = handler(operands, operation.attributes, environment)
             expected = len(operation.results)
             if expected == 1:
                 results = (results,)
@@ -149,6 +163,19 @@ class B200Executor:
             trace.append(operation.name)
         outputs = tuple(environment[value.name] for value in function.returns)
         return ExecutionResult(outputs, tuple(trace), {})
+
+    def _constant(self, operation, handler, operands, environment):
+        """Weight-preparation ops (`constant: true`) depend on graph parameters only: evaluated
+        once per set of weight tensors (same storage, same version) and kept."""
+
+        key = (operation.name, operation.results[0].name,
+               tuple((t.data_ptr(), tuple(t.shape), t._version) for t in operands))
+        if key not in self._constants:
+            if torch.cuda.is_current_stream_capturing():
+                raise ExecutionError(
+                    f"{operation.name} prepares weights: run the module once before capturing it")
+            self._constants[key] = handler(operands, operation.attributes, environment)
+        return self._constants[key]
 
     @staticmethod
     def _validate_argument(declared, runtime_value) -> None:
@@ -236,11 +263,18 @@ class B200Executor:
             raise ExecutionError("prefill_attention: GQA groups mismatch")
         variant = self._decide("prefill_attention", attributes, query.shape[2]) \
             if "lowering_plan" in attributes else None
+        causal = attributes.get("causal") is True
+        proof = attributes.get("causal_proof") if causal else None
+        if not causal and self.classify_masks and mask is not None and \
+                not torch.cuda.is_current_stream_capturing():
+            causal = kernels.b200_mask_is_causal(mask)
+            proof = "classified" if causal else None
+        self.lowering_trace.append({"backend": "b200", "op": "prefill_attention.mask",
+                                    "causal": causal, "proof": proof})
         with kernels.kernel_variants(prefill_attention=variant):
             return kernels.b200_prefill_attention(
-                query, key, value, mask, scale=float(attributes["scale"]),
-                causal=attributes.get("causal") is True,
-                numerical_mode=attributes.get("numerical_mode", "fast"))
+                query, key, value, None if causal else mask, scale=float(attributes["scale"]),
+                causal=causal, numerical_mode=attributes.get("numerical_mode", "fast"))
 
     def _decode_attention(self, operands, attributes, environment):
         if len(operands) != 3:
@@ -264,6 +298,24 @@ class B200Executor:
             raise ExecutionError("kv_store takes state, key, value and positions")
         state = _as_state(operands[0])
         return state.store(int(attributes.get("slot", 0)), operands[1], operands[2], operands[3])
+
+    @staticmethod
+    def _rope_kv_store(operands, attributes, environment):
+        if len(operands) != 6:
+            raise ExecutionError("rope_kv_store takes state, query, key, value, cosine and sine")
+        state = _as_state(operands[0])
+        query, key, value, cosine, sine = operands[1:]
+        if query.shape[-1] != int(attributes["head_dim"]):
+            raise ExecutionError("rope_kv_store: head_dim does not match the attribute")
+        key_buffer, value_buffer, positions = state._slot(int(attributes.get("slot", 0)))
+        rotated = kernels.b200_rope_kv_store(query, key, value, cosine, sine, key_buffer,
+                                             value_buffer, positions)
+        return rotated, state
+
+    @staticmethod
+    def _slice(operands, attributes, environment):
+        tensor, axis, start, stop = decode_attribute(attributes["args"], environment)
+        return tensor.narrow(int(axis), int(start), int(stop) - int(start))
 
     @staticmethod
     def _kv_prefill_store(operands, attributes, environment):

@@ -1,0 +1,267 @@
+"""Graph-level fusion passes of the B200 lowering.
+
+The reference lowers op by op and names the graph-level forms as its own next steps: a fused
+SwiGLU op and fused q|k|v / gate|up projections (docs/rope-lowering.md:162-163,
+docs/qwen2-0.5b-validation.md:200) and a compiler-proved `causal: true` prefill attention
+(docs/prefill-attention.md:43-45). These passes do that on the KernelIR itself, after
+`kernel_ir.lower_to_b200` has renamed every op, so that a module compiled by the reference
+and run by `B200Executor` launches the same kernels as a hand-wired engine:
+
+  pack_qkv            three linears on one input  -> pack_rows (weights, once) + ONE linear
+                                                     + three runtime.view.slice views
+  pack_gate_up        swiglu(linear, linear)      -> interleave_rows (once) + ONE linear whose
+                                                     epilogue is SwiGLU
+  mark_causal_masks   prefill_attention whose mask is a caller-declared causal argument
+                                                  -> causal: true (the mask is not read)
+  fuse_rope_kv_store  rope -> kv.length -> kv_store of ONE token
+                                                  -> kernel.b200.rope_kv_store (one launch)
+  chain_decode_layers (fast bf16 decode graphs)   -> the 5-launch decode layer: RMSNorm folded
+                                                     into the next projection, split-K
+                                                     projections that add their residual,
+                                                     q|k|v reduction + RoPE + KV store inside
+                                                     the attention launch
+
+Weight-preparation ops carry `"constant": true`: their operands are graph parameters, the
+executor evaluates them once per set of weight tensors and caches the result.
+"""
+
+from __future__ import annotations
+
+import re
+from typing import Any, Dict, List, Optional, Sequence
+
+from .kernel_ir import Operation, Value, _producer_map, _users, value_dtype
+
+_DIMS = re.compile(r"^tensor<(.*)x([a-z]+\d*), *([^>]+)>$")
+
+
+def _split_dims(text: str) -> List[str]:
+    parts, depth, current = [], 0, ""
+    for char in text:
+        if char == "<":
+            depth += 1
+        elif char == ">":
+            depth -= 1
+        if char == "x" and depth == 0:
+            parts.append(current)
+            current = ""
+        else:
+            current += char
+    parts.append(current)
+    return parts
+
+
+def retype(value, axis: int, extent: int) -> str:
+    """Type string of `value` with dimension `axis` replaced by the static `extent`."""
+
+    match = _DIMS.match(str(value.type))
+    if not match:
+        raise ValueError(f"not a tensor type: {value.type}")
+    dims = _split_dims(match.group(1))
+    dims[axis] = str(int(extent))
+    return f"tensor<{'x'.join(dims)}x{match.group(2)}, {match.group(3)}>"
+
+
+def _static_extent(value, axis: int) -> Optional[int]:
+    match = _DIMS.match(str(value.type))
+    if not match:
+        return None
+    text = _split_dims(match.group(1))[axis].strip()
+    return int(text) if text.isdigit() else None
+
+
+def _is_parameter(function, value) -> bool:
+    return any(argument is value or argument.name == value.name
+               for argument in function.block.arguments)
+
+
+def _fresh(function, stem: str) -> str:
+    taken = {a.name for a in function.block.arguments} | \
+        {r.name for op in function.block.operations for r in op.results}
+    index = 0
+    while f"%{stem}_{index}" in taken:
+        index += 1
+    return f"%{stem}_{index}"
+
+
+def _mode_of(operation) -> str:
+    return operation.attributes.get("numerical_mode", "fast")
+
+
+# ------------------------------------------------------------------ q|k|v packing ----
+def pack_qkv(function) -> int:
+    """Groups of >= 2 `kernel.b200.linear` ops without an epilogue that read the same input
+    and whose weights (and biases) are graph parameters become one projection over the
+    row-concatenated weight. Only groups of exactly three with equal bias presence are packed
+    (q, k, v); gate / up pairs are left to `pack_gate_up`."""
+
+    packed = 0
+    by_input: Dict[str, List[Any]] = {}
+    for operation in function.block.operations:
+        if operation.name == "kernel.b200.linear" and not operation.attributes.get("epilogue"):
+            by_input.setdefault(operation.operands[0].name, []).append(operation)
+    for group in by_input.values():
+        if len(group) != 3:
+            continue
+        has_bias = [bool(op.attributes.get("has_bias")) for op in group]
+        if len(set(has_bias)) != 1:
+            continue
+        if not all(_is_parameter(function, operand) for op in group for operand in op.operands[1:]):
+            continue
+        if len({value_dtype(op.results[0]) for op in group}) != 1 or \
+                len({_mode_of(op) for op in group}) != 1:
+            continue
+        widths = [_static_extent(op.operands[1], 0) for op in group]
+        if any(width is None for width in widths):
+            continue
+        first = function.block.operations.index(group[0])
+        total = sum(widths)
+        weight = Value(_fresh(function, "packed_weight"), retype(group[0].operands[1], 0, total))
+        prepared = [Operation("kernel.b200.pack_rows", [op.operands[1] for op in group], [weight],
+                              {"constant": True, "lowered_from": "weight preparation"})]
+        operands = [group[0].operands[0], weight]
+        if has_bias[0]:
+            bias = Value(_fresh(function, "packed_bias"), retype(group[0].operands[2], 0, total))
+            prepared.append(Operation("kernel.b200.pack_rows", [op.operands[2] for op in group],
+                                      [bias], {"constant": True, "lowered_from": "weight preparation"}))
+            operands.append(bias)
+        output = Value(_fresh(function, "qkv"), retype(group[0].results[0], -1, total))
+        attributes = {key: value for key, value in group[0].attributes.items()
+                      if key not in ("args", "fx_name", "lowering_plan")}
+        attributes.update({"output_features": total, "has_bias": has_bias[0],
+                           "lowered_from": "+".join(["kernel.b200.linear"] * 3),
+                           "packed": [int(width) for width in widths]})
+        fused = Operation("kernel.b200.linear", operands, [output], attributes)
+        slices, offset = [], 0
+        for op, width in zip(group, widths):
+            slices.append(Operation(
+                "runtime.view.slice", [output], list(op.results),
+                {"args": {"tuple": [{"ssa": output.name}, -1, offset, offset + width]},
+                 "lowered_from": "kernel.b200.linear"}))
+            offset += width
+        # everything goes where the first projection stood: its operands are defined before it,
+        # and the users of the second and third projection come later still
+        remaining = [op for op in function.block.operations if all(op is not g for g in group)]
+        function.block.operations = remaining[:first] + prepared + [fused] + slices + remaining[first:]
+        packed += 1
+    return packed
+
+
+# ---------------------------------------------------------------- gate|up packing ----
+def pack_gate_up(function) -> int:
+    """swiglu(linear(x, Wg), linear(x, Wu)) with parameter weights and no other users of the
+    two products becomes one linear over the row-interleaved weight with a SwiGLU epilogue."""
+
+    producers = _producer_map(function)
+    users = _users(function)
+    packed = 0
+    for swiglu in list(function.block.operations):
+        if swiglu.name != "kernel.b200.swiglu":
+            continue
+        gate, up = (producers.get(operand.name) for operand in swiglu.operands)
+        if gate is None or up is None or gate is up:
+            continue
+        if any(op.name != "kernel.b200.linear" or op.attributes.get("epilogue") or
+               op.attributes.get("has_bias") or len(users.get(op.results[0].name, [])) != 1
+               for op in (gate, up)):
+            continue
+        if gate.operands[0].name != up.operands[0].name or \
+                not _is_parameter(function, gate.operands[1]) or \
+                not _is_parameter(function, up.operands[1]) or _mode_of(gate) != _mode_of(up):
+            continue
+        width = _static_extent(gate.operands[1], 0)
+        if width is None or width != _static_extent(up.operands[1], 0):
+            continue
+        weight = Value(_fresh(function, "gate_up_weight"), retype(gate.operands[1], 0, 2 * width))
+        prepared = Operation("kernel.b200.interleave_rows", [gate.operands[1], up.operands[1]],
+                             [weight], {"constant": True, "lowered_from": "weight preparation"})
+        attributes = {key: value for key, value in gate.attributes.items()
+                      if key not in ("args", "fx_name", "lowering_plan")}
+        attributes.update({"output_features": 2 * width, "epilogue": "swiglu",
+                           "lowered_from": "kernel.b200.linear+kernel.b200.linear+kernel.b200.swiglu"})
+        fused = Operation("kernel.b200.linear", [gate.operands[0], weight], list(swiglu.results),
+                          attributes)
+        operations = function.block.operations
+        anchor = min(operations.index(gate), operations.index(up))  # nothing removed lies before it
+        rest = [op for op in operations if op is not gate and op is not up and op is not swiglu]
+        function.block.operations = rest[:anchor] + [prepared, fused] + rest[anchor:]
+        producers = _producer_map(function)
+        users = _users(function)
+        packed += 1
+    return packed
+
+
+# ----------------------------------------------------------------- causal masks ----
+def _through_casts(value, producers):
+    while value.name in producers and producers[value.name].name in ("kernel.b200.cast",
+                                                                     "aten.to.dtype"):
+        value = producers[value.name].operands[0]
+    return value
+
+
+def mark_causal_masks(function, causal_mask_arguments: Sequence[str]) -> int:
+    """`causal_mask_arguments` names graph inputs the caller promises to be causal masks (0 on
+    and below the diagonal, -inf above): prefill attention fed by one of them is rewritten to
+    the mask-free causal form. The operand stays (the signature is unchanged); the kernel does
+    not read it. Graph inputs nobody vouches for keep `causal: "mask"`; the executor may still
+    classify the tensor at run time."""
+
+    names = {name if name.startswith("%") else f"%{name}" for name in causal_mask_arguments}
+    producers = _producer_map(function)
+    marked = 0
+    for operation in function.block.operations:
+        if operation.name != "kernel.b200.prefill_attention" or len(operation.operands) != 4:
+            continue
+        source = _through_casts(operation.operands[3], producers)
+        if source.name in names and _is_parameter(function, source) and \
+                operation.attributes.get("causal") is not True:
+            operation.attributes["causal"] = True
+            operation.attributes["causal_proof"] = f"declared:{source.name}"
+            marked += 1
+    return marked
+
+
+# ------------------------------------------------------------- rope + kv.store ----
+def fuse_rope_kv_store(function) -> int:
+    """Decode graphs: rope(q, k) -> kv.length(slot) -> kv_store(state, k', v, positions) with
+    one token per sequence becomes `kernel.b200.rope_kv_store` (rotates q and k, writes k' and v
+    into the slot at the slot's positions, returns q' and the state) when k' has no other user."""
+
+    users = _users(function)
+    producers = _producer_map(function)
+    fused = 0
+    for store in list(function.block.operations):
+        if store.name != "kernel.b200.kv_store" or len(store.operands) != 4:
+            continue
+        state, key, value, positions = store.operands
+        rope = producers.get(key.name)
+        length = producers.get(positions.name)
+        if rope is None or rope.name != "kernel.b200.rope" or rope.results[1].name != key.name or \
+                length is None or length.name != "runtime.kv.length" or \
+                length.operands[0].name != state.name or \
+                int(length.attributes.get("slot", 0)) != int(store.attributes.get("slot", 0)):
+            continue
+        if len(users.get(key.name, [])) != 1 or _static_extent(rope.results[0], 2) != 1:
+            continue
+        operations = function.block.operations
+        if not operations.index(rope) < operations.index(store):
+            continue
+        if any(user == "return" or operations.index(user) < operations.index(store)
+               for user in users.get(rope.results[0].name, [])):
+            continue  # the rotated query is needed before the store: keep the ops apart
+        merged = Operation(
+            "kernel.b200.rope_kv_store",
+            [state, rope.operands[0], rope.operands[1], value, rope.operands[2], rope.operands[3]],
+            [rope.results[0], store.results[0]],
+            {"slot": int(store.attributes.get("slot", 0)), "head_dim": rope.attributes.get("head_dim"),
+             "numerical_mode": _mode_of(rope),
+             "lowered_from": "kernel.b200.rope+runtime.kv.length+kernel.b200.kv_store"})
+        position = operations.index(store)
+        operations[position] = merged
+        operations.remove(rope)
+        if len(users.get(positions.name, [])) == 1:
+            operations.remove(length)
+        users = _users(function)
+        producers = _producer_map(function)
+        fused += 1
+    return fused

@@ -172,7 +172,10 @@ _ELEMENTWISE_SOURCES = {
 EXECUTABLE_OPERATIONS = frozenset(_KERNEL_SOURCES.values()) | frozenset(_RUNTIME_SOURCES.values()) | \
     frozenset(_ELEMENTWISE_SOURCES.values()) | frozenset({
         "runtime.kv.init", "runtime.kv.length", "runtime.kv.advance",
-        "kernel.b200.rope_table", "kernel.b200.swiglu"})
+        "kernel.b200.rope_table", "kernel.b200.swiglu",
+        # produced by the graph-level fusion passes (fusion.py)
+        "kernel.b200.pack_rows", "kernel.b200.interleave_rows", "runtime.view.slice",
+        "kernel.b200.rope_kv_store"})
 
 NUMERICAL_MODES = ("fast", "pytorch_compatible")
 
@@ -272,7 +275,8 @@ def _replace_uses(function, old, new) -> None:
     function.returns = [new if (v is old or v.name == old.name) else v for v in function.returns]
 
 
-_PURE_PREFIXES = ("aten.", "kernel.b200.rope_table", "kernel.b200.swiglu", "runtime.view.")
+_PURE_PREFIXES = ("aten.", "kernel.b200.rope_table", "kernel.b200.swiglu", "runtime.view.",
+                  "kernel.b200.pack_rows", "kernel.b200.interleave_rows")
 
 
 def _is_pure(operation) -> bool:
@@ -437,10 +441,15 @@ class LoweringReport:
 
 
 def lower_to_b200(module, *, numerical_mode: Optional[str] = None,
-                  fuse_epilogues: bool = True) -> LoweringReport:
+                  fuse_epilogues: bool = True, fuse_graph: bool = True,
+                  causal_mask_arguments: Iterable[str] = ()) -> LoweringReport:
     """Rewrites `module` in place for the B200 target. `numerical_mode` overrides the mode the
     reference's pass recorded on each op (attribute `numerical_mode`, or implied by a
-    `kernel.cuda.*` / `kernel.cublas.*` name); default "fast". Idempotent."""
+    `kernel.cuda.*` / `kernel.cublas.*` name); default "fast". `fuse_graph` runs the
+    graph-level passes of fusion.py (packed q|k|v and gate|up projections, fused rope + KV
+    store of a decode step); `causal_mask_arguments` names graph inputs the caller declares to
+    be causal masks, which turns the prefill attention they feed into the mask-free causal
+    form. Idempotent."""
 
     if numerical_mode is not None and numerical_mode not in NUMERICAL_MODES:
         raise ValueError(f"unknown numerical mode {numerical_mode!r}; choose from {NUMERICAL_MODES}")
@@ -471,6 +480,16 @@ def lower_to_b200(module, *, numerical_mode: Optional[str] = None,
             rules[f"{source}->{target}"] += 1
         if fuse_epilogues:
             rules["linear+residual"] += _fuse_residual_epilogues(function)
+        if fuse_graph:
+            from . import fusion
+
+            rules["pack_qkv"] += fusion.pack_qkv(function)
+            rules["pack_gate_up"] += fusion.pack_gate_up(function)
+            rules["rope+kv_store"] += fusion.fuse_rope_kv_store(function)
+        if causal_mask_arguments:
+            from . import fusion
+
+            rules["causal_mask"] += fusion.mark_causal_masks(function, tuple(causal_mask_arguments))
     return LoweringReport(numerical_mode or "per-op", {k: v for k, v in sorted(rules.items()) if v},
                           removed_casts, removed_dead, analyze_lowering_coverage(module))
 

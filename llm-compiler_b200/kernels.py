@@ -654,6 +654,61 @@ def b200_prefill_attention(query: torch.Tensor, key: torch.Tensor, value: torch.
     return storage.transpose(1, 2)
 
 
+_causal_verdicts: dict = {}
+
+
+def b200_mask_is_causal(attention_mask: torch.Tensor) -> bool:
+    """Run-time proof that an additive B x 1 x T x T mask is exactly the causal mask (0 on and
+    below the diagonal, -inf above): one pass of a classifier kernel over the mask and ONE host
+    read of its verdict (a synchronisation), remembered per (storage, shape, strides, version)
+    so that the layers of a model, which all receive the same tensor, pay it once. The
+    reference names the proved form as the follow-up of its `causal: "mask"` contract
+    (docs/prefill-attention.md:43-45). Never call it under CUDA-graph capture."""
+
+    device = _require_cuda(attention_mask)
+    if attention_mask.ndim != 4 or attention_mask.shape[1] != 1 or \
+            attention_mask.shape[2] != attention_mask.shape[3]:
+        return False
+    if attention_mask.dtype not in _DTYPE_CODES:
+        return False
+    key = (device.index, attention_mask.data_ptr(), tuple(attention_mask.shape),
+           tuple(attention_mask.stride()), attention_mask._version, attention_mask.dtype)
+    verdict = _causal_verdicts.get(key)
+    if verdict is None:
+        rt = runtime(device)
+        flag = torch.empty(1, dtype=torch.int32, device=device)
+        strides = list(attention_mask.stride())
+        if attention_mask.shape[0] == 1:
+            strides[0] = 0
+        code = _lib.load().b200_classify_causal_mask(
+            attention_mask.data_ptr(), attention_mask.shape[0], attention_mask.shape[2],
+            _lib.i64_array(strides), _code(attention_mask.dtype), flag.data_ptr(), _stream())
+        _check(code, "b200_classify_causal_mask")
+        _count(rt, 2)
+        verdict = bool(flag.item())
+        if len(_causal_verdicts) > 64:
+            _causal_verdicts.clear()
+        _causal_verdicts[key] = verdict
+    return verdict
+
+
+def b200_pack_rows(*tensors: torch.Tensor) -> torch.Tensor:
+    """Weight preparation: rows of several matrices (or entries of several vectors) one after
+    the other, e.g. q|k|v projection weights into one matrix. A one-time device copy."""
+
+    device = _require_cuda(*tensors)
+    first = tensors[0]
+    if any(t.shape[1:] != first.shape[1:] or t.dtype != first.dtype for t in tensors):
+        raise ValueError("packed tensors must agree on dtype and trailing dimensions")
+    rows = sum(t.shape[0] for t in tensors)
+    packed = torch.empty((rows, *first.shape[1:]), dtype=first.dtype, device=device)
+    offset = 0
+    for tensor in tensors:
+        packed[offset:offset + tensor.shape[0]].copy_(tensor)
+        offset += tensor.shape[0]
+    return packed
+
+
 # -------------------------------------------------------------------------- linear ----
 def linear_workspace_bytes(m: int, k: int, n: int, dtype: torch.dtype,
                            epilogue: str = "none") -> int:

@@ -18,8 +18,10 @@ pytestmark = pytest.mark.gpu
 GOLDEN = Path(__file__).resolve().parent / "golden"
 
 
-def lowered(kind, mode, **options):
-    module = ir.module_from_json(json.loads((GOLDEN / f"kernel_ir_tiny_{kind}_{mode}.json").read_text()))
+def lowered(kind, mode, tag="fp32", **options):
+    name = f"kernel_ir_tiny_{kind}_{mode}.json" if tag == "fp32" else \
+        f"kernel_ir_tiny_{tag}_{kind}_{mode}.json"
+    module = ir.module_from_json(json.loads((GOLDEN / name).read_text()))
     ir.lower_to_b200(module, **options)
     return module
 
@@ -75,7 +77,11 @@ def test_prefill_then_decode_graphs_match_the_reference_executor(mode, fuse, gol
                                gold["values"], rtol=1e-4, atol=1e-5)
     assert pointers == [k.data_ptr() for k in state.keys]  # prefill -> decode on the same buffers
     assert state.generation == config.num_layers * (1 + gold["steps"])
-    assert len(executor.lowering_trace) == 5 * (1 + gold["steps"])
+    assert len([e for e in executor.lowering_trace if "rows" in e]) == 5 * (1 + gold["steps"])
+    # the caller's mask was classified on the device once and proved causal
+    masks = [e for e in executor.lowering_trace if e.get("op") == "prefill_attention.mask"]
+    assert len(masks) == config.num_layers and all(e["causal"] and e["proof"] == "classified"
+                                                   for e in masks)
 
 
 def test_decode_graph_runs_under_cuda_graph_capture(golden_tiny):
@@ -185,3 +191,91 @@ def test_dispatch_plans_are_resolved_per_call_and_recorded(golden_tiny):
     # batch 3 is nearer to the batch-2 plan than to the batch-64 one on a log scale
     assert all(e["variant"] == "split:32" and e["value"] == prompt + 1 for e in by_op["decode_attention"])
     state.check()
+
+
+@pytest.mark.parametrize("mode", ["fast", "pytorch_compatible"])
+@pytest.mark.parametrize("fuse", [True, False])
+def test_bf16_graphs_match_the_reference_executor(mode, fuse, golden_tiny):
+    """The reference-compiled bf16 KernelIR of the 2-layer model through the drop-in path
+    (lower_to_b200 + B200Executor) against what the reference's CPU executor produced for the
+    same bf16 weights (qwen2_tiny_bf16.pt): real casts, the bf16 RoPE table inside a graph, the
+    bf16 residual epilogues, packed projections and both numerical modes."""
+    gold = golden_tiny["bf16"]
+    config = q2.Qwen2Config(**gold["config"])
+    weights = {k: v.cuda() for k, v in q2.make_weights(config, seed=0, dtype=torch.bfloat16).items()}
+    inv_freq = q2.inverse_frequency(config, "cuda")
+    batch, prompt = gold["batch"], gold["prompt"]
+    executor = B200Executor(strict=True)
+    options = dict(fuse_epilogues=fuse, fuse_graph=fuse)
+
+    def check(actual, expected):
+        scale = max(1.0, float(expected.float().abs().max()))
+        assert float((actual.float().cpu() - expected.float()).abs().max()) <= 2e-2 * scale
+
+    prefill = lowered("prefill", mode, "bf16", **options)
+    result = executor.run(prefill, bind_arguments(prefill.functions[0], weights, {
+        "input_ids": gold["input_ids"].cuda(), "attention_mask": causal_mask(batch, prompt),
+        "position_ids": torch.arange(prompt).repeat(batch, 1).cuda(), "inv_freq": inv_freq}))
+    logits, state = result.outputs
+    assert logits.dtype == torch.bfloat16
+    check(logits, gold["prefill_logits"])
+    decode = lowered("decode", mode, "bf16", **options)
+    for step in range(gold["steps"]):
+        length = prompt + step
+        logits, state = executor.run(decode, bind_arguments(decode.functions[0], weights, {
+            "input_ids": gold["tokens"][:, step].view(batch, 1).cuda(),
+            "attention_mask": torch.zeros(batch, 1, 1, length + 1, device="cuda"),
+            "position_ids": torch.full((batch, 1), length, device="cuda"),
+            "kv_state": state, "inv_freq": inv_freq})).outputs
+        check(logits[:, 0], gold["decode_logits"][step])
+        reference = gold["decode_logits"][step].float()
+        picked = logits[:, 0].float().argmax(-1).cpu()
+        for row in range(batch):
+            if int(picked[row]) != int(gold["tokens"][row, step + 1]):
+                top2 = reference[row].topk(2).values
+                assert float(top2[0] - top2[1]) <= 2e-2
+    state.check()
+    used = prompt + gold["steps"]
+    assert torch.equal(torch.stack(list(state.lengths), 0).cpu(), gold["lengths"])
+    check(torch.stack([k[:, :used] for k in state.keys], 0), gold["keys"])
+    check(torch.stack([v[:, :used] for v in state.values], 0), gold["values"])
+
+
+def test_declared_and_classified_causal_masks_and_a_mask_that_is_not_causal(golden_tiny):
+    """A caller-declared causal mask is never read (a NaN mask proves it); an undeclared one is
+    classified on the device; a mask with one hole stays on the additive-mask kernel and gives
+    the reference's answer for that mask."""
+    from oracle import qwen2_model
+
+    gold = golden_tiny["fp32"]
+    config = q2.Qwen2Config(**gold["config"])
+    cpu_weights = q2.make_weights(config, seed=0)
+    weights = {k: v.cuda() for k, v in cpu_weights.items()}
+    inv_freq = q2.inverse_frequency(config, "cuda")
+    batch, prompt = gold["batch"], gold["prompt"]
+    inputs = {"input_ids": gold["input_ids"].cuda(),
+              "position_ids": torch.arange(prompt).repeat(batch, 1).cuda(), "inv_freq": inv_freq}
+    declared = lowered("prefill", "fast", causal_mask_arguments=("attention_mask",))
+    executor = B200Executor()
+    poisoned = torch.full((batch, 1, prompt, prompt), float("nan"), device="cuda")
+    logits, _ = executor.run(declared, bind_arguments(declared.functions[0], weights, {
+        **inputs, "attention_mask": poisoned})).outputs
+    torch.testing.assert_close(logits.cpu(), gold["prefill_logits"], rtol=1e-4, atol=1e-4)
+    assert all(e["proof"] == "declared:%attention_mask" for e in executor.lowering_trace
+               if e.get("op") == "prefill_attention.mask")
+
+    plain = lowered("prefill", "fast")
+    holed = causal_mask(batch, prompt)
+    holed[1, 0, 3, 1] = float("-inf")  # sequence 1: token 3 may not see token 1
+    executor = B200Executor()
+    logits, _ = executor.run(plain, bind_arguments(plain.functions[0], weights, {
+        **inputs, "attention_mask": holed})).outputs
+    assert not any(e["causal"] for e in executor.lowering_trace if e.get("op") == "prefill_attention.mask")
+    expected, _ = qwen2_model.prefill(config, cpu_weights, gold["input_ids"], capacity=gold["capacity"],
+                                      attention_mask=holed.cpu())
+    torch.testing.assert_close(logits.cpu(), expected, rtol=1e-4, atol=1e-4)
+    assert float((expected - gold["prefill_logits"]).abs().max()) > 1e-4  # the hole matters
+    never = B200Executor(classify_masks=False)
+    never.run(plain, bind_arguments(plain.functions[0], weights, {
+        **inputs, "attention_mask": causal_mask(batch, prompt)}))
+    assert not any(e["causal"] for e in never.lowering_trace if e.get("op") == "prefill_attention.mask")
