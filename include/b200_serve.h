@@ -238,7 +238,10 @@ int b200_linear(const void* input, const void* weight, const void* bias, const v
  * input (fixed slice order: deterministic). These entry points stand for the op sequences of
  * one decoder layer of the reference graph (qwen2.py:152-304 after the passes):
  *   b200_linear_partial            serve.linear without its epilogue: partials[s, m, n] (fp32),
- *                                  s < b200_linear_partial_splits(m, k, n)
+ *                                  s < b200_linear_partial_splits(m, k, n); with row_squares
+ *                                  (fp32 [splits, m], M <= 64; may be NULL) also the sum of
+ *                                  squares of every input row over each K slice, for a consumer
+ *                                  that applies an RMSNorm folded into this projection
  *   b200_reduce_residual_rms_norm  (o_proj | down_proj result) -> aten.add (residual) ->
  *                                  serve.rms_norm of the next block: x_out = r(r(sum) + residual),
  *                                  h_out = r(w * r(x_out * rsqrt(mean(x_out^2) + eps)));
@@ -248,9 +251,9 @@ int b200_linear(const void* input, const void* weight, const void* bias, const v
  *                                  k and v into the KV buffers at positions[b]
  * bf16 only; partial buffers are caller-owned, 16-byte aligned, n a multiple of 4. */
 int64_t b200_linear_partial_splits(int64_t m, int64_t k, int64_t n);
-int b200_linear_partial(const void* input, const void* weight, void* partials, int64_t m,
-                        int64_t k, int64_t n, int64_t input_row_stride, int64_t splits,
-                        int32_t* status, void* stream);
+int b200_linear_partial(const void* input, const void* weight, void* partials,
+                        void* row_squares, int64_t m, int64_t k, int64_t n,
+                        int64_t input_row_stride, int64_t splits, int32_t* status, void* stream);
 int b200_reduce_residual_rms_norm(const void* partials, int64_t splits, const void* residual,
                                   const void* norm_weight, void* x_out, void* h_out, int64_t rows,
                                   int64_t hidden, double epsilon, int mode, void* stream);
@@ -275,8 +278,38 @@ int b200_qkv_decode_attention(const void* qkv_partials, int64_t qkv_splits, cons
                               void* value_buffer, const int64_t* lengths, void* output,
                               int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
                               int64_t capacity, int64_t mask_len, double scale,
-                              int64_t split_tokens, int64_t max_length_hint, void* workspace,
-                              int64_t workspace_bytes, int32_t* status, void* stream);
+                              int64_t split_tokens, int64_t max_length_hint,
+                              const void* norm_row_squares, int64_t norm_hidden, double norm_epsilon,
+                              void* workspace, int64_t workspace_bytes, int32_t* status,
+                              void* stream);
+
+/* ---- Decode-step chain, five launches per layer (fast mode, bf16, M <= 64 rows) ----------
+ * The serve.rms_norm in front of a projection (qwen2.py:152-304: input_layernorm -> q|k|v,
+ * post_attention_layernorm -> gate|up) is folded into that projection instead of being a launch
+ * of its own: y = rsqrt(mean(x^2) + eps) * (x (W * w_norm)^T), with the norm weight multiplied
+ * into W's columns once at load time (b200_scale_columns) and the per-row factor applied to the
+ * fp32 accumulator. The bf16 roundings of the normalised activations (execution.py:686-691) are
+ * skipped: allowed in the fast mode only, inside its 2e-2 tolerance. The o / down projections,
+ * whose results feed a residual add (aten.add, qwen2.py:299-304), reduce their K slices among
+ * the CTAs of a thread-block cluster through distributed shared memory and add the residual
+ * themselves: no partials in global memory, no reduce launch.
+ *   b200_scale_columns           out[n, k] = r(weight[n, k] * scale[k])   (weight preparation)
+ *   b200_linear_rms_input        serve.rms_norm + serve.linear (+ bias, + SwiGLU epilogue) on the
+ *                                un-normalised input and the column-scaled weight
+ *   b200_linear_splitk_residual  serve.linear + aten.add: output = r(r(x W^T) + residual);
+ *                                n a multiple of 4, M <= 128
+ * b200_qkv_decode_attention takes the same fold for the q|k|v projection: with
+ * norm_row_squares (fp32 [qkv_splits, B], what b200_linear_partial left: sum of squares of the
+ * un-normalised rows of width norm_hidden per K slice) it scales the reduced sums by
+ * rsqrt(mean(x_b^2) + norm_epsilon) before the bias; NULL keeps plain sums. */
+int b200_scale_columns(const void* weight, const void* scale, void* output, int64_t rows,
+                       int64_t columns, int dtype, void* stream);
+int b200_linear_rms_input(const void* input, const void* folded_weight, const void* bias,
+                          void* output, int64_t m, int64_t k, int64_t n, int64_t input_row_stride,
+                          double epsilon, int epilogue, int32_t* status, void* stream);
+int b200_linear_splitk_residual(const void* input, const void* weight, const void* residual,
+                                void* output, int64_t m, int64_t k, int64_t n,
+                                int64_t input_row_stride, int32_t* status, void* stream);
 
 /* ---- Ops the reference leaves to PyTorch eager (execution.py:500-528) ---------- */
 /* aten.embedding.default: out[r,:] = table[ids[r],:]. */

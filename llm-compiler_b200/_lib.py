@@ -74,14 +74,18 @@ SIGNATURES = {
     "b200_linear": (c_int, [c_void_p] * 5 + [c_int64] * 4 + [c_int, c_int, c_void_p, c_int64,
                                                               c_void_p, c_void_p]),
     "b200_linear_partial_splits": (c_int64, [c_int64, c_int64, c_int64]),
-    "b200_linear_partial": (c_int, [c_void_p] * 3 + [c_int64] * 5 + [c_void_p, c_void_p]),
+    "b200_linear_partial": (c_int, [c_void_p] * 4 + [c_int64] * 5 + [c_void_p, c_void_p]),
     "b200_reduce_residual_rms_norm": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                                               c_void_p, c_int64, c_int64, c_double, c_int, c_void_p]),
     "b200_reduce_rope_kv_store": (c_int, [c_void_p, c_int64] + [c_void_p] * 7 + [c_int64] * 5 +
                                   [c_void_p, c_void_p]),
     "b200_qkv_decode_attention": (c_int, [c_void_p, c_int64] + [c_void_p] * 7 +
                                   [c_int64] * 6 + [c_double, c_int64, c_int64, c_void_p, c_int64,
-                                                   c_void_p, c_void_p]),
+                                                   c_double, c_void_p, c_int64, c_void_p, c_void_p]),
+    "b200_scale_columns": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
+    "b200_linear_rms_input": (c_int, [c_void_p] * 4 + [c_int64] * 4 + [c_double, c_int, c_void_p,
+                                                                       c_void_p]),
+    "b200_linear_splitk_residual": (c_int, [c_void_p] * 4 + [c_int64] * 4 + [c_void_p, c_void_p]),
     "b200_embedding": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
                                c_void_p, c_void_p]),
     "b200_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),

@@ -10,7 +10,7 @@ std::atomic<int> g_launch_mode{0};
 int launch_mode() { return g_launch_mode.load(std::memory_order_relaxed); }
 }  // namespace b200
 
-extern "C" int b200_abi_version(void) { return 100; }
+extern "C" int b200_abi_version(void) { return 101; }
 
 extern "C" int b200_set_launch_mode(int flags) {
   if ((flags & ~(B200_LAUNCH_PROGRAMMATIC | B200_LAUNCH_CONSTANT_WEIGHTS |

@@ -71,13 +71,29 @@ __device__ __forceinline__ float load_cluster_f32(uint32_t local_smem_addr, int 
   return value;
 }
 
+__device__ __forceinline__ float4 load_cluster_f32x4(uint32_t local_smem_addr, int rank) {
+  uint32_t remote;
+  float4 value;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(value.x), "=f"(value.y), "=f"(value.z), "=f"(value.w)
+               : "r"(remote)
+               : "memory");
+  return value;
+}
+__device__ __forceinline__ int cluster_cta_rank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return static_cast<int>(rank);
+}
+
 // Launches `kernel`; under B200_LAUNCH_PROGRAMMATIC with the programmatic attribute. Only for
-// kernels that execute grid_dependency_wait(). cluster_x > 1 makes every cluster_x consecutive
-// CTAs along x a thread-block cluster.
+// kernels that execute grid_dependency_wait(). A cluster extent > 1 makes that many consecutive
+// CTAs along x (or z) a thread-block cluster.
 template <typename... Params, typename... Args>
-inline cudaError_t launch_chained_cluster(void (*kernel)(Params...), dim3 grid, dim3 block,
-                                          size_t smem, cudaStream_t stream, unsigned cluster_x,
-                                          Args&&... args) {
+inline cudaError_t launch_chained_cluster_xz(void (*kernel)(Params...), dim3 grid, dim3 block,
+                                             size_t smem, cudaStream_t stream, unsigned cluster_x,
+                                             unsigned cluster_z, Args&&... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
@@ -90,16 +106,23 @@ inline cudaError_t launch_chained_cluster(void (*kernel)(Params...), dim3 grid, 
     attribute[count].val.programmaticStreamSerializationAllowed = 1;
     ++count;
   }
-  if (cluster_x > 1) {
+  if (cluster_x > 1 || cluster_z > 1) {
     attribute[count].id = cudaLaunchAttributeClusterDimension;
     attribute[count].val.clusterDim.x = cluster_x;
     attribute[count].val.clusterDim.y = 1;
-    attribute[count].val.clusterDim.z = 1;
+    attribute[count].val.clusterDim.z = cluster_z;
     ++count;
   }
   config.attrs = count > 0 ? attribute : nullptr;
   config.numAttrs = count;
   return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+template <typename... Params, typename... Args>
+inline cudaError_t launch_chained_cluster(void (*kernel)(Params...), dim3 grid, dim3 block,
+                                          size_t smem, cudaStream_t stream, unsigned cluster_x,
+                                          Args&&... args) {
+  return launch_chained_cluster_xz(kernel, grid, block, smem, stream, cluster_x, 1u,
+                                   static_cast<Args&&>(args)...);
 }
 template <typename... Params, typename... Args>
 inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
@@ -151,6 +174,10 @@ struct TraceScope {
   __device__ __forceinline__ void mark_middle() {  // one more globaltimer sample
     if (record != nullptr) record[7] = trace_globaltimer();
   }
+  // extra globaltimer samples in the words that otherwise hold SM clocks (2, 4, 6)
+  __device__ __forceinline__ void stamp(int word) {
+    if (record != nullptr) record[word] = trace_globaltimer();
+  }
 };
 // Fine-grained samples from block 0 of a kernel: up to 62 SM-clock values per row of 64
 // words (word 0: kernel id, word 1: top of the kernel), rows behind the records, the row
@@ -176,6 +203,7 @@ struct TraceScope {
   __device__ __forceinline__ TraceScope(int) {}
   __device__ __forceinline__ void mark(int) {}
   __device__ __forceinline__ void mark_middle() {}
+  __device__ __forceinline__ void stamp(int) {}
 };
 struct TraceSamples {
   __device__ __forceinline__ TraceSamples(int, bool) {}

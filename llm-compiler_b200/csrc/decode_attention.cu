@@ -67,6 +67,13 @@ struct DecodeParams {
   __nv_bfloat16* kstore = nullptr;  // the KV buffers again, writable
   __nv_bfloat16* vstore = nullptr;
   int qkv_splits = 0;
+  // RMSNorm folded into the q|k|v projection (norm_row_squares != nullptr): the partials are
+  // products of the un-normalised hidden rows x [B, norm_hidden] with norm-weight-scaled
+  // projection weights, norm_row_squares[qkv_splits, B] holds sum(x_b^2) per K slice; the
+  // reduced sums are scaled by rsqrt(mean(x_b^2) + norm_eps) before the bias.
+  const float* norm_row_squares = nullptr;
+  int norm_hidden = 0;
+  float norm_eps = 0.0f;
 };
 
 // No-op hook of stream_segment.
@@ -501,6 +508,10 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
   // bf16 like the projection's own output), rotates q and k, leaves q in q_stage; the owner of
   // the newest token also stores its K / V row (first head block only) and keeps it in new_k/v.
   auto prepare_fused = [&]() {
+    float row_scale = 1.0f;
+    if (p.norm_row_squares != nullptr)
+      row_scale = rsqrtf(sum_slices(p.norm_row_squares + b, p.batch, p.qkv_splits) /
+                         static_cast<float>(p.norm_hidden) + p.norm_eps);
     const int half = D / 2;
     const int width = (p.q_heads + 2 * p.kv_heads) * D;
     const int64_t slice = static_cast<int64_t>(p.batch) * width;
@@ -527,8 +538,8 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
       const float slo = __bfloat162float(sin_row[d]), shi = __bfloat162float(sin_row[d + half]);
       const float bias_lo = p.qkv_bias != nullptr ? __bfloat162float(p.qkv_bias[column + d]) : 0.0f;
       const float bias_hi = p.qkv_bias != nullptr ? __bfloat162float(p.qkv_bias[column + d + half]) : 0.0f;
-      float lo = sum_slices(prow + column + d, slice, p.qkv_splits);
-      float hi = sum_slices(prow + column + d + half, slice, p.qkv_splits);
+      float lo = sum_slices(prow + column + d, slice, p.qkv_splits) * row_scale;
+      float hi = sum_slices(prow + column + d + half, slice, p.qkv_splits) * row_scale;
       if (p.qkv_bias != nullptr) {
         lo += bias_lo;
         hi += bias_hi;
@@ -1484,8 +1495,11 @@ extern "C" int b200_qkv_decode_attention(
     const void* qkv_partials, int64_t qkv_splits, const void* qkv_bias, const void* cosine,
     const void* sine, void* key_buffer, void* value_buffer, const int64_t* lengths, void* output,
     int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim, int64_t capacity,
-    int64_t mask_len, double scale, int64_t split_tokens, int64_t max_length_hint, void* workspace,
+    int64_t mask_len, double scale, int64_t split_tokens, int64_t max_length_hint,
+    const void* norm_row_squares, int64_t norm_hidden, double norm_epsilon, void* workspace,
     int64_t workspace_bytes, int32_t* status, void* stream) {
+  if (norm_row_squares != nullptr && (norm_hidden <= 0 || !(norm_epsilon >= 0.0)))
+    return B200_ERR_BAD_ARGUMENT;
   if (!qkv_partials || !cosine || !sine || !key_buffer || !value_buffer || !lengths || !output ||
       qkv_splits <= 0 || batch < 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 ||
       capacity <= 0 || mask_len <= 0 || mask_len > capacity || q_heads % kv_heads != 0 ||
@@ -1537,6 +1551,9 @@ extern "C" int b200_qkv_decode_attention(
   p.kstore = static_cast<__nv_bfloat16*>(key_buffer);
   p.vstore = static_cast<__nv_bfloat16*>(value_buffer);
   p.qkv_splits = static_cast<int>(qkv_splits);
+  p.norm_row_squares = static_cast<const float*>(norm_row_squares);
+  p.norm_hidden = static_cast<int>(norm_hidden);
+  p.norm_eps = static_cast<float>(norm_epsilon);
   const GridPlan grid_plan = plan_grid(splits, split_tokens, batch, head_blocks);
   if (grid_plan.splits > 1 && !grid_plan.cluster) {
     const int64_t need = workspace_bytes_for(batch, q_heads, head_dim, splits);

@@ -25,6 +25,7 @@
 // still frees its TMEM columns and returns. No cluster launch, no load shared between CTAs:
 // each CTA fetches its own tiles; with BN 128 at prefill sizes a second CTA resident on the SM
 // overlaps its main loop with this one's epilogue (2 x 96 KB of stages, 2 x 128 TMEM columns).
+#include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -40,6 +41,10 @@ constexpr int kBK = 64;
 constexpr int kThreads = 128;
 
 constexpr int kEpiloguePartial = 100;  // internal: fp32 split-K partials, no rounding
+// internal: the K slices of a tile are the CTAs of one thread-block cluster (cluster extent =
+// splits along grid z); they add their fp32 accumulators through distributed shared memory and
+// write r(r(x W^T) + residual) themselves: no partials in global memory, no reduce kernel
+constexpr int kEpilogueClusterResidual = 101;
 
 struct Tcgen05Params {
   const __nv_bfloat16* bias;
@@ -50,6 +55,15 @@ struct Tcgen05Params {
   int m, k, n, epilogue, splits;
   int bn;  // columns per tile: a multiple of 16, at most the kernel's BN
   int prefetch_weights;  // W tiles may be fetched before the predecessor kernel has finished
+  // RMSNorm folded into the projection (norm_input != nullptr): the A operand is the
+  // un-normalised x, the norm weight is already multiplied into W's columns, and the epilogue
+  // scales row r of the accumulator by rsqrt(mean(x_r^2) + eps) before bias / SwiGLU.
+  const __nv_bfloat16* norm_input = nullptr;
+  int64_t norm_row_stride = 0;
+  float norm_eps = 0.0f;
+  // Partial-sum producer only: the CTAs of the first N tile also leave sum(x_r^2) over their K
+  // slice in row_squares[split, m], for the consumer that applies the folded RMSNorm.
+  float* row_squares = nullptr;
 };
 
 // silu for the fused SwiGLU epilogue: x / (1 + 2^(-x log2 e)) on the special-function unit
@@ -182,8 +196,10 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   __shared__ __align__(8) uint64_t full_bar[STAGES];
   __shared__ __align__(8) uint64_t empty_bar[STAGES];
   __shared__ __align__(8) uint64_t accum_bar;
+  __shared__ __align__(8) uint64_t reduce_bar;  // cluster split-K: all slices of my units have landed
   __shared__ uint32_t tmem_base_slot;
   __shared__ int failed;
+  __shared__ float row_scale[kBM];  // folded RMSNorm: rsqrt(mean(x_r^2) + eps) per tile row
 
   TraceScope trace(1);
   grid_launch_dependents();
@@ -194,15 +210,20 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   const int kb_first = split * kb_per;
   const int nkb = max(0, min(kb_first + kb_per, kb_total) - kb_first);
   const uint32_t smem_base = smem_u32(smem);
+  // warps 2 and 3 square the rows of x as they pass through shared memory
+  const bool squares = A_ROWS == 64 && (p.norm_input != nullptr || (p.row_squares != nullptr && tile_n == 0));
 
   if (threadIdx.x == 0) {
     failed = 0;
 #pragma unroll
     for (int s = 0; s < STAGES; ++s) {
       mbarrier_init(smem_u32(&full_bar[s]), 1);
-      mbarrier_init(smem_u32(&empty_bar[s]), 1);
+      // a stage is free once the tensor core has read it and, with a folded RMSNorm, once
+      // warps 2 and 3 have squared its rows of x as well
+      mbarrier_init(smem_u32(&empty_bar[s]), squares ? 3 : 1);
     }
     mbarrier_init(smem_u32(&accum_bar), 1);
+    mbarrier_init(smem_u32(&reduce_bar), 1);
     fence_mbarrier_init();
   }
   if (warp == 1) {  // one warp allocates the accumulator columns and later frees them
@@ -215,6 +236,16 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
+  // Cluster split-K: the other CTAs of the cluster will signal reduce_bar; none may do so
+  // before it is initialised, hence one cluster barrier here, in the prologue that overlaps
+  // the predecessor kernel. Then this CTA announces the bytes it is going to receive.
+  const int reduce_owned = p.epilogue == kEpilogueClusterResidual
+      ? (A_ROWS * (bn / 4) + p.splits - 1) / p.splits : 0;  // 16-byte units this CTA sums
+  if (p.epilogue == kEpilogueClusterResidual) {
+    cluster_sync();
+    if (threadIdx.x == 0)
+      mbarrier_arrive_expect_tx(smem_u32(&reduce_bar), static_cast<uint32_t>(p.splits * reduce_owned * 16));
+  }
 
   if (warp == 0 && lane == 0) {
     // ---- TMA producer ----
@@ -254,6 +285,44 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
     // through mbarriers, and stay out of the way of the kernels still running on the SM.
     grid_dependency_wait();
   }
+  if (warp >= 2 && squares) {
+    // Folded RMSNorm (A_ROWS == 64): warps 2 and 3 have nothing else to do until the accumulator
+    // is complete. Every k-block's 64 x 64 box of x passes through shared memory for the tensor
+    // core anyway; thread t of the two warps squares row t of each box as it lands (128 bytes,
+    // eight 16-byte reads that start at chunk t & 7 so that a quarter-warp never shares a bank;
+    // the swizzle only permutes chunks within the row, which a sum does not care about; columns
+    // beyond K are zero-filled by the copy). One fixed summation order per row, no extra global
+    // traffic, and the row factors are ready when the last k-block is.
+    const int r = (warp - 2) * 32 + lane;
+    float ss = 0.0f;
+    bool fine = true;
+    for (int kb = 0; kb < nkb && fine; ++kb) {
+      const int s = kb % STAGES;
+      fine = __all_sync(0xffffffffu, mbarrier_wait_bounded(smem_u32(&full_bar[s]), (kb / STAGES) & 1));
+      if (fine && r < A_ROWS) {
+        const uint32_t row_addr = smem_base + s * kStageBytes + r * 128;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          uint4 raw;
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                       : "r"(row_addr + (((j + r) & 7) << 4)));
+          ss = fmaf(bf16_lo(raw.x), bf16_lo(raw.x), ss); ss = fmaf(bf16_hi(raw.x), bf16_hi(raw.x), ss);
+          ss = fmaf(bf16_lo(raw.y), bf16_lo(raw.y), ss); ss = fmaf(bf16_hi(raw.y), bf16_hi(raw.y), ss);
+          ss = fmaf(bf16_lo(raw.z), bf16_lo(raw.z), ss); ss = fmaf(bf16_hi(raw.z), bf16_hi(raw.z), ss);
+          ss = fmaf(bf16_lo(raw.w), bf16_lo(raw.w), ss); ss = fmaf(bf16_hi(raw.w), bf16_hi(raw.w), ss);
+        }
+      }
+      __syncwarp();
+      if (lane == 0)
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty_bar[s])) : "memory");
+    }
+    if (!fine) failed = 1;
+    if (p.norm_input != nullptr)
+      row_scale[r] = rsqrtf(ss / static_cast<float>(p.k) + p.norm_eps);
+    else if (r < p.m)
+      p.row_squares[static_cast<int64_t>(split) * p.m + r] = fine ? ss : 0.0f;
+  }
   if (warp == 1 && lane == 0) {
     // ---- MMA issuer ----
     for (int kb = 0; kb < nkb; ++kb) {
@@ -280,11 +349,109 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   bool ok = mbarrier_wait_bounded(smem_u32(&accum_bar), 0);
   trace.mark_middle();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  if (p.norm_input != nullptr) __syncthreads();  // the row scales of warps 2 and 3
   ok = ok && failed == 0;
-  if (ok) {
-    const int row = tile_m * kBM + warp * 32 + lane;
+  if (p.epilogue == kEpilogueClusterResidual) {
+    // ---- split-K over a thread-block cluster: reduce through distributed shared memory ----
+    // The tile's 4-column units (A_ROWS x bn / 4 of them) are dealt round-robin to the CTAs of
+    // the cluster (one per K slice): unit i belongs to CTA i % splits, as its local unit
+    // i / splits. Behind the stage ring every CTA has a send region [owner][local unit] and a
+    // receive region [slice][local unit] of 16-byte units. The CTA sorts its fp32 accumulator
+    // into the send region (plain shared-memory stores), then one thread per owner ships that
+    // owner's chunk with ONE bulk copy through distributed shared memory, which completes on
+    // the owner's reduce_bar. An owner that has received all slices adds them in slice order
+    // from its own shared memory, rounds, adds the residual, rounds and stores. The cluster
+    // barrier around the sums only keeps every CTA resident until the copies that read its
+    // send region have landed. A CTA whose waits gave up still ships (zeros) and arrives.
+    // (The code is kept small on purpose -- one division per thread, rolled loops: a kernel this
+    // short pays for every instruction-cache line it touches for the first time.)
+    const int rows = min(A_ROWS, p.m - tile_m * kBM);
+    const int unit_shift = 31 - __clz(bn / 4);  // bn is 32, 64 or 128 here: 8, 16 or 32 units a row
+    const int owned = reduce_owned;
+    const uint32_t chunk_bytes = static_cast<uint32_t>(owned * 16);
+    const int rank = cluster_cta_rank();
+    const int n_end = min(p.n, (tile_n + 1) * bn);
+    const uint32_t send_base = smem_base + STAGES * kStageBytes + 9216;
+    const uint32_t recv_base = send_base + p.splits * chunk_bytes;
+    if (warp * 32 < A_ROWS) {
+      const int r = warp * 32 + lane;
+      int owner = (r << unit_shift) % p.splits, local = (r << unit_shift) / p.splits;
 #pragma unroll 1
+      for (int c0 = 0; c0 < bn; c0 += 32) {
+        float v[32];
+        tmem_load_32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + c0, v);
+        if (!ok || nkb == 0) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {  // consecutive units go to consecutive owners
+          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(
+                           send_base + owner * chunk_bytes + local * 16),
+                       "f"(v[4 * u]), "f"(v[4 * u + 1]), "f"(v[4 * u + 2]), "f"(v[4 * u + 3]) : "memory");
+          if (++owner == p.splits) {
+            owner = 0;
+            ++local;
+          }
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the copies below read these stores
+    }
+    __syncthreads();
+    trace.stamp(2);
+    if (threadIdx.x < p.splits) {
+      const int owner = threadIdx.x;
+      uint32_t remote_dst, remote_bar;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                   : "=r"(remote_dst) : "r"(recv_base + rank * chunk_bytes), "r"(owner));
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                   : "=r"(remote_bar) : "r"(smem_u32(&reduce_bar)), "r"(owner));
+      asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(remote_dst), "r"(send_base + owner * chunk_bytes), "r"(chunk_bytes), "r"(remote_bar)
+                   : "memory");
+    }
+    // the residual of this thread's first unit travels while the slices do
+    const int first_item = threadIdx.x * p.splits + rank;
+    const int first_row = first_item >> unit_shift, first_col = tile_n * bn + (first_item & ((bn / 4) - 1)) * 4;
+    const bool first_valid = threadIdx.x < owned && first_row < rows && first_col < n_end;
+    const int64_t first_offset = static_cast<int64_t>(tile_m * kBM + first_row) * p.n + first_col;
+    uint2 res = first_valid ? *reinterpret_cast<const uint2*>(p.residual + first_offset) : make_uint2(0u, 0u);
+    const bool landed = mbarrier_wait_bounded(smem_u32(&reduce_bar), 0);
+    trace.stamp(4);
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+#pragma unroll 1
+    for (int local = threadIdx.x; local < owned && landed; local += kThreads) {
+      const int item = local * p.splits + rank;
+      const int r = item >> unit_shift, col = tile_n * bn + (item & ((bn / 4) - 1)) * 4;
+      if (r >= rows || col >= n_end) continue;
+      const int64_t o = static_cast<int64_t>(tile_m * kBM + r) * p.n + col;  // n % 4 == 0
+      if (local != threadIdx.x) res = *reinterpret_cast<const uint2*>(p.residual + o);
+      float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      float4 t[8];
+#pragma unroll
+      for (int s0 = 0; s0 < 8; ++s0) {
+        const uint32_t addr = recv_base + (s0 < p.splits ? s0 : 0) * chunk_bytes + local * 16;
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                     : "=f"(t[s0].x), "=f"(t[s0].y), "=f"(t[s0].z), "=f"(t[s0].w) : "r"(addr) : "memory");
+      }
+#pragma unroll
+      for (int s0 = 0; s0 < 8; ++s0)
+        if (s0 < p.splits) { acc.x += t[s0].x; acc.y += t[s0].y; acc.z += t[s0].z; acc.w += t[s0].w; }
+      round_bf16_pair(acc.x, acc.y);
+      round_bf16_pair(acc.z, acc.w);
+      acc.x = __fadd_rn(acc.x, bf16_lo(res.x)); acc.y = __fadd_rn(acc.y, bf16_hi(res.x));
+      acc.z = __fadd_rn(acc.z, bf16_lo(res.y)); acc.w = __fadd_rn(acc.w, bf16_hi(res.y));
+      *reinterpret_cast<uint2*>(p.out + o) = make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
+    }
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    ok = ok && __syncthreads_and(landed);
+    trace.stamp(6);
+    if (!ok && threadIdx.x == 0 && p.status != nullptr) atomicOr(p.status, B200_STATUS_WAIT_TIMEOUT);
+  } else if (ok) {
+    const int row = tile_m * kBM + warp * 32 + lane;
+    const float scale = p.norm_input != nullptr ? row_scale[(warp * 32 + lane) % kBM] : 1.0f;
     const int n_end = min(p.n, (tile_n + 1) * bn);  // columns of this tile
+#pragma unroll 1
     for (int c0 = 0; c0 < bn; c0 += 32) {
       const int col0 = tile_n * bn + c0;
       if (col0 >= n_end) break;  // warp-uniform: tcgen05.ld is a warp-wide instruction
@@ -294,6 +461,10 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
       if (nkb == 0) {  // a K slice without k blocks contributes zeros, not stale TMEM
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+      }
+      if (p.norm_input != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] *= scale;
       }
       if (p.epilogue == kEpiloguePartial) {
         float* dst = p.partials + (static_cast<int64_t>(split) * p.m + row) * p.n + col0;
@@ -556,30 +727,154 @@ int launch_persistent(const Tcgen05Params& p, const CUtensorMap& a_map, const CU
   return launch_status();
 }
 
+struct PartialPlan {
+  int bn, splits;
+};
+
+// Decode-size GEMMs with rings just deep enough for their K slice: the CTAs of the next kernel
+// of the chain then fit on the SM beside them and run their set-up (and first weight fetches)
+// early. B200_GEMM_RINGS=deep keeps the deep rings.
+bool small_rings() {
+  static const bool value = [] {
+    const char* text = getenv("B200_GEMM_RINGS");
+    return text == nullptr || strcmp(text, "deep") != 0;
+  }();
+  return value;
+}
+
 template <int BN, int STAGES, int A_ROWS>
 int launch(const Tcgen05Params& p, const CUtensorMap& a_map, const CUtensorMap& b_map,
            cudaStream_t stream) {
   // slack: the last stage's 64-row x box is followed by up to 8 KB that the 128-row MMA reads past
-  constexpr int smem = STAGES * (A_ROWS + BN) * 128 + 9216;
-  static_assert(smem <= 227 * 1024, "stage ring exceeds shared memory");
+  constexpr int ring = STAGES * (A_ROWS + BN) * 128 + 9216;
+  static_assert(ring <= 227 * 1024, "stage ring exceeds shared memory");
+  if (p.bn <= 0 || p.bn > BN || p.bn % 16 != 0) return B200_ERR_BAD_ARGUMENT;
+  // cluster split-K: behind the ring, room for every slice's copy of the units this CTA owns
+  int smem = ring;
+  if (p.epilogue == kEpilogueClusterResidual) {
+    const int owned = (A_ROWS * p.bn / 4 + p.splits - 1) / p.splits;
+    if (owned > 4 * kThreads) return B200_ERR_UNSUPPORTED;
+    smem += 2 * p.splits * owned * 16;  // a send and a receive region
+    if (smem > 227 * 1024) return B200_ERR_UNSUPPORTED;
+  }
   auto kernel = linear_tcgen05_kernel<BN, STAGES, A_ROWS>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return B200_ERR_LAUNCH;
-  if (p.bn <= 0 || p.bn > BN || p.bn % 16 != 0) return B200_ERR_BAD_ARGUMENT;
   dim3 grid(static_cast<unsigned>(ceil_div(p.n, p.bn)), static_cast<unsigned>(ceil_div(p.m, kBM)),
             static_cast<unsigned>(p.splits));
-  if (launch_chained(kernel, grid, dim3(kThreads), smem, stream, p, a_map, b_map) != cudaSuccess)
+  // the K slices of a tile are one thread-block cluster when they reduce among themselves
+  const unsigned cluster_z = p.epilogue == kEpilogueClusterResidual ? static_cast<unsigned>(p.splits) : 1u;
+  if (launch_chained_cluster_xz(kernel, grid, dim3(kThreads), smem, stream, 1u, cluster_z, p, a_map,
+                                b_map) != cudaSuccess)
     return B200_ERR_LAUNCH;
   return launch_status();
+}
+
+// How many clusters of `splits` CTAs of this kernel configuration the GPU holds at once (0 if the
+// configuration cannot run). A cluster needs all its CTAs on one GPC, so the answer is not
+// simply SMs / splits: 28 clusters of 5 one-CTA-per-SM blocks, for instance, do not fit.
+template <int BN, int STAGES, int A_ROWS>
+int resident_clusters(int bn, int splits) {
+  const int owned = (A_ROWS * bn / 4 + splits - 1) / splits;
+  const int smem = STAGES * (A_ROWS + BN) * 128 + 9216 + 2 * splits * owned * 16;
+  if (owned > 4 * kThreads || smem > 227 * 1024) return 0;
+  auto kernel = linear_tcgen05_kernel<BN, STAGES, A_ROWS>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(1, 1, static_cast<unsigned>(splits));
+  config.blockDim = dim3(kThreads);
+  config.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attribute;
+  attribute.id = cudaLaunchAttributeClusterDimension;
+  attribute.val.clusterDim.x = 1;
+  attribute.val.clusterDim.y = 1;
+  attribute.val.clusterDim.z = static_cast<unsigned>(splits);
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, kernel, &config) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return clusters;
+}
+
+// The kernel configuration the cluster split-K launcher uses for a tile width and slice length
+// (rings short enough to leave room for the send and receive regions of the reduction).
+enum class ClusterConfig { k32x3, k32x8, k64x4, k64x6, k128x4, k32x6r128, k64x4r128 };
+ClusterConfig cluster_config(int a_rows, int bn, int64_t slice_blocks) {
+  if (a_rows == 64) {
+    if (bn <= 32) return small_rings() && slice_blocks <= 4 ? ClusterConfig::k32x3 : ClusterConfig::k32x8;
+    if (bn <= 64) return small_rings() ? ClusterConfig::k64x4 : ClusterConfig::k64x6;
+    return ClusterConfig::k128x4;
+  }
+  return bn <= 32 ? ClusterConfig::k32x6r128 : ClusterConfig::k64x4r128;
+}
+int resident_clusters_of(ClusterConfig config, int bn, int splits) {
+  static int cache[7][129][9];  // 0 = not asked yet, else the answer + 1 (per device 0's shape)
+  int& slot = cache[static_cast<int>(config)][bn][splits];
+  if (slot == 0) {
+    int value = 0;
+    switch (config) {
+      case ClusterConfig::k32x3: value = resident_clusters<32, 3, 64>(bn, splits); break;
+      case ClusterConfig::k32x8: value = resident_clusters<32, 8, 64>(bn, splits); break;
+      case ClusterConfig::k64x4: value = resident_clusters<64, 4, 64>(bn, splits); break;
+      case ClusterConfig::k64x6: value = resident_clusters<64, 6, 64>(bn, splits); break;
+      case ClusterConfig::k128x4: value = resident_clusters<128, 4, 64>(bn, splits); break;
+      case ClusterConfig::k32x6r128: value = resident_clusters<32, 6, 128>(bn, splits); break;
+      case ClusterConfig::k64x4r128: value = resident_clusters<64, 4, 128>(bn, splits); break;
+    }
+    slot = value + 1;
+  }
+  return slot - 1;
+}
+
+// Plan of the cluster split-K projection (M <= 128): N tile width and K slices (= cluster size,
+// at most the portable 8) with about one CTA per SM. The cost of a candidate is what one CTA
+// streams (k-blocks of its slice x stage bytes) plus a per-slice charge for the reduction.
+PartialPlan plan_cluster(int64_t m, int64_t k, int64_t n) {
+  static const char* forced = getenv("B200_SPLITK_PLAN");  // "bn,splits": experiments only
+  if (forced != nullptr) {
+    int bn = 0, splits = 0;
+    if (sscanf(forced, "%d,%d", &bn, &splits) == 2 && (bn == 32 || bn == 64 || bn == 128) &&
+        splits >= 1 && splits <= 8)
+      return PartialPlan{bn, splits};
+  }
+  const int64_t kb = ceil_div(k, kBK);
+  PartialPlan best{64, 1};
+  double best_cost = 1e300;
+  const int64_t rows = m <= 64 ? 64 : 128;
+  for (int bn : {32, 64, 128}) {
+    if (rows * bn > 64 * 128) break;  // two copies of the fp32 tile must fit behind the ring
+    const int64_t tiles = ceil_div(n, bn);
+    for (int64_t splits = 1; splits <= 8 && splits <= kb; ++splits) {
+      if (tiles * splits > kNumSMs) break;
+      const int64_t per = ceil_div(kb, splits);
+      if (ceil_div(kb, per) != splits) continue;  // a slice would be empty
+      if (ceil_div(rows * bn / 4, splits) > 4 * kThreads) continue;  // units one CTA can own
+      // every cluster resident at once: a second wave would double the time
+      if (splits > 1 && resident_clusters_of(cluster_config(static_cast<int>(rows), bn, per), bn,
+                                             static_cast<int>(splits)) < tiles)
+        continue;
+      // a thread that owns a second unit pays a second residual round trip after the barrier
+      const int64_t rounds = ceil_div(ceil_div(rows * bn / 4, splits), kThreads);
+      const double cost = static_cast<double>(per) * (64 + bn) + 6.0 * splits + 300.0 * (rounds - 1) +
+                          (tiles * splits < 64 ? 1e6 : 0.0);  // far too few CTAs to stream at speed
+      if (cost < best_cost) {
+        best_cost = cost;
+        best = PartialPlan{bn, static_cast<int>(splits)};
+      }
+    }
+  }
+  return best;
 }
 
 // Split-K plan of the partial-sum producer: N tile width and K slices chosen to put about
 // one CTA on each of the 148 SMs at the least traffic (activation re-reads per N tile +
 // fp32 partials written and read back per K slice).
-struct PartialPlan {
-  int bn, splits;
-};
-
 PartialPlan plan_partial(int64_t m, int64_t k, int64_t n) {
   const int64_t kb = ceil_div(k, kBK);
   PartialPlan best{128, 1};
@@ -610,8 +905,10 @@ PartialPlan plan_partial(int64_t m, int64_t k, int64_t n) {
 // the GPU without split-K), in which case the caller uses the warp-level kernel.
 int linear_tcgen05(const void* input, const void* weight, const void* bias, const void* residual,
                    void* output, int64_t m, int64_t k, int64_t n, int64_t input_row_stride,
-                   int epilogue, int32_t* status, cudaStream_t stream) {
+                   int epilogue, int32_t* status, cudaStream_t stream, bool fold_norm,
+                   double norm_eps) {
   if (ceil_div(m, kBM) > 65535) return B200_ERR_UNSUPPORTED;
+  if (fold_norm && m > 64) return B200_ERR_UNSUPPORTED;  // the idle-warp scheme of the decode tiles
   int bn;
   bool persistent = false;
   if (m > 64) {
@@ -639,7 +936,8 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
     // Weight streaming with one deep-pipelined CTA per SM: the N tile is the width (a
     // multiple of 16, at most 256) whose tile count fills whole waves of 148 CTAs best;
     // fewer than ~120 tiles would leave SMs idle and is left to the split-K kernel.
-    if (ceil_div(n, 16) < kNumSMs - 28) return B200_ERR_UNSUPPORTED;
+    // (a folded-norm call has no other kernel to fall back to: it runs here whatever the fill)
+    if (!fold_norm && ceil_div(n, 16) < kNumSMs - 28) return B200_ERR_UNSUPPORTED;
     double best = -1.0;
     bn = 0;
     for (int candidate = 256; candidate >= 16; candidate -= 16) {
@@ -653,7 +951,7 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
         bn = candidate;
       }
     }
-    if (best < 0.8) return B200_ERR_UNSUPPORTED;
+    if (best < 0.8 && !fold_norm) return B200_ERR_UNSUPPORTED;
     // Many waves of tiles (an LM head): 192-column tiles with a 3-stage ring leave room for two
     // CTAs per SM, so one CTA's ramp and epilogue hide under the other's streaming; measured
     // 60.2 us against 71.2 - 78.3 us for one 208 ... 256-column CTA per SM at N = 151936.
@@ -676,10 +974,17 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
   p.splits = 1;
   p.bn = bn;
   p.prefetch_weights = (launch_mode() & B200_LAUNCH_CONSTANT_WEIGHTS) != 0 ? 1 : 0;
+  if (fold_norm) {
+    p.norm_input = static_cast<const __nv_bfloat16*>(input);
+    p.norm_row_stride = input_row_stride;
+    p.norm_eps = static_cast<float>(norm_eps);
+  }
   if (m <= 64) {
     if (bn == 192 && ceil_div(n, 192) >= 4 * kNumSMs) return launch<192, 3, 64>(p, a_map, b_map, stream);
     if (bn > 128) return launch<256, 5, 64>(p, a_map, b_map, stream);
-    if (bn > 64) return launch<128, 8, 64>(p, a_map, b_map, stream);
+    if (bn > 64)
+      return small_rings() && fold_norm ? launch<128, 4, 64>(p, a_map, b_map, stream)
+                                        : launch<128, 8, 64>(p, a_map, b_map, stream);
     return launch<64, 12, 64>(p, a_map, b_map, stream);
   }
   if (persistent) return launch_persistent(p, a_map, b_map, stream);
@@ -690,9 +995,11 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
 
 int linear_partial_splits(int64_t m, int64_t k, int64_t n) { return plan_partial(m, k, n).splits; }
 
-int linear_partial_tcgen05(const void* input, const void* weight, float* partials, int64_t m,
-                           int64_t k, int64_t n, int64_t input_row_stride, int splits,
-                           int32_t* status, cudaStream_t stream) {
+int linear_partial_tcgen05(const void* input, const void* weight, float* partials,
+                           float* row_squares, int64_t m, int64_t k, int64_t n,
+                           int64_t input_row_stride, int splits, int32_t* status,
+                           cudaStream_t stream) {
+  if (row_squares != nullptr && m > 64) return B200_ERR_UNSUPPORTED;
   const PartialPlan plan = plan_partial(m, k, n);
   const int a_rows = m <= 64 ? 64 : 128;
   CUtensorMap a_map, b_map;
@@ -710,13 +1017,16 @@ int linear_partial_tcgen05(const void* input, const void* weight, float* partial
   p.n = static_cast<int>(n);
   p.epilogue = kEpiloguePartial;
   p.splits = splits;
+  p.row_squares = row_squares;
   p.bn = plan.bn;
   p.prefetch_weights = (launch_mode() & B200_LAUNCH_CONSTANT_WEIGHTS) != 0 ? 1 : 0;
   if (a_rows == 64) {
     // A K slice of many k-blocks is a long weight stream: it wants about 2 us x 44 GB/s of
     // loads in flight per SM, twice what the 96 KB rings of the short slices hold.
     const bool long_slice = ceil_div(ceil_div(k, kBK), splits) >= 24;
-    if (plan.bn == 32) return launch<32, 8, 64>(p, a_map, b_map, stream);
+    if (plan.bn == 32)
+      return small_rings() && ceil_div(ceil_div(k, kBK), splits) <= 4 ? launch<32, 4, 64>(p, a_map, b_map, stream)
+                                                                      : launch<32, 8, 64>(p, a_map, b_map, stream);
     if (plan.bn == 64)
       return long_slice ? launch<64, 12, 64>(p, a_map, b_map, stream) : launch<64, 6, 64>(p, a_map, b_map, stream);
     return long_slice ? launch<128, 8, 64>(p, a_map, b_map, stream) : launch<128, 4, 64>(p, a_map, b_map, stream);
@@ -726,9 +1036,75 @@ int linear_partial_tcgen05(const void* input, const void* weight, float* partial
   return launch<128, 3, 128>(p, a_map, b_map, stream);
 }
 
+int linear_splitk_residual_tcgen05(const void* input, const void* weight, const void* residual,
+                                   void* output, int64_t m, int64_t k, int64_t n,
+                                   int64_t input_row_stride, int32_t* status, cudaStream_t stream) {
+  const PartialPlan plan = plan_cluster(m, k, n);
+  const int a_rows = m <= 64 ? 64 : 128;
+  CUtensorMap a_map, b_map;
+  if (!make_bf16_matrix_map(&a_map, input, m, k, input_row_stride, a_rows) ||
+      !make_bf16_matrix_map(&b_map, weight, n, k, k, plan.bn))
+    return B200_ERR_UNSUPPORTED;
+  Tcgen05Params p;
+  p.bias = nullptr;
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.out = static_cast<__nv_bfloat16*>(output);
+  p.partials = nullptr;
+  p.status = status;
+  p.m = static_cast<int>(m);
+  p.k = static_cast<int>(k);
+  p.n = static_cast<int>(n);
+  p.epilogue = kEpilogueClusterResidual;
+  p.splits = plan.splits;
+  p.bn = plan.bn;
+  p.prefetch_weights = (launch_mode() & B200_LAUNCH_CONSTANT_WEIGHTS) != 0 ? 1 : 0;
+  // (rings short enough to leave room for the send and receive regions of the reduction)
+  switch (cluster_config(a_rows, plan.bn, ceil_div(ceil_div(k, kBK), plan.splits))) {
+    case ClusterConfig::k32x3: return launch<32, 3, 64>(p, a_map, b_map, stream);
+    case ClusterConfig::k32x8: return launch<32, 8, 64>(p, a_map, b_map, stream);
+    case ClusterConfig::k64x4: return launch<64, 4, 64>(p, a_map, b_map, stream);
+    case ClusterConfig::k64x6: return launch<64, 6, 64>(p, a_map, b_map, stream);
+    case ClusterConfig::k128x4: return launch<128, 4, 64>(p, a_map, b_map, stream);
+    case ClusterConfig::k32x6r128: return launch<32, 6, 128>(p, a_map, b_map, stream);
+    case ClusterConfig::k64x4r128: return launch<64, 4, 128>(p, a_map, b_map, stream);
+  }
+  return B200_ERR_UNSUPPORTED;
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_linear_splitk_residual(const void* input, const void* weight,
+                                           const void* residual, void* output, int64_t m,
+                                           int64_t k, int64_t n, int64_t input_row_stride,
+                                           int32_t* status, void* stream) {
+  if (!input || !weight || !residual || !output || m <= 0 || k <= 0 || n <= 0 ||
+      input_row_stride < k)
+    return B200_ERR_BAD_ARGUMENT;
+  if (m > 128) return B200_ERR_TOO_LARGE;
+  if (k % 8 != 0 || input_row_stride % 8 != 0 || n % 4 != 0) return B200_ERR_UNSUPPORTED;
+  if (!aligned16(input) || !aligned16(weight) || !aligned16(residual) || !aligned16(output))
+    return B200_ERR_ALIGNMENT;
+  return linear_splitk_residual_tcgen05(input, weight, residual, output, m, k, n, input_row_stride,
+                                        status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200_linear_rms_input(const void* input, const void* folded_weight, const void* bias,
+                                     void* output, int64_t m, int64_t k, int64_t n,
+                                     int64_t input_row_stride, double epsilon, int epilogue,
+                                     int32_t* status, void* stream) {
+  if (!input || !folded_weight || !output || m <= 0 || k <= 0 || n <= 0 || input_row_stride < k ||
+      !(epsilon >= 0.0))
+    return B200_ERR_BAD_ARGUMENT;
+  if (epilogue != B200_EPILOGUE_NONE && epilogue != B200_EPILOGUE_SWIGLU) return B200_ERR_BAD_ARGUMENT;
+  if (epilogue == B200_EPILOGUE_SWIGLU && n % 2 != 0) return B200_ERR_BAD_ARGUMENT;
+  if (m > 64) return B200_ERR_TOO_LARGE;
+  if (k % 8 != 0 || input_row_stride % 8 != 0) return B200_ERR_UNSUPPORTED;
+  if (!aligned16(input) || !aligned16(folded_weight)) return B200_ERR_ALIGNMENT;
+  return linear_tcgen05(input, folded_weight, bias, nullptr, output, m, k, n, input_row_stride,
+                        epilogue, status, static_cast<cudaStream_t>(stream), true, epsilon);
+}
 
 extern "C" int64_t b200_linear_partial_splits(int64_t m, int64_t k, int64_t n) {
   if (m <= 0 || k <= 0 || n <= 0) return 0;
@@ -736,15 +1112,17 @@ extern "C" int64_t b200_linear_partial_splits(int64_t m, int64_t k, int64_t n) {
 }
 
 extern "C" int b200_linear_partial(const void* input, const void* weight, void* partials,
-                                   int64_t m, int64_t k, int64_t n, int64_t input_row_stride,
-                                   int64_t splits, int32_t* status, void* stream) {
+                                   void* row_squares, int64_t m, int64_t k, int64_t n,
+                                   int64_t input_row_stride, int64_t splits, int32_t* status,
+                                   void* stream) {
   if (!input || !weight || !partials || m <= 0 || k <= 0 || n <= 0 || input_row_stride < k ||
       splits <= 0)
     return B200_ERR_BAD_ARGUMENT;
   if (m > 128 || splits > ceil_div(k, kBK) || splits > 65535) return B200_ERR_TOO_LARGE;
   if (k % 8 != 0 || input_row_stride % 8 != 0 || n % 4 != 0) return B200_ERR_UNSUPPORTED;
   if (!aligned16(input) || !aligned16(weight) || !aligned16(partials)) return B200_ERR_ALIGNMENT;
-  return linear_partial_tcgen05(input, weight, static_cast<float*>(partials), m, k, n,
-                                input_row_stride, static_cast<int>(splits), status,
-                                static_cast<cudaStream_t>(stream));
+  if (row_squares != nullptr && m > 64) return B200_ERR_TOO_LARGE;
+  return linear_partial_tcgen05(input, weight, static_cast<float*>(partials),
+                                static_cast<float*>(row_squares), m, k, n, input_row_stride,
+                                static_cast<int>(splits), status, static_cast<cudaStream_t>(stream));
 }

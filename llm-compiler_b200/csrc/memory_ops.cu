@@ -424,6 +424,17 @@ __global__ void advance_lengths_kernel(int64_t* lengths, int64_t count, int64_t 
 // below the diagonal and -inf above it (the mask make_qwen2_prefill_inputs builds,
 // qwen2.py:552-572). Grid-stride over B * T * T entries; a CTA that finds a violation clears
 // the flag once. The caller sets flag[0] = 1 before the launch (b200_classify_causal_mask does).
+// ------------------------------------------------------------ weight preparation ----
+// out[r, c] = round(weight[r, c] * scale[c]): a norm weight folded into the columns of the
+// projection that follows the norm. One-time, at load.
+template <typename T>
+__global__ void scale_columns_kernel(const T* __restrict__ weight, const T* __restrict__ scale,
+                                     T* __restrict__ out, int64_t total, int64_t columns) {
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    Elem<T>::store(out + idx, Elem<T>::load(weight + idx) * Elem<T>::load(scale + idx % columns));
+}
+
 __global__ void set_flag_kernel(int32_t* flag) { *flag = 1; }
 
 template <typename T>
@@ -771,6 +782,25 @@ int b200_advance_lengths(int64_t* lengths, int64_t slots, int64_t batch, int64_t
   advance_lengths_kernel<<<static_cast<int>(ceil_div(count, kThreads)), kThreads, 0,
                            static_cast<cudaStream_t>(stream)>>>(lengths, count, delta, capacity,
                                                                 status);
+  return launch_status();
+}
+
+int b200_scale_columns(const void* weight, const void* scale, void* output, int64_t rows,
+                       int64_t columns, int dtype, void* stream) {
+  if (!weight || !scale || !output || rows < 0 || columns <= 0) return B200_ERR_BAD_ARGUMENT;
+  if (rows == 0) return B200_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int64_t total = rows * columns;
+  if (dtype == B200_BF16)
+    scale_columns_kernel<__nv_bfloat16><<<grid_for(total), kThreads, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(weight), static_cast<const __nv_bfloat16*>(scale),
+        static_cast<__nv_bfloat16*>(output), total, columns);
+  else if (dtype == B200_F32)
+    scale_columns_kernel<float><<<grid_for(total), kThreads, 0, s>>>(
+        static_cast<const float*>(weight), static_cast<const float*>(scale),
+        static_cast<float*>(output), total, columns);
+  else
+    return B200_ERR_UNSUPPORTED;
   return launch_status();
 }
 

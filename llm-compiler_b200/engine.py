@@ -46,6 +46,12 @@ class Qwen2Engine:
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.dtype = weights["embed_tokens.weight"].dtype
         self.scale = config.head_dim ** -0.5
+        # the five-launch decode layer (RMSNorm folded into q|k|v and gate|up, cluster split-K
+        # o / down with the residual inside): bf16, fast mode, at most 64 rows
+        # (B200_DECODE_CHAIN=partials keeps the seven-launch chain with reduce consumers)
+        self.folded_norms = (self.dtype == torch.bfloat16 and numerical_mode == "fast" and
+                             batch <= 64 and config.hidden_size % 8 == 0 and
+                             os.environ.get("B200_DECODE_CHAIN", "folded") != "partials")
         self._pack_weights(weights)
         self.inv_freq = inverse_frequency(config, self.device)
 
@@ -93,14 +99,19 @@ class Qwen2Engine:
                                weights[p + "self_attn.v_proj.bias"]], dim=0).contiguous()
             gate_up = kernels.interleave_gate_up(weights[p + "mlp.gate_proj.weight"],
                                                  weights[p + "mlp.up_proj.weight"])
-            self.layers.append({
+            layer = {
                 "input_norm": weights[p + "input_layernorm.weight"],
                 "post_norm": weights[p + "post_attention_layernorm.weight"],
                 "qkv_w": qkv_w, "qkv_b": qkv_b,
                 "o_w": weights[p + "self_attn.o_proj.weight"],
                 "gate_up_w": gate_up,
                 "down_w": weights[p + "mlp.down_proj.weight"],
-            })
+            }
+            if self.folded_norms:
+                # the norm weights multiplied into the columns of the projections behind them
+                layer["qkv_w_folded"] = kernels.b200_scale_columns(qkv_w, layer["input_norm"])
+                layer["gate_up_w_folded"] = kernels.b200_scale_columns(gate_up, layer["post_norm"])
+            self.layers.append(layer)
 
     # ------------------------------------------------------------------ prefill ----
     def prefill(self, input_ids: torch.Tensor, *, all_logits: bool = False) -> torch.Tensor:
@@ -189,7 +200,42 @@ class Qwen2Engine:
                                  stable_kv_prefix=self.programmatic_launch):
             self._chain_launches()
 
+    def _folded_chain_launches(self) -> None:
+        """Five launches per layer: q|k|v partials of the un-normalised x against the
+        norm-folded weight -> attention (reduces q|k|v, applies the row's RMS factor, bias, RoPE,
+        KV store) -> o projection (cluster split-K, + residual) -> gate|up + SwiGLU on the
+        un-normalised x with the folded weight -> down projection (cluster split-K, + residual)."""
+
+        cfg = self.config
+        batch = self.batch
+        eps = cfg.rms_norm_eps
+        before = kernels.launch_count(self.device)
+        x = kernels.b200_embedding(self.embed, self.input_ids)
+        cosine, sine = kernels.b200_rope_table(self.positions.view(batch, 1), self.inv_freq,
+                                               self.dtype)
+        for index, layer in enumerate(self.layers):
+            partials, squares = kernels.b200_linear_partial(x, layer["qkv_w_folded"],
+                                                            row_squares=True)
+            attn = kernels.b200_qkv_decode_attention(
+                partials, layer["qkv_b"], cosine, sine, self.state.keys[index],
+                self.state.values[index], self.attention_lengths, q_heads=cfg.num_heads,
+                scale=self.scale, split_tokens=self.split_tokens,
+                max_length_hint=self.max_length_hint, norm_row_squares=squares,
+                norm_hidden=cfg.hidden_size, norm_epsilon=eps)
+            x = kernels.b200_linear_splitk_residual(attn.view(batch, cfg.q_size), layer["o_w"], x)
+            a = kernels.b200_linear_rms_input(x, layer["gate_up_w_folded"], epsilon=eps,
+                                              epilogue="swiglu")
+            x = kernels.b200_linear_splitk_residual(a, layer["down_w"], x)
+        h = kernels.b200_rms_norm(x, self.final_norm, epsilon=eps, round_before_weight=True,
+                                  numerical_mode=self.mode)
+        self.logits = kernels.b200_linear(h, self.lm_head)
+        kernels.b200_argmax(self.logits, self.next_ids)
+        kernels.b200_advance_lengths(self.state._length_arena, 1, self.capacity + 1)
+        self.kernels_per_step = kernels.launch_count(self.device) - before
+
     def _chain_launches(self) -> None:
+        if self.folded_norms:
+            return self._folded_chain_launches()
         cfg = self.config
         batch = self.batch
         before = kernels.launch_count(self.device)

@@ -772,9 +772,11 @@ def linear_partial_splits(m: int, k: int, n: int) -> int:
 
 
 def b200_linear_partial(tensor: torch.Tensor, weight: torch.Tensor,
-                        partials: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        partials: Optional[torch.Tensor] = None, *, row_squares: bool = False):
     """Decode-size projection without its epilogue: fp32 partial sums [splits, M, N] over K
-    slices, to be reduced by the operator that follows (b200_reduce_*). M <= 128, bf16."""
+    slices, to be reduced by the operator that follows (b200_reduce_*). M <= 128, bf16.
+    row_squares=True (M <= 64) also returns fp32 [splits, M]: the sum of squares of every input
+    row over each K slice, for a consumer that applies an RMSNorm folded into this projection."""
 
     device = _require_cuda(tensor, weight, partials)
     if weight.ndim != 2 or tensor.ndim != 2 or tensor.shape[1] != weight.shape[1]:
@@ -792,13 +794,14 @@ def b200_linear_partial(tensor: torch.Tensor, weight: torch.Tensor,
     elif partials.shape != (splits, m, n) or partials.dtype != torch.float32 or \
             not partials.is_contiguous():
         raise ValueError(f"partials must be a contiguous fp32 tensor of shape {(splits, m, n)}")
+    squares = torch.empty((splits, m), dtype=torch.float32, device=device) if row_squares else None
     rt = runtime(device)
     code = library.b200_linear_partial(tensor.data_ptr(), weight.data_ptr(), partials.data_ptr(),
-                                       m, k, n, tensor.stride(0), splits, rt.status.data_ptr(),
-                                       _stream())
+                                       _ptr(squares), m, k, n, tensor.stride(0), splits,
+                                       rt.status.data_ptr(), _stream())
     _check(code, "b200_linear_partial")
     _count(rt)
-    return partials
+    return (partials, squares) if row_squares else partials
 
 
 def b200_reduce_residual_rms_norm(partials: torch.Tensor, residual: Optional[torch.Tensor],
@@ -854,14 +857,23 @@ def b200_reduce_rope_kv_store(partials: torch.Tensor, bias: Optional[torch.Tenso
 def b200_qkv_decode_attention(partials: torch.Tensor, bias: Optional[torch.Tensor],
                               cosine: torch.Tensor, sine: torch.Tensor, key_buffer: torch.Tensor,
                               value_buffer: torch.Tensor, lengths: torch.Tensor, *, q_heads: int,
-                              scale: float, split_tokens: int = 0,
-                              max_length_hint: int = 0) -> torch.Tensor:
+                              scale: float, split_tokens: int = 0, max_length_hint: int = 0,
+                              norm_row_squares: Optional[torch.Tensor] = None,
+                              norm_hidden: int = 0, norm_epsilon: float = 0.0) -> torch.Tensor:
     """b200_reduce_rope_kv_store + b200_decode_attention of a decode step in one launch: the
     q|k|v partials are reduced (+ bias, RoPE) inside the attention kernel, the new token's K / V
     row is stored at row lengths[b] - 1 and attends from registers. lengths are the attention
-    lengths (the new token counted). Returns B x Hq x 1 x D."""
+    lengths (the new token counted). norm_row_squares (what b200_linear_partial(...,
+    row_squares=True) returned) with norm_hidden and norm_epsilon: the RMSNorm in front of the
+    projection was folded into it, and the reduced sums are scaled by rsqrt(mean(x^2) +
+    norm_epsilon) here. Returns B x Hq x 1 x D."""
 
-    device = _require_cuda(partials, bias, cosine, sine, key_buffer, value_buffer, lengths)
+    device = _require_cuda(partials, bias, cosine, sine, key_buffer, value_buffer, lengths,
+                           norm_row_squares)
+    if norm_row_squares is not None and (
+            norm_row_squares.shape != partials.shape[:2] or norm_row_squares.dtype != torch.float32
+            or not norm_row_squares.is_contiguous() or norm_hidden <= 0):
+        raise ValueError("norm_row_squares must be contiguous fp32 [splits, B] with norm_hidden > 0")
     splits, batch, width = partials.shape
     _, capacity, kv_heads, dim = key_buffer.shape
     if partials.dtype != torch.float32 or key_buffer.dtype != torch.bfloat16:
@@ -885,8 +897,88 @@ def b200_qkv_decode_attention(partials: torch.Tensor, bias: Optional[torch.Tenso
         partials.data_ptr(), splits, _ptr(bias), cos2.data_ptr(), sin2.data_ptr(),
         key_buffer.data_ptr(), value_buffer.data_ptr(), lengths.data_ptr(), output.data_ptr(),
         batch, q_heads, kv_heads, dim, capacity, capacity, float(scale), int(split_tokens),
-        int(max_length_hint), _ptr(workspace), need, rt.status.data_ptr(), _stream())
+        int(max_length_hint), _ptr(norm_row_squares), int(norm_hidden), float(norm_epsilon),
+        _ptr(workspace),
+        need, rt.status.data_ptr(), _stream())
     _check(code, "b200_qkv_decode_attention")
+    _count(rt)
+    return output
+
+
+def b200_scale_columns(weight: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """Weight preparation: weight[n, k] * scale[k], rounded to the weight dtype -- a norm
+    weight folded into the projection that follows the norm. A one-time device pass."""
+
+    device = _require_cuda(weight, scale)
+    if weight.ndim != 2 or scale.shape != (weight.shape[1],) or scale.dtype != weight.dtype:
+        raise ValueError("scale must be a vector of the weight's K in the weight's dtype")
+    weight, scale = _dense(weight), _dense(scale)
+    output = torch.empty_like(weight)
+    rt = runtime(device)
+    code = _lib.load().b200_scale_columns(weight.data_ptr(), scale.data_ptr(), output.data_ptr(),
+                                          weight.shape[0], weight.shape[1], _code(weight.dtype),
+                                          _stream())
+    _check(code, "b200_scale_columns")
+    _count(rt)
+    return output
+
+
+def b200_linear_rms_input(tensor: torch.Tensor, folded_weight: torch.Tensor,
+                          bias: Optional[torch.Tensor] = None, *, epsilon: float,
+                          epilogue: str = "none") -> torch.Tensor:
+    """serve.rms_norm + serve.linear in one launch (fast mode, bf16, at most 64 rows): `tensor`
+    is the un-normalised input, `folded_weight` the projection weight with the norm weight
+    multiplied into its columns (b200_scale_columns); the kernel scales each accumulator row by
+    rsqrt(mean(x^2) + epsilon) before the bias / SwiGLU epilogue."""
+
+    device = _require_cuda(tensor, folded_weight, bias)
+    if tensor.ndim != 2 or folded_weight.ndim != 2 or tensor.shape[1] != folded_weight.shape[1]:
+        raise ValueError("input must be M x K and weight N x K")
+    if tensor.dtype != torch.bfloat16 or folded_weight.dtype != torch.bfloat16:
+        raise ValueError("the folded-norm projection runs bf16")
+    if tensor.stride(1) != 1 or not folded_weight.is_contiguous():
+        raise ValueError("input rows and the weight must be contiguous")
+    if epilogue not in ("none", "swiglu"):
+        raise ValueError(f"unsupported epilogue {epilogue!r}")
+    m, k = tensor.shape
+    n = folded_weight.shape[0]
+    if bias is not None and (bias.shape != (n,) or bias.dtype != torch.bfloat16):
+        raise ValueError("bias must be a bf16 vector of N elements")
+    output = torch.empty((m, n // 2 if epilogue == "swiglu" else n), dtype=torch.bfloat16,
+                         device=device)
+    rt = runtime(device)
+    code = _lib.load().b200_linear_rms_input(
+        tensor.data_ptr(), folded_weight.data_ptr(), _ptr(bias), output.data_ptr(), m, k, n,
+        tensor.stride(0), float(epsilon), _EPILOGUES[epilogue], rt.status.data_ptr(), _stream())
+    _check(code, "b200_linear_rms_input")
+    _count(rt)
+    return output
+
+
+def b200_linear_splitk_residual(tensor: torch.Tensor, weight: torch.Tensor,
+                                residual: torch.Tensor) -> torch.Tensor:
+    """serve.linear + aten.add in one launch at decode sizes (bf16, at most 128 rows):
+    r(r(x W^T) + residual). The K slices of an output tile are the CTAs of one thread-block
+    cluster and add their fp32 accumulators through distributed shared memory."""
+
+    device = _require_cuda(tensor, weight, residual)
+    if tensor.ndim != 2 or weight.ndim != 2 or tensor.shape[1] != weight.shape[1]:
+        raise ValueError("input must be M x K and weight N x K")
+    if tensor.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or \
+            residual.dtype != torch.bfloat16:
+        raise ValueError("the split-K projection runs bf16")
+    m, k = tensor.shape
+    n = weight.shape[0]
+    if residual.shape != (m, n) or not residual.is_contiguous():
+        raise ValueError("residual must be a contiguous M x N tensor")
+    if tensor.stride(1) != 1 or not weight.is_contiguous():
+        raise ValueError("input rows and the weight must be contiguous")
+    output = torch.empty((m, n), dtype=torch.bfloat16, device=device)
+    rt = runtime(device)
+    code = _lib.load().b200_linear_splitk_residual(
+        tensor.data_ptr(), weight.data_ptr(), residual.data_ptr(), output.data_ptr(), m, k, n,
+        tensor.stride(0), rt.status.data_ptr(), _stream())
+    _check(code, "b200_linear_splitk_residual")
     _count(rt)
     return output
 

@@ -747,3 +747,105 @@ def test_wrappers_reject_cpu_tensors_and_bad_shapes():
     with pytest.raises(ValueError):  # 4 query heads over 3 KV heads
         b200.b200_decode_attention(q, kv, kv, torch.zeros(2, dtype=torch.int64, device="cuda"),
                                    None, scale=1.0)
+
+
+# ------------------------------------------ five-launch decode layer: its three kernels ----
+@pytest.mark.parametrize("m,k,n", [(64, 896, 896), (64, 4864, 896), (3, 256, 256), (1, 512, 256),
+                                   (33, 3584, 3584), (128, 896, 896), (100, 4864, 896),
+                                   (64, 18944, 3584), (7, 960, 1092)])
+def test_linear_splitk_residual_matches_linear_then_add(m, k, n):
+    """serve.linear + aten.add in one launch: the K slices of a tile are the CTAs of a
+    thread-block cluster that add their accumulators through distributed shared memory.
+    Against the oracle's r(r(x W^T) + residual); repeated calls are bit-identical (the slices
+    are added in a fixed order)."""
+    g = torch.Generator().manual_seed(m + k + n)
+    x = torch.randn(m, k, generator=g).bfloat16()
+    w = (torch.randn(n, k, generator=g) * k ** -0.5).bfloat16()
+    residual = torch.randn(m, n, generator=g).bfloat16()
+    ref = serve_ops.residual_add(residual, serve_ops.linear(x, w))
+    out = kernels.b200_linear_splitk_residual(x.cuda(), w.cuda(), residual.cuda())
+    close(out, ref, BF16_TOL)
+    again = kernels.b200_linear_splitk_residual(x.cuda(), w.cuda(), residual.cuda())
+    assert torch.equal(out, again)
+    # a strided input (rows of a wider matrix), as the attention output is handed over
+    wide = torch.randn(m, k + 64, generator=g).bfloat16().cuda()
+    view = wide[:, :k]
+    ref = serve_ops.residual_add(residual, serve_ops.linear(view.cpu(), w))
+    close(kernels.b200_linear_splitk_residual(view, w.cuda(), residual.cuda()), ref, BF16_TOL)
+    kernels.runtime().check_status()
+
+
+def test_scale_columns_is_the_rounded_product():
+    g = torch.Generator().manual_seed(4)
+    w = torch.randn(333, 896, generator=g).bfloat16()
+    s = torch.randn(896, generator=g).bfloat16()
+    exact(kernels.b200_scale_columns(w.cuda(), s.cuda()), (w.float() * s.float()).bfloat16())
+    wf, sf = torch.randn(7, 40, generator=g), torch.randn(40, generator=g)
+    exact(kernels.b200_scale_columns(wf.cuda(), sf.cuda()), wf * sf)
+
+
+@pytest.mark.parametrize("epilogue", ["none", "swiglu"])
+@pytest.mark.parametrize("m,k,n", [(64, 896, 9728), (4, 3584, 37888), (3, 256, 1024), (17, 896, 1152),
+                                   (64, 896, 2304)])
+def test_linear_rms_input_matches_rms_norm_then_linear(m, k, n, epilogue):
+    """serve.rms_norm folded into the projection behind it: un-normalised rows in, the norm
+    weight pre-multiplied into the weight's columns, the row factor applied to the accumulator.
+    Against the oracle's rms_norm (Qwen2 rounding order) -> linear (-> SwiGLU)."""
+    g = torch.Generator().manual_seed(m + k + n)
+    x = (torch.randn(m, k, generator=g) * 3.0).bfloat16()
+    norm_w = (1.0 + 0.2 * torch.randn(k, generator=g)).bfloat16()
+    w = (torch.randn(n, k, generator=g) * k ** -0.5).bfloat16()
+    bias = torch.randn(n, generator=g).bfloat16() if epilogue == "none" else None
+    h = serve_ops.rms_norm(x, norm_w, 1e-6, round_before_weight=True)
+    y = serve_ops.linear(h, w, bias)
+    folded = kernels.b200_scale_columns(w.cuda(), norm_w.cuda())
+    if epilogue == "swiglu":
+        ref = serve_ops.swiglu(y[:, 0::2], y[:, 1::2])  # rows of w alternate gate_j, up_j
+    else:
+        ref = y
+    out = kernels.b200_linear_rms_input(x.cuda(), folded, None if bias is None else bias.cuda(),
+                                        epsilon=1e-6, epilogue=epilogue)
+    close(out, ref, BF16_TOL)
+    kernels.runtime().check_status()
+
+
+def test_fused_attention_applies_the_folded_norm():
+    """b200_qkv_decode_attention with norm_input: the q|k|v partials come from un-normalised
+    rows and a norm-folded weight; the result and the stored K / V rows must match the oracle's
+    rms_norm -> projection -> rope -> store -> attention."""
+    g = torch.Generator().manual_seed(77)
+    hq, hkv, d, hidden, capacity = 14, 2, 64, 896, 200
+    lengths = torch.tensor([1, 64, 65, 200, 131])
+    b = lengths.numel()
+    width = (hq + 2 * hkv) * d
+    x = (torch.randn(b, hidden, generator=g) * 2.0).bfloat16()
+    norm_w = (1.0 + 0.2 * torch.randn(hidden, generator=g)).bfloat16()
+    w = (torch.randn(width, hidden, generator=g) * 0.05).bfloat16()
+    bias = torch.randn(width, generator=g).bfloat16()
+    positions = lengths - 1
+    cos, sin = serve_ops.rope_table(positions.view(b, 1), serve_ops.rope_inverse_frequency(d, 1e6),
+                                    torch.bfloat16)
+    kbuf = torch.randn(b, capacity, hkv, d, generator=g).bfloat16()
+    vbuf = torch.randn(b, capacity, hkv, d, generator=g).bfloat16()
+    qkv = serve_ops.linear(serve_ops.rms_norm(x, norm_w, 1e-6, round_before_weight=True), w, bias)
+    q = qkv[:, : hq * d].view(b, 1, hq, d).transpose(1, 2)
+    k = qkv[:, hq * d: (hq + hkv) * d].view(b, 1, hkv, d).transpose(1, 2)
+    v = qkv[:, (hq + hkv) * d:].view(b, 1, hkv, d).transpose(1, 2)
+    q_ref, k_ref = serve_ops.rope(q, k, cos, sin)
+    k_gold, v_gold = kbuf.clone(), vbuf.clone()
+    serve_ops.kv_store(k_gold, v_gold, k_ref, v, positions)
+    ref = serve_ops.decode_attention(q_ref, k_gold, v_gold, lengths, torch.zeros(b, 1, 1, capacity),
+                                     groups=hq // hkv, scale=d ** -0.5)
+    folded = kernels.b200_scale_columns(w.cuda(), norm_w.cuda())
+    x_dev = x.cuda()
+    partials, squares = kernels.b200_linear_partial(x_dev, folded, row_squares=True)
+    torch.testing.assert_close(squares.sum(0).cpu(), x.float().pow(2).sum(-1), rtol=1e-5, atol=0)
+    k_dev, v_dev = kbuf.cuda(), vbuf.cuda()
+    out = kernels.b200_qkv_decode_attention(partials, bias.cuda(), cos.cuda(), sin.cuda(), k_dev, v_dev,
+                                            lengths.cuda(), q_heads=hq, scale=d ** -0.5,
+                                            norm_row_squares=squares, norm_hidden=hidden,
+                                            norm_epsilon=1e-6)
+    close(out, ref, BF16_TOL)
+    close(k_dev, k_gold, BF16_TOL)
+    close(v_dev, v_gold, BF16_TOL)
+    kernels.runtime().check_status()
