@@ -22,6 +22,17 @@ Printed JSON (rank 0, one line):
   cpu_baseline  the CPU oracle (a port of the reference's ReferenceExecutor arithmetic) on the
              host cores, on a bounded sample of the same workload
 `--impl reference` times only that CPU path and prints it as its own line.
+
+The timed region of K steps is repeated (contexts reset between repeats, outside the timing)
+until about a second of device time has been measured; `value` and `ms_per_step` are the median
+repeat, `ms_per_step_min` / `ms_per_step_max` the spread. Before timing, the logits of one
+decode step for two sequences are compared with the CPU oracle on the same KV rows (`parity`).
+
+`--model qwen2-7b` runs the serving configuration instead: Qwen2-7B architecture, a GLOBAL batch
+of 512 sequences with contexts uniform in [1024, 8192] (seeded), KV pre-filled with N(0, 1),
+sequences dealt to the ranks by context length (serving.balanced_assignment) so that every GPU
+streams about the same KV bytes; strong scaling. One GPU cannot hold 512 contiguous KV slots
+(242 GB): at N = 1 the batch is served as two sub-batches of 256, one after the other.
 """
 
 from __future__ import annotations
@@ -47,9 +58,11 @@ UNIT = "tokens/s"
 FALLBACK_HBM_GBS = 6650.0
 RESULT_STREAM = sys.stdout  # main() replaces it with a private copy of the process's stdout
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch over 64 x 4096 =
-# 262144 tokens, from the ncu capture summarised in profiles/decode_attention_b64_l4096_ncu_full.md;
-# scaled to the bench launch by the tokens it processes (traffic is proportional to the tokens read)
-NCU_TRAFFIC_BYTES, NCU_TRAFFIC_TOKENS = 138_843_776, 262_144
+# 262144 tokens, from one ncu --set full capture of decode_attention_kernel (the kernel's streaming
+# loop has not changed since; captured at commit 68f6732); scaled to the bench launch by the
+# tokens it processes (traffic is proportional to the tokens read)
+NCU_TRAFFIC_BYTES, NCU_TRAFFIC_TOKENS, NCU_TRAFFIC_COMMIT = 138_843_776, 262_144, "68f6732"
+MIN_TIMED_SECONDS = 1.0
 
 
 def metric_name(args):
@@ -62,22 +75,54 @@ def parse_args():
     parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    parser.add_argument("--batch", type=int, default=BATCH_PER_GPU)
-    parser.add_argument("--context", type=int, default=CONTEXT)
+    parser.add_argument("--batch", type=int, default=0,
+                        help="sequences per GPU (default 64 for qwen2-0.5b; for qwen2-7b the global "
+                             "batch of 512 is split over the GPUs unless this is given)")
+    parser.add_argument("--global-batch", type=int, default=512,
+                        help="qwen2-7b serving configuration: sequences over all GPUs")
+    parser.add_argument("--context", type=int, default=0, help="default 4096 (qwen2-7b: 8192)")
     parser.add_argument("--layers", type=int, default=0, help="override the layer count (debug)")
     parser.add_argument("--split-tokens", type=int, default=0)
-    parser.add_argument("--context-source", default="prefill", choices=["prefill", "synthetic"])
+    parser.add_argument("--context-source", default="", choices=["", "prefill", "synthetic"])
     parser.add_argument("--cpu-sample-batch", type=int, default=8)
     parser.add_argument("--skip-cpu-baseline", action="store_true")
+    parser.add_argument("--skip-parity", action="store_true")
     parser.add_argument("--model", default="qwen2-0.5b", choices=["qwen2-0.5b", "qwen2-7b"],
                         help="architecture (the headline metric is quoted on qwen2-0.5b)")
-    parser.add_argument("--context-min", type=int, default=0,
+    parser.add_argument("--context-min", type=int, default=-1,
                         help="with --context-source synthetic: per-sequence contexts uniform in "
                              "[context-min, context] instead of all at --context")
-    return parser.parse_args()
+    parser.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
+                        help="repeat the K timed steps until this much device time is measured")
+    args = parser.parse_args()
+    serving = args.model == "qwen2-7b"
+    args.serving = serving and args.batch == 0  # the 512-sequence serving configuration
+    if args.context == 0:
+        args.context = 8192 if serving else CONTEXT
+    if args.context_min < 0:
+        args.context_min = 1024 if serving else 0
+    if not args.context_source:
+        args.context_source = "synthetic" if serving else "prefill"
+    if args.batch == 0:
+        args.batch = BATCH_PER_GPU  # (the serving configuration sizes its batches from --global-batch)
+    return args
 
 
 def workload_config(args, n_gpus):
+    if args.serving:
+        per = args.global_batch // n_gpus
+        sub = 2 if n_gpus == 1 and per > 256 else 1
+        return {
+            "workload": f"qwen2-7b-architecture serving: global batch {args.global_batch}, contexts "
+                        f"uniform in [{args.context_min}, {args.context}] (seed 512), KV pre-filled "
+                        "with N(0,1), greedy decode, bf16, CUDA-graph step, sequences dealt to the "
+                        "GPUs by context length"
+                        + (f"; one GPU cannot hold {args.global_batch} contiguous KV slots: served as "
+                           f"{sub} sub-batches of {per // sub} in turn" if sub > 1 else ""),
+            "global_batch": args.global_batch, "context": args.context, "layers": args.layers or 28,
+            "parallelism": f"replicas x{n_gpus} (batch-partitioned, NCCL all-gather of token ids)",
+            "l2": "inputs larger than L2 (all weights and every valid KV row are read once per step)",
+        }
     return {
         "workload": f"{args.model}-architecture greedy decode, batch {args.batch}/GPU, context "
                     + (f"uniform in [{args.context_min}, {args.context}]" if args.context_min > 0
@@ -179,6 +224,15 @@ def cpu_decode_baseline(config, weights_cpu, context, sample_batch, steps, warmu
     return sample_batch / step_s, step_s
 
 
+def host_threads():
+    """All host cores for the CPU legs. torch.distributed.run exports OMP_NUM_THREADS=1 to its
+    ranks; the CPU arm runs on rank 0 alone and may use the whole machine."""
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    return torch.get_num_threads()
+
+
 def reference_arm(args, config):
     """`--impl reference`: the reference's CPU implementation of the path (the oracle port;
     the reference package itself cannot travel to the GPU box) on the host cores."""
@@ -188,21 +242,25 @@ def reference_arm(args, config):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    cores = host_threads()
     weights = q2.make_weights(config, seed=0, dtype=torch.bfloat16, device="cpu",
                               reproducible=False)
     steps = max(1, min(args.steps, 5))
     warmup = max(1, min(args.warmup, 1))
-    value, step_s = cpu_decode_baseline(config, weights, args.context, args.cpu_sample_batch,
-                                        steps, warmup)
-    sample = (f"{args.cpu_sample_batch} of the {args.batch} sequences, all {config.num_layers} "
-              f"layers, context {args.context}, median of {steps} steps after {warmup} warm-up")
+    # the serving configuration's contexts average (min + max) / 2: the sample runs at that length
+    context = (args.context + args.context_min) // 2 if args.context_min > 0 else args.context
+    sample_batch = min(args.cpu_sample_batch, 4) if args.model == "qwen2-7b" else args.cpu_sample_batch
+    value, step_s = cpu_decode_baseline(config, weights, context, sample_batch, steps, warmup)
+    total = args.global_batch if args.serving else args.batch * args.gpus
+    sample = (f"{sample_batch} of the {total} sequences, all {config.num_layers} "
+              f"layers, context {context}, median of {steps} steps after {warmup} warm-up")
     print(json.dumps({
         "impl": "reference", "metric": metric_name(args), "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(args, args.gpus),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(),
-                         "kind": "port", "sample": sample},
+        "scaling": "strong" if args.serving else "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": workload_config(args, args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }), file=RESULT_STREAM, flush=True)
@@ -264,13 +322,55 @@ def attention_roofline(engine, lengths_sum, rounds):
     return bytes_per_launch, per_launch_s
 
 
+def oracle_step_parity(engine, config, weights, rows=(0, 1)):
+    """One decode step on the engine (not timed, lengths restored afterwards) against the CPU
+    oracle on the same KV rows, ids and weights for a few sequences: max-abs logit difference,
+    the largest reference logit, and whether the greedy tokens agree."""
+
+    from oracle import qwen2_model
+
+    rows = [r for r in rows if r < engine.batch]
+    index = torch.tensor(rows, device=engine.device)
+    lengths = engine.positions[index].cpu()
+    used = int(lengths.max()) + 1
+    state = qwen2_model.OracleKVState([], [], [], used)
+    for layer in range(config.num_layers):
+        state.keys.append(engine.state.keys[layer][index, :used].cpu())
+        state.values.append(engine.state.values[layer][index, :used].cpu())
+        state.lengths.append(lengths.clone())
+    ids = engine.input_ids[index].cpu()
+    saved = engine.state._length_arena.clone()
+    engine.decode_step(feed_back=False)
+    actual = engine.logits.view(engine.batch, -1)[index].float().cpu()
+    tokens = engine.next_ids[index].cpu()
+    engine.state._length_arena.copy_(saved)  # the row the step wrote is rewritten by the next one
+    torch.cuda.synchronize()
+    weights_cpu = {name: tensor.cpu() for name, tensor in weights.items()}
+    with torch.no_grad():
+        expected = qwen2_model.decode(config, weights_cpu, ids.view(-1, 1), state)[:, 0].float()
+    scale = float(expected.abs().max())
+    diff = float((actual - expected).abs().max())
+    picked = expected.gather(1, tokens.view(-1, 1)).view(-1)
+    return {"sequences": len(rows), "max_abs_logit_diff": diff, "logit_scale": scale,
+            "tokens_equal": bool(torch.equal(tokens, expected.argmax(-1))),
+            "picked_token_margin": float((expected.max(-1).values - picked).max()),
+            "within_2e-2": diff <= 2e-2}
+
+
+def serving_contexts(args):
+    """The serving configuration's per-sequence context lengths (seeded, the same on every rank)."""
+
+    generator = torch.Generator().manual_seed(512)
+    return torch.randint(args.context_min, args.context + 1, (args.global_batch,), generator=generator)
+
+
 def b200_arm(args, config):
     import torch.distributed as dist
 
     from llm_compiler_b200 import kernels
     from llm_compiler_b200 import qwen2 as q2
     from llm_compiler_b200.engine import Qwen2Engine
-    from llm_compiler_b200.serving import TokenGather
+    from llm_compiler_b200.serving import ReplicaServer, balanced_assignment
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -284,20 +384,50 @@ def b200_arm(args, config):
     n_gpus = world
 
     steps, warmup = args.steps, max(args.warmup, 3)
-    capacity = args.context + 2 * (steps + warmup) + 64
     weights = q2.make_weights(config, seed=rank, dtype=torch.bfloat16, device=device,
                               reproducible=False)
-    engine = Qwen2Engine(config, weights, batch=args.batch, capacity=capacity)
+    # ---- which sequences this rank serves, and in how many sub-batches ----
+    imbalance = None
+    if args.serving:
+        contexts_all = serving_contexts(args)
+        buckets = balanced_assignment(contexts_all.tolist(), world)
+        mine = torch.tensor(buckets[rank])
+        kv_sums = [int(contexts_all[torch.tensor(bucket)].sum()) for bucket in buckets]
+        imbalance = {"kv_tokens_per_rank": kv_sums,
+                     "max_over_mean": max(kv_sums) / (sum(kv_sums) / len(kv_sums))}
+        per_rank = len(buckets[rank])
+        sub_batches = 2 if per_rank > 256 else 1
+        # sub-batches are dealt the same way, so that each holds the same mix of lengths
+        parts = balanced_assignment(contexts_all[mine].tolist(), sub_batches)
+        batches = [contexts_all[mine[torch.tensor(part)]] for part in parts]
+    else:
+        contexts = torch.full((args.batch,), args.context)
+        if args.context_min > 0:
+            contexts = torch.randint(args.context_min, args.context + 1, (args.batch,),
+                                     generator=torch.Generator().manual_seed(rank))
+        batches = [contexts]
+    batch = len(batches[0])
+    if any(len(part) != batch for part in batches):
+        raise SystemExit("the global batch must divide evenly over ranks and sub-batches")
+    capacity = args.context + 2 * (steps + warmup) + 64
+    engine = Qwen2Engine(config, weights, batch=batch, capacity=capacity)
     engine.split_tokens = args.split_tokens
     engine.max_length_hint = capacity
 
+    def fill_context(contexts, seed):
+        generator = torch.Generator(device=device).manual_seed(seed)
+        for layer in range(config.num_layers):
+            engine.state.keys[layer].normal_(generator=generator)
+            engine.state.values[layer].normal_(generator=generator)
+        engine.load_context(contexts, next_ids=torch.randint(0, config.vocab_size, (batch,)))
+
     if args.context_source == "prefill":
-        prompt = q2.make_prompt_ids(config, args.batch, args.context, seed=100 + rank)
+        prompt = q2.make_prompt_ids(config, batch, args.context, seed=100 + rank)
         chunk = 8  # sequences per prefill call: bounds the activation footprint
-        if args.batch % chunk == 0 and args.batch > chunk:
+        if batch % chunk == 0 and batch > chunk:
             helper = Qwen2Engine(config, weights, batch=chunk, capacity=args.context)
             first = []
-            for begin in range(0, args.batch, chunk):
+            for begin in range(0, batch, chunk):
                 helper.prefill(prompt[begin:begin + chunk])
                 for layer in range(config.num_layers):
                     engine.state.keys[layer][begin:begin + chunk, :args.context].copy_(
@@ -306,19 +436,11 @@ def b200_arm(args, config):
                         helper.state.values[layer])
                 first.append(helper.next_ids.clone())
             del helper
-            engine.load_context(torch.full((args.batch,), args.context), next_ids=torch.cat(first))
+            engine.load_context(torch.full((batch,), args.context), next_ids=torch.cat(first))
         else:
             engine.prefill(prompt)
     else:
-        generator = torch.Generator(device=device).manual_seed(rank)
-        for layer in range(config.num_layers):
-            engine.state.keys[layer].normal_(generator=generator)
-            engine.state.values[layer].normal_(generator=generator)
-        contexts = torch.full((args.batch,), args.context)
-        if args.context_min > 0:
-            contexts = torch.randint(args.context_min, args.context + 1, (args.batch,),
-                                     generator=torch.Generator().manual_seed(rank))
-        engine.load_context(contexts, next_ids=torch.randint(0, config.vocab_size, (args.batch,)))
+        fill_context(batches[0], rank)
     torch.cuda.synchronize()
     # the split plan of decode attention comes from the measured profile that ships with the
     # package (profile-guided dispatch), resolved with this engine's batch and context bound
@@ -328,50 +450,88 @@ def b200_arm(args, config):
     else:
         decision = None
     engine.capture()
-    step_tokens_read = int(engine.attention_lengths.sum().item())  # KV rows one step reads, at the start
-    gather = TokenGather(args.batch * world, device=device) if world > 1 else None
-
-    def run_steps(count):
-        pending = None
-        for _ in range(count):
-            tokens = engine.decode_step()
-            if gather is not None:
-                if pending is not None:
-                    pending.wait()
-                gather.send.copy_(tokens)
-                pending = dist.all_gather_into_tensor(gather.padded, gather.send, async_op=True)
-        if pending is not None:
-            pending.wait()
+    parity = None
+    if rank == 0 and not args.skip_parity:
+        parity = oracle_step_parity(engine, config, weights)
+    step_tokens_read = sum(int(part.sum()) + len(part) for part in batches)  # KV rows read per global step
+    global_batch = batch * len(batches) * world
+    server = ReplicaServer(engine, batch * world) if world > 1 else None
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    with ClockSampler(local_rank) as clocks:
-        run_steps(warmup)
+    def run_steps(count):
+        pending = None
+        for _ in range(count):
+            tokens = engine.decode_step() if server is None else server.local_step()
+            if server is not None:
+                if pending is not None:
+                    pending.wait()
+                pending = server.gather_async(tokens)
+        if pending is not None:
+            pending.wait()
+
+    def timed(count):
         barrier()
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        launches_before = kernels.launch_count(device)
         start.record()
-        run_steps(steps)
+        run_steps(count)
         stop.record()
         barrier()
         elapsed = torch.tensor([start.elapsed_time(stop) * 1e-3], device=device)
         if world > 1:
             dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
-        device_s = float(elapsed.item())
+        return float(elapsed.item())
 
-        # end to end through the public host API: H2D ids, step, D2H tokens, every step
+    saved_lengths = [None] * len(batches)
+
+    def repeat_seconds():
+        """K steps on every sub-batch in turn, each from its starting context (restored outside
+        the timed regions); returns the device seconds of the K global steps."""
+        total = 0.0
+        for index, part in enumerate(batches):
+            if len(batches) > 1:
+                fill_context(part, rank * 16 + index)
+            elif saved_lengths[0] is not None:
+                engine.state._length_arena.copy_(saved_lengths[0])
+            if saved_lengths[index] is None:
+                saved_lengths[index] = engine.state._length_arena.clone()
+            run_steps(3 if len(batches) > 1 else 0)  # (a refilled sub-batch warms up again)
+            total += timed(steps)
+        return total
+
+    with ClockSampler(local_rank) as clocks:
+        run_steps(warmup)
+        saved_lengths[0] = None
+        launches_before = kernels.launch_count(device)
+        repeats = [repeat_seconds()]
+        wanted = args.min_seconds
+        while sum(repeats) < wanted and len(repeats) < 200:
+            repeats.append(repeat_seconds())
+        # (every rank sees the same max-over-ranks times, so all run the same number of repeats)
+        device_s = statistics.median(repeats)
+
+        # end to end through the public host API: H2D ids, step, all-gather of the tokens where
+        # there are several ranks, D2H tokens, every step
+        engine.state._length_arena.copy_(saved_lengths[-1])
         host_ids = engine.next_ids.cpu()
+
+        def host_step(ids):
+            tokens = engine.step(ids)
+            if server is not None:
+                server.gather_host(engine.next_ids)
+            return tokens
+
         for _ in range(3):
-            host_ids = engine.step(host_ids).clone()
+            host_ids = host_step(host_ids).clone()
         barrier()
         wall = time.perf_counter()
         for _ in range(steps):
-            host_ids = engine.step(host_ids)
+            host_ids = host_step(host_ids)
         torch.cuda.synchronize()
-        e2e_local = time.perf_counter() - wall
+        e2e_local = (time.perf_counter() - wall) * len(batches)  # (one sub-batch timed; all are alike)
         e2e_t = torch.tensor([e2e_local], device=device)
         if world > 1:
             dist.all_reduce(e2e_t, op=dist.ReduceOp.MAX)
@@ -383,11 +543,12 @@ def b200_arm(args, config):
             bytes_per_launch, launch_s = attention_roofline(engine, lengths_sum, rounds=10)
             peak, peak_kind = measured_hbm_peak()
             achieved = bytes_per_launch / launch_s / 1e9
+            headline = batch == BATCH_PER_GPU and args.model == "qwen2-0.5b"
             roofline = {"bound": "hbm", "kernel": "decode_attention_kernel", "achieved": achieved,
                         "peak": peak, "peak_source": f"{peak_kind} copy bandwidth", "unit": "GB/s",
                         "frac": achieved / peak, "frac_of_nominal_8000": achieved / 8000.0,
-                        "traffic": NCU_TRAFFIC_BYTES * lengths_sum / NCU_TRAFFIC_TOKENS
-                        if args.batch == BATCH_PER_GPU and args.model == "qwen2-0.5b" else None,
+                        "traffic": NCU_TRAFFIC_BYTES * lengths_sum / NCU_TRAFFIC_TOKENS if headline else None,
+                        "traffic_capture_commit": NCU_TRAFFIC_COMMIT if headline else None,
                         "algorithmic_bytes_per_launch": bytes_per_launch,
                         "us_per_launch": launch_s * 1e6}
     engine.state.check()
@@ -396,37 +557,48 @@ def b200_arm(args, config):
         if world > 1:
             dist.destroy_process_group()
         return
-    total_tokens = args.batch * world * steps
+    total_tokens = global_batch * steps
     kv_bytes_per_token = config.num_layers * 4 * config.num_kv_heads * config.head_dim
-    step_bytes = 2 * q2.parameter_count(config) + kv_bytes_per_token * step_tokens_read
+    # per GPU and global step: the weights once per sub-batch, every valid KV row once
+    step_bytes = 2 * q2.parameter_count(config) * len(batches) + kv_bytes_per_token * step_tokens_read
+    if not config.tie_word_embeddings:  # an untied embedding table is only gathered, not streamed
+        step_bytes -= 2 * config.vocab_size * config.hidden_size * len(batches)
     result = {
         "metric": metric_name(args), "value": total_tokens / device_s, "unit": UNIT, "n_gpus": n_gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": device_s / steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "ms_per_step_min": min(repeats) / steps * 1e3, "ms_per_step_max": max(repeats) / steps * 1e3,
+        "repeats": len(repeats),
+        "higher_is_better": True, "scaling": "strong" if args.serving else "weak",
+        "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": workload_config(args, n_gpus),
         "e2e": {"value": total_tokens / e2e_s, "unit": UNIT,
-                "h2d_bytes_per_step": args.batch * 8, "d2h_bytes_per_step": args.batch * 8,
+                "h2d_bytes_per_step": batch * 8 * len(batches), "d2h_bytes_per_step": batch * 8 * len(batches),
                 "ms_per_step": e2e_s / steps * 1e3},
-        "gpu_launches": engine.kernels_per_step * steps,
-        "kernels_per_step": engine.kernels_per_step,
+        "gpu_launches": engine.kernels_per_step * steps * len(batches),
+        "kernels_per_step": engine.kernels_per_step * len(batches),
         "dispatch": None if decision is None else {
             "op": "decode_attention", "variant": decision.variant, "source": decision.source,
             "profile_value": decision.profile_value},
         "clocks": clocks.summary(),
         "roofline": roofline,
+        "parity": parity,
         "step_bandwidth": {"algorithmic_gb_per_step": step_bytes / 1e9,
                            "achieved_gbs_per_gpu": step_bytes / (device_s / steps) / 1e9,
                            "frac_of_measured_hbm": step_bytes / (device_s / steps) / 1e9 /
                            measured_hbm_peak()[0]},
     }
+    if imbalance is not None:
+        result["balance"] = imbalance
     if world == 1 and not args.skip_cpu_baseline:
+        cores = host_threads()
         weights_cpu = {name: tensor.cpu() for name, tensor in weights.items()}
-        value, step_s = cpu_decode_baseline(config, weights_cpu, args.context,
-                                            args.cpu_sample_batch, 3, 1)
+        context = (args.context + args.context_min) // 2 if args.context_min > 0 else args.context
+        sample_batch = min(args.cpu_sample_batch, 4) if args.model == "qwen2-7b" else args.cpu_sample_batch
+        value, step_s = cpu_decode_baseline(config, weights_cpu, context, sample_batch, 3, 1)
         result["cpu_baseline"] = {
-            "value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{args.cpu_sample_batch} of the {args.batch} sequences, all "
-                      f"{config.num_layers} layers, context {args.context}, median of 3 steps "
+            "value": value, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{sample_batch} of the {global_batch} sequences, all "
+                      f"{config.num_layers} layers, context {context}, median of 3 steps "
                       f"after 1 warm-up ({step_s:.2f} s/step)"}
     print(json.dumps(result), file=RESULT_STREAM, flush=True)
     if world > 1:

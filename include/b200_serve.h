@@ -297,7 +297,7 @@ int b200_qkv_decode_attention(const void* qkv_partials, int64_t qkv_splits, cons
  *   b200_linear_rms_input        serve.rms_norm + serve.linear (+ bias, + SwiGLU epilogue) on the
  *                                un-normalised input and the column-scaled weight
  *   b200_linear_splitk_residual  serve.linear + aten.add: output = r(r(x W^T) + residual);
- *                                n a multiple of 4, M <= 128
+ *                                n a multiple of 4, M <= 256
  * b200_qkv_decode_attention takes the same fold for the q|k|v projection: with
  * norm_row_squares (fp32 [qkv_splits, B], what b200_linear_partial left: sum of squares of the
  * un-normalised rows of width norm_hidden per K slice) it scales the reduced sums by

@@ -849,7 +849,7 @@ PartialPlan plan_cluster(int64_t m, int64_t k, int64_t n) {
   const int64_t rows = m <= 64 ? 64 : 128;
   for (int bn : {32, 64, 128}) {
     if (rows * bn > 64 * 128) break;  // two copies of the fp32 tile must fit behind the ring
-    const int64_t tiles = ceil_div(n, bn);
+    const int64_t tiles = ceil_div(n, bn) * ceil_div(m, kBM);
     for (int64_t splits = 1; splits <= 8 && splits <= kb; ++splits) {
       if (tiles * splits > kNumSMs) break;
       const int64_t per = ceil_div(kb, splits);
@@ -1041,6 +1041,10 @@ int linear_splitk_residual_tcgen05(const void* input, const void* weight, const 
                                    int64_t input_row_stride, int32_t* status, cudaStream_t stream) {
   const PartialPlan plan = plan_cluster(m, k, n);
   const int a_rows = m <= 64 ? 64 : 128;
+  // enough N x M tiles to fill the GPU without cutting K: the plain kernel with the residual epilogue
+  if (plan.splits <= 1)
+    return linear_tcgen05(input, weight, nullptr, residual, output, m, k, n, input_row_stride,
+                          B200_EPILOGUE_RESIDUAL, status, stream, false, 0.0);
   CUtensorMap a_map, b_map;
   if (!make_bf16_matrix_map(&a_map, input, m, k, input_row_stride, a_rows) ||
       !make_bf16_matrix_map(&b_map, weight, n, k, k, plan.bn))
@@ -1082,7 +1086,7 @@ extern "C" int b200_linear_splitk_residual(const void* input, const void* weight
   if (!input || !weight || !residual || !output || m <= 0 || k <= 0 || n <= 0 ||
       input_row_stride < k)
     return B200_ERR_BAD_ARGUMENT;
-  if (m > 128) return B200_ERR_TOO_LARGE;
+  if (m > 256) return B200_ERR_TOO_LARGE;
   if (k % 8 != 0 || input_row_stride % 8 != 0 || n % 4 != 0) return B200_ERR_UNSUPPORTED;
   if (!aligned16(input) || !aligned16(weight) || !aligned16(residual) || !aligned16(output))
     return B200_ERR_ALIGNMENT;

@@ -295,12 +295,21 @@ class Qwen2Engine:
                 q, self.state.keys[index], self.state.values[index], self.attention_lengths,
                 None, scale=self.scale, numerical_mode=self.mode,
                 split_tokens=self.split_tokens, max_length_hint=self.max_length_hint)
-            x = kernels.b200_linear(attn.view(batch, q_size), layer["o_w"], residual=x,
-                                    epilogue="residual")
+            # o and down have few N tiles: at up to 256 bf16 rows they run as cluster split-K
+            # projections that add the residual themselves (same rounding points)
+            splitk = self.dtype == torch.bfloat16 and batch <= 256 and cfg.hidden_size % 4 == 0
+            if splitk:
+                x = kernels.b200_linear_splitk_residual(attn.view(batch, q_size), layer["o_w"], x)
+            else:
+                x = kernels.b200_linear(attn.view(batch, q_size), layer["o_w"], residual=x,
+                                        epilogue="residual")
             h = kernels.b200_rms_norm(x, layer["post_norm"], epsilon=cfg.rms_norm_eps,
                                       round_before_weight=True, numerical_mode=self.mode)
             a = kernels.b200_linear(h, layer["gate_up_w"], epilogue="swiglu")
-            x = kernels.b200_linear(a, layer["down_w"], residual=x, epilogue="residual")
+            if splitk:
+                x = kernels.b200_linear_splitk_residual(a, layer["down_w"], x)
+            else:
+                x = kernels.b200_linear(a, layer["down_w"], residual=x, epilogue="residual")
         h = kernels.b200_rms_norm(x, self.final_norm, epsilon=cfg.rms_norm_eps,
                                   round_before_weight=True, numerical_mode=self.mode)
         self.logits = kernels.b200_linear(h, self.lm_head)

@@ -957,7 +957,7 @@ def b200_linear_rms_input(tensor: torch.Tensor, folded_weight: torch.Tensor,
 
 def b200_linear_splitk_residual(tensor: torch.Tensor, weight: torch.Tensor,
                                 residual: torch.Tensor) -> torch.Tensor:
-    """serve.linear + aten.add in one launch at decode sizes (bf16, at most 128 rows):
+    """serve.linear + aten.add in one launch at decode sizes (bf16, at most 256 rows):
     r(r(x W^T) + residual). The K slices of an output tile are the CTAs of one thread-block
     cluster and add their fp32 accumulators through distributed shared memory."""
 
@@ -978,6 +978,8 @@ def b200_linear_splitk_residual(tensor: torch.Tensor, weight: torch.Tensor,
     code = _lib.load().b200_linear_splitk_residual(
         tensor.data_ptr(), weight.data_ptr(), residual.data_ptr(), output.data_ptr(), m, k, n,
         tensor.stride(0), rt.status.data_ptr(), _stream())
+    if code == _lib.ERR_UNSUPPORTED:  # no cluster plan for this shape: the general projection
+        return b200_linear(tensor, weight, residual=residual, epilogue="residual")
     _check(code, "b200_linear_splitk_residual")
     _count(rt)
     return output

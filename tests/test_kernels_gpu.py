@@ -752,7 +752,8 @@ def test_wrappers_reject_cpu_tensors_and_bad_shapes():
 # ------------------------------------------ five-launch decode layer: its three kernels ----
 @pytest.mark.parametrize("m,k,n", [(64, 896, 896), (64, 4864, 896), (3, 256, 256), (1, 512, 256),
                                    (33, 3584, 3584), (128, 896, 896), (100, 4864, 896),
-                                   (64, 18944, 3584), (7, 960, 1092)])
+                                   (64, 18944, 3584), (7, 960, 1092), (256, 896, 896),
+                                   (200, 4864, 896), (256, 3584, 3584)])
 def test_linear_splitk_residual_matches_linear_then_add(m, k, n):
     """serve.linear + aten.add in one launch: the K slices of a tile are the CTAs of a
     thread-block cluster that add their accumulators through distributed shared memory.

@@ -11,8 +11,8 @@ import pytest
 import torch
 import torch.distributed as dist
 
-from llm_compiler_b200.serving import (ReplicaServer, TokenGather, balanced_assignment,
-                                       partition_batch)
+from llm_compiler_b200.serving import (ReplicaFailure, ReplicaServer, TokenGather,
+                                       balanced_assignment, partition_batch)
 
 
 def free_port():
@@ -53,6 +53,8 @@ class FakeEngine:
         self.position = 0
 
     def decode_step(self):
+        if getattr(self, "fail_at", None) == self.position:
+            raise RuntimeError("injected host-side failure")
         self.ids = (self.ids * 3 + self.position) % 1000
         self.position += 1
         return self.ids
@@ -63,29 +65,31 @@ def _worker(rank, world, port, global_batch, fail_rank, queue):
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        store = dist.distributed_c10d._get_default_store()
         all_ids = torch.arange(global_batch, dtype=torch.int64) * 7 % 1000
         piece = partition_batch(global_batch, world, rank)
-        server = ReplicaServer(FakeEngine(all_ids[piece.start:piece.stop]), global_batch)
+        engine = FakeEngine(all_ids[piece.start:piece.stop])
+        if fail_rank == rank:
+            engine.fail_at = 2
+        if fail_rank == "silent" and rank == 1:
+            engine.vanish_at = 2
+        # the product's own failure protocol (serving.FailureMonitor inside ReplicaServer): a
+        # rank whose engine raises reports it on the host before leaving; the others check
+        # before their next collective and stop cleanly; a rank that just stops answering is
+        # found by the heartbeat timeout
+        server = ReplicaServer(engine, global_batch, check_every=1, failure_timeout_s=3.0)
         reference = FakeEngine(all_ids)
         gathered = []
         for step in range(4):
-            if fail_rank is not None:
-                # failure protocol: a rank that cannot continue says so on the host, between
-                # steps; the others check before their next collective and stop cleanly
-                if rank == fail_rank and step == 2:
-                    store.set("failed", str(rank))
-                    raise RuntimeError("injected host-side failure")
-                store.add("heartbeat", 1)
-                if step >= 2:
-                    store.wait(["failed"])
-                    queue.put((rank, "stopped", step))
-                    return
+            if getattr(engine, "vanish_at", None) == step:
+                queue.put((rank, "vanished", step))  # leaves between steps without a word
+                return
             _, full = server.decode_step()
             expected = reference.decode_step()
             assert torch.equal(full, expected), (rank, step)
             gathered.append(full.clone())
         queue.put((rank, "ok", len(gathered)))
+    except ReplicaFailure as error:
+        queue.put((rank, "stopped", str(error)))
     except RuntimeError as error:
         queue.put((rank, "raised", str(error)))
     finally:
@@ -115,8 +119,37 @@ def test_two_ranks_gather_tokens_in_lock_step(global_batch):
 
 def test_rank_failure_between_steps_is_seen_on_the_host():
     results = _run(2, 8, fail_rank=1)
-    assert results[0] == (0, "stopped", 2)
+    assert results[0][:2] == (0, "stopped") and "replica 1 reported a failure" in results[0][2]
+    assert "injected host-side failure" in results[0][2]
     assert results[1][:2] == (1, "raised")
+
+
+def test_rank_that_stops_answering_is_found_by_the_heartbeat_timeout():
+    results = _run(2, 8, fail_rank="silent")
+    assert results[0][:2] == (0, "stopped") and "did not reach step 2" in results[0][2]
+    assert results[1] == (1, "vanished", 2)
+
+
+def test_failure_monitor_on_a_plain_store():
+    """The protocol itself, on an in-process HashStore: no process group needed."""
+    from llm_compiler_b200.serving import FailureMonitor
+
+    store = dist.HashStore()
+    a = FailureMonitor(store, 0, 2, timeout_s=0.2)
+    b = FailureMonitor(store, 1, 2, timeout_s=0.2)
+    a.beat(0)
+    with pytest.raises(ReplicaFailure, match=r"replicas \[1\] did not reach step 0"):
+        a.check(0)
+    b.beat(0)
+    a.check(0)
+    b.check(0)
+    b.beat(5)
+    a.beat(3)
+    a.check(3)  # a peer that is ahead is fine
+    b.report("out of memory")
+    a.report("second report loses")
+    with pytest.raises(ReplicaFailure, match="replica 1 reported a failure before step 4: out of memory"):
+        a.check(4)
 
 
 def test_single_process_gather_is_a_copy():
