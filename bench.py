@@ -455,12 +455,14 @@ def b200_arm(args, config):
         parity = oracle_step_parity(engine, config, weights)
     step_tokens_read = sum(int(part.sum()) + len(part) for part in batches)  # KV rows read per global step
     global_batch = batch * len(batches) * world
-    server = ReplicaServer(engine, batch * world) if world > 1 else None
+    server = ReplicaServer(engine, batch * world, failure_timeout_s=60.0) if world > 1 else None
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    barrier()  # rank 0 has just spent seconds in the CPU oracle: start the steps together
 
     def run_steps(count):
         pending = None
