@@ -19,6 +19,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple
 import torch
 
 from . import kernels
+from .contracts import SymbolError, bind_symbols
 from .dispatch_plan import resolve_dispatch_plan, split_tokens_of
 from .kernel_ir import decode_attribute, require_full_lowering, value_dtype, value_rank
 from .kv_state import ExecutionError, PreallocatedKVCacheState
@@ -139,6 +140,10 @@ class B200Executor:
         for declared, runtime_value in zip(function.block.arguments, arguments):
             self._validate_argument(declared, runtime_value)
             environment[declared.name] = runtime_value
+        try:  # symbol equality and the exporter's value ranges (execution.py:1323-1347)
+            symbols = bind_symbols(function.block.arguments, arguments)
+        except SymbolError as error:
+            raise ExecutionError(str(error)) from error
         trace = []
         for operation in function.block.operations:
             handler = self._handlers.get(operation.name)
@@ -162,7 +167,7 @@ class B200Executor:
                 environment[declared.name] = runtime_value
             trace.append(operation.name)
         outputs = tuple(environment[value.name] for value in function.returns)
-        return ExecutionResult(outputs, tuple(trace), {})
+        return ExecutionResult(outputs, tuple(trace), symbols)
 
     def _constant(self, operation, handler, operands, environment):
         """Weight-preparation ops (`constant: true`) depend on graph parameters only: evaluated

@@ -584,7 +584,12 @@ def select_dispatch_plans(module, cost_model) -> Dict[str, Any]:
 
 
 def verify_module(module) -> None:
-    """SSA sanity: unique definitions, operands defined before use (ir.py:220-260)."""
+    """SSA sanity (unique definitions, operands defined before use, ir.py:220-260) and the
+    per-operation contracts of the kernel.b200.* / runtime.kv.* dialect (contracts.py: shapes,
+    dtypes, bias / epilogue operands, GQA groups, slots, as ir.py:462-835 checks them for the
+    reference's own op names). Raises ValueError listing every violation."""
+
+    from .contracts import operation_contract_errors
 
     errors = []
     for function in module.functions:
@@ -604,5 +609,6 @@ def verify_module(module) -> None:
         for value in function.returns:
             if value.name not in defined:
                 errors.append(f"@{function.name} returns undefined {value.name}")
+    errors.extend(operation_contract_errors(module))
     if errors:
         raise ValueError("\n".join(errors))

@@ -279,3 +279,29 @@ def test_declared_and_classified_causal_masks_and_a_mask_that_is_not_causal(gold
     never.run(plain, bind_arguments(plain.functions[0], weights, {
         **inputs, "attention_mask": causal_mask(batch, prompt)}))
     assert not any(e["causal"] for e in never.lowering_trace if e.get("op") == "prefill_attention.mask")
+
+
+def test_symbolic_dimensions_are_bound_and_guarded_at_run_time(golden_tiny):
+    """The reference executor binds every symbolic dimension of the signature to its run-time
+    extent and enforces the exporter's ranges (execution.py:1323-1347); so does this one."""
+    gold = golden_tiny["fp32"]
+    config = q2.Qwen2Config(**gold["config"])
+    weights = {k: v.cuda() for k, v in q2.make_weights(config, seed=0).items()}
+    inv_freq = q2.inverse_frequency(config, "cuda")
+    batch, prompt = gold["batch"], gold["prompt"]
+    prefill = lowered("prefill", "fast")
+    executor = B200Executor()
+
+    def arguments(batch, tokens, position_batch=None):
+        return bind_arguments(prefill.functions[0], weights, {
+            "input_ids": torch.zeros(batch, tokens, dtype=torch.int64, device="cuda"),
+            "attention_mask": causal_mask(batch, tokens),
+            "position_ids": torch.arange(tokens).repeat(position_batch or batch, 1).cuda(),
+            "inv_freq": inv_freq})
+
+    result = executor.run(prefill, arguments(batch, prompt))
+    assert sorted(result.symbolic_dimensions.values()) == sorted([batch, prompt])
+    with pytest.raises(ExecutionError, match="above the exporter's upper bound"):
+        executor.run(prefill, arguments(9, prompt))  # exported with max_batch = 8
+    with pytest.raises(ExecutionError, match="breaks the equality"):
+        executor.run(prefill, arguments(batch, prompt, position_batch=batch - 1))
