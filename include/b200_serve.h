@@ -197,16 +197,23 @@ int b200_decode_attention_static_scratch(
  * oracle ReferenceExecutor._serve_prefill_attention (execution.py:707-739).
  * q: B x Hq x T x D, k/v: B x Hkv x T x D strided (last dim contiguous);
  * output memory is B x T x Hq x D contiguous (the caller views it as B x Hq x T x D).
- * Causal-proved bf16 calls in the fast mode run on tcgen05 (S and O tiles in tensor memory,
- * operands by TMA); masked calls, the pytorch_compatible mode and fp32 use the warp-level and
- * CUDA-core kernels. status (may be NULL) receives B200_STATUS_WAIT_TIMEOUT. */
+ * bf16 calls in the fast mode run on tcgen05 (S and O tiles in tensor memory, operands by
+ * TMA): causal-proved ones, and masked ones (the reference's `causal: "mask"` contract,
+ * passes/prefill_attention.py:173-180) when the mask is fp32 with a contiguous last dimension
+ * and a workspace of b200_prefill_attention_workspace_bytes(batch, tokens) is given; a pre-pass
+ * then classifies the mask's 128 x 128 tiles (all zero / all -inf / mixed) so that tiles that
+ * are all -inf at either end of a row block are never touched and all-zero tiles read no mask.
+ * Other masked calls, the pytorch_compatible mode and fp32 use the warp-level and CUDA-core
+ * kernels (workspace may be NULL). status (may be NULL) receives B200_STATUS_WAIT_TIMEOUT. */
+int64_t b200_prefill_attention_workspace_bytes(int64_t batch, int64_t tokens);
 int b200_prefill_attention(const void* query, const void* key, const void* value,
                            const void* mask, void* output, int64_t batch, int64_t q_heads,
                            int64_t kv_heads, int64_t tokens, int64_t head_dim,
                            const int64_t query_strides[4], const int64_t key_strides[4],
                            const int64_t value_strides[4], const int64_t mask_strides[4],
                            int mask_dtype, double scale, int causal, int dtype, int mode,
-                           int32_t* status, void* stream);
+                           void* workspace, int64_t workspace_bytes, int32_t* status,
+                           void* stream);
 
 /* ---- Linear ------------------------------------------------------------------
  * y[M,N] = x[M,K] * W[N,K]^T (+ bias[N]) with fp32 accumulation and an optional

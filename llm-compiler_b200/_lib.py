@@ -66,8 +66,10 @@ SIGNATURES = {
     "b200_decode_attention_static_scratch": (c_int, [c_void_p] * 6 + [c_int64] * 9 +
                                              [c_int, c_double, c_int, c_int, c_int64, c_int64,
                                               c_void_p, c_void_p]),
+    "b200_prefill_attention_workspace_bytes": (c_int64, [c_int64, c_int64]),
     "b200_prefill_attention": (c_int, [c_void_p] * 5 + [c_int64] * 5 + [_I64P] * 4 +
-                               [c_int, c_double, c_int, c_int, c_int, c_void_p, c_void_p]),
+                               [c_int, c_double, c_int, c_int, c_int, c_void_p, c_int64, c_void_p,
+                                c_void_p]),
     "b200_classify_causal_mask": (c_int, [c_void_p, c_int64, c_int64, _I64P, c_int, c_void_p,
                                           c_void_p]),
     "b200_linear_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int, c_int]),

@@ -331,10 +331,17 @@ int prefill_attention_tcgen05(const void* query, const void* key, const void* va
                               int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t tokens,
                               int64_t head_dim, const int64_t query_strides[4],
                               const int64_t key_strides[4], const int64_t value_strides[4],
-                              double scale, int32_t* status, cudaStream_t stream);
+                              double scale, int32_t* status, cudaStream_t stream, const void* mask,
+                              const int64_t* mask_strides, void* workspace, int64_t workspace_bytes);
+int64_t prefill_attention_tcgen05_workspace_bytes(int64_t batch, int64_t tokens);
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int64_t b200_prefill_attention_workspace_bytes(int64_t batch, int64_t tokens) {
+  if (batch <= 0 || tokens <= 0) return 0;
+  return prefill_attention_tcgen05_workspace_bytes(batch, tokens);
+}
 
 extern "C" int b200_prefill_attention(const void* query, const void* key, const void* value,
                                       const void* mask, void* output, int64_t batch,
@@ -343,8 +350,8 @@ extern "C" int b200_prefill_attention(const void* query, const void* key, const 
                                       const int64_t key_strides[4],
                                       const int64_t value_strides[4],
                                       const int64_t mask_strides[4], int mask_dtype, double scale,
-                                      int causal, int dtype, int mode, int32_t* status,
-                                      void* stream) {
+                                      int causal, int dtype, int mode, void* workspace,
+                                      int64_t workspace_bytes, int32_t* status, void* stream) {
   if (!query || !key || !value || !output || !query_strides || !key_strides || !value_strides ||
       batch < 0 || q_heads <= 0 || kv_heads <= 0 || tokens < 0 || head_dim <= 0 ||
       q_heads % kv_heads != 0)
@@ -390,10 +397,13 @@ extern "C" int b200_prefill_attention(const void* query, const void* key, const 
     if (query_strides[i] % 8 != 0 || key_strides[i] % 8 != 0 || value_strides[i] % 8 != 0)
       return B200_ERR_ALIGNMENT;
 
-  if (mask == nullptr && causal && mode == B200_MODE_FAST) {
+  if (mode == B200_MODE_FAST && ((mask == nullptr && causal) ||
+                                 (mask != nullptr && !causal && mask_dtype == B200_F32 && workspace != nullptr))) {
+    // the tensor-core kernel: causal-proved, or the additive-mask contract with its tile pre-pass
     const int code = prefill_attention_tcgen05(query, key, value, output, batch, q_heads, kv_heads,
                                                tokens, head_dim, query_strides, key_strides,
-                                               value_strides, scale, status, s);
+                                               value_strides, scale, status, s, mask, mask_strides,
+                                               workspace, workspace_bytes);
     if (code != B200_ERR_UNSUPPORTED) return code;
   }
 

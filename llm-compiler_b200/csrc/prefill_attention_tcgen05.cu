@@ -24,6 +24,15 @@
 // owner of the 512 TMEM columns (S at 0 and 128, O behind them). Every mbarrier wait is bounded:
 // a wait that gives up sets B200_STATUS_WAIT_TIMEOUT, tensor memory is freed and the CTA
 // returns. Query blocks are handed out heaviest first across all heads and sequences.
+//
+// MASKED variant: the reference's own contract, an arbitrary additive fp32 mask B x 1 x T x T
+// (`causal: "mask"`, passes/prefill_attention.py:173-180). A pre-pass classifies every 128 x 128
+// tile of the mask as all zero, all -inf or mixed (one read of the mask); a CTA then walks only
+// the key tiles between the first and the last tile that is not all -inf for its query tiles,
+// adds nothing on all-zero tiles, and on the others adds the mask values (fetched while the
+// tensor core computes S, carried as bf16 pairs: exact for 0 and -inf) to the scaled scores
+// before the running maximum. A causal mask given as data therefore costs what the causal-proved
+// kernel costs plus the pre-pass; a row with every key masked yields NaN as in the reference.
 #include <stdlib.h>
 #include <string.h>
 
@@ -44,7 +53,41 @@ struct PrefillTcParams {
   int q_heads, groups, tokens;
   int q_token_dim1, k_token_dim1, v_token_dim1;  // coordinate order of the three tensor maps
   float scale_log2;
+  // MASKED: additive fp32 mask with a contiguous last dimension; classes of its 128 x 128 tiles
+  const float* mask = nullptr;
+  int64_t mask_stride_b = 0, mask_stride_q = 0;
+  const uint8_t* tile_class = nullptr;  // [batch or 1][q tiles][k tiles]: 0 zero, 1 -inf, 2 mixed
+  int64_t class_stride_b = 0;
 };
+
+// Classes of the 128 x 128 tiles of an additive mask. Rows beyond T are ignored, key columns
+// beyond T count as -inf (the attention kernel must not let zero-filled keys take part).
+__global__ void __launch_bounds__(256)
+mask_tile_class_kernel(const float* __restrict__ mask, int64_t stride_b, int64_t stride_q, int tokens,
+                       int tiles, uint8_t* __restrict__ classes) {
+  const int tk = blockIdx.x, tq = blockIdx.y, b = blockIdx.z;
+  const float* base = mask + b * stride_b;
+  bool nonzero = false, finite = false;  // something is not 0 / something is not -inf
+  for (int item = threadIdx.x; item < 128 * 32; item += 256) {
+    const int row = tq * 128 + item / 32, key = tk * 128 + (item % 32) * 4;
+    if (row >= tokens) continue;
+    const float* src = base + static_cast<int64_t>(row) * stride_q + key;
+    if (key + 3 < tokens) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(src));
+      nonzero |= v.x != 0.0f || v.y != 0.0f || v.z != 0.0f || v.w != 0.0f;
+      finite |= v.x != -INFINITY || v.y != -INFINITY || v.z != -INFINITY || v.w != -INFINITY;
+    } else {
+      for (int i = 0; i < 4; ++i) {
+        const float v = key + i < tokens ? __ldg(src + i) : -INFINITY;
+        nonzero |= v != 0.0f;
+        finite |= v != -INFINITY;
+      }
+    }
+  }
+  const int any_nonzero = __syncthreads_or(nonzero), any_finite = __syncthreads_or(finite);
+  if (threadIdx.x == 0)
+    classes[(static_cast<int64_t>(b) * tiles + tq) * tiles + tk] = !any_nonzero ? 0 : (!any_finite ? 1 : 2);
+}
 
 __device__ __forceinline__ float exp2_fast(float x) {
   float y;
@@ -65,7 +108,7 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 domain
 constexpr uint32_t kSpinLimit = 2000000u;   // polls of an MMA thread before it gives up (about 0.1 s)
 
 // 18 warps: five on one of the four 16 K-register sub-partitions, so at most 96 registers each.
-template <int D>
+template <int D, bool MASKED>
 __global__ void __launch_bounds__(640, 1)
 prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant__ CUtensorMap q_map,
                                  const __grid_constant__ CUtensorMap k_map,
@@ -99,10 +142,35 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
   const int kvh = hq / p.groups;
   const int q0 = q_block * G * kTile;
   const int all_tiles = (p.tokens + kTile - 1) / kTile;
-  // causal: group g (query tile G q_block + g) needs key tiles 0 .. its own
-  const int tiles_0 = min(q_block * G + 1, all_tiles), tiles_1 = min(q_block * G + 2, all_tiles);
+  // Key tiles are walked from `lo` on; `j` below counts from there (buffer slots and barrier
+  // phases follow j, coordinates lo + j). causal: group g (query tile G q_block + g) needs key
+  // tiles 0 .. its own. MASKED: from the first to the last tile that is not all -inf for the
+  // group's query tile (a group without any such tile still walks one, and yields NaN rows).
+  int lo = 0, tiles_0 = min(q_block * G + 1, all_tiles), tiles_1 = min(q_block * G + 2, all_tiles);
+  const uint8_t* class_row[G] = {nullptr, nullptr};
+  if (MASKED) {
+    int first[G], last[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const int q_tile = min(q_block * G + g, all_tiles - 1);  // (a tile past the end mirrors the last)
+      class_row[g] = p.tile_class + b * p.class_stride_b + static_cast<int64_t>(q_tile) * all_tiles;
+      first[g] = -1;
+      last[g] = 0;
+      for (int j = 0; j < all_tiles; ++j)
+        if (class_row[g][j] != 1) {
+          if (first[g] < 0) first[g] = j;
+          last[g] = j;
+        }
+      if (first[g] < 0) first[g] = 0;
+    }
+    lo = min(first[0], first[1]);
+    tiles_0 = last[0] + 1 - lo;
+    tiles_1 = last[1] + 1 - lo;
+    if (tiles_0 < 1) tiles_0 = 1;
+    if (tiles_1 < 1) tiles_1 = 1;
+  }
   auto tiles_of = [&](int g) { return g == 0 ? tiles_0 : tiles_1; };
-  const int n_tiles = tiles_1;
+  const int n_tiles = max(tiles_0, tiles_1);
 
   const uint32_t q_smem = smem_u32(smem);                   // G tiles
   const uint32_t k_smem = q_smem + G * kTileBytes;          // two buffers
@@ -158,7 +226,7 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
 #pragma unroll
       for (int panel = 0; panel < kPanels; ++panel)
         load_box(k_smem + s * kTileBytes + panel * kPanelBytes, &k_map, smem_u32(&k_full[s]),
-                 panel * 64, j * kTile, kvh, b, p.k_token_dim1);
+                 panel * 64, (lo + j) * kTile, kvh, b, p.k_token_dim1);
       return true;
     };
     bool ok = load_k(0);
@@ -172,7 +240,7 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
 #pragma unroll
       for (int panel = 0; panel < kPanels; ++panel)
         load_box(v_smem + vs * kTileBytes + panel * kPanelBytes, &v_map, smem_u32(&v_full[vs]),
-                 panel * 64, j * kTile, kvh, b, p.v_token_dim1);
+                 panel * 64, (lo + j) * kTile, kvh, b, p.v_token_dim1);
     }
     if (!ok) failed = 1;
   } else if (warp == kMmaWarp && lane == 0) {
@@ -269,15 +337,67 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
       // A wait that gives up ends this warp's work, but the warp keeps meeting the group at the
       // named barrier once per tile. (Every wait's outcome is made warp-uniform: the
       // tensor-memory accesses are warp-collective.)
+      // MASKED: this thread's 64 mask values of the tile travel while the tensor core computes S
+      uint32_t mask_pairs[MASKED ? 32 : 1];  // bf16 pairs (exact for 0 and -inf)
+      bool add_mask = false;
+      if (MASKED) {
+        add_mask = class_row[g][lo + j] != 0;
+        if (add_mask) {
+          const int q_abs = q0 + g * kTile + row, key_abs = (lo + j) * kTile + key0;
+          const float* src = p.mask + b * p.mask_stride_b + static_cast<int64_t>(q_abs) * p.mask_stride_q + key_abs;
+          if (q_abs < p.tokens && key_abs + 64 <= p.tokens) {
+#pragma unroll
+            for (int batch8 = 0; batch8 < 2; ++batch8) {
+              float4 m[8];
+#pragma unroll
+              for (int c = 0; c < 8; ++c) m[c] = __ldg(reinterpret_cast<const float4*>(src) + batch8 * 8 + c);
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {
+                mask_pairs[batch8 * 16 + 2 * c] = pack_bf16x2(m[c].x, m[c].y);
+                mask_pairs[batch8 * 16 + 2 * c + 1] = pack_bf16x2(m[c].z, m[c].w);
+              }
+            }
+          } else {  // a ragged edge: rows past T add nothing, keys past T are masked out
+#pragma unroll
+            for (int i = 0; i < 64; i += 2) {
+              const float m0 = q_abs >= p.tokens ? 0.0f : (key_abs + i < p.tokens ? __ldg(src + i) : -INFINITY);
+              const float m1 = q_abs >= p.tokens ? 0.0f : (key_abs + i + 1 < p.tokens ? __ldg(src + i + 1) : -INFINITY);
+              mask_pairs[i / 2] = pack_bf16x2(m0, m1);
+            }
+          }
+        }
+      }
       ok = ok && __all_sync(0xffffffffu, mbarrier_wait_ready_first(smem_u32(&s_full[g]), j & 1));
       uint32_t s0[32], s1[32];  // this thread's half of the row of S
       __nv_bfloat16 half_max = __float2bfloat16_rn(0.0f);
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        tmem_load_32x32_issue(s_taddr, s0);
-        tmem_load_32x32_issue(s_taddr + 32, s1);
-        tmem_load_wait(s0);
-        tmem_load_wait(s1);
+        if (MASKED) {
+          // scores to the log2 domain, mask added, one half at a time (registers)
+          tmem_load_32x32_issue(s_taddr, s0);
+          tmem_load_wait(s0);
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float m0 = add_mask ? bf16_lo(mask_pairs[i / 2]) * kLog2e : 0.0f;
+            const float m1 = add_mask ? bf16_hi(mask_pairs[i / 2]) * kLog2e : 0.0f;
+            s0[i] = __float_as_uint(fmaf(__uint_as_float(s0[i]), p.scale_log2, m0));
+            s0[i + 1] = __float_as_uint(fmaf(__uint_as_float(s0[i + 1]), p.scale_log2, m1));
+          }
+          tmem_load_32x32_issue(s_taddr + 32, s1);
+          tmem_load_wait(s1);
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float m0 = add_mask ? bf16_lo(mask_pairs[16 + i / 2]) * kLog2e : 0.0f;
+            const float m1 = add_mask ? bf16_hi(mask_pairs[16 + i / 2]) * kLog2e : 0.0f;
+            s1[i] = __float_as_uint(fmaf(__uint_as_float(s1[i]), p.scale_log2, m0));
+            s1[i + 1] = __float_as_uint(fmaf(__uint_as_float(s1[i + 1]), p.scale_log2, m1));
+          }
+        } else {
+          tmem_load_32x32_issue(s_taddr, s0);
+          tmem_load_32x32_issue(s_taddr + 32, s1);
+          tmem_load_wait(s0);
+          tmem_load_wait(s1);
+        }
         // S is free for the product with the next key tile
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
@@ -291,7 +411,7 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
           else
             failed = 1;
         }
-        if (j == q_tile) {  // diagonal tile: keys beyond the row's own position are masked
+        if (!MASKED && j == q_tile) {  // diagonal tile: keys beyond the row's own position are masked
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             if (key0 + i > row) s0[i] = 0xff800000u;
@@ -313,8 +433,10 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
       // near the maximum, not equal to it.
       row_max_slot[j & 1][g][half][row] = half_max;
       asm volatile("bar.sync %0, 256;" ::"r"(group_barrier) : "memory");
+      // (MASKED scores are in the log2 domain already)
       const float m_tile = fmaxf(__bfloat162float(half_max),
-                                 __bfloat162float(row_max_slot[j & 1][g][half ^ 1][row])) * p.scale_log2;
+                                 __bfloat162float(row_max_slot[j & 1][g][half ^ 1][row])) *
+                           (MASKED ? 1.0f : p.scale_log2);
       if (ok && j == 0) m_ref = m_tile;  // O is still empty: the first product overwrites it
       if (ok && j > 0) {
         const bool raise = __any_sync(0xffffffffu, m_tile > m_ref + kRescaleThreshold);
@@ -323,7 +445,8 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
         if (ok && raise) {  // warp-uniform: move the reference maximum of the warp's rows
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const float m_new = fmaxf(m_ref, m_tile);
-          const float factor = exp2_fast(m_ref - m_new);
+          // (a row that has seen only -inf so far holds O = 0 and sum 0: any factor keeps them)
+          const float factor = m_ref == -INFINITY ? 0.0f : exp2_fast(m_ref - m_new);
           l_run *= factor;
           m_ref = m_new;
 #pragma unroll
@@ -338,14 +461,16 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
         }
       }
       if (!ok) continue;
-      const float neg_ref = -m_ref;
+      // (a reference of -inf, every key so far masked, must not turn -inf - -inf into NaN)
+      const float neg_ref = MASKED && m_ref == -INFINITY ? 0.0f : -m_ref;
+      const float to_log2 = MASKED ? 1.0f : p.scale_log2;
       float sum0 = 0.0f, sum1 = 0.0f;
       auto emit = [&](const uint32_t (&s)[32], int c0) {  // 32 probabilities: exp2, sum, bf16, store
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = exp2_fast(fmaf(__uint_as_float(s[i]), p.scale_log2, neg_ref));
-          const float p1 = exp2_fast(fmaf(__uint_as_float(s[i + 1]), p.scale_log2, neg_ref));
+          const float p0 = exp2_fast(fmaf(__uint_as_float(s[i]), to_log2, neg_ref));
+          const float p1 = exp2_fast(fmaf(__uint_as_float(s[i + 1]), to_log2, neg_ref));
           sum0 += p0;
           sum1 += p1;
           packed[i / 2] = pack_bf16x2(p0, p1);
@@ -419,14 +544,25 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
 
 }  // namespace
 
-// Called by b200_prefill_attention for causal-proved bf16 calls in the fast mode. Returns
-// B200_ERR_UNSUPPORTED when this path does not apply (head_dim, strides that no tensor map can
-// describe, B200_PREFILL_ATTENTION_PATH=mma.sync): the caller then uses the warp-level kernel.
+// Bytes of tile classes the masked variant needs in the caller's workspace.
+int64_t prefill_attention_tcgen05_workspace_bytes(int64_t batch, int64_t tokens) {
+  const int64_t tiles = ceil_div(tokens, static_cast<int64_t>(kTile));
+  return (batch * tiles * tiles + 255) / 256 * 256;
+}
+
+// Called by b200_prefill_attention for bf16 calls in the fast mode: causal-proved (mask ==
+// nullptr), or with an additive fp32 mask whose last dimension is contiguous (mask_strides in
+// elements; a batch stride of 0 is one mask for every sequence), in which case `workspace` must
+// hold prefill_attention_tcgen05_workspace_bytes(batch, tokens). Returns B200_ERR_UNSUPPORTED
+// when this path does not apply (head_dim, strides that no tensor map can describe, a mask
+// layout without 16-byte rows, B200_PREFILL_ATTENTION_PATH=mma.sync): the caller then uses the
+// warp-level kernel.
 int prefill_attention_tcgen05(const void* query, const void* key, const void* value, void* output,
                               int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t tokens,
                               int64_t head_dim, const int64_t query_strides[4],
                               const int64_t key_strides[4], const int64_t value_strides[4],
-                              double scale, int32_t* status, cudaStream_t stream) {
+                              double scale, int32_t* status, cudaStream_t stream, const void* mask,
+                              const int64_t* mask_strides, void* workspace, int64_t workspace_bytes) {
   if ((launch_mode() & B200_LAUNCH_PREFILL_WARP_LEVEL) != 0) return B200_ERR_UNSUPPORTED;
   const char* path = getenv("B200_PREFILL_ATTENTION_PATH");
   if (path != nullptr && strcmp(path, "mma.sync") == 0) return B200_ERR_UNSUPPORTED;
@@ -434,6 +570,14 @@ int prefill_attention_tcgen05(const void* query, const void* key, const void* va
   if (!(scale > 0.0) || tokens < 1) return B200_ERR_UNSUPPORTED;
   const int64_t q_blocks = ceil_div(tokens, static_cast<int64_t>(kTile) * kGroups);
   if (q_blocks > 65535 || batch > 65535) return B200_ERR_UNSUPPORTED;
+  const int64_t tiles = ceil_div(tokens, static_cast<int64_t>(kTile));
+  if (mask != nullptr) {
+    if (mask_strides == nullptr || mask_strides[3] != 1 || mask_strides[0] % 4 != 0 ||
+        mask_strides[2] % 4 != 0 || !aligned16(mask) || tiles > 65535)
+      return B200_ERR_UNSUPPORTED;
+    if (workspace == nullptr || workspace_bytes < prefill_attention_tcgen05_workspace_bytes(batch, tokens))
+      return B200_ERR_WORKSPACE;
+  }
   CUtensorMap q_map, k_map, v_map;
   bool q_dim1, k_dim1, v_dim1;
   if (!make_bf16_bhtd_map(&q_map, query, batch, q_heads, tokens, head_dim, query_strides[0],
@@ -453,6 +597,18 @@ int prefill_attention_tcgen05(const void* query, const void* key, const void* va
   p.k_token_dim1 = k_dim1 ? 1 : 0;
   p.v_token_dim1 = v_dim1 ? 1 : 0;
   p.scale_log2 = static_cast<float>(scale) * kLog2e;
+  if (mask != nullptr) {
+    const int64_t distinct = mask_strides[0] == 0 ? 1 : batch;  // one mask for all: classified once
+    p.mask = static_cast<const float*>(mask);
+    p.mask_stride_b = mask_strides[0];
+    p.mask_stride_q = mask_strides[2];
+    p.tile_class = static_cast<const uint8_t*>(workspace);
+    p.class_stride_b = mask_strides[0] == 0 ? 0 : tiles * tiles;
+    mask_tile_class_kernel<<<dim3(static_cast<unsigned>(tiles), static_cast<unsigned>(tiles),
+                                  static_cast<unsigned>(distinct)), 256, 0, stream>>>(
+        p.mask, p.mask_stride_b, p.mask_stride_q, p.tokens, static_cast<int>(tiles),
+        static_cast<uint8_t*>(workspace));
+  }
   dim3 grid(static_cast<unsigned>(q_heads), static_cast<unsigned>(batch), static_cast<unsigned>(q_blocks));
   const int tile_bytes = static_cast<int>(head_dim) * kTile * 2;
   const int v_stages = head_dim == 64 ? 2 : 1;
@@ -464,8 +620,13 @@ int prefill_attention_tcgen05(const void* query, const void* key, const void* va
     kernel<<<grid, kThreads, smem, stream>>>(p, q_map, k_map, v_map);
     return true;
   };
-  const bool launched = head_dim == 64 ? launch(prefill_attention_tcgen05_kernel<64>)
-                                       : launch(prefill_attention_tcgen05_kernel<128>);
+  bool launched;
+  if (mask != nullptr)
+    launched = head_dim == 64 ? launch(prefill_attention_tcgen05_kernel<64, true>)
+                              : launch(prefill_attention_tcgen05_kernel<128, true>);
+  else
+    launched = head_dim == 64 ? launch(prefill_attention_tcgen05_kernel<64, false>)
+                              : launch(prefill_attention_tcgen05_kernel<128, false>);
   if (!launched) return B200_ERR_LAUNCH;
   return launch_status();
 }

@@ -17,7 +17,7 @@ and the decision record, and generalises them to the operators whose B200 kernel
 Profile rows: {"op": ..., <key fields>, <bucket field>, "variants_us": {variant: microseconds}}.
 A reference RMSNorm row ({"rows", "hidden_size", "dtype", "native_eager_us", "triton_us",
 "inductor_us"?}) is read as op "rms_norm" with variants native / triton / inductor.
-`python llm-compiler_b200/microbench.py profile` measures such a file on the GPU.
+`python llm-compiler_b200/profile_dispatch.py` measures such a file on the GPU.
 """
 
 from __future__ import annotations
@@ -158,7 +158,7 @@ class DispatchCostModel:
 
     @classmethod
     def packaged(cls) -> "DispatchCostModel":
-        """The profile measured on a B200 with `microbench.py profile` that ships with the package."""
+        """The profile measured on a B200 with `profile_dispatch.py` that ships with the package."""
 
         return cls.load(Path(__file__).resolve().parent / "dispatch_profile_b200.json")
 

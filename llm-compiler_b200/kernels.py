@@ -643,12 +643,18 @@ def b200_prefill_attention(query: torch.Tensor, key: torch.Tensor, value: torch.
     value = value if value.stride(3) == 1 else _dense(value)
     storage = torch.empty((batch, tokens, q_heads, dim), dtype=query.dtype, device=device)
     rt = runtime(device)
-    code = _lib.load().b200_prefill_attention(
+    library = _lib.load()
+    need = 0
+    if attention_mask is not None and not causal and query.dtype == torch.bfloat16:
+        need = int(library.b200_prefill_attention_workspace_bytes(batch, tokens))  # mask tile classes
+    workspace = rt.workspace("prefill_attention", need)
+    code = library.b200_prefill_attention(
         query.data_ptr(), key.data_ptr(), value.data_ptr(), _ptr(attention_mask),
         storage.data_ptr(), batch, q_heads, kv_heads, tokens, dim,
         _lib.i64_array(query.stride()), _lib.i64_array(key.stride()),
         _lib.i64_array(value.stride()), mask_strides, mask_code, float(scale), int(bool(causal)),
-        _code(query.dtype), _mode(numerical_mode), rt.status.data_ptr(), _stream())
+        _code(query.dtype), _mode(numerical_mode), _ptr(workspace), need, rt.status.data_ptr(),
+        _stream())
     _check(code, "b200_prefill_attention")
     _count(rt)
     return storage.transpose(1, 2)

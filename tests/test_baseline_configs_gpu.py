@@ -142,7 +142,7 @@ def test_prefill_attention_rope_store_then_decode_append(batch, tokens):
     causal = b200.b200_prefill_attention(q_rot, k_rot, v, None, scale=0.125, causal=True)
     mask = serve_ops.causal_mask(1, tokens).cuda().expand(batch, 1, tokens, tokens)
     masked = b200.b200_prefill_attention(q_rot, k_rot, v, mask, scale=0.125)
-    close(masked, causal, 8e-3)
+    close(masked, causal)  # two kernels, each within the tolerance of the oracle below
     if tokens < 4096 or batch == 1:
         blocks = [(0, tokens)]
     else:

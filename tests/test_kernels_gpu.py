@@ -850,3 +850,84 @@ def test_fused_attention_applies_the_folded_norm():
     close(k_dev, k_gold, BF16_TOL)
     close(v_dev, v_gold, BF16_TOL)
     kernels.runtime().check_status()
+
+
+# ------------------------------ prefill attention: the additive-mask contract on tcgen05 ----
+def _mask_case(kind, batch, tokens, generator):
+    """Additive fp32 masks B x 1 x T x T of the kinds serving meets."""
+    index = torch.arange(tokens)
+    future = index.view(1, -1) > index.view(-1, 1)
+    mask = torch.zeros(batch, 1, tokens, tokens)
+    if kind == "causal":
+        mask.masked_fill_(future, float("-inf"))
+    elif kind == "sliding_window":  # causal, and at most 200 keys back: -inf tiles at both ends
+        mask.masked_fill_(future | (index.view(1, -1) < index.view(-1, 1) - 200), float("-inf"))
+    elif kind == "padded":  # causal + the last keys of every second sequence are padding
+        mask.masked_fill_(future, float("-inf"))
+        for b in range(0, batch, 2):
+            mask[b, :, :, tokens - tokens // 3:] = float("-inf")  # rows past that point: all keys masked
+    elif kind == "soft":  # arbitrary finite biases everywhere, no structure
+        mask = torch.randn(batch, 1, tokens, tokens, generator=generator)
+    elif kind == "soft_causal":
+        mask = (0.5 * torch.randn(batch, 1, tokens, tokens, generator=generator)).masked_fill(
+            future, float("-inf"))
+    elif kind == "empty_rows":  # causal; the last 50 query rows of sequence 0 see no key at all
+        mask.masked_fill_(future, float("-inf"))
+        mask[0, :, tokens - 50:, :] = float("-inf")
+    elif kind == "zero":
+        pass
+    else:
+        raise AssertionError(kind)
+    return mask
+
+
+@pytest.mark.parametrize("kind", ["causal", "sliding_window", "padded", "soft", "soft_causal", "zero",
+                                  "empty_rows"])
+@pytest.mark.parametrize("batch,tokens,hq,hkv,d", [(2, 300, 14, 2, 64), (1, 1100, 14, 2, 64),
+                                                   (2, 257, 8, 4, 128), (3, 128, 4, 2, 64)])
+def test_prefill_attention_masked_tensor_memory_path(kind, batch, tokens, hq, hkv, d, monkeypatch):
+    """The reference's contract (any additive B x 1 x T x T mask) on the tcgen05 kernel with its
+    mask-tile pre-pass, against the oracle and against the warp-level kernel; rows whose keys are
+    all masked are NaN in both, as in the reference."""
+    g = torch.Generator().manual_seed(tokens + d + len(kind))
+    q = torch.randn(batch, tokens, hq, d, generator=g).bfloat16().transpose(1, 2)
+    k = torch.randn(batch, tokens, hkv, d, generator=g).bfloat16().transpose(1, 2)
+    v = torch.randn(batch, tokens, hkv, d, generator=g).bfloat16().transpose(1, 2)
+    mask = _mask_case(kind, batch, tokens, g)
+    ref = serve_ops.prefill_attention(q, k, v, mask, groups=hq // hkv, scale=d ** -0.5)
+    out = b200.b200_prefill_attention(q.cuda(), k.cuda(), v.cuda(), mask.cuda(), scale=d ** -0.5)
+    with kernels.kernel_variants(prefill_attention="mma.sync"):
+        warp = b200.b200_prefill_attention(q.cuda(), k.cuda(), v.cuda(), mask.cuda(), scale=d ** -0.5)
+    if kind == "empty_rows":
+        # Exactly the rows without a visible key are NaN (softmax over nothing, execution.py:733-739).
+        # (The CPU matmul behind the oracle lets the NaN probabilities of row T - 50 leak into
+        # the row before it, so that one row is left out of the comparison.)
+        assert torch.isnan(ref[0, :, -50:]).all()
+        for result in (out, warp):
+            assert torch.isnan(result[0, :, -50:]).all()
+            assert not torch.isnan(result[0, :, :tokens - 50]).any() and not torch.isnan(result[1:]).any()
+            close(result[0, :, :tokens - 51], ref[0, :, :tokens - 51], BF16_TOL)
+            if batch > 1:
+                close(result[1:], ref[1:], BF16_TOL)
+    else:
+        close(out, ref, BF16_TOL)
+        close(warp, ref, BF16_TOL)
+    # one mask for every sequence (batch stride 0) is classified once
+    if kind in ("causal", "sliding_window"):
+        shared = mask[:1].cuda().expand(batch, 1, tokens, tokens)
+        close(b200.b200_prefill_attention(q.cuda(), k.cuda(), v.cuda(), shared, scale=d ** -0.5), ref,
+              BF16_TOL)
+    kernels.runtime().check_status()
+
+
+def test_prefill_attention_masked_strided_mask_falls_back():
+    """A mask whose rows are not 16-byte aligned cannot take the vector path: it still works."""
+    g = torch.Generator().manual_seed(9)
+    batch, tokens, hq, hkv, d = 1, 130, 4, 2, 64
+    q = torch.randn(batch, tokens, hq, d, generator=g).bfloat16().transpose(1, 2)
+    k = torch.randn(batch, tokens, hkv, d, generator=g).bfloat16().transpose(1, 2)
+    v = torch.randn(batch, tokens, hkv, d, generator=g).bfloat16().transpose(1, 2)
+    wide = torch.randn(batch, 1, tokens, tokens + 1, generator=g).cuda()
+    mask = wide[..., 1:]  # row stride T + 1, first element off by 4 bytes
+    ref = serve_ops.prefill_attention(q, k, v, mask.cpu(), groups=2, scale=0.125)
+    close(b200.b200_prefill_attention(q.cuda(), k.cuda(), v.cuda(), mask, scale=0.125), ref, BF16_TOL)
