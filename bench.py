@@ -92,6 +92,9 @@ def parse_args():
     parser.add_argument("--context-min", type=int, default=-1,
                         help="with --context-source synthetic: per-sequence contexts uniform in "
                              "[context-min, context] instead of all at --context")
+    parser.add_argument("--path", default="engine", choices=["engine", "executor"],
+                        help="engine: Qwen2Engine; executor: the reference-compiled KernelIR of the "
+                             "decode step (tests/golden) through lower_to_b200 + B200Executor")
     parser.add_argument("--min-seconds", type=float, default=MIN_TIMED_SECONDS,
                         help="repeat the K timed steps until this much device time is measured")
     args = parser.parse_args()
@@ -357,6 +360,79 @@ def oracle_step_parity(engine, config, weights, rows=(0, 1)):
             "within_2e-2": diff <= 2e-2}
 
 
+class ExecutorStepper:
+    """The drop-in path as a decode loop: the reference's own KernelIR of the Qwen2-0.5B decode
+    step (exported and compiled by the reference, shipped as tests/golden/...json.gz), finished
+    by lower_to_b200 and interpreted by B200Executor over the engine's KV state, with the greedy
+    token pick and the position update, all captured in one CUDA graph. Same interface as the
+    part of Qwen2Engine the benchmark uses."""
+
+    def __init__(self, engine, weights):
+        import gzip
+
+        from llm_compiler_b200 import kernel_ir, kernels
+        from llm_compiler_b200.executor import B200Executor, bind_arguments
+        from llm_compiler_b200.kv_state import PreallocatedKVCacheState
+
+        self.engine, self.kernels = engine, kernels
+        path = REPO / "tests" / "golden" / "kernel_ir_qwen2_0_5b_decode_fast.json.gz"
+        self.module = kernel_ir.module_from_json(json.loads(gzip.open(path).read()))
+        self.report = kernel_ir.lower_to_b200(self.module, zero_mask_arguments=("attention_mask",))
+        kernel_ir.require_full_lowering(self.module)
+        self.executor = B200Executor(strict=True)
+        batch, device = engine.batch, engine.device
+        layers = engine.config.num_layers
+        # the engine's arena, seen as the state object the graph takes (slot lengths only)
+        self.state = PreallocatedKVCacheState(engine.state.keys, engine.state.values,
+                                              engine.state.lengths, engine.state.capacity)
+        object.__setattr__(self.state, "_length_arena", engine.state._length_arena[:layers])
+        self.ids = torch.zeros(batch, 1, dtype=torch.int64, device=device)
+        self.positions = torch.zeros(batch, 1, dtype=torch.int64, device=device)
+        self.mask = torch.zeros(batch, 1, 1, engine.capacity, device=device)
+        self.next_ids = torch.zeros(batch, dtype=torch.int64, device=device)
+        self.arguments = bind_arguments(self.module.functions[0], weights, {
+            "input_ids": self.ids, "attention_mask": self.mask, "position_ids": self.positions,
+            "kv_state": self.state, "inv_freq": engine.inv_freq})
+        self.graph = None
+        self.kernels_per_step = 0
+
+    def _step(self):
+        before = self.kernels.launch_count(self.engine.device)
+        with self.kernels.launch_mode(programmatic=True, constant_weights=True, stable_kv_prefix=True):
+            logits, _ = self.executor.run(self.module, self.arguments).outputs
+        self.logits = logits
+        self.kernels.b200_argmax(logits.view(self.engine.batch, -1), self.next_ids)
+        self.ids.view(-1).copy_(self.next_ids)
+        self.kernels.b200_advance_lengths(self.positions.view(-1), 1, self.engine.capacity)
+        self.kernels_per_step = self.kernels.launch_count(self.engine.device) - before
+
+    def sync_from_engine(self):
+        self.ids.view(-1).copy_(self.engine.input_ids)
+        self.positions.view(-1).copy_(self.engine.positions)
+
+    def capture(self):
+        saved = self.engine.state._length_arena.clone()
+        self.sync_from_engine()
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            self._step()  # sizes workspaces, prepares the packed / folded weights
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        self.engine.state._length_arena.copy_(saved)
+        self.sync_from_engine()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._step()
+        self.graph = graph
+        self.engine.state._length_arena.copy_(saved)
+        self.sync_from_engine()
+
+    def decode_step(self):
+        self.graph.replay()
+        return self.next_ids
+
+
 def serving_contexts(args):
     """The serving configuration's per-sequence context lengths (seeded, the same on every rank)."""
 
@@ -453,6 +529,25 @@ def b200_arm(args, config):
     parity = None
     if rank == 0 and not args.skip_parity:
         parity = oracle_step_parity(engine, config, weights)
+    stepper = None
+    if args.path == "executor":
+        if args.model != "qwen2-0.5b" or args.layers:
+            raise SystemExit("--path executor runs the shipped Qwen2-0.5B decode graph")
+        stepper = ExecutorStepper(engine, weights)
+        stepper.capture()
+        # the same step through both paths from the same state: they launch the same kernels
+        saved = engine.state._length_arena.clone()
+        engine.decode_step(feed_back=False)
+        engine_logits, engine_tokens = engine.logits.float().clone(), engine.next_ids.clone()
+        engine.state._length_arena.copy_(saved)
+        stepper.sync_from_engine()
+        stepper.decode_step()
+        difference = float((stepper.logits.view(batch, -1).float() - engine_logits.view(batch, -1)).abs().max())
+        if parity is not None:
+            parity["executor_vs_engine_max_abs_logit_diff"] = difference
+            parity["executor_vs_engine_tokens_equal"] = bool(torch.equal(stepper.next_ids, engine_tokens))
+        engine.state._length_arena.copy_(saved)
+        stepper.sync_from_engine()
     step_tokens_read = sum(int(part.sum()) + len(part) for part in batches)  # KV rows read per global step
     global_batch = batch * len(batches) * world
     server = ReplicaServer(engine, batch * world, failure_timeout_s=60.0) if world > 1 else None
@@ -467,7 +562,10 @@ def b200_arm(args, config):
     def run_steps(count):
         pending = None
         for _ in range(count):
-            tokens = engine.decode_step() if server is None else server.local_step()
+            if stepper is not None:
+                tokens = stepper.decode_step()
+            else:
+                tokens = engine.decode_step() if server is None else server.local_step()
             if server is not None:
                 if pending is not None:
                     pending.wait()
@@ -498,6 +596,8 @@ def b200_arm(args, config):
                 fill_context(part, rank * 16 + index)
             elif saved_lengths[0] is not None:
                 engine.state._length_arena.copy_(saved_lengths[0])
+                if stepper is not None:
+                    stepper.sync_from_engine()
             if saved_lengths[index] is None:
                 saved_lengths[index] = engine.state._length_arena.clone()
             run_steps(3 if len(batches) > 1 else 0)  # (a refilled sub-batch warms up again)
@@ -519,8 +619,19 @@ def b200_arm(args, config):
         # there are several ranks, D2H tokens, every step
         engine.state._length_arena.copy_(saved_lengths[-1])
         host_ids = engine.next_ids.cpu()
+        if stepper is not None:
+            stepper.sync_from_engine()
+            pinned_in = torch.zeros(batch, dtype=torch.int64).pin_memory()
+            pinned_out = torch.zeros(batch, dtype=torch.int64).pin_memory()
 
         def host_step(ids):
+            if stepper is not None:  # host ids in, graph replay, host tokens out
+                pinned_in.copy_(ids)
+                stepper.ids.view(-1).copy_(pinned_in, non_blocking=True)
+                stepper.decode_step()
+                pinned_out.copy_(stepper.next_ids, non_blocking=True)
+                torch.cuda.current_stream().synchronize()
+                return pinned_out
             tokens = engine.step(ids)
             if server is not None:
                 server.gather_host(engine.next_ids)
@@ -576,8 +687,9 @@ def b200_arm(args, config):
         "e2e": {"value": total_tokens / e2e_s, "unit": UNIT,
                 "h2d_bytes_per_step": batch * 8 * len(batches), "d2h_bytes_per_step": batch * 8 * len(batches),
                 "ms_per_step": e2e_s / steps * 1e3},
-        "gpu_launches": engine.kernels_per_step * steps * len(batches),
-        "kernels_per_step": engine.kernels_per_step * len(batches),
+        "path": args.path,
+        "gpu_launches": (stepper or engine).kernels_per_step * steps * len(batches),
+        "kernels_per_step": (stepper or engine).kernels_per_step * len(batches),
         "dispatch": None if decision is None else {
             "op": "decode_attention", "variant": decision.variant, "source": decision.source,
             "profile_value": decision.profile_value},

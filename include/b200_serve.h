@@ -279,13 +279,15 @@ int b200_reduce_rope_kv_store(const void* partials, int64_t splits, const void* 
  * also reduces that token's K and V, stores them into the buffers and lets them join the
  * softmax from registers, so no CTA reads a row another one is writing. No mask (causal
  * decode), fast numerical mode, bf16, head_dim 64 or 128. cosine / sine: B x D. Workspace as
- * for b200_decode_attention. lengths[b] < 1 sets B200_STATUS_BAD_POSITION (nothing stored). */
+ * for b200_decode_attention. lengths[b] < 1 sets B200_STATUS_BAD_POSITION (nothing stored).
+ * length_offset 1: lengths[] still hold the lengths before the new token (serve.kv.advance of
+ * every slot is deferred to one launch at the end of the step); the kernel adds 1 itself. */
 int b200_qkv_decode_attention(const void* qkv_partials, int64_t qkv_splits, const void* qkv_bias,
                               const void* cosine, const void* sine, void* key_buffer,
                               void* value_buffer, const int64_t* lengths, void* output,
                               int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
                               int64_t capacity, int64_t mask_len, double scale,
-                              int64_t split_tokens, int64_t max_length_hint,
+                              int64_t split_tokens, int64_t max_length_hint, int64_t length_offset,
                               const void* norm_row_squares, int64_t norm_hidden, double norm_epsilon,
                               void* workspace, int64_t workspace_bytes, int32_t* status,
                               void* stream);

@@ -82,8 +82,9 @@ SIGNATURES = {
     "b200_reduce_rope_kv_store": (c_int, [c_void_p, c_int64] + [c_void_p] * 7 + [c_int64] * 5 +
                                   [c_void_p, c_void_p]),
     "b200_qkv_decode_attention": (c_int, [c_void_p, c_int64] + [c_void_p] * 7 +
-                                  [c_int64] * 6 + [c_double, c_int64, c_int64, c_void_p, c_int64,
-                                                   c_double, c_void_p, c_int64, c_void_p, c_void_p]),
+                                  [c_int64] * 6 + [c_double, c_int64, c_int64, c_int64, c_void_p,
+                                                   c_int64, c_double, c_void_p, c_int64, c_void_p,
+                                                   c_void_p]),
     "b200_scale_columns": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "b200_linear_rms_input": (c_int, [c_void_p] * 4 + [c_int64] * 4 + [c_double, c_int, c_void_p,
                                                                        c_void_p]),

@@ -448,7 +448,89 @@ def _pack(c: _Check) -> None:
         c.fail("interleaves exactly two matrices of one shape")
 
 
+def _norm_linear(c: _Check) -> None:
+    op = c.operation
+    has_bias = bool(op.attributes.get("has_bias"))
+    if len(op.operands) != 4 + int(has_bias) or len(op.results) != 1:
+        c.fail("takes input, norm weight, weight, folded weight, optional bias and returns one tensor")
+        return
+    types = c.tensors(list(op.operands) + list(op.results), "operands and result")
+    if types is None:
+        return
+    input_t, norm_t, weight_t, folded_t, result_t = types[0], types[1], types[2], types[3], types[-1]
+    epilogue = op.attributes.get("epilogue") or "none"
+    if epilogue not in ("none", "swiglu"):
+        c.fail("the epilogue must be none or swiglu")
+    if weight_t.rank != 2 or folded_t != weight_t:
+        c.fail("the folded weight must have the weight's N x K type")
+        return
+    n, k = weight_t.shape
+    if norm_t.shape != (k,) or input_t.shape[-1] != k:
+        c.fail("the norm weight and the input's last dimension must equal the weight's K")
+    out = n // 2 if epilogue == "swiglu" and isinstance(n, int) else n
+    if result_t.shape != input_t.shape[:-1] + (out,):
+        c.fail("the result must be the input's leading dimensions x N (N / 2 with SwiGLU)")
+    if has_bias and types[4].shape != (n,):
+        c.fail("the bias must be a vector of N elements")
+    epsilon = op.attributes.get("epsilon")
+    if not isinstance(epsilon, (int, float)) or isinstance(epsilon, bool) or float(epsilon) < 0:
+        c.fail("epsilon must be a non-negative number")
+    if not _same(input_t, norm_t, weight_t, result_t):
+        c.fail("input, norm weight, weight and result must share one dtype")
+
+
+def _qkv_decode_attention(c: _Check) -> None:
+    op = c.operation
+    attributes = op.attributes
+    has_bias = bool(attributes.get("has_bias"))
+    if len(op.operands) != 8 + int(has_bias) or len(op.results) != 2:
+        c.fail("takes state, input, norm weight, weight, folded weight, optional bias, cosine, sine, "
+               "mask and returns the context and the state")
+        return
+    state = c.state(op.operands[0])
+    types = c.tensors(list(op.operands[1:]) + [op.results[0]], "tensor operands and the context")
+    if state is None or types is None:
+        return
+    c.slot(state)
+    input_t, norm_t, weight_t, context = types[0], types[1], types[2], types[-1]
+    q_heads, kv_heads, dim = (attributes.get(name) for name in ("q_heads", "kv_heads", "head_dim"))
+    if not all(isinstance(value, int) and value > 0 for value in (q_heads, kv_heads, dim)):
+        c.fail("q_heads, kv_heads and head_dim must be positive integers")
+        return
+    if kv_heads != state.heads or dim != state.head_dim or q_heads != kv_heads * attributes.get("groups", 0):
+        c.fail("heads / head_dim / groups do not match the KV state")
+    if weight_t.rank != 2 or weight_t.shape[0] != (q_heads + 2 * kv_heads) * dim or \
+            weight_t.shape[1] != input_t.shape[-1] or norm_t.shape != (weight_t.shape[1],):
+        c.fail("the packed q|k|v weight must be (Hq + 2 Hkv) D x K with K the input's last dimension")
+    if context.shape[-1] != q_heads * dim or context.shape[0] != input_t.shape[0]:
+        c.fail("the context must be B x 1 x (Hq D)")
+    scale = attributes.get("scale")
+    if not isinstance(scale, (int, float)) or isinstance(scale, bool) or float(scale) <= 0:
+        c.fail("scale must be a positive number")
+    if attributes.get("length_offset", 0) not in (0, 1):
+        c.fail("length_offset must be 0 or 1")
+    if not isinstance(parse_type(op.results[1].type), KVStateT):
+        c.fail("the second result must be the KV state")
+
+
+def _advance_all(c: _Check) -> None:
+    op = c.operation
+    state = c.state(op.operands[0]) if op.operands else None
+    if state is None:
+        return
+    delta, slots = op.attributes.get("delta", 1), op.attributes.get("slots", state.layers)
+    if not isinstance(delta, int) or delta <= 0:
+        c.fail("delta must be a positive integer")
+    if not isinstance(slots, int) or slots <= 0 or (state.layers and slots > state.layers):
+        c.fail("slots must lie in 1 .. the state's layers")
+
+
 _CONTRACTS = {
+    "kernel.b200.norm_linear": _norm_linear,
+    "kernel.b200.qkv_decode_attention": _qkv_decode_attention,
+    "runtime.kv.advance_all": _advance_all,
+    "kernel.b200.scale_columns": lambda c: None if len(c.operation.operands) == 2 else c.fail(
+        "takes the weight and the column scales"),
     "kernel.b200.linear": _linear,
     "kernel.b200.prefill_attention": _prefill_attention,
     "kernel.b200.decode_attention": _decode_attention,

@@ -72,6 +72,9 @@ struct DecodeParams {
   // projection weights, norm_row_squares[qkv_splits, B] holds sum(x_b^2) per K slice; the
   // reduced sums are scaled by rsqrt(mean(x_b^2) + norm_eps) before the bias.
   const float* norm_row_squares = nullptr;
+  // Fused form: lengths[] may still hold the lengths BEFORE the new token (the caller advances
+  // every slot once at the end of the step): the attention length is lengths[b] + length_bias.
+  int length_bias = 0;
   int norm_hidden = 0;
   float norm_eps = 0.0f;
 };
@@ -485,7 +488,7 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
     grid_dependency_wait();  // lengths, q and the newest KV row come from kernels before this one
     trace.mark(0);
   }
-  int64_t len = p.lengths[b];
+  int64_t len = p.lengths[b] + p.length_bias;
   if (len > p.mask_len) {
     if (threadIdx.x == 0 && split == 0 && head_block == 0 && p.status != nullptr)
       atomicOr(p.status, B200_STATUS_LENGTH_OVER_MASK);
@@ -499,7 +502,7 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
   // fused: the newest row is not streamed from the buffer (its owner is writing it right now)
   const int streamed = fused ? max(n_tokens - 1, 0) : n_tokens;
   const int end = max(start, min(start + p.split_tokens, streamed));
-  const bool owner = fused && n_tokens >= 1 && p.lengths[b] <= p.mask_len &&
+  const bool owner = fused && n_tokens >= 1 && p.lengths[b] + p.length_bias <= p.mask_len &&
                      n_tokens - 1 >= start && n_tokens - 1 < start + p.split_tokens;
   if (fused && n_tokens < 1 && threadIdx.x == 0 && split == 0 && head_block == 0 && p.status != nullptr)
     atomicOr(p.status, B200_STATUS_BAD_POSITION);  // no row for the new token
@@ -1496,10 +1499,12 @@ extern "C" int b200_qkv_decode_attention(
     const void* sine, void* key_buffer, void* value_buffer, const int64_t* lengths, void* output,
     int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim, int64_t capacity,
     int64_t mask_len, double scale, int64_t split_tokens, int64_t max_length_hint,
-    const void* norm_row_squares, int64_t norm_hidden, double norm_epsilon, void* workspace,
+    int64_t length_offset, const void* norm_row_squares, int64_t norm_hidden, double norm_epsilon,
+    void* workspace,
     int64_t workspace_bytes, int32_t* status, void* stream) {
   if (norm_row_squares != nullptr && (norm_hidden <= 0 || !(norm_epsilon >= 0.0)))
     return B200_ERR_BAD_ARGUMENT;
+  if (length_offset < 0 || length_offset > 1) return B200_ERR_BAD_ARGUMENT;
   if (!qkv_partials || !cosine || !sine || !key_buffer || !value_buffer || !lengths || !output ||
       qkv_splits <= 0 || batch < 0 || q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 ||
       capacity <= 0 || mask_len <= 0 || mask_len > capacity || q_heads % kv_heads != 0 ||
@@ -1552,6 +1557,7 @@ extern "C" int b200_qkv_decode_attention(
   p.vstore = static_cast<__nv_bfloat16*>(value_buffer);
   p.qkv_splits = static_cast<int>(qkv_splits);
   p.norm_row_squares = static_cast<const float*>(norm_row_squares);
+  p.length_bias = static_cast<int>(length_offset);
   p.norm_hidden = static_cast<int>(norm_hidden);
   p.norm_eps = static_cast<float>(norm_epsilon);
   const GridPlan grid_plan = plan_grid(splits, split_tokens, batch, head_blocks);

@@ -108,6 +108,11 @@ class B200Executor:
             "kernel.b200.kv_prefill_store": self._kv_prefill_store,
             "kernel.b200.embedding": self._embedding,
             "kernel.b200.rope_kv_store": self._rope_kv_store,
+            "kernel.b200.scale_columns": lambda o, a, e: kernels.b200_scale_columns(o[0], o[1]),
+            "kernel.b200.norm_linear": self._norm_linear,
+            "kernel.b200.qkv_decode_attention": self._qkv_decode_attention,
+            "runtime.kv.advance_all": lambda o, a, e: _as_state(o[0]).advance_all(
+                delta=int(a.get("delta", 1)), slots=a.get("slots")),
             "kernel.b200.pack_rows": lambda o, a, e: kernels.b200_pack_rows(*o),
             "kernel.b200.interleave_rows": lambda o, a, e: kernels.interleave_gate_up(o[0], o[1]),
             "runtime.view.slice": self._slice,
@@ -241,10 +246,93 @@ class B200Executor:
         tensor, weight = operands[0], operands[1]
         bias = operands[2] if has_bias else None
         residual = operands[-1] if epilogue == "residual" else None
-        variant = self._decide("linear", attributes, tensor.numel() // tensor.shape[-1]) \
-            if "lowering_plan" in attributes else None
+        rows = tensor.numel() // tensor.shape[-1]
+        variant = self._decide("linear", attributes, rows) if "lowering_plan" in attributes else None
+        if epilogue == "residual" and bias is None and variant is None and \
+                tensor.dtype == torch.bfloat16 and rows <= 256 and weight.shape[0] % 4 == 0:
+            # few N tiles at decode sizes: the cluster split-K projection that adds the residual
+            # itself (same rounding points as the plain kernel's residual epilogue)
+            flat = kernels.b200_linear_splitk_residual(
+                tensor.reshape(rows, tensor.shape[-1]), weight, residual.reshape(rows, weight.shape[0]))
+            return flat.view(residual.shape)
         with kernels.kernel_variants(linear=variant):
             return kernels.b200_linear(tensor, weight, bias, residual=residual, epilogue=epilogue)
+
+    # The decode chain (fusion.fuse_norm_linear / fuse_qkv_attention): up to this many rows the
+    # folded-norm kernels run; beyond, the same ops are executed as their unfused kernels.
+    CHAIN_ROWS = 64
+
+    def _norm_linear(self, operands, attributes, environment):
+        has_bias = bool(attributes.get("has_bias"))
+        if len(operands) != 4 + int(has_bias):
+            raise ExecutionError("norm_linear takes input, norm weight, weight, folded weight and optional bias")
+        tensor, norm_weight, weight, folded = operands[:4]
+        bias = operands[4] if has_bias else None
+        epilogue = attributes.get("epilogue") or "none"
+        epsilon = float(attributes["epsilon"])
+        rows = tensor.numel() // tensor.shape[-1]
+        self.lowering_trace.append({"backend": "b200", "op": "norm_linear", "rows": rows,
+                                    "folded": rows <= self.CHAIN_ROWS})
+        if rows <= self.CHAIN_ROWS and tensor.dtype == torch.bfloat16:
+            flat = kernels.b200_linear_rms_input(tensor.reshape(rows, tensor.shape[-1]), folded, bias,
+                                                 epsilon=epsilon, epilogue=epilogue)
+            return flat.view(*tensor.shape[:-1], flat.shape[-1])
+        normed = kernels.b200_rms_norm(tensor, norm_weight, epsilon=epsilon,
+                                       round_before_weight=bool(attributes.get("round_before_weight")),
+                                       numerical_mode=attributes.get("numerical_mode", "fast"))
+        return kernels.b200_linear(normed, weight, bias, epilogue=epilogue)
+
+    def _qkv_decode_attention(self, operands, attributes, environment):
+        has_bias = bool(attributes.get("has_bias"))
+        if len(operands) != 8 + int(has_bias):
+            raise ExecutionError("qkv_decode_attention takes state, input, norm weight, weight, folded "
+                                 "weight, optional bias, cosine, sine and mask")
+        state = _as_state(operands[0])
+        tensor, norm_weight, weight, folded = operands[1:5]
+        bias = operands[5] if has_bias else None
+        cosine, sine, mask = operands[-3:]
+        slot = int(attributes.get("slot", 0))
+        q_heads, kv_heads, dim = (int(attributes[name]) for name in ("q_heads", "kv_heads", "head_dim"))
+        epsilon, scale = float(attributes["epsilon"]), float(attributes["scale"])
+        offset = int(attributes.get("length_offset", 0))
+        key_buffer, value_buffer, lengths = state._slot(slot)
+        rows = tensor.numel() // tensor.shape[-1]
+        if key_buffer.shape[0] != rows or key_buffer.shape[2] != kv_heads or key_buffer.shape[3] != dim:
+            raise ExecutionError("qkv_decode_attention: the KV state does not match batch, heads or head_dim")
+        bound = mask.shape[-1] if mask is not None else state.capacity
+        if bound > state.capacity:
+            raise ExecutionError("decode attention mask is longer than the KV capacity")
+        self.lowering_trace.append({"backend": "b200", "op": "qkv_decode_attention", "rows": rows,
+                                    "fused": rows <= self.CHAIN_ROWS, "length_offset": offset})
+        if rows <= self.CHAIN_ROWS and tensor.dtype == torch.bfloat16:
+            flat = tensor.reshape(rows, tensor.shape[-1])
+            partials, squares = kernels.b200_linear_partial(flat, folded, row_squares=True)
+            if offset == 0:  # the graph advances this slot here: lengths then count the new token
+                state = state.advance(slot, delta=1)
+            split = kernels._profiled_split_tokens(rows, q_heads, kv_heads, dim, tensor.dtype, bound)
+            context = kernels.b200_qkv_decode_attention(
+                partials, bias, cosine, sine, key_buffer, value_buffer, lengths, q_heads=q_heads,
+                scale=scale, split_tokens=split, max_length_hint=bound, length_offset=offset,
+                norm_row_squares=squares, norm_hidden=flat.shape[1], norm_epsilon=epsilon)
+            return context.view(rows, 1, q_heads * dim), state
+        # more rows than the fused kernels take: the same ops, one kernel each
+        normed = kernels.b200_rms_norm(tensor, norm_weight, epsilon=epsilon,
+                                       round_before_weight=bool(attributes.get("round_before_weight")),
+                                       numerical_mode="fast")
+        qkv = kernels.b200_linear(normed, weight, bias).view(rows, q_heads + 2 * kv_heads, dim)
+        query = kernels.b200_rope_kv_store(qkv[:, :q_heads], qkv[:, q_heads:q_heads + kv_heads],
+                                           qkv[:, q_heads + kv_heads:], cosine, sine, key_buffer,
+                                           value_buffer, lengths)
+        if offset == 0:
+            state = state.advance(slot, delta=1)
+            attention_lengths = lengths
+        else:  # the advance is deferred to the end of the step: attend over lengths + 1
+            attention_lengths = torch.empty_like(lengths)
+            attention_lengths.copy_(lengths)
+            kernels.b200_advance_lengths(attention_lengths, 1, state.capacity)
+        context = kernels.b200_decode_attention(query, key_buffer, value_buffer, attention_lengths, mask,
+                                                scale=scale, max_length_hint=bound)
+        return context.view(rows, 1, q_heads * dim), state
 
     @staticmethod
     def _rope(operands, attributes, environment):

@@ -265,3 +265,212 @@ def fuse_rope_kv_store(function) -> int:
         producers = _producer_map(function)
         fused += 1
     return fused
+
+
+# ------------------------------------------------------------- the decode chain ----
+def _single_user(users, value) -> Optional[Any]:
+    found = users.get(value.name, [])
+    return found[0] if len(found) == 1 and found[0] != "return" else None
+
+
+def fuse_norm_linear(function) -> int:
+    """rms_norm(x, w) whose only user is a bias-free or biased `kernel.b200.linear` without a
+    residual (fast mode, bf16, parameter weights that no other op reads) becomes
+    `kernel.b200.norm_linear` [x, w, W, scale_columns(W, w), bias?]: at run time, up to 64 rows,
+    ONE launch on the un-normalised rows with the norm weight folded into W's columns and the
+    row factor applied to the accumulator; beyond that the executor runs the two kernels."""
+
+    users = _users(function)
+    fused = 0
+    for norm in list(function.block.operations):
+        if norm.name != "kernel.b200.rms_norm" or _mode_of(norm) != "fast" or \
+                value_dtype(norm.results[0]) != "bf16":
+            continue
+        linear = _single_user(users, norm.results[0])
+        if linear is None or linear.name != "kernel.b200.linear" or _mode_of(linear) != "fast" or \
+                linear.operands[0].name != norm.results[0].name or \
+                (linear.attributes.get("epilogue") or "none") not in ("none", "swiglu"):
+            continue
+        weight = linear.operands[1]
+        producer = _producer_map(function).get(weight.name)
+        prepared = producer is not None and producer.attributes.get("constant") is True
+        if not (_is_parameter(function, weight) or prepared) or len(users.get(weight.name, [])) != 1 or \
+                not _is_parameter(function, norm.operands[1]):
+            continue  # (a tied LM head is also the embedding table: it keeps its own norm launch)
+        folded = Value(_fresh(function, "folded_weight"), str(weight.type))
+        prepare = Operation("kernel.b200.scale_columns", [weight, norm.operands[1]], [folded],
+                            {"constant": True, "lowered_from": "weight preparation"})
+        attributes = {key: value for key, value in linear.attributes.items()
+                      if key not in ("args", "fx_name")}
+        attributes.update({"epsilon": norm.attributes.get("epsilon"),
+                           "round_before_weight": bool(norm.attributes.get("round_before_weight", False)),
+                           "lowered_from": "kernel.b200.rms_norm+" + str(linear.attributes.get(
+                               "lowered_from", "kernel.b200.linear"))})
+        merged = Operation("kernel.b200.norm_linear",
+                           [norm.operands[0], norm.operands[1], weight, folded] + list(linear.operands[2:]),
+                           list(linear.results), attributes)
+        operations = function.block.operations
+        position = operations.index(linear)
+        operations[position:position + 1] = [prepare, merged]
+        operations.remove(norm)
+        users = _users(function)
+        fused += 1
+    return fused
+
+
+def _view_chain(users, producers, value, names):
+    """Follows `value` through single-user ops named in `names`; returns the last value."""
+    while True:
+        user = _single_user(users, value)
+        if user is None or user.name not in names or user.operands[0].name != value.name:
+            return value
+        value = user.results[0]
+
+
+def fuse_qkv_attention(function, zero_mask_arguments: Sequence[str]) -> int:
+    """One decode layer's norm_linear(q|k|v) -> slices / views / transposes -> rope_kv_store ->
+    kv.advance -> decode_attention -> transpose / reshape becomes
+    `kernel.b200.qkv_decode_attention` [state, x, norm_w, W, folded W, bias?, cos, sin, mask]
+    -> (context B x 1 x Hq D, advanced state): up to 64 rows at run time it is two launches (the
+    split-K partial products of the packed projection, then the attention kernel that reduces
+    them, applies the folded norm, bias and RoPE, stores the new K / V row and attends).
+    Only where the caller declares the decode mask all zero (`zero_mask_arguments`): the fused
+    kernel reads no mask."""
+
+    names = {name if name.startswith("%") else f"%{name}" for name in zero_mask_arguments}
+    if not names:
+        return 0
+    fused = 0
+    for attention in list(function.block.operations):
+        if attention.name != "kernel.b200.decode_attention" or _mode_of(attention) != "fast":
+            continue
+        producers = _producer_map(function)
+        users = _users(function)
+        mask = _through_casts(attention.operands[2], producers)
+        if mask.name not in names or not _is_parameter(function, mask):
+            continue
+        advance = producers.get(attention.operands[0].name)
+        store = producers.get(advance.operands[0].name) if advance is not None and \
+            advance.name == "runtime.kv.advance" and int(advance.attributes.get("delta", 1)) == 1 else None
+        if store is None or store.name != "kernel.b200.rope_kv_store" or \
+                store.results[0].name != attention.operands[1].name or \
+                len({int(op.attributes.get("slot", 0)) for op in (attention, advance, store)}) != 1 or \
+                len(users.get(store.results[0].name, [])) != 1 or \
+                len(users.get(store.results[1].name, [])) != 1 or \
+                len(users.get(advance.results[0].name, [])) < 1:
+            continue
+        # q, k, v each come from the packed projection through slice -> view -> transpose
+        sources, chain_ops = [], []
+        for operand in store.operands[1:4]:
+            value, path = operand, []
+            for expected in ("runtime.view.transpose", "runtime.view.view", "runtime.view.slice"):
+                op = producers.get(value.name)
+                if op is None or op.name != expected or len(users.get(op.results[0].name, [])) != 1:
+                    path = None
+                    break
+                path.append(op)
+                value = op.operands[0]
+            if path is None:
+                break
+            sources.append(value)
+            chain_ops.extend(path)
+        if len(sources) != 3 or len({value.name for value in sources}) != 1:
+            continue
+        projection = producers.get(sources[0].name)
+        if projection is None or projection.name != "kernel.b200.norm_linear" or \
+                projection.attributes.get("epilogue") or "packed" not in projection.attributes or \
+                len(users.get(projection.results[0].name, [])) != 3 or \
+                value_dtype(projection.results[0]) != "bf16":
+            continue
+        offsets = [decode_attribute_static(op.attributes["args"]) for op in chain_ops
+                   if op.name == "runtime.view.slice"]
+        widths = projection.attributes["packed"]
+        expected_offsets = [(0, widths[0]), (widths[0], widths[0] + widths[1]),
+                            (widths[0] + widths[1], sum(widths))]
+        if [tuple(item[2:4]) for item in offsets] != expected_offsets:
+            continue
+        # the context leaves as B x 1 x (Hq D) through transpose(1, 2) + reshape
+        context = attention.results[0]
+        transpose = _single_user(users, context)
+        reshape = _single_user(users, transpose.results[0]) if transpose is not None and \
+            transpose.name == "runtime.view.transpose" else None
+        if reshape is None or reshape.name not in ("runtime.view.reshape", "runtime.view.view"):
+            continue
+        head_dim = store.attributes.get("head_dim")
+        q_heads = _static_extent(store.operands[1], 1)
+        kv_heads = _static_extent(store.operands[2], 1)
+        if not isinstance(head_dim, int) or q_heads is None or kv_heads is None or \
+                widths != [q_heads * head_dim, kv_heads * head_dim, kv_heads * head_dim]:
+            continue
+        attributes = {
+            "slot": int(attention.attributes.get("slot", 0)), "groups": attention.attributes["groups"],
+            "scale": attention.attributes["scale"], "head_dim": head_dim, "q_heads": q_heads,
+            "kv_heads": kv_heads, "has_bias": bool(projection.attributes.get("has_bias")),
+            "epsilon": projection.attributes.get("epsilon"),
+            "round_before_weight": projection.attributes.get("round_before_weight", False),
+            "input_features": projection.attributes.get("input_features"),
+            "output_features": projection.attributes.get("output_features"),
+            "numerical_mode": "fast", "length_offset": 0, "zero_mask": mask.name,
+            "lowered_from": "kernel.b200.norm_linear+kernel.b200.rope_kv_store+runtime.kv.advance+"
+                            "kernel.b200.decode_attention",
+        }
+        merged = Operation(
+            "kernel.b200.qkv_decode_attention",
+            [store.operands[0]] + list(projection.operands) + [store.operands[4], store.operands[5],
+                                                               attention.operands[2]],
+            [reshape.results[0], advance.results[0]], attributes)
+        operations = function.block.operations
+        position = operations.index(reshape)
+        operations[position] = merged
+        for op in [projection, store, advance, attention, transpose] + chain_ops:
+            operations.remove(op)
+        fused += 1
+    return fused
+
+
+def decode_attribute_static(tree):
+    """The importer's argument tree with SSA references left as their names."""
+    if isinstance(tree, dict):
+        if set(tree) == {"ssa"}:
+            return tree["ssa"]
+        if set(tree) == {"tuple"}:
+            return tuple(decode_attribute_static(item) for item in tree["tuple"])
+        return {key: decode_attribute_static(item) for key, item in tree.items()}
+    if isinstance(tree, list):
+        return [decode_attribute_static(item) for item in tree]
+    return tree
+
+
+def hoist_kv_advances(function) -> int:
+    """When every layer slot is advanced by exactly one fused attention op, the per-slot length
+    updates move into ONE `runtime.kv.advance_all` at the end of the function (one launch over
+    the state's length arena instead of one per layer): the fused ops get `length_offset: 1`
+    (their lengths are still the ones before the new token) and hand the state on unchanged."""
+
+    fused = [op for op in function.block.operations if op.name == "kernel.b200.qkv_decode_attention"]
+    others = [op for op in function.block.operations
+              if op.name in ("runtime.kv.advance", "runtime.kv.length", "kernel.b200.decode_attention",
+                             "kernel.b200.kv_store", "kernel.b200.rope_kv_store",
+                             "kernel.b200.kv_prefill_store")]
+    if not fused or others:
+        return 0
+    slots = sorted(int(op.attributes["slot"]) for op in fused)
+    if slots != list(range(len(fused))) or any(op.attributes.get("length_offset") for op in fused):
+        return 0
+    from .contracts import KVStateT, parse_type
+
+    state_type = parse_type(fused[0].operands[0].type)
+    if not isinstance(state_type, KVStateT) or state_type.layers != len(fused):
+        return 0
+    last = max(fused, key=lambda op: function.block.operations.index(op))
+    final_state = last.results[1]
+    if not any(value is final_state or value.name == final_state.name for value in function.returns):
+        return 0
+    for op in fused:
+        op.attributes["length_offset"] = 1
+    carried = Value(_fresh(function, "kv_state_steps"), str(final_state.type))
+    last.results = [last.results[0], carried]
+    function.block.operations.append(Operation(
+        "runtime.kv.advance_all", [carried], [final_state],
+        {"delta": 1, "slots": len(fused), "lowered_from": "runtime.kv.advance x%d" % len(fused)}))
+    return len(fused)

@@ -175,7 +175,8 @@ EXECUTABLE_OPERATIONS = frozenset(_KERNEL_SOURCES.values()) | frozenset(_RUNTIME
         "kernel.b200.rope_table", "kernel.b200.swiglu",
         # produced by the graph-level fusion passes (fusion.py)
         "kernel.b200.pack_rows", "kernel.b200.interleave_rows", "runtime.view.slice",
-        "kernel.b200.rope_kv_store"})
+        "kernel.b200.rope_kv_store", "kernel.b200.scale_columns", "kernel.b200.norm_linear",
+        "kernel.b200.qkv_decode_attention", "runtime.kv.advance_all"})
 
 NUMERICAL_MODES = ("fast", "pytorch_compatible")
 
@@ -276,7 +277,7 @@ def _replace_uses(function, old, new) -> None:
 
 
 _PURE_PREFIXES = ("aten.", "kernel.b200.rope_table", "kernel.b200.swiglu", "runtime.view.",
-                  "kernel.b200.pack_rows", "kernel.b200.interleave_rows")
+                  "kernel.b200.pack_rows", "kernel.b200.interleave_rows", "kernel.b200.scale_columns")
 
 
 def _is_pure(operation) -> bool:
@@ -442,14 +443,19 @@ class LoweringReport:
 
 def lower_to_b200(module, *, numerical_mode: Optional[str] = None,
                   fuse_epilogues: bool = True, fuse_graph: bool = True,
-                  causal_mask_arguments: Iterable[str] = ()) -> LoweringReport:
+                  causal_mask_arguments: Iterable[str] = (),
+                  zero_mask_arguments: Iterable[str] = (),
+                  fuse_decode_chain: bool = True) -> LoweringReport:
     """Rewrites `module` in place for the B200 target. `numerical_mode` overrides the mode the
     reference's pass recorded on each op (attribute `numerical_mode`, or implied by a
     `kernel.cuda.*` / `kernel.cublas.*` name); default "fast". `fuse_graph` runs the
     graph-level passes of fusion.py (packed q|k|v and gate|up projections, fused rope + KV
     store of a decode step); `causal_mask_arguments` names graph inputs the caller declares to
     be causal masks, which turns the prefill attention they feed into the mask-free causal
-    form. Idempotent."""
+    form. `fuse_decode_chain` (fast bf16 ops only) folds each RMSNorm into the projection behind
+    it and, where `zero_mask_arguments` names the decode step's mask input as all zero, turns a
+    decode layer's projection -> RoPE -> KV store -> advance -> attention into the fused
+    attention op, with the per-slot length updates hoisted into one op at the end. Idempotent."""
 
     if numerical_mode is not None and numerical_mode not in NUMERICAL_MODES:
         raise ValueError(f"unknown numerical mode {numerical_mode!r}; choose from {NUMERICAL_MODES}")
@@ -486,6 +492,11 @@ def lower_to_b200(module, *, numerical_mode: Optional[str] = None,
             rules["pack_qkv"] += fusion.pack_qkv(function)
             rules["pack_gate_up"] += fusion.pack_gate_up(function)
             rules["rope+kv_store"] += fusion.fuse_rope_kv_store(function)
+            if fuse_decode_chain:
+                rules["norm+linear"] += fusion.fuse_norm_linear(function)
+                rules["qkv+attention"] += fusion.fuse_qkv_attention(function, tuple(zero_mask_arguments))
+                rules["advance_all"] += fusion.hoist_kv_advances(function)
+                removed_dead += _eliminate_dead(function)  # shape values only the fused ops' views used
         if causal_mask_arguments:
             from . import fusion
 

@@ -864,12 +864,15 @@ def b200_qkv_decode_attention(partials: torch.Tensor, bias: Optional[torch.Tenso
                               cosine: torch.Tensor, sine: torch.Tensor, key_buffer: torch.Tensor,
                               value_buffer: torch.Tensor, lengths: torch.Tensor, *, q_heads: int,
                               scale: float, split_tokens: int = 0, max_length_hint: int = 0,
+                              length_offset: int = 0,
                               norm_row_squares: Optional[torch.Tensor] = None,
                               norm_hidden: int = 0, norm_epsilon: float = 0.0) -> torch.Tensor:
     """b200_reduce_rope_kv_store + b200_decode_attention of a decode step in one launch: the
     q|k|v partials are reduced (+ bias, RoPE) inside the attention kernel, the new token's K / V
     row is stored at row lengths[b] - 1 and attends from registers. lengths are the attention
-    lengths (the new token counted). norm_row_squares (what b200_linear_partial(...,
+    lengths (the new token counted; with length_offset=1 they are the lengths before it and the
+    kernel adds one, for callers that advance every slot once at the end of the step).
+    norm_row_squares (what b200_linear_partial(...,
     row_squares=True) returned) with norm_hidden and norm_epsilon: the RMSNorm in front of the
     projection was folded into it, and the reduced sums are scaled by rsqrt(mean(x^2) +
     norm_epsilon) here. Returns B x Hq x 1 x D."""
@@ -903,8 +906,8 @@ def b200_qkv_decode_attention(partials: torch.Tensor, bias: Optional[torch.Tenso
         partials.data_ptr(), splits, _ptr(bias), cos2.data_ptr(), sin2.data_ptr(),
         key_buffer.data_ptr(), value_buffer.data_ptr(), lengths.data_ptr(), output.data_ptr(),
         batch, q_heads, kv_heads, dim, capacity, capacity, float(scale), int(split_tokens),
-        int(max_length_hint), _ptr(norm_row_squares), int(norm_hidden), float(norm_epsilon),
-        _ptr(workspace),
+        int(max_length_hint), int(length_offset), _ptr(norm_row_squares), int(norm_hidden),
+        float(norm_epsilon), _ptr(workspace),
         need, rt.status.data_ptr(), _stream())
     _check(code, "b200_qkv_decode_attention")
     _count(rt)

@@ -162,6 +162,22 @@ class PreallocatedKVCacheState:
         kernels.b200_advance_lengths(lengths, delta, self.capacity)
         return self._derive(self.generation + 1)
 
+    def advance_all(self, *, delta: int, slots: Optional[int] = None) -> "PreallocatedKVCacheState":
+        """runtime.kv.advance of the first `slots` layer slots (default: all) at once: one launch
+        over the length arena when the state owns one, else one per slot. generation grows by
+        the number of slots, as if each had been advanced on its own (execution.py:421-443)."""
+
+        count = len(self.keys) if slots is None else int(slots)
+        if delta <= 0 or count <= 0 or count > len(self.keys):
+            raise ExecutionError("KV advance needs a positive delta and a valid slot count")
+        arena = getattr(self, "_length_arena", None)
+        if arena is not None:
+            kernels.b200_advance_lengths(arena[:count], delta, self.capacity)
+        else:
+            for slot in range(count):
+                kernels.b200_advance_lengths(self.lengths[slot], delta, self.capacity)
+        return self._derive(self.generation + count)
+
     def prefill_store(self, slot: int, key: torch.Tensor, value: torch.Tensor, *,
                       writer: Optional[Callable] = None) -> "PreallocatedKVCacheState":
         """serve.kv.prefill_store (execution.py:405-419): store at the slot's positions (an

@@ -305,3 +305,46 @@ def test_symbolic_dimensions_are_bound_and_guarded_at_run_time(golden_tiny):
         executor.run(prefill, arguments(9, prompt))  # exported with max_batch = 8
     with pytest.raises(ExecutionError, match="breaks the equality"):
         executor.run(prefill, arguments(batch, prompt, position_batch=batch - 1))
+
+
+@pytest.mark.parametrize("chain_rows", [64, 0])
+def test_bf16_decode_chain_through_the_executor(chain_rows, golden_tiny):
+    """The reference-compiled bf16 decode graph with the decode chain fused (the caller declares
+    the decode mask all zero): per layer the fused q|k|v attention op, the cluster split-K o and
+    down projections and the folded-norm gate|up, one length update for all slots at the end.
+    chain_rows = 0 makes the executor run the same fused ops as their unfused kernels (what it
+    does beyond 64 rows). Both against the reference executor's logits, lengths and KV."""
+    gold = golden_tiny["bf16"]
+    config = q2.Qwen2Config(**gold["config"])
+    weights = {k: v.cuda() for k, v in q2.make_weights(config, seed=0, dtype=torch.bfloat16).items()}
+    inv_freq = q2.inverse_frequency(config, "cuda")
+    batch, prompt = gold["batch"], gold["prompt"]
+    executor = B200Executor(strict=True)
+    executor.CHAIN_ROWS = chain_rows
+    prefill = lowered("prefill", "fast", "bf16")
+    logits, state = executor.run(prefill, bind_arguments(prefill.functions[0], weights, {
+        "input_ids": gold["input_ids"].cuda(), "attention_mask": causal_mask(batch, prompt),
+        "position_ids": torch.arange(prompt).repeat(batch, 1).cuda(), "inv_freq": inv_freq})).outputs
+    decode = lowered("decode", "fast", "bf16", zero_mask_arguments=("attention_mask",))
+    names = [op.name for op in decode.functions[0].block.operations]
+    assert names.count("kernel.b200.qkv_decode_attention") == config.num_layers
+    assert names.count("runtime.kv.advance_all") == 1 and "runtime.kv.advance" not in names
+    generation = state.generation
+    for step in range(gold["steps"]):
+        length = prompt + step
+        logits, state = executor.run(decode, bind_arguments(decode.functions[0], weights, {
+            "input_ids": gold["tokens"][:, step].view(batch, 1).cuda(),
+            "attention_mask": torch.zeros(batch, 1, 1, gold["capacity"], device="cuda"),
+            "position_ids": torch.full((batch, 1), length, device="cuda"),
+            "kv_state": state, "inv_freq": inv_freq})).outputs
+        expected = gold["decode_logits"][step].float()
+        scale = max(1.0, float(expected.abs().max()))
+        assert float((logits[:, 0].float().cpu() - expected).abs().max()) <= 2e-2 * scale
+    state.check()
+    assert state.generation == generation + config.num_layers * gold["steps"]
+    used = prompt + gold["steps"]
+    assert torch.equal(torch.stack(list(state.lengths), 0).cpu(), gold["lengths"])
+    keys = torch.stack([k[:, :used] for k in state.keys], 0).float().cpu()
+    assert float((keys - gold["keys"].float()).abs().max()) <= 2e-2 * max(1.0, float(gold["keys"].abs().max()))
+    fused = [e for e in executor.lowering_trace if e.get("op") == "qkv_decode_attention"]
+    assert fused and all(e["fused"] == (chain_rows > 0) and e["length_offset"] == 1 for e in fused)

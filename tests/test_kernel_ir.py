@@ -92,7 +92,8 @@ def test_qwen2_0_5b_graphs_lower_fully(kind, total):
     before = ir.analyze_lowering_coverage(module)
     assert before.total_operations == total
     assert before.coverage < 0.5
-    report = ir.lower_to_b200(module, causal_mask_arguments=("attention_mask",))
+    options = dict(causal_mask_arguments=("attention_mask",), fuse_decode_chain=False)
+    report = ir.lower_to_b200(module, **options)
     ir.verify_module(module)
     coverage = ir.require_full_lowering(module)
     assert coverage.is_complete
@@ -112,6 +113,30 @@ def test_qwen2_0_5b_graphs_lower_fully(kind, total):
         assert names["kernel.b200.decode_attention"] == layers
         assert names["runtime.kv.advance"] == layers
         assert launches == 8 * layers + 4  # + embedding, rope table, final norm, LM head
+        # with the decode chain and a caller-declared all-zero decode mask: five launches a layer
+        chained = load_gz(f"kernel_ir_qwen2_0_5b_{kind}_fast.json.gz")
+        chain_report = ir.lower_to_b200(chained, zero_mask_arguments=("attention_mask",))
+        ir.verify_module(chained)
+        ir.require_full_lowering(chained)
+        chain = Counter(op.name for op in chained.functions[0].block.operations)
+        assert chain["kernel.b200.qkv_decode_attention"] == layers  # partial GEMM + attention
+        assert chain["kernel.b200.norm_linear"] == layers            # gate|up with the folded norm
+        assert chain["kernel.b200.linear"] == 2 * layers + 1         # o, down (+ residual), LM head
+        assert chain["kernel.b200.rms_norm"] == 1                    # the tied LM head keeps its norm
+        assert chain["runtime.kv.advance_all"] == 1 and chain["runtime.kv.advance"] == 0
+        assert chain["kernel.b200.scale_columns"] == 2 * layers
+        assert chain_report.lowered_rules["qkv+attention"] == layers
+        fused = [op for op in chained.functions[0].block.operations
+                 if op.name == "kernel.b200.qkv_decode_attention"]
+        assert all(op.attributes["length_offset"] == 1 for op in fused)
+        assert sorted(op.attributes["slot"] for op in fused) == list(range(layers))
+        # without the declaration the mask is honoured: attention stays its own op
+        kept = load_gz(f"kernel_ir_qwen2_0_5b_{kind}_fast.json.gz")
+        ir.lower_to_b200(kept)
+        kept_names = Counter(op.name for op in kept.functions[0].block.operations)
+        assert kept_names["kernel.b200.qkv_decode_attention"] == 0
+        assert kept_names["kernel.b200.decode_attention"] == layers
+        assert kept_names["kernel.b200.norm_linear"] == 2 * layers
     else:
         assert names["kernel.b200.prefill_attention"] == layers
         assert report.lowered_rules["causal_mask"] == layers
@@ -120,7 +145,7 @@ def test_qwen2_0_5b_graphs_lower_fully(kind, total):
                    for op in module.functions[0].block.operations
                    if op.name == "kernel.b200.prefill_attention")
     snapshot = json.dumps(ir.module_to_json(module), sort_keys=True)
-    ir.lower_to_b200(module, causal_mask_arguments=("attention_mask",))
+    ir.lower_to_b200(module, **options)
     assert json.dumps(ir.module_to_json(module), sort_keys=True) == snapshot  # idempotent
 
 
@@ -135,8 +160,10 @@ def test_bf16_tiny_graphs_lower_fully(kind, mode):
     names = Counter(op.name for op in module.functions[0].block.operations)
     assert names.get("kernel.b200.cast", 0) == 0 and names["kernel.b200.rope_table"] == 1
     for op in module.functions[0].block.operations:
-        if op.name in ("kernel.b200.rms_norm", "kernel.b200.linear"):
+        if op.name in ("kernel.b200.rms_norm", "kernel.b200.linear", "kernel.b200.norm_linear"):
             assert op.attributes["numerical_mode"] == mode
+    # the RMSNorm is folded into the projection behind it in the fast mode only
+    assert (names["kernel.b200.norm_linear"] > 0) == (mode == "fast")
 
 
 def test_only_declared_masks_are_marked_causal():
