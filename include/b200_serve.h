@@ -60,9 +60,13 @@ extern "C" {
 #define B200_LAUNCH_LINEAR_WARP_LEVEL 8    /* b200_linear: warp-level kernel, not tcgen05       */
 #define B200_LAUNCH_PREFILL_WARP_LEVEL 16  /* b200_prefill_attention: warp-level kernel         */
 
-/* Process-wide launch mode of the decode-chain kernels (embedding, rope table, rms_norm fast
- * path, linear on tcgen05, linear_partial, the two reduce_* consumers, decode attention,
- * argmax, advance_lengths). No counterpart in the reference, whose Triton launches are always
+/* Launch mode of the CALLING THREAD for the decode-chain kernels (linear on tcgen05 incl. the
+ * partial-sum, folded-norm and cluster split-K forms, the two reduce_* consumers, decode
+ * attention; every other kernel, advance_lengths / embedding / rope table among them, is always
+ * launched fully serialised, which is what makes lengths[] stable before the attention's wait).
+ * Thread-local: two engines driven from two threads do not see each other's promises; launches
+ * captured into a CUDA graph keep the mode they were captured with. No counterpart in the
+ * reference, whose Triton launches are always
  * fully serialised (ReferenceExecutor.run, execution.py:530-575, runs one operation after another).
  * B200_LAUNCH_PROGRAMMATIC: each of those kernels may become resident before its predecessor
  * in the stream has finished and waits on the device (griddepcontrol.wait) before touching
@@ -78,6 +82,15 @@ extern "C" {
  * B200_ERR_BAD_ARGUMENT for unknown bits. Default 0. */
 int b200_set_launch_mode(int flags);
 int b200_get_launch_mode(void);
+
+/* Debug control of the bounded in-kernel waits (no counterpart in the reference, whose kernels
+ * have no waits to bound). Every mbarrier wait of the TMA / tcgen05 kernels gives up after
+ * `poll_limit` polls (default 4,000,000), sets B200_STATUS_WAIT_TIMEOUT, frees its tensor memory
+ * and returns. drop_loads != 0 makes the copy-issuing threads of those kernels issue nothing, so
+ * that with a small limit every wait runs out at once with no copy in flight: how the tests
+ * exercise the give-up paths without faulting or hanging the GPU. Process-wide; returns the
+ * previous limit (or B200_ERR_BAD_ARGUMENT). Restore (4000000, 0) afterwards. */
+int64_t b200_debug_set_waits(int64_t poll_limit, int drop_loads);
 
 /* Version / build probe. Returns 100 * major + minor of this ABI. */
 int b200_abi_version(void);

@@ -45,6 +45,7 @@ _I64P = POINTER(c_int64)
 SIGNATURES = {
     "b200_abi_version": (c_int, []),
     "b200_error_string": (c_char_p, [c_int]),
+    "b200_debug_set_waits": (c_int64, [c_int64, c_int]),
     "b200_set_launch_mode": (c_int, [c_int]),
     "b200_get_launch_mode": (c_int, []),
     "b200_kv_store": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,

@@ -5,10 +5,26 @@
 
 namespace b200 {
 namespace {
-std::atomic<int> g_launch_mode{0};
+// The launch mode belongs to the calling thread: CONSTANT_WEIGHTS and STABLE_KV_PREFIX are
+// promises about what that thread's own launches may assume, and two engines driven from two
+// threads must not inherit each other's. Captured launches keep the mode they were captured with.
+thread_local int g_launch_mode = 0;
+// Bound of the in-kernel mbarrier waits (polls); see b200_set_wait_limit.
+std::atomic<unsigned> g_wait_limit{4000000u};
 }
-int launch_mode() { return g_launch_mode.load(std::memory_order_relaxed); }
+int launch_mode() { return g_launch_mode; }
+unsigned wait_limit() { return g_wait_limit.load(std::memory_order_relaxed); }
+namespace {
+std::atomic<int> g_drop_loads{0};
+}
+int drop_loads() { return g_drop_loads.load(std::memory_order_relaxed); }
 }  // namespace b200
+
+extern "C" int64_t b200_debug_set_waits(int64_t poll_limit, int drop_loads) {
+  if (poll_limit < 1 || poll_limit > 4000000000ll) return B200_ERR_BAD_ARGUMENT;
+  b200::g_drop_loads.store(drop_loads != 0 ? 1 : 0, std::memory_order_relaxed);
+  return b200::g_wait_limit.exchange(static_cast<unsigned>(poll_limit), std::memory_order_relaxed);
+}
 
 extern "C" int b200_abi_version(void) { return 101; }
 
@@ -17,7 +33,9 @@ extern "C" int b200_set_launch_mode(int flags) {
                  B200_LAUNCH_STABLE_KV_PREFIX | B200_LAUNCH_LINEAR_WARP_LEVEL |
                  B200_LAUNCH_PREFILL_WARP_LEVEL)) != 0)
     return B200_ERR_BAD_ARGUMENT;
-  return b200::g_launch_mode.exchange(flags, std::memory_order_relaxed);
+  const int previous = b200::g_launch_mode;
+  b200::g_launch_mode = flags;
+  return previous;
 }
 
 extern "C" int b200_get_launch_mode(void) { return b200::launch_mode(); }

@@ -41,6 +41,8 @@ __device__ __forceinline__ float sum_slices(const float* first, int64_t slice, i
 // transitive: the wait returns once the predecessor has finished, and the predecessor could
 // not finish before its own wait did.
 int launch_mode();  // defined in api.cu
+unsigned wait_limit();  // polls a bounded in-kernel wait makes before it gives up (b200_debug_set_waits)
+int drop_loads();       // debug: producers issue no copies, so that every bounded wait runs out
 
 __device__ __forceinline__ void grid_dependency_wait() {
   asm volatile("griddepcontrol.wait;" ::: "memory");

@@ -75,6 +75,8 @@ struct DecodeParams {
   // Fused form: lengths[] may still hold the lengths BEFORE the new token (the caller advances
   // every slot once at the end of the step): the attention length is lengths[b] + length_bias.
   int length_bias = 0;
+  uint32_t wait_limit = 4000000u;  // polls of a bounded wait
+  int drop_loads = 0;              // debug: no KV copy is issued (every wait runs out)
   int norm_hidden = 0;
   float norm_eps = 0.0f;
 };
@@ -164,7 +166,7 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
     const uint32_t kdst = warp_smem + ((it0 + it) % kStages) * kStageBytes;
     const uint32_t vdst = kdst + kTileBytes;
     if (TMA) {
-      if (lane == 0) {
+      if (lane == 0 && !p.drop_loads) {
         const uint32_t bar = bar0 + ((it0 + it) % kStages) * 8;
         mbarrier_arrive_expect_tx(bar, kStageBytes);
         const int row = b * p.capacity + t0;  // rows past the tensor end are zero-filled
@@ -258,7 +260,7 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
 
   for (int it = 0; it < my_count; ++it) {
     if (TMA) {
-      if (!mbarrier_wait_bounded(bar0 + ((it0 + it) % kStages) * 8, ((it0 + it) / kStages) & 1)) {
+      if (!mbarrier_wait_bounded(bar0 + ((it0 + it) % kStages) * 8, ((it0 + it) / kStages) & 1, p.wait_limit)) {
         timed_out = true;
         break;
       }
@@ -410,8 +412,8 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
     if (timed_out) {
       if (lane == 0 && p.status != nullptr) atomicOr(p.status, B200_STATUS_WAIT_TIMEOUT);
       // give the copies still in flight a bounded chance to land before the CTA retires
-      for (int it = 0; it < my_count && it < kStages; ++it)
-        mbarrier_wait_bounded(bar0 + ((it0 + it) % kStages) * 8, 0, 100000u);
+      for (int it = 0; it < my_count && it < kStages && !p.drop_loads; ++it)
+        mbarrier_wait_bounded(bar0 + ((it0 + it) % kStages) * 8, 0, min(p.wait_limit, 100000u));
     }
   } else {
     cp_async_wait<0>();
@@ -1352,6 +1354,8 @@ extern "C" int b200_decode_attention(const void* query, const void* key_buffer,
   p.mask_dtype = mask_dtype;
   p.compat = mode == B200_MODE_PYTORCH_COMPATIBLE ? 1 : 0;
   p.early_kv = (launch_mode() & B200_LAUNCH_STABLE_KV_PREFIX) != 0 ? 1 : 0;
+  p.wait_limit = wait_limit();
+  p.drop_loads = drop_loads();
   p.scale = static_cast<float>(scale);
   p.ws_o = nullptr;
   p.ws_ml = nullptr;
@@ -1477,6 +1481,8 @@ extern "C" int b200_decode_attention_static_scratch(
   p.mask_dtype = mask_dtype;
   p.compat = mode == B200_MODE_PYTORCH_COMPATIBLE ? 1 : 0;
   p.early_kv = (launch_mode() & B200_LAUNCH_STABLE_KV_PREFIX) != 0 ? 1 : 0;
+  p.wait_limit = wait_limit();
+  p.drop_loads = drop_loads();
   p.scale = static_cast<float>(scale);
   p.ws_o = nullptr;
   p.ws_ml = nullptr;
@@ -1545,6 +1551,8 @@ extern "C" int b200_qkv_decode_attention(
   p.mask_dtype = B200_F32;
   p.compat = 0;
   p.early_kv = (launch_mode() & B200_LAUNCH_STABLE_KV_PREFIX) != 0 ? 1 : 0;
+  p.wait_limit = wait_limit();
+  p.drop_loads = drop_loads();
   p.scale = static_cast<float>(scale);
   p.ws_o = nullptr;
   p.ws_ml = nullptr;

@@ -55,6 +55,8 @@ struct Tcgen05Params {
   int m, k, n, epilogue, splits;
   int bn;  // columns per tile: a multiple of 16, at most the kernel's BN
   int prefetch_weights;  // W tiles may be fetched before the predecessor kernel has finished
+  uint32_t wait_limit = 4000000u;  // polls of a bounded wait
+  int drop_loads = 0;              // debug: the producer issues nothing (every wait runs out)
   // RMSNorm folded into the projection (norm_input != nullptr): the A operand is the
   // un-normalised x, the norm weight is already multiplied into W's columns, and the epilogue
   // scales row r of the accumulator by rsqrt(mean(x_r^2) + eps) before bias / SwiGLU.
@@ -247,7 +249,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
       mbarrier_arrive_expect_tx(smem_u32(&reduce_bar), static_cast<uint32_t>(p.splits * reduce_owned * 16));
   }
 
-  if (warp == 0 && lane == 0) {
+  if (warp == 0 && lane == 0 && !p.drop_loads) {
     // ---- TMA producer ----
     // The first ring of W tiles does not depend on the kernel before this one: fetch it
     // before waiting for that kernel (the transaction bytes are announced without arriving,
@@ -264,7 +266,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
     for (int kb = 0; kb < nkb; ++kb) {
       const int s = kb % STAGES;
       if (kb >= STAGES &&
-          !mbarrier_wait_bounded(smem_u32(&empty_bar[s]), ((kb / STAGES) - 1) & 1)) {
+          !mbarrier_wait_bounded(smem_u32(&empty_bar[s]), ((kb / STAGES) - 1) & 1, p.wait_limit)) {
         failed = 1;
         break;
       }
@@ -298,7 +300,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
     bool fine = true;
     for (int kb = 0; kb < nkb && fine; ++kb) {
       const int s = kb % STAGES;
-      fine = __all_sync(0xffffffffu, mbarrier_wait_bounded(smem_u32(&full_bar[s]), (kb / STAGES) & 1));
+      fine = __all_sync(0xffffffffu, mbarrier_wait_bounded(smem_u32(&full_bar[s]), (kb / STAGES) & 1, p.wait_limit));
       if (fine && r < A_ROWS) {
         const uint32_t row_addr = smem_base + s * kStageBytes + r * 128;
 #pragma unroll
@@ -327,7 +329,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
     // ---- MMA issuer ----
     for (int kb = 0; kb < nkb; ++kb) {
       const int s = kb % STAGES;
-      if (!mbarrier_wait_bounded(smem_u32(&full_bar[s]), (kb / STAGES) & 1)) {
+      if (!mbarrier_wait_bounded(smem_u32(&full_bar[s]), (kb / STAGES) & 1, p.wait_limit)) {
         failed = 1;
         break;
       }
@@ -346,7 +348,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   __syncwarp();
 
   // ---- epilogue: all four warps, warp w reads TMEM lanes 32w .. 32w+31 = output rows ----
-  bool ok = mbarrier_wait_bounded(smem_u32(&accum_bar), 0);
+  bool ok = mbarrier_wait_bounded(smem_u32(&accum_bar), 0, p.wait_limit);
   trace.mark_middle();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   if (p.norm_input != nullptr) __syncthreads();  // the row scales of warps 2 and 3
@@ -416,7 +418,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
     const bool first_valid = threadIdx.x < owned && first_row < rows && first_col < n_end;
     const int64_t first_offset = static_cast<int64_t>(tile_m * kBM + first_row) * p.n + first_col;
     uint2 res = first_valid ? *reinterpret_cast<const uint2*>(p.residual + first_offset) : make_uint2(0u, 0u);
-    const bool landed = mbarrier_wait_bounded(smem_u32(&reduce_bar), 0);
+    const bool landed = mbarrier_wait_bounded(smem_u32(&reduce_bar), 0, p.wait_limit);
     trace.stamp(4);
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
 #pragma unroll 1
@@ -554,7 +556,7 @@ linear_tcgen05_persistent_kernel(const Tcgen05Params p, const __grid_constant__ 
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_slot;
 
-  if (warp == 4 && lane == 0) {
+  if (warp == 4 && lane == 0 && !p.drop_loads) {
     // ---- TMA producer ----
     grid_dependency_wait();
     int round = 0;  // k-blocks issued so far, over all tiles
@@ -564,7 +566,7 @@ linear_tcgen05_persistent_kernel(const Tcgen05Params p, const __grid_constant__ 
       for (int kb = 0; kb < nkb; ++kb, ++round) {
         const int s = round % STAGES;
         if (round >= STAGES &&
-            !mbarrier_wait_bounded(smem_u32(&empty_bar[s]), ((round / STAGES) - 1) & 1)) {
+            !mbarrier_wait_bounded(smem_u32(&empty_bar[s]), ((round / STAGES) - 1) & 1, p.wait_limit)) {
           ok = false;
           break;
         }
@@ -584,7 +586,7 @@ linear_tcgen05_persistent_kernel(const Tcgen05Params p, const __grid_constant__ 
     for (int tile = blockIdx.x; ok && tile < tiles; tile += gridDim.x, ++local) {
       const int acc = local & 1;
       // the epilogue must have read this accumulator's previous tile
-      if (local >= 2 && !mbarrier_wait_bounded(smem_u32(&acc_empty[acc]), ((local >> 1) - 1) & 1)) {
+      if (local >= 2 && !mbarrier_wait_bounded(smem_u32(&acc_empty[acc]), ((local >> 1) - 1) & 1, p.wait_limit)) {
         ok = false;
         break;
       }
@@ -592,7 +594,7 @@ linear_tcgen05_persistent_kernel(const Tcgen05Params p, const __grid_constant__ 
       const uint32_t d_tmem = tmem_base + acc * kPersistentBN;
       for (int kb = 0; kb < nkb; ++kb, ++round) {
         const int s = round % STAGES;
-        if (!mbarrier_wait_bounded(smem_u32(&full_bar[s]), (round / STAGES) & 1)) {
+        if (!mbarrier_wait_bounded(smem_u32(&full_bar[s]), (round / STAGES) & 1, p.wait_limit)) {
           ok = false;
           break;
         }
@@ -617,7 +619,7 @@ linear_tcgen05_persistent_kernel(const Tcgen05Params p, const __grid_constant__ 
       const int acc = local & 1;
       const int tile_n = tile % tiles_n, tile_m = tile / tiles_n;
       // (the wait's outcome is made warp-uniform: tcgen05.ld is a warp-wide instruction)
-      ok = ok && __all_sync(0xffffffffu, mbarrier_wait_bounded(smem_u32(&acc_full[acc]), (local >> 1) & 1));
+      ok = ok && __all_sync(0xffffffffu, mbarrier_wait_bounded(smem_u32(&acc_full[acc]), (local >> 1) & 1, p.wait_limit));
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int row = tile_m * kBM + warp * 32 + lane;
@@ -974,6 +976,8 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
   p.splits = 1;
   p.bn = bn;
   p.prefetch_weights = (launch_mode() & B200_LAUNCH_CONSTANT_WEIGHTS) != 0 ? 1 : 0;
+  p.wait_limit = wait_limit();
+  p.drop_loads = drop_loads();
   if (fold_norm) {
     p.norm_input = static_cast<const __nv_bfloat16*>(input);
     p.norm_row_stride = input_row_stride;
@@ -1020,6 +1024,8 @@ int linear_partial_tcgen05(const void* input, const void* weight, float* partial
   p.row_squares = row_squares;
   p.bn = plan.bn;
   p.prefetch_weights = (launch_mode() & B200_LAUNCH_CONSTANT_WEIGHTS) != 0 ? 1 : 0;
+  p.wait_limit = wait_limit();
+  p.drop_loads = drop_loads();
   if (a_rows == 64) {
     // A K slice of many k-blocks is a long weight stream: it wants about 2 us x 44 GB/s of
     // loads in flight per SM, twice what the 96 KB rings of the short slices hold.
@@ -1062,6 +1068,8 @@ int linear_splitk_residual_tcgen05(const void* input, const void* weight, const 
   p.splits = plan.splits;
   p.bn = plan.bn;
   p.prefetch_weights = (launch_mode() & B200_LAUNCH_CONSTANT_WEIGHTS) != 0 ? 1 : 0;
+  p.wait_limit = wait_limit();
+  p.drop_loads = drop_loads();
   // (rings short enough to leave room for the send and receive regions of the reduction)
   switch (cluster_config(a_rows, plan.bn, ceil_div(ceil_div(k, kBK), plan.splits))) {
     case ClusterConfig::k32x3: return launch<32, 3, 64>(p, a_map, b_map, stream);

@@ -58,6 +58,8 @@ struct PrefillTcParams {
   int64_t mask_stride_b = 0, mask_stride_q = 0;
   const uint8_t* tile_class = nullptr;  // [batch or 1][q tiles][k tiles]: 0 zero, 1 -inf, 2 mixed
   int64_t class_stride_b = 0;
+  uint32_t wait_limit = 4000000u, spin_limit = 2000000u;  // polls of the bounded waits
+  int drop_loads = 0;  // debug: the producer issues nothing (every wait runs out)
 };
 
 // Classes of the 128 x 128 tiles of an additive mask. Rows beyond T are ignored, key columns
@@ -208,7 +210,7 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
   auto s_column = [&](int g) { return tmem_base + g * kTile; };
   auto o_column = [&](int g) { return tmem_base + G * kTile + g * D; };
 
-  if (warp == kTmaWarp && lane == 0) {
+  if (warp == kTmaWarp && lane == 0 && !p.drop_loads) {
     // ---- TMA producer ----
     mbarrier_arrive_expect_tx(smem_u32(&q_full), G * kTileBytes);
 #pragma unroll
@@ -221,7 +223,7 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
     // S), V_j only at its end, and a single V buffer is not free before the previous P V is done.
     auto load_k = [&](int j) {
       const int s = j % kKStages, use = j / kKStages;
-      if (use > 0 && !mbarrier_wait_bounded(smem_u32(&k_empty[s]), (use - 1) & 1)) return false;
+      if (use > 0 && !mbarrier_wait_bounded(smem_u32(&k_empty[s]), (use - 1) & 1, p.wait_limit)) return false;
       mbarrier_arrive_expect_tx(smem_u32(&k_full[s]), kTileBytes);
 #pragma unroll
       for (int panel = 0; panel < kPanels; ++panel)
@@ -234,7 +236,7 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
       if (j + 1 < n_tiles) ok = load_k(j + 1);
       if (!ok) break;
       const int vs = j % kVStages, v_use = j / kVStages;
-      ok = v_use == 0 || mbarrier_wait_bounded(smem_u32(&v_empty[vs]), (v_use - 1) & 1);
+      ok = v_use == 0 || mbarrier_wait_bounded(smem_u32(&v_empty[vs]), (v_use - 1) & 1, p.wait_limit);
       if (!ok) break;
       mbarrier_arrive_expect_tx(smem_u32(&v_full[vs]), kTileBytes);
 #pragma unroll
@@ -275,8 +277,8 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
       }
       umma_commit(smem_u32(&o_done[g]));
     };
-    bool ok = mbarrier_spin_bounded(smem_u32(&q_full), 0, kSpinLimit) &&
-              mbarrier_spin_bounded(smem_u32(&k_full[0]), 0, kSpinLimit);
+    bool ok = mbarrier_spin_bounded(smem_u32(&q_full), 0, p.spin_limit) &&
+              mbarrier_spin_bounded(smem_u32(&k_full[0]), 0, p.spin_limit);
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -290,7 +292,7 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         if (ok && more && j + 1 < tiles_of(g)) {
-          ok = mbarrier_spin_bounded(smem_u32(&s_free[g]), j & 1, kSpinLimit);
+          ok = mbarrier_spin_bounded(smem_u32(&s_free[g]), j & 1, p.spin_limit);
           if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             issue_s(g, j + 1);
@@ -303,9 +305,9 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
 #pragma unroll
       for (int g = 0; g < G; ++g) {
         if (ok && j < tiles_of(g)) {
-          ok = mbarrier_spin_bounded(smem_u32(&p_full[g]), j & 1, kSpinLimit) &&
+          ok = mbarrier_spin_bounded(smem_u32(&p_full[g]), j & 1, p.spin_limit) &&
                (v_landed ||
-                mbarrier_spin_bounded(smem_u32(&v_full[j % kVStages]), (j / kVStages) & 1, kSpinLimit));
+                mbarrier_spin_bounded(smem_u32(&v_full[j % kVStages]), (j / kVStages) & 1, p.spin_limit));
           v_landed = true;
           if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -367,7 +369,7 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
           }
         }
       }
-      ok = ok && __all_sync(0xffffffffu, mbarrier_wait_ready_first(smem_u32(&s_full[g]), j & 1));
+      ok = ok && __all_sync(0xffffffffu, mbarrier_wait_ready_first(smem_u32(&s_full[g]), j & 1, p.wait_limit));
       uint32_t s0[32], s1[32];  // this thread's half of the row of S
       __nv_bfloat16 half_max = __float2bfloat16_rn(0.0f);
       if (ok) {
@@ -405,7 +407,8 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
           // the group's first warp vouches for K_{j+1}: the MMA thread then needs one poll, not two
           bool landed = true;
           if ((warp & 7) == 0 && j + 1 < my_tiles)
-            landed = mbarrier_wait_ready_first(smem_u32(&k_full[(j + 1) % kKStages]), ((j + 1) / kKStages) & 1);
+            landed = mbarrier_wait_ready_first(smem_u32(&k_full[(j + 1) % kKStages]), ((j + 1) / kKStages) & 1,
+                                               p.wait_limit);
           if (landed)
             asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&s_free[g])) : "memory");
           else
@@ -441,7 +444,7 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
       if (ok && j > 0) {
         const bool raise = __any_sync(0xffffffffu, m_tile > m_ref + kRescaleThreshold);
         // P and O are in use until the group's previous product has completed
-        ok = __all_sync(0xffffffffu, mbarrier_wait_ready_first(smem_u32(&o_done[g]), (j - 1) & 1));
+        ok = __all_sync(0xffffffffu, mbarrier_wait_ready_first(smem_u32(&o_done[g]), (j - 1) & 1, p.wait_limit));
         if (ok && raise) {  // warp-uniform: move the reference maximum of the warp's rows
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const float m_new = fmaxf(m_ref, m_tile);
@@ -495,7 +498,7 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
       if (lane == 0) {
         bool landed = true;  // likewise for V_j
         if (kSoftmaxChecksV && (warp & 7) == 0)
-          landed = mbarrier_wait_ready_first(smem_u32(&v_full[j % kVStages]), (j / kVStages) & 1);
+          landed = mbarrier_wait_ready_first(smem_u32(&v_full[j % kVStages]), (j / kVStages) & 1, p.wait_limit);
         if (landed)
           asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_full[g])) : "memory");
         else
@@ -503,7 +506,7 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
       }
     }
     if (ok && my_tiles > 0)
-      ok = __all_sync(0xffffffffu, mbarrier_wait_ready_first(smem_u32(&o_done[g]), (my_tiles - 1) & 1));
+      ok = __all_sync(0xffffffffu, mbarrier_wait_ready_first(smem_u32(&o_done[g]), (my_tiles - 1) & 1, p.wait_limit));
     // The row sum is the sum of the two halves (both took the same reference maximum); they meet
     // in the first K buffer, which nothing reads any more once the last product has completed
     // (on the failure path the sums are not used).
@@ -597,6 +600,9 @@ int prefill_attention_tcgen05(const void* query, const void* key, const void* va
   p.k_token_dim1 = k_dim1 ? 1 : 0;
   p.v_token_dim1 = v_dim1 ? 1 : 0;
   p.scale_log2 = static_cast<float>(scale) * kLog2e;
+  p.wait_limit = wait_limit();
+  p.spin_limit = p.wait_limit < kSpinLimit ? p.wait_limit : kSpinLimit;
+  p.drop_loads = drop_loads();
   if (mask != nullptr) {
     const int64_t distinct = mask_strides[0] == 0 ? 1 : batch;  // one mask for all: classified once
     p.mask = static_cast<const float*>(mask);

@@ -112,9 +112,9 @@ def launch_mode(*, programmatic: bool, constant_weights: bool = False,
     touching a tensor). constant_weights promises that no kernel in flight writes a weight
     tensor, which lets the tcgen05 linear fetch weight tiles before that wait; stable_kv_prefix
     promises the same for lengths[] and every KV row below lengths[b] - 1, which lets decode
-    attention fill its pipeline before the wait. The mode is
-    process-wide in the library; launches captured into a CUDA graph keep the mode they were
-    captured with."""
+    attention fill its pipeline before the wait. The mode belongs to the calling thread (the
+    library keeps it thread-local: engines on other threads are not affected); launches captured
+    into a CUDA graph keep the mode they were captured with."""
 
     flags = (_lib.LAUNCH_PROGRAMMATIC if programmatic else 0) | \
         (_lib.LAUNCH_CONSTANT_WEIGHTS if constant_weights else 0) | \
