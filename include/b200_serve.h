@@ -203,6 +203,35 @@ int b200_decode_attention_static_scratch(
     int64_t q_head_stride, int64_t mask_batch_stride, int mask_dtype, double scale, int dtype,
     int mode, int64_t split_tokens, int64_t max_length_hint, int32_t* status, void* stream);
 
+/* ---- Paged KV layout -------------------------------------------------------------
+ * The layout the reference lists as future work (README.md:295, docs/kv-bufferization.md:319-323;
+ * `layout` of KVStateType, ir.py:87, and BufferizeKVCachePass(layout=...), passes/kv_bufferize.py:41-42,
+ * are where it would plug in): per layer slot a pool of blocks [num_blocks, block_size, Hkv, D] for
+ * K and one for V, and an int32 block table [B, max_blocks_per_sequence] that maps token t of
+ * sequence b to row t % block_size of block table[b, t / block_size]. Sequences no longer need
+ * contiguous slots sized for the longest context (512 x 8256-token Qwen2-7B slots are 242 GB;
+ * the same sequences at their real lengths fit one GPU). Same arithmetic as the contiguous
+ * entry points, results equal to them on the same logical KV:
+ *   b200_paged_kv_store         serve.kv.store through the block table (bit-exact copy); a
+ *                               position beyond the table's reach sets B200_STATUS_KV_OVERFLOW, a
+ *                               table entry outside [0, num_blocks) B200_STATUS_BAD_POSITION
+ *   b200_paged_decode_attention serve.decode_attention over the pools: one TMA box per 32-token
+ *                               step, addressed through the table (block_size % 32 == 0); bf16,
+ *                               head_dim 64 / 128; workspace as b200_decode_attention_workspace_bytes
+ *                               with max_length = max_blocks_per_sequence * block_size */
+int b200_paged_kv_store(void* key_pool, void* value_pool, const int32_t* block_table, const void* key,
+                        const void* value, const int64_t* positions, int64_t batch, int64_t heads,
+                        int64_t tokens, int64_t head_dim, int64_t num_blocks, int64_t block_size,
+                        int64_t max_blocks_per_sequence, const int64_t key_strides[4],
+                        const int64_t value_strides[4], int dtype, int32_t* status, void* stream);
+int b200_paged_decode_attention(
+    const void* query, const void* key_pool, const void* value_pool, const int32_t* block_table,
+    const int64_t* lengths, const void* mask, void* output, int64_t batch, int64_t q_heads,
+    int64_t kv_heads, int64_t head_dim, int64_t num_blocks, int64_t block_size,
+    int64_t max_blocks_per_sequence, int64_t mask_len, int64_t q_batch_stride, int64_t q_head_stride,
+    int64_t mask_batch_stride, int mask_dtype, double scale, int mode, int64_t split_tokens,
+    int64_t max_length_hint, void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
+
 /* ---- Prefill attention -------------------------------------------------------
  * T-token GQA attention with an arbitrary additive B x 1 x T x T mask, or with
  * proven causality (causal != 0: mask may be NULL and fully masked tiles are skipped).

@@ -67,6 +67,11 @@ SIGNATURES = {
     "b200_decode_attention_static_scratch": (c_int, [c_void_p] * 6 + [c_int64] * 9 +
                                              [c_int, c_double, c_int, c_int, c_int64, c_int64,
                                               c_void_p, c_void_p]),
+    "b200_paged_kv_store": (c_int, [c_void_p] * 6 + [c_int64] * 7 + [_I64P, _I64P, c_int, c_void_p,
+                                                                     c_void_p]),
+    "b200_paged_decode_attention": (c_int, [c_void_p] * 7 + [c_int64] * 11 +
+                                    [c_int, c_double, c_int, c_int64, c_int64, c_void_p, c_int64,
+                                     c_void_p, c_void_p]),
     "b200_prefill_attention_workspace_bytes": (c_int64, [c_int64, c_int64]),
     "b200_prefill_attention": (c_int, [c_void_p] * 5 + [c_int64] * 5 + [_I64P] * 4 +
                                [c_int, c_double, c_int, c_int, c_int, c_void_p, c_int64, c_void_p,

@@ -75,6 +75,13 @@ struct DecodeParams {
   // Fused form: lengths[] may still hold the lengths BEFORE the new token (the caller advances
   // every slot once at the end of the step): the attention length is lengths[b] + length_bias.
   int length_bias = 0;
+  // Paged layout (block_table != nullptr): kbuf / vbuf are block pools [blocks, block_size, Hkv,
+  // D]; token t of sequence b lives in block block_table[b * table_stride + t / block_size] at
+  // row t % block_size. block_size is a multiple of the tokens a warp copies per step, so a copy
+  // never straddles two blocks. `capacity` is then table_stride * block_size.
+  const int32_t* block_table = nullptr;
+  int block_size = 0, table_stride = 0;
+  int64_t pool_rows = 0;  // blocks x block_size: the extent of the pools' tensor maps
   uint32_t wait_limit = 4000000u;  // polls of a bounded wait
   int drop_loads = 0;              // debug: no KV copy is issued (every wait runs out)
   int norm_hidden = 0;
@@ -141,6 +148,12 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
   const int64_t token_stride = static_cast<int64_t>(p.kv_heads) * D;
   const __nv_bfloat16* kglob = p.kbuf + (static_cast<int64_t>(b) * p.capacity * p.kv_heads + kvh) * D;
   const __nv_bfloat16* vglob = p.vbuf + (static_cast<int64_t>(b) * p.capacity * p.kv_heads + kvh) * D;
+  // first buffer row of the TOK tokens that start at token t0 of this sequence
+  auto first_row = [&](int t0) -> int64_t {
+    if (p.block_table == nullptr) return static_cast<int64_t>(b) * p.capacity + t0;
+    const int block = __ldg(p.block_table + static_cast<int64_t>(b) * p.table_stride + t0 / p.block_size);
+    return static_cast<int64_t>(block) * p.block_size + t0 % p.block_size;
+  };
 
   // sub-tile j of this split covers tokens start + j*TOK ...; warp w owns j = w, w+4, ...
   const int n_sub = (end - start + TOK - 1) / TOK;
@@ -169,7 +182,9 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
       if (lane == 0 && !p.drop_loads) {
         const uint32_t bar = bar0 + ((it0 + it) % kStages) * 8;
         mbarrier_arrive_expect_tx(bar, kStageBytes);
-        const int row = b * p.capacity + t0;  // rows past the tensor end are zero-filled
+        // (rows past the tensor end are zero-filled; t0 < end <= capacity, so a paged lookup
+        // stays inside the sequence's row of the block table)
+        const int row = static_cast<int>(first_row(t0));
 #pragma unroll
         for (int panel = 0; panel < D / 64; ++panel) {
           tma_load_3d(kdst + panel * (TOK * 128), &kmap, bar, panel * 64, kvh, row);
@@ -177,8 +192,9 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
         }
       }
     } else {
-      const __nv_bfloat16* ksrc = kglob + t0 * token_stride;
-      const __nv_bfloat16* vsrc = vglob + t0 * token_stride;
+      const int64_t row0 = first_row(t0) - static_cast<int64_t>(b) * p.capacity;  // relative to kglob
+      const __nv_bfloat16* ksrc = kglob + row0 * token_stride;
+      const __nv_bfloat16* vsrc = vglob + row0 * token_stride;
       if (t0 + TOK <= end) {
 #pragma unroll
         for (int i = 0; i < kCopiesPerLane; ++i) {
@@ -1154,8 +1170,11 @@ int launch_bf16(const DecodeParams& p, cudaStream_t stream, int flat_grid = 0) {
   memset(&vmap, 0, sizeof(vmap));
   bool tma = use_tma_loads();
   if (tma)
-    tma = make_kv_tensor_map(&kmap, p.kbuf, p.batch, p.capacity, p.kv_heads, D, tokens_per_step<D>()) &&
-          make_kv_tensor_map(&vmap, p.vbuf, p.batch, p.capacity, p.kv_heads, D, tokens_per_step<D>());
+    tma = p.block_table != nullptr
+              ? make_kv_tensor_map(&kmap, p.kbuf, 1, p.pool_rows, p.kv_heads, D, tokens_per_step<D>()) &&
+                    make_kv_tensor_map(&vmap, p.vbuf, 1, p.pool_rows, p.kv_heads, D, tokens_per_step<D>())
+              : make_kv_tensor_map(&kmap, p.kbuf, p.batch, p.capacity, p.kv_heads, D, tokens_per_step<D>()) &&
+                    make_kv_tensor_map(&vmap, p.vbuf, p.batch, p.capacity, p.kv_heads, D, tokens_per_step<D>());
   int code;
 #define B200_DISPATCH(W, F, T)                                                        \
   code = flat_grid > 0 ? launch_flat_variant<D, W, F, T>(p, kmap, vmap, flat_grid, stream) \
@@ -1372,6 +1391,83 @@ extern "C" int b200_decode_attention(const void* query, const void* key_buffer,
   }
   const GridPlan grid_plan = plan_grid(splits, split_tokens, batch, head_blocks);
   if (grid_plan.splits > 1 && !grid_plan.cluster) {  // (a cluster combines its splits in shared memory)
+    const int64_t need = workspace_bytes_for(batch, q_heads, head_dim, splits);
+    if (!workspace || workspace_bytes < need) return B200_ERR_WORKSPACE;
+    if (batch * head_blocks <= kMaxCounters) p.counters = static_cast<int*>(workspace);
+    p.ws_o = reinterpret_cast<float*>(static_cast<char*>(workspace) + kCounterBytes);
+    p.ws_ml = p.ws_o + batch * q_heads * splits * head_dim;
+  }
+  return head_dim == 64 ? launch_bf16<64>(p, s) : launch_bf16<128>(p, s);
+}
+
+// ---- Paged KV layout ---------------------------------------------------------------------
+// The same kernel over block pools and a block table instead of one contiguous buffer per
+// sequence. Splits merge through the caller's workspace (the cluster merge and the fused
+// q|k|v form are for the contiguous layout).
+extern "C" int b200_paged_decode_attention(
+    const void* query, const void* key_pool, const void* value_pool, const int32_t* block_table,
+    const int64_t* lengths, const void* mask, void* output, int64_t batch, int64_t q_heads,
+    int64_t kv_heads, int64_t head_dim, int64_t num_blocks, int64_t block_size,
+    int64_t max_blocks_per_sequence, int64_t mask_len, int64_t q_batch_stride, int64_t q_head_stride,
+    int64_t mask_batch_stride, int mask_dtype, double scale, int mode, int64_t split_tokens,
+    int64_t max_length_hint, void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+  const int64_t capacity = max_blocks_per_sequence * block_size;
+  if (!query || !key_pool || !value_pool || !block_table || !lengths || !output || batch < 0 ||
+      q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || num_blocks <= 0 || block_size <= 0 ||
+      max_blocks_per_sequence <= 0 || mask_len <= 0 || mask_len > capacity || q_heads % kv_heads != 0)
+    return B200_ERR_BAD_ARGUMENT;
+  if (mask != nullptr && mask_dtype != B200_F32 && mask_dtype != B200_BF16) return B200_ERR_UNSUPPORTED;
+  if (head_dim != 64 && head_dim != 128) return B200_ERR_UNSUPPORTED;
+  if (block_size % 32 != 0) return B200_ERR_UNSUPPORTED;  // a 32-token copy must stay inside one block
+  if (batch == 0) return B200_OK;
+  if (batch > 65535) return B200_ERR_TOO_LARGE;
+  if (!aligned16(key_pool) || !aligned16(value_pool) ||
+      (reinterpret_cast<uintptr_t>(query) & 3u) != 0 || q_head_stride % 2 != 0 || q_batch_stride % 2 != 0)
+    return B200_ERR_ALIGNMENT;
+  if (capacity > INT32_MAX / 2 || num_blocks * block_size > INT32_MAX) return B200_ERR_TOO_LARGE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int groups = static_cast<int>(q_heads / kv_heads);
+  int64_t max_length = max_length_hint > 0 && max_length_hint < mask_len ? max_length_hint : mask_len;
+  const int64_t head_blocks = kv_heads * ceil_div(groups, 16);
+  if (split_tokens <= 0) split_tokens = default_split_tokens(batch, head_blocks, max_length);
+  split_tokens = round_up(split_tokens, 32);
+  const int64_t splits = ceil_div(max_length, split_tokens);
+  if (splits > 65535 || split_tokens > INT32_MAX) return B200_ERR_TOO_LARGE;
+
+  DecodeParams p;
+  p.q = static_cast<const __nv_bfloat16*>(query);
+  p.kbuf = static_cast<const __nv_bfloat16*>(key_pool);
+  p.vbuf = static_cast<const __nv_bfloat16*>(value_pool);
+  p.lengths = lengths;
+  p.mask = mask;
+  p.out = static_cast<__nv_bfloat16*>(output);
+  p.status = status;
+  p.q_batch_stride = q_batch_stride;
+  p.q_head_stride = q_head_stride;
+  p.mask_batch_stride = mask_batch_stride;
+  p.batch = static_cast<int>(batch);
+  p.q_heads = static_cast<int>(q_heads);
+  p.kv_heads = static_cast<int>(kv_heads);
+  p.groups = groups;
+  p.capacity = static_cast<int>(capacity);
+  p.mask_len = static_cast<int>(max_length);
+  p.split_tokens = static_cast<int>(split_tokens);
+  p.num_splits = static_cast<int>(splits);
+  p.mask_dtype = mask_dtype;
+  p.compat = mode == B200_MODE_PYTORCH_COMPATIBLE ? 1 : 0;
+  p.early_kv = 0;
+  p.wait_limit = wait_limit();
+  p.drop_loads = drop_loads();
+  p.scale = static_cast<float>(scale);
+  p.ws_o = nullptr;
+  p.ws_ml = nullptr;
+  p.counters = nullptr;
+  p.block_table = block_table;
+  p.block_size = static_cast<int>(block_size);
+  p.table_stride = static_cast<int>(max_blocks_per_sequence);
+  p.pool_rows = num_blocks * block_size;
+  const GridPlan grid_plan = plan_grid(splits, split_tokens, batch, head_blocks);
+  if (grid_plan.splits > 1) {
     const int64_t need = workspace_bytes_for(batch, q_heads, head_dim, splits);
     if (!workspace || workspace_bytes < need) return B200_ERR_WORKSPACE;
     if (batch * head_blocks <= kMaxCounters) p.counters = static_cast<int*>(workspace);

@@ -424,6 +424,42 @@ __global__ void advance_lengths_kernel(int64_t* lengths, int64_t count, int64_t 
 // below the diagonal and -inf above it (the mask make_qwen2_prefill_inputs builds,
 // qwen2.py:552-572). Grid-stride over B * T * T entries; a CTA that finds a violation clears
 // the flag once. The caller sets flag[0] = 1 before the launch (b200_classify_causal_mask does).
+// ------------------------------------------------------------ paged KV store ----
+// pool[block_table[b, (pos + t) / bs] * bs + (pos + t) % bs, h, :] = x[b, h, t, :]: the positional
+// write of serve.kv.store through a block table. One thread moves one 16-byte chunk of K and of V.
+template <typename T>
+__global__ void paged_kv_store_kernel(T* __restrict__ kpool, T* __restrict__ vpool,
+                                      const int32_t* __restrict__ table, const T* __restrict__ key,
+                                      const T* __restrict__ value, const int64_t* __restrict__ positions,
+                                      int64_t batch, int64_t heads, int64_t tokens, int64_t dim,
+                                      int64_t block_size, int64_t table_stride, int64_t num_blocks,
+                                      Strides4 ks, Strides4 vs, int32_t* status) {
+  constexpr int per = Elem<T>::kPerVec;
+  const int64_t chunks = dim / per;
+  const int64_t total = batch * tokens * heads * chunks;
+  for (int64_t idx = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t c = idx % chunks, h = (idx / chunks) % heads;
+    const int64_t t = (idx / (chunks * heads)) % tokens, b = idx / (chunks * heads * tokens);
+    const int64_t pos = positions[b] + t;
+    if (pos < 0 || pos >= table_stride * block_size) {
+      if (status != nullptr) atomicOr(status, pos < 0 ? B200_STATUS_BAD_POSITION : B200_STATUS_KV_OVERFLOW);
+      continue;
+    }
+    const int64_t block = table[b * table_stride + pos / block_size];
+    if (block < 0 || block >= num_blocks) {  // a table entry nobody assigned
+      if (status != nullptr) atomicOr(status, B200_STATUS_BAD_POSITION);
+      continue;
+    }
+    const int64_t dst = ((block * block_size + pos % block_size) * heads + h) * dim + c * per;
+    Vec16<T> kv, vv;
+    kv.load(key + b * ks.s[0] + h * ks.s[1] + t * ks.s[2] + c * per);
+    vv.load(value + b * vs.s[0] + h * vs.s[1] + t * vs.s[2] + c * per);
+    kv.store(kpool + dst);
+    vv.store(vpool + dst);
+  }
+}
+
 // ------------------------------------------------------------ weight preparation ----
 // out[r, c] = round(weight[r, c] * scale[c]): a norm weight folded into the columns of the
 // projection that follows the norm. One-time, at load.
@@ -782,6 +818,45 @@ int b200_advance_lengths(int64_t* lengths, int64_t slots, int64_t batch, int64_t
   advance_lengths_kernel<<<static_cast<int>(ceil_div(count, kThreads)), kThreads, 0,
                            static_cast<cudaStream_t>(stream)>>>(lengths, count, delta, capacity,
                                                                 status);
+  return launch_status();
+}
+
+int b200_paged_kv_store(void* key_pool, void* value_pool, const int32_t* block_table, const void* key,
+                        const void* value, const int64_t* positions, int64_t batch, int64_t heads,
+                        int64_t tokens, int64_t head_dim, int64_t num_blocks, int64_t block_size,
+                        int64_t max_blocks_per_sequence, const int64_t key_strides[4],
+                        const int64_t value_strides[4], int dtype, int32_t* status, void* stream) {
+  if (!key_pool || !value_pool || !block_table || !key || !value || !positions || !key_strides ||
+      !value_strides || batch < 0 || heads <= 0 || tokens < 0 || head_dim <= 0 || num_blocks <= 0 ||
+      block_size <= 0 || max_blocks_per_sequence <= 0)
+    return B200_ERR_BAD_ARGUMENT;
+  if (key_strides[3] != 1 || value_strides[3] != 1) return B200_ERR_UNSUPPORTED;
+  if (batch == 0 || tokens == 0) return B200_OK;
+  const size_t elt = dtype_bytes(dtype);
+  const int per = static_cast<int>(16 / elt);
+  if (dtype != B200_BF16 && dtype != B200_F32) return B200_ERR_UNSUPPORTED;
+  if (head_dim % per != 0 || !aligned16(key_pool) || !aligned16(value_pool) || !aligned16(key) ||
+      !aligned16(value))
+    return B200_ERR_ALIGNMENT;
+  for (int i = 0; i < 3; ++i)
+    if (key_strides[i] % per != 0 || value_strides[i] % per != 0) return B200_ERR_ALIGNMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  Strides4 ks, vs;
+  for (int i = 0; i < 4; ++i) {
+    ks.s[i] = key_strides[i];
+    vs.s[i] = value_strides[i];
+  }
+  const int64_t total = batch * tokens * heads * (head_dim / per);
+  if (dtype == B200_BF16)
+    paged_kv_store_kernel<__nv_bfloat16><<<grid_for(total), kThreads, 0, s>>>(
+        static_cast<__nv_bfloat16*>(key_pool), static_cast<__nv_bfloat16*>(value_pool), block_table,
+        static_cast<const __nv_bfloat16*>(key), static_cast<const __nv_bfloat16*>(value), positions,
+        batch, heads, tokens, head_dim, block_size, max_blocks_per_sequence, num_blocks, ks, vs, status);
+  else
+    paged_kv_store_kernel<float><<<grid_for(total), kThreads, 0, s>>>(
+        static_cast<float*>(key_pool), static_cast<float*>(value_pool), block_table,
+        static_cast<const float*>(key), static_cast<const float*>(value), positions, batch, heads,
+        tokens, head_dim, block_size, max_blocks_per_sequence, num_blocks, ks, vs, status);
   return launch_status();
 }
 

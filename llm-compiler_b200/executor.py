@@ -22,7 +22,7 @@ from . import kernels
 from .contracts import SymbolError, bind_symbols
 from .dispatch_plan import resolve_dispatch_plan, split_tokens_of
 from .kernel_ir import decode_attribute, require_full_lowering, value_dtype, value_rank
-from .kv_state import ExecutionError, PreallocatedKVCacheState
+from .kv_state import ExecutionError, PagedKVCacheState, PreallocatedKVCacheState
 
 _DTYPES = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16,
            "i64": torch.int64, "i32": torch.int32, "i1": torch.bool}
@@ -295,8 +295,12 @@ class B200Executor:
         q_heads, kv_heads, dim = (int(attributes[name]) for name in ("q_heads", "kv_heads", "head_dim"))
         epsilon, scale = float(attributes["epsilon"]), float(attributes["scale"])
         offset = int(attributes.get("length_offset", 0))
-        key_buffer, value_buffer, lengths = state._slot(slot)
         rows = tensor.numel() // tensor.shape[-1]
+        if isinstance(state, PagedKVCacheState):
+            return self._qkv_decode_attention_paged(state, slot, tensor, norm_weight, weight, bias, cosine,
+                                                    sine, mask, q_heads, kv_heads, dim, epsilon, scale,
+                                                    offset, attributes)
+        key_buffer, value_buffer, lengths = state._slot(slot)
         if key_buffer.shape[0] != rows or key_buffer.shape[2] != kv_heads or key_buffer.shape[3] != dim:
             raise ExecutionError("qkv_decode_attention: the KV state does not match batch, heads or head_dim")
         bound = mask.shape[-1] if mask is not None else state.capacity
@@ -400,10 +404,43 @@ class B200Executor:
         query, key, value, cosine, sine = operands[1:]
         if query.shape[-1] != int(attributes["head_dim"]):
             raise ExecutionError("rope_kv_store: head_dim does not match the attribute")
-        key_buffer, value_buffer, positions = state._slot(int(attributes.get("slot", 0)))
+        slot = int(attributes.get("slot", 0))
+        if isinstance(state, PagedKVCacheState):  # paged storage: rotate, then store through the table
+            rotated, rotated_key = kernels.b200_rope(query, key, cosine, sine)
+            return rotated, state.store(slot, rotated_key, value, state.positions(slot))
+        key_buffer, value_buffer, positions = state._slot(slot)
         rotated = kernels.b200_rope_kv_store(query, key, value, cosine, sine, key_buffer,
                                              value_buffer, positions)
         return rotated, state
+
+    def _qkv_decode_attention_paged(self, state, slot, tensor, norm_weight, weight, bias, cosine, sine,
+                                    mask, q_heads, kv_heads, dim, epsilon, scale, offset, attributes):
+        """The fused decode-layer op on a paged state: the same ops, one kernel each, through the
+        state's own store / attention methods (the fused kernels address contiguous slots)."""
+
+        rows = tensor.numel() // tensor.shape[-1]
+        normed = kernels.b200_rms_norm(tensor, norm_weight, epsilon=epsilon,
+                                       round_before_weight=bool(attributes.get("round_before_weight")),
+                                       numerical_mode="fast")
+        qkv = kernels.b200_linear(normed, weight, bias).view(rows, 1, q_heads + 2 * kv_heads, dim)
+        query = qkv[:, :, :q_heads].transpose(1, 2)
+        key = qkv[:, :, q_heads:q_heads + kv_heads].transpose(1, 2)
+        value = qkv[:, :, q_heads + kv_heads:].transpose(1, 2)
+        query, key = kernels.b200_rope(query, key, cosine, sine)
+        state.store(slot, key, value, state.positions(slot))
+        lengths = state.positions(slot)
+        if offset == 0:
+            state = state.advance(slot, delta=1)
+            attention_state = state
+        else:  # the advance is deferred to the end of the step: attend over lengths + 1
+            attention_lengths = torch.empty_like(lengths)
+            attention_lengths.copy_(lengths)
+            kernels.b200_advance_lengths(attention_lengths, 1, state.capacity)
+            attention_state = state._derive(state.generation)
+            object.__setattr__(attention_state, "lengths",
+                               tuple(attention_lengths if i == slot else l for i, l in enumerate(state.lengths)))
+        context = attention_state.decode_attention(slot, query, mask, groups=q_heads // kv_heads, scale=scale)
+        return context.view(rows, 1, q_heads * dim), state
 
     @staticmethod
     def _slice(operands, attributes, environment):

@@ -602,6 +602,98 @@ def b200_decode_attention_no_alloc(query: torch.Tensor, key_buffer: torch.Tensor
     return output
 
 
+# ------------------------------------------------------------------- paged KV ----
+def b200_paged_kv_store(key_pool: torch.Tensor, value_pool: torch.Tensor, block_table: torch.Tensor,
+                        key: torch.Tensor, value: torch.Tensor, positions: torch.Tensor) -> None:
+    """serve.kv.store through a block table: pool[table[b, (pos+t) // bs], (pos+t) % bs, h, :] =
+    x[b, h, t, :] for K and V. Pools are blocks x block_size x H x D, the table int32 B x
+    max_blocks_per_sequence. The paged counterpart of b200_kv_store (the reference lists the
+    layout as future work, README.md:295)."""
+
+    device = _require_cuda(key_pool, value_pool, block_table, key, value, positions)
+    if key_pool.ndim != 4 or key_pool.shape != value_pool.shape or not key_pool.is_contiguous() or \
+            not value_pool.is_contiguous():
+        raise ValueError("KV pools must be contiguous blocks x block_size x H x D tensors of one shape")
+    if key.ndim != 4 or key.shape != value.shape:
+        raise ValueError("key/value must be B x H x T x D tensors of one shape")
+    blocks, block_size, heads, dim = key_pool.shape
+    batch, _, tokens, _ = key.shape
+    if key.shape[1] != heads or key.shape[3] != dim:
+        raise ValueError("key/value heads or head_dim do not match the pools")
+    if block_table.dtype != torch.int32 or block_table.ndim != 2 or block_table.shape[0] != batch or \
+            not block_table.is_contiguous():
+        raise ValueError("block_table must be a contiguous int32 B x max_blocks tensor")
+    if positions.shape != (batch,) or positions.dtype != torch.int64 or not positions.is_contiguous():
+        raise ValueError("positions must be a contiguous int64 batch vector")
+    if len({key_pool.dtype, value_pool.dtype, key.dtype, value.dtype}) != 1:
+        raise ValueError("pools and key/value must share one dtype")
+    rt = runtime(device)
+    code = _lib.load().b200_paged_kv_store(
+        key_pool.data_ptr(), value_pool.data_ptr(), block_table.data_ptr(), key.data_ptr(),
+        value.data_ptr(), positions.data_ptr(), batch, heads, tokens, dim, blocks, block_size,
+        block_table.shape[1], _lib.i64_array(key.stride()), _lib.i64_array(value.stride()),
+        _code(key.dtype), rt.status.data_ptr(), _stream())
+    _check(code, "b200_paged_kv_store")
+    _count(rt)
+
+
+def b200_paged_decode_attention(query: torch.Tensor, key_pool: torch.Tensor, value_pool: torch.Tensor,
+                                block_table: torch.Tensor, lengths: torch.Tensor,
+                                attention_mask: Optional[torch.Tensor], *, scale: float,
+                                numerical_mode: str = "fast", split_tokens: int = 0,
+                                max_length_hint: int = 0) -> torch.Tensor:
+    """serve.decode_attention over paged KV: the kernel of b200_decode_attention reading every
+    32-token step through the block table. bf16; returns B x Hq x 1 x D."""
+
+    device = _require_cuda(query, key_pool, value_pool, block_table, lengths, attention_mask)
+    if query.ndim != 4 or query.shape[2] != 1:
+        raise ValueError("query must be B x H x 1 x D")
+    if key_pool.ndim != 4 or key_pool.shape != value_pool.shape or not key_pool.is_contiguous() or \
+            not value_pool.is_contiguous():
+        raise ValueError("KV pools must be contiguous blocks x block_size x H x D tensors of one shape")
+    batch, q_heads, _, dim = query.shape
+    blocks, block_size, kv_heads, pool_dim = key_pool.shape
+    if pool_dim != dim or kv_heads <= 0 or q_heads % kv_heads:
+        raise ValueError("query does not match the pools")
+    if not (query.dtype == key_pool.dtype == value_pool.dtype == torch.bfloat16):
+        raise ValueError("paged decode attention runs bf16")
+    if block_table.dtype != torch.int32 or block_table.ndim != 2 or block_table.shape[0] != batch or \
+            not block_table.is_contiguous():
+        raise ValueError("block_table must be a contiguous int32 B x max_blocks tensor")
+    if lengths.shape != (batch,) or lengths.dtype != torch.int64 or not lengths.is_contiguous():
+        raise ValueError("lengths must be a contiguous int64 batch vector")
+    if query.stride(3) != 1:
+        query = _dense(query)
+    capacity = block_table.shape[1] * block_size
+    mask_len, mask_stride, mask_code = capacity, 0, _lib.F32
+    if attention_mask is not None:
+        if attention_mask.ndim != 4 or attention_mask.shape[:3] != (batch, 1, 1):
+            raise ValueError("attention_mask must be B x 1 x 1 x S")
+        mask_len = attention_mask.shape[3]
+        if mask_len > capacity or mask_len <= 0:
+            raise ValueError("mask length must be in [1, capacity]")
+        if attention_mask.stride(3) != 1:
+            attention_mask = _dense(attention_mask)
+        mask_stride = attention_mask.stride(0)
+        mask_code = _code(attention_mask.dtype)
+    output = torch.empty((batch, q_heads, 1, dim), dtype=query.dtype, device=device)
+    rt = runtime(device)
+    library = _lib.load()
+    max_length = min(max_length_hint, mask_len) if max_length_hint > 0 else mask_len
+    need = int(library.b200_decode_attention_workspace_bytes(batch, q_heads, kv_heads, dim, max_length,
+                                                            split_tokens))
+    workspace = rt.workspace("decode_attention", need)
+    code = library.b200_paged_decode_attention(
+        query.data_ptr(), key_pool.data_ptr(), value_pool.data_ptr(), block_table.data_ptr(),
+        lengths.data_ptr(), _ptr(attention_mask), output.data_ptr(), batch, q_heads, kv_heads, dim,
+        blocks, block_size, block_table.shape[1], mask_len, query.stride(0), query.stride(1),
+        mask_stride, mask_code, float(scale), _mode(numerical_mode), int(split_tokens),
+        int(max_length_hint), _ptr(workspace), need, rt.status.data_ptr(), _stream())
+    _check(code, "b200_paged_decode_attention")
+    _count(rt)
+    return output
+
+
 # --------------------------------------------------------------- prefill attention ----
 def b200_prefill_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
                            attention_mask: Optional[torch.Tensor], *, scale: float,

@@ -217,3 +217,135 @@ class PreallocatedKVCacheState:
             kernels.runtime(self.keys[0].device).check_status()
         except kernels.KernelStatusError as error:
             raise ExecutionError(str(error)) from error
+
+
+class PagedKVCacheState(PreallocatedKVCacheState):
+    """The same state ABI over paged storage (layout "paged": the reference's listed future work,
+    README.md:295, docs/kv-bufferization.md:319-323): per layer slot `keys[i]` / `values[i]` are
+    block POOLS [blocks, block_size, Hkv, D] and one int32 block table [B, max_blocks] shared by
+    all slots maps token t of sequence b to row t % block_size of block table[b, t // block_size].
+    `capacity` is the logical capacity max_blocks * block_size; lengths, advance, generation and
+    the status word work as in the contiguous state, and store / decode_attention keep their
+    signatures, so a KernelIR executor drives either layout through the same calls.
+
+    Blocks are handed out by `reserve(tokens_per_sequence)` on the host between steps (a free
+    list; a sequence only holds the blocks its length needs, so sequences of very different
+    lengths share one pool instead of each owning a slot sized for the longest)."""
+
+    def __post_init__(self) -> None:  # the contiguous layout's shape checks do not apply
+        if self.capacity <= 0 or not self.keys or len(self.keys) != len(self.values) or \
+                len(self.keys) != len(self.lengths):
+            raise ExecutionError("K, V and length slot counts must agree and be non-zero")
+
+    @classmethod
+    def allocate_paged(cls, *, num_layers: int, batch: int, max_tokens: int, block_size: int,
+                       num_blocks: int, kv_heads: int, head_dim: int, dtype: torch.dtype,
+                       device: torch.device | str) -> "PagedKVCacheState":
+        if block_size <= 0 or block_size % 32 != 0:
+            raise ExecutionError("the block size must be a positive multiple of 32 tokens")
+        max_blocks = -(-max_tokens // block_size)
+        key_pool = torch.zeros((num_layers, num_blocks, block_size, kv_heads, head_dim), dtype=dtype,
+                               device=device)
+        value_pool = torch.zeros_like(key_pool)
+        length_arena = torch.zeros((num_layers, batch), dtype=torch.int64, device=device)
+        state = cls(tuple(key_pool[i] for i in range(num_layers)),
+                    tuple(value_pool[i] for i in range(num_layers)),
+                    tuple(length_arena[i] for i in range(num_layers)), max_blocks * block_size)
+        object.__setattr__(state, "_length_arena", length_arena)
+        object.__setattr__(state, "block_size", block_size)
+        # unassigned entries point at -1: a store through one raises a status bit instead of writing
+        object.__setattr__(state, "block_table",
+                           torch.full((batch, max_blocks), -1, dtype=torch.int32, device=device))
+        object.__setattr__(state, "_host_table", [[] for _ in range(batch)])
+        object.__setattr__(state, "_free", list(range(num_blocks - 1, -1, -1)))
+        return state
+
+    def _derive(self, generation: int) -> "PagedKVCacheState":
+        state = PagedKVCacheState(self.keys, self.values, self.lengths, self.capacity, generation)
+        for name in ("_length_arena", "block_size", "block_table", "_host_table", "_free"):
+            object.__setattr__(state, name, getattr(self, name))
+        return state
+
+    def reserve(self, tokens_per_sequence: Sequence[int], *, order: Optional[Sequence[int]] = None) -> None:
+        """Makes sure sequence b owns blocks for tokens_per_sequence[b] tokens (host-side, between
+        steps). `order`: the pool blocks to hand out first (tests use a shuffled order to prove
+        that nothing assumes contiguity)."""
+
+        if order is not None:
+            taken = {block for row in self._host_table for block in row}
+            self._free[:] = [block for block in reversed(list(order)) if block not in taken]
+        changed = False
+        for b, tokens in enumerate(tokens_per_sequence):
+            need = -(-int(tokens) // self.block_size)
+            if need > self.block_table.shape[1]:
+                raise ExecutionError(f"sequence {b} needs {tokens} tokens, beyond the paged capacity "
+                                     f"{self.capacity}")
+            while len(self._host_table[b]) < need:
+                if not self._free:
+                    raise ExecutionError("the KV block pool is exhausted")
+                self._host_table[b].append(self._free.pop())
+                changed = True
+        if changed:
+            host = torch.full(tuple(self.block_table.shape), -1, dtype=torch.int32)
+            for b, row in enumerate(self._host_table):
+                host[b, :len(row)] = torch.tensor(row, dtype=torch.int32)
+            self.block_table.copy_(host)
+
+    def release(self, sequence: int) -> None:
+        """Returns a finished sequence's blocks to the pool and empties its lengths."""
+
+        self._free.extend(reversed(self._host_table[sequence]))
+        self._host_table[sequence] = []
+        self.block_table[sequence].fill_(-1)
+        self._length_arena[:, sequence].zero_()
+
+    def blocks_in_use(self) -> int:
+        return sum(len(row) for row in self._host_table)
+
+    def read(self, slot: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        raise ExecutionError("a paged KV state has no contiguous logical view; gather through block_table")
+
+    def gather(self, slot: int, sequence: int, tokens: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """The first `tokens` K and V rows of one sequence as dense T x H x D tensors (a host-driven
+        debugging / test helper: index_select on the pools)."""
+
+        blocks = torch.tensor(self._host_table[sequence], dtype=torch.int64, device=self.keys[slot].device)
+        keys = self.keys[slot].index_select(0, blocks).flatten(0, 1)[:tokens]
+        values = self.values[slot].index_select(0, blocks).flatten(0, 1)[:tokens]
+        return keys, values
+
+    def store(self, slot: int, key: torch.Tensor, value: torch.Tensor, positions: torch.Tensor, *,
+              writer: Optional[Callable] = None) -> "PagedKVCacheState":
+        pool_key, pool_value, _ = self._slot(slot)
+        if key.shape != value.shape or key.ndim != 4:
+            raise ExecutionError("KV store needs K and V of one B x H x T x D shape")
+        if key.shape[0] != self.block_table.shape[0] or key.shape[1] != pool_key.shape[2] or \
+                key.shape[3] != pool_key.shape[3]:
+            raise ExecutionError("KV store batch, heads or head_dim mismatch")
+        if positions.shape != (key.shape[0],) or positions.dtype != torch.int64:
+            raise ExecutionError("KV store positions must be a one-dimensional int64 batch tensor")
+        if key.shape[2] > self.capacity:
+            raise ExecutionError(f"KV store exceeds capacity {self.capacity}")
+        if writer is not None:
+            writer(pool_key, pool_value, self.block_table, key, value, positions)
+        else:
+            kernels.b200_paged_kv_store(pool_key, pool_value, self.block_table, key, value, positions)
+        return self
+
+    def decode_attention(self, slot: int, query: torch.Tensor, attention_mask: torch.Tensor, *,
+                         groups: int, scale: float, runner: Optional[Callable] = None,
+                         **options) -> torch.Tensor:
+        pool_key, pool_value, lengths = self._slot(slot)
+        if query.ndim != 4 or query.shape[2] != 1:
+            raise ExecutionError("decode attention query must be B x H x 1 x D")
+        if attention_mask is not None and (attention_mask.ndim != 4 or attention_mask.shape[2] != 1 or
+                                           attention_mask.shape[-1] > self.capacity):
+            raise ExecutionError("decode attention mask must be B x 1 x 1 x S with S <= capacity")
+        if groups <= 0 or query.shape[1] != pool_key.shape[2] * groups or \
+                query.shape[3] != pool_key.shape[3]:
+            raise ExecutionError("decode attention GQA groups or head_dim mismatch")
+        if options.get("split_tokens") is None:  # (None = "the packaged plan": built-in here)
+            options.pop("split_tokens", None)
+        run = runner or kernels.b200_paged_decode_attention
+        return run(query, pool_key, pool_value, self.block_table, lengths, attention_mask, scale=scale,
+                   **options)
