@@ -59,9 +59,9 @@ FALLBACK_HBM_GBS = 6650.0
 RESULT_STREAM = sys.stdout  # main() replaces it with a private copy of the process's stdout
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode-attention launch over 64 x 4096 =
 # 262144 tokens, from one ncu --set full capture of decode_attention_kernel (the kernel's streaming
-# loop has not changed since; captured at commit 68f6732); scaled to the bench launch by the
+# loop has not changed since; captured at commit a29196d); scaled to the bench launch by the
 # tokens it processes (traffic is proportional to the tokens read)
-NCU_TRAFFIC_BYTES, NCU_TRAFFIC_TOKENS, NCU_TRAFFIC_COMMIT = 138_843_776, 262_144, "68f6732"
+NCU_TRAFFIC_BYTES, NCU_TRAFFIC_TOKENS, NCU_TRAFFIC_COMMIT = 138_338_944, 262_144, "a29196d"
 MIN_TIMED_SECONDS = 1.0
 
 

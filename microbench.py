@@ -6,6 +6,8 @@ the reference's own Triton kernels.
     python microbench.py decode_attention --sweep
     python microbench.py prefill_attention --batch 4 --tokens 4096
     python microbench.py linear --m 64 --k 896 --n 9728 --epilogue swiglu
+    python microbench.py linear_splitk --m 64 --k 4864 --n 896        (o / down of the decode chain)
+    python microbench.py linear_rms --m 64 --k 896 --n 9728 --epilogue swiglu   (gate|up, folded norm)
     python microbench.py kv_store --batch 16 --tokens 4096
     python microbench.py prefill_step --model qwen2-0.5b --batch 4 --tokens 4096
     python microbench.py timeline --batch 64 --length 4096      (a -DB200_TRACE build only)
@@ -79,6 +81,35 @@ def rms_norm_case(args):
     seconds = graph_time(launch, sets, args.warmup, args.iters)
     return {"op": "rms_norm", "rows": rows, "hidden": hidden, "mode": args.mode,
             "us": seconds * 1e6, "gbs": rows * hidden * 4 / seconds / 1e9}
+
+
+def decode_gemm_case(args, form):
+    """The two decode-layer projections that have no stand-alone reference op: `splitk` is
+    serve.linear + residual add as a cluster split-K launch (o / down), `rms` is serve.rms_norm
+    folded into serve.linear (gate|up with --epilogue swiglu). Launched back to back with
+    programmatic dependent launch, each launch reading the one before (the residual stream), the
+    way the decode chain runs them; weights rotate through more than L2."""
+
+    m, k, n = args.m, args.k, args.n
+    sets = sets_for(n * k * 2)
+    g = torch.Generator(device="cuda").manual_seed(m + k + n)
+    weights = [(torch.randn(n, k, generator=g, device="cuda") * k ** -0.5).bfloat16() for _ in range(sets)]
+    x = torch.randn(m, k, generator=g, device="cuda").bfloat16()
+    residual = torch.randn(m, n, generator=g, device="cuda").bfloat16()
+    norm = (1 + 0.1 * torch.randn(k, generator=g, device="cuda")).bfloat16()
+    folded = [kernels.b200_scale_columns(w, norm) for w in weights] if form == "rms" else None
+    carry = [residual]
+
+    def launch(index):
+        with kernels.launch_mode(programmatic=True, constant_weights=True):
+            if form == "splitk":
+                carry[0] = kernels.b200_linear_splitk_residual(x, weights[index], carry[0])
+            else:
+                kernels.b200_linear_rms_input(x, folded[index], epsilon=1e-6, epilogue=args.epilogue)
+
+    seconds = (time_launches if args.no_graph else graph_time)(launch, sets, args.warmup, args.iters)
+    return {"op": f"linear_{form}", "m": m, "k": k, "n": n, "epilogue": args.epilogue, "us": seconds * 1e6,
+            "gbs": (m * k + n * k + m * n) * 2 / seconds / 1e9}
 
 
 def prefill_step_case(args):
@@ -328,7 +359,8 @@ def compare_case(args):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("op", choices=["decode_attention", "prefill_attention", "kv_store", "linear",
-                                       "rms_norm", "timeline", "prefill_step", "compare"])
+                                       "rms_norm", "timeline", "prefill_step", "compare",
+                                       "linear_splitk", "linear_rms"])
     parser.add_argument("--model", default="qwen2-0.5b", choices=["qwen2-0.5b", "qwen2-7b"],
                         help="prefill_step: architecture")
     parser.add_argument("--launches", type=int, default=40, help="timeline: launches to print")
@@ -353,6 +385,8 @@ def main():
         print(json.dumps(timeline_case(args)))
     elif args.op == "compare":
         compare_case(args)
+    elif args.op in ("linear_splitk", "linear_rms"):
+        print(json.dumps(decode_gemm_case(args, args.op.split("_")[1])))
     elif args.op == "prefill_step":
         print(json.dumps(prefill_step_case(args)))
     else:
