@@ -92,6 +92,9 @@ def parse_args():
     parser.add_argument("--context-min", type=int, default=-1,
                         help="with --context-source synthetic: per-sequence contexts uniform in "
                              "[context-min, context] instead of all at --context")
+    parser.add_argument("--kv-layout", default="contiguous", choices=["contiguous", "paged"],
+                        help="paged: K / V in block pools behind a block table (PagedKVCacheState)")
+    parser.add_argument("--block-size", type=int, default=128, help="tokens per KV block (paged layout)")
     parser.add_argument("--path", default="engine", choices=["engine", "executor"],
                         help="engine: Qwen2Engine; executor: the reference-compiled KernelIR of the "
                              "decode step (tests/golden) through lower_to_b200 + B200Executor")
@@ -121,7 +124,10 @@ def workload_config(args, n_gpus):
                         "with N(0,1), greedy decode, bf16, CUDA-graph step, sequences dealt to the "
                         "GPUs by context length"
                         + (f"; one GPU cannot hold {args.global_batch} contiguous KV slots: served as "
-                           f"{sub} sub-batches of {per // sub} in turn" if sub > 1 else ""),
+                           f"{sub} sub-batches of {per // sub} in turn" if sub > 1 else "")
+                        + (f"; KV in pools of {args.block_size}-token blocks behind a block table"
+                           if args.kv_layout == "paged" else ""),
+            "kv_layout": args.kv_layout,
             "global_batch": args.global_batch, "context": args.context, "layers": args.layers or 28,
             "parallelism": f"replicas x{n_gpus} (batch-partitioned, NCCL all-gather of token ids)",
             "l2": "inputs larger than L2 (all weights and every valid KV row are read once per step)",
@@ -130,7 +136,10 @@ def workload_config(args, n_gpus):
         "workload": f"{args.model}-architecture greedy decode, batch {args.batch}/GPU, context "
                     + (f"uniform in [{args.context_min}, {args.context}]" if args.context_min > 0
                        else f"{args.context}")
-                    + f", bf16, CUDA-graph step, KV from a {args.context_source} prompt",
+                    + f", bf16, CUDA-graph step, KV from a {args.context_source} prompt"
+                    + (f", KV in pools of {args.block_size}-token blocks behind a block table"
+                       if args.kv_layout == "paged" else ""),
+        "kv_layout": args.kv_layout,
         "global_batch": args.batch * n_gpus,
         "context": args.context,
         "layers": args.layers or (24 if args.model == "qwen2-0.5b" else 28),
@@ -280,6 +289,15 @@ def measured_hbm_peak():
     return FALLBACK_HBM_GBS, "fallback"
 
 
+def restore_lengths(engine, saved):
+    """Puts back a saved copy of the length arena (the rows the undone steps wrote are rewritten
+    by the next ones); on the paged layout the engine's host mirror of the lengths follows."""
+
+    engine.state._length_arena.copy_(saved)
+    if engine.paged:
+        engine.sync_host_lengths()
+
+
 def attention_roofline(engine, lengths_sum, rounds):
     """Decode-attention kernel alone, one launch per layer over the engine's own KV buffers
     (24 x 134 MB, far beyond L2), captured in a graph so that host launch gaps do not count."""
@@ -294,6 +312,13 @@ def attention_roofline(engine, lengths_sum, rounds):
 
     def launches():
         for index in range(config.num_layers):
+            if engine.paged:
+                kernels.b200_paged_decode_attention(
+                    query, engine.state.keys[index], engine.state.values[index],
+                    engine.state.block_table, engine.attention_lengths, None, scale=engine.scale,
+                    numerical_mode=engine.mode, split_tokens=engine.split_tokens,
+                    max_length_hint=engine.max_length_hint)
+                continue
             kernels.b200_decode_attention(
                 query, engine.state.keys[index], engine.state.values[index],
                 engine.attention_lengths, None, scale=engine.scale, numerical_mode=engine.mode,
@@ -338,15 +363,20 @@ def oracle_step_parity(engine, config, weights, rows=(0, 1)):
     used = int(lengths.max()) + 1
     state = qwen2_model.OracleKVState([], [], [], used)
     for layer in range(config.num_layers):
-        state.keys.append(engine.state.keys[layer][index, :used].cpu())
-        state.values.append(engine.state.values[layer][index, :used].cpu())
+        if engine.paged:  # rows of each sequence gathered through the block table
+            rows_k = [engine.state.gather(layer, r, used) for r in rows]
+            state.keys.append(torch.stack([k for k, _ in rows_k]).cpu())
+            state.values.append(torch.stack([v for _, v in rows_k]).cpu())
+        else:
+            state.keys.append(engine.state.keys[layer][index, :used].cpu())
+            state.values.append(engine.state.values[layer][index, :used].cpu())
         state.lengths.append(lengths.clone())
     ids = engine.input_ids[index].cpu()
     saved = engine.state._length_arena.clone()
     engine.decode_step(feed_back=False)
     actual = engine.logits.view(engine.batch, -1)[index].float().cpu()
     tokens = engine.next_ids[index].cpu()
-    engine.state._length_arena.copy_(saved)  # the row the step wrote is rewritten by the next one
+    restore_lengths(engine, saved)  # the row the step wrote is rewritten by the next one
     torch.cuda.synchronize()
     weights_cpu = {name: tensor.cpu() for name, tensor in weights.items()}
     with torch.no_grad():
@@ -419,13 +449,13 @@ class ExecutorStepper:
             self._step()  # sizes workspaces, prepares the packed / folded weights
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize()
-        self.engine.state._length_arena.copy_(saved)
+        restore_lengths(self.engine, saved)
         self.sync_from_engine()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             self._step()
         self.graph = graph
-        self.engine.state._length_arena.copy_(saved)
+        restore_lengths(self.engine, saved)
         self.sync_from_engine()
 
     def decode_step(self):
@@ -486,7 +516,9 @@ def b200_arm(args, config):
     if any(len(part) != batch for part in batches):
         raise SystemExit("the global batch must divide evenly over ranks and sub-batches")
     capacity = args.context + 2 * (steps + warmup) + 64
-    engine = Qwen2Engine(config, weights, batch=batch, capacity=capacity)
+    engine = Qwen2Engine(config, weights, batch=batch, capacity=capacity, kv_layout=args.kv_layout,
+                         block_size=args.block_size)
+    capacity = engine.capacity  # (whole blocks on the paged layout)
     engine.split_tokens = args.split_tokens
     engine.max_length_hint = capacity
 
@@ -503,9 +535,17 @@ def b200_arm(args, config):
         if batch % chunk == 0 and batch > chunk:
             helper = Qwen2Engine(config, weights, batch=chunk, capacity=args.context)
             first = []
+            if engine.paged:  # the prompts' rows, then one store per layer through the block table
+                shape = (batch, args.context, config.num_kv_heads, config.head_dim)
+                rows_k = [torch.empty(shape, dtype=engine.dtype, device=device) for _ in range(config.num_layers)]
+                rows_v = [torch.empty(shape, dtype=engine.dtype, device=device) for _ in range(config.num_layers)]
             for begin in range(0, batch, chunk):
                 helper.prefill(prompt[begin:begin + chunk])
                 for layer in range(config.num_layers):
+                    if engine.paged:
+                        rows_k[layer][begin:begin + chunk].copy_(helper.state.keys[layer])
+                        rows_v[layer][begin:begin + chunk].copy_(helper.state.values[layer])
+                        continue
                     engine.state.keys[layer][begin:begin + chunk, :args.context].copy_(
                         helper.state.keys[layer])
                     engine.state.values[layer][begin:begin + chunk, :args.context].copy_(
@@ -513,6 +553,11 @@ def b200_arm(args, config):
                 first.append(helper.next_ids.clone())
             del helper
             engine.load_context(torch.full((batch,), args.context), next_ids=torch.cat(first))
+            if engine.paged:
+                zeros = torch.zeros(batch, dtype=torch.int64, device=device)
+                for layer in range(config.num_layers):
+                    engine.state.store(layer, rows_k[layer].transpose(1, 2), rows_v[layer].transpose(1, 2), zeros)
+                del rows_k, rows_v
         else:
             engine.prefill(prompt)
     else:
@@ -533,20 +578,22 @@ def b200_arm(args, config):
     if args.path == "executor":
         if args.model != "qwen2-0.5b" or args.layers:
             raise SystemExit("--path executor runs the shipped Qwen2-0.5B decode graph")
+        if engine.paged:
+            raise SystemExit("--path executor measures the contiguous layout")
         stepper = ExecutorStepper(engine, weights)
         stepper.capture()
         # the same step through both paths from the same state: they launch the same kernels
         saved = engine.state._length_arena.clone()
         engine.decode_step(feed_back=False)
         engine_logits, engine_tokens = engine.logits.float().clone(), engine.next_ids.clone()
-        engine.state._length_arena.copy_(saved)
+        restore_lengths(engine, saved)
         stepper.sync_from_engine()
         stepper.decode_step()
         difference = float((stepper.logits.view(batch, -1).float() - engine_logits.view(batch, -1)).abs().max())
         if parity is not None:
             parity["executor_vs_engine_max_abs_logit_diff"] = difference
             parity["executor_vs_engine_tokens_equal"] = bool(torch.equal(stepper.next_ids, engine_tokens))
-        engine.state._length_arena.copy_(saved)
+        restore_lengths(engine, saved)
         stepper.sync_from_engine()
     step_tokens_read = sum(int(part.sum()) + len(part) for part in batches)  # KV rows read per global step
     global_batch = batch * len(batches) * world
@@ -595,7 +642,7 @@ def b200_arm(args, config):
             if len(batches) > 1:
                 fill_context(part, rank * 16 + index)
             elif saved_lengths[0] is not None:
-                engine.state._length_arena.copy_(saved_lengths[0])
+                restore_lengths(engine, saved_lengths[0])
                 if stepper is not None:
                     stepper.sync_from_engine()
             if saved_lengths[index] is None:
@@ -617,7 +664,7 @@ def b200_arm(args, config):
 
         # end to end through the public host API: H2D ids, step, all-gather of the tokens where
         # there are several ranks, D2H tokens, every step
-        engine.state._length_arena.copy_(saved_lengths[-1])
+        restore_lengths(engine, saved_lengths[-1])
         host_ids = engine.next_ids.cpu()
         if stepper is not None:
             stepper.sync_from_engine()

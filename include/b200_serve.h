@@ -218,7 +218,11 @@ int b200_decode_attention_static_scratch(
  *   b200_paged_decode_attention serve.decode_attention over the pools: one TMA box per 32-token
  *                               step, addressed through the table (block_size % 32 == 0); bf16,
  *                               head_dim 64 / 128; workspace as b200_decode_attention_workspace_bytes
- *                               with max_length = max_blocks_per_sequence * block_size */
+ *                               with max_length = max_blocks_per_sequence * block_size
+ *   b200_paged_qkv_decode_attention  b200_qkv_decode_attention (below) on this layout: the new
+ *                               token's K / V row is written to the block the table names for
+ *                               position lengths[b] - 1; no block there sets B200_STATUS_KV_OVERFLOW
+ *                               and writes nothing */
 int b200_paged_kv_store(void* key_pool, void* value_pool, const int32_t* block_table, const void* key,
                         const void* value, const int64_t* positions, int64_t batch, int64_t heads,
                         int64_t tokens, int64_t head_dim, int64_t num_blocks, int64_t block_size,
@@ -231,6 +235,14 @@ int b200_paged_decode_attention(
     int64_t max_blocks_per_sequence, int64_t mask_len, int64_t q_batch_stride, int64_t q_head_stride,
     int64_t mask_batch_stride, int mask_dtype, double scale, int mode, int64_t split_tokens,
     int64_t max_length_hint, void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
+int b200_paged_qkv_decode_attention(
+    const void* qkv_partials, int64_t qkv_splits, const void* qkv_bias, const void* cosine,
+    const void* sine, void* key_pool, void* value_pool, const int32_t* block_table,
+    const int64_t* lengths, void* output, int64_t batch, int64_t q_heads, int64_t kv_heads,
+    int64_t head_dim, int64_t num_blocks, int64_t block_size, int64_t max_blocks_per_sequence,
+    int64_t mask_len, double scale, int64_t split_tokens, int64_t max_length_hint,
+    int64_t length_offset, const void* norm_row_squares, int64_t norm_hidden, double norm_epsilon,
+    void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
 
 /* ---- Prefill attention -------------------------------------------------------
  * T-token GQA attention with an arbitrary additive B x 1 x T x T mask, or with
@@ -348,7 +360,12 @@ int b200_qkv_decode_attention(const void* qkv_partials, int64_t qkv_splits, cons
  *   b200_linear_rms_input        serve.rms_norm + serve.linear (+ bias, + SwiGLU epilogue) on the
  *                                un-normalised input and the column-scaled weight
  *   b200_linear_splitk_residual  serve.linear + aten.add: output = r(r(x W^T) + residual);
- *                                n a multiple of 4, M <= 256
+ *                                n a multiple of 4, M <= 256. With row_squares_out (fp32
+ *                                [b200_linear_splitk_slices(m, k, n), m], NULL to skip) it also
+ *                                leaves sum(output_r^2) in slices, for a folded RMSNorm behind it;
+ *                                a slice count of 0 means this shape writes none.
+ * b200_linear_rms_input with row_squares (fp32 [row_square_slices, m], as left by
+ * b200_linear_splitk_residual for the same rows) adds those slices instead of squaring x itself.
  * b200_qkv_decode_attention takes the same fold for the q|k|v projection: with
  * norm_row_squares (fp32 [qkv_splits, B], what b200_linear_partial left: sum of squares of the
  * un-normalised rows of width norm_hidden per K slice) it scales the reduced sums by
@@ -356,11 +373,13 @@ int b200_qkv_decode_attention(const void* qkv_partials, int64_t qkv_splits, cons
 int b200_scale_columns(const void* weight, const void* scale, void* output, int64_t rows,
                        int64_t columns, int dtype, void* stream);
 int b200_linear_rms_input(const void* input, const void* folded_weight, const void* bias,
-                          void* output, int64_t m, int64_t k, int64_t n, int64_t input_row_stride,
+                          void* output, const void* row_squares, int64_t row_square_slices,
+                          int64_t m, int64_t k, int64_t n, int64_t input_row_stride,
                           double epsilon, int epilogue, int32_t* status, void* stream);
+int64_t b200_linear_splitk_slices(int64_t m, int64_t k, int64_t n);
 int b200_linear_splitk_residual(const void* input, const void* weight, const void* residual,
-                                void* output, int64_t m, int64_t k, int64_t n,
-                                int64_t input_row_stride, int32_t* status, void* stream);
+                                void* output, void* row_squares_out, int64_t m, int64_t k,
+                                int64_t n, int64_t input_row_stride, int32_t* status, void* stream);
 
 /* ---- Ops the reference leaves to PyTorch eager (execution.py:500-528) ---------- */
 /* aten.embedding.default: out[r,:] = table[ids[r],:]. */

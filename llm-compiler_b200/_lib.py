@@ -91,10 +91,15 @@ SIGNATURES = {
                                   [c_int64] * 6 + [c_double, c_int64, c_int64, c_int64, c_void_p,
                                                    c_int64, c_double, c_void_p, c_int64, c_void_p,
                                                    c_void_p]),
+    "b200_paged_qkv_decode_attention": (c_int, [c_void_p, c_int64] + [c_void_p] * 8 +
+                                        [c_int64] * 8 + [c_double, c_int64, c_int64, c_int64,
+                                                         c_void_p, c_int64, c_double, c_void_p,
+                                                         c_int64, c_void_p, c_void_p]),
     "b200_scale_columns": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
-    "b200_linear_rms_input": (c_int, [c_void_p] * 4 + [c_int64] * 4 + [c_double, c_int, c_void_p,
+    "b200_linear_rms_input": (c_int, [c_void_p] * 5 + [c_int64] * 5 + [c_double, c_int, c_void_p,
                                                                        c_void_p]),
-    "b200_linear_splitk_residual": (c_int, [c_void_p] * 4 + [c_int64] * 4 + [c_void_p, c_void_p]),
+    "b200_linear_splitk_slices": (c_int64, [c_int64] * 3),
+    "b200_linear_splitk_residual": (c_int, [c_void_p] * 5 + [c_int64] * 4 + [c_void_p, c_void_p]),
     "b200_embedding": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int,
                                c_void_p, c_void_p]),
     "b200_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),

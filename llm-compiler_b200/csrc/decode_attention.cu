@@ -580,8 +580,18 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
         keep[d] = ylo;
         keep[d + half] = yhi;
         if (g0 == 0) {
-          __nv_bfloat16* dst = (rotate ? p.kstore : p.vstore) +
-              ((static_cast<int64_t>(b) * p.capacity + (n_tokens - 1)) * p.kv_heads + kvh) * D;
+          // the row of the newest token: contiguous slot b, or through the block table
+          int64_t row = static_cast<int64_t>(b) * p.capacity + (n_tokens - 1);
+          if (p.block_table != nullptr) {
+            const int t = n_tokens - 1;
+            const int block = __ldg(p.block_table + static_cast<int64_t>(b) * p.table_stride + t / p.block_size);
+            row = static_cast<int64_t>(block) * p.block_size + t % p.block_size;
+            if (block < 0 || row >= p.pool_rows) {  // no block assigned: nothing is written
+              if (d == 0 && p.status != nullptr) atomicOr(p.status, B200_STATUS_KV_OVERFLOW);
+              continue;
+            }
+          }
+          __nv_bfloat16* dst = (rotate ? p.kstore : p.vstore) + (row * p.kv_heads + kvh) * D;
           dst[d] = __float2bfloat16_rn(ylo);
           dst[d + half] = __float2bfloat16_rn(yhi);
         }
@@ -1596,14 +1606,17 @@ extern "C" int b200_decode_attention_static_scratch(
 }
 
 // ---- Fused q|k|v reduction + RoPE + KV store + decode attention ---------------------------
-extern "C" int b200_qkv_decode_attention(
+// block_table == nullptr: key_buffer / value_buffer are the contiguous [B, capacity, Hkv, D]
+// buffers; else they are block pools [num_blocks, block_size, Hkv, D] and capacity is
+// max_blocks_per_sequence * block_size.
+static int qkv_decode_attention_impl(
     const void* qkv_partials, int64_t qkv_splits, const void* qkv_bias, const void* cosine,
     const void* sine, void* key_buffer, void* value_buffer, const int64_t* lengths, void* output,
     int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim, int64_t capacity,
     int64_t mask_len, double scale, int64_t split_tokens, int64_t max_length_hint,
     int64_t length_offset, const void* norm_row_squares, int64_t norm_hidden, double norm_epsilon,
-    void* workspace,
-    int64_t workspace_bytes, int32_t* status, void* stream) {
+    void* workspace, int64_t workspace_bytes, int32_t* status, void* stream,
+    const int32_t* block_table, int64_t num_blocks, int64_t block_size) {
   if (norm_row_squares != nullptr && (norm_hidden <= 0 || !(norm_epsilon >= 0.0)))
     return B200_ERR_BAD_ARGUMENT;
   if (length_offset < 0 || length_offset > 1) return B200_ERR_BAD_ARGUMENT;
@@ -1617,7 +1630,9 @@ extern "C" int b200_qkv_decode_attention(
   if (batch > 65535) return B200_ERR_TOO_LARGE;
   if (!aligned16(key_buffer) || !aligned16(value_buffer) || !aligned16(qkv_partials))
     return B200_ERR_ALIGNMENT;
-  if (capacity > INT32_MAX / 2 || batch * capacity > INT32_MAX) return B200_ERR_TOO_LARGE;
+  if (capacity > INT32_MAX / 2 ||
+      (block_table == nullptr ? batch * capacity : num_blocks * block_size) > INT32_MAX)
+    return B200_ERR_TOO_LARGE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int groups = static_cast<int>(q_heads / kv_heads);
   int64_t max_length = max_length_hint > 0 && max_length_hint < mask_len ? max_length_hint : mask_len;
@@ -1664,6 +1679,12 @@ extern "C" int b200_qkv_decode_attention(
   p.length_bias = static_cast<int>(length_offset);
   p.norm_hidden = static_cast<int>(norm_hidden);
   p.norm_eps = static_cast<float>(norm_epsilon);
+  if (block_table != nullptr) {
+    p.block_table = block_table;
+    p.block_size = static_cast<int>(block_size);
+    p.table_stride = static_cast<int>(capacity / block_size);
+    p.pool_rows = num_blocks * block_size;
+  }
   const GridPlan grid_plan = plan_grid(splits, split_tokens, batch, head_blocks);
   if (grid_plan.splits > 1 && !grid_plan.cluster) {
     const int64_t need = workspace_bytes_for(batch, q_heads, head_dim, splits);
@@ -1673,4 +1694,37 @@ extern "C" int b200_qkv_decode_attention(
     p.ws_ml = p.ws_o + batch * q_heads * splits * head_dim;
   }
   return head_dim == 64 ? launch_bf16<64>(p, s) : launch_bf16<128>(p, s);
+}
+
+extern "C" int b200_qkv_decode_attention(
+    const void* qkv_partials, int64_t qkv_splits, const void* qkv_bias, const void* cosine,
+    const void* sine, void* key_buffer, void* value_buffer, const int64_t* lengths, void* output,
+    int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim, int64_t capacity,
+    int64_t mask_len, double scale, int64_t split_tokens, int64_t max_length_hint,
+    int64_t length_offset, const void* norm_row_squares, int64_t norm_hidden, double norm_epsilon,
+    void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+  return qkv_decode_attention_impl(qkv_partials, qkv_splits, qkv_bias, cosine, sine, key_buffer,
+                                   value_buffer, lengths, output, batch, q_heads, kv_heads, head_dim,
+                                   capacity, mask_len, scale, split_tokens, max_length_hint,
+                                   length_offset, norm_row_squares, norm_hidden, norm_epsilon,
+                                   workspace, workspace_bytes, status, stream, nullptr, 0, 0);
+}
+
+extern "C" int b200_paged_qkv_decode_attention(
+    const void* qkv_partials, int64_t qkv_splits, const void* qkv_bias, const void* cosine,
+    const void* sine, void* key_pool, void* value_pool, const int32_t* block_table,
+    const int64_t* lengths, void* output, int64_t batch, int64_t q_heads, int64_t kv_heads,
+    int64_t head_dim, int64_t num_blocks, int64_t block_size, int64_t max_blocks_per_sequence,
+    int64_t mask_len, double scale, int64_t split_tokens, int64_t max_length_hint,
+    int64_t length_offset, const void* norm_row_squares, int64_t norm_hidden, double norm_epsilon,
+    void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+  if (!block_table || num_blocks <= 0 || block_size <= 0 || max_blocks_per_sequence <= 0)
+    return B200_ERR_BAD_ARGUMENT;
+  if (block_size % 32 != 0) return B200_ERR_UNSUPPORTED;  // a 32-token copy must stay inside one block
+  return qkv_decode_attention_impl(qkv_partials, qkv_splits, qkv_bias, cosine, sine, key_pool,
+                                   value_pool, lengths, output, batch, q_heads, kv_heads, head_dim,
+                                   max_blocks_per_sequence * block_size, mask_len, scale, split_tokens,
+                                   max_length_hint, length_offset, norm_row_squares, norm_hidden,
+                                   norm_epsilon, workspace, workspace_bytes, status, stream,
+                                   block_table, num_blocks, block_size);
 }

@@ -339,7 +339,7 @@ namespace b200 {
 int linear_tcgen05(const void* input, const void* weight, const void* bias, const void* residual,
                    void* output, int64_t m, int64_t k, int64_t n, int64_t input_row_stride,
                    int epilogue, int32_t* status, cudaStream_t stream, bool fold_norm = false,
-                   double norm_eps = 0.0);
+                   double norm_eps = 0.0, const float* norm_squares = nullptr, int norm_slices = 0);
 }
 
 using namespace b200;

@@ -66,6 +66,14 @@ struct Tcgen05Params {
   // Partial-sum producer only: the CTAs of the first N tile also leave sum(x_r^2) over their K
   // slice in row_squares[split, m], for the consumer that applies the folded RMSNorm.
   float* row_squares = nullptr;
+  // Cluster split-K only: sum(y_r^2) of the stored (rounded) output rows over the units this
+  // CTA owns, squares_out[(N tile * splits + K slice), m]: the row sums of squares that a folded
+  // RMSNorm behind this projection needs, left for it in slices that it adds in a fixed order.
+  float* squares_out = nullptr;
+  // Folded RMSNorm whose producer left such slices (norm_squares[norm_slices, m]): the two idle
+  // warps add them instead of squaring every x box.
+  const float* norm_squares = nullptr;
+  int norm_slices = 0;
 };
 
 // silu for the fused SwiGLU epilogue: x / (1 + 2^(-x log2 e)) on the special-function unit
@@ -213,7 +221,8 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   const int nkb = max(0, min(kb_first + kb_per, kb_total) - kb_first);
   const uint32_t smem_base = smem_u32(smem);
   // warps 2 and 3 square the rows of x as they pass through shared memory
-  const bool squares = A_ROWS == 64 && (p.norm_input != nullptr || (p.row_squares != nullptr && tile_n == 0));
+  const bool squares = A_ROWS == 64 && ((p.norm_input != nullptr && p.norm_squares == nullptr) ||
+                                        (p.row_squares != nullptr && tile_n == 0));
 
   if (threadIdx.x == 0) {
     failed = 0;
@@ -325,6 +334,30 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
     else if (r < p.m)
       p.row_squares[static_cast<int64_t>(split) * p.m + r] = fine ? ss : 0.0f;
   }
+  if (warp >= 2 && A_ROWS == 64 && p.norm_squares != nullptr) {
+    // Folded RMSNorm, row sums of squares left by the kernel that produced x: thread t of warps
+    // 2 and 3 adds the slices of row t in slice order (L2 reads, sixteen in flight) while the
+    // main loop runs. The slices are that kernel's output: wait for it first.
+    if (lane == 0) grid_dependency_wait();
+    __syncwarp();
+    const int r = (warp - 2) * 32 + lane;
+    float ss = 0.0f;
+    if (r < p.m) {
+      const float* src = p.norm_squares + r;
+      int slice = 0;
+#pragma unroll 1
+      for (; slice + 16 <= p.norm_slices; slice += 16) {
+        float t[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) t[i] = __ldcg(src + static_cast<int64_t>(slice + i) * p.m);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) ss += t[i];
+      }
+#pragma unroll 1
+      for (; slice < p.norm_slices; ++slice) ss += __ldcg(src + static_cast<int64_t>(slice) * p.m);
+    }
+    row_scale[r] = rsqrtf(ss / static_cast<float>(p.k) + p.norm_eps);
+  }
   if (warp == 1 && lane == 0) {
     // ---- MMA issuer ----
     for (int kb = 0; kb < nkb; ++kb) {
@@ -425,7 +458,11 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
     for (int local = threadIdx.x; local < owned && landed; local += kThreads) {
       const int item = local * p.splits + rank;
       const int r = item >> unit_shift, col = tile_n * bn + (item & ((bn / 4) - 1)) * 4;
-      if (r >= rows || col >= n_end) continue;
+      if (r >= rows || col >= n_end) {
+        if (p.squares_out != nullptr)
+          asm volatile("st.shared.f32 [%0], %1;" ::"r"(recv_base + local * 16), "f"(0.0f) : "memory");
+        continue;
+      }
       const int64_t o = static_cast<int64_t>(tile_m * kBM + r) * p.n + col;  // n % 4 == 0
       if (local != threadIdx.x) res = *reinterpret_cast<const uint2*>(p.residual + o);
       float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
@@ -444,6 +481,28 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
       acc.x = __fadd_rn(acc.x, bf16_lo(res.x)); acc.y = __fadd_rn(acc.y, bf16_hi(res.x));
       acc.z = __fadd_rn(acc.z, bf16_lo(res.y)); acc.w = __fadd_rn(acc.w, bf16_hi(res.y));
       *reinterpret_cast<uint2*>(p.out + o) = make_uint2(pack_bf16x2(acc.x, acc.y), pack_bf16x2(acc.z, acc.w));
+      if (p.squares_out != nullptr) {
+        // the squares of what was stored; slice 0's copy of this unit, read by this thread alone, is free
+        round_bf16_pair(acc.x, acc.y);
+        round_bf16_pair(acc.z, acc.w);
+        const float sq = fmaf(acc.x, acc.x, fmaf(acc.y, acc.y, fmaf(acc.z, acc.z, acc.w * acc.w)));
+        asm volatile("st.shared.f32 [%0], %1;" ::"r"(recv_base + local * 16), "f"(sq) : "memory");
+      }
+    }
+    if (p.squares_out != nullptr) {
+      // one thread per row adds the units of its row that this CTA owns, in unit order
+      __syncthreads();
+      const int r = threadIdx.x, units_per_row = bn / 4, first = r * units_per_row;
+      if (r < rows && landed) {
+        float ss = 0.0f;
+#pragma unroll 1
+        for (int i = first + (rank - first % p.splits + p.splits) % p.splits; i < first + units_per_row; i += p.splits) {
+          float sq;
+          asm volatile("ld.shared.f32 %0, [%1];" : "=f"(sq) : "r"(recv_base + (i / p.splits) * 16) : "memory");
+          ss += sq;
+        }
+        p.squares_out[static_cast<int64_t>(tile_n * p.splits + rank) * p.m + tile_m * kBM + r] = ss;
+      }
     }
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     ok = ok && __syncthreads_and(landed);
@@ -908,7 +967,7 @@ PartialPlan plan_partial(int64_t m, int64_t k, int64_t n) {
 int linear_tcgen05(const void* input, const void* weight, const void* bias, const void* residual,
                    void* output, int64_t m, int64_t k, int64_t n, int64_t input_row_stride,
                    int epilogue, int32_t* status, cudaStream_t stream, bool fold_norm,
-                   double norm_eps) {
+                   double norm_eps, const float* norm_squares, int norm_slices) {
   if (ceil_div(m, kBM) > 65535) return B200_ERR_UNSUPPORTED;
   if (fold_norm && m > 64) return B200_ERR_UNSUPPORTED;  // the idle-warp scheme of the decode tiles
   int bn;
@@ -954,6 +1013,22 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
       }
     }
     if (best < 0.8 && !fold_norm) return B200_ERR_UNSUPPORTED;
+    // A folded-norm projection at decode sizes (gate|up: 17 MB of weights) is a chain of
+    // latencies, not a stream: 64-column tiles with short rings put two or three CTAs on an SM,
+    // whose ring round trips and two-warp SwiGLU epilogues overlap. Measured on the Qwen2-0.5B
+    // step: 1.389 ms with 152 x 64 columns against 1.449 ms with 122 x 80 (one CTA per SM).
+    if (fold_norm && small_rings()) {
+      const int64_t tiles64 = ceil_div(n, 64);
+      if (tiles64 >= kNumSMs - 28 && tiles64 <= 3 * kNumSMs) bn = 64;
+    }
+    if (fold_norm) {  // B200_FOLD_BN: tile width of the folded-norm projection (experiments only)
+      static const int forced = [] {
+        const char* text = getenv("B200_FOLD_BN");
+        const int value = text != nullptr ? atoi(text) : 0;
+        return value >= 16 && value <= 256 && value % 16 == 0 ? value : 0;
+      }();
+      if (forced != 0) bn = forced;
+    }
     // Many waves of tiles (an LM head): 192-column tiles with a 3-stage ring leave room for two
     // CTAs per SM, so one CTA's ramp and epilogue hide under the other's streaming; measured
     // 60.2 us against 71.2 - 78.3 us for one 208 ... 256-column CTA per SM at N = 151936.
@@ -982,6 +1057,8 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
     p.norm_input = static_cast<const __nv_bfloat16*>(input);
     p.norm_row_stride = input_row_stride;
     p.norm_eps = static_cast<float>(norm_eps);
+    p.norm_squares = norm_slices > 0 ? norm_squares : nullptr;
+    p.norm_slices = norm_slices;
   }
   if (m <= 64) {
     if (bn == 192 && ceil_div(n, 192) >= 4 * kNumSMs) return launch<192, 3, 64>(p, a_map, b_map, stream);
@@ -989,6 +1066,9 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
     if (bn > 64)
       return small_rings() && fold_norm ? launch<128, 4, 64>(p, a_map, b_map, stream)
                                         : launch<128, 8, 64>(p, a_map, b_map, stream);
+    // narrow tiles of a folded-norm projection: short rings, three CTAs per SM
+    if (small_rings() && fold_norm)
+      return bn > 32 ? launch<64, 4, 64>(p, a_map, b_map, stream) : launch<32, 4, 64>(p, a_map, b_map, stream);
     return launch<64, 12, 64>(p, a_map, b_map, stream);
   }
   if (persistent) return launch_persistent(p, a_map, b_map, stream);
@@ -1044,13 +1124,14 @@ int linear_partial_tcgen05(const void* input, const void* weight, float* partial
 
 int linear_splitk_residual_tcgen05(const void* input, const void* weight, const void* residual,
                                    void* output, int64_t m, int64_t k, int64_t n,
-                                   int64_t input_row_stride, int32_t* status, cudaStream_t stream) {
+                                   int64_t input_row_stride, int32_t* status, cudaStream_t stream,
+                                   float* squares_out) {
   const PartialPlan plan = plan_cluster(m, k, n);
   const int a_rows = m <= 64 ? 64 : 128;
   // enough N x M tiles to fill the GPU without cutting K: the plain kernel with the residual epilogue
   if (plan.splits <= 1)
     return linear_tcgen05(input, weight, nullptr, residual, output, m, k, n, input_row_stride,
-                          B200_EPILOGUE_RESIDUAL, status, stream, false, 0.0);
+                          B200_EPILOGUE_RESIDUAL, status, stream, false, 0.0, nullptr, 0);
   CUtensorMap a_map, b_map;
   if (!make_bf16_matrix_map(&a_map, input, m, k, input_row_stride, a_rows) ||
       !make_bf16_matrix_map(&b_map, weight, n, k, k, plan.bn))
@@ -1065,6 +1146,7 @@ int linear_splitk_residual_tcgen05(const void* input, const void* weight, const 
   p.k = static_cast<int>(k);
   p.n = static_cast<int>(n);
   p.epilogue = kEpilogueClusterResidual;
+  p.squares_out = squares_out;
   p.splits = plan.splits;
   p.bn = plan.bn;
   p.prefetch_weights = (launch_mode() & B200_LAUNCH_CONSTANT_WEIGHTS) != 0 ? 1 : 0;
@@ -1083,14 +1165,26 @@ int linear_splitk_residual_tcgen05(const void* input, const void* weight, const 
   return B200_ERR_UNSUPPORTED;
 }
 
+// Slices of row sums of squares that the cluster split-K projection leaves (N tiles x K slices);
+// 0 when the shape runs without a cluster (then nothing is written).
+int64_t linear_splitk_slices(int64_t m, int64_t k, int64_t n) {
+  const PartialPlan plan = plan_cluster(m, k, n);
+  return plan.splits <= 1 ? 0 : ceil_div(n, static_cast<int64_t>(plan.bn)) * plan.splits;
+}
+
 }  // namespace b200
 
 using namespace b200;
 
+extern "C" int64_t b200_linear_splitk_slices(int64_t m, int64_t k, int64_t n) {
+  if (m <= 0 || m > 256 || k <= 0 || n <= 0) return 0;
+  return linear_splitk_slices(m, k, n);
+}
+
 extern "C" int b200_linear_splitk_residual(const void* input, const void* weight,
-                                           const void* residual, void* output, int64_t m,
-                                           int64_t k, int64_t n, int64_t input_row_stride,
-                                           int32_t* status, void* stream) {
+                                           const void* residual, void* output,
+                                           void* row_squares_out, int64_t m, int64_t k, int64_t n,
+                                           int64_t input_row_stride, int32_t* status, void* stream) {
   if (!input || !weight || !residual || !output || m <= 0 || k <= 0 || n <= 0 ||
       input_row_stride < k)
     return B200_ERR_BAD_ARGUMENT;
@@ -1099,15 +1193,17 @@ extern "C" int b200_linear_splitk_residual(const void* input, const void* weight
   if (!aligned16(input) || !aligned16(weight) || !aligned16(residual) || !aligned16(output))
     return B200_ERR_ALIGNMENT;
   return linear_splitk_residual_tcgen05(input, weight, residual, output, m, k, n, input_row_stride,
-                                        status, static_cast<cudaStream_t>(stream));
+                                        status, static_cast<cudaStream_t>(stream),
+                                        static_cast<float*>(row_squares_out));
 }
 
 extern "C" int b200_linear_rms_input(const void* input, const void* folded_weight, const void* bias,
-                                     void* output, int64_t m, int64_t k, int64_t n,
-                                     int64_t input_row_stride, double epsilon, int epilogue,
-                                     int32_t* status, void* stream) {
+                                     void* output, const void* row_squares, int64_t row_square_slices,
+                                     int64_t m, int64_t k, int64_t n, int64_t input_row_stride,
+                                     double epsilon, int epilogue, int32_t* status, void* stream) {
   if (!input || !folded_weight || !output || m <= 0 || k <= 0 || n <= 0 || input_row_stride < k ||
-      !(epsilon >= 0.0))
+      !(epsilon >= 0.0) || row_square_slices < 0 || row_square_slices > 65535 ||
+      (row_square_slices > 0 && !row_squares))
     return B200_ERR_BAD_ARGUMENT;
   if (epilogue != B200_EPILOGUE_NONE && epilogue != B200_EPILOGUE_SWIGLU) return B200_ERR_BAD_ARGUMENT;
   if (epilogue == B200_EPILOGUE_SWIGLU && n % 2 != 0) return B200_ERR_BAD_ARGUMENT;
@@ -1115,7 +1211,8 @@ extern "C" int b200_linear_rms_input(const void* input, const void* folded_weigh
   if (k % 8 != 0 || input_row_stride % 8 != 0) return B200_ERR_UNSUPPORTED;
   if (!aligned16(input) || !aligned16(folded_weight)) return B200_ERR_ALIGNMENT;
   return linear_tcgen05(input, folded_weight, bias, nullptr, output, m, k, n, input_row_stride,
-                        epilogue, status, static_cast<cudaStream_t>(stream), true, epsilon);
+                        epilogue, status, static_cast<cudaStream_t>(stream), true, epsilon,
+                        static_cast<const float*>(row_squares), static_cast<int>(row_square_slices));
 }
 
 extern "C" int64_t b200_linear_partial_splits(int64_t m, int64_t k, int64_t n) {

@@ -339,61 +339,64 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
       // A wait that gives up ends this warp's work, but the warp keeps meeting the group at the
       // named barrier once per tile. (Every wait's outcome is made warp-uniform: the
       // tensor-memory accesses are warp-collective.)
-      // MASKED: this thread's 64 mask values of the tile travel while the tensor core computes S
-      uint32_t mask_pairs[MASKED ? 32 : 1];  // bf16 pairs (exact for 0 and -inf)
-      bool add_mask = false;
+      // MASKED: a tile of class "zero" takes the same path as the causal-proved kernel (raw scores,
+      // the scale folded into the exponent). For a "mixed" tile this thread's 64 mask values (two
+      // 128-byte lines of its mask row) are requested into L2 while the tensor core computes S,
+      // read once S is in registers, and the scores move to the log2 domain with the mask added.
+      // Nothing of the mask is held in registers across the wait: the kernel sits at its
+      // register cap, and the zero tiles are the common case.
+      bool mixed = false;  // uniform over the group
+      const float* mask_src = nullptr;
+      bool mask_whole = false;  // all 64 values exist: 16-byte loads
       if (MASKED) {
-        add_mask = class_row[g][lo + j] != 0;
-        if (add_mask) {
+        mixed = class_row[g][lo + j] != 0;
+        if (mixed) {
           const int q_abs = q0 + g * kTile + row, key_abs = (lo + j) * kTile + key0;
-          const float* src = p.mask + b * p.mask_stride_b + static_cast<int64_t>(q_abs) * p.mask_stride_q + key_abs;
-          if (q_abs < p.tokens && key_abs + 64 <= p.tokens) {
-#pragma unroll
-            for (int batch8 = 0; batch8 < 2; ++batch8) {
-              float4 m[8];
-#pragma unroll
-              for (int c = 0; c < 8; ++c) m[c] = __ldg(reinterpret_cast<const float4*>(src) + batch8 * 8 + c);
-#pragma unroll
-              for (int c = 0; c < 8; ++c) {
-                mask_pairs[batch8 * 16 + 2 * c] = pack_bf16x2(m[c].x, m[c].y);
-                mask_pairs[batch8 * 16 + 2 * c + 1] = pack_bf16x2(m[c].z, m[c].w);
-              }
-            }
-          } else {  // a ragged edge: rows past T add nothing, keys past T are masked out
-#pragma unroll
-            for (int i = 0; i < 64; i += 2) {
-              const float m0 = q_abs >= p.tokens ? 0.0f : (key_abs + i < p.tokens ? __ldg(src + i) : -INFINITY);
-              const float m1 = q_abs >= p.tokens ? 0.0f : (key_abs + i + 1 < p.tokens ? __ldg(src + i + 1) : -INFINITY);
-              mask_pairs[i / 2] = pack_bf16x2(m0, m1);
-            }
+          mask_src = p.mask + b * p.mask_stride_b + static_cast<int64_t>(min(q_abs, p.tokens - 1)) * p.mask_stride_q + key_abs;
+          mask_whole = q_abs < p.tokens && key_abs + 64 <= p.tokens;
+          if (mask_whole) {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(mask_src));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(mask_src + 32));
           }
         }
       }
+      const float to_log2 = MASKED && mixed ? 1.0f : p.scale_log2;
       ok = ok && __all_sync(0xffffffffu, mbarrier_wait_ready_first(smem_u32(&s_full[g]), j & 1, p.wait_limit));
       uint32_t s0[32], s1[32];  // this thread's half of the row of S
       __nv_bfloat16 half_max = __float2bfloat16_rn(0.0f);
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (MASKED) {
-          // scores to the log2 domain, mask added, one half at a time (registers)
+        if (MASKED && mixed) {
+          // scores to the log2 domain, mask added, one half at a time
+          const int q_abs = q0 + g * kTile + row, key_abs = (lo + j) * kTile + key0;
+          // (the tensor-memory wait is warp-collective: it stays outside the per-thread branches)
+          auto add_mask = [&](uint32_t (&s)[32], int first) {
+            float4 m[8];
+            if (mask_whole) {
+#pragma unroll
+              for (int c = 0; c < 8; ++c) m[c] = __ldg(reinterpret_cast<const float4*>(mask_src + first) + c);
+            } else {  // a ragged edge: rows past T add nothing, keys past T are masked out
+              auto value = [&](int i) {
+                return q_abs >= p.tokens ? 0.0f
+                       : (key_abs + first + i < p.tokens ? __ldg(mask_src + first + i) : -INFINITY);
+              };
+#pragma unroll
+              for (int c = 0; c < 8; ++c)
+                m[c] = make_float4(value(4 * c), value(4 * c + 1), value(4 * c + 2), value(4 * c + 3));
+            }
+            tmem_load_wait(s);
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              s[4 * c] = __float_as_uint(fmaf(__uint_as_float(s[4 * c]), p.scale_log2, m[c].x * kLog2e));
+              s[4 * c + 1] = __float_as_uint(fmaf(__uint_as_float(s[4 * c + 1]), p.scale_log2, m[c].y * kLog2e));
+              s[4 * c + 2] = __float_as_uint(fmaf(__uint_as_float(s[4 * c + 2]), p.scale_log2, m[c].z * kLog2e));
+              s[4 * c + 3] = __float_as_uint(fmaf(__uint_as_float(s[4 * c + 3]), p.scale_log2, m[c].w * kLog2e));
+            }
+          };
           tmem_load_32x32_issue(s_taddr, s0);
-          tmem_load_wait(s0);
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float m0 = add_mask ? bf16_lo(mask_pairs[i / 2]) * kLog2e : 0.0f;
-            const float m1 = add_mask ? bf16_hi(mask_pairs[i / 2]) * kLog2e : 0.0f;
-            s0[i] = __float_as_uint(fmaf(__uint_as_float(s0[i]), p.scale_log2, m0));
-            s0[i + 1] = __float_as_uint(fmaf(__uint_as_float(s0[i + 1]), p.scale_log2, m1));
-          }
+          add_mask(s0, 0);
           tmem_load_32x32_issue(s_taddr + 32, s1);
-          tmem_load_wait(s1);
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float m0 = add_mask ? bf16_lo(mask_pairs[16 + i / 2]) * kLog2e : 0.0f;
-            const float m1 = add_mask ? bf16_hi(mask_pairs[16 + i / 2]) * kLog2e : 0.0f;
-            s1[i] = __float_as_uint(fmaf(__uint_as_float(s1[i]), p.scale_log2, m0));
-            s1[i + 1] = __float_as_uint(fmaf(__uint_as_float(s1[i + 1]), p.scale_log2, m1));
-          }
+          add_mask(s1, 32);
         } else {
           tmem_load_32x32_issue(s_taddr, s0);
           tmem_load_32x32_issue(s_taddr + 32, s1);
@@ -436,10 +439,9 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
       // near the maximum, not equal to it.
       row_max_slot[j & 1][g][half][row] = half_max;
       asm volatile("bar.sync %0, 256;" ::"r"(group_barrier) : "memory");
-      // (MASKED scores are in the log2 domain already)
+      // (the scores of a mixed tile are in the log2 domain already)
       const float m_tile = fmaxf(__bfloat162float(half_max),
-                                 __bfloat162float(row_max_slot[j & 1][g][half ^ 1][row])) *
-                           (MASKED ? 1.0f : p.scale_log2);
+                                 __bfloat162float(row_max_slot[j & 1][g][half ^ 1][row])) * to_log2;
       if (ok && j == 0) m_ref = m_tile;  // O is still empty: the first product overwrites it
       if (ok && j > 0) {
         const bool raise = __any_sync(0xffffffffu, m_tile > m_ref + kRescaleThreshold);
@@ -466,7 +468,6 @@ prefill_attention_tcgen05_kernel(const PrefillTcParams p, const __grid_constant_
       if (!ok) continue;
       // (a reference of -inf, every key so far masked, must not turn -inf - -inf into NaN)
       const float neg_ref = MASKED && m_ref == -INFINITY ? 0.0f : -m_ref;
-      const float to_log2 = MASKED ? 1.0f : p.scale_log2;
       float sum0 = 0.0f, sum1 = 0.0f;
       auto emit = [&](const uint32_t (&s)[32], int c0) {  // 32 probabilities: exp2, sum, bf16, store
         uint32_t packed[16];

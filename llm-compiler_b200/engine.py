@@ -29,16 +29,24 @@ from typing import Dict, Optional
 import torch
 
 from . import kernels
-from .kv_state import ExecutionError, PreallocatedKVCacheState
+from .kv_state import ExecutionError, PagedKVCacheState, PreallocatedKVCacheState
 from .qwen2 import Qwen2Config, inverse_frequency
 
 
 class Qwen2Engine:
     def __init__(self, config: Qwen2Config, weights: Dict[str, torch.Tensor], *, batch: int,
                  capacity: int, numerical_mode: str = "fast",
-                 device: Optional[torch.device] = None) -> None:
+                 device: Optional[torch.device] = None, kv_layout: str = "contiguous",
+                 block_size: int = 128, num_blocks: Optional[int] = None) -> None:
+        """kv_layout "paged": K / V live in block pools of `num_blocks` blocks of `block_size`
+        tokens per layer (default: as many as the contiguous layout would hold) behind one block
+        table; `capacity` is then the longest context one sequence may reach. Blocks are handed
+        out on the host, ahead of the steps that need them."""
+
         if numerical_mode not in ("fast", "pytorch_compatible"):
             raise ValueError(f"unknown numerical mode {numerical_mode!r}")
+        if kv_layout not in ("contiguous", "paged"):
+            raise ValueError(f"unknown KV layout {kv_layout!r}")
         self.config = config
         self.batch = batch
         self.capacity = capacity
@@ -52,14 +60,31 @@ class Qwen2Engine:
         self.folded_norms = (self.dtype == torch.bfloat16 and numerical_mode == "fast" and
                              batch <= 64 and config.hidden_size % 8 == 0 and
                              os.environ.get("B200_DECODE_CHAIN", "folded") != "partials")
+        # the o projection leaves the row sums of squares that the gate|up projection's folded
+        # RMSNorm needs (B200_NORM_SQUARES=own: gate|up squares its input rows itself)
+        self.producer_squares = os.environ.get("B200_NORM_SQUARES", "producer") != "own"
         self._pack_weights(weights)
         self.inv_freq = inverse_frequency(config, self.device)
 
         layers = config.num_layers
+        self.paged = kv_layout == "paged"
         # length arena rows: [0, L) per-slot lengths, L = positions, L + 1 = attention lengths
-        self.state = PreallocatedKVCacheState.allocate(
-            num_layers=layers, batch=batch, capacity=capacity, kv_heads=config.num_kv_heads,
-            head_dim=config.head_dim, dtype=self.dtype, device=self.device, extra_length_rows=2)
+        if self.paged:
+            if self.dtype != torch.bfloat16:
+                raise ValueError("the paged KV layout holds bf16")
+            blocks = num_blocks if num_blocks is not None else batch * -(-capacity // block_size)
+            self.state = PagedKVCacheState.allocate_paged(
+                num_layers=layers, batch=batch, max_tokens=capacity, block_size=block_size,
+                num_blocks=blocks, kv_heads=config.num_kv_heads, head_dim=config.head_dim,
+                dtype=self.dtype, device=self.device, extra_length_rows=2)
+            self.capacity = capacity = self.state.capacity  # whole blocks
+        else:
+            self.state = PreallocatedKVCacheState.allocate(
+                num_layers=layers, batch=batch, capacity=capacity, kv_heads=config.num_kv_heads,
+                head_dim=config.head_dim, dtype=self.dtype, device=self.device, extra_length_rows=2)
+        # host mirror of the context lengths: which blocks the next steps need (paged layout)
+        self._host_lengths = [0] * batch
+        self._block_slack = 0  # steps every sequence can still take inside its reserved blocks
         arena = self.state._length_arena
         self.positions = arena[layers]
         self.attention_lengths = arena[layers + 1]
@@ -127,6 +152,12 @@ class Qwen2Engine:
             raise ExecutionError(f"prompt of {tokens} tokens exceeds capacity {self.capacity}")
         ids = input_ids.to(self.device)
         self.state._length_arena.zero_()
+        if self.paged:
+            for sequence in range(batch):
+                self.state.release(sequence)
+            self._host_lengths = [tokens] * batch
+            self._block_slack = 0
+            self._reserve_blocks()
         position_ids = torch.arange(tokens, dtype=torch.int64, device=self.device).repeat(batch, 1)
         x = kernels.b200_embedding(self.embed, ids)
         cosine, sine = kernels.b200_rope_table(position_ids, self.inv_freq, self.dtype)
@@ -142,7 +173,11 @@ class Qwen2Engine:
             v = qkv[..., q_size + kv_size:].view(batch, tokens, cfg.num_kv_heads,
                                                  cfg.head_dim).transpose(1, 2)
             q, k = kernels.b200_rope(q, k, cosine, sine)
-            kernels.b200_kv_store(self.state.keys[index], self.state.values[index], k, v, zeros)
+            if self.paged:
+                kernels.b200_paged_kv_store(self.state.keys[index], self.state.values[index],
+                                            self.state.block_table, k, v, zeros)
+            else:
+                kernels.b200_kv_store(self.state.keys[index], self.state.values[index], k, v, zeros)
             attn = kernels.b200_prefill_attention(q, k, v, None, scale=self.scale, causal=True,
                                                   numerical_mode=self.mode)
             attn = attn.transpose(1, 2).reshape(batch, tokens, q_size)  # a view: memory is B,T,H,D
@@ -179,10 +214,40 @@ class Qwen2Engine:
         self.attention_lengths.copy_(lengths + 1)
         if next_ids is not None:
             self.input_ids.copy_(next_ids.to(self.device))
+        self._host_lengths = [int(n) for n in lengths.tolist()]
+        self._block_slack = 0
+        self._reserve_blocks()
+
+    def _reserve_blocks(self) -> None:
+        """Paged layout: every sequence owns the blocks for its context plus at least one more
+        token before a step is launched; done a block ahead, so the host touches the table once
+        per block_size steps (the table's address is fixed: a captured graph sees the update)."""
+
+        if not self.paged or self._block_slack > 0:
+            return
+        size = self.state.block_size
+        self.state.reserve([min(n + size, self.capacity) for n in self._host_lengths])
+        self._block_slack = min(min(-(-(n + size) // size) * size, self.capacity) - n
+                                for n in self._host_lengths)
+
+    def sync_host_lengths(self) -> None:
+        """Re-reads the context lengths from the device (one synchronising copy): for callers
+        that set the length vectors themselves."""
+
+        self._host_lengths = [int(n) for n in self.positions.tolist()]
+        self._block_slack = 0
+        self._reserve_blocks()
+
+    def _count_step(self) -> None:
+        if self.paged:
+            self._host_lengths = [n + 1 for n in self._host_lengths]
+            self._block_slack -= 1
 
     # ------------------------------------------------------------------- decode ----
     def _decode_step(self) -> None:
-        if self.dtype == torch.bfloat16 and self.mode == "fast" and self.batch <= 128:
+        # (the paged layout has the folded five-launch chain and the separate kernels)
+        if self.dtype == torch.bfloat16 and self.mode == "fast" and self.batch <= 128 and \
+                (not self.paged or self.folded_norms):
             self._decode_step_chain()
         else:
             self._decode_step_separate()
@@ -216,15 +281,22 @@ class Qwen2Engine:
         for index, layer in enumerate(self.layers):
             partials, squares = kernels.b200_linear_partial(x, layer["qkv_w_folded"],
                                                             row_squares=True)
-            attn = kernels.b200_qkv_decode_attention(
-                partials, layer["qkv_b"], cosine, sine, self.state.keys[index],
-                self.state.values[index], self.attention_lengths, q_heads=cfg.num_heads,
-                scale=self.scale, split_tokens=self.split_tokens,
-                max_length_hint=self.max_length_hint, norm_row_squares=squares,
-                norm_hidden=cfg.hidden_size, norm_epsilon=eps)
-            x = kernels.b200_linear_splitk_residual(attn.view(batch, cfg.q_size), layer["o_w"], x)
+            common = dict(q_heads=cfg.num_heads, scale=self.scale, split_tokens=self.split_tokens,
+                          max_length_hint=self.max_length_hint, norm_row_squares=squares,
+                          norm_hidden=cfg.hidden_size, norm_epsilon=eps)
+            if self.paged:
+                attn = kernels.b200_paged_qkv_decode_attention(
+                    partials, layer["qkv_b"], cosine, sine, self.state.keys[index],
+                    self.state.values[index], self.state.block_table, self.attention_lengths, **common)
+            else:
+                attn = kernels.b200_qkv_decode_attention(
+                    partials, layer["qkv_b"], cosine, sine, self.state.keys[index],
+                    self.state.values[index], self.attention_lengths, **common)
+            x = kernels.b200_linear_splitk_residual(attn.view(batch, cfg.q_size), layer["o_w"], x,
+                                                    row_squares=self.producer_squares)
+            x, x_squares = x if self.producer_squares else (x, None)
             a = kernels.b200_linear_rms_input(x, layer["gate_up_w_folded"], epsilon=eps,
-                                              epilogue="swiglu")
+                                              epilogue="swiglu", row_squares=x_squares)
             x = kernels.b200_linear_splitk_residual(a, layer["down_w"], x)
         h = kernels.b200_rms_norm(x, self.final_norm, epsilon=eps, round_before_weight=True,
                                   numerical_mode=self.mode)
@@ -289,12 +361,21 @@ class Qwen2Engine:
             q = qkv[:, :q_size].view(batch, cfg.num_heads, cfg.head_dim)
             k = qkv[:, q_size:q_size + kv_size].view(batch, cfg.num_kv_heads, cfg.head_dim)
             v = qkv[:, q_size + kv_size:].view(batch, cfg.num_kv_heads, cfg.head_dim)
-            q = kernels.b200_rope_kv_store(q, k, v, cosine, sine, self.state.keys[index],
-                                           self.state.values[index], self.positions)
-            attn = kernels.b200_decode_attention(
-                q, self.state.keys[index], self.state.values[index], self.attention_lengths,
-                None, scale=self.scale, numerical_mode=self.mode,
-                split_tokens=self.split_tokens, max_length_hint=self.max_length_hint)
+            if self.paged:
+                q, k = kernels.b200_rope(q.unsqueeze(2), k.unsqueeze(2), cosine, sine)
+                kernels.b200_paged_kv_store(self.state.keys[index], self.state.values[index],
+                                            self.state.block_table, k, v.unsqueeze(2), self.positions)
+                attn = kernels.b200_paged_decode_attention(
+                    q, self.state.keys[index], self.state.values[index], self.state.block_table,
+                    self.attention_lengths, None, scale=self.scale, numerical_mode=self.mode,
+                    split_tokens=self.split_tokens, max_length_hint=self.max_length_hint)
+            else:
+                q = kernels.b200_rope_kv_store(q, k, v, cosine, sine, self.state.keys[index],
+                                               self.state.values[index], self.positions)
+                attn = kernels.b200_decode_attention(
+                    q, self.state.keys[index], self.state.values[index], self.attention_lengths,
+                    None, scale=self.scale, numerical_mode=self.mode,
+                    split_tokens=self.split_tokens, max_length_hint=self.max_length_hint)
             # o and down have few N tiles: at up to 256 bf16 rows they run as cluster split-K
             # projections that add the residual themselves (same rounding points)
             splitk = self.dtype == torch.bfloat16 and batch <= 256 and cfg.hidden_size % 4 == 0
@@ -343,6 +424,7 @@ class Qwen2Engine:
         workspace exists; lengths, positions and ids are restored afterwards (the KV row the
         warm-up wrote lies beyond the valid length and is overwritten by the real step)."""
 
+        self._reserve_blocks()
         saved_lengths = self.state._length_arena.clone()
         saved_ids = self.input_ids.clone()
         stream = torch.cuda.Stream(device=self.device)
@@ -374,11 +456,13 @@ class Qwen2Engine:
         """One decode step for the whole batch on device-resident inputs. Returns the device
         tensor of greedy tokens; with feed_back they become the next step's input ids."""
 
+        self._reserve_blocks()
         if self._graph is not None:
             self._graph.replay()
             self.logits = self._graph_logits
         else:
             self._decode_step()
+        self._count_step()
         if feed_back:
             self.input_ids.copy_(self.next_ids, non_blocking=True)
         return self.next_ids
@@ -390,8 +474,10 @@ class Qwen2Engine:
 
         self._host_ids.copy_(host_ids)
         if self._step_graph is not None:
+            self._reserve_blocks()
             self._step_graph.replay()
             self.logits = self._step_logits
+            self._count_step()
         else:
             self.input_ids.copy_(self._host_ids, non_blocking=True)
             self.decode_step(feed_back=False)

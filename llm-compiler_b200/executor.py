@@ -97,6 +97,10 @@ class B200Executor:
         self.classify_masks = classify_masks
         self.lowering_trace: List[Dict[str, Any]] = []
         self._constants: Dict[Any, Any] = {}  # weight-preparation results, by operand storage
+        # Row sums of squares that a cluster split-K projection left beside its output during the
+        # current run, by the output's address: (output, squares). The output is held here, so
+        # its memory cannot be handed to another tensor while the entry exists.
+        self._row_squares: Dict[int, Any] = {}
         self._handlers = {
             "kernel.b200.rms_norm": self._rms_norm,
             "kernel.b200.linear": self._linear,
@@ -150,6 +154,7 @@ class B200Executor:
         except SymbolError as error:
             raise ExecutionError(str(error)) from error
         trace = []
+        self._row_squares.clear()
         for operation in function.block.operations:
             handler = self._handlers.get(operation.name)
             if handler is None:
@@ -171,6 +176,7 @@ class B200Executor:
             for declared, runtime_value in zip(operation.results, results):
                 environment[declared.name] = runtime_value
             trace.append(operation.name)
+        self._row_squares.clear()
         outputs = tuple(environment[value.name] for value in function.returns)
         return ExecutionResult(outputs, tuple(trace), symbols)
 
@@ -252,8 +258,14 @@ class B200Executor:
                 tensor.dtype == torch.bfloat16 and rows <= 256 and weight.shape[0] % 4 == 0:
             # few N tiles at decode sizes: the cluster split-K projection that adds the residual
             # itself (same rounding points as the plain kernel's residual epilogue)
+            chain = rows <= self.CHAIN_ROWS  # a folded RMSNorm may follow: leave it the row squares
             flat = kernels.b200_linear_splitk_residual(
-                tensor.reshape(rows, tensor.shape[-1]), weight, residual.reshape(rows, weight.shape[0]))
+                tensor.reshape(rows, tensor.shape[-1]), weight, residual.reshape(rows, weight.shape[0]),
+                row_squares=chain)
+            if chain:
+                flat, squares = flat
+                if squares is not None:
+                    self._row_squares[flat.data_ptr()] = (flat, squares)
             return flat.view(residual.shape)
         with kernels.kernel_variants(linear=variant):
             return kernels.b200_linear(tensor, weight, bias, residual=residual, epilogue=epilogue)
@@ -274,8 +286,13 @@ class B200Executor:
         self.lowering_trace.append({"backend": "b200", "op": "norm_linear", "rows": rows,
                                     "folded": rows <= self.CHAIN_ROWS})
         if rows <= self.CHAIN_ROWS and tensor.dtype == torch.bfloat16:
-            flat = kernels.b200_linear_rms_input(tensor.reshape(rows, tensor.shape[-1]), folded, bias,
-                                                 epsilon=epsilon, epilogue=epilogue)
+            rows_2d = tensor.reshape(rows, tensor.shape[-1])
+            left = self._row_squares.get(rows_2d.data_ptr())
+            squares = None
+            if left is not None and left[0].shape == rows_2d.shape and left[1].shape[1] == rows:
+                squares = left[1]  # what the projection that produced these rows left
+            flat = kernels.b200_linear_rms_input(rows_2d, folded, bias, epsilon=epsilon,
+                                                 epilogue=epilogue, row_squares=squares)
             return flat.view(*tensor.shape[:-1], flat.shape[-1])
         normed = kernels.b200_rms_norm(tensor, norm_weight, epsilon=epsilon,
                                        round_before_weight=bool(attributes.get("round_before_weight")),
@@ -297,9 +314,9 @@ class B200Executor:
         offset = int(attributes.get("length_offset", 0))
         rows = tensor.numel() // tensor.shape[-1]
         if isinstance(state, PagedKVCacheState):
-            return self._qkv_decode_attention_paged(state, slot, tensor, norm_weight, weight, bias, cosine,
-                                                    sine, mask, q_heads, kv_heads, dim, epsilon, scale,
-                                                    offset, attributes)
+            return self._qkv_decode_attention_paged(state, slot, tensor, norm_weight, weight, folded, bias,
+                                                    cosine, sine, mask, q_heads, kv_heads, dim, epsilon,
+                                                    scale, offset, attributes)
         key_buffer, value_buffer, lengths = state._slot(slot)
         if key_buffer.shape[0] != rows or key_buffer.shape[2] != kv_heads or key_buffer.shape[3] != dim:
             raise ExecutionError("qkv_decode_attention: the KV state does not match batch, heads or head_dim")
@@ -413,12 +430,30 @@ class B200Executor:
                                              value_buffer, positions)
         return rotated, state
 
-    def _qkv_decode_attention_paged(self, state, slot, tensor, norm_weight, weight, bias, cosine, sine,
-                                    mask, q_heads, kv_heads, dim, epsilon, scale, offset, attributes):
-        """The fused decode-layer op on a paged state: the same ops, one kernel each, through the
-        state's own store / attention methods (the fused kernels address contiguous slots)."""
+    def _qkv_decode_attention_paged(self, state, slot, tensor, norm_weight, weight, folded, bias, cosine,
+                                    sine, mask, q_heads, kv_heads, dim, epsilon, scale, offset, attributes):
+        """The fused decode-layer op on a paged state: up to CHAIN_ROWS bf16 rows the same two
+        launches as on the contiguous layout, through the block table; beyond, the same ops one
+        kernel each through the state's own store / attention methods."""
 
         rows = tensor.numel() // tensor.shape[-1]
+        bound = mask.shape[-1] if mask is not None else state.capacity
+        if bound > state.capacity:
+            raise ExecutionError("decode attention mask is longer than the KV capacity")
+        self.lowering_trace.append({"backend": "b200", "op": "qkv_decode_attention", "rows": rows,
+                                    "fused": rows <= self.CHAIN_ROWS, "length_offset": offset,
+                                    "layout": "paged"})
+        if rows <= self.CHAIN_ROWS and tensor.dtype == torch.bfloat16:
+            flat = tensor.reshape(rows, tensor.shape[-1])
+            partials, squares = kernels.b200_linear_partial(flat, folded, row_squares=True)
+            pool_key, pool_value, lengths = state._slot(slot)
+            if offset == 0:  # the graph advances this slot here: lengths then count the new token
+                state = state.advance(slot, delta=1)
+            context = kernels.b200_paged_qkv_decode_attention(
+                partials, bias, cosine, sine, pool_key, pool_value, state.block_table, lengths,
+                q_heads=q_heads, scale=scale, max_length_hint=bound, length_offset=offset,
+                norm_row_squares=squares, norm_hidden=flat.shape[1], norm_epsilon=epsilon)
+            return context.view(rows, 1, q_heads * dim), state
         normed = kernels.b200_rms_norm(tensor, norm_weight, epsilon=epsilon,
                                        round_before_weight=bool(attributes.get("round_before_weight")),
                                        numerical_mode="fast")

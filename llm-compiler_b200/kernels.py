@@ -1006,6 +1006,62 @@ def b200_qkv_decode_attention(partials: torch.Tensor, bias: Optional[torch.Tenso
     return output
 
 
+def b200_paged_qkv_decode_attention(partials: torch.Tensor, bias: Optional[torch.Tensor],
+                                    cosine: torch.Tensor, sine: torch.Tensor, key_pool: torch.Tensor,
+                                    value_pool: torch.Tensor, block_table: torch.Tensor,
+                                    lengths: torch.Tensor, *, q_heads: int, scale: float,
+                                    split_tokens: int = 0, max_length_hint: int = 0,
+                                    length_offset: int = 0,
+                                    norm_row_squares: Optional[torch.Tensor] = None,
+                                    norm_hidden: int = 0, norm_epsilon: float = 0.0) -> torch.Tensor:
+    """b200_qkv_decode_attention on the paged layout: K / V pools [blocks, block_size, Hkv, D]
+    and an int32 block table [B, max_blocks]; the new token's row goes to the block the table
+    names for position lengths[b] - 1 (a missing block raises the KV-overflow status bit)."""
+
+    device = _require_cuda(partials, bias, cosine, sine, key_pool, value_pool, block_table, lengths,
+                           norm_row_squares)
+    if norm_row_squares is not None and (
+            norm_row_squares.shape != partials.shape[:2] or norm_row_squares.dtype != torch.float32
+            or not norm_row_squares.is_contiguous() or norm_hidden <= 0):
+        raise ValueError("norm_row_squares must be contiguous fp32 [splits, B] with norm_hidden > 0")
+    splits, batch, width = partials.shape
+    blocks, block_size, kv_heads, dim = key_pool.shape
+    if partials.dtype != torch.float32 or key_pool.dtype != torch.bfloat16:
+        raise ValueError("fp32 partials and bf16 KV pools expected")
+    if width != (q_heads + 2 * kv_heads) * dim or value_pool.shape != key_pool.shape:
+        raise ValueError("partials do not match the head layout of the KV pools")
+    if block_table.dtype != torch.int32 or block_table.ndim != 2 or block_table.shape[0] != batch \
+            or not block_table.is_contiguous():
+        raise ValueError("block_table must be a contiguous int32 [B, max_blocks] tensor")
+    if block_size % 32 != 0:
+        raise ValueError("block_size must be a multiple of 32 tokens")
+    if not (key_pool.is_contiguous() and value_pool.is_contiguous() and partials.is_contiguous()):
+        raise ValueError("partials and KV pools must be contiguous")
+    cos2, sin2 = cosine.reshape(batch, dim), sine.reshape(batch, dim)
+    if not (cos2.is_contiguous() and sin2.is_contiguous()):
+        raise ValueError("cosine / sine must be contiguous")
+    lengths = _dense_index(lengths, "lengths")
+    output = torch.empty((batch, q_heads, 1, dim), dtype=torch.bfloat16, device=device)
+    rt = runtime(device)
+    library = _lib.load()
+    max_blocks = block_table.shape[1]
+    capacity = max_blocks * block_size
+    max_length = min(max_length_hint, capacity) if max_length_hint > 0 else capacity
+    need = int(library.b200_decode_attention_workspace_bytes(batch, q_heads, kv_heads, dim,
+                                                            max_length, split_tokens))
+    workspace = rt.workspace("decode_attention", need)
+    code = library.b200_paged_qkv_decode_attention(
+        partials.data_ptr(), splits, _ptr(bias), cos2.data_ptr(), sin2.data_ptr(),
+        key_pool.data_ptr(), value_pool.data_ptr(), block_table.data_ptr(), lengths.data_ptr(),
+        output.data_ptr(), batch, q_heads, kv_heads, dim, blocks, block_size, max_blocks, capacity,
+        float(scale), int(split_tokens), int(max_length_hint), int(length_offset),
+        _ptr(norm_row_squares), int(norm_hidden), float(norm_epsilon), _ptr(workspace), need,
+        rt.status.data_ptr(), _stream())
+    _check(code, "b200_paged_qkv_decode_attention")
+    _count(rt)
+    return output
+
+
 def b200_scale_columns(weight: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
     """Weight preparation: weight[n, k] * scale[k], rounded to the weight dtype -- a norm
     weight folded into the projection that follows the norm. A one-time device pass."""
@@ -1026,11 +1082,14 @@ def b200_scale_columns(weight: torch.Tensor, scale: torch.Tensor) -> torch.Tenso
 
 def b200_linear_rms_input(tensor: torch.Tensor, folded_weight: torch.Tensor,
                           bias: Optional[torch.Tensor] = None, *, epsilon: float,
-                          epilogue: str = "none") -> torch.Tensor:
+                          epilogue: str = "none",
+                          row_squares: Optional[torch.Tensor] = None) -> torch.Tensor:
     """serve.rms_norm + serve.linear in one launch (fast mode, bf16, at most 64 rows): `tensor`
     is the un-normalised input, `folded_weight` the projection weight with the norm weight
     multiplied into its columns (b200_scale_columns); the kernel scales each accumulator row by
-    rsqrt(mean(x^2) + epsilon) before the bias / SwiGLU epilogue."""
+    rsqrt(mean(x^2) + epsilon) before the bias / SwiGLU epilogue. `row_squares` (fp32
+    [slices, M], what b200_linear_splitk_residual(..., row_squares=True) left for these very
+    rows): the kernel adds the slices instead of squaring the rows itself."""
 
     device = _require_cuda(tensor, folded_weight, bias)
     if tensor.ndim != 2 or folded_weight.ndim != 2 or tensor.shape[1] != folded_weight.shape[1]:
@@ -1045,11 +1104,19 @@ def b200_linear_rms_input(tensor: torch.Tensor, folded_weight: torch.Tensor,
     n = folded_weight.shape[0]
     if bias is not None and (bias.shape != (n,) or bias.dtype != torch.bfloat16):
         raise ValueError("bias must be a bf16 vector of N elements")
+    slices = 0
+    if row_squares is not None:
+        _require_cuda(tensor, row_squares)
+        if row_squares.dtype != torch.float32 or row_squares.ndim != 2 or \
+                row_squares.shape[1] != m or not row_squares.is_contiguous():
+            raise ValueError("row_squares must be a contiguous fp32 [slices, M] tensor")
+        slices = row_squares.shape[0]
     output = torch.empty((m, n // 2 if epilogue == "swiglu" else n), dtype=torch.bfloat16,
                          device=device)
     rt = runtime(device)
     code = _lib.load().b200_linear_rms_input(
-        tensor.data_ptr(), folded_weight.data_ptr(), _ptr(bias), output.data_ptr(), m, k, n,
+        tensor.data_ptr(), folded_weight.data_ptr(), _ptr(bias), output.data_ptr(),
+        _ptr(row_squares) if slices else None, slices, m, k, n,
         tensor.stride(0), float(epsilon), _EPILOGUES[epilogue], rt.status.data_ptr(), _stream())
     _check(code, "b200_linear_rms_input")
     _count(rt)
@@ -1057,10 +1124,13 @@ def b200_linear_rms_input(tensor: torch.Tensor, folded_weight: torch.Tensor,
 
 
 def b200_linear_splitk_residual(tensor: torch.Tensor, weight: torch.Tensor,
-                                residual: torch.Tensor) -> torch.Tensor:
+                                residual: torch.Tensor, *, row_squares: bool = False):
     """serve.linear + aten.add in one launch at decode sizes (bf16, at most 256 rows):
     r(r(x W^T) + residual). The K slices of an output tile are the CTAs of one thread-block
-    cluster and add their fp32 accumulators through distributed shared memory."""
+    cluster and add their fp32 accumulators through distributed shared memory. With
+    `row_squares` the result is (output, squares): fp32 [slices, M] partial sums of the squared
+    output rows for a folded RMSNorm behind this projection (b200_linear_rms_input), or None
+    where the shape runs without a cluster and leaves none."""
 
     device = _require_cuda(tensor, weight, residual)
     if tensor.ndim != 2 or weight.ndim != 2 or tensor.shape[1] != weight.shape[1]:
@@ -1076,14 +1146,21 @@ def b200_linear_splitk_residual(tensor: torch.Tensor, weight: torch.Tensor,
         raise ValueError("input rows and the weight must be contiguous")
     output = torch.empty((m, n), dtype=torch.bfloat16, device=device)
     rt = runtime(device)
-    code = _lib.load().b200_linear_splitk_residual(
-        tensor.data_ptr(), weight.data_ptr(), residual.data_ptr(), output.data_ptr(), m, k, n,
-        tensor.stride(0), rt.status.data_ptr(), _stream())
+    library = _lib.load()
+    squares = None
+    if row_squares:
+        slices = library.b200_linear_splitk_slices(m, k, n) if m <= 256 else 0
+        if slices > 0:
+            squares = torch.empty((slices, m), dtype=torch.float32, device=device)
+    code = library.b200_linear_splitk_residual(
+        tensor.data_ptr(), weight.data_ptr(), residual.data_ptr(), output.data_ptr(),
+        _ptr(squares), m, k, n, tensor.stride(0), rt.status.data_ptr(), _stream())
     if code == _lib.ERR_UNSUPPORTED:  # no cluster plan for this shape: the general projection
-        return b200_linear(tensor, weight, residual=residual, epilogue="residual")
+        output = b200_linear(tensor, weight, residual=residual, epilogue="residual")
+        return (output, None) if row_squares else output
     _check(code, "b200_linear_splitk_residual")
     _count(rt)
-    return output
+    return (output, squares) if row_squares else output
 
 
 def interleave_gate_up(gate_weight: torch.Tensor, up_weight: torch.Tensor) -> torch.Tensor:

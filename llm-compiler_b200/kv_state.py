@@ -240,14 +240,16 @@ class PagedKVCacheState(PreallocatedKVCacheState):
     @classmethod
     def allocate_paged(cls, *, num_layers: int, batch: int, max_tokens: int, block_size: int,
                        num_blocks: int, kv_heads: int, head_dim: int, dtype: torch.dtype,
-                       device: torch.device | str) -> "PagedKVCacheState":
+                       device: torch.device | str, extra_length_rows: int = 0) -> "PagedKVCacheState":
         if block_size <= 0 or block_size % 32 != 0:
             raise ExecutionError("the block size must be a positive multiple of 32 tokens")
         max_blocks = -(-max_tokens // block_size)
         key_pool = torch.zeros((num_layers, num_blocks, block_size, kv_heads, head_dim), dtype=dtype,
                                device=device)
         value_pool = torch.zeros_like(key_pool)
-        length_arena = torch.zeros((num_layers, batch), dtype=torch.int64, device=device)
+        # (extra rows: an engine's own length vectors, advanced by the same launch as the slots')
+        length_arena = torch.zeros((num_layers + extra_length_rows, batch), dtype=torch.int64,
+                                   device=device)
         state = cls(tuple(key_pool[i] for i in range(num_layers)),
                     tuple(value_pool[i] for i in range(num_layers)),
                     tuple(length_arena[i] for i in range(num_layers)), max_blocks * block_size)

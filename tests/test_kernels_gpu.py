@@ -810,6 +810,59 @@ def test_linear_rms_input_matches_rms_norm_then_linear(m, k, n, epilogue):
     kernels.runtime().check_status()
 
 
+@pytest.mark.parametrize("m,k,n", [(64, 896, 896), (64, 4864, 896), (3, 256, 256), (33, 3584, 3584),
+                                   (7, 960, 1092), (128, 896, 896), (256, 3584, 3584)])
+def test_linear_splitk_residual_leaves_row_sums_of_squares(m, k, n):
+    """With row_squares the cluster split-K projection also leaves sum(output_r^2) in slices
+    (one per N tile and K slice): their sum over the slices is the sum of squares of the stored
+    bf16 rows, the output itself is unchanged, and a shape that runs without a cluster says so
+    by returning None."""
+    g = torch.Generator().manual_seed(m * 3 + k + n)
+    x = torch.randn(m, k, generator=g).bfloat16().cuda()
+    w = (torch.randn(n, k, generator=g) * k ** -0.5).bfloat16().cuda()
+    residual = torch.randn(m, n, generator=g).bfloat16().cuda()
+    plain = kernels.b200_linear_splitk_residual(x, w, residual)
+    out, squares = kernels.b200_linear_splitk_residual(x, w, residual, row_squares=True)
+    assert torch.equal(out, plain)
+    if squares is None:
+        assert kernels._lib.load().b200_linear_splitk_slices(m, k, n) == 0
+    else:
+        assert squares.shape == (kernels._lib.load().b200_linear_splitk_slices(m, k, n), m)
+        expected = out.double().pow(2).sum(dim=1)
+        assert torch.allclose(squares.double().sum(dim=0), expected, rtol=1e-5, atol=1e-5)
+        again = kernels.b200_linear_splitk_residual(x, w, residual, row_squares=True)[1]
+        assert torch.equal(squares, again)
+    kernels.runtime().check_status()
+
+
+@pytest.mark.parametrize("epilogue", ["none", "swiglu"])
+@pytest.mark.parametrize("m,k_in,hidden,n", [(64, 896, 896, 9728), (64, 4864, 896, 1152), (5, 256, 256, 1024),
+                                             (33, 512, 1536, 2304)])
+def test_linear_rms_input_takes_the_producers_row_squares(m, k_in, hidden, n, epilogue):
+    """The folded-RMSNorm projection fed with the row sums of squares that the projection before
+    it left (o projection -> gate|up in a decode layer): same result as squaring the rows itself
+    up to the order of an fp32 sum, and the oracle's rms_norm -> linear (-> SwiGLU)."""
+    g = torch.Generator().manual_seed(m + k_in + hidden + n)
+    a = torch.randn(m, k_in, generator=g).bfloat16()
+    wo = (torch.randn(hidden, k_in, generator=g) * k_in ** -0.5).bfloat16()
+    residual = (torch.randn(m, hidden, generator=g) * 2.0).bfloat16()
+    norm_w = (1.0 + 0.2 * torch.randn(hidden, generator=g)).bfloat16()
+    w = (torch.randn(n, hidden, generator=g) * hidden ** -0.5).bfloat16()
+    x, squares = kernels.b200_linear_splitk_residual(a.cuda(), wo.cuda(), residual.cuda(), row_squares=True)
+    folded = kernels.b200_scale_columns(w.cuda(), norm_w.cuda())
+    own = kernels.b200_linear_rms_input(x, folded, epsilon=1e-6, epilogue=epilogue)
+    if squares is None:
+        pytest.skip("this shape runs without a cluster: no slices to hand over")
+    fed = kernels.b200_linear_rms_input(x, folded, epsilon=1e-6, epilogue=epilogue, row_squares=squares)
+    assert (fed.float() - own.float()).abs().max().item() <= 2.0 ** -7 * own.float().abs().max().item() + 1e-6
+    y = serve_ops.linear(serve_ops.rms_norm(x.cpu(), norm_w, 1e-6, round_before_weight=True), w)
+    ref = serve_ops.swiglu(y[:, 0::2], y[:, 1::2]) if epilogue == "swiglu" else y
+    close(fed, ref, BF16_TOL)
+    with pytest.raises(ValueError):  # slices for another row count
+        kernels.b200_linear_rms_input(x, folded, epsilon=1e-6, row_squares=squares[:, :-1].contiguous())
+    kernels.runtime().check_status()
+
+
 def test_fused_attention_applies_the_folded_norm():
     """b200_qkv_decode_attention with norm_input: the q|k|v partials come from un-normalised
     rows and a norm-folded weight; the result and the stored K / V rows must match the oracle's

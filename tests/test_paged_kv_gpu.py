@@ -13,6 +13,7 @@ import llm_compiler_b200 as b200
 from llm_compiler_b200 import kernel_ir as ir
 from llm_compiler_b200 import kernels
 from llm_compiler_b200 import qwen2 as q2
+from llm_compiler_b200.engine import Qwen2Engine
 from llm_compiler_b200.executor import B200Executor, bind_arguments
 from llm_compiler_b200.kv_state import ExecutionError, PagedKVCacheState
 
@@ -74,6 +75,58 @@ def test_paged_store_and_decode_attention_match_the_contiguous_oracle(hq, hkv, d
     state.check()
 
 
+@pytest.mark.parametrize("hq,hkv,d", [(14, 2, 64), (28, 4, 128)])
+@pytest.mark.parametrize("block_size", [32, 128])
+def test_fused_qkv_attention_on_pools_equals_the_contiguous_launch(hq, hkv, d, block_size):
+    """The decode layer's fused launch (q|k|v reduced from split-K partials, folded-RMSNorm factor,
+    bias, RoPE, KV store, attention) through a block table: output and stored rows bit-equal to
+    the same launch on contiguous buffers holding the same logical KV; a sequence whose next row
+    has no block raises the overflow bit and writes nothing."""
+    g = torch.Generator().manual_seed(hq * 7 + block_size)
+    hidden, capacity = 256, 512
+    lengths = torch.tensor([1, 64, 65, 200, 511, 131])  # attention lengths, the new token counted
+    batch = lengths.numel()
+    width = (hq + 2 * hkv) * d
+    x = (torch.randn(batch, hidden, generator=g) * 2.0).bfloat16().cuda()
+    norm_w = (1.0 + 0.2 * torch.randn(hidden, generator=g)).bfloat16().cuda()
+    w = (torch.randn(width, hidden, generator=g) * 0.05).bfloat16().cuda()
+    bias = torch.randn(width, generator=g).bfloat16().cuda()
+    cos, sin = serve_ops.rope_table((lengths - 1).view(batch, 1), serve_ops.rope_inverse_frequency(d, 1e6),
+                                    torch.bfloat16)
+    kbuf = torch.randn(batch, capacity, hkv, d, generator=g).bfloat16().cuda()
+    vbuf = torch.randn(batch, capacity, hkv, d, generator=g).bfloat16().cuda()
+    state = PagedKVCacheState.allocate_paged(
+        num_layers=1, batch=batch, max_tokens=capacity, block_size=block_size,
+        num_blocks=batch * capacity // block_size, kv_heads=hkv, head_dim=d, dtype=torch.bfloat16,
+        device="cuda")
+    order = torch.randperm(batch * capacity // block_size, generator=g).tolist()
+    state.reserve([capacity] * batch, order=order)
+    state.store(0, kbuf.transpose(1, 2), vbuf.transpose(1, 2), torch.zeros(batch, dtype=torch.int64, device="cuda"))
+    folded = kernels.b200_scale_columns(w, norm_w)
+    partials, squares = kernels.b200_linear_partial(x, folded, row_squares=True)
+    device_lengths = lengths.cuda()
+    common = dict(q_heads=hq, scale=d ** -0.5, norm_row_squares=squares, norm_hidden=hidden, norm_epsilon=1e-6)
+    flat = kernels.b200_qkv_decode_attention(partials, bias, cos.cuda(), sin.cuda(), kbuf, vbuf,
+                                             device_lengths, **common)
+    paged = kernels.b200_paged_qkv_decode_attention(partials, bias, cos.cuda(), sin.cuda(), state.keys[0],
+                                                    state.values[0], state.block_table, device_lengths,
+                                                    **common)
+    assert torch.equal(paged, flat)
+    for b in range(batch):
+        got_k, got_v = state.gather(0, b, int(lengths[b]))
+        assert torch.equal(got_k, kbuf[b, :lengths[b]]) and torch.equal(got_v, vbuf[b, :lengths[b]])
+    kernels.runtime().check_status()
+    # sequence 3 loses its blocks: its new row has nowhere to go
+    state.release(3)
+    before_k = state.keys[0].clone()
+    kernels.b200_paged_qkv_decode_attention(partials, bias, cos.cuda(), sin.cuda(), state.keys[0],
+                                            state.values[0], state.block_table, device_lengths, **common)
+    with pytest.raises((ExecutionError, ValueError, RuntimeError)):
+        kernels.runtime().check_status()
+    rows_written = (state.keys[0] != before_k).flatten(2).any(dim=2).sum().item()
+    assert rows_written == 0  # the other sequences rewrote identical rows, sequence 3 wrote none
+
+
 def test_a_pool_smaller_than_batch_times_capacity_serves_ragged_sequences():
     """Four sequences of 2000 / 100 / 64 / 1500 tokens with a logical capacity of 2048: contiguous
     slots need 4 x 16 blocks of 128 tokens, the pool holds 32; a fifth long sequence does not fit
@@ -95,6 +148,49 @@ def test_a_pool_smaller_than_batch_times_capacity_serves_ragged_sequences():
     state.store(0, key, key, torch.tensor([0, 2000, 0, 0], device="cuda"))  # sequence 1 owns 1 block
     with pytest.raises(ExecutionError):
         state.check()
+
+
+@pytest.mark.parametrize("batch,mode", [(4, "fast"), (64, "fast"), (70, "fast"), (4, "pytorch_compatible")])
+def test_engine_on_the_paged_layout_equals_the_contiguous_engine(batch, mode):
+    """Qwen2Engine(kv_layout="paged"): prefill stores through the block table, the decode step
+    (the five-launch chain up to 64 sequences, the separate kernels beyond and in the compatible
+    mode) reads and appends through it, blocks are handed out a block ahead of the captured
+    graph's replays. 32-token blocks and 45 steps from a 50-token prompt: every sequence crosses
+    a block boundary under graph replay. Logits and tokens bit-equal to the contiguous
+    engine (same kernels, same arithmetic, another address map)."""
+    config = q2.Qwen2Config(hidden_size=896, intermediate_size=4864, num_layers=3, num_heads=14,
+                            num_kv_heads=2, rms_norm_eps=1e-6, rope_theta=1e6, vocab_size=8192,
+                            tie_word_embeddings=True)
+    weights = {k: v.cuda() for k, v in q2.make_weights(config, seed=9, dtype=torch.bfloat16).items()}
+    prompt = q2.make_prompt_ids(config, batch, 50, seed=4)
+    # 65 - 128 sequences: the contiguous engine runs its seven-launch chain, the paged one the
+    # separate kernels (other summation orders): compared within the bf16 tolerance, teacher-forced
+    exact = not (mode == "fast" and 64 < batch <= 128)
+    runs = {}
+    for layout in ("contiguous", "paged"):
+        engine = Qwen2Engine(config, weights, batch=batch, capacity=128, numerical_mode=mode,
+                             kv_layout=layout, block_size=32)
+        engine.prefill(prompt)
+        record = [engine.logits.clone()]
+        forced = runs.get("contiguous")
+        for step in range(45):
+            if step == 1:
+                engine.capture()  # the first step ran eagerly
+            if forced is not None:
+                engine.input_ids.copy_(forced[2 * step + 1])
+            record.append(engine.input_ids.clone())
+            engine.decode_step(feed_back=forced is None)
+            record.append(engine.logits.clone())
+        engine.state.check()
+        runs[layout] = record
+        if layout == "paged":
+            assert engine.state.blocks_in_use() == batch * 3  # 95 tokens held: 3 of the 4 blocks a slot would pin
+    for flat, paged in zip(runs["contiguous"], runs["paged"]):
+        if exact or flat.dtype == torch.int64:
+            assert torch.equal(flat, paged)
+        else:
+            scale = float(flat.float().abs().max())
+            assert float((flat.float() - paged.float()).abs().max()) <= max(5e-2 * scale, 2e-3)
 
 
 @pytest.mark.parametrize("chain", [True, False])
