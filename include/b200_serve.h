@@ -176,6 +176,20 @@ int b200_decode_attention(const void* query, const void* key_buffer, const void*
                           int mode, int64_t split_tokens, int64_t max_length_hint,
                           void* workspace, int64_t workspace_bytes, int32_t* status,
                           void* stream);
+/* The same with a service order (bf16): the i-th group of CTAs serves sequence sequence_order[i]
+ * (int32 [batch], a permutation of 0 .. batch-1; an entry outside that range skips its group).
+ * CTAs are placed in grid order, so listing the longest sequences first gives longest-first
+ * scheduling when the (sequence, KV head) pairs outnumber the CTAs the GPU holds at once; the
+ * result does not depend on the order. No counterpart in the reference. */
+int b200_decode_attention_ordered(const void* query, const void* key_buffer, const void* value_buffer,
+                                  const int64_t* lengths, const void* mask, void* output,
+                                  const int32_t* sequence_order, int64_t batch, int64_t q_heads,
+                                  int64_t kv_heads, int64_t head_dim, int64_t capacity,
+                                  int64_t mask_len, int64_t q_batch_stride, int64_t q_head_stride,
+                                  int64_t mask_batch_stride, int mask_dtype, double scale, int dtype,
+                                  int mode, int64_t split_tokens, int64_t max_length_hint,
+                                  void* workspace, int64_t workspace_bytes, int32_t* status,
+                                  void* stream);
 
 /* Decode attention for callers that must not allocate device memory (no counterpart in
  * the reference, whose wrappers allocate with torch.empty on every call). Some hosts of

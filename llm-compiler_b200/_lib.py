@@ -63,6 +63,9 @@ SIGNATURES = {
                                                                        c_int, c_int64, c_int64,
                                                                        c_void_p, c_int64, c_void_p,
                                                                        c_void_p]),
+    "b200_decode_attention_ordered": (c_int, [c_void_p] * 7 + [c_int64] * 9 +
+                                      [c_int, c_double, c_int, c_int, c_int64, c_int64,
+                                       c_void_p, c_int64, c_void_p, c_void_p]),
     "b200_decode_attention_static_scratch_bytes": (c_int64, []),
     "b200_decode_attention_static_scratch": (c_int, [c_void_p] * 6 + [c_int64] * 9 +
                                              [c_int, c_double, c_int, c_int, c_int64, c_int64,

@@ -80,6 +80,10 @@ struct DecodeParams {
   // row t % block_size. block_size is a multiple of the tokens a warp copies per step, so a copy
   // never straddles two blocks. `capacity` is then table_stride * block_size.
   const int32_t* block_table = nullptr;
+  // order != nullptr: grid z = i serves sequence order[i] (a permutation of 0 .. batch-1). CTAs
+  // are placed in grid order, so a caller that lists the longest sequences first gets
+  // longest-first scheduling when the grid is several waves of CTAs.
+  const int32_t* order = nullptr;
   int block_size = 0, table_stride = 0;
   int64_t pool_rows = 0;  // blocks x block_size: the extent of the pools' tensor maps
   uint32_t wait_limit = 4000000u;  // polls of a bounded wait
@@ -492,7 +496,8 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
 
   const int split = blockIdx.x;
   const int head_block = blockIdx.y;  // kv head * blocks-per-kv-head + 16-row block
-  const int b = blockIdx.z;
+  const int b = p.order != nullptr ? __ldg(p.order + blockIdx.z) : static_cast<int>(blockIdx.z);
+  if (b < 0 || b >= p.batch) return;  // (not a permutation: every CTA of that z leaves alike)
   const int row_blocks = (p.groups + 15) / 16;
   const int kvh = head_block / row_blocks;
   const int g0 = (head_block % row_blocks) * 16;  // first group row of this CTA
@@ -1306,16 +1311,16 @@ extern "C" int64_t b200_decode_attention_workspace_bytes(int64_t batch, int64_t 
   return workspace_bytes_for(batch, q_heads, head_dim, splits);
 }
 
-extern "C" int b200_decode_attention(const void* query, const void* key_buffer,
-                                     const void* value_buffer, const int64_t* lengths,
-                                     const void* mask, void* output, int64_t batch,
-                                     int64_t q_heads, int64_t kv_heads, int64_t head_dim,
-                                     int64_t capacity, int64_t mask_len, int64_t q_batch_stride,
-                                     int64_t q_head_stride, int64_t mask_batch_stride,
-                                     int mask_dtype, double scale, int dtype, int mode,
-                                     int64_t split_tokens, int64_t max_length_hint,
-                                     void* workspace, int64_t workspace_bytes, int32_t* status,
-                                     void* stream) {
+static int decode_attention_impl(const void* query, const void* key_buffer,
+                                 const void* value_buffer, const int64_t* lengths,
+                                 const void* mask, void* output, int64_t batch,
+                                 int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                                 int64_t capacity, int64_t mask_len, int64_t q_batch_stride,
+                                 int64_t q_head_stride, int64_t mask_batch_stride,
+                                 int mask_dtype, double scale, int dtype, int mode,
+                                 int64_t split_tokens, int64_t max_length_hint,
+                                 void* workspace, int64_t workspace_bytes, int32_t* status,
+                                 void* stream, const int32_t* sequence_order) {
   if (!query || !key_buffer || !value_buffer || !lengths || !output || batch < 0 ||
       q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || capacity <= 0 || mask_len <= 0 ||
       mask_len > capacity || q_heads % kv_heads != 0)
@@ -1389,6 +1394,7 @@ extern "C" int b200_decode_attention(const void* query, const void* key_buffer,
   p.ws_o = nullptr;
   p.ws_ml = nullptr;
   p.counters = nullptr;
+  p.order = flat.usable ? nullptr : sequence_order;  // (the flat schedule balances by itself)
   if (flat.usable) {
     if (flat.max_parts > 1) {
       if (!workspace || workspace_bytes < flat.workspace_bytes) return B200_ERR_WORKSPACE;
@@ -1408,6 +1414,39 @@ extern "C" int b200_decode_attention(const void* query, const void* key_buffer,
     p.ws_ml = p.ws_o + batch * q_heads * splits * head_dim;
   }
   return head_dim == 64 ? launch_bf16<64>(p, s) : launch_bf16<128>(p, s);
+}
+
+extern "C" int b200_decode_attention(const void* query, const void* key_buffer,
+                                     const void* value_buffer, const int64_t* lengths,
+                                     const void* mask, void* output, int64_t batch,
+                                     int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                                     int64_t capacity, int64_t mask_len, int64_t q_batch_stride,
+                                     int64_t q_head_stride, int64_t mask_batch_stride,
+                                     int mask_dtype, double scale, int dtype, int mode,
+                                     int64_t split_tokens, int64_t max_length_hint,
+                                     void* workspace, int64_t workspace_bytes, int32_t* status,
+                                     void* stream) {
+  return decode_attention_impl(query, key_buffer, value_buffer, lengths, mask, output, batch, q_heads,
+                               kv_heads, head_dim, capacity, mask_len, q_batch_stride, q_head_stride,
+                               mask_batch_stride, mask_dtype, scale, dtype, mode, split_tokens,
+                               max_length_hint, workspace, workspace_bytes, status, stream, nullptr);
+}
+
+// The same with a service order: CTA group i of the grid serves sequence sequence_order[i].
+extern "C" int b200_decode_attention_ordered(
+    const void* query, const void* key_buffer, const void* value_buffer, const int64_t* lengths,
+    const void* mask, void* output, const int32_t* sequence_order, int64_t batch, int64_t q_heads,
+    int64_t kv_heads, int64_t head_dim, int64_t capacity, int64_t mask_len, int64_t q_batch_stride,
+    int64_t q_head_stride, int64_t mask_batch_stride, int mask_dtype, double scale, int dtype,
+    int mode, int64_t split_tokens, int64_t max_length_hint, void* workspace,
+    int64_t workspace_bytes, int32_t* status, void* stream) {
+  if (!sequence_order) return B200_ERR_BAD_ARGUMENT;
+  if (dtype != B200_BF16) return B200_ERR_UNSUPPORTED;
+  return decode_attention_impl(query, key_buffer, value_buffer, lengths, mask, output, batch, q_heads,
+                               kv_heads, head_dim, capacity, mask_len, q_batch_stride, q_head_stride,
+                               mask_batch_stride, mask_dtype, scale, dtype, mode, split_tokens,
+                               max_length_hint, workspace, workspace_bytes, status, stream,
+                               sequence_order);
 }
 
 // ---- Paged KV layout ---------------------------------------------------------------------

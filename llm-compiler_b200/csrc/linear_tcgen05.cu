@@ -897,11 +897,13 @@ int resident_clusters_of(ClusterConfig config, int bn, int splits) {
 // at most the portable 8) with about one CTA per SM. The cost of a candidate is what one CTA
 // streams (k-blocks of its slice x stage bytes) plus a per-slice charge for the reduction.
 PartialPlan plan_cluster(int64_t m, int64_t k, int64_t n) {
-  static const char* forced = getenv("B200_SPLITK_PLAN");  // "bn,splits": experiments only
+  static const char* forced = getenv("B200_SPLITK_PLAN");  // "bn,splits[,k]": experiments only
   if (forced != nullptr) {
     int bn = 0, splits = 0;
-    if (sscanf(forced, "%d,%d", &bn, &splits) == 2 && (bn == 32 || bn == 64 || bn == 128) &&
-        splits >= 1 && splits <= 8)
+    long long only_k = 0;
+    const int fields = sscanf(forced, "%d,%d,%lld", &bn, &splits, &only_k);
+    if (fields >= 2 && (bn == 32 || bn == 64 || bn == 128) && splits >= 1 && splits <= 8 &&
+        (fields < 3 || only_k == k))
       return PartialPlan{bn, splits};
   }
   const int64_t kb = ceil_div(k, kBK);
@@ -913,8 +915,9 @@ PartialPlan plan_cluster(int64_t m, int64_t k, int64_t n) {
     const int64_t tiles = ceil_div(n, bn) * ceil_div(m, kBM);
     for (int64_t splits = 1; splits <= 8 && splits <= kb; ++splits) {
       if (tiles * splits > kNumSMs) break;
+      // (the last slices may come out empty, e.g. 14 k-blocks over 8 slices of 2: such a CTA
+      // ships zeros; 8 slices of at most 2 k-blocks measured faster than 4 slices of 4)
       const int64_t per = ceil_div(kb, splits);
-      if (ceil_div(kb, per) != splits) continue;  // a slice would be empty
       if (ceil_div(rows * bn / 4, splits) > 4 * kThreads) continue;  // units one CTA can own
       // every cluster resident at once: a second wave would double the time
       if (splits > 1 && resident_clusters_of(cluster_config(static_cast<int>(rows), bn, per), bn,
@@ -937,19 +940,30 @@ PartialPlan plan_cluster(int64_t m, int64_t k, int64_t n) {
 // one CTA on each of the 148 SMs at the least traffic (activation re-reads per N tile +
 // fp32 partials written and read back per K slice).
 PartialPlan plan_partial(int64_t m, int64_t k, int64_t n) {
+  static const char* forced = getenv("B200_PARTIAL_PLAN");  // "bn,splits": experiments only
+  if (forced != nullptr) {
+    int bn = 0, splits = 0;
+    if (sscanf(forced, "%d,%d", &bn, &splits) == 2 && (bn == 32 || bn == 64 || bn == 128) &&
+        splits >= 1 && splits <= ceil_div(k, kBK))
+      return PartialPlan{bn, splits};
+  }
   const int64_t kb = ceil_div(k, kBK);
   PartialPlan best{128, 1};
   double best_cost = 1e300;
   for (int bn : {32, 64, 128}) {
     const int64_t tiles = ceil_div(n, bn);
-    int64_t splits = (kNumSMs + tiles / 2) / tiles;
+    // A small weight matrix (the q|k|v projection of a 0.5B model: 2 MB) is fetched in a
+    // couple of microseconds by a hundred CTAs; more K slices only add partials for the
+    // consumer to sum (36 tiles x 3 slices measured 0.7 % of the decode step faster than x 4).
+    const int64_t target = n * k * 2 <= (4ll << 20) ? kNumSMs * 3 / 4 : kNumSMs;
+    int64_t splits = (target + tiles / 2) / tiles;
     if (splits < 1) splits = 1;
     if (splits > kb) splits = kb;
     const int64_t per = ceil_div(kb, splits);
     splits = ceil_div(kb, per);
     const double ctas = static_cast<double>(tiles * splits);
     const double bytes = static_cast<double>(tiles) * m * k * 2 + 2.0 * splits * m * n * 4;
-    const double fill = ctas >= kNumSMs ? 1.0 : ctas / kNumSMs;
+    const double fill = ctas >= target ? 1.0 : ctas / target;
     const double cost = bytes / fill;
     if (cost < best_cost) {
       best_cost = cost;

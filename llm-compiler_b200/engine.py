@@ -103,6 +103,12 @@ class Qwen2Engine:
         self.fused_qkv_attention = os.environ.get("B200_FUSED_QKV_ATTENTION", "1") != "0"
         self.split_tokens = 0
         self.kernels_per_step = 0
+        # longest-first service order of decode attention (ragged batches with more
+        # (sequence, KV head) pairs than the GPU holds at once): one buffer, rewritten in place
+        # by load_context, so that a captured step keeps reading the current order
+        self.sequence_order: Optional[torch.Tensor] = None
+        if self.dtype == torch.bfloat16:
+            self.sequence_order = torch.arange(batch, dtype=torch.int32, device=self.device)
 
     # ------------------------------------------------------------------ weights ----
     def _pack_weights(self, weights: Dict[str, torch.Tensor]) -> None:
@@ -151,6 +157,8 @@ class Qwen2Engine:
         if tokens > self.capacity:
             raise ExecutionError(f"prompt of {tokens} tokens exceeds capacity {self.capacity}")
         ids = input_ids.to(self.device)
+        if self.sequence_order is not None:  # every sequence holds the same number of tokens
+            self.sequence_order.copy_(torch.arange(batch, dtype=torch.int32, device=self.device))
         self.state._length_arena.zero_()
         if self.paged:
             for sequence in range(batch):
@@ -217,6 +225,8 @@ class Qwen2Engine:
         self._host_lengths = [int(n) for n in lengths.tolist()]
         self._block_slack = 0
         self._reserve_blocks()
+        if self.sequence_order is not None:
+            self.sequence_order.copy_(kernels.sequence_order_of(lengths))
 
     def _reserve_blocks(self) -> None:
         """Paged layout: every sequence owns the blocks for its context plus at least one more
@@ -375,7 +385,8 @@ class Qwen2Engine:
                 attn = kernels.b200_decode_attention(
                     q, self.state.keys[index], self.state.values[index], self.attention_lengths,
                     None, scale=self.scale, numerical_mode=self.mode,
-                    split_tokens=self.split_tokens, max_length_hint=self.max_length_hint)
+                    split_tokens=self.split_tokens, max_length_hint=self.max_length_hint,
+                    sequence_order=self.sequence_order)
             # o and down have few N tiles: at up to 256 bf16 rows they run as cluster split-K
             # projections that add the residual themselves (same rounding points)
             splitk = self.dtype == torch.bfloat16 and batch <= 256 and cfg.hidden_size % 4 == 0

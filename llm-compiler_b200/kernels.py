@@ -472,9 +472,14 @@ def b200_decode_attention(query: torch.Tensor, key_buffer: torch.Tensor,
                           attention_mask: Optional[torch.Tensor], *, scale: float,
                           numerical_mode: str = "fast", split_tokens: Optional[int] = None,
                           max_length_hint: int = 0,
-                          output: Optional[torch.Tensor] = None) -> torch.Tensor:
+                          output: Optional[torch.Tensor] = None,
+                          sequence_order: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One-token GQA attention over the physical KV buffers. Mirrors
     triton_decode_attention (backends/triton_attention.py:134-210).
+
+    sequence_order (int32 [B], a permutation of the batch; bf16 only): the order in which the
+    sequences are handed to the GPU. With more (sequence, KV head) pairs than the GPU holds at
+    once, listing the longest sequences first keeps the last wave short (sequence_order_of).
 
     attention_mask is B x 1 x 1 x S additive (S <= capacity) or None for an all-zero mask
     of length `capacity`. Returns B x Hq x 1 x D (memory order B, Hq, D).
@@ -527,15 +532,37 @@ def b200_decode_attention(query: torch.Tensor, key_buffer: torch.Tensor,
         need = int(library.b200_decode_attention_workspace_bytes(
             batch, q_heads, kv_heads, dim, max_length, split_tokens))
     workspace = rt.workspace("decode_attention", need)
-    code = library.b200_decode_attention(
-        query.data_ptr(), key_buffer.data_ptr(), value_buffer.data_ptr(), lengths.data_ptr(),
-        _ptr(attention_mask), output.data_ptr(), batch, q_heads, kv_heads, dim, capacity,
-        mask_len, query.stride(0), query.stride(1), mask_stride, mask_code, float(scale),
-        _code(query.dtype), _mode(numerical_mode), int(split_tokens), int(max_length_hint),
-        _ptr(workspace), need, rt.status.data_ptr(), _stream())
+    if sequence_order is not None:
+        _require_cuda(query, sequence_order)
+        if sequence_order.dtype != torch.int32 or sequence_order.shape != (batch,) or \
+                not sequence_order.is_contiguous():
+            raise ValueError("sequence_order must be a contiguous int32 vector of B entries")
+        if query.dtype != torch.bfloat16:
+            raise ValueError("a sequence order is taken by the bf16 kernel only")
+        code = library.b200_decode_attention_ordered(
+            query.data_ptr(), key_buffer.data_ptr(), value_buffer.data_ptr(), lengths.data_ptr(),
+            _ptr(attention_mask), output.data_ptr(), sequence_order.data_ptr(), batch, q_heads,
+            kv_heads, dim, capacity, mask_len, query.stride(0), query.stride(1), mask_stride,
+            mask_code, float(scale), _code(query.dtype), _mode(numerical_mode), int(split_tokens),
+            int(max_length_hint), _ptr(workspace), need, rt.status.data_ptr(), _stream())
+    else:
+        code = library.b200_decode_attention(
+            query.data_ptr(), key_buffer.data_ptr(), value_buffer.data_ptr(), lengths.data_ptr(),
+            _ptr(attention_mask), output.data_ptr(), batch, q_heads, kv_heads, dim, capacity,
+            mask_len, query.stride(0), query.stride(1), mask_stride, mask_code, float(scale),
+            _code(query.dtype), _mode(numerical_mode), int(split_tokens), int(max_length_hint),
+            _ptr(workspace), need, rt.status.data_ptr(), _stream())
     _check(code, "b200_decode_attention")
     _count(rt)
     return output
+
+
+def sequence_order_of(lengths: torch.Tensor) -> torch.Tensor:
+    """Longest-first service order for b200_decode_attention(sequence_order=...): the batch
+    indices sorted by descending length (stable), int32, on the lengths' device. Lengths that
+    all grow by one per step keep their order, so a serving loop computes this once per batch."""
+
+    return torch.argsort(lengths, descending=True, stable=True).to(torch.int32)
 
 
 def b200_decode_attention_no_alloc(query: torch.Tensor, key_buffer: torch.Tensor,

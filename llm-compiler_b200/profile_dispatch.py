@@ -94,11 +94,13 @@ def decode_attention_case(args, batch, length):
     query = torch.randn(batch, hq, 1, d, device="cuda", dtype=torch.bfloat16)
     output = torch.empty_like(query)
 
+    order = kernels.sequence_order_of(lengths) if getattr(args, "longest_first", False) else None
+
     def launch(index):
         kernels.b200_decode_attention(query, keys[index], values[index], lengths, None,
                                       scale=d ** -0.5, split_tokens=args.split_tokens,
                                       max_length_hint=length, output=output,
-                                      numerical_mode=args.mode)
+                                      numerical_mode=args.mode, sequence_order=order)
 
     timer = time_launches if args.no_graph else graph_time
     seconds = timer(launch, sets, args.warmup, args.iters)
@@ -106,7 +108,8 @@ def decode_attention_case(args, batch, length):
     flops = 4 * hq * d * total
     return {"op": "decode_attention", "batch": batch, "max_length": length, "buffer_rows": rows,
             "sum_lengths": total, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
-            "split_tokens": args.split_tokens, "buffer_sets": sets, "us": seconds * 1e6,
+            "split_tokens": args.split_tokens, "longest_first": order is not None,
+            "buffer_sets": sets, "us": seconds * 1e6,
             "gbs": algorithmic / seconds / 1e9, "tflops": flops / seconds / 1e12,
             "algorithmic_bytes": algorithmic}
 
@@ -221,6 +224,8 @@ def measurement_arguments(parser: argparse.ArgumentParser) -> None:
     parser.add_argument("--epilogue", default="none")
     parser.add_argument("--mode", default="fast")
     parser.add_argument("--general-mask", action="store_true")
+    parser.add_argument("--longest-first", action="store_true",
+                        help="decode attention: hand the sequences to the GPU longest first")
     parser.add_argument("--full-length", action="store_true",
                         help="every sequence at --length instead of uniform [64, length]")
     parser.add_argument("--no-graph", action="store_true")

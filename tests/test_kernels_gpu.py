@@ -749,6 +749,48 @@ def test_wrappers_reject_cpu_tensors_and_bad_shapes():
                                    None, scale=1.0)
 
 
+@pytest.mark.parametrize("split_tokens", [0, 128])
+def test_decode_attention_service_order_changes_nothing(split_tokens):
+    """sequence_order only decides which sequence a group of CTAs serves: any permutation gives
+    the bit-identical output (here longest first and a shuffle, with and without KV splits, on
+    more (sequence, KV head) pairs than the GPU holds at once); an entry outside the batch
+    skips its group and touches nothing else."""
+    g = torch.Generator().manual_seed(31 + split_tokens)
+    batch, capacity, hq, hkv, d = 200, 640, 14, 2, 64
+    lengths = torch.randint(1, capacity + 1, (batch,), generator=g)
+    q = torch.randn(batch, hq, 1, d, generator=g).bfloat16().cuda()
+    k = torch.randn(batch, capacity, hkv, d, generator=g).bfloat16().cuda()
+    v = torch.randn(batch, capacity, hkv, d, generator=g).bfloat16().cuda()
+    device_lengths = lengths.cuda()
+    plain = kernels.b200_decode_attention(q, k, v, device_lengths, None, scale=d ** -0.5,
+                                          split_tokens=split_tokens)
+    longest_first = kernels.sequence_order_of(device_lengths)
+    assert longest_first.dtype == torch.int32 and sorted(longest_first.tolist()) == list(range(batch))
+    assert lengths[longest_first.cpu().long()].diff().max().item() <= 0
+    shuffled = torch.randperm(batch, generator=g).to(torch.int32).cuda()
+    for order in (longest_first, shuffled):
+        out = kernels.b200_decode_attention(q, k, v, device_lengths, None, scale=d ** -0.5,
+                                            split_tokens=split_tokens, sequence_order=order)
+        assert torch.equal(out, plain)
+    ref = serve_ops.decode_attention(q.cpu()[:8], k.cpu()[:8], v.cpu()[:8], lengths[:8],
+                                     torch.zeros(8, 1, 1, capacity), groups=hq // hkv, scale=d ** -0.5)
+    close(plain[:8], ref, BF16_TOL)
+    holed = longest_first.clone()
+    holed[5] = batch + 3  # not a sequence: that group does nothing
+    skipped = int(longest_first[5])
+    marked = torch.full_like(plain, 7.0)
+    kernels.b200_decode_attention(q, k, v, device_lengths, None, scale=d ** -0.5, split_tokens=split_tokens,
+                                  sequence_order=holed, output=marked)
+    keep = torch.ones(batch, dtype=torch.bool)
+    keep[skipped] = False
+    assert torch.equal(marked[keep.cuda()], plain[keep.cuda()])
+    assert torch.all(marked[skipped] == 7.0)
+    with pytest.raises(ValueError):
+        kernels.b200_decode_attention(q, k, v, device_lengths, None, scale=d ** -0.5,
+                                      sequence_order=longest_first.long())
+    kernels.runtime().check_status()
+
+
 # ------------------------------------------ five-launch decode layer: its three kernels ----
 @pytest.mark.parametrize("m,k,n", [(64, 896, 896), (64, 4864, 896), (3, 256, 256), (1, 512, 256),
                                    (33, 3584, 3584), (128, 896, 896), (100, 4864, 896),
