@@ -446,6 +446,15 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tensor_map
       : "memory");
 }
 
+// The box a tma_load_2d at these coordinates would copy, requested into L2 only: no shared
+// memory, no barrier, nothing to wait for.
+__device__ __forceinline__ void tma_prefetch_l2_2d(const void* tensor_map, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];\n" ::"l"(
+                   reinterpret_cast<uint64_t>(tensor_map)),
+               "r"(c0), "r"(c1)
+               : "memory");
+}
+
 // Shared-memory tiles whose rows are 128 bytes (64 bf16) are stored with the 16-byte
 // chunk index XOR-ed by (row & 7): ldmatrix reads of 8 consecutive rows at one logical
 // chunk then touch 8 different bank groups.

@@ -55,6 +55,14 @@ struct Tcgen05Params {
   int m, k, n, epilogue, splits;
   int bn;  // columns per tile: a multiple of 16, at most the kernel's BN
   int prefetch_weights;  // W tiles may be fetched before the predecessor kernel has finished
+  // Grid x walks the M tiles (and y the N tiles) instead of the other way round: CTAs are placed
+  // in x-fastest order, so the few M tiles of one N tile then run side by side and the second
+  // finds the W tile in L2. With N fastest and a W larger than L2 (a 7B gate|up projection at
+  // 256 rows: 271 MB, two M tiles) every M tile streamed W from HBM again.
+  int m_fastest = 0;
+  // With prefetch_weights: the W tiles behind the first ring are requested into L2 before the
+  // dependency wait as well, so that the ring's later rounds cost an L2 hit, not an HBM access.
+  int prefetch_l2 = 0;
   uint32_t wait_limit = 4000000u;  // polls of a bounded wait
   int drop_loads = 0;              // debug: the producer issues nothing (every wait runs out)
   // RMSNorm folded into the projection (norm_input != nullptr): the A operand is the
@@ -214,7 +222,8 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   TraceScope trace(1);
   grid_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile_n = blockIdx.x, tile_m = blockIdx.y, split = blockIdx.z;
+  const int tile_n = p.m_fastest ? blockIdx.y : blockIdx.x, tile_m = p.m_fastest ? blockIdx.x : blockIdx.y;
+  const int split = blockIdx.z;
   const int kb_total = (p.k + kBK - 1) / kBK;
   const int kb_per = (kb_total + p.splits - 1) / p.splits;
   const int kb_first = split * kb_per;
@@ -264,12 +273,14 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
     // before waiting for that kernel (the transaction bytes are announced without arriving,
     // so a stage cannot complete before its x box has been requested as well).
     const int early = p.prefetch_weights ? min(nkb, STAGES) : 0;
+    auto k_of = [&](int kb) { return (kb_first + kb) * kBK; };  // element offset of the kb-th k-block
     for (int kb = 0; kb < early; ++kb) {
       const uint32_t bar = smem_u32(&full_bar[kb]);
       mbarrier_expect_tx(bar, static_cast<uint32_t>(bn * 128));
-      tma_load_2d(smem_base + kb * kStageBytes + kABytes, &b_map, bar, (kb_first + kb) * kBK,
-                  tile_n * bn);
+      tma_load_2d(smem_base + kb * kStageBytes + kABytes, &b_map, bar, k_of(kb), tile_n * bn);
     }
+    if (p.prefetch_l2)
+      for (int kb = early; kb < nkb; ++kb) tma_prefetch_l2_2d(&b_map, k_of(kb), tile_n * bn);
     grid_dependency_wait();
     trace.mark(0);
     for (int kb = 0; kb < nkb; ++kb) {
@@ -283,11 +294,11 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
       const uint32_t a_dst = smem_base + s * kStageBytes;
       if (kb < early) {
         mbarrier_arrive_expect_tx(bar, static_cast<uint32_t>(kABytes));
-        tma_load_2d(a_dst, &a_map, bar, (kb_first + kb) * kBK, tile_m * kBM);
+        tma_load_2d(a_dst, &a_map, bar, k_of(kb), tile_m * kBM);
       } else {
         mbarrier_arrive_expect_tx(bar, stage_tx_bytes);
-        tma_load_2d(a_dst, &a_map, bar, (kb_first + kb) * kBK, tile_m * kBM);
-        tma_load_2d(a_dst + kABytes, &b_map, bar, (kb_first + kb) * kBK, tile_n * bn);
+        tma_load_2d(a_dst, &a_map, bar, k_of(kb), tile_m * kBM);
+        tma_load_2d(a_dst + kABytes, &b_map, bar, k_of(kb), tile_n * bn);
       }
     }
   } else if (warp == 1 && lane == 0) {
@@ -821,11 +832,26 @@ int launch(const Tcgen05Params& p, const CUtensorMap& a_map, const CUtensorMap& 
   auto kernel = linear_tcgen05_kernel<BN, STAGES, A_ROWS>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return B200_ERR_LAUNCH;
-  dim3 grid(static_cast<unsigned>(ceil_div(p.n, p.bn)), static_cast<unsigned>(ceil_div(p.m, kBM)),
-            static_cast<unsigned>(p.splits));
+  const int64_t tiles_n = ceil_div(p.n, p.bn), tiles_m = ceil_div(p.m, kBM);
+  Tcgen05Params q = p;
+  static const bool n_fastest_always = [] {  // B200_TILE_ORDER=n: the comparison run
+    const char* text = getenv("B200_TILE_ORDER");
+    return text != nullptr && strcmp(text, "n") == 0;
+  }();
+  // a decode-size launch whose W (at most 64 MB, with L2 to spare) is a constant
+  static const bool l2_prefetch_off = [] {  // B200_WEIGHT_L2_PREFETCH=0: the comparison run
+    const char* text = getenv("B200_WEIGHT_L2_PREFETCH");
+    return text != nullptr && strcmp(text, "0") == 0;
+  }();
+  q.prefetch_l2 = !l2_prefetch_off && p.prefetch_weights && A_ROWS == 64 &&
+                          static_cast<int64_t>(p.n) * p.k * 2 <= (64ll << 20) ? 1 : 0;
+  q.m_fastest = !n_fastest_always && tiles_m >= 2 && tiles_m <= 16 && tiles_n <= 65535 &&
+                        static_cast<int64_t>(p.n) * p.k * 2 > (64ll << 20) ? 1 : 0;
+  dim3 grid(static_cast<unsigned>(q.m_fastest ? tiles_m : tiles_n),
+            static_cast<unsigned>(q.m_fastest ? tiles_n : tiles_m), static_cast<unsigned>(p.splits));
   // the K slices of a tile are one thread-block cluster when they reduce among themselves
   const unsigned cluster_z = p.epilogue == kEpilogueClusterResidual ? static_cast<unsigned>(p.splits) : 1u;
-  if (launch_chained_cluster_xz(kernel, grid, dim3(kThreads), smem, stream, 1u, cluster_z, p, a_map,
+  if (launch_chained_cluster_xz(kernel, grid, dim3(kThreads), smem, stream, 1u, cluster_z, q, a_map,
                                 b_map) != cudaSuccess)
     return B200_ERR_LAUNCH;
   return launch_status();
@@ -988,6 +1014,19 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
   bool persistent = false;
   if (m > 64) {
     bn = n % 256 == 0 || n > 1024 ? 256 : 128;
+    // A few M tiles (65 .. 1023 rows: large decode batches, short prefills) stream W rather than
+    // reuse it: the widest tile that still gives about three quarters of the SMs a CTA, else the
+    // narrowest (a 3584-column projection at 256 rows: 112 CTAs of 64 columns instead of 28 of 256).
+    if (m < 1024) {
+      const int64_t tiles_m = ceil_div(m, kBM);
+      bn = 64;
+      for (int candidate : {256, 128}) {
+        if (ceil_div(n, candidate) * tiles_m >= kNumSMs * 3 / 4) {
+          bn = candidate;
+          break;
+        }
+      }
+    }
     // From a few tiles per SM on, the persistent kernel (B200_LINEAR_PERSISTENT=0 keeps one tile
     // per CTA, for comparison). Its tile width is the multiple of 16 up to 256 that wastes the
     // fewest columns of the last N tile (896 -> 224, 1152 -> 192); 256 if that pads N by at most 1.5 %.
@@ -1081,6 +1120,7 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
       return small_rings() && fold_norm ? launch<128, 4, 64>(p, a_map, b_map, stream)
                                         : launch<128, 8, 64>(p, a_map, b_map, stream);
     // narrow tiles of a folded-norm projection: short rings, three CTAs per SM
+    // (4-stage rings measured best: 3 stages -4 %, 6 stages -2 %, 12 stages -17 % of the decode step)
     if (small_rings() && fold_norm)
       return bn > 32 ? launch<64, 4, 64>(p, a_map, b_map, stream) : launch<32, 4, 64>(p, a_map, b_map, stream);
     return launch<64, 12, 64>(p, a_map, b_map, stream);

@@ -119,6 +119,9 @@ class Qwen2Engine:
         self.embed = weights["embed_tokens.weight"]
         self.lm_head = weights["lm_head.weight"]
         self.final_norm = weights["decoder.norm.weight"]
+        # the final RMSNorm folded into the LM head as well (a second copy of that matrix)
+        self.lm_head_folded = kernels.b200_scale_columns(self.lm_head, self.final_norm) \
+            if self.folded_norms else None
         self.layers = []
         for index in range(cfg.num_layers):
             p = f"decoder.layers.{index}."
@@ -307,10 +310,11 @@ class Qwen2Engine:
             x, x_squares = x if self.producer_squares else (x, None)
             a = kernels.b200_linear_rms_input(x, layer["gate_up_w_folded"], epsilon=eps,
                                               epilogue="swiglu", row_squares=x_squares)
-            x = kernels.b200_linear_splitk_residual(a, layer["down_w"], x)
-        h = kernels.b200_rms_norm(x, self.final_norm, epsilon=eps, round_before_weight=True,
-                                  numerical_mode=self.mode)
-        self.logits = kernels.b200_linear(h, self.lm_head)
+            last = self.producer_squares and index + 1 == len(self.layers)
+            x = kernels.b200_linear_splitk_residual(a, layer["down_w"], x, row_squares=last)
+            x, x_squares = x if last else (x, None)  # (only the LM head's norm takes them)
+        self.logits = kernels.b200_linear_rms_input(x, self.lm_head_folded, epsilon=eps,
+                                                    row_squares=x_squares)
         kernels.b200_argmax(self.logits, self.next_ids)
         kernels.b200_advance_lengths(self.state._length_arena, 1, self.capacity + 1)
         self.kernels_per_step = kernels.launch_count(self.device) - before

@@ -275,7 +275,7 @@ def _single_user(users, value) -> Optional[Any]:
 
 def fuse_norm_linear(function) -> int:
     """rms_norm(x, w) whose only user is a bias-free or biased `kernel.b200.linear` without a
-    residual (fast mode, bf16, parameter weights that no other op reads) becomes
+    residual (fast mode, bf16, parameter weights) becomes
     `kernel.b200.norm_linear` [x, w, W, scale_columns(W, w), bias?]: at run time, up to 64 rows,
     ONE launch on the un-normalised rows with the norm weight folded into W's columns and the
     row factor applied to the accumulator; beyond that the executor runs the two kernels."""
@@ -294,9 +294,11 @@ def fuse_norm_linear(function) -> int:
         weight = linear.operands[1]
         producer = _producer_map(function).get(weight.name)
         prepared = producer is not None and producer.attributes.get("constant") is True
-        if not (_is_parameter(function, weight) or prepared) or len(users.get(weight.name, [])) != 1 or \
+        # (a weight with other readers -- a tied LM head is also the embedding table -- keeps its
+        # plain copy for them; the folded copy costs its size in memory, nothing per step)
+        if not (_is_parameter(function, weight) or prepared) or \
                 not _is_parameter(function, norm.operands[1]):
-            continue  # (a tied LM head is also the embedding table: it keeps its own norm launch)
+            continue
         folded = Value(_fresh(function, "folded_weight"), str(weight.type))
         prepare = Operation("kernel.b200.scale_columns", [weight, norm.operands[1]], [folded],
                             {"constant": True, "lowered_from": "weight preparation"})

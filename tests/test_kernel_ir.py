@@ -120,11 +120,11 @@ def test_qwen2_0_5b_graphs_lower_fully(kind, total):
         ir.require_full_lowering(chained)
         chain = Counter(op.name for op in chained.functions[0].block.operations)
         assert chain["kernel.b200.qkv_decode_attention"] == layers  # partial GEMM + attention
-        assert chain["kernel.b200.norm_linear"] == layers            # gate|up with the folded norm
-        assert chain["kernel.b200.linear"] == 2 * layers + 1         # o, down (+ residual), LM head
-        assert chain["kernel.b200.rms_norm"] == 1                    # the tied LM head keeps its norm
+        assert chain["kernel.b200.norm_linear"] == layers + 1        # gate|up and the LM head with their folded norms
+        assert chain["kernel.b200.linear"] == 2 * layers             # o, down (+ residual)
+        assert chain["kernel.b200.rms_norm"] == 0
         assert chain["runtime.kv.advance_all"] == 1 and chain["runtime.kv.advance"] == 0
-        assert chain["kernel.b200.scale_columns"] == 2 * layers
+        assert chain["kernel.b200.scale_columns"] == 2 * layers + 1  # (the tied LM head gets a folded copy)
         assert chain_report.lowered_rules["qkv+attention"] == layers
         fused = [op for op in chained.functions[0].block.operations
                  if op.name == "kernel.b200.qkv_decode_attention"]
@@ -136,7 +136,7 @@ def test_qwen2_0_5b_graphs_lower_fully(kind, total):
         kept_names = Counter(op.name for op in kept.functions[0].block.operations)
         assert kept_names["kernel.b200.qkv_decode_attention"] == 0
         assert kept_names["kernel.b200.decode_attention"] == layers
-        assert kept_names["kernel.b200.norm_linear"] == 2 * layers
+        assert kept_names["kernel.b200.norm_linear"] == 2 * layers + 1
     else:
         assert names["kernel.b200.prefill_attention"] == layers
         assert report.lowered_rules["causal_mask"] == layers
