@@ -41,10 +41,10 @@ class B200LibraryError(RuntimeError):
 
 _I64P = POINTER(c_int64)
 
-# name -> (restype, argtypes); mirrors include/b200_serve.h one to one
 # What b200_abi_version() of a matching library returns (bumped with every signature change).
 ABI_VERSION = 102
 
+# name -> (restype, argtypes); mirrors include/b200_serve.h one to one
 SIGNATURES = {
     "b200_abi_version": (c_int, []),
     "b200_error_string": (c_char_p, [c_int]),

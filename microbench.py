@@ -356,11 +356,101 @@ def compare_case(args):
             unit_bytes=rows * 896 * 4)
 
 
+def cpu_baseline_case(args):
+    """The CPU oracle (the restatement of the reference's CPU executor) timed on this machine's
+    host cores: per operator on the benchmark configurations' shapes, and the whole Qwen2-0.5B
+    architecture (24 layers, vocabulary 151936) through a 512-token prefill and decode steps at
+    batch 1 and 16. No GPU work: the numbers stand beside the GPU tables."""
+
+    import os
+    import statistics
+    import time
+
+    from llm_compiler_b200 import qwen2 as q2
+    from oracle import qwen2_model, serve_ops
+
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+
+    def timed(fn, repeats=3):
+        fn()
+        samples = []
+        for _ in range(repeats):
+            start = time.perf_counter()
+            fn()
+            samples.append(time.perf_counter() - start)
+        return statistics.median(samples)
+
+    def emit(op, case, seconds, **extra):
+        print(json.dumps({"op": op, **case, "cpu_ms": seconds * 1e3, "threads": threads, **extra}), flush=True)
+
+    g = torch.Generator().manual_seed(0)
+    hq, hkv, d = 14, 2, 64
+    with torch.no_grad():
+        for batch, length in ((8, 1024), (8, 4096), (64, 4096)):
+            q = torch.randn(batch, hq, 1, d, generator=g).bfloat16()
+            k = torch.randn(batch, length, hkv, d, generator=g).bfloat16()
+            v = torch.randn(batch, length, hkv, d, generator=g).bfloat16()
+            lengths = torch.full((batch,), length)
+            mask = torch.zeros(batch, 1, 1, length)
+            emit("decode_attention", {"batch": batch, "length": length},
+                 timed(lambda: serve_ops.decode_attention(q, k, v, lengths, mask, groups=hq // hkv, scale=d ** -0.5)))
+        for batch, tokens in ((4, 512), (4, 2048), (1, 4096)):
+            q = torch.randn(batch, hq, tokens, d, generator=g).bfloat16()
+            k = torch.randn(batch, hkv, tokens, d, generator=g).bfloat16()
+            v = torch.randn(batch, hkv, tokens, d, generator=g).bfloat16()
+            mask = serve_ops.causal_mask(batch, tokens)
+            emit("prefill_attention", {"batch": batch, "tokens": tokens},
+                 timed(lambda: serve_ops.prefill_attention(q, k, v, mask, groups=hq // hkv, scale=d ** -0.5)))
+        for m in (64, 4096):
+            for name, (k_dim, n) in {"q|k|v": (896, 1152), "gate": (896, 4864), "down": (4864, 896),
+                                     "lm_head": (896, 151936)}.items():
+                if name == "lm_head" and m != 64:
+                    continue
+                x = torch.randn(m, k_dim, generator=g).bfloat16()
+                w = (torch.randn(n, k_dim, generator=g) * 0.02).bfloat16()
+                emit("linear", {"name": name, "m": m, "k": k_dim, "n": n}, timed(lambda: serve_ops.linear(x, w)))
+        x = torch.randn(16384, 896, generator=g).bfloat16()
+        w = torch.ones(896).bfloat16()
+        emit("rms_norm", {"rows": 16384, "hidden": 896},
+             timed(lambda: serve_ops.rms_norm(x, w, 1e-6, round_before_weight=True)))
+        q = torch.randn(4, hq, 2048, d, generator=g).bfloat16()
+        k = torch.randn(4, hkv, 2048, d, generator=g).bfloat16()
+        cos = torch.randn(4, 2048, d, generator=g).bfloat16()
+        sin = torch.randn(4, 2048, d, generator=g).bfloat16()
+        emit("rope", {"batch": 4, "tokens": 2048}, timed(lambda: serve_ops.rope(q, k, cos, sin)))
+        kbuf = torch.zeros(4, 8192, hkv, d).bfloat16()
+        vbuf = torch.zeros_like(kbuf)
+        positions = torch.zeros(4, dtype=torch.int64)
+        emit("kv_store", {"batch": 4, "tokens": 2048},
+             timed(lambda: serve_ops.kv_store(kbuf, vbuf, k, k, positions)))
+
+        # the whole model, in full: prefill of 512 tokens, then decode steps
+        config = q2.QWEN2_0_5B
+        weights = q2.make_weights(config, seed=0, dtype=torch.bfloat16)
+        for batch in (1, 16):
+            prompt = q2.make_prompt_ids(config, batch, 512, seed=batch)
+            start = time.perf_counter()
+            logits, state = qwen2_model.prefill(config, weights, prompt, capacity=640)
+            prefill_s = time.perf_counter() - start
+            ids = logits[:, -1].argmax(-1).view(-1, 1)
+            steps = []
+            for _ in range(5):
+                start = time.perf_counter()
+                logits = qwen2_model.decode(config, weights, ids, state)
+                ids = logits[:, 0].argmax(-1).view(-1, 1)
+                steps.append(time.perf_counter() - start)
+            step_s = statistics.median(steps[1:])
+            emit("qwen2_0.5b_full_model", {"batch": batch, "prompt_tokens": 512}, prefill_s,
+                 prefill_tokens_per_s=batch * 512 / prefill_s, decode_ms_per_step=step_s * 1e3,
+                 decode_tokens_per_s=batch / step_s)
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("op", choices=["decode_attention", "prefill_attention", "kv_store", "linear",
                                        "rms_norm", "timeline", "prefill_step", "compare",
-                                       "linear_splitk", "linear_rms"])
+                                       "linear_splitk", "linear_rms", "cpu_baseline"])
     parser.add_argument("--model", default="qwen2-0.5b", choices=["qwen2-0.5b", "qwen2-7b"],
                         help="prefill_step: architecture")
     parser.add_argument("--launches", type=int, default=40, help="timeline: launches to print")
@@ -368,6 +458,9 @@ def main():
                         help="decode attention over batch {1,8,64,256} x length {64,1024,4096,32768}")
     measurement_arguments(parser)
     args = parser.parse_args()
+    if args.op == "cpu_baseline":  # host cores only
+        cpu_baseline_case(args)
+        return
     if not torch.cuda.is_available():
         raise SystemExit("microbench.py needs a CUDA device")
     if args.op == "decode_attention":
