@@ -256,7 +256,8 @@ int b200_paged_qkv_decode_attention(
     int64_t head_dim, int64_t num_blocks, int64_t block_size, int64_t max_blocks_per_sequence,
     int64_t mask_len, double scale, int64_t split_tokens, int64_t max_length_hint,
     int64_t length_offset, const void* norm_row_squares, int64_t norm_hidden, double norm_epsilon,
-    void* workspace, int64_t workspace_bytes, int32_t* status, void* stream);
+    const int32_t* sequence_order, void* workspace, int64_t workspace_bytes, int32_t* status,
+    void* stream);
 
 /* ---- Prefill attention -------------------------------------------------------
  * T-token GQA attention with an arbitrary additive B x 1 x T x T mask, or with
@@ -349,7 +350,8 @@ int b200_reduce_rope_kv_store(const void* partials, int64_t splits, const void* 
  * decode), fast numerical mode, bf16, head_dim 64 or 128. cosine / sine: B x D. Workspace as
  * for b200_decode_attention. lengths[b] < 1 sets B200_STATUS_BAD_POSITION (nothing stored).
  * length_offset 1: lengths[] still hold the lengths before the new token (serve.kv.advance of
- * every slot is deferred to one launch at the end of the step); the kernel adds 1 itself. */
+ * every slot is deferred to one launch at the end of the step); the kernel adds 1 itself.
+ * sequence_order: NULL, or the service order of b200_decode_attention_ordered. */
 int b200_qkv_decode_attention(const void* qkv_partials, int64_t qkv_splits, const void* qkv_bias,
                               const void* cosine, const void* sine, void* key_buffer,
                               void* value_buffer, const int64_t* lengths, void* output,
@@ -357,8 +359,8 @@ int b200_qkv_decode_attention(const void* qkv_partials, int64_t qkv_splits, cons
                               int64_t capacity, int64_t mask_len, double scale,
                               int64_t split_tokens, int64_t max_length_hint, int64_t length_offset,
                               const void* norm_row_squares, int64_t norm_hidden, double norm_epsilon,
-                              void* workspace, int64_t workspace_bytes, int32_t* status,
-                              void* stream);
+                              const int32_t* sequence_order, void* workspace, int64_t workspace_bytes,
+                              int32_t* status, void* stream);
 
 /* ---- Decode-step chain, five launches per layer (fast mode, bf16, M <= 64 rows) ----------
  * The serve.rms_norm in front of a projection (qwen2.py:152-304: input_layernorm -> q|k|v,

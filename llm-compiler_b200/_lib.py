@@ -42,7 +42,7 @@ class B200LibraryError(RuntimeError):
 _I64P = POINTER(c_int64)
 
 # What b200_abi_version() of a matching library returns (bumped with every signature change).
-ABI_VERSION = 102
+ABI_VERSION = 103
 
 # name -> (restype, argtypes); mirrors include/b200_serve.h one to one
 SIGNATURES = {
@@ -95,12 +95,12 @@ SIGNATURES = {
                                   [c_void_p, c_void_p]),
     "b200_qkv_decode_attention": (c_int, [c_void_p, c_int64] + [c_void_p] * 7 +
                                   [c_int64] * 6 + [c_double, c_int64, c_int64, c_int64, c_void_p,
-                                                   c_int64, c_double, c_void_p, c_int64, c_void_p,
-                                                   c_void_p]),
+                                                   c_int64, c_double, c_void_p, c_void_p, c_int64,
+                                                   c_void_p, c_void_p]),
     "b200_paged_qkv_decode_attention": (c_int, [c_void_p, c_int64] + [c_void_p] * 8 +
                                         [c_int64] * 8 + [c_double, c_int64, c_int64, c_int64,
                                                          c_void_p, c_int64, c_double, c_void_p,
-                                                         c_int64, c_void_p, c_void_p]),
+                                                         c_void_p, c_int64, c_void_p, c_void_p]),
     "b200_scale_columns": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int, c_void_p]),
     "b200_linear_rms_input": (c_int, [c_void_p] * 5 + [c_int64] * 5 + [c_double, c_int, c_void_p,
                                                                        c_void_p]),

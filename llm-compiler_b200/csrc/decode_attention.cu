@@ -1655,7 +1655,8 @@ static int qkv_decode_attention_impl(
     int64_t mask_len, double scale, int64_t split_tokens, int64_t max_length_hint,
     int64_t length_offset, const void* norm_row_squares, int64_t norm_hidden, double norm_epsilon,
     void* workspace, int64_t workspace_bytes, int32_t* status, void* stream,
-    const int32_t* block_table, int64_t num_blocks, int64_t block_size) {
+    const int32_t* block_table, int64_t num_blocks, int64_t block_size,
+    const int32_t* sequence_order) {
   if (norm_row_squares != nullptr && (norm_hidden <= 0 || !(norm_epsilon >= 0.0)))
     return B200_ERR_BAD_ARGUMENT;
   if (length_offset < 0 || length_offset > 1) return B200_ERR_BAD_ARGUMENT;
@@ -1724,6 +1725,7 @@ static int qkv_decode_attention_impl(
     p.table_stride = static_cast<int>(capacity / block_size);
     p.pool_rows = num_blocks * block_size;
   }
+  p.order = sequence_order;
   const GridPlan grid_plan = plan_grid(splits, split_tokens, batch, head_blocks);
   if (grid_plan.splits > 1 && !grid_plan.cluster) {
     const int64_t need = workspace_bytes_for(batch, q_heads, head_dim, splits);
@@ -1741,12 +1743,14 @@ extern "C" int b200_qkv_decode_attention(
     int64_t batch, int64_t q_heads, int64_t kv_heads, int64_t head_dim, int64_t capacity,
     int64_t mask_len, double scale, int64_t split_tokens, int64_t max_length_hint,
     int64_t length_offset, const void* norm_row_squares, int64_t norm_hidden, double norm_epsilon,
-    void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+    const int32_t* sequence_order, void* workspace, int64_t workspace_bytes, int32_t* status,
+    void* stream) {
   return qkv_decode_attention_impl(qkv_partials, qkv_splits, qkv_bias, cosine, sine, key_buffer,
                                    value_buffer, lengths, output, batch, q_heads, kv_heads, head_dim,
                                    capacity, mask_len, scale, split_tokens, max_length_hint,
                                    length_offset, norm_row_squares, norm_hidden, norm_epsilon,
-                                   workspace, workspace_bytes, status, stream, nullptr, 0, 0);
+                                   workspace, workspace_bytes, status, stream, nullptr, 0, 0,
+                                   sequence_order);
 }
 
 extern "C" int b200_paged_qkv_decode_attention(
@@ -1756,7 +1760,8 @@ extern "C" int b200_paged_qkv_decode_attention(
     int64_t head_dim, int64_t num_blocks, int64_t block_size, int64_t max_blocks_per_sequence,
     int64_t mask_len, double scale, int64_t split_tokens, int64_t max_length_hint,
     int64_t length_offset, const void* norm_row_squares, int64_t norm_hidden, double norm_epsilon,
-    void* workspace, int64_t workspace_bytes, int32_t* status, void* stream) {
+    const int32_t* sequence_order, void* workspace, int64_t workspace_bytes, int32_t* status,
+    void* stream) {
   if (!block_table || num_blocks <= 0 || block_size <= 0 || max_blocks_per_sequence <= 0)
     return B200_ERR_BAD_ARGUMENT;
   if (block_size % 32 != 0) return B200_ERR_UNSUPPORTED;  // a 32-token copy must stay inside one block
@@ -1765,5 +1770,5 @@ extern "C" int b200_paged_qkv_decode_attention(
                                    max_blocks_per_sequence * block_size, mask_len, scale, split_tokens,
                                    max_length_hint, length_offset, norm_row_squares, norm_hidden,
                                    norm_epsilon, workspace, workspace_bytes, status, stream,
-                                   block_table, num_blocks, block_size);
+                                   block_table, num_blocks, block_size, sequence_order);
 }

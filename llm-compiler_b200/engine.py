@@ -228,7 +228,7 @@ class Qwen2Engine:
         self._host_lengths = [int(n) for n in lengths.tolist()]
         self._block_slack = 0
         self._reserve_blocks()
-        if self.sequence_order is not None:
+        if self.sequence_order is not None and os.environ.get("B200_SEQUENCE_ORDER", "longest") != "grid":
             self.sequence_order.copy_(kernels.sequence_order_of(lengths))
 
     def _reserve_blocks(self) -> None:
@@ -296,7 +296,8 @@ class Qwen2Engine:
                                                             row_squares=True)
             common = dict(q_heads=cfg.num_heads, scale=self.scale, split_tokens=self.split_tokens,
                           max_length_hint=self.max_length_hint, norm_row_squares=squares,
-                          norm_hidden=cfg.hidden_size, norm_epsilon=eps)
+                          norm_hidden=cfg.hidden_size, norm_epsilon=eps,
+                          sequence_order=self.sequence_order)
             if self.paged:
                 attn = kernels.b200_paged_qkv_decode_attention(
                     partials, layer["qkv_b"], cosine, sine, self.state.keys[index],
@@ -337,7 +338,7 @@ class Qwen2Engine:
                     partials, layer["qkv_b"], cosine, sine, self.state.keys[index],
                     self.state.values[index], self.attention_lengths, q_heads=cfg.num_heads,
                     scale=self.scale, split_tokens=self.split_tokens,
-                    max_length_hint=self.max_length_hint)
+                    max_length_hint=self.max_length_hint, sequence_order=self.sequence_order)
             else:
                 q = kernels.b200_reduce_rope_kv_store(
                     partials, layer["qkv_b"], cosine, sine, self.state.keys[index],

@@ -557,6 +557,15 @@ def b200_decode_attention(query: torch.Tensor, key_buffer: torch.Tensor,
     return output
 
 
+def _order_pointer(sequence_order: Optional[torch.Tensor], batch: int, device) -> Optional[int]:
+    if sequence_order is None:
+        return None
+    if sequence_order.dtype != torch.int32 or sequence_order.shape != (batch,) or \
+            not sequence_order.is_contiguous() or sequence_order.device != device:
+        raise ValueError("sequence_order must be a contiguous int32 vector of B entries on the operands' device")
+    return sequence_order.data_ptr()
+
+
 def sequence_order_of(lengths: torch.Tensor) -> torch.Tensor:
     """Longest-first service order for b200_decode_attention(sequence_order=...): the batch
     indices sorted by descending length (stable), int32, on the lengths' device. Lengths that
@@ -985,7 +994,8 @@ def b200_qkv_decode_attention(partials: torch.Tensor, bias: Optional[torch.Tenso
                               scale: float, split_tokens: int = 0, max_length_hint: int = 0,
                               length_offset: int = 0,
                               norm_row_squares: Optional[torch.Tensor] = None,
-                              norm_hidden: int = 0, norm_epsilon: float = 0.0) -> torch.Tensor:
+                              norm_hidden: int = 0, norm_epsilon: float = 0.0,
+                              sequence_order: Optional[torch.Tensor] = None) -> torch.Tensor:
     """b200_reduce_rope_kv_store + b200_decode_attention of a decode step in one launch: the
     q|k|v partials are reduced (+ bias, RoPE) inside the attention kernel, the new token's K / V
     row is stored at row lengths[b] - 1 and attends from registers. lengths are the attention
@@ -1026,7 +1036,7 @@ def b200_qkv_decode_attention(partials: torch.Tensor, bias: Optional[torch.Tenso
         key_buffer.data_ptr(), value_buffer.data_ptr(), lengths.data_ptr(), output.data_ptr(),
         batch, q_heads, kv_heads, dim, capacity, capacity, float(scale), int(split_tokens),
         int(max_length_hint), int(length_offset), _ptr(norm_row_squares), int(norm_hidden),
-        float(norm_epsilon), _ptr(workspace),
+        float(norm_epsilon), _order_pointer(sequence_order, batch, device), _ptr(workspace),
         need, rt.status.data_ptr(), _stream())
     _check(code, "b200_qkv_decode_attention")
     _count(rt)
@@ -1040,7 +1050,8 @@ def b200_paged_qkv_decode_attention(partials: torch.Tensor, bias: Optional[torch
                                     split_tokens: int = 0, max_length_hint: int = 0,
                                     length_offset: int = 0,
                                     norm_row_squares: Optional[torch.Tensor] = None,
-                                    norm_hidden: int = 0, norm_epsilon: float = 0.0) -> torch.Tensor:
+                                    norm_hidden: int = 0, norm_epsilon: float = 0.0,
+                                    sequence_order: Optional[torch.Tensor] = None) -> torch.Tensor:
     """b200_qkv_decode_attention on the paged layout: K / V pools [blocks, block_size, Hkv, D]
     and an int32 block table [B, max_blocks]; the new token's row goes to the block the table
     names for position lengths[b] - 1 (a missing block raises the KV-overflow status bit)."""
@@ -1082,7 +1093,8 @@ def b200_paged_qkv_decode_attention(partials: torch.Tensor, bias: Optional[torch
         key_pool.data_ptr(), value_pool.data_ptr(), block_table.data_ptr(), lengths.data_ptr(),
         output.data_ptr(), batch, q_heads, kv_heads, dim, blocks, block_size, max_blocks, capacity,
         float(scale), int(split_tokens), int(max_length_hint), int(length_offset),
-        _ptr(norm_row_squares), int(norm_hidden), float(norm_epsilon), _ptr(workspace), need,
+        _ptr(norm_row_squares), int(norm_hidden), float(norm_epsilon),
+        _order_pointer(sequence_order, batch, device), _ptr(workspace), need,
         rt.status.data_ptr(), _stream())
     _check(code, "b200_paged_qkv_decode_attention")
     _count(rt)

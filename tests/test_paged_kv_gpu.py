@@ -112,6 +112,13 @@ def test_fused_qkv_attention_on_pools_equals_the_contiguous_launch(hq, hkv, d, b
                                                     state.values[0], state.block_table, device_lengths,
                                                     **common)
     assert torch.equal(paged, flat)
+    # a service order only decides which CTAs take which sequence
+    order = torch.tensor([4, 3, 5, 2, 1, 0], dtype=torch.int32, device="cuda")
+    assert torch.equal(kernels.b200_qkv_decode_attention(partials, bias, cos.cuda(), sin.cuda(), kbuf, vbuf,
+                                                         device_lengths, sequence_order=order, **common), flat)
+    assert torch.equal(kernels.b200_paged_qkv_decode_attention(
+        partials, bias, cos.cuda(), sin.cuda(), state.keys[0], state.values[0], state.block_table,
+        device_lengths, sequence_order=order, **common), flat)
     for b in range(batch):
         got_k, got_v = state.gather(0, b, int(lengths[b]))
         assert torch.equal(got_k, kbuf[b, :lengths[b]]) and torch.equal(got_v, vbuf[b, :lengths[b]])
