@@ -162,6 +162,9 @@ def timeline_case(args):
     library.b200_trace_attach.argtypes = [ctypes.c_void_p]
     device = torch.device("cuda", torch.cuda.current_device())
     config = q2.QWEN2_0_5B
+    if args.model == "qwen2-7b":  # four full-width layers show the chain; the rest only repeat it
+        import dataclasses
+        config = dataclasses.replace(q2.QWEN2_7B, num_layers=4)
     weights = q2.make_weights(config, seed=0, dtype=torch.bfloat16, device=device,
                               reproducible=False)
     engine = Qwen2Engine(config, weights, batch=args.batch, capacity=args.length + 128)
@@ -452,7 +455,7 @@ def main():
                                        "rms_norm", "timeline", "prefill_step", "compare",
                                        "linear_splitk", "linear_rms", "cpu_baseline"])
     parser.add_argument("--model", default="qwen2-0.5b", choices=["qwen2-0.5b", "qwen2-7b"],
-                        help="prefill_step: architecture")
+                        help="prefill_step, timeline: architecture")
     parser.add_argument("--launches", type=int, default=40, help="timeline: launches to print")
     parser.add_argument("--sweep", action="store_true",
                         help="decode attention over batch {1,8,64,256} x length {64,1024,4096,32768}")
