@@ -125,18 +125,70 @@ def prefill_step_case(args):
     device = torch.device("cuda", torch.cuda.current_device())
     config = q2.QWEN2_7B if args.model == "qwen2-7b" else q2.QWEN2_0_5B
     weights = q2.make_weights(config, seed=0, dtype=torch.bfloat16, device=device, reproducible=False)
-    engine = Qwen2Engine(config, weights, batch=args.batch, capacity=args.tokens + 64)
     ids = torch.randint(0, config.vocab_size, (args.batch, args.tokens), device=device)
-    seconds = time_launches(lambda _: engine.prefill(ids), 1, min(args.warmup, 3), min(args.iters, 10))
+    if args.path == "executor":
+        return prefill_graph_case(args, config, weights, ids)
+    engine = Qwen2Engine(config, weights, batch=args.batch, capacity=args.tokens + 64)
+    if args.all_logits:
+        seconds = time_launches(lambda _: engine.prefill(ids, all_logits=True), 1, min(args.warmup, 3),
+                                min(args.iters, 10))
+    else:
+        seconds = time_launches(lambda _: engine.prefill(ids), 1, min(args.warmup, 3), min(args.iters, 10))
     layer_params = (config.hidden_size * (config.q_size + 2 * config.kv_size) + config.q_size * config.hidden_size +
                     3 * config.hidden_size * config.intermediate_size)
     tokens = args.batch * args.tokens
     gemm_flops = 2 * tokens * layer_params * config.num_layers
     attention_flops = 2 * args.batch * config.num_heads * args.tokens ** 2 * config.head_dim * config.num_layers
     return {"op": "prefill_step", "model": args.model, "batch": args.batch, "tokens": args.tokens,
+            "path": "engine", "all_logits": bool(args.all_logits),
             "ms": seconds * 1e3, "prompt_tokens_per_s": tokens / seconds,
             "tflops": (gemm_flops + attention_flops) / seconds / 1e12,
             "gemm_tflop": gemm_flops / 1e12, "causal_attention_tflop": attention_flops / 1e12}
+
+
+def prefill_graph_case(args, config, weights, ids):
+    """The drop-in path for prefill: the reference's own KernelIR of the Qwen2-0.5B prefill
+    (exported and compiled by the reference, tests/golden/...json.gz: logits for every position,
+    the additive mask an argument of the graph), finished by lower_to_b200 and interpreted by
+    B200Executor, eagerly as the reference's executor runs it. Three ways of treating the mask:
+    declared causal by the caller, classified on the device by the executor, taken as data."""
+
+    import gzip
+
+    from llm_compiler_b200 import kernel_ir
+    from llm_compiler_b200 import qwen2 as q2
+    from llm_compiler_b200.executor import B200Executor, bind_arguments
+
+    if args.model != "qwen2-0.5b":
+        raise SystemExit("--path executor runs the shipped Qwen2-0.5B prefill graph")
+    batch, tokens = ids.shape
+    device = ids.device
+    future = torch.triu(torch.ones(tokens, tokens, dtype=torch.bool, device=device), diagonal=1)
+    mask = torch.zeros(batch, 1, tokens, tokens, device=device).masked_fill(future, float("-inf"))
+    positions = torch.arange(tokens, device=device).repeat(batch, 1)
+    path = Path(__file__).resolve().parent / "tests" / "golden" / "kernel_ir_qwen2_0_5b_prefill_fast.json.gz"
+    rows = []
+    for label, declared, classify in (("declared causal", ("attention_mask",), True),
+                                      ("classified on the device", (), True),
+                                      ("mask as data", (), False)):
+        module = kernel_ir.module_from_json(json.loads(gzip.open(path).read()))
+        kernel_ir.lower_to_b200(module, causal_mask_arguments=declared)
+        kernel_ir.require_full_lowering(module)
+        executor = B200Executor(strict=True, classify_masks=classify)
+        arguments = bind_arguments(module.functions[0], weights, {
+            "input_ids": ids, "attention_mask": mask, "position_ids": positions,
+            "inv_freq": q2.inverse_frequency(config, device)})
+        before = kernels.launch_count(device)
+        executor.run(module, arguments)
+        launches = kernels.launch_count(device) - before
+        seconds = time_launches(lambda _: executor.run(module, arguments), 1, 1, min(args.iters, 5))
+        rows.append({"op": "prefill_step", "model": args.model, "batch": batch, "tokens": tokens,
+                     "path": "executor", "mask": label, "all_logits": True, "kernels": launches,
+                     "ms": seconds * 1e3, "prompt_tokens_per_s": batch * tokens / seconds})
+        print(json.dumps(rows[-1]), flush=True)
+        del executor, module, arguments
+        torch.cuda.empty_cache()
+    return {"op": "prefill_step", "path": "executor", "variants": len(rows)}
 
 
 def timeline_case(args):
@@ -457,6 +509,11 @@ def main():
     parser.add_argument("--model", default="qwen2-0.5b", choices=["qwen2-0.5b", "qwen2-7b"],
                         help="prefill_step, timeline: architecture")
     parser.add_argument("--launches", type=int, default=40, help="timeline: launches to print")
+    parser.add_argument("--path", default="engine", choices=["engine", "executor"],
+                        help="prefill_step: Qwen2Engine.prefill, or the reference's prefill KernelIR "
+                             "through lower_to_b200 + B200Executor")
+    parser.add_argument("--all-logits", action="store_true",
+                        help="prefill_step --path engine: logits for every position, as the reference's graph")
     parser.add_argument("--sweep", action="store_true",
                         help="decode attention over batch {1,8,64,256} x length {64,1024,4096,32768}")
     measurement_arguments(parser)
