@@ -545,6 +545,8 @@ _CONTRACTS = {
     "kernel.b200.add": _elementwise,
     "kernel.b200.pack_rows": _pack,
     "kernel.b200.interleave_rows": _pack,
+    "runtime.view.last_token": lambda c: None if len(c.operation.operands) == 1 and
+    len(c.operation.results) == 1 else c.fail("takes one tensor and yields one view"),
     "runtime.kv.init": _kv_runtime,
     "runtime.kv.length": _kv_runtime,
     "runtime.kv.advance": _kv_runtime,

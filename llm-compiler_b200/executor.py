@@ -120,6 +120,7 @@ class B200Executor:
             "kernel.b200.pack_rows": lambda o, a, e: kernels.b200_pack_rows(*o),
             "kernel.b200.interleave_rows": lambda o, a, e: kernels.interleave_gate_up(o[0], o[1]),
             "runtime.view.slice": self._slice,
+            "runtime.view.last_token": self._last_token,
             "kernel.b200.swiglu": lambda o, a, e: kernels.b200_swiglu(o[0], o[1]),
             "kernel.b200.add": lambda o, a, e: kernels.b200_add(o[0], o[1]),
             "kernel.b200.contiguous": self._contiguous,
@@ -481,6 +482,13 @@ class B200Executor:
     def _slice(operands, attributes, environment):
         tensor, axis, start, stop = decode_attribute(attributes["args"], environment)
         return tensor.narrow(int(axis), int(start), int(stop) - int(start))
+
+    @staticmethod
+    def _last_token(operands, attributes, environment):
+        if len(operands) != 1 or operands[0].ndim < 2:
+            raise ExecutionError("last_token takes one tensor of rank 2 or more")
+        axis = int(attributes.get("axis", 1))
+        return operands[0].narrow(axis, operands[0].shape[axis] - 1, 1)
 
     @staticmethod
     def _kv_prefill_store(operands, attributes, environment):

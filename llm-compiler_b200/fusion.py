@@ -430,6 +430,46 @@ def fuse_qkv_attention(function, zero_mask_arguments: Sequence[str]) -> int:
     return fused
 
 
+def take_last_token_logits(function) -> int:
+    """Prefill graphs return logits for every position (qwen2.py:418-424) although a serving
+    loop samples from the last one only. Where the caller opts in, the hidden rows are cut to the
+    last position in front of the final norm (or, if that is not a single-use rms_norm, in front
+    of the LM head): `runtime.view.last_token` [x] -> x[:, -1:, :], a view. The first result of
+    the function becomes B x 1 x V. Returns 1 if the graph was rewritten."""
+
+    if not function.returns:
+        return 0
+    producers = _producer_map(function)
+    users = _users(function)
+    head = producers.get(function.returns[0].name)
+    if head is None or head.name not in ("kernel.b200.linear", "kernel.b200.norm_linear") or \
+            (head.attributes.get("epilogue") or "none") != "none":
+        return 0
+    chain = [head]
+    if head.name == "kernel.b200.linear":
+        norm = producers.get(head.operands[0].name)
+        if norm is not None and norm.name == "kernel.b200.rms_norm" and \
+                _single_user(users, norm.results[0]) is head:
+            chain.insert(0, norm)
+    hidden = chain[0].operands[0]
+    match = _DIMS.match(str(hidden.type))
+    if not match or len(_split_dims(match.group(1))) != 3 or _static_extent(hidden, 1) == 1:
+        return 0
+    last = Value(_fresh(function, "last_token"), retype(hidden, 1, 1))
+    view = Operation("runtime.view.last_token", [hidden], [last],
+                     {"axis": 1, "lowered_from": "last-token logits"})
+    operations = function.block.operations
+    operations.insert(operations.index(chain[0]), view)
+    chain[0].operands[0] = last
+    for operation in chain:  # B x T x * becomes B x 1 x * down to the returned logits
+        for result in operation.results:
+            result.type = retype(result, 1, 1)
+    for value in function.returns:
+        if value.name == head.results[0].name:
+            value.type = head.results[0].type
+    return 1
+
+
 def decode_attribute_static(tree):
     """The importer's argument tree with SSA references left as their names."""
     if isinstance(tree, dict):

@@ -175,6 +175,7 @@ EXECUTABLE_OPERATIONS = frozenset(_KERNEL_SOURCES.values()) | frozenset(_RUNTIME
         "kernel.b200.rope_table", "kernel.b200.swiglu",
         # produced by the graph-level fusion passes (fusion.py)
         "kernel.b200.pack_rows", "kernel.b200.interleave_rows", "runtime.view.slice",
+        "runtime.view.last_token",
         "kernel.b200.rope_kv_store", "kernel.b200.scale_columns", "kernel.b200.norm_linear",
         "kernel.b200.qkv_decode_attention", "runtime.kv.advance_all"})
 
@@ -445,7 +446,8 @@ def lower_to_b200(module, *, numerical_mode: Optional[str] = None,
                   fuse_epilogues: bool = True, fuse_graph: bool = True,
                   causal_mask_arguments: Iterable[str] = (),
                   zero_mask_arguments: Iterable[str] = (),
-                  fuse_decode_chain: bool = True) -> LoweringReport:
+                  fuse_decode_chain: bool = True,
+                  last_token_logits: bool = False) -> LoweringReport:
     """Rewrites `module` in place for the B200 target. `numerical_mode` overrides the mode the
     reference's pass recorded on each op (attribute `numerical_mode`, or implied by a
     `kernel.cuda.*` / `kernel.cublas.*` name); default "fast". `fuse_graph` runs the
@@ -455,7 +457,9 @@ def lower_to_b200(module, *, numerical_mode: Optional[str] = None,
     form. `fuse_decode_chain` (fast bf16 ops only) folds each RMSNorm into the projection behind
     it and, where `zero_mask_arguments` names the decode step's mask input as all zero, turns a
     decode layer's projection -> RoPE -> KV store -> advance -> attention into the fused
-    attention op, with the per-slot length updates hoisted into one op at the end. Idempotent."""
+    attention op, with the per-slot length updates hoisted into one op at the end.
+    `last_token_logits` (opt-in: it changes the first result to B x 1 x V) computes the final norm
+    and the LM head of a prefill for the last position only. Idempotent."""
 
     if numerical_mode is not None and numerical_mode not in NUMERICAL_MODES:
         raise ValueError(f"unknown numerical mode {numerical_mode!r}; choose from {NUMERICAL_MODES}")
@@ -501,6 +505,10 @@ def lower_to_b200(module, *, numerical_mode: Optional[str] = None,
             from . import fusion
 
             rules["causal_mask"] += fusion.mark_causal_masks(function, tuple(causal_mask_arguments))
+        if last_token_logits:
+            from . import fusion
+
+            rules["last_token_logits"] += fusion.take_last_token_logits(function)
     return LoweringReport(numerical_mode or "per-op", {k: v for k, v in sorted(rules.items()) if v},
                           removed_casts, removed_dead, analyze_lowering_coverage(module))
 

@@ -168,11 +168,12 @@ def prefill_graph_case(args, config, weights, ids):
     positions = torch.arange(tokens, device=device).repeat(batch, 1)
     path = Path(__file__).resolve().parent / "tests" / "golden" / "kernel_ir_qwen2_0_5b_prefill_fast.json.gz"
     rows = []
-    for label, declared, classify in (("declared causal", ("attention_mask",), True),
-                                      ("classified on the device", (), True),
-                                      ("mask as data", (), False)):
+    for label, declared, classify, last in (("declared causal", ("attention_mask",), True, False),
+                                            ("classified on the device", (), True, False),
+                                            ("mask as data", (), False, False),
+                                            ("declared causal, last-token logits", ("attention_mask",), True, True)):
         module = kernel_ir.module_from_json(json.loads(gzip.open(path).read()))
-        kernel_ir.lower_to_b200(module, causal_mask_arguments=declared)
+        kernel_ir.lower_to_b200(module, causal_mask_arguments=declared, last_token_logits=last)
         kernel_ir.require_full_lowering(module)
         executor = B200Executor(strict=True, classify_masks=classify)
         arguments = bind_arguments(module.functions[0], weights, {
@@ -183,7 +184,7 @@ def prefill_graph_case(args, config, weights, ids):
         launches = kernels.launch_count(device) - before
         seconds = time_launches(lambda _: executor.run(module, arguments), 1, 1, min(args.iters, 5))
         rows.append({"op": "prefill_step", "model": args.model, "batch": batch, "tokens": tokens,
-                     "path": "executor", "mask": label, "all_logits": True, "kernels": launches,
+                     "path": "executor", "mask": label, "all_logits": not last, "kernels": launches,
                      "ms": seconds * 1e3, "prompt_tokens_per_s": batch * tokens / seconds})
         print(json.dumps(rows[-1]), flush=True)
         del executor, module, arguments

@@ -84,6 +84,42 @@ def test_prefill_then_decode_graphs_match_the_reference_executor(mode, fuse, gol
                                                    for e in masks)
 
 
+@pytest.mark.parametrize("tag,mode", [("fp32", "fast"), ("fp32", "pytorch_compatible"), ("bf16", "fast")])
+def test_last_token_logits_prefill_matches_the_last_row_of_the_reference(tag, mode, golden_tiny):
+    """lower_to_b200(last_token_logits=True): the prefill returns B x 1 x V logits equal to the
+    last position of the reference executor's full logits, and the same KV state as the full
+    graph (the cut sits behind the last decoder layer)."""
+    gold = golden_tiny[tag]
+    config = q2.Qwen2Config(**gold["config"])
+    dtype = torch.float32 if tag == "fp32" else torch.bfloat16
+    weights = {k: v.cuda() for k, v in q2.make_weights(config, seed=0, dtype=dtype).items()}
+    batch, prompt = gold["batch"], gold["prompt"]
+    inputs = {"input_ids": gold["input_ids"].cuda(), "attention_mask": causal_mask(batch, prompt),
+              "position_ids": torch.arange(prompt).repeat(batch, 1).cuda(),
+              "inv_freq": q2.inverse_frequency(config, "cuda")}
+    outputs = {}
+    for cut in (False, True):
+        module = lowered("prefill", mode, tag, last_token_logits=cut)
+        result = B200Executor(strict=True).run(module, bind_arguments(module.functions[0], weights, inputs))
+        outputs[cut] = result.outputs
+        assert ("runtime.view.last_token" in result.executed_operations) == cut
+    logits, state = outputs[True]
+    assert logits.shape == (batch, 1, config.vocab_size)
+    reference = gold["prefill_logits"][:, -1:]
+    if tag == "fp32":
+        torch.testing.assert_close(logits.cpu(), reference, rtol=1e-4, atol=1e-4)
+    else:
+        scale = float(reference.float().abs().max())
+        assert float((logits.float().cpu() - reference.float()).abs().max()) <= max(5e-2 * scale, 2e-2)
+    if tag == "fp32":
+        assert torch.equal(logits[:, 0].argmax(-1).cpu(), gold["tokens"][:, 0])
+    full_state = outputs[False][1]
+    for layer in range(config.num_layers):
+        assert torch.equal(state.keys[layer][:, :prompt], full_state.keys[layer][:, :prompt])
+        assert torch.equal(state.values[layer][:, :prompt], full_state.values[layer][:, :prompt])
+        assert torch.equal(state.lengths[layer], full_state.lengths[layer])
+
+
 def test_decode_graph_runs_under_cuda_graph_capture(golden_tiny):
     """The interpreter itself is capture-safe: one decode step captured and replayed."""
     gold = golden_tiny["fp32"]

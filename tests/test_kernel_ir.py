@@ -10,6 +10,7 @@ from pathlib import Path
 
 import pytest
 
+from llm_compiler_b200 import fusion
 from llm_compiler_b200 import kernel_ir as ir
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
@@ -164,6 +165,41 @@ def test_bf16_tiny_graphs_lower_fully(kind, mode):
             assert op.attributes["numerical_mode"] == mode
     # the RMSNorm is folded into the projection behind it in the fast mode only
     assert (names["kernel.b200.norm_linear"] > 0) == (mode == "fast")
+
+
+@pytest.mark.parametrize("source", ["tiny_fp32", "tiny_bf16", "qwen2_0_5b"])
+def test_last_token_logits_cut_the_prefill_in_front_of_the_final_norm(source):
+    """lower_to_b200(last_token_logits=True): the hidden rows are cut to the last position in
+    front of the final norm + LM head (a view op), the first result becomes B x 1 x V, every
+    other op keeps its type; decode graphs (one token already) and a second application change
+    nothing."""
+    def fresh(kind):
+        if source == "qwen2_0_5b":
+            return load_gz(f"kernel_ir_qwen2_0_5b_{kind}_fast.json.gz")
+        if source == "tiny_bf16":
+            return ir.module_from_json(json.loads((GOLDEN / f"kernel_ir_tiny_bf16_{kind}_fast.json").read_text()))
+        return load(kind, "fast")
+
+    full, cut = fresh("prefill"), fresh("prefill")
+    ir.lower_to_b200(full)
+    report = ir.lower_to_b200(cut, last_token_logits=True)
+    assert report.lowered_rules["last_token_logits"] == 1
+    ir.verify_module(cut)
+    ir.require_full_lowering(cut)
+    names = Counter(op.name for op in cut.functions[0].block.operations)
+    assert names["runtime.view.last_token"] == 1
+    assert len(cut.functions[0].block.operations) == len(full.functions[0].block.operations) + 1
+    dims = lambda value: fusion._split_dims(fusion._DIMS.match(str(value.type)).group(1))
+    before, after = dims(full.functions[0].returns[0]), dims(cut.functions[0].returns[0])
+    assert after[1] == "1" and after[0] == before[0] and after[2] == before[2] and before[1] != "1"
+    view = next(op for op in cut.functions[0].block.operations if op.name == "runtime.view.last_token")
+    consumer = next(op for op in cut.functions[0].block.operations
+                    if any(operand is view.results[0] for operand in op.operands))
+    assert consumer.name in ("kernel.b200.rms_norm", "kernel.b200.norm_linear")
+    again = ir.lower_to_b200(cut, last_token_logits=True)
+    assert "last_token_logits" not in again.lowered_rules
+    decode = fresh("decode")
+    assert "last_token_logits" not in ir.lower_to_b200(decode, last_token_logits=True).lowered_rules
 
 
 def test_only_declared_masks_are_marked_causal():
