@@ -10,6 +10,7 @@ import pytest
 import torch
 
 from llm_compiler_b200 import kernel_ir as ir
+from llm_compiler_b200 import kernels
 from llm_compiler_b200 import qwen2 as q2
 from llm_compiler_b200.executor import B200Executor, bind_arguments
 from llm_compiler_b200.kv_state import ExecutionError, PreallocatedKVCacheState
@@ -118,6 +119,42 @@ def test_last_token_logits_prefill_matches_the_last_row_of_the_reference(tag, mo
         assert torch.equal(state.keys[layer][:, :prompt], full_state.keys[layer][:, :prompt])
         assert torch.equal(state.values[layer][:, :prompt], full_state.values[layer][:, :prompt])
         assert torch.equal(state.lengths[layer], full_state.lengths[layer])
+
+
+@pytest.mark.parametrize("tag", ["fp32", "bf16"])
+def test_prefill_graph_runs_under_cuda_graph_capture(tag, golden_tiny):
+    """A whole prefill (state creation included) captured once and replayed on new token ids:
+    logits and KV equal to the eager run of the same module on those ids. The mask is declared
+    causal (a mask left to the executor is not classified under capture and takes the
+    additive-mask kernel: also captured below)."""
+    gold = golden_tiny[tag]
+    config = q2.Qwen2Config(**gold["config"])
+    dtype = torch.float32 if tag == "fp32" else torch.bfloat16
+    weights = {k: v.cuda() for k, v in q2.make_weights(config, seed=0, dtype=dtype).items()}
+    batch, prompt = gold["batch"], gold["prompt"]
+    ids = gold["input_ids"].cuda().clone()
+    inputs = {"input_ids": ids, "attention_mask": causal_mask(batch, prompt),
+              "position_ids": torch.arange(prompt).repeat(batch, 1).cuda(),
+              "inv_freq": q2.inverse_frequency(config, "cuda")}
+    other = (gold["input_ids"].cuda() * 7 + 3) % config.vocab_size
+    for options in ({"causal_mask_arguments": ("attention_mask",), "last_token_logits": True}, {}):
+        module = lowered("prefill", "fast", tag, **options)
+        executor = B200Executor(strict=True)
+        arguments = bind_arguments(module.functions[0], weights, inputs)
+        ids.copy_(other)
+        eager_logits, eager_state = executor.run(module, arguments).outputs  # also sizes the workspaces
+        eager_logits = eager_logits.clone()
+        ids.copy_(gold["input_ids"].cuda())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits, state = executor.run(module, arguments).outputs
+        ids.copy_(other)
+        graph.replay()
+        assert torch.equal(logits, eager_logits)
+        for layer in range(config.num_layers):
+            assert torch.equal(state.keys[layer], eager_state.keys[layer])
+            assert torch.equal(state.lengths[layer], eager_state.lengths[layer])
+        kernels.runtime().check_status()
 
 
 def test_decode_graph_runs_under_cuda_graph_capture(golden_tiny):
