@@ -1215,14 +1215,30 @@ int launch_bf16(const DecodeParams& p, cudaStream_t stream, int flat_grid = 0) {
 
 int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
-// Tokens per split when the caller does not choose. The grid is (splits x head blocks x
-// batch) CTAs over 148 SMs x 2 resident CTAs; the score of a candidate split count is the
-// fill of its last wave times the share of a CTA's life spent streaming rather than ramping
-// its pipeline up (about 96 tokens' worth). Splits are multiples of the 128 tokens the four
-// warps cover per step and never shorter than 256 tokens.
+// Tokens per split when the caller does not choose. A (sequence, head block) unit is served by
+// 8-warp CTAs, one per SM (an even number of 4-warp splits is run as half as many 8-warp CTAs):
+// - up to 148 units: as many 8-warp CTAs per unit as fit one wave of 148, none shorter than
+//   768 tokens, none longer than 8192. Measured at 4580 tokens, 14 / 2 heads x 64 (us, this rule / the rule it
+//   replaced, which scored "fill of 296 slots x streaming share"): 16 sequences 12.3 / 17.1,
+//   32: 17.7 / 29.5, 48: 21.7 / 36.8, 64: unchanged (one 8-warp CTA per unit);
+// - up to 296 units: one 4-warp CTA per unit, two per SM, all resident at once (96 sequences
+//   38.0 / 51.7, 128: 48.7 / 63.6);
+// - beyond: several waves whatever the split; the earlier scoring stands (splits are multiples
+//   of the 128 tokens four warps cover per step and never shorter than 256 tokens).
 int64_t default_split_tokens(int64_t batch, int64_t head_blocks, int64_t max_length) {
-  const int64_t slots = static_cast<int64_t>(kNumSMs) * 2;
   const int64_t units = batch * head_blocks;
+  if (units <= kNumSMs) {
+    int64_t wide = std::min<int64_t>(kNumSMs / std::max<int64_t>(units, 1), std::max<int64_t>(max_length / 768, 1));
+    // (nor longer than 8192 tokens: with ragged lengths the longest sequence would set the time;
+    // several waves of 2 MB pieces balance, and their fixed cost is small beside 20 us of streaming)
+    wide = std::max<int64_t>(wide, ceil_div(max_length, 8192));
+    for (; wide >= 1; --wide) {
+      const int64_t tokens = round_up(ceil_div(max_length, 2 * wide), 128);
+      if (ceil_div(max_length, tokens) == 2 * wide || wide == 1) return tokens;
+    }
+  }
+  if (units <= 2 * kNumSMs) return round_up(max_length, 128);
+  const int64_t slots = static_cast<int64_t>(kNumSMs) * 2;
   int64_t best_tokens = round_up(max_length, 128);
   double best_score = -1.0;
   for (int64_t splits = 1; splits <= 64; ++splits) {

@@ -165,7 +165,7 @@ def profile_case(args):
     probe.warmup, probe.iters = max(3, args.warmup // 2), max(10, args.iters // 4)
     layout = {"q_heads": args.q_heads, "kv_heads": args.kv_heads, "head_dim": args.head_dim,
               "dtype": "bf16"}
-    for batch in (1, 8, 64, 256):
+    for batch in (1, 8, 16, 32, 64, 128, 256):
         for length in (256, 1024, 4096, 16384, 32768):
             costs = {}
             for split in (0, 512, 1024, 2048, 4096, 8192):
