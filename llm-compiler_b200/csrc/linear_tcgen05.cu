@@ -230,7 +230,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   const int nkb = max(0, min(kb_first + kb_per, kb_total) - kb_first);
   const uint32_t smem_base = smem_u32(smem);
   // warps 2 and 3 square the rows of x as they pass through shared memory
-  const bool squares = A_ROWS == 64 && ((p.norm_input != nullptr && p.norm_squares == nullptr) ||
+  const bool squares = A_ROWS <= 128 && ((p.norm_input != nullptr && p.norm_squares == nullptr) ||
                                         (p.row_squares != nullptr && tile_n == 0));
 
   if (threadIdx.x == 0) {
@@ -315,24 +315,31 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
     // the swizzle only permutes chunks within the row, which a sum does not care about; columns
     // beyond K are zero-filled by the copy). One fixed summation order per row, no extra global
     // traffic, and the row factors are ready when the last k-block is.
+    // (A_ROWS == 128: the same 64 threads take rows t and t + 64 of every box)
+    constexpr int kRowsEach = A_ROWS / 64;
     const int r = (warp - 2) * 32 + lane;
-    float ss = 0.0f;
+    float ss[kRowsEach];
+#pragma unroll
+    for (int h = 0; h < kRowsEach; ++h) ss[h] = 0.0f;
     bool fine = true;
     for (int kb = 0; kb < nkb && fine; ++kb) {
       const int s = kb % STAGES;
       fine = __all_sync(0xffffffffu, mbarrier_wait_bounded(smem_u32(&full_bar[s]), (kb / STAGES) & 1, p.wait_limit));
-      if (fine && r < A_ROWS) {
-        const uint32_t row_addr = smem_base + s * kStageBytes + r * 128;
+      if (fine) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          uint4 raw;
-          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
-                       : "r"(row_addr + (((j + r) & 7) << 4)));
-          ss = fmaf(bf16_lo(raw.x), bf16_lo(raw.x), ss); ss = fmaf(bf16_hi(raw.x), bf16_hi(raw.x), ss);
-          ss = fmaf(bf16_lo(raw.y), bf16_lo(raw.y), ss); ss = fmaf(bf16_hi(raw.y), bf16_hi(raw.y), ss);
-          ss = fmaf(bf16_lo(raw.z), bf16_lo(raw.z), ss); ss = fmaf(bf16_hi(raw.z), bf16_hi(raw.z), ss);
-          ss = fmaf(bf16_lo(raw.w), bf16_lo(raw.w), ss); ss = fmaf(bf16_hi(raw.w), bf16_hi(raw.w), ss);
+        for (int h = 0; h < kRowsEach; ++h) {
+          const uint32_t row_addr = smem_base + s * kStageBytes + (r + 64 * h) * 128;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint4 raw;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                         : "r"(row_addr + (((j + r) & 7) << 4)));
+            ss[h] = fmaf(bf16_lo(raw.x), bf16_lo(raw.x), ss[h]); ss[h] = fmaf(bf16_hi(raw.x), bf16_hi(raw.x), ss[h]);
+            ss[h] = fmaf(bf16_lo(raw.y), bf16_lo(raw.y), ss[h]); ss[h] = fmaf(bf16_hi(raw.y), bf16_hi(raw.y), ss[h]);
+            ss[h] = fmaf(bf16_lo(raw.z), bf16_lo(raw.z), ss[h]); ss[h] = fmaf(bf16_hi(raw.z), bf16_hi(raw.z), ss[h]);
+            ss[h] = fmaf(bf16_lo(raw.w), bf16_lo(raw.w), ss[h]); ss[h] = fmaf(bf16_hi(raw.w), bf16_hi(raw.w), ss[h]);
+          }
         }
       }
       __syncwarp();
@@ -340,34 +347,42 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty_bar[s])) : "memory");
     }
     if (!fine) failed = 1;
-    if (p.norm_input != nullptr)
-      row_scale[r] = rsqrtf(ss / static_cast<float>(p.k) + p.norm_eps);
-    else if (r < p.m)
-      p.row_squares[static_cast<int64_t>(split) * p.m + r] = fine ? ss : 0.0f;
+#pragma unroll
+    for (int h = 0; h < kRowsEach; ++h) {
+      const int row = r + 64 * h;
+      if (p.norm_input != nullptr)
+        row_scale[row] = rsqrtf(ss[h] / static_cast<float>(p.k) + p.norm_eps);
+      else if (tile_m * kBM + row < p.m)
+        p.row_squares[static_cast<int64_t>(split) * p.m + tile_m * kBM + row] = fine ? ss[h] : 0.0f;
+    }
   }
-  if (warp >= 2 && A_ROWS == 64 && p.norm_squares != nullptr) {
+  if (warp >= 2 && p.norm_squares != nullptr) {
     // Folded RMSNorm, row sums of squares left by the kernel that produced x: thread t of warps
-    // 2 and 3 adds the slices of row t in slice order (L2 reads, sixteen in flight) while the
-    // main loop runs. The slices are that kernel's output: wait for it first.
+    // 2 and 3 adds the slices of row t (and of row t + 64 of a 128-row tile) in slice order (L2
+    // reads, sixteen in flight) while the main loop runs. The slices are that kernel's output:
+    // wait for it first.
     if (lane == 0) grid_dependency_wait();
     __syncwarp();
-    const int r = (warp - 2) * 32 + lane;
-    float ss = 0.0f;
-    if (r < p.m) {
-      const float* src = p.norm_squares + r;
-      int slice = 0;
 #pragma unroll 1
-      for (; slice + 16 <= p.norm_slices; slice += 16) {
-        float t[16];
+    for (int row = (warp - 2) * 32 + lane; row < A_ROWS; row += 64) {
+      const int global_row = tile_m * kBM + row;
+      float ss = 0.0f;
+      if (global_row < p.m) {
+        const float* src = p.norm_squares + global_row;
+        int slice = 0;
+#pragma unroll 1
+        for (; slice + 16 <= p.norm_slices; slice += 16) {
+          float t[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) t[i] = __ldcg(src + static_cast<int64_t>(slice + i) * p.m);
+          for (int i = 0; i < 16; ++i) t[i] = __ldcg(src + static_cast<int64_t>(slice + i) * p.m);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) ss += t[i];
+          for (int i = 0; i < 16; ++i) ss += t[i];
+        }
+#pragma unroll 1
+        for (; slice < p.norm_slices; ++slice) ss += __ldcg(src + static_cast<int64_t>(slice) * p.m);
       }
-#pragma unroll 1
-      for (; slice < p.norm_slices; ++slice) ss += __ldcg(src + static_cast<int64_t>(slice) * p.m);
+      row_scale[row] = rsqrtf(ss / static_cast<float>(p.k) + p.norm_eps);
     }
-    row_scale[r] = rsqrtf(ss / static_cast<float>(p.k) + p.norm_eps);
   }
   if (warp == 1 && lane == 0) {
     // ---- MMA issuer ----
@@ -1009,7 +1024,7 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
                    int epilogue, int32_t* status, cudaStream_t stream, bool fold_norm,
                    double norm_eps, const float* norm_squares, int norm_slices) {
   if (ceil_div(m, kBM) > 65535) return B200_ERR_UNSUPPORTED;
-  if (fold_norm && m > 64) return B200_ERR_UNSUPPORTED;  // the idle-warp scheme of the decode tiles
+  if (fold_norm && m > 128) return B200_ERR_UNSUPPORTED;  // the idle-warp scheme: one or two rows a thread
   int bn;
   bool persistent = false;
   if (m > 64) {
@@ -1137,7 +1152,7 @@ int linear_partial_tcgen05(const void* input, const void* weight, float* partial
                            float* row_squares, int64_t m, int64_t k, int64_t n,
                            int64_t input_row_stride, int splits, int32_t* status,
                            cudaStream_t stream) {
-  if (row_squares != nullptr && m > 64) return B200_ERR_UNSUPPORTED;
+  if (row_squares != nullptr && m > 128) return B200_ERR_UNSUPPORTED;
   const PartialPlan plan = plan_partial(m, k, n);
   const int a_rows = m <= 64 ? 64 : 128;
   CUtensorMap a_map, b_map;
@@ -1261,7 +1276,7 @@ extern "C" int b200_linear_rms_input(const void* input, const void* folded_weigh
     return B200_ERR_BAD_ARGUMENT;
   if (epilogue != B200_EPILOGUE_NONE && epilogue != B200_EPILOGUE_SWIGLU) return B200_ERR_BAD_ARGUMENT;
   if (epilogue == B200_EPILOGUE_SWIGLU && n % 2 != 0) return B200_ERR_BAD_ARGUMENT;
-  if (m > 64) return B200_ERR_TOO_LARGE;
+  if (m > 128) return B200_ERR_TOO_LARGE;
   if (k % 8 != 0 || input_row_stride % 8 != 0) return B200_ERR_UNSUPPORTED;
   if (!aligned16(input) || !aligned16(folded_weight)) return B200_ERR_ALIGNMENT;
   return linear_tcgen05(input, folded_weight, bias, nullptr, output, m, k, n, input_row_stride,
@@ -1284,7 +1299,7 @@ extern "C" int b200_linear_partial(const void* input, const void* weight, void* 
   if (m > 128 || splits > ceil_div(k, kBK) || splits > 65535) return B200_ERR_TOO_LARGE;
   if (k % 8 != 0 || input_row_stride % 8 != 0 || n % 4 != 0) return B200_ERR_UNSUPPORTED;
   if (!aligned16(input) || !aligned16(weight) || !aligned16(partials)) return B200_ERR_ALIGNMENT;
-  if (row_squares != nullptr && m > 64) return B200_ERR_TOO_LARGE;
+  if (row_squares != nullptr && m > 128) return B200_ERR_TOO_LARGE;
   return linear_partial_tcgen05(input, weight, static_cast<float*>(partials),
                                 static_cast<float*>(row_squares), m, k, n, input_row_stride,
                                 static_cast<int>(splits), status, static_cast<cudaStream_t>(stream));

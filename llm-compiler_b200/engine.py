@@ -55,10 +55,12 @@ class Qwen2Engine:
         self.dtype = weights["embed_tokens.weight"].dtype
         self.scale = config.head_dim ** -0.5
         # the five-launch decode layer (RMSNorm folded into q|k|v and gate|up, cluster split-K
-        # o / down with the residual inside): bf16, fast mode, at most 64 rows
+        # o / down with the residual inside): bf16, fast mode, at most 128 rows (B200_CHAIN_ROWS=64
+        # keeps the seven-launch layer from 65 rows on)
         # (B200_DECODE_CHAIN=partials keeps the seven-launch chain with reduce consumers)
         self.folded_norms = (self.dtype == torch.bfloat16 and numerical_mode == "fast" and
-                             batch <= 64 and config.hidden_size % 8 == 0 and
+                             batch <= int(os.environ.get("B200_CHAIN_ROWS", "128")) and
+                             config.hidden_size % 8 == 0 and
                              os.environ.get("B200_DECODE_CHAIN", "folded") != "partials")
         # the o projection leaves the row sums of squares that the gate|up projection's folded
         # RMSNorm needs (B200_NORM_SQUARES=own: gate|up squares its input rows itself)

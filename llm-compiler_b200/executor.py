@@ -272,8 +272,9 @@ class B200Executor:
             return kernels.b200_linear(tensor, weight, bias, residual=residual, epilogue=epilogue)
 
     # The decode chain (fusion.fuse_norm_linear / fuse_qkv_attention): up to this many rows the
-    # folded-norm kernels run; beyond, the same ops are executed as their unfused kernels.
-    CHAIN_ROWS = 64
+    # folded-norm kernels run (one or two rows per idle-warp thread); beyond, the same ops are
+    # executed as their unfused kernels.
+    CHAIN_ROWS = 128
 
     def _norm_linear(self, operands, attributes, environment):
         has_bias = bool(attributes.get("has_bias"))

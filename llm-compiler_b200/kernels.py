@@ -909,7 +909,7 @@ def b200_linear_partial(tensor: torch.Tensor, weight: torch.Tensor,
                         partials: Optional[torch.Tensor] = None, *, row_squares: bool = False):
     """Decode-size projection without its epilogue: fp32 partial sums [splits, M, N] over K
     slices, to be reduced by the operator that follows (b200_reduce_*). M <= 128, bf16.
-    row_squares=True (M <= 64) also returns fp32 [splits, M]: the sum of squares of every input
+    row_squares=True (M <= 128) also returns fp32 [splits, M]: the sum of squares of every input
     row over each K slice, for a consumer that applies an RMSNorm folded into this projection."""
 
     device = _require_cuda(tensor, weight, partials)
@@ -1123,7 +1123,7 @@ def b200_linear_rms_input(tensor: torch.Tensor, folded_weight: torch.Tensor,
                           bias: Optional[torch.Tensor] = None, *, epsilon: float,
                           epilogue: str = "none",
                           row_squares: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """serve.rms_norm + serve.linear in one launch (fast mode, bf16, at most 64 rows): `tensor`
+    """serve.rms_norm + serve.linear in one launch (fast mode, bf16, at most 128 rows): `tensor`
     is the un-normalised input, `folded_weight` the projection weight with the norm weight
     multiplied into its columns (b200_scale_columns); the kernel scales each accumulator row by
     rsqrt(mean(x^2) + epsilon) before the bias / SwiGLU epilogue. `row_squares` (fp32

@@ -204,6 +204,32 @@ def test_captured_graph_survives_workspace_growth():
     small.state.check()
 
 
+@pytest.mark.parametrize("chain_rows", ["128", "64"])
+def test_65_to_128_sequences_on_either_decode_layer(chain_rows, monkeypatch):
+    """100 sequences: the five-launch layer on 128-row tiles (two rows of squares or slices per
+    idle-warp thread), and with B200_CHAIN_ROWS=64 the seven-launch layer of split-K partial
+    producers and reduce consumers; both against the CPU oracle, teacher-forced."""
+    monkeypatch.setenv("B200_CHAIN_ROWS", chain_rows)
+    config = q2.Qwen2Config(hidden_size=896, intermediate_size=4864, num_layers=2, num_heads=14,
+                            num_kv_heads=2, rms_norm_eps=1e-6, rope_theta=1e6, vocab_size=2048,
+                            tie_word_embeddings=True)
+    weights = q2.make_weights(config, seed=6, dtype=torch.bfloat16)
+    prompt = q2.make_prompt_ids(config, 100, 9, seed=8)
+    ref_tokens, ref_logits, _ = qwen2_model.greedy_generate(config, weights, prompt, 2, capacity=16)
+    engine = Qwen2Engine(config, {k: v.cuda() for k, v in weights.items()}, batch=100, capacity=16)
+    assert engine.folded_norms == (chain_rows == "128")
+    engine.prefill(prompt)
+    assert_logits(engine.logits, ref_logits[0], 2e-2)
+    engine.capture()
+    assert engine.kernels_per_step == (2 * 5 + 5 if chain_rows == "128" else 2 * 7 + 6)
+    for step in range(2):
+        engine.input_ids.copy_(ref_tokens[:, step].cuda())
+        engine.decode_step(feed_back=False)
+        assert_logits(engine.logits, ref_logits[step + 1], 2e-2)
+        assert_tokens(engine.next_ids, ref_tokens[:, step + 1], ref_logits[step + 1], 2e-2)
+    engine.state.check()
+
+
 def test_batch_above_the_chain_limit_uses_plain_and_cluster_split_k_projections():
     """130 sequences: beyond the 128 rows of the partial-sum chain, the decode step runs one
     projection per launch, with o / down as cluster split-K projections over two row tiles."""

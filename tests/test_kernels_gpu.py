@@ -829,7 +829,7 @@ def test_scale_columns_is_the_rounded_product():
 
 @pytest.mark.parametrize("epilogue", ["none", "swiglu"])
 @pytest.mark.parametrize("m,k,n", [(64, 896, 9728), (4, 3584, 37888), (3, 256, 1024), (17, 896, 1152),
-                                   (64, 896, 2304)])
+                                   (64, 896, 2304), (100, 896, 9728), (128, 896, 2304), (65, 3584, 4608)])
 def test_linear_rms_input_matches_rms_norm_then_linear(m, k, n, epilogue):
     """serve.rms_norm folded into the projection behind it: un-normalised rows in, the norm
     weight pre-multiplied into the weight's columns, the row factor applied to the accumulator.
@@ -879,7 +879,7 @@ def test_linear_splitk_residual_leaves_row_sums_of_squares(m, k, n):
 
 @pytest.mark.parametrize("epilogue", ["none", "swiglu"])
 @pytest.mark.parametrize("m,k_in,hidden,n", [(64, 896, 896, 9728), (64, 4864, 896, 1152), (5, 256, 256, 1024),
-                                             (33, 512, 1536, 2304)])
+                                             (33, 512, 1536, 2304), (128, 896, 896, 9728), (90, 4864, 896, 2304)])
 def test_linear_rms_input_takes_the_producers_row_squares(m, k_in, hidden, n, epilogue):
     """The folded-RMSNorm projection fed with the row sums of squares that the projection before
     it left (o projection -> gate|up in a decode layer): same result as squaring the rows itself
@@ -905,13 +905,17 @@ def test_linear_rms_input_takes_the_producers_row_squares(m, k_in, hidden, n, ep
     kernels.runtime().check_status()
 
 
-def test_fused_attention_applies_the_folded_norm():
+@pytest.mark.parametrize("batch", [5, 100])
+def test_fused_attention_applies_the_folded_norm(batch):
     """b200_qkv_decode_attention with norm_input: the q|k|v partials come from un-normalised
     rows and a norm-folded weight; the result and the stored K / V rows must match the oracle's
-    rms_norm -> projection -> rope -> store -> attention."""
+    rms_norm -> projection -> rope -> store -> attention. 100 rows: the 128-row tile of the
+    partial producer, two rows of squares per idle-warp thread."""
     g = torch.Generator().manual_seed(77)
     hq, hkv, d, hidden, capacity = 14, 2, 64, 896, 200
     lengths = torch.tensor([1, 64, 65, 200, 131])
+    if batch > lengths.numel():
+        lengths = torch.cat([lengths, torch.randint(1, capacity + 1, (batch - lengths.numel(),), generator=g)])
     b = lengths.numel()
     width = (hq + 2 * hkv) * d
     x = (torch.randn(b, hidden, generator=g) * 2.0).bfloat16()
