@@ -55,11 +55,14 @@ class Qwen2Engine:
         self.dtype = weights["embed_tokens.weight"].dtype
         self.scale = config.head_dim ** -0.5
         # the five-launch decode layer (RMSNorm folded into q|k|v and gate|up, cluster split-K
-        # o / down with the residual inside): bf16, fast mode, at most 128 rows (B200_CHAIN_ROWS=64
-        # keeps the seven-launch layer from 65 rows on)
-        # (B200_DECODE_CHAIN=partials keeps the seven-launch chain with reduce consumers)
+        # o / down with the residual inside): bf16, fast mode, up to 128 rows while the layer's
+        # largest matrix, gate|up, keeps its launch a chain of latencies, 64 rows for large models
+        # (kernels.decode_chain_rows; B200_CHAIN_ROWS overrides). B200_DECODE_CHAIN=partials keeps
+        # the seven-launch layer with reduce consumers.
+        gate_up_bytes = 2 * config.intermediate_size * config.hidden_size * 2
+        chain_rows = int(os.environ.get("B200_CHAIN_ROWS", "0")) or kernels.decode_chain_rows(gate_up_bytes)
         self.folded_norms = (self.dtype == torch.bfloat16 and numerical_mode == "fast" and
-                             batch <= int(os.environ.get("B200_CHAIN_ROWS", "128")) and
+                             batch <= chain_rows and
                              config.hidden_size % 8 == 0 and
                              os.environ.get("B200_DECODE_CHAIN", "folded") != "partials")
         # the o projection leaves the row sums of squares that the gate|up projection's folded

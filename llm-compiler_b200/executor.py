@@ -259,7 +259,7 @@ class B200Executor:
                 tensor.dtype == torch.bfloat16 and rows <= 256 and weight.shape[0] % 4 == 0:
             # few N tiles at decode sizes: the cluster split-K projection that adds the residual
             # itself (same rounding points as the plain kernel's residual epilogue)
-            chain = rows <= self.CHAIN_ROWS  # a folded RMSNorm may follow: leave it the row squares
+            chain = rows <= self._chain_rows(weight)  # a folded RMSNorm may follow: leave it the row squares
             flat = kernels.b200_linear_splitk_residual(
                 tensor.reshape(rows, tensor.shape[-1]), weight, residual.reshape(rows, weight.shape[0]),
                 row_squares=chain)
@@ -276,6 +276,9 @@ class B200Executor:
     # executed as their unfused kernels.
     CHAIN_ROWS = 128
 
+    def _chain_rows(self, weight) -> int:
+        return min(self.CHAIN_ROWS, kernels.decode_chain_rows(weight))
+
     def _norm_linear(self, operands, attributes, environment):
         has_bias = bool(attributes.get("has_bias"))
         if len(operands) != 4 + int(has_bias):
@@ -286,8 +289,8 @@ class B200Executor:
         epsilon = float(attributes["epsilon"])
         rows = tensor.numel() // tensor.shape[-1]
         self.lowering_trace.append({"backend": "b200", "op": "norm_linear", "rows": rows,
-                                    "folded": rows <= self.CHAIN_ROWS})
-        if rows <= self.CHAIN_ROWS and tensor.dtype == torch.bfloat16:
+                                    "folded": rows <= self._chain_rows(weight)})
+        if rows <= self._chain_rows(weight) and tensor.dtype == torch.bfloat16:
             rows_2d = tensor.reshape(rows, tensor.shape[-1])
             left = self._row_squares.get(rows_2d.data_ptr())
             squares = None
@@ -326,8 +329,8 @@ class B200Executor:
         if bound > state.capacity:
             raise ExecutionError("decode attention mask is longer than the KV capacity")
         self.lowering_trace.append({"backend": "b200", "op": "qkv_decode_attention", "rows": rows,
-                                    "fused": rows <= self.CHAIN_ROWS, "length_offset": offset})
-        if rows <= self.CHAIN_ROWS and tensor.dtype == torch.bfloat16:
+                                    "fused": rows <= self._chain_rows(weight), "length_offset": offset})
+        if rows <= self._chain_rows(weight) and tensor.dtype == torch.bfloat16:
             flat = tensor.reshape(rows, tensor.shape[-1])
             partials, squares = kernels.b200_linear_partial(flat, folded, row_squares=True)
             if offset == 0:  # the graph advances this slot here: lengths then count the new token
@@ -443,9 +446,9 @@ class B200Executor:
         if bound > state.capacity:
             raise ExecutionError("decode attention mask is longer than the KV capacity")
         self.lowering_trace.append({"backend": "b200", "op": "qkv_decode_attention", "rows": rows,
-                                    "fused": rows <= self.CHAIN_ROWS, "length_offset": offset,
+                                    "fused": rows <= self._chain_rows(weight), "length_offset": offset,
                                     "layout": "paged"})
-        if rows <= self.CHAIN_ROWS and tensor.dtype == torch.bfloat16:
+        if rows <= self._chain_rows(weight) and tensor.dtype == torch.bfloat16:
             flat = tensor.reshape(rows, tensor.shape[-1])
             partials, squares = kernels.b200_linear_partial(flat, folded, row_squares=True)
             pool_key, pool_value, lengths = state._slot(slot)

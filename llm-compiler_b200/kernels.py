@@ -1119,6 +1119,19 @@ def b200_scale_columns(weight: torch.Tensor, scale: torch.Tensor) -> torch.Tenso
     return output
 
 
+def decode_chain_rows(weight) -> int:
+    """Rows up to which the five-launch decode layer's kernels (folded-norm projection, cluster
+    split-K, fused q|k|v attention) are the faster form of a projection with this weight (a
+    tensor, or its size in bytes): 128
+    while the matrix is small enough for the launch to be a chain of latencies (a Qwen2-0.5B
+    layer at 96 sequences: 1.82 -> 1.69 ms per step), 64 for large matrices, where the 128-row
+    tiles of those kernels re-read the activations through L2 once per 64 columns and lose to
+    the split-K partial producers (Qwen2-7B layers at 128 sequences: 10.1 -> 11.8 ms)."""
+
+    nbytes = weight if isinstance(weight, int) else weight.numel() * weight.element_size()
+    return 128 if nbytes <= (32 << 20) else 64
+
+
 def b200_linear_rms_input(tensor: torch.Tensor, folded_weight: torch.Tensor,
                           bias: Optional[torch.Tensor] = None, *, epsilon: float,
                           epilogue: str = "none",
