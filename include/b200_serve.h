@@ -293,9 +293,11 @@ int b200_prefill_attention(const void* query, const void* key, const void* value
  * aten.add.Tensor that follows o_proj / down_proj, qwen2.py:299-304); 2 SwiGLU over
  * row-interleaved gate/up weights: W holds n rows (gate_j, up_j alternating), the output is
  * [M, n/2] and y[m,j] = r(r(silu(r(gate_j))) * r(up_j)) (qwen2.py:262-264).
- * bf16 problems with more than 64 rows run on tcgen05 tensor cores (TMEM accumulator, TMA-fed
- * 128 x 256 tiles); up to 64 rows on warp-level tiles that stream every weight byte once,
- * with deterministic split-K. Workspace (split-K partial sums + tile counters):
+ * bf16 problems run on tcgen05 tensor cores (TMEM accumulator, TMA-fed stage ring): 64-row
+ * activation boxes and a tile width chosen at run time at decode sizes, 128 x 64..256 tiles
+ * beyond, a persistent two-accumulator kernel from 1024 rows on. Decode-size calls with too
+ * few N tiles to fill the GPU, operands no tensor map can describe and fp32 run on warp-level /
+ * CUDA-core kernels with deterministic split-K. Workspace (split-K partial sums + tile counters):
  * b200_linear_workspace_bytes. `status` receives B200_STATUS_WAIT_TIMEOUT if a bounded
  * in-kernel wait gives up. */
 #define B200_EPILOGUE_NONE 0
@@ -315,7 +317,7 @@ int b200_linear(const void* input, const void* weight, const void* bias, const v
  * one decoder layer of the reference graph (qwen2.py:152-304 after the passes):
  *   b200_linear_partial            serve.linear without its epilogue: partials[s, m, n] (fp32),
  *                                  s < b200_linear_partial_splits(m, k, n); with row_squares
- *                                  (fp32 [splits, m], M <= 64; may be NULL) also the sum of
+ *                                  (fp32 [splits, m], M <= 128; may be NULL) also the sum of
  *                                  squares of every input row over each K slice, for a consumer
  *                                  that applies an RMSNorm folded into this projection
  *   b200_reduce_residual_rms_norm  (o_proj | down_proj result) -> aten.add (residual) ->
@@ -362,7 +364,7 @@ int b200_qkv_decode_attention(const void* qkv_partials, int64_t qkv_splits, cons
                               const int32_t* sequence_order, void* workspace, int64_t workspace_bytes,
                               int32_t* status, void* stream);
 
-/* ---- Decode-step chain, five launches per layer (fast mode, bf16, M <= 64 rows) ----------
+/* ---- Decode-step chain, five launches per layer (fast mode, bf16, M <= 128 rows) ---------
  * The serve.rms_norm in front of a projection (qwen2.py:152-304: input_layernorm -> q|k|v,
  * post_attention_layernorm -> gate|up) is folded into that projection instead of being a launch
  * of its own: y = rsqrt(mean(x^2) + eps) * (x (W * w_norm)^T), with the norm weight multiplied
