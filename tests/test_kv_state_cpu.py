@@ -68,3 +68,14 @@ def test_contiguous_state_checks_its_slots_before_any_launch():
         state._slot(2)
     with pytest.raises(ExecutionError):
         PreallocatedKVCacheState(keys, keys[:1], lengths, 64)
+
+
+def test_decode_chain_rows_and_service_order_helpers():
+    from llm_compiler_b200 import kernels
+
+    assert kernels.decode_chain_rows(torch.empty(9728, 896, dtype=torch.bfloat16)) == 128  # 17 MB
+    assert kernels.decode_chain_rows(torch.empty(37888, 3584, dtype=torch.bfloat16, device="meta")) == 64
+    assert kernels.decode_chain_rows(32 << 20) == 128 and kernels.decode_chain_rows((32 << 20) + 1) == 64
+    lengths = torch.tensor([5, 900, 17, 900, 3])
+    order = kernels.sequence_order_of(lengths)
+    assert order.dtype == torch.int32 and order.tolist() == [1, 3, 2, 0, 4]  # longest first, stable
