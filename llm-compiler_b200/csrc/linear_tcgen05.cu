@@ -114,11 +114,11 @@ __device__ __forceinline__ void add_bias(const Tcgen05Params& p, int col0, int n
 }
 
 // r(r(x W^T + b) + residual) for 32 columns of one output row.
-__device__ __forceinline__ void add_residual(const Tcgen05Params& p, int row, int col0, int n_end,
-                                             float (&v)[32]) {
+__device__ __forceinline__ void add_residual(const Tcgen05Params& p, int epilogue, int row, int col0,
+                                             int n_end, float (&v)[32]) {
   const bool whole = col0 + 32 <= n_end;
   const int64_t o = static_cast<int64_t>(row) * p.n + col0;
-  if (p.epilogue == B200_EPILOGUE_RESIDUAL) {  // r(r(x W^T + b) + residual)
+  if (epilogue == B200_EPILOGUE_RESIDUAL) {  // r(r(x W^T + b) + residual)
 #pragma unroll
     for (int i = 0; i < 32; i += 2) round_bf16_pair(v[i], v[i + 1]);
     if (whole && (reinterpret_cast<uintptr_t>(p.residual + o) & 15u) == 0) {
@@ -155,12 +155,16 @@ __device__ __forceinline__ void swiglu_of_chunk(float (&v)[32], float (&y)[16]) 
 
 // The bf16 epilogue of 32 accumulator columns of one output row: bias, then SwiGLU (columns
 // 2j / 2j+1 are gate_j / up_j) or the residual, with the reference's bf16 rounding points.
+// EPI >= 0: the epilogue is known at compile time (the decode chain's instantiations carry
+// only their own); -1: taken from the parameters.
+template <int EPI = -1>
 __device__ __forceinline__ void store_chunk(const Tcgen05Params& p, int row, int col0, int n_end,
                                             float (&v)[32]) {
-  const int out_cols = p.epilogue == B200_EPILOGUE_SWIGLU ? p.n / 2 : p.n;
+  const int epilogue = EPI >= 0 ? EPI : p.epilogue;
+  const int out_cols = epilogue == B200_EPILOGUE_SWIGLU ? p.n / 2 : p.n;
   const bool whole = col0 + 32 <= n_end;  // all 32 columns exist: 16-byte accesses where aligned
   add_bias(p, col0, n_end, v);
-  if (p.epilogue == B200_EPILOGUE_SWIGLU) {
+  if (epilogue == B200_EPILOGUE_SWIGLU) {
     // columns 2j / 2j+1 are gate_j / up_j
     __nv_bfloat16* dst = p.out + static_cast<int64_t>(row) * out_cols + col0 / 2;
     float y[16];
@@ -179,7 +183,7 @@ __device__ __forceinline__ void store_chunk(const Tcgen05Params& p, int row, int
     return;
   }
   const int64_t o = static_cast<int64_t>(row) * p.n + col0;
-  add_residual(p, row, col0, n_end, v);
+  add_residual(p, epilogue, row, col0, n_end, v);
   __nv_bfloat16* dst = p.out + o;
   if (whole && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
@@ -197,10 +201,22 @@ __device__ __forceinline__ void store_chunk(const Tcgen05Params& p, int row, int
 // A_ROWS: rows of the x box a stage holds. With at most 64 activation rows (decode) the box
 // is 64 rows and the MMA, which always spans 128 rows, reads on into the W tile behind it:
 // accumulator lanes 64..127 then hold junk that the epilogue never touches (rows >= M).
-template <int BN, int STAGES, int A_ROWS>
+// FORM: which of the four jobs this instantiation does (a compile-time choice: a decode-size
+// launch pays for every instruction it carries, in registers and in first-touch instruction
+// fetches; two extra branches in the producer / MMA loops once cost 7 % of a decode step).
+constexpr int kFormPlain = 0;    // bias / residual / SwiGLU epilogue
+constexpr int kFormPartial = 1;  // fp32 split-K partials (+ row sums of squares of x)
+constexpr int kFormCluster = 2;  // split-K over a thread-block cluster, residual inside
+constexpr int kFormNorm = 3;     // folded RMSNorm, bias, no other epilogue (an LM head)
+constexpr int kFormNormSwiglu = 4;  // folded RMSNorm + SwiGLU (a gate|up projection)
+
+template <int BN, int STAGES, int A_ROWS, int FORM>
 __global__ void __launch_bounds__(kThreads)
 linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap a_map,
                       const __grid_constant__ CUtensorMap b_map) {
+  constexpr bool kCluster = FORM == kFormCluster, kPartial = FORM == kFormPartial;
+  constexpr bool kNorm = FORM == kFormNorm || FORM == kFormNormSwiglu;
+  constexpr int kEpilogue = FORM == kFormNormSwiglu ? B200_EPILOGUE_SWIGLU : FORM == kFormNorm ? B200_EPILOGUE_NONE : -1;
   constexpr int kABytes = A_ROWS * 128;
   // TMEM is allocated in powers of two of at least 32 columns
   constexpr int kTmemColumns = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : BN <= 256 ? 256 : 512;
@@ -230,8 +246,8 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   const int nkb = max(0, min(kb_first + kb_per, kb_total) - kb_first);
   const uint32_t smem_base = smem_u32(smem);
   // warps 2 and 3 square the rows of x as they pass through shared memory
-  const bool squares = A_ROWS <= 128 && ((p.norm_input != nullptr && p.norm_squares == nullptr) ||
-                                        (p.row_squares != nullptr && tile_n == 0));
+  const bool squares = (kNorm && p.norm_squares == nullptr) ||
+                       (kPartial && p.row_squares != nullptr && tile_n == 0);
 
   if (threadIdx.x == 0) {
     failed = 0;
@@ -259,9 +275,9 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   // Cluster split-K: the other CTAs of the cluster will signal reduce_bar; none may do so
   // before it is initialised, hence one cluster barrier here, in the prologue that overlaps
   // the predecessor kernel. Then this CTA announces the bytes it is going to receive.
-  const int reduce_owned = p.epilogue == kEpilogueClusterResidual
+  const int reduce_owned = kCluster
       ? (A_ROWS * (bn / 4) + p.splits - 1) / p.splits : 0;  // 16-byte units this CTA sums
-  if (p.epilogue == kEpilogueClusterResidual) {
+  if (kCluster) {
     cluster_sync();
     if (threadIdx.x == 0)
       mbarrier_arrive_expect_tx(smem_u32(&reduce_bar), static_cast<uint32_t>(p.splits * reduce_owned * 16));
@@ -307,7 +323,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
     // through mbarriers, and stay out of the way of the kernels still running on the SM.
     grid_dependency_wait();
   }
-  if (warp >= 2 && squares) {
+  if ((kNorm || kPartial) && warp >= 2 && squares) {
     // Folded RMSNorm (A_ROWS == 64): warps 2 and 3 have nothing else to do until the accumulator
     // is complete. Every k-block's 64 x 64 box of x passes through shared memory for the tensor
     // core anyway; thread t of the two warps squares row t of each box as it lands (128 bytes,
@@ -350,13 +366,13 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
 #pragma unroll
     for (int h = 0; h < kRowsEach; ++h) {
       const int row = r + 64 * h;
-      if (p.norm_input != nullptr)
+      if (kNorm)
         row_scale[row] = rsqrtf(ss[h] / static_cast<float>(p.k) + p.norm_eps);
       else if (tile_m * kBM + row < p.m)
         p.row_squares[static_cast<int64_t>(split) * p.m + tile_m * kBM + row] = fine ? ss[h] : 0.0f;
     }
   }
-  if (warp >= 2 && p.norm_squares != nullptr) {
+  if (kNorm && warp >= 2 && p.norm_squares != nullptr) {
     // Folded RMSNorm, row sums of squares left by the kernel that produced x: thread t of warps
     // 2 and 3 adds the slices of row t (and of row t + 64 of a 128-row tile) in slice order (L2
     // reads, sixteen in flight) while the main loop runs. The slices are that kernel's output:
@@ -410,9 +426,9 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
   bool ok = mbarrier_wait_bounded(smem_u32(&accum_bar), 0, p.wait_limit);
   trace.mark_middle();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  if (p.norm_input != nullptr) __syncthreads();  // the row scales of warps 2 and 3
+  if (kNorm) __syncthreads();  // the row scales of warps 2 and 3
   ok = ok && failed == 0;
-  if (p.epilogue == kEpilogueClusterResidual) {
+  if constexpr (kCluster) {
     // ---- split-K over a thread-block cluster: reduce through distributed shared memory ----
     // The tile's 4-column units (A_ROWS x bn / 4 of them) are dealt round-robin to the CTAs of
     // the cluster (one per K slice): unit i belongs to CTA i % splits, as its local unit
@@ -536,7 +552,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
     if (!ok && threadIdx.x == 0 && p.status != nullptr) atomicOr(p.status, B200_STATUS_WAIT_TIMEOUT);
   } else if (ok) {
     const int row = tile_m * kBM + warp * 32 + lane;
-    const float scale = p.norm_input != nullptr ? row_scale[(warp * 32 + lane) % kBM] : 1.0f;
+    const float scale = kNorm ? row_scale[(warp * 32 + lane) % kBM] : 1.0f;
     const int n_end = min(p.n, (tile_n + 1) * bn);  // columns of this tile
 #pragma unroll 1
     for (int c0 = 0; c0 < bn; c0 += 32) {
@@ -549,11 +565,11 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = 0.0f;
       }
-      if (p.norm_input != nullptr) {
+      if (kNorm) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] *= scale;
       }
-      if (p.epilogue == kEpiloguePartial) {
+      if (kPartial) {
         float* dst = p.partials + (static_cast<int64_t>(split) * p.m + row) * p.n + col0;
         if (col0 + 32 <= n_end && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
 #pragma unroll
@@ -567,7 +583,7 @@ linear_tcgen05_kernel(const Tcgen05Params p, const __grid_constant__ CUtensorMap
         }
         continue;
       }
-      store_chunk(p, row, col0, n_end, v);
+      store_chunk<kEpilogue>(p, row, col0, n_end, v);
     }
   } else if (threadIdx.x == 0 && p.status != nullptr) {
     atomicOr(p.status, B200_STATUS_WAIT_TIMEOUT);
@@ -745,7 +761,7 @@ linear_tcgen05_persistent_kernel(const Tcgen05Params p, const __grid_constant__ 
               tmem_load_32x32(t_addr + c0 + half * 32, v);
               if (row < p.m) {
                 add_bias(p, col0 + half * 32, n_end, v);
-                add_residual(p, row, col0 + half * 32, n_end, v);
+                add_residual(p, p.epilogue, row, col0 + half * 32, n_end, v);
               }
 #pragma unroll
               for (int i = 0; i < 4; ++i)
@@ -829,9 +845,16 @@ bool small_rings() {
   return value;
 }
 
-template <int BN, int STAGES, int A_ROWS>
+template <int BN, int STAGES, int A_ROWS, int FORM>
 int launch(const Tcgen05Params& p, const CUtensorMap& a_map, const CUtensorMap& b_map,
            cudaStream_t stream) {
+  // the instantiation must be the one the parameters describe
+  if ((FORM == kFormCluster) != (p.epilogue == kEpilogueClusterResidual) ||
+      (FORM == kFormPartial) != (p.epilogue == kEpiloguePartial) ||
+      (FORM == kFormNorm || FORM == kFormNormSwiglu) != (p.norm_input != nullptr) ||
+      (FORM == kFormNormSwiglu && p.epilogue != B200_EPILOGUE_SWIGLU) ||
+      (FORM == kFormNorm && p.epilogue != B200_EPILOGUE_NONE))
+    return B200_ERR_BAD_ARGUMENT;
   // slack: the last stage's 64-row x box is followed by up to 8 KB that the 128-row MMA reads past
   constexpr int ring = STAGES * (A_ROWS + BN) * 128 + 9216;
   static_assert(ring <= 227 * 1024, "stage ring exceeds shared memory");
@@ -844,7 +867,7 @@ int launch(const Tcgen05Params& p, const CUtensorMap& a_map, const CUtensorMap& 
     smem += 2 * p.splits * owned * 16;  // a send and a receive region
     if (smem > 227 * 1024) return B200_ERR_UNSUPPORTED;
   }
-  auto kernel = linear_tcgen05_kernel<BN, STAGES, A_ROWS>;
+  auto kernel = linear_tcgen05_kernel<BN, STAGES, A_ROWS, FORM>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return B200_ERR_LAUNCH;
   const int64_t tiles_n = ceil_div(p.n, p.bn), tiles_m = ceil_div(p.m, kBM);
@@ -872,6 +895,15 @@ int launch(const Tcgen05Params& p, const CUtensorMap& a_map, const CUtensorMap& 
   return launch_status();
 }
 
+// serve.linear proper: with or without the folded RMSNorm
+template <int BN, int STAGES, int A_ROWS>
+int launch_linear(const Tcgen05Params& p, const CUtensorMap& a_map, const CUtensorMap& b_map,
+                  cudaStream_t stream) {
+  if (p.norm_input == nullptr) return launch<BN, STAGES, A_ROWS, kFormPlain>(p, a_map, b_map, stream);
+  return p.epilogue == B200_EPILOGUE_SWIGLU ? launch<BN, STAGES, A_ROWS, kFormNormSwiglu>(p, a_map, b_map, stream)
+                                            : launch<BN, STAGES, A_ROWS, kFormNorm>(p, a_map, b_map, stream);
+}
+
 // How many clusters of `splits` CTAs of this kernel configuration the GPU holds at once (0 if the
 // configuration cannot run). A cluster needs all its CTAs on one GPC, so the answer is not
 // simply SMs / splits: 28 clusters of 5 one-CTA-per-SM blocks, for instance, do not fit.
@@ -880,7 +912,7 @@ int resident_clusters(int bn, int splits) {
   const int owned = (A_ROWS * bn / 4 + splits - 1) / splits;
   const int smem = STAGES * (A_ROWS + BN) * 128 + 9216 + 2 * splits * owned * 16;
   if (owned > 4 * kThreads || smem > 227 * 1024) return 0;
-  auto kernel = linear_tcgen05_kernel<BN, STAGES, A_ROWS>;
+  auto kernel = linear_tcgen05_kernel<BN, STAGES, A_ROWS, kFormCluster>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
     (void)cudaGetLastError();
     return 0;
@@ -1129,21 +1161,21 @@ int linear_tcgen05(const void* input, const void* weight, const void* bias, cons
     p.norm_slices = norm_slices;
   }
   if (m <= 64) {
-    if (bn == 192 && ceil_div(n, 192) >= 4 * kNumSMs) return launch<192, 3, 64>(p, a_map, b_map, stream);
-    if (bn > 128) return launch<256, 5, 64>(p, a_map, b_map, stream);
+    if (bn == 192 && ceil_div(n, 192) >= 4 * kNumSMs) return launch_linear<192, 3, 64>(p, a_map, b_map, stream);
+    if (bn > 128) return launch_linear<256, 5, 64>(p, a_map, b_map, stream);
     if (bn > 64)
-      return small_rings() && fold_norm ? launch<128, 4, 64>(p, a_map, b_map, stream)
-                                        : launch<128, 8, 64>(p, a_map, b_map, stream);
+      return small_rings() && fold_norm ? launch_linear<128, 4, 64>(p, a_map, b_map, stream)
+                                        : launch_linear<128, 8, 64>(p, a_map, b_map, stream);
     // narrow tiles of a folded-norm projection: short rings, three CTAs per SM
     // (4-stage rings measured best: 3 stages -4 %, 6 stages -2 %, 12 stages -17 % of the decode step)
     if (small_rings() && fold_norm)
-      return bn > 32 ? launch<64, 4, 64>(p, a_map, b_map, stream) : launch<32, 4, 64>(p, a_map, b_map, stream);
-    return launch<64, 12, 64>(p, a_map, b_map, stream);
+      return bn > 32 ? launch_linear<64, 4, 64>(p, a_map, b_map, stream) : launch_linear<32, 4, 64>(p, a_map, b_map, stream);
+    return launch_linear<64, 12, 64>(p, a_map, b_map, stream);
   }
   if (persistent) return launch_persistent(p, a_map, b_map, stream);
-  if (bn == 256) return launch<256, 4, 128>(p, a_map, b_map, stream);
-  if (bn == 128) return launch<128, 3, 128>(p, a_map, b_map, stream);
-  return launch<64, 4, 128>(p, a_map, b_map, stream);
+  if (bn == 256) return launch_linear<256, 4, 128>(p, a_map, b_map, stream);
+  if (bn == 128) return launch_linear<128, 3, 128>(p, a_map, b_map, stream);
+  return launch_linear<64, 4, 128>(p, a_map, b_map, stream);
 }
 
 int linear_partial_splits(int64_t m, int64_t k, int64_t n) { return plan_partial(m, k, n).splits; }
@@ -1180,15 +1212,15 @@ int linear_partial_tcgen05(const void* input, const void* weight, float* partial
     // loads in flight per SM, twice what the 96 KB rings of the short slices hold.
     const bool long_slice = ceil_div(ceil_div(k, kBK), splits) >= 24;
     if (plan.bn == 32)
-      return small_rings() && ceil_div(ceil_div(k, kBK), splits) <= 4 ? launch<32, 4, 64>(p, a_map, b_map, stream)
-                                                                      : launch<32, 8, 64>(p, a_map, b_map, stream);
+      return small_rings() && ceil_div(ceil_div(k, kBK), splits) <= 4 ? launch<32, 4, 64, kFormPartial>(p, a_map, b_map, stream)
+                                                                      : launch<32, 8, 64, kFormPartial>(p, a_map, b_map, stream);
     if (plan.bn == 64)
-      return long_slice ? launch<64, 12, 64>(p, a_map, b_map, stream) : launch<64, 6, 64>(p, a_map, b_map, stream);
-    return long_slice ? launch<128, 8, 64>(p, a_map, b_map, stream) : launch<128, 4, 64>(p, a_map, b_map, stream);
+      return long_slice ? launch<64, 12, 64, kFormPartial>(p, a_map, b_map, stream) : launch<64, 6, 64, kFormPartial>(p, a_map, b_map, stream);
+    return long_slice ? launch<128, 8, 64, kFormPartial>(p, a_map, b_map, stream) : launch<128, 4, 64, kFormPartial>(p, a_map, b_map, stream);
   }
-  if (plan.bn == 32) return launch<32, 6, 128>(p, a_map, b_map, stream);
-  if (plan.bn == 64) return launch<64, 4, 128>(p, a_map, b_map, stream);
-  return launch<128, 3, 128>(p, a_map, b_map, stream);
+  if (plan.bn == 32) return launch<32, 6, 128, kFormPartial>(p, a_map, b_map, stream);
+  if (plan.bn == 64) return launch<64, 4, 128, kFormPartial>(p, a_map, b_map, stream);
+  return launch<128, 3, 128, kFormPartial>(p, a_map, b_map, stream);
 }
 
 int linear_splitk_residual_tcgen05(const void* input, const void* weight, const void* residual,
@@ -1223,13 +1255,13 @@ int linear_splitk_residual_tcgen05(const void* input, const void* weight, const 
   p.drop_loads = drop_loads();
   // (rings short enough to leave room for the send and receive regions of the reduction)
   switch (cluster_config(a_rows, plan.bn, ceil_div(ceil_div(k, kBK), plan.splits))) {
-    case ClusterConfig::k32x3: return launch<32, 3, 64>(p, a_map, b_map, stream);
-    case ClusterConfig::k32x8: return launch<32, 8, 64>(p, a_map, b_map, stream);
-    case ClusterConfig::k64x4: return launch<64, 4, 64>(p, a_map, b_map, stream);
-    case ClusterConfig::k64x6: return launch<64, 6, 64>(p, a_map, b_map, stream);
-    case ClusterConfig::k128x4: return launch<128, 4, 64>(p, a_map, b_map, stream);
-    case ClusterConfig::k32x6r128: return launch<32, 6, 128>(p, a_map, b_map, stream);
-    case ClusterConfig::k64x4r128: return launch<64, 4, 128>(p, a_map, b_map, stream);
+    case ClusterConfig::k32x3: return launch<32, 3, 64, kFormCluster>(p, a_map, b_map, stream);
+    case ClusterConfig::k32x8: return launch<32, 8, 64, kFormCluster>(p, a_map, b_map, stream);
+    case ClusterConfig::k64x4: return launch<64, 4, 64, kFormCluster>(p, a_map, b_map, stream);
+    case ClusterConfig::k64x6: return launch<64, 6, 64, kFormCluster>(p, a_map, b_map, stream);
+    case ClusterConfig::k128x4: return launch<128, 4, 64, kFormCluster>(p, a_map, b_map, stream);
+    case ClusterConfig::k32x6r128: return launch<32, 6, 128, kFormCluster>(p, a_map, b_map, stream);
+    case ClusterConfig::k64x4r128: return launch<64, 4, 128, kFormCluster>(p, a_map, b_map, stream);
   }
   return B200_ERR_UNSUPPORTED;
 }
