@@ -477,7 +477,7 @@ __device__ __forceinline__ bool stream_segment(const DecodeParams& p, const CUte
 // CLUSTER: the splits of one (sequence, head block) form a thread-block cluster (gridDim.x ==
 // cluster size <= 8) and are combined through distributed shared memory by the cluster's
 // first CTA; otherwise through the fp32 scratch in global memory by whichever CTA arrives last.
-template <int D, int TOK, bool WIDE, bool FAST, bool TMA, bool CLUSTER, int WARPS>
+template <int D, int TOK, bool WIDE, bool FAST, bool TMA, bool CLUSTER, int WARPS, bool FUSED>
 __global__ void __launch_bounds__(WARPS * 32)
 decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap kmap,
                         const __grid_constant__ CUtensorMap vmap) {
@@ -521,7 +521,7 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
   const int n_tokens = static_cast<int>(len);
   const int start = split * p.split_tokens;
   if (!CLUSTER && start >= n_tokens && split > 0) return;  // (a cluster member must stay for the barriers)
-  const bool fused = p.qkv_partials != nullptr;
+  constexpr bool fused = FUSED;  // (the launcher picks the instantiation by p.qkv_partials)
   // fused: the newest row is not streamed from the buffer (its owner is writing it right now)
   const int streamed = fused ? max(n_tokens - 1, 0) : n_tokens;
   const int end = max(start, min(start + p.split_tokens, streamed));
@@ -616,7 +616,7 @@ decode_attention_kernel(const DecodeParams p, const __grid_constant__ CUtensorMa
   }
   int it_base = 0;
   const int stable_end = p.early_kv ? max(n_tokens - 1, 0) : -1;
-  if (fused)
+  if constexpr (FUSED)
     stream_segment<D, TOK, WIDE, FAST, TMA, decltype(prepare_fused), WARPS>(
         p, kmap, vmap, smem, bar0, b, kvh, g0, rows, start, end, it_base, stable_end, &trace, q_stage,
         static_cast<int64_t>(D), prepare_fused);
@@ -1130,15 +1130,15 @@ GridPlan plan_grid(int64_t splits, int64_t split_tokens, int64_t batch, int64_t 
   return plan;
 }
 
-template <int D, bool WIDE, bool FAST, bool TMA, int WARPS>
+template <int D, bool WIDE, bool FAST, bool TMA, int WARPS, bool FUSED>
 int launch_grid(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap,
                 bool cluster, cudaStream_t stream) {
   constexpr int TOK = tokens_per_step<D>();
   constexpr int smem = WARPS * kStages * 2 * TOK * D * 2;
   const int row_blocks = (p.groups + 15) / 16;
   dim3 grid(p.num_splits, p.kv_heads * row_blocks, p.batch);
-  auto kernel = cluster ? decode_attention_kernel<D, TOK, WIDE, FAST, TMA, true, WARPS>
-                        : decode_attention_kernel<D, TOK, WIDE, FAST, TMA, false, WARPS>;
+  auto kernel = cluster ? decode_attention_kernel<D, TOK, WIDE, FAST, TMA, true, WARPS, FUSED>
+                        : decode_attention_kernel<D, TOK, WIDE, FAST, TMA, false, WARPS, FUSED>;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
     return B200_ERR_LAUNCH;
   if (launch_chained_cluster(kernel, grid, dim3(WARPS * 32), smem, stream,
@@ -1148,7 +1148,7 @@ int launch_grid(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMa
   return cudaGetLastError() == cudaSuccess ? B200_OK : B200_ERR_LAUNCH;
 }
 
-template <int D, bool WIDE, bool FAST, bool TMA>
+template <int D, bool WIDE, bool FAST, bool TMA, bool FUSED = false>
 int launch_variant(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap,
                    cudaStream_t stream) {
   const int row_blocks = (p.groups + 15) / 16;
@@ -1158,8 +1158,9 @@ int launch_variant(const DecodeParams& p, const CUtensorMap& kmap, const CUtenso
   q.split_tokens = plan.split_tokens;
   if (q.ws_o != nullptr)  // the scratch was sized for at least this many splits
     q.ws_ml = q.ws_o + static_cast<int64_t>(p.batch) * p.q_heads * plan.splits * D;
-  if (plan.warps == kWarps) return launch_grid<D, WIDE, FAST, TMA, kWarps>(q, kmap, vmap, plan.cluster, stream);
-  return launch_grid<D, WIDE, FAST, TMA, 2 * kWarps>(q, kmap, vmap, plan.cluster, stream);
+  if (plan.warps == kWarps)
+    return launch_grid<D, WIDE, FAST, TMA, kWarps, FUSED>(q, kmap, vmap, plan.cluster, stream);
+  return launch_grid<D, WIDE, FAST, TMA, 2 * kWarps, FUSED>(q, kmap, vmap, plan.cluster, stream);
 }
 
 template <int D, bool WIDE, bool FAST, bool TMA>
@@ -1191,6 +1192,15 @@ int launch_bf16(const DecodeParams& p, cudaStream_t stream, int flat_grid = 0) {
               : make_kv_tensor_map(&kmap, p.kbuf, p.batch, p.capacity, p.kv_heads, D, tokens_per_step<D>()) &&
                     make_kv_tensor_map(&vmap, p.vbuf, p.batch, p.capacity, p.kv_heads, D, tokens_per_step<D>());
   int code;
+  if (p.qkv_partials != nullptr) {
+    // the fused form (q|k|v reduction, RoPE and KV store in front of the streaming) is its own
+    // instantiation, so that neither form carries the other's code; it is always the fast one
+    if (!fast || flat_grid > 0) return B200_ERR_UNSUPPORTED;
+    if (tma) code = wide ? launch_variant<D, true, true, true, true>(p, kmap, vmap, stream)
+                         : launch_variant<D, false, true, true, true>(p, kmap, vmap, stream);
+    else code = wide ? launch_variant<D, true, true, false, true>(p, kmap, vmap, stream)
+                     : launch_variant<D, false, true, false, true>(p, kmap, vmap, stream);
+  } else {
 #define B200_DISPATCH(W, F, T)                                                        \
   code = flat_grid > 0 ? launch_flat_variant<D, W, F, T>(p, kmap, vmap, flat_grid, stream) \
                        : launch_variant<D, W, F, T>(p, kmap, vmap, stream)
@@ -1202,6 +1212,7 @@ int launch_bf16(const DecodeParams& p, cudaStream_t stream, int flat_grid = 0) {
     else { if (fast) B200_DISPATCH(false, true, false); else B200_DISPATCH(false, false, false); }
   }
 #undef B200_DISPATCH
+  }
   if (code != B200_OK) return code;
   const GridPlan plan = plan_grid(p.num_splits, p.split_tokens, p.batch,
                                   p.kv_heads * ((p.groups + 15) / 16));
