@@ -32,6 +32,8 @@ extern "C" {
 /* element types */
 #define B200_F32 0
 #define B200_BF16 1
+#define B200_F16 2 /* generic (non-tensor-core) kernels only; the reference's kernels accept it:
+                      backends/triton_linear.py:100-105 */
 
 /* numerical modes: lowering.py:24-37 (_NUMERICAL_LOWERINGS) */
 #define B200_MODE_FAST 0

@@ -15,7 +15,7 @@ PACKAGE_DIR = Path(__file__).resolve().parent
 # B200_LIBRARY_PATH: another build of the same library (for instance the -DB200_TRACE one)
 LIBRARY_PATH = Path(os.environ.get("B200_LIBRARY_PATH", PACKAGE_DIR / "libb200serve.so"))
 
-F32, BF16 = 0, 1
+F32, BF16, F16 = 0, 1, 2
 MODE_FAST, MODE_PYTORCH_COMPATIBLE = 0, 1
 EPILOGUE_NONE, EPILOGUE_RESIDUAL, EPILOGUE_SWIGLU = 0, 1, 2
 
@@ -42,7 +42,7 @@ class B200LibraryError(RuntimeError):
 _I64P = POINTER(c_int64)
 
 # What b200_abi_version() of a matching library returns (bumped with every signature change).
-ABI_VERSION = 103
+ABI_VERSION = 104
 
 # name -> (restype, argtypes); mirrors include/b200_serve.h one to one
 SIGNATURES = {

@@ -26,7 +26,7 @@ extern "C" int64_t b200_debug_set_waits(int64_t poll_limit, int drop_loads) {
   return b200::g_wait_limit.exchange(static_cast<unsigned>(poll_limit), std::memory_order_relaxed);
 }
 
-extern "C" int b200_abi_version(void) { return 103; }
+extern "C" int b200_abi_version(void) { return 104; }
 
 extern "C" int b200_set_launch_mode(int flags) {
   if ((flags & ~(B200_LAUNCH_PROGRAMMATIC | B200_LAUNCH_CONSTANT_WEIGHTS |

@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -266,6 +267,32 @@ struct Elem<__nv_bfloat16> {
   __device__ static float round(float v) { return round_bf16(v); }
   __device__ static void round_pair(float& a, float& b) { round_bf16_pair(a, b); }  // one conversion
 };
+template <>
+struct Elem<__half> {  // fp16 tensors run on the generic (non-tensor-core) kernels only
+  static constexpr int kPerVec = 8;
+  __device__ static float load(const __half* p) { return __half2float(*p); }
+  __device__ static void store(__half* p, float v) { *p = __float2half_rn(v); }
+  __device__ static float round(float v) { return __half2float(__float2half_rn(v)); }
+  __device__ static void round_pair(float& a, float& b) {
+    const float2 r = __half22float2(__floats2half2_rn(a, b));
+    a = r.x;
+    b = r.y;
+  }
+};
+
+// Calls f(TypeTag<T>{}) with the element type of a dtype code; false for an unknown code.
+template <typename T>
+struct TypeTag { using type = T; };
+template <typename F>
+inline bool with_element_type(int dtype, F&& f) {
+  switch (dtype) {
+    case B200_F32: f(TypeTag<float>{}); return true;
+    case B200_BF16: f(TypeTag<__nv_bfloat16>{}); return true;
+    case B200_F16: f(TypeTag<__half>{}); return true;
+    default: return false;
+  }
+}
+inline bool known_dtype(int dtype) { return dtype == B200_F32 || dtype == B200_BF16 || dtype == B200_F16; }
 
 // 16-byte vector of elements, unpacked to floats and back.
 template <typename T>
@@ -294,6 +321,30 @@ struct Vec16<__nv_bfloat16> {
     t.x = pack_bf16x2(v[0], v[1]); t.y = pack_bf16x2(v[2], v[3]);
     t.z = pack_bf16x2(v[4], v[5]); t.w = pack_bf16x2(v[6], v[7]);
     *reinterpret_cast<uint4*>(p) = t;
+  }
+};
+
+template <>
+struct Vec16<__half> {
+  float v[8];
+  __device__ void load(const __half* p) {
+    const uint4 t = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  }
+  __device__ void store(__half* p) const {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __half2 h = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
   }
 };
 

@@ -105,6 +105,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 __device__ __forceinline__ float load_mask(const void* mask, int dtype, int64_t index) {
   if (dtype == B200_F32) return static_cast<const float*>(mask)[index];
+  if (dtype == B200_F16) return __half2float(static_cast<const __half*>(mask)[index]);
   return __bfloat162float(static_cast<const __nv_bfloat16*>(mask)[index]);
 }
 
@@ -997,17 +998,21 @@ __global__ void decode_merge_kernel(const float* __restrict__ ws_o, const float*
 // ---- fp32 path (CUDA cores, IEEE fp32 dots): small graphs in full precision ----------
 // One CTA per (sequence, q head); thread t walks tokens t, t+blockDim, ... with its own
 // online-softmax state, then the CTA merges. Matches the oracle to fp32 round-off.
-template <int D>
-__global__ void decode_attention_f32_kernel(const float* __restrict__ q,
-                                            const float* __restrict__ kbuf,
-                                            const float* __restrict__ vbuf,
-                                            const int64_t* __restrict__ lengths,
-                                            const void* __restrict__ mask, float* __restrict__ out,
-                                            int q_heads, int kv_heads, int groups, int capacity,
-                                            int mask_len, int64_t q_batch_stride,
-                                            int64_t q_head_stride, int64_t mask_batch_stride,
-                                            int mask_dtype, float scale, int32_t* status) {
-  constexpr int kT = 64;
+// The generic kernel: fp32, fp16, and the head sizes the tensor-core kernels do not take
+// (16, 32, 256). One CTA of 64 threads per (sequence, query head), thread t owning tokens
+// t, t + 64, ...; all arithmetic in fp32 on the CUDA cores, one rounding on the way out (and,
+// in the compatible mode of a 16-bit type, the reference's two roundings of the scores).
+template <int D, typename T>
+__global__ void decode_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ kbuf,
+                                                const T* __restrict__ vbuf,
+                                                const int64_t* __restrict__ lengths,
+                                                const void* __restrict__ mask, T* __restrict__ out,
+                                                int q_heads, int kv_heads, int groups, int capacity,
+                                                int mask_len, int64_t q_batch_stride,
+                                                int64_t q_head_stride, int64_t mask_batch_stride,
+                                                int mask_dtype, float scale, bool compat,
+                                                int32_t* status) {
+  constexpr int kT = D > 128 ? 32 : 64;  // (the merge buffer of 64 threads x 256 columns would not fit)
   const int hq = blockIdx.x;
   const int b = blockIdx.y;
   const int kvh = hq / groups;
@@ -1022,18 +1027,18 @@ __global__ void decode_attention_f32_kernel(const float* __restrict__ q,
   __shared__ float sm[kT], sl[kT];
   __shared__ float so[kT][D + 1];
   for (int d = threadIdx.x; d < D; d += kT)
-    sq[d] = q[b * q_batch_stride + hq * q_head_stride + d];
+    sq[d] = Elem<T>::load(q + b * q_batch_stride + hq * q_head_stride + d);
   __syncthreads();
   float m = -INFINITY, l = 0.0f, acc[D];
 #pragma unroll
   for (int d = 0; d < D; ++d) acc[d] = 0.0f;
   for (int t = threadIdx.x; t < len; t += kT) {
-    const float* krow = kbuf + ((static_cast<int64_t>(b) * capacity + t) * kv_heads + kvh) * D;
-    const float* vrow = vbuf + ((static_cast<int64_t>(b) * capacity + t) * kv_heads + kvh) * D;
+    const T* krow = kbuf + ((static_cast<int64_t>(b) * capacity + t) * kv_heads + kvh) * D;
+    const T* vrow = vbuf + ((static_cast<int64_t>(b) * capacity + t) * kv_heads + kvh) * D;
     float s = 0.0f;
 #pragma unroll
-    for (int d = 0; d < D; ++d) s = fmaf(sq[d], krow[d], s);
-    s *= scale;
+    for (int d = 0; d < D; ++d) s = fmaf(sq[d], Elem<T>::load(krow + d), s);
+    s = compat ? Elem<T>::round(Elem<T>::round(s) * scale) : s * scale;
     if (mask != nullptr) s += load_mask(mask, mask_dtype, b * mask_batch_stride + t);
     const float m_new = fmaxf(m, s);
     const float m_safe = m_new == -INFINITY ? 0.0f : m_new;
@@ -1041,7 +1046,7 @@ __global__ void decode_attention_f32_kernel(const float* __restrict__ q,
     const float pr = expf(s - m_safe);
     l = l * alpha + pr;
 #pragma unroll
-    for (int d = 0; d < D; ++d) acc[d] = acc[d] * alpha + pr * vrow[d];
+    for (int d = 0; d < D; ++d) acc[d] = acc[d] * alpha + pr * Elem<T>::load(vrow + d);
     m = m_new;
   }
   sm[threadIdx.x] = m;
@@ -1058,7 +1063,7 @@ __global__ void decode_attention_f32_kernel(const float* __restrict__ q,
       l_all += sl[t] * wgt;
       o_all += so[t][d] * wgt;
     }
-    out[(static_cast<int64_t>(b) * q_heads + hq) * D + d] = o_all / l_all;
+    Elem<T>::store(out + (static_cast<int64_t>(b) * q_heads + hq) * D + d, o_all / l_all);
   }
 }
 
@@ -1352,32 +1357,38 @@ static int decode_attention_impl(const void* query, const void* key_buffer,
       q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || capacity <= 0 || mask_len <= 0 ||
       mask_len > capacity || q_heads % kv_heads != 0)
     return B200_ERR_BAD_ARGUMENT;
-  if (mask != nullptr && mask_dtype != B200_F32 && mask_dtype != B200_BF16)
+  if (mask != nullptr && !known_dtype(mask_dtype))
     return B200_ERR_UNSUPPORTED;
   if (batch == 0) return B200_OK;
   if (batch > 65535) return B200_ERR_TOO_LARGE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int groups = static_cast<int>(q_heads / kv_heads);
 
-  if (dtype == B200_F32) {
+  if (!known_dtype(dtype)) return B200_ERR_UNSUPPORTED;
+  if (dtype != B200_BF16 || (head_dim != 64 && head_dim != 128)) {
+    if (sequence_order != nullptr) return B200_ERR_UNSUPPORTED;  // (a service order is the tensor-core kernel's)
+    if (head_dim != 16 && head_dim != 32 && head_dim != 64 && head_dim != 128 && head_dim != 256)
+      return B200_ERR_UNSUPPORTED;
     dim3 grid(static_cast<unsigned>(q_heads), static_cast<unsigned>(batch));
-#define B200_LAUNCH_F32(DIM)                                                                   \
-  decode_attention_f32_kernel<DIM><<<grid, 64, 0, s>>>(                                        \
-      static_cast<const float*>(query), static_cast<const float*>(key_buffer),                \
-      static_cast<const float*>(value_buffer), lengths, mask, static_cast<float*>(output),    \
-      static_cast<int>(q_heads), static_cast<int>(kv_heads), groups,                          \
-      static_cast<int>(capacity), static_cast<int>(mask_len), q_batch_stride, q_head_stride,  \
-      mask_batch_stride, mask_dtype, static_cast<float>(scale), status)
-    if (head_dim == 64) B200_LAUNCH_F32(64);
-    else if (head_dim == 16) B200_LAUNCH_F32(16);
-    else if (head_dim == 32) B200_LAUNCH_F32(32);
-    else if (head_dim == 128) B200_LAUNCH_F32(128);
-    else return B200_ERR_UNSUPPORTED;
-#undef B200_LAUNCH_F32
+    const bool compat = mode == B200_MODE_PYTORCH_COMPATIBLE && dtype != B200_F32;
+    with_element_type(dtype, [&](auto tag) {
+      using T = typename decltype(tag)::type;
+      auto run = [&](auto kernel) {
+        kernel<<<grid, head_dim > 128 ? 32 : 64, 0, s>>>(
+            static_cast<const T*>(query), static_cast<const T*>(key_buffer),
+            static_cast<const T*>(value_buffer), lengths, mask, static_cast<T*>(output),
+            static_cast<int>(q_heads), static_cast<int>(kv_heads), groups, static_cast<int>(capacity),
+            static_cast<int>(mask_len), q_batch_stride, q_head_stride, mask_batch_stride, mask_dtype,
+            static_cast<float>(scale), compat, status);
+      };
+      if (head_dim == 16) run(decode_attention_generic_kernel<16, T>);
+      else if (head_dim == 32) run(decode_attention_generic_kernel<32, T>);
+      else if (head_dim == 64) run(decode_attention_generic_kernel<64, T>);
+      else if (head_dim == 128) run(decode_attention_generic_kernel<128, T>);
+      else run(decode_attention_generic_kernel<256, T>);
+    });
     return launch_status();
   }
-  if (dtype != B200_BF16) return B200_ERR_UNSUPPORTED;
-  if (head_dim != 64 && head_dim != 128) return B200_ERR_UNSUPPORTED;
   if (!aligned16(key_buffer) || !aligned16(value_buffer) ||
       (reinterpret_cast<uintptr_t>(query) & 3u) != 0 || q_head_stride % 2 != 0 ||
       q_batch_stride % 2 != 0)
@@ -1492,7 +1503,7 @@ extern "C" int b200_paged_decode_attention(
       q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || num_blocks <= 0 || block_size <= 0 ||
       max_blocks_per_sequence <= 0 || mask_len <= 0 || mask_len > capacity || q_heads % kv_heads != 0)
     return B200_ERR_BAD_ARGUMENT;
-  if (mask != nullptr && mask_dtype != B200_F32 && mask_dtype != B200_BF16) return B200_ERR_UNSUPPORTED;
+  if (mask != nullptr && !known_dtype(mask_dtype)) return B200_ERR_UNSUPPORTED;
   if (head_dim != 64 && head_dim != 128) return B200_ERR_UNSUPPORTED;
   if (block_size % 32 != 0) return B200_ERR_UNSUPPORTED;  // a 32-token copy must stay inside one block
   if (batch == 0) return B200_OK;
@@ -1595,7 +1606,7 @@ extern "C" int b200_decode_attention_static_scratch(
       q_heads <= 0 || kv_heads <= 0 || head_dim <= 0 || capacity <= 0 || mask_len <= 0 ||
       mask_len > capacity || q_heads % kv_heads != 0)
     return B200_ERR_BAD_ARGUMENT;
-  if (mask != nullptr && mask_dtype != B200_F32 && mask_dtype != B200_BF16)
+  if (mask != nullptr && !known_dtype(mask_dtype))
     return B200_ERR_UNSUPPORTED;
   if (dtype != B200_BF16) return B200_ERR_UNSUPPORTED;  // the fp32 kernel needs no scratch
   if (head_dim != 64 && head_dim != 128) return B200_ERR_UNSUPPORTED;

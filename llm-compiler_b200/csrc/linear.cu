@@ -205,18 +205,23 @@ __global__ void __launch_bounds__(WM* WN * 32) linear_bf16_kernel(const LinearPa
   }
 }
 
-// ------------------------------------------------------------------ fp32 ----
-struct LinearParamsF32 {
-  const float* x;
-  const float* w;
-  const float* bias;
-  const float* residual;
-  float* out;
+// ------------------------------------------------------- generic: fp32, fp16 ----
+// fp32 arithmetic on the CUDA cores for the element types the tensor-core kernels do not
+// take; a 16-bit type is rounded where the reference's kernels round theirs (the result,
+// the sum in front of a residual add, gate / up / silu(gate) of a SwiGLU).
+template <typename T>
+struct LinearParamsGeneric {
+  const T* x;
+  const T* w;
+  const T* bias;
+  const T* residual;
+  T* out;
   int64_t x_row_stride;
   int m, k, n, epilogue;
 };
 
-__global__ void __launch_bounds__(256) linear_f32_kernel(const LinearParamsF32 p) {
+template <typename T>
+__global__ void __launch_bounds__(256) linear_generic_kernel(const LinearParamsGeneric<T> p) {
   constexpr int BM = 64, BN = 64, BKF = 16;
   __shared__ float As[BKF][BM + 1];
   __shared__ float Bs[BKF][BN + 1];
@@ -231,9 +236,9 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(const LinearParamsF32 p
     for (int id = threadIdx.x; id < BM * BKF; id += 256) {
       const int r = id / BKF, c = id % BKF;
       const int m = m_base + r, kk = k0 + c;
-      As[c][r] = (m < p.m && kk < p.k) ? p.x[static_cast<int64_t>(m) * p.x_row_stride + kk] : 0.0f;
+      As[c][r] = (m < p.m && kk < p.k) ? Elem<T>::load(p.x + static_cast<int64_t>(m) * p.x_row_stride + kk) : 0.0f;
       const int n = n_base + r;
-      Bs[c][r] = (n < p.n && kk < p.k) ? p.w[static_cast<int64_t>(n) * p.k + kk] : 0.0f;
+      Bs[c][r] = (n < p.n && kk < p.k) ? Elem<T>::load(p.w + static_cast<int64_t>(n) * p.k + kk) : 0.0f;
     }
     __syncthreads();
 #pragma unroll
@@ -259,19 +264,21 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(const LinearParamsF32 p
       const int n = n_base + tx * 4 + j;
       if (n >= p.n) continue;
       float v = acc[i][j];
-      if (p.bias != nullptr) v += p.bias[n];
+      if (p.bias != nullptr) v += Elem<T>::load(p.bias + n);
       if (p.epilogue == B200_EPILOGUE_SWIGLU) {
         // gate in even columns, up in odd columns: pair them inside the thread
         if ((j & 1) == 0) {
           float u = acc[i][j + 1];
-          if (p.bias != nullptr) u += p.bias[n + 1];
-          p.out[static_cast<int64_t>(m) * (p.n / 2) + n / 2] = silu_f32(v) * u;
+          if (p.bias != nullptr) u += Elem<T>::load(p.bias + n + 1);
+          const float gate = Elem<T>::round(silu_f32(Elem<T>::round(v)));
+          Elem<T>::store(p.out + static_cast<int64_t>(m) * (p.n / 2) + n / 2, gate * Elem<T>::round(u));
         }
         continue;
       }
       const int64_t o = static_cast<int64_t>(m) * p.n + n;
-      if (p.epilogue == B200_EPILOGUE_RESIDUAL) v = __fadd_rn(v, p.residual[o]);
-      p.out[o] = v;
+      if (p.epilogue == B200_EPILOGUE_RESIDUAL)
+        v = __fadd_rn(Elem<T>::round(v), Elem<T>::load(p.residual + o));
+      Elem<T>::store(p.out + o, v);
     }
   }
 }
@@ -379,21 +386,24 @@ extern "C" int b200_linear(const void* input, const void* weight, const void* bi
   if (m > INT32_MAX || k > INT32_MAX || n > INT32_MAX) return B200_ERR_TOO_LARGE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 
-  if (dtype == B200_F32) {
-    LinearParamsF32 p;
-    p.x = static_cast<const float*>(input);
-    p.w = static_cast<const float*>(weight);
-    p.bias = static_cast<const float*>(bias);
-    p.residual = static_cast<const float*>(residual);
-    p.out = static_cast<float*>(output);
-    p.x_row_stride = input_row_stride;
-    p.m = static_cast<int>(m);
-    p.k = static_cast<int>(k);
-    p.n = static_cast<int>(n);
-    p.epilogue = epilogue;
+  if (dtype == B200_F32 || dtype == B200_F16) {
     dim3 grid(static_cast<unsigned>(ceil_div(n, 64)), static_cast<unsigned>(ceil_div(m, 64)));
     if (grid.y > 65535) return B200_ERR_TOO_LARGE;
-    linear_f32_kernel<<<grid, 256, 0, s>>>(p);
+    with_element_type(dtype, [&](auto tag) {
+      using T = typename decltype(tag)::type;
+      LinearParamsGeneric<T> p;
+      p.x = static_cast<const T*>(input);
+      p.w = static_cast<const T*>(weight);
+      p.bias = static_cast<const T*>(bias);
+      p.residual = static_cast<const T*>(residual);
+      p.out = static_cast<T*>(output);
+      p.x_row_stride = input_row_stride;
+      p.m = static_cast<int>(m);
+      p.k = static_cast<int>(k);
+      p.n = static_cast<int>(n);
+      p.epilogue = epilogue;
+      linear_generic_kernel<T><<<grid, 256, 0, s>>>(p);
+    });
     return launch_status();
   }
   if (dtype != B200_BF16) return B200_ERR_UNSUPPORTED;

@@ -580,15 +580,13 @@ int b200_kv_store(void* key_buffer, void* value_buffer, const void* key, const v
       head_dim <= 0)
     return B200_ERR_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == B200_BF16)
-    return kv_store_typed<__nv_bfloat16>(key_buffer, value_buffer, key, value, positions, batch,
-                                         capacity, kv_heads, tokens, head_dim, key_strides,
-                                         value_strides, status, s);
-  if (dtype == B200_F32)
-    return kv_store_typed<float>(key_buffer, value_buffer, key, value, positions, batch,
-                                 capacity, kv_heads, tokens, head_dim, key_strides,
-                                 value_strides, status, s);
-  return B200_ERR_UNSUPPORTED;
+  int code = B200_ERR_UNSUPPORTED;
+  with_element_type(dtype, [&](auto tag) {
+    using T = typename decltype(tag)::type;
+    code = kv_store_typed<T>(key_buffer, value_buffer, key, value, positions, batch, capacity,
+                             kv_heads, tokens, head_dim, key_strides, value_strides, status, s);
+  });
+  return code;
 }
 
 int b200_rope(const void* query, const void* key, const void* cosine, const void* sine,
@@ -602,15 +600,13 @@ int b200_rope(const void* query, const void* key, const void* cosine, const void
     return B200_ERR_BAD_ARGUMENT;
   if (head_dim % 2 != 0) return B200_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == B200_BF16)
-    return rope_typed<__nv_bfloat16>(query, key, cosine, sine, query_out, key_out, batch,
-                                     q_heads, kv_heads, tokens, head_dim, query_strides,
-                                     key_strides, cos_strides, sin_strides, s);
-  if (dtype == B200_F32)
-    return rope_typed<float>(query, key, cosine, sine, query_out, key_out, batch, q_heads,
-                             kv_heads, tokens, head_dim, query_strides, key_strides, cos_strides,
-                             sin_strides, s);
-  return B200_ERR_UNSUPPORTED;
+  int code = B200_ERR_UNSUPPORTED;
+  with_element_type(dtype, [&](auto tag) {
+    using T = typename decltype(tag)::type;
+    code = rope_typed<T>(query, key, cosine, sine, query_out, key_out, batch, q_heads, kv_heads,
+                         tokens, head_dim, query_strides, key_strides, cos_strides, sin_strides, s);
+  });
+  return code;
 }
 
 int b200_rope_kv_store(const void* query, const void* key, const void* value, const void* cosine,
@@ -624,7 +620,7 @@ int b200_rope_kv_store(const void* query, const void* key, const void* value, co
       !value_buffer || !positions || batch < 0 || q_heads <= 0 || kv_heads <= 0 ||
       head_dim <= 0 || capacity <= 0)
     return B200_ERR_BAD_ARGUMENT;
-  if (dtype != B200_BF16 && dtype != B200_F32) return B200_ERR_UNSUPPORTED;
+  if (!known_dtype(dtype)) return B200_ERR_UNSUPPORTED;
   const size_t elt = dtype_bytes(dtype);
   const int per = 16 / static_cast<int>(elt);
   if (head_dim % 2 != 0 || (head_dim / 2) % per != 0) return B200_ERR_UNSUPPORTED;
@@ -639,23 +635,15 @@ int b200_rope_kv_store(const void* query, const void* key, const void* value, co
   if (total == 0) return B200_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int grid = grid_for(total);
-  if (dtype == B200_BF16) {
-    using T = __nv_bfloat16;
+  with_element_type(dtype, [&](auto tag) {
+    using T = typename decltype(tag)::type;
     rope_kv_store_kernel<T><<<grid, kThreads, 0, s>>>(
         static_cast<const T*>(query), static_cast<const T*>(key), static_cast<const T*>(value),
         static_cast<const T*>(cosine), static_cast<const T*>(sine), static_cast<T*>(query_out),
         static_cast<T*>(key_buffer), static_cast<T*>(value_buffer), positions, batch, q_heads,
         kv_heads, head_dim, capacity, q_batch_stride, q_head_stride, k_batch_stride,
         k_head_stride, v_batch_stride, v_head_stride, cos_batch_stride, status);
-  } else {
-    using T = float;
-    rope_kv_store_kernel<T><<<grid, kThreads, 0, s>>>(
-        static_cast<const T*>(query), static_cast<const T*>(key), static_cast<const T*>(value),
-        static_cast<const T*>(cosine), static_cast<const T*>(sine), static_cast<T*>(query_out),
-        static_cast<T*>(key_buffer), static_cast<T*>(value_buffer), positions, batch, q_heads,
-        kv_heads, head_dim, capacity, q_batch_stride, q_head_stride, k_batch_stride,
-        k_head_stride, v_batch_stride, v_head_stride, cos_batch_stride, status);
-  }
+  });
   return launch_status();
 }
 
@@ -666,60 +654,47 @@ int b200_rope_table(const int64_t* position_ids, const float* inv_freq, void* co
   if (rows == 0) return B200_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int grid = grid_for(rows * half_dim);
-  if (out_dtype == B200_BF16)
-    rope_table_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(
-        position_ids, inv_freq, static_cast<__nv_bfloat16*>(cosine),
-        static_cast<__nv_bfloat16*>(sine), rows, half_dim);
-  else if (out_dtype == B200_F32)
-    rope_table_kernel<float><<<grid, kThreads, 0, s>>>(
-        position_ids, inv_freq, static_cast<float*>(cosine), static_cast<float*>(sine), rows,
-        half_dim);
-  else
-    return B200_ERR_UNSUPPORTED;
-  return launch_status();
+  const bool known = with_element_type(out_dtype, [&](auto tag) {
+    using T = typename decltype(tag)::type;
+    rope_table_kernel<T><<<grid, kThreads, 0, s>>>(position_ids, inv_freq, static_cast<T*>(cosine),
+                                                   static_cast<T*>(sine), rows, half_dim);
+  });
+  return known ? launch_status() : B200_ERR_UNSUPPORTED;
 }
 
 int b200_embedding(const void* table, const int64_t* ids, void* output, int64_t rows,
                    int64_t hidden, int64_t vocab, int dtype, int32_t* status, void* stream) {
   if (!table || !ids || !output || rows < 0 || hidden <= 0 || vocab <= 0)
     return B200_ERR_BAD_ARGUMENT;
-  if (dtype != B200_BF16 && dtype != B200_F32) return B200_ERR_UNSUPPORTED;
+  if (!known_dtype(dtype)) return B200_ERR_UNSUPPORTED;
   if (rows == 0) return B200_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int per = 16 / static_cast<int>(dtype_bytes(dtype));
   const bool vec = hidden % per == 0 && aligned16(table) && aligned16(output);
   const int grid = grid_for(rows * (vec ? hidden / per : hidden));
-  if (dtype == B200_BF16) {
-    using T = __nv_bfloat16;
+  with_element_type(dtype, [&](auto tag) {
+    using T = typename decltype(tag)::type;
     if (vec)
       embedding_kernel<T, true><<<grid, kThreads, 0, s>>>(
           static_cast<const T*>(table), ids, static_cast<T*>(output), rows, hidden, vocab, status);
     else
       embedding_kernel<T, false><<<grid, kThreads, 0, s>>>(
           static_cast<const T*>(table), ids, static_cast<T*>(output), rows, hidden, vocab, status);
-  } else {
-    using T = float;
-    if (vec)
-      embedding_kernel<T, true><<<grid, kThreads, 0, s>>>(
-          static_cast<const T*>(table), ids, static_cast<T*>(output), rows, hidden, vocab, status);
-    else
-      embedding_kernel<T, false><<<grid, kThreads, 0, s>>>(
-          static_cast<const T*>(table), ids, static_cast<T*>(output), rows, hidden, vocab, status);
-  }
+  });
   return launch_status();
 }
 
 int b200_swiglu(const void* gate, const void* up, void* output, int64_t count, int dtype,
                 void* stream) {
   if (!gate || !up || !output || count < 0) return B200_ERR_BAD_ARGUMENT;
-  if (dtype != B200_BF16 && dtype != B200_F32) return B200_ERR_UNSUPPORTED;
+  if (!known_dtype(dtype)) return B200_ERR_UNSUPPORTED;
   if (count == 0) return B200_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int per = 16 / static_cast<int>(dtype_bytes(dtype));
   const bool vec = count % per == 0 && aligned16(gate) && aligned16(up) && aligned16(output);
   const int grid = grid_for(vec ? count / per : count);
-  if (dtype == B200_BF16) {
-    using T = __nv_bfloat16;
+  with_element_type(dtype, [&](auto tag) {
+    using T = typename decltype(tag)::type;
     if (vec)
       swiglu_kernel<T, true><<<grid, kThreads, 0, s>>>(static_cast<const T*>(gate),
                                                        static_cast<const T*>(up),
@@ -728,30 +703,20 @@ int b200_swiglu(const void* gate, const void* up, void* output, int64_t count, i
       swiglu_kernel<T, false><<<grid, kThreads, 0, s>>>(static_cast<const T*>(gate),
                                                         static_cast<const T*>(up),
                                                         static_cast<T*>(output), count);
-  } else {
-    using T = float;
-    if (vec)
-      swiglu_kernel<T, true><<<grid, kThreads, 0, s>>>(static_cast<const T*>(gate),
-                                                       static_cast<const T*>(up),
-                                                       static_cast<T*>(output), count);
-    else
-      swiglu_kernel<T, false><<<grid, kThreads, 0, s>>>(static_cast<const T*>(gate),
-                                                        static_cast<const T*>(up),
-                                                        static_cast<T*>(output), count);
-  }
+  });
   return launch_status();
 }
 
 int b200_add(const void* a, const void* b, void* output, int64_t count, int dtype, void* stream) {
   if (!a || !b || !output || count < 0) return B200_ERR_BAD_ARGUMENT;
-  if (dtype != B200_BF16 && dtype != B200_F32) return B200_ERR_UNSUPPORTED;
+  if (!known_dtype(dtype)) return B200_ERR_UNSUPPORTED;
   if (count == 0) return B200_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int per = 16 / static_cast<int>(dtype_bytes(dtype));
   const bool vec = count % per == 0 && aligned16(a) && aligned16(b) && aligned16(output);
   const int grid = grid_for(vec ? count / per : count);
-  if (dtype == B200_BF16) {
-    using T = __nv_bfloat16;
+  with_element_type(dtype, [&](auto tag) {
+    using T = typename decltype(tag)::type;
     if (vec)
       add_kernel<T, true><<<grid, kThreads, 0, s>>>(static_cast<const T*>(a),
                                                     static_cast<const T*>(b),
@@ -760,17 +725,7 @@ int b200_add(const void* a, const void* b, void* output, int64_t count, int dtyp
       add_kernel<T, false><<<grid, kThreads, 0, s>>>(static_cast<const T*>(a),
                                                      static_cast<const T*>(b),
                                                      static_cast<T*>(output), count);
-  } else {
-    using T = float;
-    if (vec)
-      add_kernel<T, true><<<grid, kThreads, 0, s>>>(static_cast<const T*>(a),
-                                                    static_cast<const T*>(b),
-                                                    static_cast<T*>(output), count);
-    else
-      add_kernel<T, false><<<grid, kThreads, 0, s>>>(static_cast<const T*>(a),
-                                                     static_cast<const T*>(b),
-                                                     static_cast<T*>(output), count);
-  }
+  });
   return launch_status();
 }
 
@@ -787,25 +742,16 @@ int b200_copy_4d(const void* input, void* output, const int64_t sizes[4],
   if (total == 0) return B200_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int grid = grid_for(total);
-  using BF = __nv_bfloat16;
-  if (in_dtype == B200_BF16 && out_dtype == B200_BF16)
-    copy4d_kernel<BF, BF><<<grid, kThreads, 0, s>>>(static_cast<const BF*>(input),
-                                                    static_cast<BF*>(output), sizes[0], sizes[1],
-                                                    sizes[2], sizes[3], st);
-  else if (in_dtype == B200_F32 && out_dtype == B200_F32)
-    copy4d_kernel<float, float><<<grid, kThreads, 0, s>>>(
-        static_cast<const float*>(input), static_cast<float*>(output), sizes[0], sizes[1],
-        sizes[2], sizes[3], st);
-  else if (in_dtype == B200_F32 && out_dtype == B200_BF16)
-    copy4d_kernel<float, BF><<<grid, kThreads, 0, s>>>(static_cast<const float*>(input),
-                                                       static_cast<BF*>(output), sizes[0],
-                                                       sizes[1], sizes[2], sizes[3], st);
-  else if (in_dtype == B200_BF16 && out_dtype == B200_F32)
-    copy4d_kernel<BF, float><<<grid, kThreads, 0, s>>>(static_cast<const BF*>(input),
-                                                       static_cast<float*>(output), sizes[0],
-                                                       sizes[1], sizes[2], sizes[3], st);
-  else
-    return B200_ERR_UNSUPPORTED;
+  if (!known_dtype(in_dtype) || !known_dtype(out_dtype)) return B200_ERR_UNSUPPORTED;
+  with_element_type(in_dtype, [&](auto in_tag) {
+    using TIn = typename decltype(in_tag)::type;
+    with_element_type(out_dtype, [&](auto out_tag) {
+      using TOut = typename decltype(out_tag)::type;
+      copy4d_kernel<TIn, TOut><<<grid, kThreads, 0, s>>>(static_cast<const TIn*>(input),
+                                                          static_cast<TOut*>(output), sizes[0],
+                                                          sizes[1], sizes[2], sizes[3], st);
+    });
+  });
   return launch_status();
 }
 
@@ -834,7 +780,7 @@ int b200_paged_kv_store(void* key_pool, void* value_pool, const int32_t* block_t
   if (batch == 0 || tokens == 0) return B200_OK;
   const size_t elt = dtype_bytes(dtype);
   const int per = static_cast<int>(16 / elt);
-  if (dtype != B200_BF16 && dtype != B200_F32) return B200_ERR_UNSUPPORTED;
+  if (!known_dtype(dtype)) return B200_ERR_UNSUPPORTED;
   if (head_dim % per != 0 || !aligned16(key_pool) || !aligned16(value_pool) || !aligned16(key) ||
       !aligned16(value))
     return B200_ERR_ALIGNMENT;
@@ -847,16 +793,13 @@ int b200_paged_kv_store(void* key_pool, void* value_pool, const int32_t* block_t
     vs.s[i] = value_strides[i];
   }
   const int64_t total = batch * tokens * heads * (head_dim / per);
-  if (dtype == B200_BF16)
-    paged_kv_store_kernel<__nv_bfloat16><<<grid_for(total), kThreads, 0, s>>>(
-        static_cast<__nv_bfloat16*>(key_pool), static_cast<__nv_bfloat16*>(value_pool), block_table,
-        static_cast<const __nv_bfloat16*>(key), static_cast<const __nv_bfloat16*>(value), positions,
-        batch, heads, tokens, head_dim, block_size, max_blocks_per_sequence, num_blocks, ks, vs, status);
-  else
-    paged_kv_store_kernel<float><<<grid_for(total), kThreads, 0, s>>>(
-        static_cast<float*>(key_pool), static_cast<float*>(value_pool), block_table,
-        static_cast<const float*>(key), static_cast<const float*>(value), positions, batch, heads,
-        tokens, head_dim, block_size, max_blocks_per_sequence, num_blocks, ks, vs, status);
+  with_element_type(dtype, [&](auto tag) {
+    using T = typename decltype(tag)::type;
+    paged_kv_store_kernel<T><<<grid_for(total), kThreads, 0, s>>>(
+        static_cast<T*>(key_pool), static_cast<T*>(value_pool), block_table,
+        static_cast<const T*>(key), static_cast<const T*>(value), positions, batch, heads, tokens,
+        head_dim, block_size, max_blocks_per_sequence, num_blocks, ks, vs, status);
+  });
   return launch_status();
 }
 
@@ -866,36 +809,30 @@ int b200_scale_columns(const void* weight, const void* scale, void* output, int6
   if (rows == 0) return B200_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t total = rows * columns;
-  if (dtype == B200_BF16)
-    scale_columns_kernel<__nv_bfloat16><<<grid_for(total), kThreads, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(weight), static_cast<const __nv_bfloat16*>(scale),
-        static_cast<__nv_bfloat16*>(output), total, columns);
-  else if (dtype == B200_F32)
-    scale_columns_kernel<float><<<grid_for(total), kThreads, 0, s>>>(
-        static_cast<const float*>(weight), static_cast<const float*>(scale),
-        static_cast<float*>(output), total, columns);
-  else
-    return B200_ERR_UNSUPPORTED;
-  return launch_status();
+  const bool known = with_element_type(dtype, [&](auto tag) {
+    using T = typename decltype(tag)::type;
+    scale_columns_kernel<T><<<grid_for(total), kThreads, 0, s>>>(
+        static_cast<const T*>(weight), static_cast<const T*>(scale), static_cast<T*>(output), total,
+        columns);
+  });
+  return known ? launch_status() : B200_ERR_UNSUPPORTED;
 }
 
 int b200_classify_causal_mask(const void* mask, int64_t batch, int64_t tokens,
                               const int64_t strides[4], int dtype, int32_t* flag, void* stream) {
   if (!mask || !strides || !flag || batch <= 0 || tokens <= 0) return B200_ERR_BAD_ARGUMENT;
-  if (dtype != B200_F32 && dtype != B200_BF16) return B200_ERR_UNSUPPORTED;
+  if (!known_dtype(dtype)) return B200_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // a batch-broadcast mask (stride 0) is checked once
   const int64_t distinct = strides[0] == 0 ? 1 : batch;
   const int64_t total = distinct * tokens * tokens;
   const int grid = static_cast<int>(std::min<int64_t>(ceil_div(total, kThreads), 16 * kNumSMs));
   set_flag_kernel<<<1, 1, 0, s>>>(flag);
-  if (dtype == B200_F32)
-    classify_causal_mask_kernel<float><<<grid, kThreads, 0, s>>>(
-        static_cast<const float*>(mask), distinct, tokens, strides[0], strides[2], strides[3], flag);
-  else
-    classify_causal_mask_kernel<__nv_bfloat16><<<grid, kThreads, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(mask), distinct, tokens, strides[0], strides[2],
-        strides[3], flag);
+  with_element_type(dtype, [&](auto tag) {
+    using T = typename decltype(tag)::type;
+    classify_causal_mask_kernel<T><<<grid, kThreads, 0, s>>>(
+        static_cast<const T*>(mask), distinct, tokens, strides[0], strides[2], strides[3], flag);
+  });
   return launch_status();
 }
 
@@ -907,15 +844,12 @@ int b200_argmax(const void* logits, int64_t* ids, int64_t rows, int64_t vocab,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t elt = dtype_bytes(dtype);
   const bool vec = aligned16(logits) && (row_stride * static_cast<int64_t>(elt)) % 16 == 0;
-  if (dtype == B200_BF16)
-    argmax_kernel<__nv_bfloat16><<<static_cast<int>(rows), kArgmaxThreads, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(logits), ids, vocab, row_stride, vec);
-  else if (dtype == B200_F32)
-    argmax_kernel<float><<<static_cast<int>(rows), kArgmaxThreads, 0, s>>>(
-        static_cast<const float*>(logits), ids, vocab, row_stride, vec);
-  else
-    return B200_ERR_UNSUPPORTED;
-  return launch_status();
+  const bool known = with_element_type(dtype, [&](auto tag) {
+    using T = typename decltype(tag)::type;
+    argmax_kernel<T><<<static_cast<int>(rows), kArgmaxThreads, 0, s>>>(
+        static_cast<const T*>(logits), ids, vocab, row_stride, vec);
+  });
+  return known ? launch_status() : B200_ERR_UNSUPPORTED;
 }
 
 }  // extern "C"

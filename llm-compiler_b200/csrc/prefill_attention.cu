@@ -44,6 +44,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 
 __device__ __forceinline__ float load_mask(const void* mask, int dtype, int64_t index) {
   if (dtype == B200_F32) return static_cast<const float*>(mask)[index];
+  if (dtype == B200_F16) return __half2float(static_cast<const __half*>(mask)[index]);
   return __bfloat162float(static_cast<const __nv_bfloat16*>(mask)[index]);
 }
 
@@ -251,37 +252,38 @@ __global__ void __launch_bounds__(kThreads) prefill_attention_kernel(const Prefi
   }
 }
 
-// ---- fp32 path: one CTA per (query token, q head, sequence) ---------------------------
-template <int D>
-__global__ void prefill_attention_f32_kernel(const float* __restrict__ q,
-                                             const float* __restrict__ k,
-                                             const float* __restrict__ v,
-                                             const void* __restrict__ mask,
-                                             float* __restrict__ out, int q_heads, int groups,
-                                             int tokens, int64_t qs0, int64_t qs1, int64_t qs2,
-                                             int64_t ks0, int64_t ks1, int64_t ks2, int64_t vs0,
-                                             int64_t vs1, int64_t vs2, int64_t ms0, int64_t ms2,
-                                             int64_t ms3, int mask_dtype, int causal,
-                                             float scale) {
-  constexpr int kT = 64;
+// ---- generic path (fp32, fp16, head sizes 16 / 32 / 256): one CTA per (query token, q head,
+// sequence), fp32 arithmetic on the CUDA cores, one rounding on the way out (and, in the
+// compatible mode of a 16-bit type, the reference's two roundings of the scores) ----------
+template <int D, typename T>
+__global__ void prefill_attention_generic_kernel(const T* __restrict__ q, const T* __restrict__ k,
+                                                 const T* __restrict__ v,
+                                                 const void* __restrict__ mask, T* __restrict__ out,
+                                                 int q_heads, int groups, int tokens, int64_t qs0,
+                                                 int64_t qs1, int64_t qs2, int64_t ks0, int64_t ks1,
+                                                 int64_t ks2, int64_t vs0, int64_t vs1, int64_t vs2,
+                                                 int64_t ms0, int64_t ms2, int64_t ms3,
+                                                 int mask_dtype, int causal, float scale,
+                                                 bool compat) {
+  constexpr int kT = D > 128 ? 32 : 64;  // (the merge buffer of 64 threads x 256 columns would not fit)
   const int qt = blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
   const int kvh = hq / groups;
   __shared__ float sq[D];
   __shared__ float sm[kT], sl[kT];
   __shared__ float so[kT][D + 1];
-  for (int d = threadIdx.x; d < D; d += kT) sq[d] = q[b * qs0 + hq * qs1 + qt * qs2 + d];
+  for (int d = threadIdx.x; d < D; d += kT) sq[d] = Elem<T>::load(q + b * qs0 + hq * qs1 + qt * qs2 + d);
   __syncthreads();
   float m = -INFINITY, l = 0.0f, acc[D];
 #pragma unroll
   for (int d = 0; d < D; ++d) acc[d] = 0.0f;
   const int key_end = causal ? qt + 1 : tokens;
   for (int t = threadIdx.x; t < key_end; t += kT) {
-    const float* krow = k + b * ks0 + kvh * ks1 + t * ks2;
-    const float* vrow = v + b * vs0 + kvh * vs1 + t * vs2;
+    const T* krow = k + b * ks0 + kvh * ks1 + t * ks2;
+    const T* vrow = v + b * vs0 + kvh * vs1 + t * vs2;
     float s = 0.0f;
 #pragma unroll
-    for (int d = 0; d < D; ++d) s = fmaf(sq[d], krow[d], s);
-    s *= scale;
+    for (int d = 0; d < D; ++d) s = fmaf(sq[d], Elem<T>::load(krow + d), s);
+    s = compat ? Elem<T>::round(Elem<T>::round(s) * scale) : s * scale;
     if (mask != nullptr)
       s += load_mask(mask, mask_dtype, b * ms0 + static_cast<int64_t>(qt) * ms2 + t * ms3);
     const float m_new = fmaxf(m, s);
@@ -290,7 +292,7 @@ __global__ void prefill_attention_f32_kernel(const float* __restrict__ q,
     const float pr = expf(s - m_safe);
     l = l * alpha + pr;
 #pragma unroll
-    for (int d = 0; d < D; ++d) acc[d] = acc[d] * alpha + pr * vrow[d];
+    for (int d = 0; d < D; ++d) acc[d] = acc[d] * alpha + pr * Elem<T>::load(vrow + d);
     m = m_new;
   }
   sm[threadIdx.x] = m;
@@ -307,7 +309,7 @@ __global__ void prefill_attention_f32_kernel(const float* __restrict__ q,
       l_all += sl[t] * wgt;
       o_all += so[t][d] * wgt;
     }
-    out[((static_cast<int64_t>(b) * tokens + qt) * q_heads + hq) * D + d] = o_all / l_all;
+    Elem<T>::store(out + ((static_cast<int64_t>(b) * tokens + qt) * q_heads + hq) * D + d, o_all / l_all);
   }
 }
 
@@ -357,7 +359,7 @@ extern "C" int b200_prefill_attention(const void* query, const void* key, const 
       q_heads % kv_heads != 0)
     return B200_ERR_BAD_ARGUMENT;
   if (mask == nullptr && !causal) return B200_ERR_BAD_ARGUMENT;
-  if (mask != nullptr && (!mask_strides || (mask_dtype != B200_F32 && mask_dtype != B200_BF16)))
+  if (mask != nullptr && (!mask_strides || (!known_dtype(mask_dtype))))
     return B200_ERR_BAD_ARGUMENT;
   if (query_strides[3] != 1 || key_strides[3] != 1 || value_strides[3] != 1)
     return B200_ERR_UNSUPPORTED;
@@ -368,28 +370,33 @@ extern "C" int b200_prefill_attention(const void* query, const void* key, const 
   const int64_t zero4[4] = {0, 0, 0, 0};
   const int64_t* ms = mask != nullptr ? mask_strides : zero4;
 
-  if (dtype == B200_F32) {
+  if (!known_dtype(dtype)) return B200_ERR_UNSUPPORTED;
+  if (dtype != B200_BF16 || (head_dim != 64 && head_dim != 128)) {
+    if (head_dim != 16 && head_dim != 32 && head_dim != 64 && head_dim != 128 && head_dim != 256)
+      return B200_ERR_UNSUPPORTED;
     if (tokens > 65535 * 64) return B200_ERR_TOO_LARGE;
     dim3 grid(static_cast<unsigned>(tokens), static_cast<unsigned>(q_heads),
               static_cast<unsigned>(batch));
-#define B200_LAUNCH_F32(DIM)                                                                     \
-  prefill_attention_f32_kernel<DIM><<<grid, 64, 0, s>>>(                                         \
-      static_cast<const float*>(query), static_cast<const float*>(key),                         \
-      static_cast<const float*>(value), mask, static_cast<float*>(output),                      \
-      static_cast<int>(q_heads), groups, static_cast<int>(tokens), query_strides[0],            \
-      query_strides[1], query_strides[2], key_strides[0], key_strides[1], key_strides[2],       \
-      value_strides[0], value_strides[1], value_strides[2], ms[0], ms[2], ms[3], mask_dtype,    \
-      causal, static_cast<float>(scale))
-    if (head_dim == 64) B200_LAUNCH_F32(64);
-    else if (head_dim == 16) B200_LAUNCH_F32(16);
-    else if (head_dim == 32) B200_LAUNCH_F32(32);
-    else if (head_dim == 128) B200_LAUNCH_F32(128);
-    else return B200_ERR_UNSUPPORTED;
-#undef B200_LAUNCH_F32
+    const bool compat = mode == B200_MODE_PYTORCH_COMPATIBLE && dtype != B200_F32;
+    with_element_type(dtype, [&](auto tag) {
+      using T = typename decltype(tag)::type;
+      auto run = [&](auto kernel) {
+        kernel<<<grid, head_dim > 128 ? 32 : 64, 0, s>>>(
+            static_cast<const T*>(query), static_cast<const T*>(key), static_cast<const T*>(value),
+            mask, static_cast<T*>(output), static_cast<int>(q_heads), groups,
+            static_cast<int>(tokens), query_strides[0], query_strides[1], query_strides[2],
+            key_strides[0], key_strides[1], key_strides[2], value_strides[0], value_strides[1],
+            value_strides[2], ms[0], ms[2], ms[3], mask_dtype, causal, static_cast<float>(scale),
+            compat);
+      };
+      if (head_dim == 16) run(prefill_attention_generic_kernel<16, T>);
+      else if (head_dim == 32) run(prefill_attention_generic_kernel<32, T>);
+      else if (head_dim == 64) run(prefill_attention_generic_kernel<64, T>);
+      else if (head_dim == 128) run(prefill_attention_generic_kernel<128, T>);
+      else run(prefill_attention_generic_kernel<256, T>);
+    });
     return launch_status();
   }
-  if (dtype != B200_BF16) return B200_ERR_UNSUPPORTED;
-  if (head_dim != 64 && head_dim != 128) return B200_ERR_UNSUPPORTED;
   if (!aligned16(query) || !aligned16(key) || !aligned16(value) ||
       (reinterpret_cast<uintptr_t>(output) & 3u) != 0)
     return B200_ERR_ALIGNMENT;

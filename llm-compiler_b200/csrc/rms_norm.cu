@@ -311,11 +311,11 @@ extern "C" int b200_rms_norm(const void* input, const void* weight, void* output
   if (rows == 0) return B200_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const float eps = static_cast<float>(epsilon);
-  if (in_dtype == B200_BF16)
-    return rms_norm_typed<__nv_bfloat16>(input, weight, output, rows, hidden, input_row_stride,
-                                         eps, round_before_weight != 0, mode, s);
-  if (in_dtype == B200_F32)
-    return rms_norm_typed<float>(input, weight, output, rows, hidden, input_row_stride, eps,
-                                 round_before_weight != 0, mode, s);
-  return B200_ERR_UNSUPPORTED;
+  int code = B200_ERR_UNSUPPORTED;
+  with_element_type(in_dtype, [&](auto tag) {
+    using T = typename decltype(tag)::type;
+    code = rms_norm_typed<T>(input, weight, output, rows, hidden, input_row_stride, eps,
+                             round_before_weight != 0, mode, s);
+  });
+  return code;
 }

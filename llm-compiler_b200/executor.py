@@ -525,8 +525,8 @@ class B200Executor:
         tensor, dtype = args[0], _DTYPES[args[1]]
         if tensor.dtype == dtype:
             return tensor
-        if tensor.dtype not in (torch.float32, torch.bfloat16) or \
-                dtype not in (torch.float32, torch.bfloat16):
+        floats = (torch.float32, torch.bfloat16, torch.float16)
+        if tensor.dtype not in floats or dtype not in floats:
             raise ExecutionError(f"no B200 kernel casts {tensor.dtype} to {dtype}")
         return kernels.b200_contiguous(tensor, dtype)
 

@@ -18,7 +18,9 @@ import torch
 
 from . import _lib
 
-_DTYPE_CODES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16}
+# (fp16 runs on the generic CUDA-core kernels: the reference's kernels accept it,
+# backends/triton_linear.py:100-105, and no benchmark configuration uses it)
+_DTYPE_CODES = {torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.float16: _lib.F16}
 _MODES = {"fast": _lib.MODE_FAST, "pytorch_compatible": _lib.MODE_PYTORCH_COMPATIBLE}
 _EPILOGUES = {"none": _lib.EPILOGUE_NONE, "residual": _lib.EPILOGUE_RESIDUAL,
               "swiglu": _lib.EPILOGUE_SWIGLU}
@@ -184,7 +186,7 @@ def _code(dtype: torch.dtype) -> int:
     try:
         return _DTYPE_CODES[dtype]
     except KeyError as error:
-        raise ValueError(f"unsupported dtype {dtype}: the B200 backend runs f32 and bf16") from error
+        raise ValueError(f"unsupported dtype {dtype}: the B200 backend runs f32, bf16 and f16") from error
 
 
 def _mode(numerical_mode: str) -> int:

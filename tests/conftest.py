@@ -34,4 +34,4 @@ def golden_ops():
 @pytest.fixture(scope="session")
 def golden_tiny():
     return {tag: torch.load(GOLDEN / f"qwen2_tiny_{tag}.pt", weights_only=False)
-            for tag in ("fp32", "bf16")}
+            for tag in ("fp32", "bf16", "fp16")}

@@ -30,7 +30,7 @@ def test_every_declared_symbol_is_exported_and_bound():
 
 def test_abi_version_and_error_strings():
     library = _lib.load()
-    assert library.b200_abi_version() == _lib.ABI_VERSION == 103
+    assert library.b200_abi_version() == _lib.ABI_VERSION == 104
     assert _lib.error_string(0) == "ok"
     for code in range(-6, 0):
         assert _lib.error_string(code) not in ("ok", "unknown error code")

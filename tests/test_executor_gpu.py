@@ -268,14 +268,17 @@ def test_dispatch_plans_are_resolved_per_call_and_recorded(golden_tiny):
 
 @pytest.mark.parametrize("mode", ["fast", "pytorch_compatible"])
 @pytest.mark.parametrize("fuse", [True, False])
-def test_bf16_graphs_match_the_reference_executor(mode, fuse, golden_tiny):
-    """The reference-compiled bf16 KernelIR of the 2-layer model through the drop-in path
+@pytest.mark.parametrize("tag", ["bf16", "fp16"])
+def test_16_bit_graphs_match_the_reference_executor(mode, fuse, tag, golden_tiny):
+    """The reference-compiled bf16 (fp16) KernelIR of the 2-layer model through the drop-in path
     (lower_to_b200 + B200Executor) against what the reference's CPU executor produced for the
-    same bf16 weights (qwen2_tiny_bf16.pt): real casts, the bf16 RoPE table inside a graph, the
-    bf16 residual epilogues, packed projections and both numerical modes."""
-    gold = golden_tiny["bf16"]
+    same weights (qwen2_tiny_bf16.pt, qwen2_tiny_fp16.pt): real casts, the 16-bit RoPE table
+    inside a graph, the residual epilogues, packed projections and both numerical modes. bf16
+    runs on the tensor-core kernels, fp16 on the generic ones."""
+    gold = golden_tiny[tag]
+    dtype, tolerance = (torch.bfloat16, 2e-2) if tag == "bf16" else (torch.float16, 1e-2)
     config = q2.Qwen2Config(**gold["config"])
-    weights = {k: v.cuda() for k, v in q2.make_weights(config, seed=0, dtype=torch.bfloat16).items()}
+    weights = {k: v.cuda() for k, v in q2.make_weights(config, seed=0, dtype=dtype).items()}
     inv_freq = q2.inverse_frequency(config, "cuda")
     batch, prompt = gold["batch"], gold["prompt"]
     executor = B200Executor(strict=True)
@@ -283,16 +286,16 @@ def test_bf16_graphs_match_the_reference_executor(mode, fuse, golden_tiny):
 
     def check(actual, expected):
         scale = max(1.0, float(expected.float().abs().max()))
-        assert float((actual.float().cpu() - expected.float()).abs().max()) <= 2e-2 * scale
+        assert float((actual.float().cpu() - expected.float()).abs().max()) <= tolerance * scale
 
-    prefill = lowered("prefill", mode, "bf16", **options)
+    prefill = lowered("prefill", mode, tag, **options)
     result = executor.run(prefill, bind_arguments(prefill.functions[0], weights, {
         "input_ids": gold["input_ids"].cuda(), "attention_mask": causal_mask(batch, prompt),
         "position_ids": torch.arange(prompt).repeat(batch, 1).cuda(), "inv_freq": inv_freq}))
     logits, state = result.outputs
-    assert logits.dtype == torch.bfloat16
+    assert logits.dtype == dtype
     check(logits, gold["prefill_logits"])
-    decode = lowered("decode", mode, "bf16", **options)
+    decode = lowered("decode", mode, tag, **options)
     for step in range(gold["steps"]):
         length = prompt + step
         logits, state = executor.run(decode, bind_arguments(decode.functions[0], weights, {

@@ -108,13 +108,13 @@ def test_linear(name, golden_ops):
     same(serve_ops.linear(x["input"], x["weight"], x["bias"]), golden_ops[name]["output"])
 
 
-@pytest.mark.parametrize("tag", ["fp32", "bf16"])
+@pytest.mark.parametrize("tag", ["fp32", "bf16", "fp16"])
 def test_qwen2_tiny_stateful_decode(tag, golden_tiny):
     """Config 1 of the benchmark plan: 2-layer Qwen2, batch 3, prompt 5, capacity 64, 4 greedy
     steps; the oracle model must match the reference executor's logits, tokens and KV state."""
 
     gold = golden_tiny[tag]
-    dtype = torch.float32 if tag == "fp32" else torch.bfloat16
+    dtype = {"fp32": torch.float32, "bf16": torch.bfloat16, "fp16": torch.float16}[tag]
     config = q2.Qwen2Config(**gold["config"])
     weights = q2.make_weights(config, seed=gold["seed"], dtype=dtype)
     same(q2.make_prompt_ids(config, gold["batch"], gold["prompt"], seed=0), gold["input_ids"])
