@@ -166,6 +166,8 @@ int b200_rms_norm(const void* input, const void* weight, void* output, int64_t r
  *  output  B x Hq x D contiguous (viewed by the caller as B x Hq x 1 x D)
  *  split_tokens  tokens per split (0 = library default); max_length_hint: an upper
  *                bound on lengths[] known to the host (0 = mask_len / capacity).
+ * bf16 with head_dim 64 / 128 runs the tensor-core kernel; fp32, fp16 and head_dim 16 / 32 /
+ * 256 (any dtype) a generic one without scratch.
  * Workspace: b200_decode_attention_workspace_bytes(...) bytes, 256-byte aligned. */
 int64_t b200_decode_attention_workspace_bytes(int64_t batch, int64_t q_heads, int64_t kv_heads,
                                               int64_t head_dim, int64_t max_length,
@@ -274,8 +276,8 @@ int b200_paged_qkv_decode_attention(
  * and a workspace of b200_prefill_attention_workspace_bytes(batch, tokens) is given; a pre-pass
  * then classifies the mask's 128 x 128 tiles (all zero / all -inf / mixed) so that tiles that
  * are all -inf at either end of a row block are never touched and all-zero tiles read no mask.
- * Other masked calls, the pytorch_compatible mode and fp32 use the warp-level and CUDA-core
- * kernels (workspace may be NULL). status (may be NULL) receives B200_STATUS_WAIT_TIMEOUT. */
+ * Other masked calls and the pytorch_compatible mode use the warp-level kernel; fp32, fp16 and
+ * head_dim 16 / 32 / 256 (any dtype) a generic CUDA-core kernel (workspace may be NULL). status (may be NULL) receives B200_STATUS_WAIT_TIMEOUT. */
 int64_t b200_prefill_attention_workspace_bytes(int64_t batch, int64_t tokens);
 int b200_prefill_attention(const void* query, const void* key, const void* value,
                            const void* mask, void* output, int64_t batch, int64_t q_heads,
@@ -298,8 +300,8 @@ int b200_prefill_attention(const void* query, const void* key, const void* value
  * bf16 problems run on tcgen05 tensor cores (TMEM accumulator, TMA-fed stage ring): 64-row
  * activation boxes and a tile width chosen at run time at decode sizes, 128 x 64..256 tiles
  * beyond, a persistent two-accumulator kernel from 1024 rows on. Decode-size calls with too
- * few N tiles to fill the GPU, operands no tensor map can describe and fp32 run on warp-level /
- * CUDA-core kernels with deterministic split-K. Workspace (split-K partial sums + tile counters):
+ * few N tiles to fill the GPU and operands no tensor map can describe run on the warp-level
+ * kernel with deterministic split-K, fp32 and fp16 on a generic CUDA-core kernel. Workspace (split-K partial sums + tile counters):
  * b200_linear_workspace_bytes. `status` receives B200_STATUS_WAIT_TIMEOUT if a bounded
  * in-kernel wait gives up. */
 #define B200_EPILOGUE_NONE 0

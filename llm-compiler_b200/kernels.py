@@ -1286,7 +1286,7 @@ def b200_add(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
 
 def b200_contiguous(tensor: torch.Tensor, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """aten.contiguous.default / a real aten.to.dtype: dense copy of a (<= 4-D) strided view,
-    optionally converting between f32 and bf16."""
+    optionally converting between f32, bf16 and f16."""
 
     device = _require_cuda(tensor)
     dtype = dtype or tensor.dtype

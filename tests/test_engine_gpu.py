@@ -1,8 +1,8 @@
 """Whole-model parity of the serving engine (CUDA-graph decode) against the reference.
 
-qwen2_tiny_{fp32,bf16}.pt hold what the reference's own ReferenceExecutor produced for the
+qwen2_tiny_{fp32,bf16,fp16}.pt hold what the reference's own ReferenceExecutor produced for the
 2-layer stateful decode (batch 3, prompt 5, capacity 64, 4 greedy steps). Tolerances: fp32
-graphs 1e-4 on logits; bf16 graphs 2e-2 with greedy tokens equal (a token may differ only
+graphs 1e-4 on logits; bf16 graphs 2e-2 (fp16: 1e-2) with greedy tokens equal (a token may differ only
 where the reference's own top-2 logits are closer than the tolerance).
 """
 
@@ -38,11 +38,12 @@ def assert_tokens(actual, expected, expected_logits, tol):
 
 
 @pytest.mark.parametrize("tag,mode", [("fp32", "fast"), ("fp32", "pytorch_compatible"),
-                                      ("bf16", "fast"), ("bf16", "pytorch_compatible")])
+                                      ("bf16", "fast"), ("bf16", "pytorch_compatible"),
+                                      ("fp16", "fast"), ("fp16", "pytorch_compatible")])
 def test_tiny_stateful_decode_matches_reference(tag, mode, golden_tiny):
     gold = golden_tiny[tag]
-    dtype = torch.float32 if tag == "fp32" else torch.bfloat16
-    tol = 1e-4 if tag == "fp32" else 2e-2
+    dtype, tol = {"fp32": (torch.float32, 1e-4), "bf16": (torch.bfloat16, 2e-2),
+                  "fp16": (torch.float16, 1e-2)}[tag]
     config = q2.Qwen2Config(**gold["config"])
     engine = Qwen2Engine(config, cuda_weights(config, dtype), batch=gold["batch"],
                          capacity=gold["capacity"], numerical_mode=mode)
