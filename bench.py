@@ -325,15 +325,24 @@ def attention_roofline(engine, lengths_sum, rounds):
                 split_tokens=engine.split_tokens, max_length_hint=engine.max_length_hint,
                 output=outputs)
 
-    stream = torch.cuda.Stream()
-    stream.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(stream):
-        launches()
-    torch.cuda.current_stream().wait_stream(stream)
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        launches()
+    # The step launches the fused form of this kernel, which (head_dim 64) serves a CTA's tokens
+    # with 16 warps where the plain operator uses 8: time the plain operator in the step's shape.
+    forced = os.environ.get("B200_DECODE_ATTENTION_WARPS")
+    if forced is None and getattr(engine, "attention_is_fused", False) and config.head_dim == 64:
+        os.environ["B200_DECODE_ATTENTION_WARPS"] = "16"
+    try:
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            launches()
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            launches()
+    finally:
+        if forced is None:
+            os.environ.pop("B200_DECODE_ATTENTION_WARPS", None)
     for _ in range(3):
         graph.replay()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

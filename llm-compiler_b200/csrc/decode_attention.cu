@@ -1107,6 +1107,19 @@ bool wide_cta_enabled() {
   return value == nullptr || strcmp(value, "4") != 0;
 }
 
+// Head_dim 64, TMA, fast mode: the token range of an 8-warp CTA can be served by 16 warps on
+// 16-token sub-tiles (the same 196 KB of rings). The fused form does so: its prologue (q|k|v
+// reduction, RoPE, KV store) and its merge are spread over 512 threads, and the decode step of
+// 64 sequences x 4096 tokens measured 1.289 against 1.302 ms, 32 sequences 1.056 against 1.069.
+// The plain form keeps 8 warps (alone, 64 x 4096: 24.4 against 24.8 us; ragged 64 x 4096: 17.8
+// against 19.5). B200_DECODE_ATTENTION_WARPS=16 / 8 forces either for both forms.
+bool sixteen_warps(bool fused) {
+  const char* value = getenv("B200_DECODE_ATTENTION_WARPS");
+  if (value != nullptr && strcmp(value, "16") == 0) return true;
+  if (value != nullptr && strcmp(value, "8") == 0) return false;
+  return fused;
+}
+
 // The splits of a pair merge through distributed shared memory when they fit one portable
 // cluster and the whole grid is resident at once: that is the latency-bound regime the cluster
 // merge is for. Larger grids measured slower as clusters (batch 256 x 4096: 86 vs 60 us),
@@ -1135,10 +1148,9 @@ GridPlan plan_grid(int64_t splits, int64_t split_tokens, int64_t batch, int64_t 
   return plan;
 }
 
-template <int D, bool WIDE, bool FAST, bool TMA, int WARPS, bool FUSED>
+template <int D, bool WIDE, bool FAST, bool TMA, int WARPS, bool FUSED, int TOK = tokens_per_step<D>()>
 int launch_grid(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap,
                 bool cluster, cudaStream_t stream) {
-  constexpr int TOK = tokens_per_step<D>();
   constexpr int smem = WARPS * kStages * 2 * TOK * D * 2;
   const int row_blocks = (p.groups + 15) / 16;
   dim3 grid(p.num_splits, p.kv_heads * row_blocks, p.batch);
@@ -1165,6 +1177,10 @@ int launch_variant(const DecodeParams& p, const CUtensorMap& kmap, const CUtenso
     q.ws_ml = q.ws_o + static_cast<int64_t>(p.batch) * p.q_heads * plan.splits * D;
   if (plan.warps == kWarps)
     return launch_grid<D, WIDE, FAST, TMA, kWarps, FUSED>(q, kmap, vmap, plan.cluster, stream);
+  if constexpr (D == 64 && TMA && FAST) {
+    if (sixteen_warps(FUSED))  // (the caller built the tensor maps with 16-token boxes)
+      return launch_grid<D, WIDE, FAST, TMA, 4 * kWarps, FUSED, 16>(q, kmap, vmap, plan.cluster, stream);
+  }
   return launch_grid<D, WIDE, FAST, TMA, 2 * kWarps, FUSED>(q, kmap, vmap, plan.cluster, stream);
 }
 
@@ -1190,12 +1206,16 @@ int launch_bf16(const DecodeParams& p, cudaStream_t stream, int flat_grid = 0) {
   memset(&kmap, 0, sizeof(kmap));
   memset(&vmap, 0, sizeof(vmap));
   bool tma = use_tma_loads();
+  int box_tokens = tokens_per_step<D>();
+  if (D == 64 && tma && fast && flat_grid == 0 && sixteen_warps(p.qkv_partials != nullptr) &&
+      plan_grid(p.num_splits, p.split_tokens, p.batch, p.kv_heads * ((p.groups + 15) / 16)).warps == 2 * kWarps)
+    box_tokens = 16;
   if (tma)
     tma = p.block_table != nullptr
-              ? make_kv_tensor_map(&kmap, p.kbuf, 1, p.pool_rows, p.kv_heads, D, tokens_per_step<D>()) &&
-                    make_kv_tensor_map(&vmap, p.vbuf, 1, p.pool_rows, p.kv_heads, D, tokens_per_step<D>())
-              : make_kv_tensor_map(&kmap, p.kbuf, p.batch, p.capacity, p.kv_heads, D, tokens_per_step<D>()) &&
-                    make_kv_tensor_map(&vmap, p.vbuf, p.batch, p.capacity, p.kv_heads, D, tokens_per_step<D>());
+              ? make_kv_tensor_map(&kmap, p.kbuf, 1, p.pool_rows, p.kv_heads, D, box_tokens) &&
+                    make_kv_tensor_map(&vmap, p.vbuf, 1, p.pool_rows, p.kv_heads, D, box_tokens)
+              : make_kv_tensor_map(&kmap, p.kbuf, p.batch, p.capacity, p.kv_heads, D, box_tokens) &&
+                    make_kv_tensor_map(&vmap, p.vbuf, p.batch, p.capacity, p.kv_heads, D, box_tokens);
   int code;
   if (p.qkv_partials != nullptr) {
     // the fused form (q|k|v reduction, RoPE and KV store in front of the streaming) is its own

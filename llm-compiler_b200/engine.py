@@ -262,10 +262,21 @@ class Qwen2Engine:
             self._block_slack -= 1
 
     # ------------------------------------------------------------------- decode ----
-    def _decode_step(self) -> None:
+    @property
+    def chained(self) -> bool:
+        """Whether a decode step runs the launch chain (fast bf16, up to 128 sequences)."""
         # (the paged layout has the folded five-launch chain and the separate kernels)
-        if self.dtype == torch.bfloat16 and self.mode == "fast" and self.batch <= 128 and \
-                (not self.paged or self.folded_norms):
+        return self.dtype == torch.bfloat16 and self.mode == "fast" and self.batch <= 128 and \
+            (not self.paged or self.folded_norms)
+
+    @property
+    def attention_is_fused(self) -> bool:
+        """Whether the step's attention launches are the fused form (q|k|v reduction, RoPE and
+        KV store inside), which serves a CTA's tokens with 16 warps at head_dim 64."""
+        return self.chained and self.fused_qkv_attention
+
+    def _decode_step(self) -> None:
+        if self.chained:
             self._decode_step_chain()
         else:
             self._decode_step_separate()
@@ -273,7 +284,8 @@ class Qwen2Engine:
     def _decode_step_chain(self) -> None:
         """Fast bf16 decode step: every small projection is a split-K partial-sum producer on
         the tcgen05 kernel and the reduction rides in the next operator (bias + RoPE + KV store
-        after q|k|v; residual + RMSNorm after o and down). 8 launches per layer."""
+        after q|k|v; residual + RMSNorm after o and down; with folded norms and cluster split-K
+        five launches per layer, otherwise seven)."""
 
         # The weights are written once, when the engine is built. Lengths move at the end of a
         # step (advance_lengths, a fully serialised launch) and the only KV row a step writes
