@@ -28,7 +28,9 @@ def pytest_collection_modifyitems(config, items):
 
 @pytest.fixture(scope="session")
 def golden_ops():
-    return torch.load(GOLDEN / "ops.pt", weights_only=False)
+    """Per-operator outputs of the reference: ops.pt (fp32, bf16) and ops_fp16.pt."""
+    return {**torch.load(GOLDEN / "ops.pt", weights_only=False),
+            **torch.load(GOLDEN / "ops_fp16.pt", weights_only=False)}
 
 
 @pytest.fixture(scope="session")

@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import torch
 
-F32, BF16 = torch.float32, torch.bfloat16
+F32, BF16, F16 = torch.float32, torch.bfloat16, torch.float16
 
 
 def _randn(generator, *shape, dtype=F32):
@@ -79,9 +79,39 @@ ROPE_TABLE = {  # name: (B, T, head_dim, theta, dtype, first position)
     "rope_table_f32": (3, 1, 64, 1e4, F32, 5),
 }
 
+# fp16 cases (outputs in ops_fp16.pt): the reference's kernels take fp16 next to bf16
+# (backends/triton_linear.py:100-105); same shapes and seeds as the bf16 cases above.
+KV_STORE_F16 = {"kv_store_f16_strided": (2, 40, 2, 64, 5, F16, [0, 33])}
+ROPE_F16 = {
+    "rope_f16": (2, 14, 2, 7, 64, F16, 2026, 1e6, 3),
+    "rope_f16_decode": (5, 14, 2, 1, 64, F16, 7, 1e6, 4095),
+}
+RMS_NORM_F16 = {
+    "rms_norm_f16_rbw": (7, 896, F16, True),
+    "rms_norm_f16": (7, 896, F16, False),
+}
+DECODE_ATTENTION_F16 = {
+    "decode_attention_f16": (3, 300, 14, 2, 64, F16, [1, 130, 300]),
+    "decode_attention_f16_d128": (2, 260, 28, 4, 128, F16, [260, 17]),
+}
+PREFILL_ATTENTION_F16 = {
+    "prefill_attention_f16": (2, 7, 14, 2, 64, F16, False),
+    "prefill_attention_f16_130": (1, 130, 14, 2, 64, F16, False),
+    "prefill_attention_f16_zero_mask": (2, 70, 14, 2, 64, F16, True),
+}
+LINEAR_F16 = {
+    "linear_f16_bias": (2, 5, 896, 128, True, F16),
+    "linear_f16": (1, 8, 512, 384, False, F16),
+}
+ROPE_TABLE_F16 = {"rope_table_f16": (2, 9, 64, 1e6, F16, 0)}
+
+
+def _case(table, table_f16, name):
+    return table[name] if name in table else table_f16[name]
+
 
 def kv_store_inputs(name):
-    b, c, h, d, t, dtype, pos = KV_STORE[name]
+    b, c, h, d, t, dtype, pos = _case(KV_STORE, KV_STORE_F16, name)
     g = torch.Generator().manual_seed(11 + c)
     return dict(key_buffer=_randn(g, b, c, h, d, dtype=dtype),
                 value_buffer=_randn(g, b, c, h, d, dtype=dtype),
@@ -91,7 +121,7 @@ def kv_store_inputs(name):
 
 
 def rope_inputs(name):
-    b, hq, hkv, t, d, dtype, seed, theta, first = ROPE[name]
+    b, hq, hkv, t, d, dtype, seed, theta, first = _case(ROPE, ROPE_F16, name)
     g = torch.Generator().manual_seed(seed)
     return dict(query=_randn(g, b, t, hq, d, dtype=dtype).transpose(1, 2),
                 key=_randn(g, b, t, hkv, d, dtype=dtype).transpose(1, 2),
@@ -100,7 +130,7 @@ def rope_inputs(name):
 
 
 def rms_norm_inputs(name):
-    rows, hidden, dtype, rbw = RMS_NORM[name]
+    rows, hidden, dtype, rbw = _case(RMS_NORM, RMS_NORM_F16, name)
     g = torch.Generator().manual_seed(hidden + rows)
     return dict(input=_randn(g, rows, hidden, dtype=dtype),
                 weight=(1.0 + 0.1 * torch.randn(hidden, generator=g)).to(dtype),
@@ -108,7 +138,7 @@ def rms_norm_inputs(name):
 
 
 def decode_attention_inputs(name):
-    b, c, hq, hkv, d, dtype, lens = DECODE_ATTENTION[name]
+    b, c, hq, hkv, d, dtype, lens = _case(DECODE_ATTENTION, DECODE_ATTENTION_F16, name)
     g = torch.Generator().manual_seed(c * 7 + d)
     return dict(query=_randn(g, b, 1, hq, d, dtype=dtype).transpose(1, 2),
                 key_buffer=_randn(g, b, c, hkv, d, dtype=dtype),
@@ -118,7 +148,7 @@ def decode_attention_inputs(name):
 
 
 def prefill_attention_inputs(name):
-    b, t, hq, hkv, d, dtype, zero_mask = PREFILL_ATTENTION[name]
+    b, t, hq, hkv, d, dtype, zero_mask = _case(PREFILL_ATTENTION, PREFILL_ATTENTION_F16, name)
     g = torch.Generator().manual_seed(2026 + t)
     return dict(query=_randn(g, b, t, hq, d, dtype=dtype).transpose(1, 2),
                 key=_randn(g, b, t, hkv, d, dtype=dtype).transpose(1, 2),
@@ -128,7 +158,7 @@ def prefill_attention_inputs(name):
 
 
 def linear_inputs(name):
-    b, t, k, n, bias, dtype = LINEAR[name]
+    b, t, k, n, bias, dtype = _case(LINEAR, LINEAR_F16, name)
     g = torch.Generator().manual_seed(k + n)
     return dict(input=_randn(g, b, t, k, dtype=dtype),
                 weight=(0.05 * torch.randn(n, k, generator=g)).to(dtype),
@@ -136,6 +166,6 @@ def linear_inputs(name):
 
 
 def rope_table_inputs(name):
-    b, t, d, theta, dtype, first = ROPE_TABLE[name]
+    b, t, d, theta, dtype, first = _case(ROPE_TABLE, ROPE_TABLE_F16, name)
     return dict(position_ids=(torch.arange(t, dtype=torch.int64).view(1, -1).expand(b, -1) + first * (1 + torch.arange(b).view(-1, 1))).contiguous(),
                 head_dim=d, theta=theta, dtype=dtype)

@@ -5,12 +5,14 @@ The reference's Triton kernels accept fp16 next to bf16 and fp32
 configuration uses either. Here both run on the generic CUDA-core kernels (fp32 arithmetic,
 the 16-bit type rounded where the reference rounds), so the bar is the reference's own fp16
 tolerance band (tests/test_linear.py:165-180: 2e-3 ... 3e-2): 4e-3 of the output scale;
-copies are bit-exact.
+copies are bit-exact. The last block compares with the reference's own fp16 outputs
+(tests/golden/ops_fp16.pt), to which the oracle is pinned bit for bit.
 """
 
 import pytest
 import torch
 
+import cases
 from oracle import serve_ops
 import llm_compiler_b200 as b200
 from llm_compiler_b200 import kernels
@@ -206,3 +208,62 @@ def test_head_sizes_beside_64_and_128(d, dtype):
     close(b200.b200_prefill_attention(qp.cuda(), kp.cuda(), vp.cuda(), serve_ops.causal_mask(b, t).cuda(),
                                       scale=d ** -0.5), ref, tol)
     kernels.runtime().check_status()
+
+
+# ------------------------------- the reference's own fp16 outputs (tests/golden/ops_fp16.pt) ----
+@pytest.mark.parametrize("name", list(cases.KV_STORE_F16))
+def test_fp16_kv_store_golden(name, golden_ops):
+    x = cases.kv_store_inputs(name)
+    kbuf, vbuf = x["key_buffer"].cuda(), x["value_buffer"].cuda()
+    b200.b200_kv_store(kbuf, vbuf, x["key"].cuda(), x["value"].cuda(), x["positions"].cuda())
+    exact(kbuf, golden_ops[name]["key_out"])
+    exact(vbuf, golden_ops[name]["value_out"])
+
+
+@pytest.mark.parametrize("name", list(cases.ROPE_F16))
+def test_fp16_rope_golden(name, golden_ops):
+    x, gold = cases.rope_inputs(name), golden_ops[name]
+    q, k = b200.b200_rope(x["query"].cuda(), x["key"].cuda(), gold["cosine"].cuda(), gold["sine"].cuda())
+    close(q, gold["query_out"], 1e-3)
+    close(k, gold["key_out"], 1e-3)
+
+
+@pytest.mark.parametrize("mode", ["fast", "pytorch_compatible"])
+@pytest.mark.parametrize("name", list(cases.RMS_NORM_F16))
+def test_fp16_rms_norm_golden(name, mode, golden_ops):
+    x = cases.rms_norm_inputs(name)
+    out = b200.b200_rms_norm(x["input"].cuda(), x["weight"].cuda(), epsilon=x["epsilon"],
+                             round_before_weight=x["round_before_weight"], numerical_mode=mode)
+    close(out, golden_ops[name]["output"], 2e-3)
+
+
+@pytest.mark.parametrize("name", list(cases.DECODE_ATTENTION_F16))
+def test_fp16_decode_attention_golden(name, golden_ops):
+    x = cases.decode_attention_inputs(name)
+    out = b200.b200_decode_attention(x["query"].cuda(), x["key_buffer"].cuda(), x["value_buffer"].cuda(),
+                                     x["lengths"].cuda(), x["mask"].cuda(), scale=x["scale"])
+    close(out, golden_ops[name]["output"], F16_TOL)
+
+
+@pytest.mark.parametrize("name", list(cases.PREFILL_ATTENTION_F16))
+def test_fp16_prefill_attention_golden(name, golden_ops):
+    x = cases.prefill_attention_inputs(name)
+    out = b200.b200_prefill_attention(x["query"].cuda(), x["key"].cuda(), x["value"].cuda(), x["mask"].cuda(),
+                                      scale=x["scale"])
+    close(out, golden_ops[name]["output"], F16_TOL)
+
+
+@pytest.mark.parametrize("name", list(cases.LINEAR_F16))
+def test_fp16_linear_golden(name, golden_ops):
+    x = cases.linear_inputs(name)
+    bias = x["bias"].cuda() if x["bias"] is not None else None
+    close(b200.b200_linear(x["input"].cuda(), x["weight"].cuda(), bias), golden_ops[name]["output"], F16_TOL)
+
+
+@pytest.mark.parametrize("name", list(cases.ROPE_TABLE_F16))
+def test_fp16_rope_table_golden(name, golden_ops):
+    x = cases.rope_table_inputs(name)
+    inv_freq = serve_ops.rope_inverse_frequency(x["head_dim"], x["theta"])
+    cos, sin = b200.b200_rope_table(x["position_ids"].cuda(), inv_freq.cuda(), torch.float16)
+    close(cos, golden_ops[name]["cosine"], 1e-3)
+    close(sin, golden_ops[name]["sine"], 1e-3)

@@ -1,6 +1,6 @@
 """The CPU oracle against the reference's own outputs (tests/golden), atol = 0.
 
-ops.pt and qwen2_tiny_*.pt were produced by the reference's ReferenceExecutor; every oracle
+ops.pt, ops_fp16.pt and qwen2_tiny_*.pt were produced by the reference's ReferenceExecutor; every oracle
 function must reproduce them exactly on the seeded inputs of tests/golden/cases.py.
 """
 
@@ -17,7 +17,7 @@ def same(a, b):
     torch.testing.assert_close(a, b, rtol=0, atol=0, equal_nan=True)
 
 
-@pytest.mark.parametrize("name", list(cases.KV_STORE))
+@pytest.mark.parametrize("name", list(cases.KV_STORE) + list(cases.KV_STORE_F16))
 def test_kv_store(name, golden_ops):
     x = cases.kv_store_inputs(name)
     kbuf, vbuf = x["key_buffer"].clone(), x["value_buffer"].clone()
@@ -33,7 +33,7 @@ def test_kv_store_overflow_raises():
                            torch.tensor([1, 5, 16]))
 
 
-@pytest.mark.parametrize("name", list(cases.ROPE))
+@pytest.mark.parametrize("name", list(cases.ROPE) + list(cases.ROPE_F16))
 def test_rope(name, golden_ops):
     x = cases.rope_inputs(name)
     inv_freq = serve_ops.rope_inverse_frequency(x["head_dim"], x["theta"])
@@ -45,7 +45,7 @@ def test_rope(name, golden_ops):
     same(k, golden_ops[name]["key_out"])
 
 
-@pytest.mark.parametrize("name", list(cases.ROPE_TABLE))
+@pytest.mark.parametrize("name", list(cases.ROPE_TABLE) + list(cases.ROPE_TABLE_F16))
 def test_rope_table(name, golden_ops):
     x = cases.rope_table_inputs(name)
     inv_freq = serve_ops.rope_inverse_frequency(x["head_dim"], x["theta"])
@@ -54,7 +54,7 @@ def test_rope_table(name, golden_ops):
     same(sin, golden_ops[name]["sine"])
 
 
-@pytest.mark.parametrize("name", list(cases.RMS_NORM))
+@pytest.mark.parametrize("name", list(cases.RMS_NORM) + list(cases.RMS_NORM_F16))
 def test_rms_norm(name, golden_ops):
     x = cases.rms_norm_inputs(name)
     kwargs = dict(round_before_weight=x["round_before_weight"])
@@ -73,7 +73,7 @@ def test_float_sum_order(count):
     assert np.float32(row.sum().item()) == serve_ops.float_sum_explicit(row.numpy())
 
 
-@pytest.mark.parametrize("name", list(cases.DECODE_ATTENTION))
+@pytest.mark.parametrize("name", list(cases.DECODE_ATTENTION) + list(cases.DECODE_ATTENTION_F16))
 def test_decode_attention(name, golden_ops):
     x = cases.decode_attention_inputs(name)
     out = serve_ops.decode_attention(x["query"], x["key_buffer"], x["value_buffer"], x["lengths"],
@@ -89,7 +89,7 @@ def test_decode_attention_empty_sequence_is_nan():
     assert torch.isnan(out[0]).all() and not torch.isnan(out[1:]).any()
 
 
-@pytest.mark.parametrize("name", list(cases.PREFILL_ATTENTION))
+@pytest.mark.parametrize("name", list(cases.PREFILL_ATTENTION) + list(cases.PREFILL_ATTENTION_F16))
 def test_prefill_attention(name, golden_ops):
     x = cases.prefill_attention_inputs(name)
     out = serve_ops.prefill_attention(x["query"], x["key"], x["value"], x["mask"],
@@ -102,7 +102,7 @@ def test_prefill_attention(name, golden_ops):
              golden_ops[name]["output"])
 
 
-@pytest.mark.parametrize("name", list(cases.LINEAR))
+@pytest.mark.parametrize("name", list(cases.LINEAR) + list(cases.LINEAR_F16))
 def test_linear(name, golden_ops):
     x = cases.linear_inputs(name)
     same(serve_ops.linear(x["input"], x["weight"], x["bias"]), golden_ops[name]["output"])
